@@ -1,0 +1,131 @@
+// Command-line driver for the C++ plugin surface: builds a CPU-side index holder,
+// converts it with duckdb::GetGpuBackend().CpuToGpu(), searches the way
+// FaissIndex::Search does (src/faiss_index.cpp:708-762: one query per call, labels
+// -1 skipped) and as one batch, converts back with GpuToCpu() and checks that the
+// rows survived bit for bit.  The GPU tests run it and compare its output file with
+// the CPU oracle.
+//
+//   backend_driver info
+//   backend_driver flat|ivf <in.bin> <out.bin>
+// in.bin : int64 {d, n, nq, k, metric, nlist, nprobe}, float xb[n*d], float xq[nq*d],
+//          for ivf: float centroids[nlist*d], int64 assign[n]
+// out.bin: float D_batch[nq*k], int64 I_batch[nq*k], float D_single[nq*k], int64 I_single[nq*k]
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <vector>
+
+#ifndef FAISS_AVAILABLE
+#define FAISS_AVAILABLE
+#endif
+#include "gpu_backend.hpp"
+#include "gpu_backend_cuda.hpp"
+
+template <class T>
+static bool read_vec(FILE *f, std::vector<T> &v, size_t n) {
+    v.resize(n);
+    return n == 0 || fread(v.data(), sizeof(T), n, f) == n;
+}
+
+int main(int argc, char **argv) {
+    try {
+        duckdb::GpuBackend &backend = duckdb::GetGpuBackend();
+        if (argc >= 2 && strcmp(argv[1], "info") == 0) {
+            printf("{\"available\": %s, \"backend\": \"%s\", \"device\": \"%s\"}\n", backend.IsAvailable() ? "true" : "false",
+                   backend.BackendName().c_str(), backend.DeviceInfo().c_str());
+            return 0;
+        }
+        if (argc < 4) {
+            fprintf(stderr, "usage: %s info | flat|ivf in.bin out.bin\n", argv[0]);
+            return 2;
+        }
+        const bool ivf = strcmp(argv[1], "ivf") == 0;
+        FILE *f = fopen(argv[2], "rb");
+        if (!f) return 2;
+        int64_t h[7];
+        if (fread(h, 8, 7, f) != 7) return 2;
+        const int64_t d = h[0], n = h[1], nq = h[2], k = h[3], nlist = h[5], nprobe = h[6];
+        const faiss::MetricType metric = h[4] == 1 ? faiss::METRIC_L2 : faiss::METRIC_INNER_PRODUCT;
+        std::vector<float> xb, xq, cent;
+        std::vector<int64_t> assign;
+        if (!read_vec(f, xb, (size_t)(n * d)) || !read_vec(f, xq, (size_t)(nq * d))) return 2;
+        if (ivf && (!read_vec(f, cent, (size_t)(nlist * d)) || !read_vec(f, assign, (size_t)n))) return 2;
+        fclose(f);
+
+        std::unique_ptr<faiss::Index> cpu;
+        if (!ivf) {
+            auto *flat = new faiss::IndexFlat(d, metric);
+            flat->add(n, xb.data());
+            cpu.reset(flat);
+        } else {
+            auto *quantizer = new faiss::IndexFlat(d, metric);
+            quantizer->add(nlist, cent.data());
+            auto *idx = new faiss::IndexIVFFlat(quantizer, (size_t)d, (size_t)nlist, metric);
+            idx->own_fields = true;
+            idx->nprobe = (size_t)nprobe;
+            for (int64_t i = 0; i < n; i++)
+                idx->invlists->add_entries((size_t)assign[i], 1, &i, reinterpret_cast<const uint8_t *>(xb.data() + i * d));
+            idx->ntotal = n;
+            cpu.reset(idx);
+        }
+        std::unique_ptr<faiss::Index> gpu = backend.CpuToGpu(cpu.get());
+        if (gpu->ntotal != n || gpu->d != d) {
+            fprintf(stderr, "converted index has ntotal=%lld d=%d\n", (long long)gpu->ntotal, gpu->d);
+            return 1;
+        }
+        std::vector<float> D((size_t)(nq * k)), D1((size_t)(nq * k));
+        std::vector<int64_t> I((size_t)(nq * k)), I1((size_t)(nq * k));
+        gpu->search(nq, xq.data(), k, D.data(), I.data());
+        for (int64_t q = 0; q < nq; q++) gpu->search(1, xq.data() + q * d, k, D1.data() + q * k, I1.data() + q * k);
+
+        // round trip: every row comes back bit for bit
+        std::unique_ptr<faiss::Index> back = backend.GpuToCpu(gpu.get());
+        int roundtrip_ok = back->ntotal == n;
+        if (!ivf) {
+            auto *bf = dynamic_cast<faiss::IndexFlat *>(back.get());
+            roundtrip_ok = roundtrip_ok && bf && memcmp(bf->get_xb(), xb.data(), xb.size() * 4) == 0;
+            std::vector<float> one((size_t)d);
+            if (n > 0) {
+                gpu->reconstruct(n - 1, one.data());
+                roundtrip_ok = roundtrip_ok && memcmp(one.data(), xb.data() + (n - 1) * d, (size_t)d * 4) == 0;
+            }
+        } else {
+            auto *bi = dynamic_cast<faiss::IndexIVFFlat *>(back.get());
+            roundtrip_ok = roundtrip_ok && bi && bi->nprobe == (size_t)nprobe;
+            auto *ci = dynamic_cast<faiss::IndexIVFFlat *>(cpu.get());
+            for (size_t l = 0; roundtrip_ok && l < (size_t)nlist; l++) {
+                const size_t sz = ci->invlists->list_size(l);
+                roundtrip_ok = bi->invlists->list_size(l) == sz &&
+                               (sz == 0 || (memcmp(bi->invlists->get_ids(l), ci->invlists->get_ids(l), sz * 8) == 0 &&
+                                            memcmp(bi->invlists->get_codes(l), ci->invlists->get_codes(l), sz * d * 4) == 0));
+            }
+        }
+        // unsupported type -> std::runtime_error (gpu_backend_metal.mm:58-59)
+        int rejects_unknown = 0;
+        struct Other : faiss::Index {
+            void add(faiss::idx_t, const float *) override {}
+            void search(faiss::idx_t, const float *, faiss::idx_t, float *, faiss::idx_t *,
+                        const faiss::SearchParameters *) const override {}
+            void reset() override {}
+        } other;
+        try {
+            backend.CpuToGpu(&other);
+        } catch (const std::runtime_error &) {
+            rejects_unknown = 1;
+        }
+        FILE *o = fopen(argv[3], "wb");
+        if (!o) return 2;
+        fwrite(D.data(), 4, D.size(), o);
+        fwrite(I.data(), 8, I.size(), o);
+        fwrite(D1.data(), 4, D1.size(), o);
+        fwrite(I1.data(), 8, I1.size(), o);
+        fclose(o);
+        printf("{\"backend\": \"%s\", \"roundtrip_ok\": %d, \"rejects_unknown\": %d}\n", backend.BackendName().c_str(),
+               roundtrip_ok, rejects_unknown);
+        return 0;
+    } catch (const std::exception &e) {
+        fprintf(stderr, "error: %s\n", e.what());
+        return 1;
+    }
+}

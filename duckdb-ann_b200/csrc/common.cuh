@@ -1,0 +1,103 @@
+// Shared host/device helpers of the CUDA search library (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+namespace anncuda {
+
+// ---- per-thread error text ---------------------------------------------------
+inline std::string &last_error_ref() {
+    static thread_local std::string msg;
+    return msg;
+}
+
+inline int set_error(const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    last_error_ref() = buf;
+    return -1;
+}
+
+#define ANN_CUDA_TRY(expr)                                                                          \
+    do {                                                                                            \
+        cudaError_t err__ = (expr);                                                                 \
+        if (err__ != cudaSuccess) {                                                                 \
+            return ::anncuda::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(err__),  \
+                                        __FILE__, __LINE__);                                        \
+        }                                                                                           \
+    } while (0)
+
+// Sets the device for the current scope and restores the caller's on exit, so
+// library calls never change the calling thread's current device.
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = false;
+    explicit DeviceGuard(int device) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        ok = (cudaSetDevice(device) == cudaSuccess);
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+// A device buffer that only grows (next power of two), reused across calls.
+struct GrowBuf {
+    void *ptr = nullptr;
+    size_t cap = 0;
+    int ensure(size_t bytes) {
+        if (bytes <= cap) return 0;
+        size_t want = 4096;
+        while (want < bytes) want <<= 1;
+        if (ptr) cudaFree(ptr);
+        ptr = nullptr;
+        cap = 0;
+        ANN_CUDA_TRY(cudaMalloc(&ptr, want));
+        cap = want;
+        return 0;
+    }
+    void release() {
+        if (ptr) cudaFree(ptr);
+        ptr = nullptr;
+        cap = 0;
+    }
+    template <class T>
+    T *as() const {
+        return static_cast<T *>(ptr);
+    }
+};
+
+inline int sm_count(int device) {
+    static int cached[64];
+    static std::once_flag once;
+    std::call_once(once, [] { memset(cached, 0, sizeof cached); });
+    if (device < 0 || device >= 64) return 148;
+    if (cached[device] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || v <= 0) v = 148;
+        cached[device] = v;
+    }
+    return cached[device];
+}
+
+// ---- device helpers -----------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+constexpr float kInf = __builtin_huge_valf();
+
+}  // namespace anncuda

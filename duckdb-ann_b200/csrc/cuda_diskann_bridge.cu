@@ -1,0 +1,579 @@
+// DiskANN batch-distance bridge for sm_100a: L2 / inner-product / SQ8-asymmetric
+// distance of many (query, row) pairs in one launch.
+//
+// Replaces the reference's Metal bridge (src/metal_diskann_bridge.mm) and its
+// four kernels (faiss-metal/shaders/diskann_distance.metal:15,64,111,155) behind
+// the same three C symbols, and adds entry points that take row ids into a
+// device-resident table.  The work is a pure stream over the candidate rows,
+// so the kernels are shaped for HBM bandwidth: one warp per row, 128-bit
+// loads that bypass L1 allocation for the rows, several rows in flight per
+// warp, warp-shuffle reductions.  There is no CPU path in this file.
+#include "cuda_diskann_bridge.h"
+
+#include <cstdlib>
+#include <memory>
+
+#include "common.cuh"
+
+using namespace anncuda;
+
+// ---------------------------------------------------------------------------------------------
+// Kernels
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+__device__ __forceinline__ float4 ld_stream4(const float4 *p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ uint4 ld_stream4u(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float acc4(float acc, float4 q, float4 x, bool l2) {
+    if (l2) {
+        float a = q.x - x.x, b = q.y - x.y, c = q.z - x.z, d = q.w - x.w;
+        acc = fmaf(a, a, acc);
+        acc = fmaf(b, b, acc);
+        acc = fmaf(c, c, acc);
+        acc = fmaf(d, d, acc);
+    } else {
+        acc = fmaf(q.x, x.x, acc);
+        acc = fmaf(q.y, x.y, acc);
+        acc = fmaf(q.z, x.z, acc);
+        acc = fmaf(q.w, x.w, acc);
+    }
+    return acc;
+}
+
+// fp32 rows.  WPR warps cooperate on one row (1 for large batches; 4 for the
+// small single-query batches, where there are fewer rows than resident warps).
+// ids == nullptr: row i is candidates[i*dim ...] (the reference's gathered layout,
+// src/metal_diskann_bridge.mm:180-198); else row ids[i] of the table.
+// qmap == nullptr: every row uses query 0.
+template <int WPR, bool VEC4>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+batch_distance_f32_kernel(const float *__restrict__ table, size_t num, int dim, const float *__restrict__ queries,
+                          int nq, const uint32_t *__restrict__ ids, const uint32_t *__restrict__ qmap, int total_n,
+                          int metric, float *__restrict__ out) {
+    constexpr int kRowsPerBlock = kWarpsPerBlock / WPR;
+    __shared__ float partial[kWarpsPerBlock];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = warp % WPR;  // which slice of the row this warp sums
+    const bool l2 = (metric == 0);
+    for (long long row0 = (long long)blockIdx.x * kRowsPerBlock; row0 < total_n;
+         row0 += (long long)gridDim.x * kRowsPerBlock) {
+        const long long i = row0 + warp / WPR;
+        float acc = 0.f;
+        bool valid = i < total_n;
+        size_t r = 0;
+        uint32_t qi = 0;
+        if (valid) {
+            r = ids ? (size_t)ids[i] : (size_t)i;
+            qi = qmap ? qmap[i] : 0u;
+            if (r >= num || qi >= (uint32_t)nq) valid = false;
+        }
+        if (valid) {
+            const float *x = table + r * (size_t)dim;
+            const float *q = queries + (size_t)qi * dim;
+            if (VEC4) {
+                const float4 *x4 = reinterpret_cast<const float4 *>(x);
+                const float4 *q4 = reinterpret_cast<const float4 *>(q);
+                const int n4 = dim >> 2;
+                int c = sub * 32 + lane;
+                constexpr int kStep = 32 * WPR;
+                // four independent 16-byte loads in flight per lane
+                for (; c + 3 * kStep < n4; c += 4 * kStep) {
+                    float4 a0 = ld_stream4(x4 + c), a1 = ld_stream4(x4 + c + kStep);
+                    float4 a2 = ld_stream4(x4 + c + 2 * kStep), a3 = ld_stream4(x4 + c + 3 * kStep);
+                    acc = acc4(acc, __ldg(q4 + c), a0, l2);
+                    acc = acc4(acc, __ldg(q4 + c + kStep), a1, l2);
+                    acc = acc4(acc, __ldg(q4 + c + 2 * kStep), a2, l2);
+                    acc = acc4(acc, __ldg(q4 + c + 3 * kStep), a3, l2);
+                }
+                for (; c < n4; c += kStep) acc = acc4(acc, __ldg(q4 + c), ld_stream4(x4 + c), l2);
+            } else {
+                for (int c = sub * 32 + lane; c < dim; c += 32 * WPR) {
+                    float xv = __ldg(x + c), qv = __ldg(q + c);
+                    if (l2) {
+                        float t = qv - xv;
+                        acc = fmaf(t, t, acc);
+                    } else {
+                        acc = fmaf(qv, xv, acc);
+                    }
+                }
+            }
+        }
+        acc = warp_sum(acc);
+        if (WPR > 1) {
+            if (lane == 0) partial[warp] = acc;
+            __syncthreads();
+            if (sub == 0 && lane == 0) {
+                float s = 0.f;
+#pragma unroll
+                for (int w = 0; w < WPR; w++) s += partial[warp + w];
+                acc = s;
+            }
+            __syncthreads();
+        }
+        if (sub == 0 && lane == 0 && i < total_n) {
+            out[i] = valid ? (l2 ? acc : -acc) : __int_as_float(0x7fc00000);
+        }
+    }
+}
+
+// code/255 rounded exactly as an IEEE fp32 division: multiply by the rounded
+// reciprocal, then one fused correction step.  Equal to (float)c / 255.0f for
+// all 256 codes (checked exhaustively by the unit tests on the host formula).
+__device__ __forceinline__ float code_over_255(float c) {
+    const float inv = 1.0f / 255.0f;
+    float q = __fmul_rn(c, inv);
+    float r = fmaf(-q, 255.0f, c);
+    return fmaf(r, inv, q);
+}
+
+// Dequantise one code exactly as the reference does, (code/255)*scale+min with
+// separate roundings (rust_lib/src/provider.rs:142-143), and add to the sum.
+__device__ __forceinline__ float sq8_acc(float acc, float q, uint32_t code, float s, float m, bool l2) {
+    float xh = __fadd_rn(__fmul_rn(code_over_255((float)code), s), m);
+    if (l2) {
+        float t = q - xh;
+        return fmaf(t, t, acc);
+    }
+    return fmaf(q, xh, acc);
+}
+
+__device__ __forceinline__ float sq8_acc_word(float acc, float4 q, uint32_t w, float4 s, float4 m, bool l2) {
+    acc = sq8_acc(acc, q.x, w & 0xffu, s.x, m.x, l2);
+    acc = sq8_acc(acc, q.y, (w >> 8) & 0xffu, s.y, m.y, l2);
+    acc = sq8_acc(acc, q.z, (w >> 16) & 0xffu, s.z, m.z, l2);
+    acc = sq8_acc(acc, q.w, w >> 24, s.w, m.w, l2);
+    return acc;
+}
+
+// SQ8 rows, dim % 16 == 0 and dim <= 512: lane c owns dimensions [16c, 16c+16)
+// of every row, so its slice of min / scale lives in registers for the whole
+// kernel and its slice of the query is reloaded only when the query changes
+// (rows of one query are adjacent in DiskANN's lock-step batches,
+// rust_lib/src/disk_provider.rs:546-581).  A row is then one 16-byte load per
+// lane: the only traffic per row is the codes themselves.
+constexpr int kSq8RowsPerWarp = 8;
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+batch_distance_sq8_regs_kernel(const uint8_t *__restrict__ codes, size_t num, int dim,
+                               const float *__restrict__ mins, const float *__restrict__ scale,
+                               const float *__restrict__ queries, int nq, const uint32_t *__restrict__ ids,
+                               const uint32_t *__restrict__ qmap, int total_n, int metric,
+                               float *__restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const long long warp_global = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const long long warps_total = (long long)gridDim.x * kWarpsPerBlock;
+    const bool l2 = (metric == 0);
+    const int nchunk = dim >> 4;
+    const bool active = lane < nchunk;
+    float4 m[4], s[4], q[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        m[j] = active ? __ldg(reinterpret_cast<const float4 *>(mins) + lane * 4 + j) : make_float4(0, 0, 0, 0);
+        s[j] = active ? __ldg(reinterpret_cast<const float4 *>(scale) + lane * 4 + j) : make_float4(0, 0, 0, 0);
+        q[j] = make_float4(0, 0, 0, 0);
+    }
+    uint32_t cur_q = 0xffffffffu;
+    for (long long base = warp_global * kSq8RowsPerWarp; base < total_n; base += warps_total * kSq8RowsPerWarp) {
+        uint4 w[kSq8RowsPerWarp];
+        uint32_t qi[kSq8RowsPerWarp];
+        bool ok[kSq8RowsPerWarp];
+#pragma unroll
+        for (int t = 0; t < kSq8RowsPerWarp; t++) {
+            const long long i = base + t;
+            ok[t] = false;
+            qi[t] = 0;
+            w[t] = make_uint4(0, 0, 0, 0);
+            if (i < total_n) {
+                size_t r = ids ? (size_t)ids[i] : (size_t)i;
+                qi[t] = qmap ? qmap[i] : 0u;
+                ok[t] = r < num && qi[t] < (uint32_t)nq;
+                if (ok[t] && active) w[t] = ld_stream4u(reinterpret_cast<const uint4 *>(codes + r * (size_t)dim) + lane);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < kSq8RowsPerWarp; t++) {
+            const long long i = base + t;
+            if (i >= total_n) break;  // warp-uniform
+            if (ok[t] && qi[t] != cur_q) {  // warp-uniform: qi is the same in every lane
+                cur_q = qi[t];
+                const float4 *q4 = reinterpret_cast<const float4 *>(queries + (size_t)cur_q * dim) + lane * 4;
+#pragma unroll
+                for (int j = 0; j < 4; j++) q[j] = active ? __ldg(q4 + j) : make_float4(0, 0, 0, 0);
+            }
+            float acc = 0.f;
+            if (ok[t] && active) {
+                acc = sq8_acc_word(acc, q[0], w[t].x, s[0], m[0], l2);
+                acc = sq8_acc_word(acc, q[1], w[t].y, s[1], m[1], l2);
+                acc = sq8_acc_word(acc, q[2], w[t].z, s[2], m[2], l2);
+                acc = sq8_acc_word(acc, q[3], w[t].w, s[3], m[3], l2);
+            }
+            acc = warp_sum(acc);
+            if (lane == 0) out[i] = ok[t] ? (l2 ? acc : -acc) : __int_as_float(0x7fc00000);
+        }
+    }
+}
+
+// SQ8 rows, any dimension: one warp per row, byte loads.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+batch_distance_sq8_generic_kernel(const uint8_t *__restrict__ codes, size_t num, int dim,
+                                  const float *__restrict__ mins, const float *__restrict__ scale,
+                                  const float *__restrict__ queries, int nq, const uint32_t *__restrict__ ids,
+                                  const uint32_t *__restrict__ qmap, int total_n, int metric,
+                                  float *__restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const bool l2 = (metric == 0);
+    for (long long i = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); i < total_n;
+         i += (long long)gridDim.x * kWarpsPerBlock) {
+        size_t r = ids ? (size_t)ids[i] : (size_t)i;
+        uint32_t qi = qmap ? qmap[i] : 0u;
+        const bool ok = r < num && qi < (uint32_t)nq;
+        float acc = 0.f;
+        if (ok) {
+            const uint8_t *c = codes + r * (size_t)dim;
+            const float *q = queries + (size_t)qi * dim;
+            for (int d = lane; d < dim; d += 32)
+                acc = sq8_acc(acc, __ldg(q + d), (uint32_t)__ldg(c + d), __ldg(scale + d), __ldg(mins + d), l2);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) out[i] = ok ? (l2 ? acc : -acc) : __int_as_float(0x7fc00000);
+    }
+}
+
+__global__ void check_ids_kernel(const uint32_t *__restrict__ ids, const uint32_t *__restrict__ qmap, int total_n,
+                                 size_t num, int nq, int *__restrict__ bad) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total_n) return;
+    if ((ids && (size_t)ids[i] >= num) || (qmap && qmap[i] >= (uint32_t)nq)) atomicExch(bad, 1);
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+struct diskann_cuda_table {
+    int device = 0;
+    size_t num = 0;
+    int dim = 0;
+    bool sq8 = false;
+    bool owns_rows = false;
+    void *rows = nullptr;  // float* or uint8_t*
+    float *mins = nullptr;
+    float *scale = nullptr;
+};
+
+namespace {
+
+int launch_distance(const diskann_cuda_table &t, const float *queries, int nq, const uint32_t *ids,
+                    const uint32_t *qmap, int total_n, int metric, float *out, cudaStream_t stream) {
+    const int sms = sm_count(t.device);
+    if (!t.sq8) {
+        const float *rows = static_cast<const float *>(t.rows);
+        const bool vec = (t.dim % 4 == 0) && ((reinterpret_cast<uintptr_t>(rows) & 15) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(queries) & 15) == 0);
+        // fewer rows than resident warps: put four warps on each row
+        const bool small = total_n < sms * 16;
+        const int wpr = small ? 4 : 1;
+        const int rows_per_block = kWarpsPerBlock / wpr;
+        long long blocks = ((long long)total_n + rows_per_block - 1) / rows_per_block;
+        const long long cap = (long long)sms * 32;
+        if (blocks > cap) blocks = cap;
+        dim3 grid((unsigned)blocks), block(kWarpsPerBlock * 32);
+        if (small) {
+            if (vec)
+                batch_distance_f32_kernel<4, true><<<grid, block, 0, stream>>>(rows, t.num, t.dim, queries, nq, ids,
+                                                                                qmap, total_n, metric, out);
+            else
+                batch_distance_f32_kernel<4, false><<<grid, block, 0, stream>>>(rows, t.num, t.dim, queries, nq, ids,
+                                                                                 qmap, total_n, metric, out);
+        } else {
+            if (vec)
+                batch_distance_f32_kernel<1, true><<<grid, block, 0, stream>>>(rows, t.num, t.dim, queries, nq, ids,
+                                                                                qmap, total_n, metric, out);
+            else
+                batch_distance_f32_kernel<1, false><<<grid, block, 0, stream>>>(rows, t.num, t.dim, queries, nq, ids,
+                                                                                 qmap, total_n, metric, out);
+        }
+    } else {
+        const uint8_t *codes = static_cast<const uint8_t *>(t.rows);
+        const bool regs = (t.dim % 16 == 0) && t.dim <= 512 && ((reinterpret_cast<uintptr_t>(codes) & 15) == 0) &&
+                          ((reinterpret_cast<uintptr_t>(queries) & 15) == 0);
+        if (regs) {
+            long long warps = ((long long)total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
+            long long blocks = (warps + kWarpsPerBlock - 1) / kWarpsPerBlock;
+            const long long cap = (long long)sms * 8;
+            if (blocks > cap) blocks = cap;
+            batch_distance_sq8_regs_kernel<<<(unsigned)blocks, kWarpsPerBlock * 32, 0, stream>>>(
+                codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out);
+        } else {
+            long long blocks = ((long long)total_n + kWarpsPerBlock - 1) / kWarpsPerBlock;
+            const long long cap = (long long)sms * 32;
+            if (blocks > cap) blocks = cap;
+            batch_distance_sq8_generic_kernel<<<(unsigned)blocks, kWarpsPerBlock * 32, 0, stream>>>(
+                codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out);
+        }
+    }
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+// One call's worth of device staging for the host-pointer entry points.  The
+// reference's bridge shares one ring of buffers between all threads with no
+// lock (src/metal_diskann_bridge.mm:52-53,118-120); here every call takes a
+// private context from a pool, so concurrent callers never share buffers.
+struct CallCtx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    GrowBuf q, cand, ids, map, out, flag;
+};
+
+struct BridgeState {
+    std::mutex mu;
+    bool probed = false;
+    bool available = false;
+    int device = 0;
+    std::vector<CallCtx *> free_list;
+
+    bool probe() {
+        std::lock_guard<std::mutex> lock(mu);
+        if (probed) return available;
+        probed = true;
+        int count = 0;
+        if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+            cudaGetLastError();
+            set_error("no CUDA device");
+            return false;
+        }
+        const char *env = getenv("ANN_CUDA_DEVICE");
+        device = env ? atoi(env) : 0;
+        if (device < 0 || device >= count) device = 0;
+        cudaDeviceProp prop;
+        if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return false;
+        if (prop.major != 10) {
+            set_error("device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+            return false;
+        }
+        available = true;
+        return true;
+    }
+
+    CallCtx *acquire(int dev) {
+        {
+            std::lock_guard<std::mutex> lock(mu);
+            for (size_t i = 0; i < free_list.size(); i++) {
+                if (free_list[i]->device == dev) {
+                    CallCtx *c = free_list[i];
+                    free_list.erase(free_list.begin() + i);
+                    return c;
+                }
+            }
+        }
+        CallCtx *c = new CallCtx();
+        c->device = dev;
+        if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) {
+            delete c;
+            return nullptr;
+        }
+        return c;
+    }
+    void release(CallCtx *c) {
+        std::lock_guard<std::mutex> lock(mu);
+        free_list.push_back(c);
+    }
+};
+
+BridgeState &state() {
+    static BridgeState *s = new BridgeState();  // intentionally leaked: safe at process exit
+    return *s;
+}
+
+struct CtxLease {
+    CallCtx *ctx;
+    explicit CtxLease(int dev) : ctx(state().acquire(dev)) {}
+    ~CtxLease() {
+        if (ctx) state().release(ctx);
+    }
+};
+
+int host_call(const diskann_cuda_table *table, const float *gathered, const float *queries, int nq,
+              const uint32_t *ids, const uint32_t *qmap, int total_n, int dim, int metric, float *out) {
+    const int dev = table ? table->device : state().device;
+    DeviceGuard guard(dev);
+    if (!guard.ok) return set_error("cudaSetDevice(%d) failed", dev);
+    CtxLease lease(dev);
+    CallCtx *c = lease.ctx;
+    if (!c) return set_error("could not create a CUDA stream");
+    const size_t qbytes = (size_t)nq * dim * sizeof(float);
+    const size_t obytes = (size_t)total_n * sizeof(float);
+    if (c->q.ensure(qbytes) || c->out.ensure(obytes) || c->flag.ensure(sizeof(int))) return -1;
+    ANN_CUDA_TRY(cudaMemcpyAsync(c->q.ptr, queries, qbytes, cudaMemcpyHostToDevice, c->stream));
+    const uint32_t *d_ids = nullptr, *d_map = nullptr;
+    if (ids) {
+        if (c->ids.ensure((size_t)total_n * 4)) return -1;
+        ANN_CUDA_TRY(cudaMemcpyAsync(c->ids.ptr, ids, (size_t)total_n * 4, cudaMemcpyHostToDevice, c->stream));
+        d_ids = c->ids.as<uint32_t>();
+    }
+    if (qmap) {
+        if (c->map.ensure((size_t)total_n * 4)) return -1;
+        ANN_CUDA_TRY(cudaMemcpyAsync(c->map.ptr, qmap, (size_t)total_n * 4, cudaMemcpyHostToDevice, c->stream));
+        d_map = c->map.as<uint32_t>();
+    }
+    diskann_cuda_table tmp;
+    const diskann_cuda_table *t = table;
+    if (!t) {
+        const size_t cbytes = (size_t)total_n * dim * sizeof(float);
+        if (c->cand.ensure(cbytes)) return -1;
+        ANN_CUDA_TRY(cudaMemcpyAsync(c->cand.ptr, gathered, cbytes, cudaMemcpyHostToDevice, c->stream));
+        tmp.device = dev;
+        tmp.num = (size_t)total_n;
+        tmp.dim = dim;
+        tmp.rows = c->cand.ptr;
+        t = &tmp;
+    }
+    ANN_CUDA_TRY(cudaMemsetAsync(c->flag.ptr, 0, sizeof(int), c->stream));
+    if (d_ids || d_map) {
+        check_ids_kernel<<<(total_n + 255) / 256, 256, 0, c->stream>>>(d_ids, d_map, total_n, t->num, nq,
+                                                                      c->flag.as<int>());
+        ANN_CUDA_TRY(cudaGetLastError());
+    }
+    if (launch_distance(*t, c->q.as<float>(), nq, d_ids, d_map, total_n, metric, c->out.as<float>(), c->stream))
+        return -1;
+    int bad = 0;
+    ANN_CUDA_TRY(cudaMemcpyAsync(out, c->out.ptr, obytes, cudaMemcpyDeviceToHost, c->stream));
+    ANN_CUDA_TRY(cudaMemcpyAsync(&bad, c->flag.ptr, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+    ANN_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    if (bad) return set_error("row id or query_map entry out of range");
+    return 0;
+}
+
+int make_table(int device, const void *rows, bool rows_on_device, const float *mins, const float *scale, size_t num,
+               int dim, bool sq8, diskann_cuda_table **out) {
+    if (!out) return set_error("null output handle");
+    *out = nullptr;
+    if (!rows || num == 0 || dim <= 0 || (sq8 && (!mins || !scale))) return set_error("invalid table arguments");
+    if (num > 0xffffffffull) return set_error("row ids are 32-bit: at most 2^32 rows");
+    if (!state().probe()) return -1;
+    DeviceGuard guard(device);
+    if (!guard.ok) return set_error("cudaSetDevice(%d) failed", device);
+    std::unique_ptr<diskann_cuda_table> t(new diskann_cuda_table());
+    t->device = device;
+    t->num = num;
+    t->dim = dim;
+    t->sq8 = sq8;
+    const size_t bytes = num * (size_t)dim * (sq8 ? 1 : sizeof(float));
+    if (rows_on_device) {
+        t->rows = const_cast<void *>(rows);
+    } else {
+        ANN_CUDA_TRY(cudaMalloc(&t->rows, bytes));
+        t->owns_rows = true;
+        cudaError_t e = cudaMemcpy(t->rows, rows, bytes, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) {
+            cudaFree(t->rows);
+            return set_error("table upload failed: %s", cudaGetErrorString(e));
+        }
+    }
+    if (sq8) {
+        cudaError_t e1 = cudaMalloc(&t->mins, (size_t)dim * 4), e2 = cudaMalloc(&t->scale, (size_t)dim * 4);
+        if (e1 == cudaSuccess && e2 == cudaSuccess) {
+            e1 = cudaMemcpy(t->mins, mins, (size_t)dim * 4, cudaMemcpyHostToDevice);
+            e2 = cudaMemcpy(t->scale, scale, (size_t)dim * 4, cudaMemcpyHostToDevice);
+        }
+        if (e1 != cudaSuccess || e2 != cudaSuccess) {
+            diskann_cuda_unregister(t.release());
+            return set_error("SQ8 parameter upload failed");
+        }
+    }
+    *out = t.release();
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *diskann_cuda_last_error(void) { return last_error_ref().c_str(); }
+
+int diskann_metal_available(void) { return state().probe() ? 1 : 0; }
+
+int diskann_metal_batch_distances(const float *query, const float *candidates, int n, int dim, int metric,
+                                  float *out_distances) {
+    if (!query || !candidates || !out_distances || n <= 0 || dim <= 0) return set_error("invalid arguments");
+    if (!state().probe()) return -1;
+    return host_call(nullptr, candidates, query, 1, nullptr, nullptr, n, dim, metric, out_distances);
+}
+
+int diskann_metal_multi_batch_distances(const float *queries, const float *candidates, const unsigned int *query_map,
+                                        int total_n, int nq, int dim, int metric, float *out_distances) {
+    if (!queries || !candidates || !query_map || !out_distances || total_n <= 0 || nq <= 0 || dim <= 0)
+        return set_error("invalid arguments");
+    if (!state().probe()) return -1;
+    return host_call(nullptr, candidates, queries, nq, nullptr, query_map, total_n, dim, metric, out_distances);
+}
+
+int diskann_cuda_register_table(int device, const float *host_rows, size_t num, int dim, diskann_cuda_table **out) {
+    return make_table(device, host_rows, false, nullptr, nullptr, num, dim, false, out);
+}
+
+int diskann_cuda_register_table_device(int device, const float *device_rows, size_t num, int dim,
+                                       diskann_cuda_table **out) {
+    return make_table(device, device_rows, true, nullptr, nullptr, num, dim, false, out);
+}
+
+int diskann_cuda_register_sq8(int device, const uint8_t *codes, const float *mins, const float *scale, size_t num,
+                              int dim, diskann_cuda_table **out) {
+    return make_table(device, codes, false, mins, scale, num, dim, true, out);
+}
+
+int diskann_cuda_register_sq8_device(int device, const uint8_t *device_codes, const float *mins, const float *scale,
+                                     size_t num, int dim, diskann_cuda_table **out) {
+    return make_table(device, device_codes, true, mins, scale, num, dim, true, out);
+}
+
+int diskann_cuda_unregister(diskann_cuda_table *t) {
+    if (!t) return 0;
+    DeviceGuard guard(t->device);
+    if (t->owns_rows && t->rows) cudaFree(t->rows);
+    if (t->mins) cudaFree(t->mins);
+    if (t->scale) cudaFree(t->scale);
+    delete t;
+    return 0;
+}
+
+int diskann_cuda_batch_distances_by_id(const diskann_cuda_table *table, const float *queries, int nq,
+                                       const uint32_t *ids, const uint32_t *query_map, int total_n, int metric,
+                                       float *out_distances) {
+    if (!table || !queries || !ids || !out_distances || total_n <= 0 || nq <= 0)
+        return set_error("invalid arguments");
+    if (!query_map && nq != 1) return set_error("query_map may be NULL only when nq == 1");
+    return host_call(table, nullptr, queries, nq, ids, query_map, total_n, table->dim, metric, out_distances);
+}
+
+int diskann_cuda_batch_distances_by_id_device(const diskann_cuda_table *table, const float *queries, int nq,
+                                              const uint32_t *ids, const uint32_t *query_map, int total_n,
+                                              int metric, float *out_distances, void *stream) {
+    if (!table || !queries || !ids || !out_distances || total_n <= 0 || nq <= 0)
+        return set_error("invalid arguments");
+    if (!query_map && nq != 1) return set_error("query_map may be NULL only when nq == 1");
+    DeviceGuard guard(table->device);
+    if (!guard.ok) return set_error("cudaSetDevice(%d) failed", table->device);
+    return launch_distance(*table, queries, nq, ids, query_map, total_n, metric, out_distances,
+                           static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

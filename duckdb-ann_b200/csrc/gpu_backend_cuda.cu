@@ -1,0 +1,221 @@
+// CudaGpuBackend and the faiss::Index subclasses it hands out.
+//
+// Counterpart of the reference's src/gpu_backend_metal.mm (backend) and of the
+// index classes in faiss-metal/src/MetalIndexFlat.mm / MetalIndexIVFFlat.mm; all
+// device work goes through the C ABI in ann_cuda.h.
+#include "gpu_backend_cuda.hpp"
+
+#include <cstdlib>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "ann_cuda.h"
+
+#ifndef FAISS_AVAILABLE
+#define FAISS_AVAILABLE
+#endif
+#include "gpu_backend.hpp"
+
+#if defined(__GNUC__)
+#define ANN_CUDA_EXPORT __attribute__((visibility("default")))
+#else
+#define ANN_CUDA_EXPORT
+#endif
+
+namespace faiss_cuda {
+
+namespace {
+[[noreturn]] void fail(const char *what) {
+    throw std::runtime_error(std::string(what) + ": " + ann_cuda_last_error());
+}
+int metric_code(faiss::MetricType m) {
+    if (m == faiss::METRIC_L2) return ANN_CUDA_METRIC_L2;
+    if (m == faiss::METRIC_INNER_PRODUCT) return ANN_CUDA_METRIC_INNER_PRODUCT;
+    throw std::runtime_error("CUDA GPU backend supports METRIC_L2 and METRIC_INNER_PRODUCT only");
+}
+}  // namespace
+
+// ---------------------------------------------------------------- CudaIndexFlat
+ANN_CUDA_EXPORT CudaIndexFlat::CudaIndexFlat(int device, int d, faiss::MetricType metric) : faiss::Index(d, metric) {
+    if (ann_cuda_flat_create(device, d, metric_code(metric), &handle_)) fail("CudaIndexFlat");
+    is_trained = true;
+}
+ANN_CUDA_EXPORT CudaIndexFlat::~CudaIndexFlat() { ann_cuda_index_free(handle_); }
+
+ANN_CUDA_EXPORT void CudaIndexFlat::add(faiss::idx_t n, const float *x) {
+    if (ann_cuda_index_add(handle_, n, x)) fail("CudaIndexFlat::add");
+    ntotal = ann_cuda_index_ntotal(handle_);
+}
+ANN_CUDA_EXPORT void CudaIndexFlat::search(faiss::idx_t n, const float *x, faiss::idx_t k, float *distances,
+                                           faiss::idx_t *labels, const faiss::SearchParameters *) const {
+    if (k <= 0) throw std::runtime_error("k must be > 0");
+    if (ann_cuda_index_search(handle_, n, x, k, distances, labels)) fail("CudaIndexFlat::search");
+}
+ANN_CUDA_EXPORT void CudaIndexFlat::reset() {
+    if (ann_cuda_index_reset(handle_)) fail("CudaIndexFlat::reset");
+    ntotal = 0;
+}
+ANN_CUDA_EXPORT void CudaIndexFlat::reconstruct(faiss::idx_t key, float *recons) const {
+    if (ann_cuda_index_reconstruct(handle_, key, recons)) fail("CudaIndexFlat::reconstruct");
+}
+ANN_CUDA_EXPORT void CudaIndexFlat::getRows(faiss::idx_t first, faiss::idx_t n, float *rows) const {
+    if (ann_cuda_flat_get_rows(handle_, first, n, rows)) fail("CudaIndexFlat::getRows");
+}
+
+// ---------------------------------------------------------------- CudaIndexIVFFlat
+ANN_CUDA_EXPORT CudaIndexIVFFlat::CudaIndexIVFFlat(int device, int d, size_t nlist, faiss::MetricType metric)
+    : faiss::Index(d, metric) {
+    if (ann_cuda_ivfflat_create(device, d, (int64_t)nlist, metric_code(metric), &handle_)) fail("CudaIndexIVFFlat");
+    is_trained = false;
+}
+ANN_CUDA_EXPORT CudaIndexIVFFlat::~CudaIndexIVFFlat() { ann_cuda_index_free(handle_); }
+
+ANN_CUDA_EXPORT void CudaIndexIVFFlat::train(faiss::idx_t n, const float *x) {
+    if (ann_cuda_ivfflat_train(handle_, n, x)) fail("CudaIndexIVFFlat::train");
+    is_trained = true;
+}
+ANN_CUDA_EXPORT void CudaIndexIVFFlat::add(faiss::idx_t n, const float *x) {
+    if (!is_trained) throw std::runtime_error("add: index must be trained first");
+    if (ann_cuda_index_add(handle_, n, x)) fail("CudaIndexIVFFlat::add");
+    ntotal = ann_cuda_index_ntotal(handle_);
+}
+ANN_CUDA_EXPORT void CudaIndexIVFFlat::search(faiss::idx_t n, const float *x, faiss::idx_t k, float *distances,
+                                              faiss::idx_t *labels, const faiss::SearchParameters *) const {
+    if (!is_trained) throw std::runtime_error("search: index must be trained first");
+    if (k <= 0) throw std::runtime_error("k must be > 0");
+    if (ann_cuda_index_search(handle_, n, x, k, distances, labels)) fail("CudaIndexIVFFlat::search");
+}
+ANN_CUDA_EXPORT void CudaIndexIVFFlat::reset() {
+    if (ann_cuda_index_reset(handle_)) fail("CudaIndexIVFFlat::reset");
+    ntotal = 0;
+}
+ANN_CUDA_EXPORT void CudaIndexIVFFlat::reconstruct(faiss::idx_t key, float *recons) const {
+    if (ann_cuda_index_reconstruct(handle_, key, recons)) fail("CudaIndexIVFFlat::reconstruct");
+}
+ANN_CUDA_EXPORT size_t CudaIndexIVFFlat::getNlist() const { return (size_t)ann_cuda_ivfflat_nlist(handle_); }
+ANN_CUDA_EXPORT size_t CudaIndexIVFFlat::getNprobe() const { return (size_t)ann_cuda_ivfflat_get_nprobe(handle_); }
+ANN_CUDA_EXPORT void CudaIndexIVFFlat::setNprobe(size_t nprobe) {
+    if (ann_cuda_ivfflat_set_nprobe(handle_, (int64_t)nprobe)) fail("CudaIndexIVFFlat::setNprobe");
+}
+
+// ---------------------------------------------------------------- conversions
+ANN_CUDA_EXPORT std::unique_ptr<CudaIndexFlat> index_cpu_to_cuda(int device, const faiss::IndexFlat *cpu) {
+    std::unique_ptr<CudaIndexFlat> gpu(new CudaIndexFlat(device, cpu->d, cpu->metric_type));
+    if (cpu->ntotal > 0) {
+        if (ann_cuda_index_reserve(gpu->handle(), cpu->ntotal)) fail("index_cpu_to_cuda");
+        gpu->add(cpu->ntotal, cpu->get_xb());
+    }
+    return gpu;
+}
+
+ANN_CUDA_EXPORT std::unique_ptr<faiss::IndexFlat> index_cuda_to_cpu(const CudaIndexFlat *gpu) {
+    std::unique_ptr<faiss::IndexFlat> cpu(new faiss::IndexFlat(gpu->d, gpu->metric_type));
+    if (gpu->ntotal > 0) {
+        std::vector<float> rows((size_t)gpu->ntotal * gpu->d);
+        gpu->getRows(0, gpu->ntotal, rows.data());
+        cpu->add(gpu->ntotal, rows.data());
+    }
+    return cpu;
+}
+
+ANN_CUDA_EXPORT std::unique_ptr<CudaIndexIVFFlat> index_cpu_to_cuda_ivf(int device, const faiss::IndexIVFFlat *cpu) {
+    if (!cpu->is_trained) throw std::runtime_error("CPU IndexIVFFlat must be trained");
+    auto *quantizer = dynamic_cast<const faiss::IndexFlat *>(cpu->quantizer);
+    if (!quantizer) throw std::runtime_error("IndexIVFFlat quantizer must be IndexFlat");
+    if ((size_t)quantizer->ntotal != cpu->nlist) throw std::runtime_error("quantizer size does not match nlist");
+    std::unique_ptr<CudaIndexIVFFlat> gpu(new CudaIndexIVFFlat(device, cpu->d, cpu->nlist, cpu->metric_type));
+    if (ann_cuda_ivfflat_set_centroids(gpu->handle_, quantizer->get_xb())) fail("index_cpu_to_cuda_ivf");
+    gpu->is_trained = true;
+    if (ann_cuda_index_reserve(gpu->handle_, cpu->ntotal)) fail("index_cpu_to_cuda_ivf");
+    const faiss::InvertedLists *lists = cpu->invlists;
+    for (size_t c = 0; c < cpu->nlist; c++) {
+        const size_t n = lists->list_size(c);
+        if (n == 0) continue;
+        const faiss::idx_t *ids = lists->get_ids(c);
+        const uint8_t *codes = lists->get_codes(c);
+        const int rc = ann_cuda_ivfflat_add_list(gpu->handle_, (int64_t)c, (int64_t)n, ids,
+                                                 reinterpret_cast<const float *>(codes));
+        lists->release_ids(c, ids);
+        lists->release_codes(c, codes);
+        if (rc) fail("index_cpu_to_cuda_ivf");
+    }
+    gpu->ntotal = cpu->ntotal;
+    gpu->setNprobe(cpu->nprobe);
+    return gpu;
+}
+
+ANN_CUDA_EXPORT std::unique_ptr<faiss::IndexIVFFlat> index_cuda_to_cpu_ivf(const CudaIndexIVFFlat *gpu) {
+    if (!gpu->is_trained) throw std::runtime_error("CUDA index must be trained");
+    const int d = gpu->d;
+    const size_t nlist = gpu->getNlist();
+    std::vector<float> cent(nlist * (size_t)d);
+    if (ann_cuda_ivfflat_get_centroids(gpu->handle(), cent.data())) fail("index_cuda_to_cpu_ivf");
+    auto *quantizer = new faiss::IndexFlat(d, gpu->metric_type);
+    quantizer->add((faiss::idx_t)nlist, cent.data());
+    std::unique_ptr<faiss::IndexIVFFlat> cpu(new faiss::IndexIVFFlat(quantizer, d, nlist, gpu->metric_type));
+    cpu->own_fields = true;
+    cpu->is_trained = true;
+    cpu->nprobe = gpu->getNprobe();
+    std::vector<faiss::idx_t> ids;
+    std::vector<float> rows;
+    for (size_t c = 0; c < nlist; c++) {
+        const int64_t n = ann_cuda_ivfflat_list_size(gpu->handle(), (int64_t)c);
+        if (n < 0) fail("index_cuda_to_cpu_ivf");
+        if (n == 0) continue;
+        ids.resize((size_t)n);
+        rows.resize((size_t)n * d);
+        if (ann_cuda_ivfflat_get_list(gpu->handle(), (int64_t)c, ids.data(), rows.data())) fail("index_cuda_to_cpu_ivf");
+        cpu->invlists->add_entries(c, (size_t)n, ids.data(), reinterpret_cast<const uint8_t *>(rows.data()));
+    }
+    cpu->ntotal = gpu->ntotal;
+    return cpu;
+}
+
+}  // namespace faiss_cuda
+
+// ---------------------------------------------------------------- the backend
+namespace duckdb {
+
+class ANN_CUDA_EXPORT CudaGpuBackend : public GpuBackend {
+public:
+    // Availability is a flag; the constructor never throws (gpu_backend_metal.mm:17-24).
+    CudaGpuBackend() {
+        available_ = ann_cuda_available() != 0;
+        const char *env = std::getenv("ANN_CUDA_DEVICE");
+        device_ = env ? std::atoi(env) : 0;
+        if (device_ < 0 || device_ >= ann_cuda_device_count()) device_ = 0;
+    }
+    bool IsAvailable() const override { return available_; }
+    std::string DeviceInfo() const override {
+        if (!available_) return "CUDA: not available";
+        char buf[256];
+        if (ann_cuda_device_info(buf, sizeof buf)) return "CUDA GPU";
+        return buf;
+    }
+    std::string BackendName() const override { return "cuda"; }
+
+    std::unique_ptr<faiss::Index> CpuToGpu(faiss::Index *cpu_index) override {
+        if (!available_) throw std::runtime_error("CUDA GPU backend not available");
+        // IVFFlat first: it also contains an IndexFlat quantizer (gpu_backend_metal.mm:47-51)
+        if (auto *ivf = dynamic_cast<faiss::IndexIVFFlat *>(cpu_index)) return faiss_cuda::index_cpu_to_cuda_ivf(device_, ivf);
+        if (auto *flat = dynamic_cast<faiss::IndexFlat *>(cpu_index)) return faiss_cuda::index_cpu_to_cuda(device_, flat);
+        throw std::runtime_error("CUDA GPU supports IndexFlat and IndexIVFFlat. Got an unsupported index type.");
+    }
+    std::unique_ptr<faiss::Index> GpuToCpu(faiss::Index *gpu_index) override {
+        if (auto *ivf = dynamic_cast<faiss_cuda::CudaIndexIVFFlat *>(gpu_index)) return faiss_cuda::index_cuda_to_cpu_ivf(ivf);
+        if (auto *flat = dynamic_cast<faiss_cuda::CudaIndexFlat *>(gpu_index)) return faiss_cuda::index_cuda_to_cpu(flat);
+        throw std::runtime_error("Index is not a CUDA index -- cannot convert to CPU");
+    }
+
+private:
+    bool available_ = false;
+    int device_ = 0;
+};
+
+ANN_CUDA_EXPORT GpuBackend &GetGpuBackend() {
+    static CudaGpuBackend instance;
+    return instance;
+}
+
+}  // namespace duckdb

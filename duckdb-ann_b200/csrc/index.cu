@@ -1,0 +1,899 @@
+// Index objects behind the C ABI of include/ann_cuda.h: device-resident Flat and
+// IVFFlat indexes and their search drivers.
+//
+// Data layout in HBM (one GPU):
+//   Flat      hi, lo : ntotal x dp fp32 each (TF32 split of every row, dp = d padded
+//             to 32 floats), norms : ntotal fp32.  hi + lo is the original row, bit
+//             for bit, so reconstruct() needs no third copy.
+//   IVFFlat   centroids as a split store (nlist x dp) for the coarse quantiser;
+//             vectors : ntotal x dp fp32 grouped by list (CSR: list_off[nlist+1]),
+//             ids : ntotal int64.  The reference keeps the lists in host vectors and
+//             gathers them per query (faiss-metal/src/MetalIndexIVFFlat.mm:32-37,158-194);
+//             here they never leave the device.
+// Searches draw their scratch from a per-index pool of workspaces, one per
+// concurrent caller, so `search` can run from many host threads at once
+// (the reference's Metal index shares scratch without a lock,
+// faiss-metal/src/MetalIndexFlat.mm:104-140).
+#include "ann_cuda.h"
+
+#include <algorithm>
+#include <atomic>
+#include <cstdlib>
+#include <memory>
+#include <numeric>
+
+#include "common.cuh"
+#include "kernels.h"
+
+using namespace anncuda;
+
+namespace {
+
+enum class FlatKernel { TC, SIMT };
+
+std::atomic<int> g_flat_kernel{-1};  // -1 = not chosen yet
+
+FlatKernel flat_kernel_choice() {
+    int v = g_flat_kernel.load(std::memory_order_relaxed);
+    if (v < 0) {
+        const char *e = getenv("ANN_CUDA_FLAT_KERNEL");
+        v = (e && strcmp(e, "simt") == 0) ? 1 : 0;
+        g_flat_kernel.store(v, std::memory_order_relaxed);
+    }
+    return v == 1 ? FlatKernel::SIMT : FlatKernel::TC;
+}
+
+// Split (hi/lo) row store that grows by doubling, at least 1024 rows at a time
+// (the growth rule of faiss-metal/src/MetalIndexFlat.mm:255-270).
+struct SplitStore {
+    float *hi = nullptr, *lo = nullptr, *norms = nullptr;
+    int64_t n = 0, cap = 0;
+    int dp = 0;
+
+    int reserve(int64_t want) {
+        if (want <= cap) return 0;
+        float *nh = nullptr, *nl = nullptr, *nn = nullptr;
+        const size_t row = (size_t)dp * sizeof(float);
+        if (cudaMalloc(&nh, (size_t)want * row) != cudaSuccess || cudaMalloc(&nl, (size_t)want * row) != cudaSuccess ||
+            cudaMalloc(&nn, (size_t)want * sizeof(float)) != cudaSuccess) {
+            cudaGetLastError();
+            if (nh) cudaFree(nh);
+            if (nl) cudaFree(nl);
+            if (nn) cudaFree(nn);
+            return set_error("out of device memory reserving %lld rows of %d floats (x2 for the TF32 split)",
+                             (long long)want, dp);
+        }
+        if (n > 0) {
+            ANN_CUDA_TRY(cudaMemcpy(nh, hi, (size_t)n * row, cudaMemcpyDeviceToDevice));
+            ANN_CUDA_TRY(cudaMemcpy(nl, lo, (size_t)n * row, cudaMemcpyDeviceToDevice));
+            ANN_CUDA_TRY(cudaMemcpy(nn, norms, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice));
+        }
+        release_buffers();
+        hi = nh; lo = nl; norms = nn; cap = want;
+        return 0;
+    }
+    int grow_for(int64_t extra) {
+        if (n + extra <= cap) return 0;
+        int64_t want = std::max<int64_t>(cap * 2, 1024);
+        while (want < n + extra) want *= 2;
+        return reserve(want);
+    }
+    // x: device rows (cnt x d)
+    int append_device(const float *x, int64_t cnt, int d, cudaStream_t stream) {
+        if (grow_for(cnt)) return -1;
+        if (launch_split_rows(x, cnt, d, dp, hi + n * dp, lo + n * dp, norms + n, stream)) return -1;
+        n += cnt;
+        return 0;
+    }
+    void release_buffers() {
+        if (hi) cudaFree(hi);
+        if (lo) cudaFree(lo);
+        if (norms) cudaFree(norms);
+        hi = lo = norms = nullptr;
+        cap = 0;
+    }
+};
+
+struct Workspace {
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t bound = nullptr;  // stream whose work may still use these buffers
+    GrowBuf x, qhi, qlo, qn, part_key, part_idx, sel_key, sel_idx, status, out_d, out_i;
+    GrowBuf item_q, item_rb, item_re, item_slot, scratch, probes_key, probes;
+    int *status_host = nullptr;  // pinned
+    void release() {
+        for (GrowBuf *b : {&x, &qhi, &qlo, &qn, &part_key, &part_idx, &sel_key, &sel_idx, &status, &out_d, &out_i,
+                           &item_q, &item_rb, &item_re, &item_slot, &scratch, &probes_key, &probes})
+            b->release();
+        if (status_host) cudaFreeHost(status_host);
+        if (own_stream) cudaStreamDestroy(own_stream);
+    }
+};
+
+}  // namespace
+
+struct ann_cuda_index {
+    int device = 0;
+    int d = 0, dp = 0;
+    int metric = ANN_CUDA_METRIC_L2;
+    bool ivf = false;
+    bool trained = true;
+    int64_t ntotal = 0;
+
+    SplitStore store;  // Flat: the database.  IVFFlat: the centroids.
+
+    // IVFFlat
+    int64_t nlist = 0, nprobe = 1;
+    int shard_rank = 0, shard_count = 1;
+    float *vecs = nullptr;    // rows x dp, plain fp32
+    int64_t *ids = nullptr;   // rows
+    int64_t rows = 0, rows_cap = 0;
+    std::vector<int32_t> row_list;  // list of every stored row, physical order (host)
+    bool rows_sorted = true;        // physical order is already grouped by list
+    mutable bool csr_dirty = true;
+    mutable int64_t *list_off = nullptr;  // device, nlist + 1
+    mutable std::vector<int64_t> list_off_host;
+    mutable std::mutex build_mu;
+
+    mutable std::mutex ws_mu;
+    mutable std::vector<Workspace *> ws_free;
+
+    Workspace *acquire_ws(cudaStream_t user_stream, bool internal) const {
+        {
+            std::lock_guard<std::mutex> lock(ws_mu);
+            for (size_t i = 0; i < ws_free.size(); i++) {
+                Workspace *w = ws_free[i];
+                if (internal ? (w->bound == w->own_stream) : (w->bound == user_stream && w->bound != w->own_stream)) {
+                    ws_free.erase(ws_free.begin() + i);
+                    return w;
+                }
+            }
+        }
+        Workspace *w = new Workspace();
+        if (cudaStreamCreateWithFlags(&w->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaMallocHost(&w->status_host, sizeof(int)) != cudaSuccess) {
+            cudaGetLastError();
+            w->release();
+            delete w;
+            set_error("could not create a search workspace");
+            return nullptr;
+        }
+        *w->status_host = 0;
+        w->bound = internal ? w->own_stream : user_stream;
+        return w;
+    }
+    void release_ws(Workspace *w) const {
+        std::lock_guard<std::mutex> lock(ws_mu);
+        ws_free.push_back(w);
+    }
+};
+
+namespace {
+
+struct WsLease {
+    const ann_cuda_index *idx;
+    Workspace *ws;
+    WsLease(const ann_cuda_index *i, cudaStream_t s, bool internal) : idx(i), ws(i->acquire_ws(s, internal)) {}
+    ~WsLease() {
+        if (ws) idx->release_ws(ws);
+    }
+};
+
+constexpr int64_t kQueryBlock = 16384;  // queries per pass, bounds the scratch size
+
+// ---- k-means helper kernels (index build, not the search path) -------------------------------
+__global__ void kmeans_accumulate_kernel(const float *__restrict__ x, int64_t n, int d, const int32_t *__restrict__ assign,
+                                         float *__restrict__ sums, int *__restrict__ counts) {
+    const int lane = threadIdx.x & 31;
+    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n;
+         r += (int64_t)gridDim.x * (blockDim.x >> 5)) {
+        const int c = assign[r];
+        if (c < 0) continue;
+        if (lane == 0) atomicAdd(&counts[c], 1);
+        for (int j = lane; j < d; j += 32) atomicAdd(&sums[(int64_t)c * d + j], x[r * (int64_t)d + j]);
+    }
+}
+__global__ void kmeans_update_kernel(float *__restrict__ cent, const float *__restrict__ sums,
+                                     const int *__restrict__ counts, int64_t nlist, int d) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= nlist * d) return;
+    const int c = (int)(t / d);
+    if (counts[c] > 0) cent[t] = sums[t] / (float)counts[c];  // an empty cluster keeps its centroid
+}
+__global__ void gather_rows_kernel(const float *__restrict__ src, const int64_t *__restrict__ src_ids,
+                                   const int64_t *__restrict__ perm, int64_t n, int dp, float *__restrict__ dst,
+                                   int64_t *__restrict__ dst_ids) {
+    const int lane = threadIdx.x & 31;
+    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n;
+         r += (int64_t)gridDim.x * (blockDim.x >> 5)) {
+        const int64_t s = perm[r];
+        for (int c = lane; c < dp; c += 32) dst[r * (int64_t)dp + c] = src[s * (int64_t)dp + c];
+        if (lane == 0) dst_ids[r] = src_ids[s];
+    }
+}
+__global__ void find_id_kernel(const int64_t *__restrict__ ids, int64_t n, int64_t key, long long *found) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n && ids[t] == key) atomicMin(found, (long long)t);
+}
+
+// ---- top-k over a split store (flat database, or IVF centroids) ---------------------------------
+// x_dev: nq x d queries on the device.  Leaves (nq x k) keys and int32 rows, best
+// first, in ws.sel_key / ws.sel_idx.
+int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &ws, const float *x_dev, int64_t nq,
+                     int k, cudaStream_t stream) {
+    const int dp = st.dp, d = ix.d;
+    if (ws.qhi.ensure((size_t)nq * dp * 4) || ws.qlo.ensure((size_t)nq * dp * 4) || ws.qn.ensure((size_t)nq * 4) ||
+        ws.sel_key.ensure((size_t)nq * k * 4) || ws.sel_idx.ensure((size_t)nq * k * 4) || ws.status.ensure(4))
+        return -1;
+    if (flat_kernel_choice() == FlatKernel::TC) {
+        if (launch_split_rows(x_dev, nq, d, dp, ws.qhi.as<float>(), ws.qlo.as<float>(), ws.qn.as<float>(), stream))
+            return -1;
+        const FlatPlan plan = make_flat_plan(nq, st.n, k, sm_count(ix.device));
+        if (ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4)) return -1;
+        ANN_CUDA_TRY(cudaMemsetAsync(ws.status.ptr, 0, 4, stream));
+        if (launch_flat_tc(plan, st.hi, st.lo, st.norms, st.n, ws.qhi.as<float>(), ws.qlo.as<float>(), nq, dp, k,
+                           ix.metric, ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.status.as<int>(),
+                           ix.device, stream))
+            return -1;
+        ANN_CUDA_TRY(cudaMemcpyAsync(ws.status_host, ws.status.ptr, 4, cudaMemcpyDeviceToHost, stream));
+        return launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 0, plan.nq_tiles, nullptr,
+                                  plan.chunks, nq, k, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device,
+                                  stream);
+    }
+    // exact-fp32 cross-check kernel: items = (query, database chunk)
+    int chunks = (int)std::max<int64_t>(1, std::min<int64_t>({(int64_t)8192 / k, (st.n + 255) / 256,
+                                                             (int64_t)sm_count(ix.device) * 32 / std::max<int64_t>(nq, 1) + 1}));
+    const int64_t per = (st.n + chunks - 1) / chunks;
+    chunks = (int)((st.n + per - 1) / per);
+    const int64_t n_items = nq * chunks;
+    std::vector<int32_t> iq((size_t)n_items);
+    std::vector<int64_t> rb((size_t)n_items), re((size_t)n_items);
+    for (int64_t q = 0; q < nq; q++)
+        for (int c = 0; c < chunks; c++) {
+            const int64_t i = q * chunks + c;
+            iq[i] = (int32_t)q;
+            rb[i] = c * per;
+            re[i] = std::min<int64_t>(st.n, (c + 1) * per);
+        }
+    if (ws.item_q.ensure(n_items * 4) || ws.item_rb.ensure(n_items * 8) || ws.item_re.ensure(n_items * 8) ||
+        ws.part_key.ensure((size_t)n_items * k * 4) || ws.part_idx.ensure((size_t)n_items * k * 4))
+        return -1;
+    ANN_CUDA_TRY(cudaMemcpyAsync(ws.item_q.ptr, iq.data(), n_items * 4, cudaMemcpyHostToDevice, stream));
+    ANN_CUDA_TRY(cudaMemcpyAsync(ws.item_rb.ptr, rb.data(), n_items * 8, cudaMemcpyHostToDevice, stream));
+    ANN_CUDA_TRY(cudaMemcpyAsync(ws.item_re.ptr, re.data(), n_items * 8, cudaMemcpyHostToDevice, stream));
+    ANN_CUDA_TRY(cudaStreamSynchronize(stream));  // the host vectors go out of scope
+    if (launch_scan_items(st.hi, st.lo, dp, d, x_dev, d, ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(),
+                          ws.item_re.as<int64_t>(), n_items, k, ix.metric, ws.part_key.as<float>(),
+                          ws.part_idx.as<int32_t>(), ix.device, stream))
+        return -1;
+    return launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, 0, nullptr, chunks, nq, k,
+                              ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream);
+}
+
+// ---- IVF: (re)build the CSR form after adds ------------------------------------------------------
+int ivf_finalize_lists(const ann_cuda_index &cix) {
+    std::lock_guard<std::mutex> lock(cix.build_mu);
+    if (!cix.csr_dirty) return 0;
+    ann_cuda_index &ix = const_cast<ann_cuda_index &>(cix);
+    const int64_t n = ix.rows;
+    std::vector<int64_t> off((size_t)ix.nlist + 1, 0);
+    for (int64_t i = 0; i < n; i++) off[(size_t)ix.row_list[i] + 1]++;
+    for (int64_t l = 0; l < ix.nlist; l++) off[l + 1] += off[l];
+    if (!ix.rows_sorted && n > 0) {
+        // stable counting sort by list: rows keep their add order inside a list
+        std::vector<int64_t> cursor(off.begin(), off.end() - 1), perm((size_t)n);
+        for (int64_t i = 0; i < n; i++) perm[(size_t)cursor[ix.row_list[i]]++] = i;
+        float *nv = nullptr;
+        int64_t *ni = nullptr, *dperm = nullptr;
+        const int64_t cap = std::max<int64_t>(n, 1);
+        if (cudaMalloc(&nv, (size_t)cap * ix.dp * 4) != cudaSuccess || cudaMalloc(&ni, (size_t)cap * 8) != cudaSuccess ||
+            cudaMalloc(&dperm, (size_t)n * 8) != cudaSuccess) {
+            cudaGetLastError();
+            if (nv) cudaFree(nv);
+            if (ni) cudaFree(ni);
+            if (dperm) cudaFree(dperm);
+            return set_error("out of device memory regrouping the inverted lists");
+        }
+        ANN_CUDA_TRY(cudaMemcpy(dperm, perm.data(), (size_t)n * 8, cudaMemcpyHostToDevice));
+        gather_rows_kernel<<<(unsigned)std::min<int64_t>((n + 7) / 8, 148 * 32), 256>>>(ix.vecs, ix.ids, dperm, n, ix.dp,
+                                                                                     nv, ni);
+        count_launch();
+        ANN_CUDA_TRY(cudaGetLastError());
+        ANN_CUDA_TRY(cudaDeviceSynchronize());
+        cudaFree(dperm);
+        cudaFree(ix.vecs);
+        cudaFree(ix.ids);
+        ix.vecs = nv;
+        ix.ids = ni;
+        ix.rows_cap = cap;
+        std::vector<int32_t> sorted_list((size_t)n);
+        for (int64_t i = 0; i < n; i++) sorted_list[i] = ix.row_list[perm[i]];
+        ix.row_list.swap(sorted_list);
+        ix.rows_sorted = true;
+    }
+    if (!ix.list_off) ANN_CUDA_TRY(cudaMalloc(&ix.list_off, (size_t)(ix.nlist + 1) * 8));
+    ANN_CUDA_TRY(cudaMemcpy(ix.list_off, off.data(), (size_t)(ix.nlist + 1) * 8, cudaMemcpyHostToDevice));
+    ix.list_off_host.swap(off);
+    ix.csr_dirty = false;
+    return 0;
+}
+
+int ivf_grow_rows(ann_cuda_index &ix, int64_t extra) {
+    if (ix.rows + extra <= ix.rows_cap) return 0;
+    int64_t want = std::max<int64_t>(ix.rows_cap * 2, 1024);
+    while (want < ix.rows + extra) want *= 2;
+    float *nv = nullptr;
+    int64_t *ni = nullptr;
+    if (cudaMalloc(&nv, (size_t)want * ix.dp * 4) != cudaSuccess || cudaMalloc(&ni, (size_t)want * 8) != cudaSuccess) {
+        cudaGetLastError();
+        if (nv) cudaFree(nv);
+        if (ni) cudaFree(ni);
+        return set_error("out of device memory growing the inverted lists to %lld rows", (long long)want);
+    }
+    if (ix.rows > 0) {
+        ANN_CUDA_TRY(cudaMemcpy(nv, ix.vecs, (size_t)ix.rows * ix.dp * 4, cudaMemcpyDeviceToDevice));
+        ANN_CUDA_TRY(cudaMemcpy(ni, ix.ids, (size_t)ix.rows * 8, cudaMemcpyDeviceToDevice));
+    }
+    if (ix.vecs) cudaFree(ix.vecs);
+    if (ix.ids) cudaFree(ix.ids);
+    ix.vecs = nv;
+    ix.ids = ni;
+    ix.rows_cap = want;
+    return 0;
+}
+
+bool ivf_owns(const ann_cuda_index &ix, int64_t list_no) { return list_no % ix.shard_count == ix.shard_rank; }
+
+// Nearest centroid of n device rows -> host vector.
+int ivf_assign_device(const ann_cuda_index &ix, const float *x_dev, int64_t n, std::vector<int32_t> &assign) {
+    assign.resize((size_t)n);
+    WsLease lease(&ix, nullptr, true);
+    if (!lease.ws) return -1;
+    Workspace &ws = *lease.ws;
+    cudaStream_t s = ws.own_stream;
+    for (int64_t q0 = 0; q0 < n; q0 += kQueryBlock) {
+        const int64_t nb = std::min(kQueryBlock, n - q0);
+        if (split_store_topk(ix, ix.store, ws, x_dev + q0 * ix.d, nb, 1, s)) return -1;
+        ANN_CUDA_TRY(cudaMemcpyAsync(assign.data() + q0, ws.sel_idx.ptr, (size_t)nb * 4, cudaMemcpyDeviceToHost, s));
+        ANN_CUDA_TRY(cudaStreamSynchronize(s));
+        if (*ws.status_host) return set_error("flat kernel gave up on a wait (code %d)", *ws.status_host);
+    }
+    return 0;
+}
+
+// Appends rows (device, n x d) with known lists and labels.
+int ivf_append(ann_cuda_index &ix, const float *x_dev, int64_t n, const int32_t *lists, const int64_t *labels) {
+    std::vector<int64_t> dst((size_t)n), kept_ids;
+    int64_t kept = 0;
+    for (int64_t i = 0; i < n; i++) {
+        if (lists[i] >= 0 && lists[i] < ix.nlist && ivf_owns(ix, lists[i])) {
+            dst[i] = ix.rows + kept++;
+        } else {
+            dst[i] = -1;
+        }
+    }
+    if (kept == 0) return 0;
+    if (ivf_grow_rows(ix, kept)) return -1;
+    kept_ids.reserve((size_t)kept);
+    for (int64_t i = 0; i < n; i++) {
+        if (dst[i] < 0) continue;
+        kept_ids.push_back(labels[i]);
+        if (!ix.row_list.empty() && lists[i] < ix.row_list.back()) ix.rows_sorted = false;
+        ix.row_list.push_back(lists[i]);
+    }
+    int64_t *ddst = nullptr;
+    ANN_CUDA_TRY(cudaMalloc(&ddst, (size_t)n * 8));
+    cudaError_t e = cudaMemcpy(ddst, dst.data(), (size_t)n * 8, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(ix.ids + ix.rows, kept_ids.data(), (size_t)kept * 8, cudaMemcpyHostToDevice);
+    int rc = 0;
+    if (e == cudaSuccess) rc = launch_scatter_rows(x_dev, n, ix.d, ix.dp, ddst, ix.vecs, nullptr);
+    if (e == cudaSuccess && rc == 0) e = cudaDeviceSynchronize();
+    cudaFree(ddst);
+    if (e != cudaSuccess) return set_error("appending rows failed: %s", cudaGetErrorString(e));
+    if (rc) return -1;
+    ix.rows += kept;
+    ix.csr_dirty = true;
+    return 0;
+}
+
+int ensure_device(const ann_cuda_index *ix, DeviceGuard &g) {
+    if (!g.ok) return set_error("cudaSetDevice(%d) failed", ix->device);
+    return 0;
+}
+
+// The whole search for one block of queries, all pointers on the device.
+int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const float *x_dev, int64_t k,
+                        float *d_dev, int64_t *i_dev, int64_t label_offset, cudaStream_t stream) {
+    if (!ix.ivf) {
+        const int k_sel = (int)std::min<int64_t>(k, ix.store.n);
+        if (split_store_topk(ix, ix.store, ws, x_dev, nq, k_sel, stream)) return -1;
+        return launch_refine_finalize(ix.store.hi, ix.store.lo, ix.dp, ix.d, x_dev, ix.d, ws.sel_idx.as<int32_t>(), nq,
+                                      k_sel, (int)k, ix.metric, nullptr, label_offset, d_dev, i_dev, ix.device, stream);
+    }
+    const int nprobe = (int)std::min<int64_t>(std::max<int64_t>(ix.nprobe, 1), ix.nlist);
+    const int k_sel = (int)std::min<int64_t>(k, kMaxK);
+    if ((int64_t)nprobe * k_sel > 8192)
+        return set_error("nprobe * k = %lld exceeds the 8192 candidates the merge step holds", (long long)nprobe * k_sel);
+    // coarse quantiser: nprobe nearest centroids under the index metric
+    if (split_store_topk(ix, ix.store, ws, x_dev, nq, nprobe, stream)) return -1;
+    const int64_t n_items = nq * nprobe;
+    if (ws.probes.ensure((size_t)n_items * 4) || ws.item_q.ensure(n_items * 4) || ws.item_rb.ensure(n_items * 8) ||
+        ws.item_re.ensure(n_items * 8) || ws.item_slot.ensure(n_items * 4) ||
+        ws.scratch.ensure((size_t)(ix.nlist + 1) * 2 * 4) || ws.part_key.ensure((size_t)n_items * k_sel * 4) ||
+        ws.part_idx.ensure((size_t)n_items * k_sel * 4))
+        return -1;
+    ANN_CUDA_TRY(cudaMemcpyAsync(ws.probes.ptr, ws.sel_idx.ptr, (size_t)n_items * 4, cudaMemcpyDeviceToDevice, stream));
+    if (launch_build_ivf_items(ws.probes.as<int32_t>(), nq, nprobe, ix.nlist, ix.list_off, ws.item_q.as<int32_t>(),
+                               ws.item_rb.as<int64_t>(), ws.item_re.as<int64_t>(), ws.item_slot.as<int32_t>(),
+                               ws.scratch.as<int>(), stream))
+        return -1;
+    if (launch_scan_items(ix.vecs, nullptr, ix.dp, ix.d, x_dev, ix.d, ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(),
+                          ws.item_re.as<int64_t>(), n_items, k_sel, ix.metric, ws.part_key.as<float>(),
+                          ws.part_idx.as<int32_t>(), ix.device, stream))
+        return -1;
+    if (ws.sel_key.ensure((size_t)nq * k_sel * 4) || ws.sel_idx.ensure((size_t)nq * k_sel * 4)) return -1;
+    if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, 0, ws.item_slot.as<int32_t>(), nprobe,
+                           nq, k_sel, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream))
+        return -1;
+    return launch_finalize(ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), nq, k_sel, (int)k, ix.metric, ix.ids,
+                           label_offset, d_dev, i_dev, stream);
+}
+
+int search_device_impl(const ann_cuda_index &ix, Workspace &ws, int64_t n, const float *x_dev, int64_t k, float *d_dev,
+                       int64_t *i_dev, int64_t label_offset, cudaStream_t stream) {
+    if (k <= 0) return set_error("k must be > 0");  // MetalIndexFlat.mm:297
+    if (n <= 0) return 0;
+    if (!ix.trained) return set_error("search: index must be trained first");  // MetalIndexIVFFlat.mm:125
+    const int64_t stored = ix.ivf ? ix.rows : ix.store.n;
+    if (ix.ntotal == 0 || stored == 0) return launch_fill_missing(d_dev, i_dev, n * k, ix.metric, stream);
+    if (!ix.ivf && std::min<int64_t>(k, ix.store.n) > kMaxK) return set_error("k is limited to %d", kMaxK);
+    if (ix.ivf && ivf_finalize_lists(ix)) return -1;
+    for (int64_t q0 = 0; q0 < n; q0 += kQueryBlock) {
+        const int64_t nb = std::min(kQueryBlock, n - q0);
+        if (search_block_device(ix, ws, nb, x_dev + q0 * ix.d, k, d_dev + q0 * k, i_dev + q0 * k, label_offset, stream))
+            return -1;
+    }
+    return 0;
+}
+
+int upload_and(ann_cuda_index *ix, int64_t n, const float *x_host,
+               int (*fn)(ann_cuda_index *, int64_t, const float *)) {
+    // host rows -> device in slabs of at most 256 MB
+    const int64_t slab = std::max<int64_t>(1, (256ll << 20) / ((int64_t)ix->d * 4));
+    float *buf = nullptr;
+    ANN_CUDA_TRY(cudaMalloc(&buf, (size_t)std::min(slab, n) * ix->d * 4));
+    int rc = 0;
+    for (int64_t r0 = 0; r0 < n && rc == 0; r0 += slab) {
+        const int64_t nb = std::min(slab, n - r0);
+        cudaError_t e = cudaMemcpy(buf, x_host + r0 * ix->d, (size_t)nb * ix->d * 4, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) {
+            rc = set_error("host to device copy failed: %s", cudaGetErrorString(e));
+            break;
+        }
+        rc = fn(ix, nb, buf);
+        if (rc == 0 && cudaDeviceSynchronize() != cudaSuccess) rc = set_error("device error during add");
+    }
+    cudaFree(buf);
+    return rc;
+}
+
+int add_device_impl(ann_cuda_index *ix, int64_t n, const float *x_dev) {
+    if (!ix->ivf) {
+        if (ix->store.append_device(x_dev, n, ix->d, nullptr)) return -1;
+        ANN_CUDA_TRY(cudaStreamSynchronize(nullptr));
+        ix->ntotal = ix->store.n;
+        return 0;
+    }
+    if (!ix->trained) return set_error("add: index must be trained first");  // MetalIndexIVFFlat.mm:103
+    std::vector<int32_t> assign;
+    if (ivf_assign_device(*ix, x_dev, n, assign)) return -1;
+    std::vector<int64_t> labels((size_t)n);
+    std::iota(labels.begin(), labels.end(), ix->ntotal);  // label = running ntotal (MetalIndexIVFFlat.mm:112)
+    if (ivf_append(*ix, x_dev, n, assign.data(), labels.data())) return -1;
+    ix->ntotal += n;
+    return 0;
+}
+
+}  // namespace
+
+// =================================================================================================
+extern "C" {
+
+const char *ann_cuda_last_error(void) { return last_error_ref().c_str(); }
+
+int ann_cuda_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+int ann_cuda_available(void) {
+    static int cached = -1;
+    if (cached >= 0) return cached;
+    const int n = ann_cuda_device_count();
+    int ok = n > 0;
+    for (int i = 0; i < n && ok; i++) {
+        cudaDeviceProp p;
+        if (cudaGetDeviceProperties(&p, i) != cudaSuccess || p.major != 10) ok = 0;
+    }
+    cached = ok;
+    return ok;
+}
+
+int ann_cuda_device_info(char *buf, size_t buflen) {
+    if (!buf || buflen == 0) return set_error("null buffer");
+    const int n = ann_cuda_device_count();
+    if (n <= 0) {
+        snprintf(buf, buflen, "CUDA: not available");
+        return 0;
+    }
+    cudaDeviceProp p;
+    ANN_CUDA_TRY(cudaGetDeviceProperties(&p, 0));
+    snprintf(buf, buflen, "CUDA GPU (%s, sm_%d%d, %d SMs, %.0f GB, %d device%s)", p.name, p.major, p.minor,
+             p.multiProcessorCount, (double)p.totalGlobalMem / 1e9, n, n == 1 ? "" : "s");
+    return 0;
+}
+
+const char *ann_cuda_flat_kernel_name(void) { return flat_kernel_choice() == FlatKernel::TC ? "tcgen05" : "simt"; }
+
+int ann_cuda_set_flat_kernel(const char *name) {
+    if (name && strcmp(name, "tcgen05") == 0) {
+        g_flat_kernel.store(0);
+        return 0;
+    }
+    if (name && strcmp(name, "simt") == 0) {
+        g_flat_kernel.store(1);
+        return 0;
+    }
+    return set_error("unknown flat kernel name (tcgen05 | simt)");
+}
+
+uint64_t ann_cuda_launch_count(void) { return launch_count_value(); }
+
+static int create_common(int device, int d, int metric, bool ivf, int64_t nlist, ann_cuda_index **out) {
+    if (!out) return set_error("null output handle");
+    *out = nullptr;
+    if (d <= 0) return set_error("dimension must be > 0");
+    if (metric != ANN_CUDA_METRIC_L2 && metric != ANN_CUDA_METRIC_INNER_PRODUCT)
+        return set_error("unsupported metric %d (L2 and inner product only)", metric);
+    if (ivf && nlist <= 0) return set_error("nlist must be > 0");
+    if (device < 0 || device >= ann_cuda_device_count()) return set_error("no CUDA device %d", device);
+    cudaDeviceProp p;
+    ANN_CUDA_TRY(cudaGetDeviceProperties(&p, device));
+    if (p.major != 10) return set_error("device %d is sm_%d%d; this library is built for sm_100a only", device, p.major, p.minor);
+    ann_cuda_index *ix = new ann_cuda_index();
+    ix->device = device;
+    ix->d = d;
+    ix->dp = pad_dim(d);
+    ix->metric = metric;
+    ix->ivf = ivf;
+    ix->store.dp = ix->dp;
+    ix->nlist = nlist;
+    ix->trained = !ivf;
+    *out = ix;
+    return 0;
+}
+
+int ann_cuda_flat_create(int device, int d, int metric, ann_cuda_index **out) {
+    return create_common(device, d, metric, false, 0, out);
+}
+
+int ann_cuda_ivfflat_create(int device, int d, int64_t nlist, int metric, ann_cuda_index **out) {
+    return create_common(device, d, metric, true, nlist, out);
+}
+
+void ann_cuda_index_free(ann_cuda_index *ix) {
+    if (!ix) return;
+    DeviceGuard g(ix->device);
+    cudaDeviceSynchronize();
+    ix->store.release_buffers();
+    if (ix->vecs) cudaFree(ix->vecs);
+    if (ix->ids) cudaFree(ix->ids);
+    if (ix->list_off) cudaFree(ix->list_off);
+    for (Workspace *w : ix->ws_free) {
+        w->release();
+        delete w;
+    }
+    delete ix;
+}
+
+int ann_cuda_ivfflat_set_centroids(ann_cuda_index *ix, const float *centroids) {
+    if (!ix || !ix->ivf || !centroids) return set_error("invalid arguments");
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    ix->store.n = 0;
+    float *buf = nullptr;
+    ANN_CUDA_TRY(cudaMalloc(&buf, (size_t)ix->nlist * ix->d * 4));
+    cudaError_t e = cudaMemcpy(buf, centroids, (size_t)ix->nlist * ix->d * 4, cudaMemcpyHostToDevice);
+    int rc = e == cudaSuccess ? ix->store.append_device(buf, ix->nlist, ix->d, nullptr) : set_error("centroid upload failed");
+    cudaDeviceSynchronize();
+    cudaFree(buf);
+    if (rc) return -1;
+    ix->trained = true;
+    return 0;
+}
+
+int ann_cuda_ivfflat_get_centroids(const ann_cuda_index *ix, float *centroids) {
+    if (!ix || !ix->ivf || !centroids) return set_error("invalid arguments");
+    if (!ix->trained) return set_error("index is not trained");
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    float *buf = nullptr;
+    ANN_CUDA_TRY(cudaMalloc(&buf, (size_t)ix->nlist * ix->d * 4));
+    int rc = launch_join_rows(ix->store.hi, ix->store.lo, ix->nlist, ix->d, ix->dp, buf, nullptr);
+    cudaError_t e = cudaMemcpy(centroids, buf, (size_t)ix->nlist * ix->d * 4, cudaMemcpyDeviceToHost);
+    cudaFree(buf);
+    if (rc) return -1;
+    if (e != cudaSuccess) return set_error("centroid download failed: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+int ann_cuda_ivfflat_train(ann_cuda_index *ix, int64_t n, const float *x) {
+    if (!ix || !ix->ivf || !x) return set_error("invalid arguments");
+    if (n < ix->nlist) return set_error("train: need at least nlist = %lld rows, got %lld", (long long)ix->nlist, (long long)n);
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    const int d = ix->d;
+    const int64_t nlist = ix->nlist;
+    float *dx = nullptr, *cent = nullptr, *sums = nullptr;
+    int *counts = nullptr;
+    int32_t *dassign = nullptr;
+    int rc = 0;
+    auto cleanup = [&] {
+        for (void *p : {(void *)dx, (void *)cent, (void *)sums, (void *)counts, (void *)dassign})
+            if (p) cudaFree(p);
+    };
+    if (cudaMalloc(&dx, (size_t)n * d * 4) != cudaSuccess || cudaMalloc(&cent, (size_t)nlist * d * 4) != cudaSuccess ||
+        cudaMalloc(&sums, (size_t)nlist * d * 4) != cudaSuccess || cudaMalloc(&counts, (size_t)nlist * 4) != cudaSuccess ||
+        cudaMalloc(&dassign, (size_t)n * 4) != cudaSuccess) {
+        cudaGetLastError();
+        cleanup();
+        return set_error("out of device memory in train");
+    }
+    cudaMemcpy(dx, x, (size_t)n * d * 4, cudaMemcpyHostToDevice);
+    // initial centroids: nlist rows spread evenly over the training set
+    for (int64_t c = 0; c < nlist; c++)
+        cudaMemcpy(cent + c * d, dx + (c * n / nlist) * d, (size_t)d * 4, cudaMemcpyDeviceToDevice);
+    const int saved_metric = ix->metric;
+    ix->metric = ANN_CUDA_METRIC_L2;  // Lloyd iterations assign by L2
+    ix->trained = true;
+    std::vector<int32_t> assign;
+    for (int it = 0; it < 10 && rc == 0; it++) {
+        ix->store.n = 0;
+        rc = ix->store.append_device(cent, nlist, d, nullptr);
+        if (rc == 0) rc = ivf_assign_device(*ix, dx, n, assign);
+        if (rc) break;
+        cudaMemcpy(dassign, assign.data(), (size_t)n * 4, cudaMemcpyHostToDevice);
+        cudaMemset(sums, 0, (size_t)nlist * d * 4);
+        cudaMemset(counts, 0, (size_t)nlist * 4);
+        kmeans_accumulate_kernel<<<(unsigned)std::min<int64_t>((n + 7) / 8, 148 * 16), 256>>>(dx, n, d, dassign, sums, counts);
+        kmeans_update_kernel<<<(unsigned)((nlist * d + 255) / 256), 256>>>(cent, sums, counts, nlist, d);
+        count_launch(2);
+        if (cudaDeviceSynchronize() != cudaSuccess) rc = set_error("device error in train");
+    }
+    ix->metric = saved_metric;
+    if (rc == 0) {
+        ix->store.n = 0;
+        rc = ix->store.append_device(cent, nlist, d, nullptr);
+        cudaDeviceSynchronize();
+    }
+    cleanup();
+    if (rc) {
+        ix->trained = false;
+        return -1;
+    }
+    return 0;
+}
+
+int ann_cuda_ivfflat_add_list(ann_cuda_index *ix, int64_t list_no, int64_t n, const int64_t *ids, const float *rows) {
+    if (!ix || !ix->ivf || list_no < 0 || list_no >= ix->nlist || n < 0 || (n > 0 && (!ids || !rows)))
+        return set_error("invalid arguments");
+    if (n == 0) return 0;
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    ix->ntotal += n;
+    if (!ivf_owns(*ix, list_no)) return 0;
+    float *buf = nullptr;
+    ANN_CUDA_TRY(cudaMalloc(&buf, (size_t)n * ix->d * 4));
+    cudaError_t e = cudaMemcpy(buf, rows, (size_t)n * ix->d * 4, cudaMemcpyHostToDevice);
+    int rc = 0;
+    if (e != cudaSuccess) {
+        rc = set_error("list upload failed: %s", cudaGetErrorString(e));
+    } else {
+        std::vector<int32_t> lists((size_t)n, (int32_t)list_no);
+        rc = ivf_append(*ix, buf, n, lists.data(), ids);
+    }
+    cudaFree(buf);
+    return rc;
+}
+
+int64_t ann_cuda_ivfflat_list_size(const ann_cuda_index *ix, int64_t list_no) {
+    if (!ix || !ix->ivf || list_no < 0 || list_no >= ix->nlist) return -1;
+    DeviceGuard g(ix->device);
+    if (ivf_finalize_lists(*ix)) return -1;
+    return ix->list_off_host[list_no + 1] - ix->list_off_host[list_no];
+}
+
+int ann_cuda_ivfflat_get_list(const ann_cuda_index *ix, int64_t list_no, int64_t *ids, float *rows) {
+    if (!ix || !ix->ivf || list_no < 0 || list_no >= ix->nlist) return set_error("invalid arguments");
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    if (ivf_finalize_lists(*ix)) return -1;
+    const int64_t b = ix->list_off_host[list_no], n = ix->list_off_host[list_no + 1] - b;
+    if (n == 0) return 0;
+    if (ids) ANN_CUDA_TRY(cudaMemcpy(ids, ix->ids + b, (size_t)n * 8, cudaMemcpyDeviceToHost));
+    if (rows)
+        ANN_CUDA_TRY(cudaMemcpy2D(rows, (size_t)ix->d * 4, ix->vecs + b * ix->dp, (size_t)ix->dp * 4, (size_t)ix->d * 4,
+                                  (size_t)n, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int ann_cuda_ivfflat_set_nprobe(ann_cuda_index *ix, int64_t nprobe) {
+    if (!ix || !ix->ivf) return set_error("not an IVFFlat index");
+    ix->nprobe = std::max<int64_t>(1, std::min(nprobe, ix->nlist));  // MetalIndexIVFFlat.mm:275-279
+    return 0;
+}
+int64_t ann_cuda_ivfflat_get_nprobe(const ann_cuda_index *ix) { return ix && ix->ivf ? ix->nprobe : -1; }
+int64_t ann_cuda_ivfflat_nlist(const ann_cuda_index *ix) { return ix && ix->ivf ? ix->nlist : -1; }
+
+int ann_cuda_ivfflat_set_shard(ann_cuda_index *ix, int shard_rank, int shard_count) {
+    if (!ix || !ix->ivf || shard_count <= 0 || shard_rank < 0 || shard_rank >= shard_count)
+        return set_error("invalid shard arguments");
+    if (ix->rows > 0) return set_error("set_shard must be called before rows are added");
+    ix->shard_rank = shard_rank;
+    ix->shard_count = shard_count;
+    return 0;
+}
+
+int ann_cuda_index_reserve(ann_cuda_index *ix, int64_t n_total) {
+    if (!ix || n_total < 0) return set_error("invalid arguments");
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    if (!ix->ivf) return ix->store.reserve(n_total);
+    return n_total > ix->rows ? ivf_grow_rows(*ix, n_total - ix->rows) : 0;
+}
+
+int ann_cuda_index_add_device(ann_cuda_index *ix, int64_t n, const float *x_device) {
+    if (!ix || n < 0 || (n > 0 && !x_device)) return set_error("invalid arguments");
+    if (n == 0) return 0;
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    return add_device_impl(ix, n, x_device);
+}
+
+int ann_cuda_index_add(ann_cuda_index *ix, int64_t n, const float *x) {
+    if (!ix || n < 0 || (n > 0 && !x)) return set_error("invalid arguments");
+    if (n == 0) return 0;
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    if (!ix->ivf && ix->store.grow_for(n)) return -1;
+    return upload_and(ix, n, x, add_device_impl);
+}
+
+int ann_cuda_index_search_device(const ann_cuda_index *ix, int64_t n, const float *x_device, int64_t k,
+                                 float *distances_device, int64_t *labels_device, int64_t label_offset, void *stream) {
+    if (!ix || n < 0 || (n > 0 && (!x_device || !distances_device || !labels_device)))
+        return set_error("invalid arguments");
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    WsLease lease(ix, s, false);
+    if (!lease.ws) return -1;
+    if (*lease.ws->status_host) {
+        const int code = *lease.ws->status_host;
+        *lease.ws->status_host = 0;
+        return set_error("an earlier search on this stream gave up on a wait inside the flat kernel (code %d)", code);
+    }
+    return search_device_impl(*ix, *lease.ws, n, x_device, k, distances_device, labels_device, label_offset, s);
+}
+
+int ann_cuda_index_search(const ann_cuda_index *ix, int64_t n, const float *x, int64_t k, float *distances,
+                          int64_t *labels) {
+    if (!ix || n < 0 || (n > 0 && (!x || !distances || !labels))) return set_error("invalid arguments");
+    if (k <= 0) return set_error("k must be > 0");
+    if (n == 0) return 0;
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    WsLease lease(ix, nullptr, true);
+    if (!lease.ws) return -1;
+    Workspace &ws = *lease.ws;
+    cudaStream_t s = ws.own_stream;
+    // query blocks keep the staging buffers bounded
+    for (int64_t q0 = 0; q0 < n; q0 += kQueryBlock) {
+        const int64_t nb = std::min(kQueryBlock, n - q0);
+        if (ws.x.ensure((size_t)nb * ix->d * 4) || ws.out_d.ensure((size_t)nb * k * 4) || ws.out_i.ensure((size_t)nb * k * 8))
+            return -1;
+        ANN_CUDA_TRY(cudaMemcpyAsync(ws.x.ptr, x + q0 * ix->d, (size_t)nb * ix->d * 4, cudaMemcpyHostToDevice, s));
+        *ws.status_host = 0;
+        if (search_device_impl(*ix, ws, nb, ws.x.as<float>(), k, ws.out_d.as<float>(), ws.out_i.as<int64_t>(), 0, s))
+            return -1;
+        ANN_CUDA_TRY(cudaMemcpyAsync(distances + q0 * k, ws.out_d.ptr, (size_t)nb * k * 4, cudaMemcpyDeviceToHost, s));
+        ANN_CUDA_TRY(cudaMemcpyAsync(labels + q0 * k, ws.out_i.ptr, (size_t)nb * k * 8, cudaMemcpyDeviceToHost, s));
+        ANN_CUDA_TRY(cudaStreamSynchronize(s));
+        if (*ws.status_host) {
+            const int code = *ws.status_host;
+            *ws.status_host = 0;
+            return set_error("flat kernel gave up on a wait (code %d)", code);
+        }
+    }
+    return 0;
+}
+
+int ann_cuda_index_reset(ann_cuda_index *ix) {
+    if (!ix) return set_error("null index");
+    DeviceGuard g(ix->device);
+    cudaDeviceSynchronize();
+    ix->ntotal = 0;
+    if (!ix->ivf) {
+        ix->store.n = 0;
+    } else {
+        ix->rows = 0;
+        ix->row_list.clear();
+        ix->rows_sorted = true;
+        ix->csr_dirty = true;
+    }
+    return 0;
+}
+
+int ann_cuda_index_reconstruct(const ann_cuda_index *ix, int64_t key, float *recons) {
+    if (!ix || !recons) return set_error("invalid arguments");
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    if (!ix->ivf) {
+        if (key < 0 || key >= ix->store.n) return set_error("reconstruct: key %lld out of range", (long long)key);
+        return ann_cuda_flat_get_rows(ix, key, 1, recons);
+    }
+    if (ix->rows == 0) return set_error("reconstruct: key %lld not found", (long long)key);
+    long long *found = nullptr, h = 0x7fffffffffffffffll;
+    ANN_CUDA_TRY(cudaMalloc(&found, 8));
+    cudaMemcpy(found, &h, 8, cudaMemcpyHostToDevice);
+    find_id_kernel<<<(unsigned)((ix->rows + 255) / 256), 256>>>(ix->ids, ix->rows, key, found);
+    count_launch();
+    cudaMemcpy(&h, found, 8, cudaMemcpyDeviceToHost);
+    cudaFree(found);
+    if (h == 0x7fffffffffffffffll) return set_error("reconstruct: key %lld not found", (long long)key);
+    ANN_CUDA_TRY(cudaMemcpy(recons, ix->vecs + h * ix->dp, (size_t)ix->d * 4, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int ann_cuda_flat_get_rows(const ann_cuda_index *ix, int64_t first, int64_t n, float *rows) {
+    if (!ix || ix->ivf || !rows || first < 0 || n < 0 || first + n > ix->store.n) return set_error("invalid arguments");
+    if (n == 0) return 0;
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    const int64_t slab = std::max<int64_t>(1, (256ll << 20) / ((int64_t)ix->d * 4));
+    float *buf = nullptr;
+    ANN_CUDA_TRY(cudaMalloc(&buf, (size_t)std::min(slab, n) * ix->d * 4));
+    int rc = 0;
+    for (int64_t r0 = 0; r0 < n && rc == 0; r0 += slab) {
+        const int64_t nb = std::min(slab, n - r0);
+        rc = launch_join_rows(ix->store.hi + (first + r0) * ix->dp, ix->store.lo + (first + r0) * ix->dp, nb, ix->d,
+                              ix->dp, buf, nullptr);
+        if (rc == 0 && cudaMemcpy(rows + r0 * ix->d, buf, (size_t)nb * ix->d * 4, cudaMemcpyDeviceToHost) != cudaSuccess)
+            rc = set_error("device to host copy failed");
+    }
+    cudaFree(buf);
+    return rc;
+}
+
+int64_t ann_cuda_index_ntotal(const ann_cuda_index *ix) { return ix ? ix->ntotal : -1; }
+int ann_cuda_index_d(const ann_cuda_index *ix) { return ix ? ix->d : -1; }
+int ann_cuda_index_metric(const ann_cuda_index *ix) { return ix ? ix->metric : -1; }
+int ann_cuda_index_is_trained(const ann_cuda_index *ix) { return ix ? (int)ix->trained : 0; }
+int ann_cuda_index_is_ivf(const ann_cuda_index *ix) { return ix ? (int)ix->ivf : 0; }
+int ann_cuda_index_device(const ann_cuda_index *ix) { return ix ? ix->device : -1; }
+
+int ann_cuda_merge_topk_device(int device, const float *parts_distances, const int64_t *parts_labels, int nparts,
+                               int64_t nq, int64_t k, int metric, float *out_distances, int64_t *out_labels,
+                               void *stream) {
+    if (!parts_distances || !parts_labels || !out_distances || !out_labels || nparts <= 0 || nq < 0 || k <= 0)
+        return set_error("invalid arguments");
+    DeviceGuard g(device);
+    if (!g.ok) return set_error("cudaSetDevice(%d) failed", device);
+    return launch_merge_results(parts_distances, parts_labels, nparts, nq, (int)k, metric, out_distances, out_labels,
+                                device, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

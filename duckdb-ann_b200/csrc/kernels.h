@@ -1,0 +1,105 @@
+// Launchers shared between the translation units of the CUDA search library.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace anncuda {
+
+// Rows are stored padded to a multiple of kDimPad floats so that every row is a
+// whole number of 128-byte TMA boxes.
+constexpr int kDimPad = 32;
+constexpr int kMaxK = 2048;  // largest k a search accepts
+
+inline int pad_dim(int d) { return (d + kDimPad - 1) / kDimPad * kDimPad; }
+
+uint64_t launch_count_value();
+void count_launch(int n = 1);
+
+// ---- prep.cu -----------------------------------------------------------------------------
+// x (n x d, row stride d) -> hi, lo (n x dp each): hi = x rounded to TF32, lo = x - hi
+// (exact in fp32, so hi + lo reconstructs x bit for bit); pad columns are zero;
+// norms[i] = sum x^2 in fp32 (may be nullptr).
+int launch_split_rows(const float *x, int64_t n, int d, int dp, float *hi, float *lo, float *norms,
+                      cudaStream_t stream);
+// x (n x d) -> out (n x dp) zero padded, norms (may be nullptr).
+int launch_pad_rows(const float *x, int64_t n, int d, int dp, float *out, float *norms, cudaStream_t stream);
+// out (n x d) <- hi + lo (n x dp)
+int launch_join_rows(const float *hi, const float *lo, int64_t n, int d, int dp, float *out, cudaStream_t stream);
+
+// ---- flat_tc.cu --------------------------------------------------------------------------
+struct FlatPlan {
+    int nq_tiles = 0;      // ceil(nq / 128)
+    int chunks = 0;        // database chunks (partial lists per query)
+    int tiles_per_chunk = 0;
+    int units = 0;         // nq_tiles * chunks
+    int grid = 0;
+    size_t part_entries = 0;  // units * 128 * k
+};
+// Chooses the decomposition for nq queries against n rows on a device with `sms` SMs.
+FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms);
+
+// Fused split-TF32 GEMM + k-selection on the tensor cores.  Inputs are hi/lo row
+// stores of the database (n x dp) and the queries (nq x dp), plus row norms for L2.
+// Writes, per work unit, 128 unsorted lists of k (key, local row) pairs.
+// status: device int, set non-zero if a bounded wait inside the kernel ran out.
+int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
+                   const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
+                   int32_t *part_idx, int *status, int device, cudaStream_t stream);
+
+// ---- scan.cu -----------------------------------------------------------------------------
+// Exact-fp32 scan of row ranges with warp k-selection: one warp per (query, range)
+// item.  Item i scans rows [range_begin[i], range_end[i]) for query item_query[i] and
+// writes an unsorted list of k (key, row) at part_*[i * k ...].  Rows are read from
+// `x` (n x dp); when `xlo` is non-null the row is x + xlo (a split store).
+// key = squared L2 distance, or negated dot.
+int launch_scan_items(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
+                      const int32_t *item_query, const int64_t *range_begin, const int64_t *range_end,
+                      int64_t n_items, int k, int metric, float *part_key, int32_t *part_idx, int device,
+                      cudaStream_t stream);
+
+// Builds the (query, list) items of an IVF search from the coarse result:
+// probes (nq x nprobe) int32 list numbers (-1 = none); items are grouped by list so
+// that warps scanning the same list run together.  Outputs arrays of nq*nprobe items;
+// the item of (q, p) is written at slot perm[q*nprobe+p].  `scratch` needs
+// (nlist + 1) * 2 ints.
+int launch_build_ivf_items(const int32_t *probes, int64_t nq, int nprobe, int64_t nlist, const int64_t *list_off,
+                           int32_t *item_query, int64_t *range_begin, int64_t *range_end, int32_t *item_slot,
+                           int *scratch, cudaStream_t stream);
+
+// ---- merge.cu ----------------------------------------------------------------------------
+// Per query: the k best of `nparts` unsorted lists, sorted best first.
+// The list of (query q, part p) starts at part_*[(p * part_stride_p + q_major(q)) * k].
+// Layout kinds: 0 = flat units (unit = p * nq_tiles + q / 128, row q % 128),
+//               1 = item slots (slot_of[q * nparts + p], or q * nparts + p if null).
+int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layout, int nq_tiles,
+                       const int32_t *slot_of, int nparts, int64_t nq, int k, float *out_key, int32_t *out_idx,
+                       int device, cudaStream_t stream);
+
+// Flat: recomputes the distance of every selected (query, row) pair in exact fp32
+// from the split store, sorts the k results best first and writes the user-facing
+// distances (squared L2 / raw dot) and int64 labels (row + label_offset, or
+// ids[row] when ids is non-null).  Empty slots -> (+-inf, -1).
+int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, const float *queries, int q_stride,
+                           const int32_t *sel_idx, int64_t nq, int k_sel, int k_out, int metric,
+                           const int64_t *ids, int64_t label_offset, float *out_d, int64_t *out_i, int device,
+                           cudaStream_t stream);
+
+// Already-exact keys: just convert to user-facing values and labels, padding to k_out.
+int launch_finalize(const float *sel_key, const int32_t *sel_idx, int64_t nq, int k_sel, int k_out, int metric,
+                    const int64_t *ids, int64_t label_offset, float *out_d, int64_t *out_i, cudaStream_t stream);
+
+// Multi-GPU: k best of nparts sorted (distance, label) runs per query.
+int launch_merge_results(const float *parts_d, const int64_t *parts_i, int nparts, int64_t nq, int k, int metric,
+                         float *out_d, int64_t *out_i, int device, cudaStream_t stream);
+
+// Fills n (distance, label) slots with the "missing" sentinel.
+int launch_fill_missing(float *d, int64_t *i, int64_t n, int metric, cudaStream_t stream);
+
+// IVF add: scatter rows into their lists.  dst_row[i] is the destination row (or -1 to drop).
+int launch_scatter_rows(const float *x, int64_t n, int d, int dp, const int64_t *dst_row, float *store,
+                        cudaStream_t stream);
+
+}  // namespace anncuda

@@ -1,0 +1,234 @@
+// Exact-fp32 scan of row ranges with fused warp k-selection.
+//
+// One warp owns one (query, row range) item: it streams the rows with 16-byte
+// coalesced loads (lanes across the dimension), reduces each row's distance with
+// warp shuffles and keeps the k best in a register-resident replace-max list, so
+// no distance ever goes to memory.  Two callers:
+//   - IVFFlat list scan: the item is (query, probed inverted list); this replaces
+//     the reference's per-query host gather + distance + select
+//     (faiss-metal/src/MetalIndexIVFFlat.mm:149-250) with lists resident in HBM;
+//   - the "simt" flat kernel: items are (query, database chunk); same arithmetic as
+//     the reference's fused_l2_topk_min / fused_ip_topk_max shaders
+//     (faiss-metal/shaders/fused_l2_topk.metal:18,135) and used as an on-device
+//     cross-check of the tensor-core path.
+// Distances are the direct forms sum (q-x)^2 and sum q*x in fp32.
+#include "common.cuh"
+#include "kernels.h"
+#include "select.cuh"
+
+namespace anncuda {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kRows = 8;  // rows in flight per warp
+
+__device__ __forceinline__ float4 ld_row4(const float4 *p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <int KR>
+__global__ void __launch_bounds__(kWarps * 32)
+scan_items_kernel(const float *__restrict__ x, const float *__restrict__ xlo, int dp, int d,
+                  const float *__restrict__ queries, int q_stride, const int32_t *__restrict__ item_query,
+                  const int64_t *__restrict__ range_begin, const int64_t *__restrict__ range_end, int64_t n_items,
+                  int k, int metric, float *__restrict__ part_key, int32_t *__restrict__ part_idx) {
+    extern __shared__ float4 smem_q4[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float *myq = reinterpret_cast<float *>(smem_q4) + (size_t)warp * dp;
+    const float4 *myq4 = reinterpret_cast<const float4 *>(myq);
+    const bool l2 = metric != 0;  // FAISS codes: 1 = L2, 0 = inner product
+    const int n4 = dp >> 2;
+    for (int64_t item = (int64_t)blockIdx.x * kWarps + warp; item < n_items; item += (int64_t)gridDim.x * kWarps) {
+        const int q = item_query[item];
+        const int64_t begin = range_begin[item], end = range_end[item];
+        float *lk = part_key + item * (int64_t)k;
+        int32_t *li = part_idx + item * (int64_t)k;
+        WarpList<KR> list;
+        list.fill_empty(k, lane);
+        for (int slot = lane; slot < k; slot += 32) li[slot] = -1;
+        float m;
+        int pos;
+        list.argmax(lane, m, pos);
+        if (q >= 0 && begin < end) {
+            __syncwarp();
+            for (int c = lane; c < dp; c += 32) myq[c] = c < d ? queries[(int64_t)q * q_stride + c] : 0.f;
+            __syncwarp();
+            for (int64_t row0 = begin; row0 < end; row0 += kRows) {
+                const int nrows = (int)((end - row0) < kRows ? (end - row0) : kRows);
+                float acc[kRows];
+#pragma unroll
+                for (int r = 0; r < kRows; r++) acc[r] = 0.f;
+                for (int c4 = lane; c4 < n4; c4 += 32) {
+                    const float4 qv = myq4[c4];
+                    float4 xv[kRows];
+#pragma unroll
+                    for (int r = 0; r < kRows; r++) {
+                        if (r < nrows) {
+                            const int64_t off = (row0 + r) * (int64_t)n4 + c4;
+                            xv[r] = ld_row4(reinterpret_cast<const float4 *>(x) + off);
+                            if (xlo) {
+                                float4 t = ld_row4(reinterpret_cast<const float4 *>(xlo) + off);
+                                xv[r].x += t.x; xv[r].y += t.y; xv[r].z += t.z; xv[r].w += t.w;
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int r = 0; r < kRows; r++) {
+                        if (r < nrows) {
+                            if (l2) {
+                                float a = qv.x - xv[r].x, b = qv.y - xv[r].y, c = qv.z - xv[r].z, e = qv.w - xv[r].w;
+                                acc[r] = fmaf(a, a, acc[r]);
+                                acc[r] = fmaf(b, b, acc[r]);
+                                acc[r] = fmaf(c, c, acc[r]);
+                                acc[r] = fmaf(e, e, acc[r]);
+                            } else {
+                                acc[r] = fmaf(qv.x, xv[r].x, acc[r]);
+                                acc[r] = fmaf(qv.y, xv[r].y, acc[r]);
+                                acc[r] = fmaf(qv.z, xv[r].z, acc[r]);
+                                acc[r] = fmaf(qv.w, xv[r].w, acc[r]);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < kRows; r++) acc[r] = warp_sum(acc[r]);
+#pragma unroll
+                for (int r = 0; r < kRows; r++) {
+                    if (r < nrows) {
+                        const float key = l2 ? acc[r] : -acc[r];
+                        if (key < m) {  // warp-uniform: every lane holds the same sum
+                            if (lane == (pos & 31)) li[pos] = (int32_t)(row0 + r);
+                            list.set(pos, key, lane);
+                            list.argmax(lane, m, pos);
+                        }
+                    }
+                }
+            }
+        }
+        list.store(lk, k, lane);
+    }
+}
+
+// ---- IVF item construction ------------------------------------------------------------------
+__global__ void ivf_count_kernel(const int32_t *__restrict__ probes, int64_t n, int64_t nlist, int *counts) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int l = probes[i];
+    atomicAdd(&counts[(l >= 0 && l < nlist) ? l : nlist], 1);
+}
+
+// Exclusive scan of nlist+1 counters by one block; cursors[i] = start of bucket i.
+__global__ void ivf_scan_kernel(const int *__restrict__ counts, int *__restrict__ cursors, int64_t nbuckets) {
+    __shared__ int carry;
+    __shared__ int warp_tot[32];
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int64_t base = 0; base < nbuckets; base += blockDim.x) {
+        int64_t i = base + threadIdx.x;
+        int v = i < nbuckets ? counts[i] : 0;
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int t = __shfl_up_sync(kFullMask, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = lane < (int)(blockDim.x >> 5) ? warp_tot[lane] : 0;
+            int wi = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                int t = __shfl_up_sync(kFullMask, wi, o);
+                if (lane >= o) wi += t;
+            }
+            warp_tot[lane] = wi - w;  // exclusive prefix of the warp totals
+        }
+        __syncthreads();
+        int excl = carry + warp_tot[warp] + incl - v;
+        if (i < nbuckets) cursors[i] = excl;
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry = excl + v;
+        __syncthreads();
+    }
+}
+
+__global__ void ivf_place_kernel(const int32_t *__restrict__ probes, int64_t n, int nprobe, int64_t nlist,
+                                 const int64_t *__restrict__ list_off, int *cursors,
+                                 int32_t *__restrict__ item_query, int64_t *__restrict__ range_begin,
+                                 int64_t *__restrict__ range_end, int32_t *__restrict__ item_slot) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int l = probes[i];
+    const bool ok = l >= 0 && l < nlist;
+    int slot = atomicAdd(&cursors[ok ? l : nlist], 1);
+    item_slot[i] = slot;
+    item_query[slot] = ok ? (int32_t)(i / nprobe) : -1;
+    range_begin[slot] = ok ? list_off[l] : 0;
+    range_end[slot] = ok ? list_off[l + 1] : 0;
+}
+
+template <int KR>
+int launch_scan_kr(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
+                   const int32_t *item_query, const int64_t *rb, const int64_t *re, int64_t n_items, int k,
+                   int metric, float *part_key, int32_t *part_idx, int device, cudaStream_t stream) {
+    const size_t smem = (size_t)kWarps * dp * sizeof(float);
+    if (smem > 48 * 1024) {
+        ANN_CUDA_TRY(cudaFuncSetAttribute(scan_items_kernel<KR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)smem));
+    }
+    int64_t blocks = (n_items + kWarps - 1) / kWarps;
+    const int64_t cap = (int64_t)sm_count(device) * 16;
+    if (blocks > cap) blocks = cap;
+    scan_items_kernel<KR><<<(unsigned)blocks, kWarps * 32, smem, stream>>>(
+        x, xlo, dp, d, queries, q_stride, item_query, rb, re, n_items, k, metric, part_key, part_idx);
+    count_launch();
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace
+
+int launch_scan_items(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
+                      const int32_t *item_query, const int64_t *range_begin, const int64_t *range_end,
+                      int64_t n_items, int k, int metric, float *part_key, int32_t *part_idx, int device,
+                      cudaStream_t stream) {
+    if (n_items <= 0) return 0;
+    if (k <= 0 || k > kMaxK) return set_error("k must be in [1, %d]", kMaxK);
+    if ((size_t)kWarps * dp * sizeof(float) > 200 * 1024) return set_error("dimension %d too large for the scan kernel", d);
+    if (k <= 32)
+        return launch_scan_kr<1>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k,
+                                 metric, part_key, part_idx, device, stream);
+    if (k <= 128)
+        return launch_scan_kr<4>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k,
+                                 metric, part_key, part_idx, device, stream);
+    if (k <= 512)
+        return launch_scan_kr<16>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k,
+                                  metric, part_key, part_idx, device, stream);
+    return launch_scan_kr<64>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k, metric,
+                              part_key, part_idx, device, stream);
+}
+
+int launch_build_ivf_items(const int32_t *probes, int64_t nq, int nprobe, int64_t nlist, const int64_t *list_off,
+                           int32_t *item_query, int64_t *range_begin, int64_t *range_end, int32_t *item_slot,
+                           int *scratch, cudaStream_t stream) {
+    const int64_t n = nq * nprobe;
+    if (n <= 0) return 0;
+    int *counts = scratch, *cursors = scratch + (nlist + 1);
+    ANN_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)(nlist + 1), stream));
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    ivf_count_kernel<<<blocks, 256, 0, stream>>>(probes, n, nlist, counts);
+    ivf_scan_kernel<<<1, 1024, 0, stream>>>(counts, cursors, nlist + 1);
+    ivf_place_kernel<<<blocks, 256, 0, stream>>>(probes, n, nprobe, nlist, list_off, cursors, item_query,
+                                                 range_begin, range_end, item_slot);
+    count_launch(3);
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace anncuda

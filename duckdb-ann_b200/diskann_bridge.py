@@ -1,0 +1,165 @@
+"""Host-side wrappers of the DiskANN batch-distance ABI.
+
+`metal_batch_distances` / `metal_multi_batch_distances` mirror the safe wrappers
+of rust_lib/src/metal_ffi.rs:67-141 (same names, same gating and return
+convention: True = `out` is valid, False = caller must use its CPU loop), with
+the thresholds re-derived for a discrete GPU.  `DeviceTable` wraps the
+device-resident table entry points.  `cuda_ffi.rs` beside the CUDA sources is
+the Rust form of this file.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+# Minimum n*dim for one call to be worth a launch plus two PCIe copies.  The
+# reference uses 131072 (iterative search) and 49152 (one-shot) for Metal's
+# ~100-450 us dispatch (rust_lib/src/metal_ffi.rs:36-46); a CUDA launch with
+# pageable copies costs ~20-30 us, so the break-even moves down.
+MIN_GPU_WORK = 65536
+MIN_GPU_WORK_ONESHOT = 32768
+
+_status = -1  # cached availability: -1 unchecked, 0 no, 1 yes (metal_ffi.rs:33,49-57)
+
+
+def _pkg():
+    import sys
+    return sys.modules[__name__.rsplit(".", 1)[0]]
+
+
+def _p(a):
+    return C.c_void_p(a.ctypes.data) if a is not None else None
+
+
+def is_metal_available() -> bool:
+    """Name kept from metal_ffi.rs:49; reports the CUDA bridge."""
+    global _status
+    if _status < 0:
+        _status = int(_pkg().lib().diskann_metal_available())
+    return _status == 1
+
+
+def metal_batch_distances(query, candidates, n: int, dim: int, metric: int, out) -> bool:
+    """metal_ffi.rs:67-96.  query (dim,), candidates (n*dim,), out (>= n)."""
+    if n == 0 or dim == 0:
+        return True
+    if n * dim < MIN_GPU_WORK or not is_metal_available():
+        return False
+    return batch_distances_raw(query, candidates, n, dim, metric, out) == 0
+
+
+def metal_multi_batch_distances(queries, candidates, query_map, total_n: int, nq: int, dim: int, metric: int,
+                                out) -> bool:
+    """metal_ffi.rs:107-141.  Does not check MIN_GPU_WORK: the caller does."""
+    if total_n == 0 or nq == 0 or dim == 0:
+        return True
+    if not is_metal_available():
+        return False
+    return multi_batch_distances_raw(queries, candidates, query_map, total_n, nq, dim, metric, out) == 0
+
+
+def batch_distances_raw(query, candidates, n, dim, metric, out) -> int:
+    """diskann_metal_batch_distances, ungated; returns the C return code."""
+    q = np.ascontiguousarray(query, np.float32) if query is not None else None
+    c = np.ascontiguousarray(candidates, np.float32) if candidates is not None else None
+    return int(_pkg().lib().diskann_metal_batch_distances(_p(q), _p(c), n, dim, metric, _p(out)))
+
+
+def multi_batch_distances_raw(queries, candidates, query_map, total_n, nq, dim, metric, out) -> int:
+    q = np.ascontiguousarray(queries, np.float32) if queries is not None else None
+    c = np.ascontiguousarray(candidates, np.float32) if candidates is not None else None
+    m = np.ascontiguousarray(query_map, np.uint32) if query_map is not None else None
+    return int(_pkg().lib().diskann_metal_multi_batch_distances(_p(q), _p(c), _p(m), total_n, nq, dim, metric,
+                                                               _p(out)))
+
+
+class DeviceTable:
+    """A vector table resident in GPU memory (fp32 rows, or SQ8 codes + min/scale),
+    scored by row id: diskann_cuda_register_* / diskann_cuda_batch_distances_by_id."""
+
+    def __init__(self, handle, num: int, dim: int, sq8: bool, keepalive=None):
+        self._h = handle
+        self.num, self.dim, self.sq8 = num, dim, sq8
+        self._keepalive = keepalive
+
+    @staticmethod
+    def from_host(rows, device: int = 0) -> "DeviceTable":
+        rows = np.ascontiguousarray(rows, np.float32)
+        h = C.c_void_p()
+        p = _pkg()
+        p.check(p.lib().diskann_cuda_register_table(device, _p(rows), rows.shape[0], rows.shape[1], C.byref(h)),
+                "register_table")
+        return DeviceTable(h, rows.shape[0], rows.shape[1], False)
+
+    @staticmethod
+    def from_device(rows) -> "DeviceTable":
+        """rows: contiguous float32 torch CUDA tensor (num, dim); kept alive by the table."""
+        h = C.c_void_p()
+        p = _pkg()
+        p.check(p.lib().diskann_cuda_register_table_device(rows.device.index or 0, C.c_void_p(rows.data_ptr()),
+                                                           rows.shape[0], rows.shape[1], C.byref(h)),
+                "register_table_device")
+        return DeviceTable(h, rows.shape[0], rows.shape[1], False, keepalive=rows)
+
+    @staticmethod
+    def sq8_from_host(codes, mins, scale, device: int = 0) -> "DeviceTable":
+        codes = np.ascontiguousarray(codes, np.uint8)
+        mins = np.ascontiguousarray(mins, np.float32)
+        scale = np.ascontiguousarray(scale, np.float32)
+        h = C.c_void_p()
+        p = _pkg()
+        p.check(p.lib().diskann_cuda_register_sq8(device, _p(codes), _p(mins), _p(scale), codes.shape[0],
+                                                  codes.shape[1], C.byref(h)), "register_sq8")
+        return DeviceTable(h, codes.shape[0], codes.shape[1], True)
+
+    @staticmethod
+    def sq8_from_device(codes, mins, scale) -> "DeviceTable":
+        """codes: contiguous uint8 torch CUDA tensor; mins/scale: host float32 arrays."""
+        mins = np.ascontiguousarray(mins, np.float32)
+        scale = np.ascontiguousarray(scale, np.float32)
+        h = C.c_void_p()
+        p = _pkg()
+        p.check(p.lib().diskann_cuda_register_sq8_device(codes.device.index or 0, C.c_void_p(codes.data_ptr()),
+                                                         _p(mins), _p(scale), codes.shape[0], codes.shape[1],
+                                                         C.byref(h)), "register_sq8_device")
+        return DeviceTable(h, codes.shape[0], codes.shape[1], True, keepalive=codes)
+
+    def batch_distances_by_id(self, queries, ids, query_map, metric: int):
+        """Host buffers in, host distances out (synchronous)."""
+        q = np.ascontiguousarray(queries, np.float32).reshape(-1, self.dim)
+        ids = np.ascontiguousarray(ids, np.uint32)
+        qm = None if query_map is None else np.ascontiguousarray(query_map, np.uint32)
+        out = np.empty(ids.shape[0], np.float32)
+        p = _pkg()
+        p.check(p.lib().diskann_cuda_batch_distances_by_id(self._h, _p(q), q.shape[0], _p(ids), _p(qm),
+                                                           ids.shape[0], metric, _p(out)), "batch_distances_by_id")
+        return out
+
+    def batch_distances_by_id_device(self, queries, ids, query_map, metric: int, out=None, stream=None):
+        """torch CUDA tensors in and out; enqueued on `stream`, not synchronised.
+        ids / query_map are int32 tensors holding the uint32 values."""
+        import torch
+        nq = queries.shape[0]
+        total_n = ids.shape[0]
+        if out is None:
+            out = torch.empty(total_n, dtype=torch.float32, device=queries.device)
+        s = stream if stream is not None else torch.cuda.current_stream(queries.device)
+        p = _pkg()
+        p.check(p.lib().diskann_cuda_batch_distances_by_id_device(
+            self._h, C.c_void_p(queries.data_ptr()), nq, C.c_void_p(ids.data_ptr()),
+            C.c_void_p(query_map.data_ptr()) if query_map is not None else None, total_n, metric,
+            C.c_void_p(out.data_ptr()), C.c_void_p(s.cuda_stream)), "batch_distances_by_id_device")
+        return out
+
+    def close(self) -> None:
+        if self._h:
+            _pkg().lib().diskann_cuda_unregister(self._h)
+            self._h = C.c_void_p()
+            self._keepalive = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

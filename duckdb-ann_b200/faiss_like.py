@@ -1,0 +1,245 @@
+"""Python mirror of the reference's C++ plugin surface for FAISS indexes.
+
+Same names and argument meaning as the classes a maintainer sees in C++
+(`faiss::Index` members used at src/faiss_index.cpp:108-153, 708-762; index
+classes of faiss-metal/include/faiss-metal/MetalIndexFlat.h:47-101 and
+MetalIndexIVFFlat.h:25-76; backend of src/gpu_backend_metal.mm:15-84), so the
+parity tests read like the reference's own tests.  Every method is one call into
+the C ABI; numpy arrays are host buffers, torch CUDA tensors are device buffers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+METRIC_INNER_PRODUCT = 0  # faiss::METRIC_INNER_PRODUCT
+METRIC_L2 = 1             # faiss::METRIC_L2
+
+
+def _pkg():
+    import sys
+    return sys.modules[__name__.rsplit(".", 1)[0]]
+
+
+def _np_f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _ptr(a):
+    return C.c_void_p(a.ctypes.data) if a is not None else None
+
+
+class _CudaIndex:
+    """Common faiss::Index surface: d, ntotal, metric_type, is_trained, add,
+    search, reset, reconstruct."""
+
+    def __init__(self):
+        self._h = C.c_void_p()
+
+    # -- fields of faiss::Index
+    @property
+    def d(self) -> int:
+        return _pkg().lib().ann_cuda_index_d(self._h)
+
+    @property
+    def ntotal(self) -> int:
+        return _pkg().lib().ann_cuda_index_ntotal(self._h)
+
+    @property
+    def metric_type(self) -> int:
+        return _pkg().lib().ann_cuda_index_metric(self._h)
+
+    @property
+    def is_trained(self) -> bool:
+        return bool(_pkg().lib().ann_cuda_index_is_trained(self._h))
+
+    @property
+    def device(self) -> int:
+        return _pkg().lib().ann_cuda_index_device(self._h)
+
+    def add(self, x) -> None:
+        """faiss::Index::add(n, x); x is (n, d) float32 on the host."""
+        x = _np_f32(x)
+        if x.ndim != 2 or x.shape[1] != self.d:
+            raise ValueError(f"add: expected (n, {self.d}) rows")
+        p = _pkg()
+        p.check(p.lib().ann_cuda_index_add(self._h, x.shape[0], _ptr(x)), "add")
+
+    def add_device(self, x) -> None:
+        """add() with the rows already on this index's GPU (a torch CUDA tensor)."""
+        assert x.is_cuda and x.is_contiguous() and x.dim() == 2 and x.shape[1] == self.d
+        p = _pkg()
+        p.check(p.lib().ann_cuda_index_add_device(self._h, x.shape[0], C.c_void_p(x.data_ptr())), "add_device")
+
+    def reserve(self, n_total: int) -> None:
+        p = _pkg()
+        p.check(p.lib().ann_cuda_index_reserve(self._h, n_total), "reserve")
+
+    def search(self, x, k: int):
+        """faiss::Index::search(n, x, k, D, I) with host buffers -> (D, I)."""
+        x = _np_f32(x)
+        if x.ndim != 2 or x.shape[1] != self.d:
+            raise ValueError(f"search: expected (n, {self.d}) queries")
+        n = x.shape[0]
+        D = np.empty((n, max(k, 0)), np.float32)
+        I = np.empty((n, max(k, 0)), np.int64)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_index_search(self._h, n, _ptr(x), k, _ptr(D), _ptr(I)), "search")
+        return D, I
+
+    def search_device(self, x, k: int, D=None, I=None, label_offset: int = 0, stream=None):
+        """search() on device buffers (torch CUDA tensors), enqueued on `stream`
+        (a torch.cuda.Stream; default: torch's current stream), not synchronised."""
+        import torch
+        assert x.is_cuda and x.is_contiguous() and x.dtype == torch.float32 and x.shape[1] == self.d
+        n = x.shape[0]
+        if D is None:
+            D = torch.empty((n, k), dtype=torch.float32, device=x.device)
+        if I is None:
+            I = torch.empty((n, k), dtype=torch.int64, device=x.device)
+        s = stream if stream is not None else torch.cuda.current_stream(x.device)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_index_search_device(self._h, n, C.c_void_p(x.data_ptr()), k,
+                                                     C.c_void_p(D.data_ptr()), C.c_void_p(I.data_ptr()),
+                                                     label_offset, C.c_void_p(s.cuda_stream)), "search_device")
+        return D, I
+
+    def reset(self) -> None:
+        p = _pkg()
+        p.check(p.lib().ann_cuda_index_reset(self._h), "reset")
+
+    def reconstruct(self, key: int):
+        out = np.empty(self.d, np.float32)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_index_reconstruct(self._h, key, _ptr(out)), "reconstruct")
+        return out
+
+    def close(self) -> None:
+        if self._h:
+            _pkg().lib().ann_cuda_index_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class CudaIndexFlat(_CudaIndex):
+    """MetalIndexFlat(resources, d, metric) -> CudaIndexFlat(d, metric, device)."""
+
+    def __init__(self, d: int, metric: int = METRIC_L2, device: int = 0):
+        super().__init__()
+        p = _pkg()
+        p.check(p.lib().ann_cuda_flat_create(device, d, metric, C.byref(self._h)), "CudaIndexFlat")
+
+    def get_rows(self, first: int, n: int):
+        out = np.empty((n, self.d), np.float32)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_flat_get_rows(self._h, first, n, _ptr(out)), "get_rows")
+        return out
+
+
+class CudaIndexIVFFlat(_CudaIndex):
+    """MetalIndexIVFFlat(resources, d, nlist, metric) -> CudaIndexIVFFlat(d, nlist, metric, device)."""
+
+    def __init__(self, d: int, nlist: int, metric: int = METRIC_L2, device: int = 0):
+        super().__init__()
+        p = _pkg()
+        p.check(p.lib().ann_cuda_ivfflat_create(device, d, nlist, metric, C.byref(self._h)), "CudaIndexIVFFlat")
+
+    def train(self, x) -> None:
+        x = _np_f32(x)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_ivfflat_train(self._h, x.shape[0], _ptr(x)), "train")
+
+    def set_centroids(self, centroids) -> None:
+        c = _np_f32(centroids)
+        if c.shape != (self.getNlist(), self.d):
+            raise ValueError("set_centroids: expected (nlist, d)")
+        p = _pkg()
+        p.check(p.lib().ann_cuda_ivfflat_set_centroids(self._h, _ptr(c)), "set_centroids")
+
+    def get_centroids(self):
+        out = np.empty((self.getNlist(), self.d), np.float32)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_ivfflat_get_centroids(self._h, _ptr(out)), "get_centroids")
+        return out
+
+    def add_list(self, list_no: int, ids, rows) -> None:
+        ids = np.ascontiguousarray(ids, np.int64)
+        rows = _np_f32(rows).reshape(len(ids), self.d)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_ivfflat_add_list(self._h, list_no, len(ids), _ptr(ids), _ptr(rows)), "add_list")
+
+    def list_size(self, list_no: int) -> int:
+        return _pkg().lib().ann_cuda_ivfflat_list_size(self._h, list_no)
+
+    def get_list(self, list_no: int):
+        n = self.list_size(list_no)
+        ids = np.empty(n, np.int64)
+        rows = np.empty((n, self.d), np.float32)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_ivfflat_get_list(self._h, list_no, _ptr(ids), _ptr(rows)), "get_list")
+        return ids, rows
+
+    def getNlist(self) -> int:
+        return _pkg().lib().ann_cuda_ivfflat_nlist(self._h)
+
+    def getNprobe(self) -> int:
+        return _pkg().lib().ann_cuda_ivfflat_get_nprobe(self._h)
+
+    def setNprobe(self, nprobe: int) -> None:
+        p = _pkg()
+        p.check(p.lib().ann_cuda_ivfflat_set_nprobe(self._h, nprobe), "setNprobe")
+
+    def set_shard(self, rank: int, count: int) -> None:
+        p = _pkg()
+        p.check(p.lib().ann_cuda_ivfflat_set_shard(self._h, rank, count), "set_shard")
+
+
+class CudaGpuBackend:
+    """duckdb::GpuBackend for CUDA: IsAvailable / DeviceInfo / BackendName
+    (src/include/gpu_backend.hpp:12-33, src/faiss_fn_gpu.cpp:33-46)."""
+
+    def IsAvailable(self) -> bool:
+        return bool(_pkg().lib().ann_cuda_available())
+
+    def DeviceInfo(self) -> str:
+        buf = C.create_string_buffer(256)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_device_info(buf, 256), "DeviceInfo")
+        return buf.value.decode()
+
+    def BackendName(self) -> str:
+        return "cuda"
+
+
+_backend = None
+
+
+def get_gpu_backend() -> CudaGpuBackend:
+    global _backend
+    if _backend is None:
+        _backend = CudaGpuBackend()
+    return _backend
+
+
+def merge_topk_device(parts_d, parts_i, metric: int, out_d=None, out_i=None, stream=None):
+    """Final k-select over per-shard results: (nparts, nq, k) CUDA tensors -> (nq, k)."""
+    import torch
+    assert parts_d.is_cuda and parts_d.is_contiguous() and parts_i.is_contiguous()
+    nparts, nq, k = parts_d.shape
+    if out_d is None:
+        out_d = torch.empty((nq, k), dtype=torch.float32, device=parts_d.device)
+    if out_i is None:
+        out_i = torch.empty((nq, k), dtype=torch.int64, device=parts_d.device)
+    s = stream if stream is not None else torch.cuda.current_stream(parts_d.device)
+    p = _pkg()
+    p.check(p.lib().ann_cuda_merge_topk_device(parts_d.device.index or 0, C.c_void_p(parts_d.data_ptr()),
+                                               C.c_void_p(parts_i.data_ptr()), nparts, nq, k, metric,
+                                               C.c_void_p(out_d.data_ptr()), C.c_void_p(out_i.data_ptr()),
+                                               C.c_void_p(s.cuda_stream)), "merge_topk_device")
+    return out_d, out_i

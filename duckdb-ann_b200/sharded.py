@@ -1,0 +1,83 @@
+"""Multi-GPU sharding of Flat / IVFFlat search inside one box.
+
+One process per GPU (torch.distributed).  Flat: database rows are split into
+contiguous ranges, one per rank.  IVFFlat: inverted list l lives on rank
+l % world; the coarse quantiser is replicated.  Every rank searches its shard
+for ALL queries, the per-shard (distance, label) top-k lists are exchanged with
+one all-gather (k * 12 bytes per query per rank) and a final k-select kernel
+merges them on every rank.  The reference has no multi-GPU path; this follows
+the sharding the benchmark configurations describe.
+
+The planner functions are pure Python and are unit-tested on CPU; the search
+itself needs CUDA (the local search and the merge are CUDA kernels) unless a
+test injects its own `local_search` / `merge`.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+
+def row_range(n_rows: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous row range [begin, end) of `rank`: ranges differ by at most one row."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError("bad rank / world")
+    base, rem = divmod(n_rows, world)
+    begin = rank * base + min(rank, rem)
+    return begin, begin + base + (1 if rank < rem else 0)
+
+
+def list_owner(list_no: int, world: int) -> int:
+    """Rank that stores inverted list `list_no` (round-robin deal)."""
+    return list_no % world
+
+
+def lists_of_rank(nlist: int, rank: int, world: int) -> list[int]:
+    return list(range(rank, nlist, world))
+
+
+class ShardedSearcher:
+    """Searches a sharded index: local search -> all-gather -> merge.
+
+    `local_search(x, k) -> (D, I)` returns this rank's (nq, k) results with GLOBAL
+    labels, best first, missing = (+-inf, -1).  `merge(parts_d, parts_i) -> (D, I)`
+    reduces the gathered (world, nq, k) lists.  With a CUDA index both default to
+    the library's kernels.
+    """
+
+    def __init__(self, index=None, metric: int = 1, label_offset: int = 0, group=None,
+                 local_search: Optional[Callable] = None, merge: Optional[Callable] = None):
+        self.index = index
+        self.metric = metric
+        self.label_offset = label_offset
+        self.group = group
+        self._local_search = local_search
+        self._merge = merge
+        self._gather_d = None
+        self._gather_i = None
+
+    def _world(self) -> int:
+        import torch.distributed as dist
+        return dist.get_world_size(self.group) if dist.is_available() and dist.is_initialized() else 1
+
+    def search(self, x, k: int):
+        import torch
+        import torch.distributed as dist
+        world = self._world()
+        if self._local_search is not None:
+            d_loc, i_loc = self._local_search(x, k)
+        else:
+            if self.index is None:
+                raise RuntimeError("ShardedSearcher needs a CUDA index (there is no CPU search path)")
+            d_loc, i_loc = self.index.search_device(x, k, label_offset=self.label_offset)
+        if world == 1:
+            return d_loc, i_loc
+        shape = (world,) + tuple(d_loc.shape)
+        if self._gather_d is None or tuple(self._gather_d.shape) != shape or self._gather_d.device != d_loc.device:
+            self._gather_d = torch.empty(shape, dtype=d_loc.dtype, device=d_loc.device)
+            self._gather_i = torch.empty(shape, dtype=i_loc.dtype, device=i_loc.device)
+        dist.all_gather_into_tensor(self._gather_d, d_loc.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(self._gather_i, i_loc.contiguous(), group=self.group)
+        if self._merge is not None:
+            return self._merge(self._gather_d, self._gather_i)
+        from .faiss_like import merge_topk_device
+        return merge_topk_device(self._gather_d, self._gather_i, self.metric)

@@ -1,0 +1,156 @@
+/*
+ * C ABI of the CUDA (sm_100a) FAISS-search backend: exact Flat and IVFFlat
+ * top-k search for L2 and inner product.
+ *
+ * In the reference this path is C++: a `faiss::Index` subclass handed out by
+ * `duckdb::GpuBackend::CpuToGpu` (src/include/gpu_backend.hpp:12-33,
+ * src/gpu_backend_metal.mm:42-60).  The C++ classes in gpu_backend_cuda.hpp are
+ * thin wrappers over the functions below; every function here names the
+ * reference member it stands behind.
+ *
+ * Conventions: plain C, no exceptions; 0 = success, -1 = error with the reason
+ * kept per thread (ann_cuda_last_error).  Metric codes are FAISS's:
+ * 0 = METRIC_INNER_PRODUCT (larger is better, raw dot returned),
+ * 1 = METRIC_L2 (SQUARED distance, smaller is better).  Results are sorted best
+ * first; missing slots hold label -1 and distance +inf (L2) / -inf (IP)
+ * (faiss-metal/src/MetalIndexFlat.mm:303-309, 363-367).  Labels are int64
+ * (faiss::idx_t).  search() is safe to call from many threads at once on one
+ * index (src/faiss_index.cpp:729-737 does so); add/reset/train are not.
+ */
+#ifndef ANN_CUDA_H
+#define ANN_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* exported even when the library is built with hidden visibility */
+#endif
+
+#define ANN_CUDA_METRIC_INNER_PRODUCT 0
+#define ANN_CUDA_METRIC_L2 1
+
+typedef struct ann_cuda_index ann_cuda_index;
+
+/* Reason of the calling thread's last -1 ("" if none). */
+const char *ann_cuda_last_error(void);
+
+/* GpuBackend::IsAvailable (src/include/gpu_backend.hpp:17,
+ * src/gpu_backend_metal.mm:26-28): 1 if device 0..n-1 exist and are sm_100. */
+int ann_cuda_available(void);
+int ann_cuda_device_count(void);
+
+/* GpuBackend::DeviceInfo (gpu_backend.hpp:20, gpu_backend_metal.mm:30-36):
+ * writes e.g. "CUDA GPU (NVIDIA B200, sm_100, 148 SMs, 8 devices)". */
+int ann_cuda_device_info(char *buf, size_t buflen);
+
+/* ---- Flat --------------------------------------------------------------------
+ * MetalIndexFlat(resources, d, metric) (faiss-metal/include/faiss-metal/MetalIndexFlat.h:47-59). */
+int ann_cuda_flat_create(int device, int d, int metric, ann_cuda_index **out);
+
+/* ---- IVFFlat -----------------------------------------------------------------
+ * MetalIndexIVFFlat(resources, d, nlist, metric) (faiss-metal/include/faiss-metal/MetalIndexIVFFlat.h:25-33). */
+int ann_cuda_ivfflat_create(int device, int d, int64_t nlist, int metric, ann_cuda_index **out);
+
+/* Installs trained centroids (nlist x d, host) and marks the index trained: the
+ * centroid copy of index_cpu_to_metal_ivf (faiss-metal/src/MetalIndexIVFFlat.mm:291-296). */
+int ann_cuda_ivfflat_set_centroids(ann_cuda_index *index, const float *centroids);
+
+/* MetalIndexIVFFlat::train (MetalIndexIVFFlat.mm:86-100): k-means on n host rows. */
+int ann_cuda_ivfflat_train(ann_cuda_index *index, int64_t n, const float *x);
+
+/* Appends one inverted list's content as stored by the CPU index: ids and
+ * rows of list `list_no` (MetalIndexIVFFlat.mm:299-311).  Host pointers. */
+int ann_cuda_ivfflat_add_list(ann_cuda_index *index, int64_t list_no, int64_t n, const int64_t *ids,
+                              const float *rows);
+
+/* Reads list `list_no` back: size, then ids/rows (either may be NULL)
+ * (index_metal_to_cpu_ivf, MetalIndexIVFFlat.mm:336-354). */
+int64_t ann_cuda_ivfflat_list_size(const ann_cuda_index *index, int64_t list_no);
+int ann_cuda_ivfflat_get_list(const ann_cuda_index *index, int64_t list_no, int64_t *ids, float *rows);
+int ann_cuda_ivfflat_get_centroids(const ann_cuda_index *index, float *centroids);
+
+/* setNprobe / getNprobe (MetalIndexIVFFlat.mm:267-279): clamped to [1, nlist]. */
+int ann_cuda_ivfflat_set_nprobe(ann_cuda_index *index, int64_t nprobe);
+int64_t ann_cuda_ivfflat_get_nprobe(const ann_cuda_index *index);
+int64_t ann_cuda_ivfflat_nlist(const ann_cuda_index *index);
+
+/* Sharding of the inverted lists across GPUs: this index keeps only lists with
+ * list_no % shard_count == shard_rank; rows added to other lists are dropped
+ * (they live on another GPU).  The coarse quantiser stays complete on every
+ * shard.  No counterpart in the reference (single device).  Call before add. */
+int ann_cuda_ivfflat_set_shard(ann_cuda_index *index, int shard_rank, int shard_count);
+
+/* ---- common faiss::Index surface ------------------------------------------------ */
+
+/* faiss::Index::add (MetalIndexFlat.mm:173-292; MetalIndexIVFFlat.mm:102-120).
+ * Flat: appends rows, label = position.  IVFFlat: assigns each row to its
+ * nearest centroid on the GPU; label = running ntotal. */
+int ann_cuda_index_add(ann_cuda_index *index, int64_t n, const float *x);
+
+/* Same with x in the index's device memory space (no host copy). */
+int ann_cuda_index_add_device(ann_cuda_index *index, int64_t n, const float *x_device);
+
+/* Pre-sizes the storage for `n_total` rows so add never reallocates. */
+int ann_cuda_index_reserve(ann_cuda_index *index, int64_t n_total);
+
+/* faiss::Index::search (MetalIndexFlat.mm:294-369; MetalIndexIVFFlat.mm:122-256).
+ * x: n x d (host), distances/labels: n x k (host).  Synchronous. */
+int ann_cuda_index_search(const ann_cuda_index *index, int64_t n, const float *x, int64_t k, float *distances,
+                          int64_t *labels);
+
+/* Same with DEVICE pointers; work is enqueued on `stream` (cudaStream_t, NULL =
+ * default stream) and not synchronised.  label_offset is added to every valid
+ * label (row-sharded indexes pass the shard's first row). */
+int ann_cuda_index_search_device(const ann_cuda_index *index, int64_t n, const float *x_device, int64_t k,
+                                 float *distances_device, int64_t *labels_device, int64_t label_offset,
+                                 void *stream);
+
+/* faiss::Index::reset / reconstruct (MetalIndexFlat.mm:445-478). reconstruct is
+ * bit-exact; for IVFFlat `key` is the label given at add time. */
+int ann_cuda_index_reset(ann_cuda_index *index);
+int ann_cuda_index_reconstruct(const ann_cuda_index *index, int64_t key, float *recons);
+
+/* Flat only: copies rows [first, first+n) to host (getVectorsData / get_xb,
+ * MetalIndexFlat.mm:480-487, used by index_metal_to_cpu :517-535). */
+int ann_cuda_flat_get_rows(const ann_cuda_index *index, int64_t first, int64_t n, float *rows);
+
+int64_t ann_cuda_index_ntotal(const ann_cuda_index *index);
+int ann_cuda_index_d(const ann_cuda_index *index);
+int ann_cuda_index_metric(const ann_cuda_index *index);
+int ann_cuda_index_is_trained(const ann_cuda_index *index);
+int ann_cuda_index_is_ivf(const ann_cuda_index *index);
+int ann_cuda_index_device(const ann_cuda_index *index);
+void ann_cuda_index_free(ann_cuda_index *index);
+
+/* ---- multi-GPU merge -------------------------------------------------------------
+ * Final k-select over per-shard results.  parts_*: (nparts x nq x k) in DEVICE
+ * memory, each (part, query) run sorted best first as search_device writes it;
+ * out_*: (nq x k) device.  Enqueued on `stream`.  No counterpart in the
+ * reference (single device); it is the last step of the sharded search. */
+int ann_cuda_merge_topk_device(int device, const float *parts_distances, const int64_t *parts_labels, int nparts,
+                               int64_t nq, int64_t k, int metric, float *out_distances, int64_t *out_labels,
+                               void *stream);
+
+/* Which flat-search kernel the library runs: "tcgen05" (tensor cores, the
+ * product path) or "simt" (exact-fp32 cross-check kernel).  Selected by the
+ * environment variable ANN_CUDA_FLAT_KERNEL; default tcgen05. */
+const char *ann_cuda_flat_kernel_name(void);
+/* Overrides that choice for the whole process ("tcgen05" | "simt"); used by the
+ * tests to cross-check one kernel against the other. */
+int ann_cuda_set_flat_kernel(const char *name);
+
+/* Number of kernel launches this library has issued from the calling process
+ * since load (all threads).  For the benchmark's launch accounting. */
+uint64_t ann_cuda_launch_count(void);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* ANN_CUDA_H */

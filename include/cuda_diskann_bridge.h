@@ -1,0 +1,107 @@
+/*
+ * C ABI of the DiskANN batch-distance bridge, CUDA (sm_100a) implementation.
+ *
+ * The first three symbols keep the names, argument order, units and return
+ * codes of the reference's bridge header (src/include/metal_diskann_bridge.h:8-23)
+ * so that the Rust side (rust_lib/src/metal_ffi.rs:10-30) and the C++ caller
+ * (src/ann_search.cpp:723-732) link against this library unchanged.
+ *
+ * Conventions, all entry points:
+ *   - plain C, no exceptions, never aborts; 0 = success, -1 = error.  On -1
+ *     the reference's callers fall back to their CPU loop
+ *     (rust_lib/src/disk_provider.rs:436-453, src/ann_search.cpp:727-731); the
+ *     reason is kept per thread and returned by diskann_cuda_last_error().
+ *   - metric 0 = L2 (SQUARED distance), any other value = inner product,
+ *     returned NEGATED (src/metal_diskann_bridge.mm:167,
+ *     faiss-metal/shaders/diskann_distance.metal:148,192).
+ *   - callable from any number of host threads at once.
+ */
+#ifndef ANN_CUDA_DISKANN_BRIDGE_H
+#define ANN_CUDA_DISKANN_BRIDGE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* exported even when the library is built with hidden visibility */
+#endif
+
+/* Replaces diskann_metal_available (src/include/metal_diskann_bridge.h:8,
+ * src/metal_diskann_bridge.mm:145-153).  1 if a CUDA device of compute
+ * capability 10.x is usable, else 0.  Initialises lazily; cheap afterwards. */
+int diskann_metal_available(void);
+
+/* Replaces diskann_metal_batch_distances (metal_diskann_bridge.h:14,
+ * src/metal_diskann_bridge.mm:155-253).  One query (dim floats) against n
+ * gathered rows (n*dim contiguous floats); writes n distances.  All pointers
+ * are HOST memory owned by the caller; the call is synchronous. */
+int diskann_metal_batch_distances(const float *query, const float *candidates, int n, int dim, int metric,
+                                  float *out_distances);
+
+/* Replaces diskann_metal_multi_batch_distances (metal_diskann_bridge.h:22,
+ * src/metal_diskann_bridge.mm:255-323).  Row i is scored against
+ * queries[query_map[i]]; query_map values must be < nq.  HOST pointers. */
+int diskann_metal_multi_batch_distances(const float *queries, const float *candidates,
+                                        const unsigned int *query_map, int total_n, int nq, int dim, int metric,
+                                        float *out_distances);
+
+/* ---- additive entry points: device-resident tables, rows named by id -------
+ * The reference gathers neighbour rows on the host before every call
+ * (rust_lib/src/disk_provider.rs:420-424, 592-600; rust_lib/src/provider.rs:385-400).
+ * These keep the vector table in GPU memory and take the row ids instead, so
+ * the distance pass reads rows from HBM rather than over PCIe. */
+
+typedef struct diskann_cuda_table diskann_cuda_table;
+
+/* Last error message of the calling thread ("" if none). */
+const char *diskann_cuda_last_error(void);
+
+/* Copies num x dim fp32 rows (host) to the device `device`.  The fp32 table of
+ * the in-memory provider / the .diskann vector section
+ * (rust_lib/src/provider.rs:159-160, rust_lib/src/file_format.rs:3-18). */
+int diskann_cuda_register_table(int device, const float *host_rows, size_t num, int dim,
+                                diskann_cuda_table **out);
+
+/* Same, rows already in device memory (adopted by reference: the caller keeps
+ * ownership and must keep them alive until unregister). */
+int diskann_cuda_register_table_device(int device, const float *device_rows, size_t num, int dim,
+                                       diskann_cuda_table **out);
+
+/* SQ8 table: u8 codes (num x dim) plus per-dimension min and scale, as
+ * produced by quantize_sq8 (rust_lib/src/provider.rs:161-210).  Host pointers. */
+int diskann_cuda_register_sq8(int device, const uint8_t *codes, const float *mins, const float *scale, size_t num,
+                              int dim, diskann_cuda_table **out);
+
+/* Same with the codes already in device memory (adopted by reference);
+ * mins/scale are host pointers and are copied. */
+int diskann_cuda_register_sq8_device(int device, const uint8_t *device_codes, const float *mins,
+                                     const float *scale, size_t num, int dim, diskann_cuda_table **out);
+
+int diskann_cuda_unregister(diskann_cuda_table *table);
+
+/* out[i] = distance(queries[query_map[i]], row ids[i]); query_map may be NULL
+ * when nq == 1.  For an SQ8 table the row is dequantised as
+ * (code/255)*scale+min (rust_lib/src/provider.rs:138-147) and scored against the
+ * fp32 query (asymmetric distance).  HOST pointers; synchronous.  ids >= num
+ * or query_map >= nq give -1 and leave out_distances unspecified. */
+int diskann_cuda_batch_distances_by_id(const diskann_cuda_table *table, const float *queries, int nq,
+                                       const uint32_t *ids, const uint32_t *query_map, int total_n, int metric,
+                                       float *out_distances);
+
+/* Same with DEVICE pointers, enqueued on `stream` (a cudaStream_t; NULL = the
+ * default stream) without synchronising.  Ids and map are range-checked on the
+ * device: a bad entry writes NaN to its slot and the call still returns 0. */
+int diskann_cuda_batch_distances_by_id_device(const diskann_cuda_table *table, const float *queries, int nq,
+                                              const uint32_t *ids, const uint32_t *query_map, int total_n,
+                                              int metric, float *out_distances, void *stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* ANN_CUDA_DISKANN_BRIDGE_H */
