@@ -1,0 +1,598 @@
+#!/usr/bin/env python
+"""Benchmark of the GPU search path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Under `python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N` every rank
+owns one GPU and one shard; rank 0 prints ONE JSON line.
+
+Workloads (synthetic, seeded; shapes of the reference configurations):
+  flat_ip_20m   (default) Flat inner product, 20,000,000 x 768 unit-norm rows, 4,096 queries, k=100,
+                rows sharded over the ranks, per-shard top-k merged after an all-gather.  STRONG scaling.
+  flat_l2_100k  Flat L2, 100,000 x 384 uniform[0,1) rows, 1,000 queries, k=10.
+  ivf_1m        IVFFlat L2, 1,000,000 x 768 rows from 1,024 Gaussian clusters, nlist=1024, nprobe=16,
+                10,000 queries, k=100, inverted lists sharded over the ranks.
+  batch_c2      DiskANN batch distance, table 1,000,000 x 1536, 256 queries x 128 random rows (L2).
+  sq8_c5        SQ8 asymmetric L2, 10,000,000 x 384 codes, 1,024 queries x 128 random rows.
+A step is one pass of the hot path over one batch of queries.  `value` is measured with the
+inputs resident in HBM; `e2e` goes through the host-pointer C-ABI call (or, for N > 1, pinned-host
+copies around the sharded search) with the copies inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def load_package():
+    name = "duckdb_ann_b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    pkg_dir = os.path.join(ROOT, "duckdb-ann_b200")
+    spec = importlib.util.spec_from_file_location(name, os.path.join(pkg_dir, "__init__.py"),
+                                                  submodule_search_locations=[pkg_dir])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["_source"] = "measured"
+        return p
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "_source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def wait_first_sample(self, timeout=3.0):
+        t0 = time.perf_counter()
+        while not self.lines and time.perf_counter() - t0 < timeout:
+            time.sleep(0.02)
+
+    def mark(self):
+        return time.perf_counter()
+
+    def stop(self, t_begin=None, t_end=None):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        in_region = [l for (t, l) in self.lines if t_begin is None or (t_begin <= t <= t_end + 0.15)]
+        where = "timed region"
+        if not in_region:  # region shorter than the sampling period: use the samples taken under the warm-up load
+            in_region = [l for (_, l) in self.lines]
+            where = "warm-up + timed region (timed region shorter than the 100 ms sampling period)"
+        for line in in_region:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm), "sampled_over": where}
+
+
+def dist_info(args):
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    return rank, local, world
+
+
+def unit_rows(gen_seed, rows, d, device, torch):
+    g = torch.Generator(device=device).manual_seed(gen_seed)
+    x = torch.randn((rows, d), generator=g, device=device, dtype=torch.float32)
+    x /= x.norm(dim=1, keepdim=True)
+    return x
+
+
+# ------------------------------------------------------------------------------------------------
+# Workloads
+# ------------------------------------------------------------------------------------------------
+class FlatWorkload:
+    def __init__(self, name, n, d, nq, k, metric_name, dist_kind, scale=1.0):
+        self.name, self.d, self.nq, self.k = name, d, nq, k
+        self.n = max(1024, int(n * scale))
+        self.metric_name, self.dist_kind = metric_name, dist_kind
+        self.chunk = 250_000
+        self.metric = "flat_topk_queries_per_s"
+        self.unit = "queries/s"
+        self.dtype = "f32 (split-TF32 tensor cores, fp32 accumulate)"
+        self.scaling = "strong"
+
+    def gen_chunk(self, c, device, torch):
+        """Rows [c*chunk, (c+1)*chunk) of the global database, the same on any rank count."""
+        rows = min(self.chunk, self.n - c * self.chunk)
+        if self.dist_kind == "unit":
+            return unit_rows(1000 + c, rows, self.d, device, torch)
+        g = torch.Generator(device=device).manual_seed(1000 + c)
+        return torch.rand((rows, self.d), generator=g, device=device, dtype=torch.float32)
+
+    def queries_host(self, torch):
+        g = torch.Generator().manual_seed(43)
+        if self.dist_kind == "unit":
+            q = torch.randn((self.nq, self.d), generator=g)
+            q /= q.norm(dim=1, keepdim=True)
+        else:
+            q = torch.rand((self.nq, self.d), generator=g)
+        return q.contiguous().pin_memory()
+
+    def setup(self, pkg, torch, rank, world, device):
+        self.pkg = pkg
+        m = pkg.METRIC_INNER_PRODUCT if self.metric_name == "IP" else pkg.METRIC_L2
+        self.m = m
+        lo, hi = pkg.sharded.row_range(self.n, rank, world)
+        self.lo, self.hi = lo, hi
+        self.index = pkg.CudaIndexFlat(self.d, m, device.index)
+        self.index.reserve(hi - lo)
+        c0, c1 = lo // self.chunk, (hi - 1) // self.chunk
+        for c in range(c0, c1 + 1):
+            x = self.gen_chunk(c, device, torch)
+            a, b = max(lo, c * self.chunk) - c * self.chunk, min(hi, (c + 1) * self.chunk) - c * self.chunk
+            self.index.add_device(x[a:b].contiguous())
+            del x
+        assert self.index.ntotal == hi - lo
+        self.q_host = self.queries_host(torch)
+        self.q_dev = self.q_host.to(device)
+        self.searcher = pkg.sharded.ShardedSearcher(self.index, m, label_offset=lo)
+        self.out_host_d = torch.empty((self.nq, self.k), dtype=torch.float32).pin_memory()
+        self.out_host_i = torch.empty((self.nq, self.k), dtype=torch.int64).pin_memory()
+        self.world = world
+
+    def step(self):
+        return self.searcher.search(self.q_dev, self.k)
+
+    def step_e2e(self, torch):
+        if self.world == 1:
+            # the reference-facing call: host buffers in, host buffers out, synchronous
+            return self.index.search(self.q_host.numpy(), self.k)
+        q = self.q_host.to(self.q_dev.device, non_blocking=True)
+        D, I = self.searcher.search(q, self.k)
+        self.out_host_d.copy_(D, non_blocking=True)
+        self.out_host_i.copy_(I, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.out_host_d, self.out_host_i
+
+    def units_per_step(self):
+        return self.nq
+
+    def e2e_bytes(self):
+        return self.nq * self.d * 4, self.nq * self.k * 12
+
+    def config(self, world):
+        return {"workload": self.name, "rows": self.n, "dim": self.d, "queries": self.nq, "k": self.k,
+                "metric": self.metric_name, "sharding": f"rows/{world}", "distribution": self.dist_kind,
+                "l2_flush": "database shard (>= 7 GB per GPU) is far larger than L2; no explicit flush"
+                if self.n * self.d * 8 / max(world, 1) > 1e9 else "database is L2-sized: see DESIGN.md",
+                "flat_kernel": self.pkg.lib().ann_cuda_flat_kernel_name().decode()}
+
+    def roofline(self, peaks, kernel_ms):
+        local_rows = self.hi - self.lo
+        flops = 2.0 * self.nq * local_rows * self.d
+        achieved = flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms and kernel_ms > 0 else None
+        peak = peaks["bf16_tflops_sustained"] / 6.0
+        return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak if achieved else None, "traffic": None,
+                "kernel": "flat_tc_kernel", "kernel_ms": kernel_ms,
+                "algorithmic_flops_per_launch": flops,
+                "peak_note": f"{peaks['_source']} bf16 sustained {peaks['bf16_tflops_sustained']} TFLOP/s / 2 (TF32 rate) "
+                             "/ 3 (split-TF32 issues three MMAs per product); 'achieved' counts 2*Q*N*d once"}
+
+    def verify(self, torch, D, I):
+        """Size-independent properties: sorted best first, labels valid and distinct, and the
+        reported distance of a sample of (query, label) pairs equals the exact dot / L2."""
+        D, I = D.cpu().numpy(), I.cpu().numpy()
+        sgn = -1.0 if self.metric_name == "IP" else 1.0
+        assert (np.diff(sgn * D, axis=1) >= 0).all(), "results are not sorted best first"
+        assert (I >= 0).all() and (I < self.n).all()
+        assert all(len(set(r.tolist())) == len(r) for r in I[:64]), "duplicate labels"
+        q = self.q_host.numpy()
+        for qi in (0, self.nq // 2, self.nq - 1):
+            for j in (0, self.k - 1):
+                lab = int(I[qi, j])
+                if not (self.lo <= lab < self.hi):
+                    continue
+                row = self.index.reconstruct(lab - self.lo).astype(np.float64)
+                true = float(row @ q[qi].astype(np.float64)) if self.metric_name == "IP" else float(
+                    ((row - q[qi].astype(np.float64)) ** 2).sum())
+                assert abs(true - float(D[qi, j])) <= 1e-4 * abs(true) + 1e-7, (qi, j, true, float(D[qi, j]))
+
+    # ---- CPU baseline: blocked sgemm + heap on the host cores, on a bounded sample
+    def cpu_sample(self, torch, device):
+        rows = min(self.n, 1_000_000 if self.n > 2_000_000 else self.n)
+        nq = min(self.nq, 256 if self.n > 2_000_000 else self.nq)
+        parts = []
+        for c in range((rows + self.chunk - 1) // self.chunk):
+            x = self.gen_chunk(c, device, torch)
+            parts.append(x[: min(self.chunk, rows - c * self.chunk)].cpu().numpy())
+            del x
+        xb = np.concatenate(parts)
+        xq = self.queries_host(torch).numpy()[:nq].copy()
+        return xb, xq, rows, nq
+
+    def cpu_run(self, oracle, sample):
+        xb, xq, rows, nq = sample
+        m = oracle.METRIC_IP if self.metric_name == "IP" else oracle.METRIC_L2
+        t0 = time.perf_counter()
+        oracle.flat_search_blas(xb, xq, self.k, m)
+        dt = time.perf_counter() - t0
+        # queries/s over the FULL database: time scales with the number of rows scanned
+        qps = nq / (dt * (self.n / rows))
+        return qps, dt, f"{nq} queries x {rows:,} of {self.n:,} rows (blocked sgemm + heap), time scaled x{self.n / rows:g}"
+
+
+class IvfWorkload:
+    def __init__(self, scale=1.0):
+        self.name = "ivf_1m"
+        self.n = max(20_000, int(1_000_000 * scale))
+        self.d, self.nlist, self.nprobe, self.k = 768, 1024, 16, 100
+        self.nq = max(256, int(10_000 * scale))
+        self.nclusters = 1024
+        self.chunk = 100_000
+        self.metric = "ivfflat_topk_queries_per_s"
+        self.unit = "queries/s"
+        self.dtype = "f32"
+        self.scaling = "strong"
+        self.metric_name = "L2"
+
+    def centers(self, device, torch):
+        g = torch.Generator(device=device).manual_seed(45)
+        return torch.randn((self.nclusters, self.d), generator=g, device=device)
+
+    def gen_chunk(self, c, device, torch, centers):
+        rows = min(self.chunk, self.n - c * self.chunk)
+        g = torch.Generator(device=device).manual_seed(2000 + c)
+        lab = torch.randint(0, self.nclusters, (rows,), generator=g, device=device)
+        return centers[lab] + 0.1 * torch.randn((rows, self.d), generator=g, device=device)
+
+    def setup(self, pkg, torch, rank, world, device):
+        self.pkg, self.world = pkg, world
+        self.m = pkg.METRIC_L2
+        centers = self.centers(device, torch)
+        self.index = pkg.CudaIndexIVFFlat(self.d, self.nlist, pkg.METRIC_L2, device.index)
+        self.index.set_shard(rank, world)
+        # train on every 10th row (the train_sample rule of src/faiss_index.cpp:304-315), same on every rank
+        sample = torch.cat([self.gen_chunk(c, device, torch, centers)[::10] for c in
+                            range((self.n + self.chunk - 1) // self.chunk)])
+        self.index.train(sample.cpu().numpy())
+        del sample
+        for c in range((self.n + self.chunk - 1) // self.chunk):
+            self.index.add_device(self.gen_chunk(c, device, torch, centers).contiguous())
+        self.index.setNprobe(self.nprobe)
+        g = torch.Generator(device=device).manual_seed(43)
+        lab = torch.randint(0, self.nclusters, (self.nq,), generator=g, device=device)
+        q = centers[lab] + 0.1 * torch.randn((self.nq, self.d), generator=g, device=device)
+        self.q_host = q.cpu().contiguous().pin_memory()
+        self.q_dev = q.contiguous()
+        self.searcher = pkg.sharded.ShardedSearcher(self.index, pkg.METRIC_L2)
+        self.out_host_d = torch.empty((self.nq, self.k), dtype=torch.float32).pin_memory()
+        self.out_host_i = torch.empty((self.nq, self.k), dtype=torch.int64).pin_memory()
+        sizes = np.array([self.index.list_size(l) for l in range(self.nlist)], np.int64)
+        self.list_sizes = sizes
+
+    def step(self):
+        return self.searcher.search(self.q_dev, self.k)
+
+    step_e2e = FlatWorkload.step_e2e
+
+    def units_per_step(self):
+        return self.nq
+
+    def e2e_bytes(self):
+        return self.nq * self.d * 4, self.nq * self.k * 12
+
+    def config(self, world):
+        return {"workload": self.name, "rows": self.n, "dim": self.d, "queries": self.nq, "k": self.k,
+                "nlist": self.nlist, "nprobe": self.nprobe, "metric": "L2", "sharding": f"lists/{world}",
+                "l2_flush": "probed lists (3 GB of rows) exceed L2; no explicit flush"}
+
+    def roofline(self, peaks, kernel_ms):
+        return {"bound": "hbm", "achieved": None, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None,
+                "traffic": None, "kernel": "scan_items_kernel"}
+
+    def verify(self, torch, D, I):
+        D = D.cpu().numpy()
+        assert (np.diff(D, axis=1) >= 0).all()
+
+
+class BatchWorkload:
+    def __init__(self, sq8: bool, scale=1.0):
+        self.sq8 = sq8
+        if sq8:
+            self.name, self.num, self.dim, self.nq, self.per = "sq8_c5", int(10_000_000 * scale), 384, 1024, 128
+        else:
+            self.name, self.num, self.dim, self.nq, self.per = "batch_c2", int(1_000_000 * scale), 1536, 256, 128
+        self.metric = "batch_distance_gbytes_per_s"
+        self.unit = "GB/s"
+        self.dtype = "u8 codes -> f32" if sq8 else "f32"
+        self.scaling = "weak"
+        self.metric_name = "L2"
+        self.batches = 64  # distinct id batches cycled through, so consecutive launches touch different rows
+
+    def setup(self, pkg, torch, rank, world, device):
+        self.pkg = pkg
+        g = torch.Generator(device=device).manual_seed(42 + rank)
+        br = pkg.diskann_bridge
+        if self.sq8:
+            x = torch.randn((self.num, self.dim), generator=g, device=device)
+            mins = x.min(0).values
+            scale = x.max(0).values - mins
+            codes = torch.clamp(torch.round(((x - mins) / scale) * 255.0), 0, 255).to(torch.uint8).contiguous()
+            del x
+            self.table = br.DeviceTable.sq8_from_device(codes, mins.cpu().numpy(), scale.cpu().numpy())
+            self.row_bytes = self.dim
+        else:
+            rows = torch.randn((self.num, self.dim), generator=g, device=device)
+            self.table = br.DeviceTable.from_device(rows)
+            self.row_bytes = self.dim * 4
+        total = self.nq * self.per
+        self.q_dev = torch.randn((self.nq, self.dim), generator=g, device=device)
+        self.ids = [torch.randint(0, self.num, (total,), generator=g, device=device, dtype=torch.int32)
+                    for _ in range(self.batches)]
+        self.qmap = torch.arange(self.nq, device=device, dtype=torch.int32).repeat_interleave(self.per)
+        self.out = torch.empty(total, dtype=torch.float32, device=device)
+        self.q_host = self.q_dev.cpu().numpy()
+        self.ids_host = [i.cpu().numpy().astype(np.uint32) for i in self.ids[:4]]
+        self.qmap_host = self.qmap.cpu().numpy().astype(np.uint32)
+        self.it = 0
+        self.total = total
+
+    def bytes_per_step(self):
+        # rows + queries + ids, map, out
+        return self.total * self.row_bytes + self.nq * self.dim * 4 + self.total * 12 + (2 * self.dim * 4 if self.sq8 else 0)
+
+    def step(self):
+        ids = self.ids[self.it % self.batches]
+        self.it += 1
+        return self.table.batch_distances_by_id_device(self.q_dev, ids, self.qmap, 0, out=self.out), None
+
+    def step_e2e(self, torch):
+        ids = self.ids_host[self.it % len(self.ids_host)]
+        self.it += 1
+        return self.table.batch_distances_by_id(self.q_host, ids, self.qmap_host, 0), None
+
+    def units_per_step(self):
+        return self.bytes_per_step() / 1e9
+
+    def e2e_bytes(self):
+        return self.nq * self.dim * 4 + self.total * 8, self.total * 4
+
+    def config(self, world):
+        return {"workload": self.name, "table_rows": self.num, "dim": self.dim, "queries": self.nq,
+                "rows_per_query": self.per, "metric": "L2", "bytes_per_step": self.bytes_per_step(),
+                "l2_flush": f"{self.batches} id batches cycled; table ({self.num * self.row_bytes / 1e9:.1f} GB) >> L2"}
+
+    def roofline(self, peaks, kernel_ms):
+        return {"bound": "hbm", "achieved": None, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None,
+                "traffic": None, "kernel": "batch_distance_sq8_regs_kernel" if self.sq8 else "batch_distance_f32_kernel"}
+
+    def verify(self, torch, D, I):
+        assert torch.isfinite(D).all()
+
+
+def make_workload(name, scale):
+    if name == "flat_ip_20m":
+        return FlatWorkload(name, 20_000_000, 768, 4096, 100, "IP", "unit", scale)
+    if name == "flat_l2_100k":
+        return FlatWorkload(name, 100_000, 384, 1000, 10, "L2", "uniform", scale)
+    if name == "ivf_1m":
+        return IvfWorkload(scale)
+    if name == "batch_c2":
+        return BatchWorkload(False, scale)
+    if name == "sq8_c5":
+        return BatchWorkload(True, scale)
+    raise SystemExit(f"unknown workload {name}")
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference(args, wl):
+    """The reference's CPU path (oracle port: blocked sgemm + heap, all host threads) on a bounded
+    sample per step.  Rank 0 only."""
+    import torch
+    rank, local, world = dist_info(args)
+    if rank != 0:
+        return
+    from oracle import oracle
+    oracle.build()
+    if not isinstance(wl, FlatWorkload):
+        print(json.dumps({"impl": "reference", "unavailable": "the reference arm is implemented for the flat workloads"}))
+        return
+    device = torch.device("cuda", local) if torch.cuda.is_available() else torch.device("cpu")
+    sample = wl.cpu_sample(torch, device)
+    for _ in range(min(args.warmup, 1)):
+        wl.cpu_run(oracle, sample)
+    vals, times = [], []
+    for _ in range(args.steps):
+        qps, dt, desc = wl.cpu_run(oracle, sample)
+        vals.append(qps)
+        times.append(dt)
+    value = len(vals) / sum(1.0 / v for v in vals)
+    line = {"impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
+            "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": wl.config(1) | {"flat_kernel": "cpu"},
+            "cpu_baseline": {"value": value, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
+                             "sample": desc},
+            "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="flat_ip_20m")
+    ap.add_argument("--scale", type=float, default=1.0, help="shrinks the row counts (debugging / profiling captures)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    wl = make_workload(args.workload, args.scale)
+    if args.impl == "reference":
+        run_reference(args, wl)
+        return
+
+    import torch
+    import torch.distributed as dist
+    rank, local, world = dist_info(args)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    pkg = load_package()
+    if not pkg.get_gpu_backend().IsAvailable():
+        raise SystemExit("no sm_100 GPU: " + pkg.get_gpu_backend().DeviceInfo())
+    peaks = measured_peaks()
+    lib = pkg.lib()
+
+    t_setup = time.perf_counter()
+    wl.setup(pkg, torch, rank, world, device)
+    torch.cuda.synchronize()
+    t_setup = time.perf_counter() - t_setup
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    sampler.wait_first_sample()
+    for _ in range(args.warmup):
+        out = wl.step()
+    barrier()
+
+    # ---- timed region: K steps, CUDA events on the launching stream, max over ranks
+    lib.ann_cuda_set_kernel_timing(1)
+    launches0 = lib.ann_cuda_launch_count()
+    kernel_ms = []
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_begin = sampler.mark()
+    ev0.record()
+    for _ in range(args.steps):
+        out = wl.step()
+    ev1.record()
+    barrier()
+    t_end = sampler.mark()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    launches = lib.ann_cuda_launch_count() - launches0
+    clocks = sampler.stop(t_begin, t_end)
+    if hasattr(wl, "index"):
+        ms = lib.ann_cuda_index_last_flat_kernel_ms(wl.index._h)
+        if ms > 0:
+            kernel_ms.append(ms)
+    lib.ann_cuda_set_kernel_timing(0)
+    t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(t.item())
+    units = wl.units_per_step() * args.steps * (world if wl.scaling == "weak" else 1)
+    value = units / (elapsed_ms * 1e-3)
+    wl.verify(torch, out[0], out[1])
+
+    # ---- end to end: host buffers, copies inside the timed region
+    for _ in range(2):
+        wl.step_e2e(torch)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        wl.step_e2e(torch)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    t = torch.tensor([e2e_s], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t.item())
+    h2d, d2h = wl.e2e_bytes()
+    e2e_value = units / e2e_s
+
+    roof = wl.roofline(peaks, kernel_ms[-1] if kernel_ms else None)
+    if roof["bound"] == "hbm" and isinstance(wl, BatchWorkload):
+        per_launch_ms = elapsed_ms / args.steps
+        roof["achieved"] = wl.bytes_per_step() / 1e9 / (per_launch_ms * 1e-3)
+        roof["frac"] = roof["achieved"] / roof["peak"]
+        roof["kernel_ms"] = per_launch_ms
+    roof["peak_source"] = peaks["_source"]
+
+    line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+            "config": wl.config(world), "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": 1e3 * e2e_s / args.steps},
+            "gpu_launches": int(launches), "roofline": roof, "setup_s": t_setup}
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and isinstance(wl, FlatWorkload):
+        from oracle import oracle
+        oracle.build()
+        sample = wl.cpu_sample(torch, device)
+        qps, dt, desc = wl.cpu_run(oracle, sample)
+        line["cpu_baseline"] = {"value": qps, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
+                                "sample": desc, "seconds": dt}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -80,6 +80,8 @@ SIGNATURES = {
     "ann_cuda_merge_topk_device": (C.c_int, [C.c_int, _P, _P, C.c_int, _I64, _I64, C.c_int, _P, _P, _P]),
     "ann_cuda_flat_kernel_name": (C.c_char_p, []),
     "ann_cuda_set_flat_kernel": (C.c_int, [C.c_char_p]),
+    "ann_cuda_set_kernel_timing": (None, [C.c_int]),
+    "ann_cuda_index_last_flat_kernel_ms": (C.c_float, [_P]),
     "ann_cuda_launch_count": (C.c_uint64, []),
     # include/cuda_diskann_bridge.h
     "diskann_metal_available": (C.c_int, []),

@@ -14,6 +14,7 @@
 #include <memory>
 
 #include "common.cuh"
+#include "kernels.h"
 
 using namespace anncuda;
 
@@ -329,6 +330,7 @@ int launch_distance(const diskann_cuda_table &t, const float *queries, int nq, c
                 codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out);
         }
     }
+    count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
 }
@@ -450,6 +452,7 @@ int host_call(const diskann_cuda_table *table, const float *gathered, const floa
     if (d_ids || d_map) {
         check_ids_kernel<<<(total_n + 255) / 256, 256, 0, c->stream>>>(d_ids, d_map, total_n, t->num, nq,
                                                                       c->flag.as<int>());
+        count_launch();
         ANN_CUDA_TRY(cudaGetLastError());
     }
     if (launch_distance(*t, c->q.as<float>(), nq, d_ids, d_map, total_n, metric, c->out.as<float>(), c->stream))

@@ -39,6 +39,8 @@
 // writes a code to *status and all roles leave their loops.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "select.cuh"
@@ -213,6 +215,7 @@ struct KernelArgs {
     float *part_key;
     int32_t *part_idx;
     int *status;
+    int debug;  // measurement only: bit 0 = epilogue skips selection, bit 1 = MMA issuer skips the MMAs
 };
 
 template <int KR, bool SMALLK>
@@ -312,6 +315,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             const uint64_t a_lo = make_smem_desc(base + kABytes + ks * 32);
                             const uint64_t b_hi = make_smem_desc(base + 2 * kABytes + ks * 32);
                             const uint64_t b_lo = make_smem_desc(base + 2 * kABytes + kBBytes + ks * 32);
+                            if (args.debug & 2) continue;
                             mma_tf32(tmem_d, a_hi, b_lo, (kb | ks) != 0);
                             mma_tf32(tmem_d, a_lo, b_hi, 1);
                             mma_tf32(tmem_d, a_hi, b_hi, 1);
@@ -377,7 +381,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 const int32_t col0 = (int32_t)(tile * BN);
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
                 for (int cb = 0; cb < BN / 16; cb++) {
-                    if (cb * 16 >= ncols) break;
+                    if (cb * 16 >= ncols || (args.debug & 1)) break;
                     float key[16];
                     tmem_ld16(taddr + cb * 16, key);
 #pragma unroll
@@ -543,6 +547,10 @@ int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, con
     a.part_key = part_key;
     a.part_idx = part_idx;
     a.status = status;
+    {
+        const char *e = getenv("ANN_CUDA_TC_DEBUG");
+        a.debug = e ? atoi(e) : 0;
+    }
     if (k <= kQueueDepth) return launch_variant<1, true>(plan, maps, a, stream);
     if (k <= 32) return launch_variant<1, false>(plan, maps, a, stream);
     if (k <= 128) return launch_variant<4, false>(plan, maps, a, stream);

@@ -32,6 +32,7 @@ namespace {
 enum class FlatKernel { TC, SIMT };
 
 std::atomic<int> g_flat_kernel{-1};  // -1 = not chosen yet
+std::atomic<int> g_time_kernels{0};
 
 FlatKernel flat_kernel_choice() {
     int v = g_flat_kernel.load(std::memory_order_relaxed);
@@ -100,7 +101,11 @@ struct Workspace {
     GrowBuf x, qhi, qlo, qn, part_key, part_idx, sel_key, sel_idx, status, out_d, out_i;
     GrowBuf item_q, item_rb, item_re, item_slot, scratch, probes_key, probes;
     int *status_host = nullptr;  // pinned
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;  // bracket the flat kernel when timing is on
+    bool timed = false;
     void release() {
+        if (ev0) cudaEventDestroy(ev0);
+        if (ev1) cudaEventDestroy(ev1);
         for (GrowBuf *b : {&x, &qhi, &qlo, &qn, &part_key, &part_idx, &sel_key, &sel_idx, &status, &out_d, &out_i,
                            &item_q, &item_rb, &item_re, &item_slot, &scratch, &probes_key, &probes})
             b->release();
@@ -136,6 +141,7 @@ struct ann_cuda_index {
 
     mutable std::mutex ws_mu;
     mutable std::vector<Workspace *> ws_free;
+    mutable Workspace *last_timed_ws = nullptr;
 
     Workspace *acquire_ws(cudaStream_t user_stream, bool internal) const {
         {
@@ -230,10 +236,23 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         const FlatPlan plan = make_flat_plan(nq, st.n, k, sm_count(ix.device));
         if (ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4)) return -1;
         ANN_CUDA_TRY(cudaMemsetAsync(ws.status.ptr, 0, 4, stream));
+        const bool timing = g_time_kernels.load(std::memory_order_relaxed) != 0;
+        if (timing) {
+            if (!ws.ev0) {
+                ANN_CUDA_TRY(cudaEventCreate(&ws.ev0));
+                ANN_CUDA_TRY(cudaEventCreate(&ws.ev1));
+            }
+            ANN_CUDA_TRY(cudaEventRecord(ws.ev0, stream));
+        }
         if (launch_flat_tc(plan, st.hi, st.lo, st.norms, st.n, ws.qhi.as<float>(), ws.qlo.as<float>(), nq, dp, k,
                            ix.metric, ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.status.as<int>(),
                            ix.device, stream))
             return -1;
+        if (timing) {
+            ANN_CUDA_TRY(cudaEventRecord(ws.ev1, stream));
+            ws.timed = true;
+            ix.last_timed_ws = &ws;
+        }
         ANN_CUDA_TRY(cudaMemcpyAsync(ws.status_host, ws.status.ptr, 4, cudaMemcpyDeviceToHost, stream));
         return launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 0, plan.nq_tiles, nullptr,
                                   plan.chunks, nq, k, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device,
@@ -548,6 +567,17 @@ int ann_cuda_set_flat_kernel(const char *name) {
         return 0;
     }
     return set_error("unknown flat kernel name (tcgen05 | simt)");
+}
+
+void ann_cuda_set_kernel_timing(int on) { g_time_kernels.store(on ? 1 : 0); }
+
+float ann_cuda_index_last_flat_kernel_ms(const ann_cuda_index *ix) {
+    if (!ix || !ix->last_timed_ws || !ix->last_timed_ws->timed) return -1.f;
+    DeviceGuard g(ix->device);
+    float ms = -1.f;
+    if (cudaEventSynchronize(ix->last_timed_ws->ev1) != cudaSuccess) return -1.f;
+    if (cudaEventElapsedTime(&ms, ix->last_timed_ws->ev0, ix->last_timed_ws->ev1) != cudaSuccess) return -1.f;
+    return ms;
 }
 
 uint64_t ann_cuda_launch_count(void) { return launch_count_value(); }

@@ -75,8 +75,8 @@ class ShardedSearcher:
         if self._gather_d is None or tuple(self._gather_d.shape) != shape or self._gather_d.device != d_loc.device:
             self._gather_d = torch.empty(shape, dtype=d_loc.dtype, device=d_loc.device)
             self._gather_i = torch.empty(shape, dtype=i_loc.dtype, device=i_loc.device)
-        dist.all_gather_into_tensor(self._gather_d, d_loc.contiguous(), group=self.group)
-        dist.all_gather_into_tensor(self._gather_i, i_loc.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(self._gather_d.view(-1, d_loc.shape[-1]), d_loc.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(self._gather_i.view(-1, i_loc.shape[-1]), i_loc.contiguous(), group=self.group)
         if self._merge is not None:
             return self._merge(self._gather_d, self._gather_i)
         from .faiss_like import merge_topk_device

@@ -143,6 +143,13 @@ const char *ann_cuda_flat_kernel_name(void);
  * tests to cross-check one kernel against the other. */
 int ann_cuda_set_flat_kernel(const char *name);
 
+/* Measurement hook.  With timing on, every search records CUDA events around
+ * its flat-search kernel on the stream the kernel is launched on;
+ * ann_cuda_index_last_flat_kernel_ms waits for the latest such kernel of `index`
+ * and returns its duration in milliseconds (-1 if none was timed). */
+void ann_cuda_set_kernel_timing(int on);
+float ann_cuda_index_last_flat_kernel_ms(const ann_cuda_index *index);
+
 /* Number of kernel launches this library has issued from the calling process
  * since load (all threads).  For the benchmark's launch accounting. */
 uint64_t ann_cuda_launch_count(void);

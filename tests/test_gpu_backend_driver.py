@@ -1,0 +1,65 @@
+"""The C++ plugin surface (duckdb::GetGpuBackend / CpuToGpu / faiss::Index::search /
+GpuToCpu) exercised by the compiled driver, checked against the CPU oracle."""
+import json
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+from parity import assert_topk_matches
+
+pytestmark = pytest.mark.gpu
+DRIVER = os.path.join(ROOT, "duckdb-ann_b200", "backend_driver")
+
+
+def _run(tmp_path, mode, d, k, metric, xb, xq, nlist=0, nprobe=0, cent=None, assign=None):
+    inp, out = tmp_path / "in.bin", tmp_path / "out.bin"
+    with open(inp, "wb") as f:
+        f.write(np.array([d, len(xb), len(xq), k, metric, nlist, nprobe], np.int64).tobytes())
+        f.write(xb.tobytes()); f.write(xq.tobytes())
+        if cent is not None:
+            f.write(cent.tobytes()); f.write(assign.astype(np.int64).tobytes())
+    res = subprocess.run([DRIVER, mode, str(inp), str(out)], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr
+    info = json.loads(res.stdout.strip().splitlines()[-1])
+    raw = open(out, "rb").read()
+    nq = len(xq)
+    o = 0
+    D = np.frombuffer(raw, np.float32, nq * k, o).reshape(nq, k); o += nq * k * 4
+    I = np.frombuffer(raw, np.int64, nq * k, o).reshape(nq, k); o += nq * k * 8
+    D1 = np.frombuffer(raw, np.float32, nq * k, o).reshape(nq, k); o += nq * k * 4
+    I1 = np.frombuffer(raw, np.int64, nq * k, o).reshape(nq, k)
+    return info, D, I, D1, I1
+
+
+def test_info():
+    out = json.loads(subprocess.check_output([DRIVER, "info"], text=True))
+    assert out["available"] is True and out["backend"] == "cuda" and "B200" in out["device"]  # faiss_gpu_info()
+
+
+@pytest.mark.parametrize("metric", [1, 0])
+def test_flat_through_gpu_backend(tmp_path, oracle, metric):
+    rng = np.random.default_rng(42)
+    xb = rng.uniform(-1, 1, (3000, 96)).astype(np.float32)
+    xq = rng.uniform(-1, 1, (12, 96)).astype(np.float32)
+    info, D, I, D1, I1 = _run(tmp_path, "flat", 96, 7, metric, xb, xq)
+    assert info == {"backend": "cuda", "roundtrip_ok": 1, "rejects_unknown": 1}
+    Dref, Iref = oracle.flat_search(xb, xq, 7, metric)
+    assert_topk_matches(oracle, xb, xq, metric, D, I, Dref, Iref, "batch")
+    assert_topk_matches(oracle, xb, xq, metric, D1, I1, Dref, Iref, "one query per call")
+
+
+def test_ivf_through_gpu_backend(tmp_path, oracle):
+    rng = np.random.default_rng(43)
+    xb = rng.uniform(-1, 1, (2500, 64)).astype(np.float32)
+    xq = rng.uniform(-1, 1, (9, 64)).astype(np.float32)
+    cent = oracle.kmeans(xb, 12, niter=5, seed=2)
+    assign = oracle.ivf_assign(xb, cent, oracle.METRIC_L2)
+    off, rows = oracle.lists_from_assign(assign, 12)
+    info, D, I, D1, I1 = _run(tmp_path, "ivf", 64, 6, 1, xb, xq, 12, 12, cent, assign)
+    assert info["roundtrip_ok"] == 1
+    Dref, Iref = oracle.ivf_search(xb, cent, off, rows, xq, 6, 12, oracle.METRIC_L2)
+    assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D, I, Dref, Iref, "ivf batch")
+    assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D1, I1, Dref, Iref, "ivf one query per call")
