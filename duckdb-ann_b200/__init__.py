@@ -20,7 +20,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libann_cuda.so")
+LIB_PATH = os.environ.get("ANN_CUDA_LIB") or os.path.join(HERE, "libann_cuda.so")
 
 _lib = None
 

@@ -154,44 +154,53 @@ __device__ __forceinline__ float sq8_acc(float acc, float q, uint32_t code, floa
     return fmaf(q, xh, acc);
 }
 
-__device__ __forceinline__ float sq8_acc_word(float acc, float4 q, uint32_t w, float4 s, float4 m, bool l2) {
-    acc = sq8_acc(acc, q.x, w & 0xffu, s.x, m.x, l2);
-    acc = sq8_acc(acc, q.y, (w >> 8) & 0xffu, s.y, m.y, l2);
-    acc = sq8_acc(acc, q.z, (w >> 16) & 0xffu, s.z, m.z, l2);
-    acc = sq8_acc(acc, q.w, w >> 24, s.w, m.w, l2);
-    return acc;
-}
-
-// SQ8 rows, dim % 16 == 0 and dim <= 512: lane c owns dimensions [16c, 16c+16)
-// of every row, so its slice of min / scale lives in registers for the whole
-// kernel and its slice of the query is reloaded only when the query changes
-// (rows of one query are adjacent in DiskANN's lock-step batches,
-// rust_lib/src/disk_provider.rs:546-581).  A row is then one 16-byte load per
-// lane: the only traffic per row is the codes themselves.
+// SQ8 rows with dim % 4 == 0 and dim <= 512.  Lane l owns the 4*WPL consecutive
+// dimensions starting at 4*WPL*l of EVERY row, so its slice of min / scale stays
+// in registers for the whole kernel and its slice of the query is reloaded only
+// when the query changes (rows of one query are adjacent in DiskANN's lock-step
+// batches, rust_lib/src/disk_provider.rs:546-581).  A row is then WPL coalesced
+// 4-byte loads per lane and nothing else: the only traffic per row is its codes.
+// code/255 comes from a table in shared memory, replicated once per bank so the
+// lookups never conflict; the rest of the dequantisation is the reference's two
+// separately rounded operations.
 constexpr int kSq8RowsPerWarp = 8;
 
+__device__ __forceinline__ float sq8_lut_acc(float acc, float q, float t, float s, float m, bool l2) {
+    const float xh = __fadd_rn(__fmul_rn(t, s), m);  // (code/255)*scale+min, rust_lib/src/provider.rs:142-143
+    if (l2) {
+        const float d = q - xh;
+        return fmaf(d, d, acc);
+    }
+    return fmaf(q, xh, acc);
+}
+
+template <int WPL>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 batch_distance_sq8_regs_kernel(const uint8_t *__restrict__ codes, size_t num, int dim,
                                const float *__restrict__ mins, const float *__restrict__ scale,
                                const float *__restrict__ queries, int nq, const uint32_t *__restrict__ ids,
                                const uint32_t *__restrict__ qmap, int total_n, int metric,
                                float *__restrict__ out) {
+    __shared__ float lut[256 * 32];  // lut[c * 32 + lane] = c / 255
+    for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) lut[i] = code_over_255((float)(i >> 5));
+    __syncthreads();
     const int lane = threadIdx.x & 31;
     const long long warp_global = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const long long warps_total = (long long)gridDim.x * kWarpsPerBlock;
     const bool l2 = (metric == 0);
-    const int nchunk = dim >> 4;
-    const bool active = lane < nchunk;
-    float4 m[4], s[4], q[4];
+    const int d0 = lane * 4 * WPL;   // first dimension of this lane
+    const bool active = d0 < dim;    // dim is a multiple of 4 * WPL
+    const float *mylut = lut + lane;
+    float4 m[WPL], s[WPL], q[WPL];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        m[j] = active ? __ldg(reinterpret_cast<const float4 *>(mins) + lane * 4 + j) : make_float4(0, 0, 0, 0);
-        s[j] = active ? __ldg(reinterpret_cast<const float4 *>(scale) + lane * 4 + j) : make_float4(0, 0, 0, 0);
+    for (int j = 0; j < WPL; j++) {
+        m[j] = active ? __ldg(reinterpret_cast<const float4 *>(mins + d0) + j) : make_float4(0, 0, 0, 0);
+        s[j] = active ? __ldg(reinterpret_cast<const float4 *>(scale + d0) + j) : make_float4(0, 0, 0, 0);
         q[j] = make_float4(0, 0, 0, 0);
     }
     uint32_t cur_q = 0xffffffffu;
     for (long long base = warp_global * kSq8RowsPerWarp; base < total_n; base += warps_total * kSq8RowsPerWarp) {
-        uint4 w[kSq8RowsPerWarp];
+        uint32_t w[kSq8RowsPerWarp][WPL];
         uint32_t qi[kSq8RowsPerWarp];
         bool ok[kSq8RowsPerWarp];
 #pragma unroll
@@ -199,30 +208,40 @@ batch_distance_sq8_regs_kernel(const uint8_t *__restrict__ codes, size_t num, in
             const long long i = base + t;
             ok[t] = false;
             qi[t] = 0;
-            w[t] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int j = 0; j < WPL; j++) w[t][j] = 0;
             if (i < total_n) {
-                size_t r = ids ? (size_t)ids[i] : (size_t)i;
+                const size_t r = ids ? (size_t)ids[i] : (size_t)i;
                 qi[t] = qmap ? qmap[i] : 0u;
                 ok[t] = r < num && qi[t] < (uint32_t)nq;
-                if (ok[t] && active) w[t] = ld_stream4u(reinterpret_cast<const uint4 *>(codes + r * (size_t)dim) + lane);
+                if (ok[t] && active) {
+                    const uint32_t *p = reinterpret_cast<const uint32_t *>(codes + r * (size_t)dim + d0);
+#pragma unroll
+                    for (int j = 0; j < WPL; j++)
+                        asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(w[t][j]) : "l"(p + j));
+                }
             }
         }
 #pragma unroll
         for (int t = 0; t < kSq8RowsPerWarp; t++) {
             const long long i = base + t;
-            if (i >= total_n) break;  // warp-uniform
-            if (ok[t] && qi[t] != cur_q) {  // warp-uniform: qi is the same in every lane
+            if (i >= total_n) break;        // warp-uniform
+            if (ok[t] && qi[t] != cur_q) {  // warp-uniform: every lane reads the same map entry
                 cur_q = qi[t];
-                const float4 *q4 = reinterpret_cast<const float4 *>(queries + (size_t)cur_q * dim) + lane * 4;
+                const float4 *q4 = reinterpret_cast<const float4 *>(queries + (size_t)cur_q * dim + d0);
 #pragma unroll
-                for (int j = 0; j < 4; j++) q[j] = active ? __ldg(q4 + j) : make_float4(0, 0, 0, 0);
+                for (int j = 0; j < WPL; j++) q[j] = active ? __ldg(q4 + j) : make_float4(0, 0, 0, 0);
             }
             float acc = 0.f;
             if (ok[t] && active) {
-                acc = sq8_acc_word(acc, q[0], w[t].x, s[0], m[0], l2);
-                acc = sq8_acc_word(acc, q[1], w[t].y, s[1], m[1], l2);
-                acc = sq8_acc_word(acc, q[2], w[t].z, s[2], m[2], l2);
-                acc = sq8_acc_word(acc, q[3], w[t].w, s[3], m[3], l2);
+#pragma unroll
+                for (int j = 0; j < WPL; j++) {
+                    const uint32_t ww = w[t][j];
+                    acc = sq8_lut_acc(acc, q[j].x, mylut[(ww & 0xffu) << 5], s[j].x, m[j].x, l2);
+                    acc = sq8_lut_acc(acc, q[j].y, mylut[((ww >> 8) & 0xffu) << 5], s[j].y, m[j].y, l2);
+                    acc = sq8_lut_acc(acc, q[j].z, mylut[((ww >> 16) & 0xffu) << 5], s[j].z, m[j].z, l2);
+                    acc = sq8_lut_acc(acc, q[j].w, mylut[(ww >> 24) << 5], s[j].w, m[j].w, l2);
+                }
             }
             acc = warp_sum(acc);
             if (lane == 0) out[i] = ok[t] ? (l2 ? acc : -acc) : __int_as_float(0x7fc00000);
@@ -313,15 +332,24 @@ int launch_distance(const diskann_cuda_table &t, const float *queries, int nq, c
         }
     } else {
         const uint8_t *codes = static_cast<const uint8_t *>(t.rows);
-        const bool regs = (t.dim % 16 == 0) && t.dim <= 512 && ((reinterpret_cast<uintptr_t>(codes) & 15) == 0) &&
+        // words (4 codes) per lane: the smallest count that covers the row with 32 lanes
+        int wpl = 0;
+        for (int c = 1; c <= 4 && !wpl; c++)
+            if (t.dim <= 128 * c && t.dim % (4 * c) == 0) wpl = c;
+        const bool regs = wpl != 0 && ((reinterpret_cast<uintptr_t>(codes) & 3) == 0) &&
                           ((reinterpret_cast<uintptr_t>(queries) & 15) == 0);
         if (regs) {
             long long warps = ((long long)total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
             long long blocks = (warps + kWarpsPerBlock - 1) / kWarpsPerBlock;
-            const long long cap = (long long)sms * 8;
+            const long long cap = (long long)sms * 4;
             if (blocks > cap) blocks = cap;
-            batch_distance_sq8_regs_kernel<<<(unsigned)blocks, kWarpsPerBlock * 32, 0, stream>>>(
-                codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out);
+            const unsigned g = (unsigned)blocks, b = kWarpsPerBlock * 32;
+            switch (wpl) {
+            case 1: batch_distance_sq8_regs_kernel<1><<<g, b, 0, stream>>>(codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out); break;
+            case 2: batch_distance_sq8_regs_kernel<2><<<g, b, 0, stream>>>(codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out); break;
+            case 3: batch_distance_sq8_regs_kernel<3><<<g, b, 0, stream>>>(codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out); break;
+            default: batch_distance_sq8_regs_kernel<4><<<g, b, 0, stream>>>(codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out); break;
+            }
         } else {
             long long blocks = ((long long)total_n + kWarpsPerBlock - 1) / kWarpsPerBlock;
             const long long cap = (long long)sms * 32;

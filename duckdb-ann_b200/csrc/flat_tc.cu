@@ -14,16 +14,29 @@
 // L2 uses key = |x|^2 - 2 q.x (the query norm is constant per query); inner
 // product uses key = -q.x.  Smaller key is better.
 //
-// Decomposition.  A work unit is (tile of 128 queries) x (chunk of database
-// tiles, 256 rows each).  CTAs are persistent and walk units round-robin, query
-// tile fastest, so the CTAs running at any moment read the same database rows
-// and share them through L2.  Per unit the kernel leaves 128 unsorted k-lists in
-// global memory; merge.cu reduces the chunks of a query to the final top-k.
+// Shared threshold.  Once a chunk holds k rows for a query, its k-th best key
+// bounds the query's final k-th best, so rows of ANY chunk above it cannot be in
+// the answer.  Each chunk publishes that key with atomicMin to a per-query word
+// and reads the word at every tile; the number of list insertions per query then
+// grows like k log N for the whole database instead of per chunk.
+//
+// Decomposition.  Work is handed out dynamically.  The database is cut into
+// chunks of a few 256-row tiles; every tile of 128 queries has a counter of
+// chunks not yet taken.  A CTA adopts a query tile (its home tile first), takes
+// chunks of it one by one with atomicAdd, and keeps ONE k-list per row for as long
+// as it stays with that query tile, so a list sees a long stream of rows and
+// settles after the first few tiles.  When a query tile has no chunks left the CTA
+// moves to another one and starts a new list there.  All query tiles advance
+// through the chunks in the same order at the same rate, so the CTAs running at
+// any moment read the same database rows and share them through L2.  At the end
+// each query has one unsorted k-list per CTA that worked on its tile (at most
+// lists_per_qt); merge.cu reduces them to the final top-k.
 //
 // CTA layout (192 threads, one CTA per SM):
-//   warp 0     TMA producer: per K block of 32 floats, four tiled loads
-//              (q_hi, q_lo: 128 x 32; x_hi, x_lo: 256 x 32; 128-byte swizzle)
-//              into a 2-stage shared-memory ring, signalled by mbarriers;
+//   warp 0     scheduler + TMA producer: takes the next chunk, announces it to the
+//              other roles through a small descriptor ring, then per K block
+//              issues four tiled loads (q_hi, q_lo: 128 rows; x_hi, x_lo: 256 rows;
+//              swizzled) into the shared-memory ring, signalled by mbarriers;
 //   warp 1     allocates 512 TMEM columns (two 128 x 256 fp32 accumulators) and
 //              issues the MMAs; tcgen05.commit releases ring stages and hands
 //              finished accumulators to the epilogue;
@@ -50,13 +63,21 @@ namespace {
 
 constexpr int BM = 128;           // queries per tile (TMEM lanes)
 constexpr int BN = 256;           // database rows per tile (TMEM columns)
-constexpr int BK = 32;            // floats per K block = one 128-byte swizzled row
-constexpr int kStages = 2;
+#ifndef ANN_TC_BK
+#define ANN_TC_BK 16
+#endif
+constexpr int BK = ANN_TC_BK;     // floats per K block: 32 = one 128-byte swizzled row, 16 = one 64-byte row
+static_assert(BK == 32 || BK == 16, "K block is one 128-byte or one 64-byte swizzled row");
+constexpr int kStages = 64 / BK;  // the ring always holds 64 floats of K: 2 x 96 KB or 4 x 48 KB
+constexpr int kRowBytes = BK * 4;
+constexpr uint64_t kDescLayout = BK == 32 ? 2ull : 4ull;    // SWIZZLE_128B : SWIZZLE_64B
+constexpr uint64_t kDescSbo = (8 * kRowBytes) >> 4;         // 8-row group stride, in 16-byte units
 constexpr int kABytes = BM * BK * 4;                    // 16 KB
 constexpr int kBBytes = BN * BK * 4;                    // 32 KB
 constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;  // hi + lo of both operands: 96 KB
 constexpr int kQueueDepth = 16;   // per-row candidate queue, also the small-k list capacity
 constexpr int kThreads = 192;
+constexpr int kWorkRing = 4;       // chunk descriptors in flight between the scheduler and the other roles
 
 struct SmemLayout {
     static constexpr int stages = 0;
@@ -64,8 +85,10 @@ struct SmemLayout {
     static constexpr int queue_idx = queue_key + kQueueDepth * BM * 4;
     static constexpr int xnorm = queue_idx + kQueueDepth * BM * 4;
     static constexpr int barriers = xnorm + 4 * 2 * BN * 4;  // (after a private norm copy per epilogue warp)
-    // barriers: full[2] empty[2] tmem_full[2] tmem_empty[2]
-    static constexpr int tmem_ptr = barriers + 8 * 8;
+    // barriers: full[kStages] empty[kStages] tmem_full[2] tmem_empty[2]
+    static constexpr int work_bars = barriers + (2 * kStages + 4) * 8;  // wfull[kWorkRing] wempty[kWorkRing]
+    static constexpr int work_ring = work_bars + 2 * kWorkRing * 8;    // kWorkRing descriptors of 32 bytes
+    static constexpr int tmem_ptr = work_ring + kWorkRing * 32;
     static constexpr int abort_flag = tmem_ptr + 4;
     static constexpr int total = abort_flag + 4;
 };
@@ -137,10 +160,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128
-// bytes, 8-row groups 1024 bytes apart.
+// Shared-memory matrix descriptor: K-major operand, rows of kRowBytes with the
+// matching swizzle, 8-row groups 8 * kRowBytes apart.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
-    return (uint64_t)((addr >> 4) & 0x3fffu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+    return (uint64_t)((addr >> 4) & 0x3fffu) | (1ull << 16) | (kDescSbo << 32) | (1ull << 46) | (kDescLayout << 61);
 }
 
 __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
@@ -174,7 +197,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
 // Folds the queues of this warp's 32 rows into their k-lists in global memory.
 template <int KR>
 __device__ __noinline__ void flush_queues(float *unit_key, int32_t *unit_idx, int k, int row0, const float *qkey,
-                                          const int32_t *qidx, int &cnt, float &tau, int lane) {
+                                          const int32_t *qidx, int &cnt, float &tau, int lane, uint32_t *qtau_tile) {
     for (int r = 0; r < 32; r++) {
         const int c = __shfl_sync(kFullMask, cnt, r);
         if (c == 0) continue;
@@ -196,8 +219,11 @@ __device__ __noinline__ void flush_queues(float *unit_key, int32_t *unit_idx, in
         }
         list.store(lk, k, lane);
         if (lane == r) {
-            tau = m;
+            // m is the k-th best key of this chunk so far: no row of any chunk with a
+            // larger key can be in the query's final top-k, so it is published for all
+            tau = fminf(tau, m);
             cnt = 0;
+            if (m < kInf) atomicMin(qtau_tile + row, float_to_ordered(m));
         }
     }
     __syncwarp();
@@ -210,19 +236,140 @@ struct KernelArgs {
     int kblocks;  // dp / BK
     int k;
     int l2;
-    int nq_tiles, chunks, tiles_per_chunk, units;
+    int nq_tiles, nchunks, tiles_per_chunk, lists_per_qt;
     int64_t ntiles;
+    int *next_chunk;  // [nq_tiles] chunks handed out so far (zero on entry)
+    int *nlists;      // [nq_tiles] lists started so far (zero on entry)
     float *part_key;
     int32_t *part_idx;
+    uint32_t *qtau;  // per query: smallest k-th-best key any chunk has published (ordered-uint form)
     int *status;
+    unsigned long long *stats;  // measurement only (may be null): see kStat* below
     int debug;  // measurement only: bit 0 = epilogue skips selection, bit 1 = MMA issuer skips the MMAs
 };
 
-template <int KR, bool SMALLK>
+// How the epilogue keeps the k best keys of a row:
+//   kSelSmem    k <= 16: the list sits in shared memory, one column per thread;
+//   kSelAppend  16 < k <= 128: every key below the row's threshold is appended to a
+//               512-slot buffer of the row in global memory (a plain store, no
+//               dependent work); when a buffer is nearly full the warp sorts it in
+//               registers (bitonic, 16 keys per lane), keeps the best k and tightens
+//               the threshold to the k-th.  Buffers fill at n = 512, ~2.5k, ~13k, ...
+//               rows seen, so a row is compacted a handful of times per search;
+//   kSelReplace k > 128: 16-deep queue in shared memory folded into a replace-max
+//               list in global memory (exact for any k, slower).
+// Slots of the optional statistics array (cycle counts are summed over CTAs / warps).
+enum { kStatCompactRows = 0, kStatAppends = 1, kStatCompactCycles = 2, kStatEpiWaitCycles = 3, kStatMmaWaitTmem = 4,
+       kStatMmaWaitSmem = 5, kStatEpiTileCycles = 6, kStatTiles = 7 };
+
+enum SelMode { kSelSmem = 0, kSelAppend = 1, kSelReplace = 2 };
+constexpr int kBuf = 512;  // candidate slots per row in append mode
+static_assert(kAppendMaxK <= kBuf / 2, "a compacted row must leave room for new candidates");
+
+// ---- bitonic sort of 512 (key, idx) pairs held by a warp, 16 per lane -------------------------
+// Element e lives in lane e / 16, register e % 16, so exchanges at distance < 16 stay
+// inside a thread and larger ones are one shuffle.  Ascending by key.
+__device__ __forceinline__ void sort512(float (&key)[16], int32_t (&idx)[16], int lane) {
+#pragma unroll
+    for (int size = 2; size <= 512; size <<= 1) {
+#pragma unroll
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            if (stride >= 16) {
+                const int ls = stride >> 4;
+                const bool upper = (lane & ls) != 0;
+                const bool asc = (((lane << 4) & size) == 0);
+                const bool keep_min = (!upper) == asc;
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float ok = __shfl_xor_sync(kFullMask, key[i], ls);
+                    const int32_t oi = __shfl_xor_sync(kFullMask, idx[i], ls);
+                    const bool take = keep_min ? (ok < key[i]) : (ok > key[i]);
+                    if (take) {
+                        key[i] = ok;
+                        idx[i] = oi;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    if ((i & stride) == 0) {
+                        const int j = i | stride;
+                        const bool asc = ((((lane << 4) | i) & size) == 0);
+                        const bool sw = asc ? (key[i] > key[j]) : (key[i] < key[j]);
+                        if (sw) {
+                            const float tk = key[i];
+                            key[i] = key[j];
+                            key[j] = tk;
+                            const int32_t ti = idx[i];
+                            idx[i] = idx[j];
+                            idx[j] = ti;
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Append mode: sorts the buffers of the rows in `need` (bit r = row row0 + r of this
+// warp), keeps their best k entries in slots [0, k) (sorted, unused slots get index
+// -1) and tightens the rows' thresholds.
+__device__ __noinline__ void compact_rows(float *slot_key, int32_t *slot_idx, int k, int row0, unsigned need, int &cnt,
+                                          float &tau, int lane, uint32_t *qtau_tile) {
+    __syncwarp();  // the appends of every lane are visible to the whole warp
+    while (need) {
+        const int r = __ffs(need) - 1;
+        need &= need - 1;
+        const int c = __shfl_sync(kFullMask, cnt, r);
+        float *bk = slot_key + (size_t)(row0 + r) * kBuf;
+        int32_t *bi = slot_idx + (size_t)(row0 + r) * kBuf;
+        float key[16];
+        int32_t idx[16];
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            const float4 kk = *reinterpret_cast<const float4 *>(bk + lane * 16 + v * 4);
+            const int4 ii = *reinterpret_cast<const int4 *>(bi + lane * 16 + v * 4);
+            key[v * 4 + 0] = kk.x; key[v * 4 + 1] = kk.y; key[v * 4 + 2] = kk.z; key[v * 4 + 3] = kk.w;
+            idx[v * 4 + 0] = ii.x; idx[v * 4 + 1] = ii.y; idx[v * 4 + 2] = ii.z; idx[v * 4 + 3] = ii.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            if (lane * 16 + i >= c) {  // slots past the fill hold stale data
+                key[i] = kInf;
+                idx[i] = -1;
+            }
+        }
+        sort512(key, idx, lane);
+        float kth = kInf;
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int e = lane * 16 + i;
+            if (e < k) {
+                bk[e] = key[i];
+                bi[e] = idx[i];
+            }
+            if (e == k - 1) kth = key[i];
+        }
+        kth = __shfl_sync(kFullMask, kth, (k - 1) >> 4);
+        if (lane == r) {
+            cnt = c < k ? c : k;
+            if (c >= k) {
+                // the k-th best key so far: nothing above it can reach the final top-k
+                tau = fminf(tau, kth);
+                atomicMin(qtau_tile + row0 + r, float_to_ordered(kth));
+            }
+        }
+    }
+    __syncwarp();
+}
+
+template <int KR, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constant__ CUtensorMap map_qlo,
                const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
                const KernelArgs args) {
+    constexpr bool SMALLK = (MODE == kSelSmem);
+    constexpr bool APPEND = (MODE == kSelAppend);
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
@@ -247,6 +394,10 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             mbar_init(bar_tfull + 8 * b, 1);
             mbar_init(bar_tempty + 8 * b, 4);  // one arrival per epilogue warp
         }
+        for (int w = 0; w < kWorkRing; w++) {
+            mbar_init(smem_base + SmemLayout::work_bars + 8 * w, 1);                    // written by the scheduler
+            mbar_init(smem_base + SmemLayout::work_bars + 8 * (kWorkRing + w), 5);      // read by MMA + 4 epilogue warps
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -263,23 +414,64 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
     tmem_fence_after();
     const uint32_t tmem_base = *tmem_ptr_s;
 
+    struct Work {
+        int qt, tile_begin, tile_end, slot, fresh, pad[3];
+    };
+    volatile Work *ring = reinterpret_cast<volatile Work *>(smem + SmemLayout::work_ring);
+    const uint32_t bar_wfull = smem_base + SmemLayout::work_bars;
+    const uint32_t bar_wempty = bar_wfull + 8 * kWorkRing;
+
     if (warp == 0) {
-        // ---------------------------------------------------------------- TMA producer
+        // ---------------------------------------------------------------- scheduler + TMA producer
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
-            for (int u = blockIdx.x; u < args.units; u += gridDim.x) {
-                const int qt = u % args.nq_tiles, chunk = u / args.nq_tiles;
-                const int64_t t_begin = (int64_t)chunk * args.tiles_per_chunk;
+            uint32_t wi = 0;  // work items announced
+            int cur = -1, slot = -1, fresh = 0;
+            // Adopts query tile t if it still has chunks and a free list slot.
+            auto adopt = [&](int t) -> bool {
+                if (*reinterpret_cast<volatile int *>(args.next_chunk + t) >= args.nchunks) return false;
+                const int j = atomicAdd(args.nlists + t, 1);
+                if (j >= args.lists_per_qt) return false;
+                cur = t;
+                slot = t * args.lists_per_qt + j;
+                fresh = 1;
+                return true;
+            };
+            const int home = blockIdx.x % args.nq_tiles;
+            bool have = false;
+            for (int i = 0; i < args.nq_tiles && !have; i++) have = adopt((home + i) % args.nq_tiles);
+            while (have) {
+                const int c = atomicAdd(args.next_chunk + cur, 1);
+                if (c >= args.nchunks) {  // this query tile is finished: look for another one
+                    have = false;
+                    const int from = cur;
+                    for (int i = 1; i < args.nq_tiles && !have; i++) have = adopt((from + i) % args.nq_tiles);
+                    continue;
+                }
+                const int64_t t_begin = (int64_t)c * args.tiles_per_chunk;
                 int64_t t_end = t_begin + args.tiles_per_chunk;
                 if (t_end > args.ntiles) t_end = args.ntiles;
+                {
+                    const uint32_t w = wi % kWorkRing;
+                    if (!mbar_wait(bar_wempty + 8 * w, ((wi / kWorkRing) & 1) ^ 1, abort_flag, args.status, 5)) goto done;
+                    ring[w].qt = cur;
+                    ring[w].tile_begin = (int)t_begin;
+                    ring[w].tile_end = (int)t_end;
+                    ring[w].slot = slot;
+                    ring[w].fresh = fresh;
+                    fresh = 0;
+                    __threadfence_block();
+                    mbar_arrive(bar_wfull + 8 * w);
+                    wi++;
+                }
                 for (int64_t tile = t_begin; tile < t_end; tile++) {
                     for (int kb = 0; kb < args.kblocks; kb++) {
                         if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, args.status, 1)) goto done;
                         const uint32_t full = bar_full + 8 * stage;
                         const uint32_t base = smem_base + stage * kStageBytes;
                         mbar_expect_tx(full, kStageBytes);
-                        tma_load_2d(base, &map_qhi, kb * BK, qt * BM, full);
-                        tma_load_2d(base + kABytes, &map_qlo, kb * BK, qt * BM, full);
+                        tma_load_2d(base, &map_qhi, kb * BK, cur * BM, full);
+                        tma_load_2d(base + kABytes, &map_qlo, kb * BK, cur * BM, full);
                         tma_load_2d(base + 2 * kABytes, &map_xhi, kb * BK, (int32_t)(tile * BN), full);
                         tma_load_2d(base + 2 * kABytes + kBBytes, &map_xlo, kb * BK, (int32_t)(tile * BN), full);
                         if (++stage == kStages) {
@@ -289,24 +481,37 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     }
                 }
             }
+            {  // end marker
+                const uint32_t w = wi % kWorkRing;
+                if (!mbar_wait(bar_wempty + 8 * w, ((wi / kWorkRing) & 1) ^ 1, abort_flag, args.status, 5)) goto done;
+                ring[w].qt = -1;
+                __threadfence_block();
+                mbar_arrive(bar_wfull + 8 * w);
+            }
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             uint32_t it = 0;  // tiles issued by this CTA
-            for (int u = blockIdx.x; u < args.units; u += gridDim.x) {
-                const int chunk = u / args.nq_tiles;
-                const int64_t t_begin = (int64_t)chunk * args.tiles_per_chunk;
-                int64_t t_end = t_begin + args.tiles_per_chunk;
-                if (t_end > args.ntiles) t_end = args.ntiles;
+            for (uint32_t wi = 0;; wi++) {
+                const uint32_t w = wi % kWorkRing;
+                if (!mbar_wait(bar_wfull + 8 * w, (wi / kWorkRing) & 1, abort_flag, args.status, 6)) goto done;
+                const int qt = ring[w].qt;
+                const int64_t t_begin = ring[w].tile_begin, t_end = ring[w].tile_end;
+                mbar_arrive(bar_wempty + 8 * w);
+                if (qt < 0) break;
                 for (int64_t tile = t_begin; tile < t_end; tile++, it++) {
                     const uint32_t buf = it & 1;
+                    long long t0 = args.stats ? clock64() : 0;
                     if (!mbar_wait(bar_tempty + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag, args.status, 2)) goto done;
+                    if (args.stats) atomicAdd(args.stats + kStatMmaWaitTmem, (unsigned long long)(clock64() - t0));
                     tmem_fence_after();
                     const uint32_t tmem_d = tmem_base + buf * BN;
                     for (int kb = 0; kb < args.kblocks; kb++) {
+                        t0 = args.stats ? clock64() : 0;
                         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, args.status, 3)) goto done;
+                        if (args.stats) atomicAdd(args.stats + kStatMmaWaitSmem, (unsigned long long)(clock64() - t0));
                         tmem_fence_after();
                         const uint32_t base = smem_base + stage * kStageBytes;
 #pragma unroll
@@ -340,28 +545,63 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
         float *xn_s = xn_all + quarter * (2 * BN);
         const int k = args.k;
         uint32_t it = 0;
-        for (int u = blockIdx.x; u < args.units; u += gridDim.x) {
-            const int qt = u % args.nq_tiles, chunk = u / args.nq_tiles;
-            const int64_t t_begin = (int64_t)chunk * args.tiles_per_chunk;
-            int64_t t_end = t_begin + args.tiles_per_chunk;
-            if (t_end > args.ntiles) t_end = args.ntiles;
-            const bool row_valid = (int64_t)qt * BM + row < args.nq;
-            float *unit_key = args.part_key + (size_t)u * BM * k;
-            int32_t *unit_idx = args.part_idx + (size_t)u * BM * k;
-            float tau = row_valid ? kInf : -kInf;
-            int cnt = 0;   // queue fill (large k)
-            int pos = 0;   // slot of the current maximum (small k)
-            if (SMALLK) {
+        // state of the current list (one per row, kept while the CTA stays with a query tile)
+        float *unit_key = nullptr;
+        int32_t *unit_idx = nullptr;
+        uint32_t *qtau_tile = nullptr;
+        bool row_valid = false;
+        float tau = -kInf;       // a key must be below this to matter
+        float list_max = kInf;   // small k: current maximum of this row's list
+        float published = kInf;
+        int cnt = 0;             // queue fill (large k)
+        int pos = 0;             // slot of the current maximum (small k)
+        const int stride = APPEND ? kBuf : k;  // slots per row in the list memory
+        auto close_list = [&]() {
+            if (!unit_key) return;
+            if (APPEND) {
+                const unsigned need = __ballot_sync(kFullMask, cnt > 0);
+                if (need) compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_tile);
+            } else if (SMALLK) {
                 for (int s = 0; s < k; s++) {
-                    qkey[s * BM + row] = kInf;
-                    qidx[s * BM + row] = -1;
+                    unit_key[(size_t)row * k + s] = qkey[s * BM + row];
+                    unit_idx[(size_t)row * k + s] = qidx[s * BM + row];
                 }
             } else {
-                for (int r = 0; r < 32; r++) {
-                    const size_t base = (size_t)(quarter * 32 + r) * k;
-                    for (int s = lane; s < k; s += 32) {
-                        unit_key[base + s] = kInf;
-                        unit_idx[base + s] = -1;
+                if (__any_sync(kFullMask, cnt > 0))
+                    flush_queues<KR>(unit_key, unit_idx, k, quarter * 32, qkey, qidx, cnt, tau, lane, qtau_tile);
+            }
+        };
+        for (uint32_t wi = 0;; wi++) {
+            const uint32_t w = wi % kWorkRing;
+            if (!mbar_wait(bar_wfull + 8 * w, (wi / kWorkRing) & 1, abort_flag, args.status, 7)) goto done;
+            const int qt = ring[w].qt, slot = ring[w].slot, fresh = ring[w].fresh;
+            const int64_t t_begin = ring[w].tile_begin, t_end = ring[w].tile_end;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_wempty + 8 * w);
+            if (qt < 0) break;
+            if (fresh) {
+                close_list();
+                unit_key = args.part_key + (size_t)slot * BM * stride;
+                unit_idx = args.part_idx + (size_t)slot * BM * stride;
+                qtau_tile = args.qtau + (size_t)qt * BM;
+                row_valid = (int64_t)qt * BM + row < args.nq;
+                tau = row_valid ? kInf : -kInf;
+                list_max = kInf;
+                published = kInf;
+                cnt = 0;
+                pos = 0;
+                if (APPEND) {
+                    // nothing to initialise: a row's buffer is valid up to its fill count
+                } else if (SMALLK) {
+                    for (int s = 0; s < k; s++) {
+                        qkey[s * BM + row] = kInf;
+                        qidx[s * BM + row] = -1;
+                    }
+                } else {
+                    // indices of every slot are -1 on entry (host memset); keys start at +inf
+                    for (int r = 0; r < 32; r++) {
+                        const size_t base = (size_t)(quarter * 32 + r) * k;
+                        for (int s = lane; s < k; s += 32) unit_key[base + s] = kInf;
                     }
                 }
             }
@@ -374,8 +614,20 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     }
                     __syncwarp();
                 }
+                long long t0 = (args.stats && lane == 0) ? clock64() : 0;
                 if (!mbar_wait(bar_tfull + 8 * buf, (it >> 1) & 1, abort_flag, args.status, 4)) goto done;
+                long long t1 = 0;
+                if (args.stats && lane == 0) {
+                    t1 = clock64();
+                    atomicAdd(args.stats + kStatEpiWaitCycles, (unsigned long long)(t1 - t0));
+                    atomicAdd(args.stats + kStatTiles, 1ull);
+                }
                 tmem_fence_after();
+                if (row_valid) {
+                    // thresholds published by the other CTAs working on this query (L2-coherent read)
+                    const uint32_t tg = __ldcg(qtau_tile + row);
+                    if (tg < float_to_ordered(tau)) tau = ordered_to_float(tg);
+                }
                 const int64_t rem = args.n - tile * BN;
                 const int ncols = rem < BN ? (int)rem : BN;
                 const int32_t col0 = (int32_t)(tile * BN);
@@ -388,7 +640,37 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     for (int j = 0; j < 16; j++)
                         key[j] = args.l2 ? fmaf(-2.f, key[j], xn_s[buf * BN + cb * 16 + j]) : -key[j];
                     const int nvalid = ncols - cb * 16;  // >= 1
-                    if (SMALLK) {
+                    if (APPEND) {
+                        uint32_t mask = 0;
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (j < nvalid && key[j] < tau) mask |= 1u << j;
+                        const unsigned need = __ballot_sync(kFullMask, cnt + __popc(mask) > kBuf);
+                        if (need) {
+                            const long long c0 = args.stats ? clock64() : 0;
+                            compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_tile);
+                            if (args.stats && lane == 0) {
+                                atomicAdd(args.stats + kStatCompactCycles, (unsigned long long)(clock64() - c0));
+                                atomicAdd(args.stats + kStatCompactRows, (unsigned long long)__popc(need));
+                            }
+                            mask = 0;
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                if (j < nvalid && key[j] < tau) mask |= 1u << j;
+                        }
+                        if (args.debug & 4) mask = 0;
+                        if (args.stats && mask) atomicAdd(args.stats + kStatAppends, (unsigned long long)__popc(mask));
+                        float *bk = unit_key + (size_t)row * kBuf;
+                        int32_t *bi = unit_idx + (size_t)row * kBuf;
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            if (mask & (1u << j)) {
+                                bk[cnt] = key[j];
+                                bi[cnt] = col0 + cb * 16 + j;
+                                cnt++;
+                            }
+                        }
+                    } else if (SMALLK) {
 #pragma unroll
                         for (int j = 0; j < 16; j++) {
                             if (j < nvalid && key[j] < tau) {
@@ -402,7 +684,8 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                                         pos = s;
                                     }
                                 }
-                                tau = m;
+                                list_max = m;
+                                tau = fminf(tau, m);
                             }
                         }
                     } else {
@@ -412,7 +695,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             if (j < nvalid && key[j] < tau) mask |= 1u << j;
                         const bool overflow = cnt + __popc(mask) > kQueueDepth;
                         if (__any_sync(kFullMask, overflow)) {
-                            flush_queues<KR>(unit_key, unit_idx, k, quarter * 32, qkey, qidx, cnt, tau, lane);
+                            flush_queues<KR>(unit_key, unit_idx, k, quarter * 32, qkey, qidx, cnt, tau, lane, qtau_tile);
                             mask = 0;
 #pragma unroll
                             for (int j = 0; j < 16; j++)
@@ -431,17 +714,14 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 tmem_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
-            }
-            if (SMALLK) {
-                for (int s = 0; s < k; s++) {
-                    unit_key[(size_t)row * k + s] = qkey[s * BM + row];
-                    unit_idx[(size_t)row * k + s] = qidx[s * BM + row];
+                if (args.stats && lane == 0) atomicAdd(args.stats + kStatEpiTileCycles, (unsigned long long)(clock64() - t1));
+                if (SMALLK && list_max < published) {
+                    published = list_max;
+                    atomicMin(qtau_tile + row, float_to_ordered(list_max));
                 }
-            } else {
-                if (__any_sync(kFullMask, cnt > 0))
-                    flush_queues<KR>(unit_key, unit_idx, k, quarter * 32, qkey, qidx, cnt, tau, lane);
             }
         }
+        close_list();
     }
 done:
     tmem_fence_before();
@@ -469,8 +749,8 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// Row-major (rows x dp) fp32 matrix, boxes of box_rows x 32 floats, 128-byte
-// swizzle.  Rows past `rows` read as zero.
+// Row-major (rows x dp) fp32 matrix, boxes of box_rows x BK floats, swizzled by
+// row width.  Rows past `rows` read as zero.
 int make_map(CUtensorMap *map, const float *base, int64_t rows, int dp, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return set_error("cuTensorMapEncodeTiled is not available from the driver");
@@ -479,17 +759,18 @@ int make_map(CUtensorMap *map, const float *base, int64_t rows, int dp, int box_
     cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, BK == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return set_error("cuTensorMapEncodeTiled failed with code %d", (int)r);
     return 0;
 }
 
-template <int KR, bool SMALLK>
+template <int KR, int MODE>
 int launch_variant(const FlatPlan &plan, const CUtensorMap maps[4], const KernelArgs &args, cudaStream_t stream) {
-    ANN_CUDA_TRY(cudaFuncSetAttribute(flat_tc_kernel<KR, SMALLK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    ANN_CUDA_TRY(cudaFuncSetAttribute(flat_tc_kernel<KR, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       kSmemBytes));
-    flat_tc_kernel<KR, SMALLK><<<plan.grid, kThreads, kSmemBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], args);
+    flat_tc_kernel<KR, MODE><<<plan.grid, kThreads, kSmemBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], args);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -501,28 +782,30 @@ FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms) {
     FlatPlan p;
     p.nq_tiles = (int)((nq + BM - 1) / BM);
     const int64_t ntiles = (n + BN - 1) / BN;
-    int64_t max_chunks = 8192 / (k > 0 ? k : 1);  // the merge sorts chunks * k candidates per query
-    if (max_chunks < 1) max_chunks = 1;
-    if (max_chunks > ntiles) max_chunks = ntiles;
-    int64_t chunks = 1;
-    for (int waves = 8; waves >= 1; waves >>= 1) {
-        chunks = (int64_t)sms * waves / p.nq_tiles;  // rounded down: units fill at most `waves` full waves
-        if (chunks < 1) chunks = 1;
-        if (waves == 1 || ntiles / chunks >= 32) break;
-    }
-    if (chunks > max_chunks) chunks = max_chunks;
-    if (chunks < 1) chunks = 1;
-    p.tiles_per_chunk = (int)((ntiles + chunks - 1) / chunks);
-    p.chunks = (int)((ntiles + p.tiles_per_chunk - 1) / p.tiles_per_chunk);
-    p.units = p.nq_tiles * p.chunks;
-    p.grid = p.units < sms ? p.units : sms;
-    p.part_entries = (size_t)p.units * BM * (size_t)k;
+    // CTAs that will share one query tile, and chunks small enough that they finish together
+    const int ctas_per_qt = (sms + p.nq_tiles - 1) / p.nq_tiles;
+    int64_t tpc = ntiles / ((int64_t)ctas_per_qt * 8);
+    if (tpc < 1) tpc = 1;
+    if (tpc > 512) tpc = 512;
+    p.tiles_per_chunk = (int)tpc;
+    p.nchunks = (int)((ntiles + tpc - 1) / tpc);
+    // one k-list per CTA that ever works on a query tile; the merge sorts lists * k candidates
+    int lists = 2 * ctas_per_qt + 2;
+    const int cap = kMergeCandidates / (k > 0 ? k : 1);
+    if (lists > cap) lists = cap;
+    if (lists > p.nchunks) lists = p.nchunks;
+    if (lists < 1) lists = 1;
+    p.lists_per_qt = lists;
+    const int64_t work = (int64_t)p.nq_tiles * p.nchunks;
+    p.grid = (int)(work < sms ? work : sms);
+    p.list_stride = (k > kQueueDepth && k <= kAppendMaxK) ? kBuf : k;
+    p.part_entries = (size_t)p.nq_tiles * lists * BM * (size_t)p.list_stride;
     return p;
 }
 
 int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
-                   int32_t *part_idx, int *status, int device, cudaStream_t stream) {
+                   int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream) {
     (void)device;
     if (n <= 0 || nq <= 0) return 0;
     if (k <= 0 || k > kMaxK) return set_error("k must be in [1, %d]", kMaxK);
@@ -540,22 +823,43 @@ int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, con
     a.k = k;
     a.l2 = metric != 0;
     a.nq_tiles = plan.nq_tiles;
-    a.chunks = plan.chunks;
+    a.nchunks = plan.nchunks;
     a.tiles_per_chunk = plan.tiles_per_chunk;
-    a.units = plan.units;
+    a.lists_per_qt = plan.lists_per_qt;
+    a.next_chunk = sched;
+    a.nlists = sched + plan.nq_tiles;
     a.ntiles = (n + BN - 1) / BN;
     a.part_key = part_key;
     a.part_idx = part_idx;
+    a.qtau = qtau;
     a.status = status;
     {
         const char *e = getenv("ANN_CUDA_TC_DEBUG");
         a.debug = e ? atoi(e) : 0;
     }
-    if (k <= kQueueDepth) return launch_variant<1, true>(plan, maps, a, stream);
-    if (k <= 32) return launch_variant<1, false>(plan, maps, a, stream);
-    if (k <= 128) return launch_variant<4, false>(plan, maps, a, stream);
-    if (k <= 512) return launch_variant<16, false>(plan, maps, a, stream);
-    return launch_variant<64, false>(plan, maps, a, stream);
+    a.stats = nullptr;
+    static unsigned long long *stats_dev = nullptr;
+    if (getenv("ANN_CUDA_TC_STATS")) {  // measurement only: synchronises and prints
+        if (!stats_dev) ANN_CUDA_TRY(cudaMalloc(&stats_dev, 8 * sizeof(unsigned long long)));
+        ANN_CUDA_TRY(cudaMemsetAsync(stats_dev, 0, 8 * sizeof(unsigned long long), stream));
+        a.stats = stats_dev;
+    }
+    int rc;
+    if (k <= kQueueDepth) rc = launch_variant<1, kSelSmem>(plan, maps, a, stream);
+    else if (k <= kAppendMaxK) rc = launch_variant<1, kSelAppend>(plan, maps, a, stream);
+    else if (k <= 512) rc = launch_variant<16, kSelReplace>(plan, maps, a, stream);
+    else rc = launch_variant<64, kSelReplace>(plan, maps, a, stream);
+    if (rc == 0 && a.stats) {
+        unsigned long long h[8];
+        ANN_CUDA_TRY(cudaStreamSynchronize(stream));
+        ANN_CUDA_TRY(cudaMemcpy(h, a.stats, sizeof h, cudaMemcpyDeviceToHost));
+        fprintf(stderr,
+                "[flat_tc stats] grid %d k %d tiles(x4 warps) %llu | compact rows %llu cycles %llu | appends %llu | "
+                "epilogue: wait %llu work %llu cycles | mma wait: tmem %llu smem %llu cycles\n",
+                plan.grid, k, h[kStatTiles], h[kStatCompactRows], h[kStatCompactCycles], h[kStatAppends],
+                h[kStatEpiWaitCycles], h[kStatEpiTileCycles], h[kStatMmaWaitTmem], h[kStatMmaWaitSmem]);
+    }
+    return rc;
 }
 
 }  // namespace anncuda

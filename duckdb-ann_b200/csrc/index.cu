@@ -99,7 +99,7 @@ struct Workspace {
     cudaStream_t own_stream = nullptr;
     cudaStream_t bound = nullptr;  // stream whose work may still use these buffers
     GrowBuf x, qhi, qlo, qn, part_key, part_idx, sel_key, sel_idx, status, out_d, out_i;
-    GrowBuf item_q, item_rb, item_re, item_slot, scratch, probes_key, probes;
+    GrowBuf item_q, item_rb, item_re, item_slot, scratch, probes_key, probes, qtau, sched;
     int *status_host = nullptr;  // pinned
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;  // bracket the flat kernel when timing is on
     bool timed = false;
@@ -107,7 +107,7 @@ struct Workspace {
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
         for (GrowBuf *b : {&x, &qhi, &qlo, &qn, &part_key, &part_idx, &sel_key, &sel_idx, &status, &out_d, &out_i,
-                           &item_q, &item_rb, &item_re, &item_slot, &scratch, &probes_key, &probes})
+                           &item_q, &item_rb, &item_re, &item_slot, &scratch, &probes_key, &probes, &qtau, &sched})
             b->release();
         if (status_host) cudaFreeHost(status_host);
         if (own_stream) cudaStreamDestroy(own_stream);
@@ -234,8 +234,16 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         if (launch_split_rows(x_dev, nq, d, dp, ws.qhi.as<float>(), ws.qlo.as<float>(), ws.qn.as<float>(), stream))
             return -1;
         const FlatPlan plan = make_flat_plan(nq, st.n, k, sm_count(ix.device));
-        if (ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4)) return -1;
+        const size_t qtau_bytes = (size_t)plan.nq_tiles * 128 * 4, sched_bytes = (size_t)plan.nq_tiles * 2 * 4;
+        if (ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4) ||
+            ws.qtau.ensure(qtau_bytes) || ws.sched.ensure(sched_bytes))
+            return -1;
         ANN_CUDA_TRY(cudaMemsetAsync(ws.status.ptr, 0, 4, stream));
+        ANN_CUDA_TRY(cudaMemsetAsync(ws.qtau.ptr, 0xFF, qtau_bytes, stream));  // "no threshold yet"
+        ANN_CUDA_TRY(cudaMemsetAsync(ws.sched.ptr, 0, sched_bytes, stream));
+        // every list empty: index -1 in the k slots the merge reads of each row
+        ANN_CUDA_TRY(cudaMemset2DAsync(ws.part_idx.ptr, (size_t)plan.list_stride * 4, 0xFF, (size_t)k * 4,
+                                       plan.part_entries / plan.list_stride, stream));
         const bool timing = g_time_kernels.load(std::memory_order_relaxed) != 0;
         if (timing) {
             if (!ws.ev0) {
@@ -245,7 +253,8 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
             ANN_CUDA_TRY(cudaEventRecord(ws.ev0, stream));
         }
         if (launch_flat_tc(plan, st.hi, st.lo, st.norms, st.n, ws.qhi.as<float>(), ws.qlo.as<float>(), nq, dp, k,
-                           ix.metric, ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.status.as<int>(),
+                           ix.metric, ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.qtau.as<uint32_t>(),
+                           ws.sched.as<int>(), ws.status.as<int>(),
                            ix.device, stream))
             return -1;
         if (timing) {
@@ -254,12 +263,12 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
             ix.last_timed_ws = &ws;
         }
         ANN_CUDA_TRY(cudaMemcpyAsync(ws.status_host, ws.status.ptr, 4, cudaMemcpyDeviceToHost, stream));
-        return launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 0, plan.nq_tiles, nullptr,
-                                  plan.chunks, nq, k, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device,
-                                  stream);
+        return launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 0,
+                                  ws.sched.as<int>() + plan.nq_tiles, nullptr, plan.lists_per_qt, nq, k,
+                                  plan.list_stride, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream);
     }
     // exact-fp32 cross-check kernel: items = (query, database chunk)
-    int chunks = (int)std::max<int64_t>(1, std::min<int64_t>({(int64_t)8192 / k, (st.n + 255) / 256,
+    int chunks = (int)std::max<int64_t>(1, std::min<int64_t>({(int64_t)kMergeCandidates / k, (st.n + 255) / 256,
                                                              (int64_t)sm_count(ix.device) * 32 / std::max<int64_t>(nq, 1) + 1}));
     const int64_t per = (st.n + chunks - 1) / chunks;
     chunks = (int)((st.n + per - 1) / per);
@@ -282,9 +291,9 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
     ANN_CUDA_TRY(cudaStreamSynchronize(stream));  // the host vectors go out of scope
     if (launch_scan_items(st.hi, st.lo, dp, d, x_dev, d, ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(),
                           ws.item_re.as<int64_t>(), n_items, k, ix.metric, ws.part_key.as<float>(),
-                          ws.part_idx.as<int32_t>(), ix.device, stream))
+                          ws.part_idx.as<int32_t>(), nullptr, ix.device, stream))
         return -1;
-    return launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, 0, nullptr, chunks, nq, k,
+    return launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, nullptr, nullptr, chunks, nq, k, k,
                               ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream);
 }
 
@@ -430,8 +439,9 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
     }
     const int nprobe = (int)std::min<int64_t>(std::max<int64_t>(ix.nprobe, 1), ix.nlist);
     const int k_sel = (int)std::min<int64_t>(k, kMaxK);
-    if ((int64_t)nprobe * k_sel > 8192)
-        return set_error("nprobe * k = %lld exceeds the 8192 candidates the merge step holds", (long long)nprobe * k_sel);
+    if ((int64_t)nprobe * k_sel > kMergeCandidates)
+        return set_error("nprobe * k = %lld exceeds the %d candidates the merge step holds", (long long)nprobe * k_sel,
+                         kMergeCandidates);
     // coarse quantiser: nprobe nearest centroids under the index metric
     if (split_store_topk(ix, ix.store, ws, x_dev, nq, nprobe, stream)) return -1;
     const int64_t n_items = nq * nprobe;
@@ -445,13 +455,15 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
                                ws.item_rb.as<int64_t>(), ws.item_re.as<int64_t>(), ws.item_slot.as<int32_t>(),
                                ws.scratch.as<int>(), stream))
         return -1;
+    if (ws.qtau.ensure((size_t)nq * 4)) return -1;
+    ANN_CUDA_TRY(cudaMemsetAsync(ws.qtau.ptr, 0xFF, (size_t)nq * 4, stream));
     if (launch_scan_items(ix.vecs, nullptr, ix.dp, ix.d, x_dev, ix.d, ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(),
                           ws.item_re.as<int64_t>(), n_items, k_sel, ix.metric, ws.part_key.as<float>(),
-                          ws.part_idx.as<int32_t>(), ix.device, stream))
+                          ws.part_idx.as<int32_t>(), ws.qtau.as<uint32_t>(), ix.device, stream))
         return -1;
     if (ws.sel_key.ensure((size_t)nq * k_sel * 4) || ws.sel_idx.ensure((size_t)nq * k_sel * 4)) return -1;
-    if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, 0, ws.item_slot.as<int32_t>(), nprobe,
-                           nq, k_sel, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream))
+    if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, nullptr, ws.item_slot.as<int32_t>(), nprobe,
+                           nq, k_sel, k_sel, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream))
         return -1;
     return launch_finalize(ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), nq, k_sel, (int)k, ix.metric, ix.ids,
                            label_offset, d_dev, i_dev, stream);

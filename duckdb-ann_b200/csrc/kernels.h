@@ -30,35 +30,44 @@ int launch_pad_rows(const float *x, int64_t n, int d, int dp, float *out, float 
 int launch_join_rows(const float *hi, const float *lo, int64_t n, int d, int dp, float *out, cudaStream_t stream);
 
 // ---- flat_tc.cu --------------------------------------------------------------------------
+constexpr int kAppendMaxK = 128;         // largest k the append-and-compact selection handles
+constexpr int kMergeCandidates = 16384;  // most (list, slot) candidates per query the merge kernel sorts
+
 struct FlatPlan {
-    int nq_tiles = 0;      // ceil(nq / 128)
-    int chunks = 0;        // database chunks (partial lists per query)
-    int tiles_per_chunk = 0;
-    int units = 0;         // nq_tiles * chunks
+    int nq_tiles = 0;         // ceil(nq / 128)
+    int tiles_per_chunk = 0;  // 256-row tiles handed out at a time
+    int nchunks = 0;          // chunks per query tile
+    int lists_per_qt = 0;     // k-lists a query tile can end up with (one per CTA that worked on it)
     int grid = 0;
-    size_t part_entries = 0;  // units * 128 * k
+    int list_stride = 0;      // slots per row in the list memory (k, or the append buffer size)
+    size_t part_entries = 0;  // nq_tiles * lists_per_qt * 128 * list_stride
 };
 // Chooses the decomposition for nq queries against n rows on a device with `sms` SMs.
 FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms);
 
 // Fused split-TF32 GEMM + k-selection on the tensor cores.  Inputs are hi/lo row
 // stores of the database (n x dp) and the queries (nq x dp), plus row norms for L2.
-// Writes, per work unit, 128 unsorted lists of k (key, local row) pairs.
+// Writes 128 unsorted lists of k (key, local row) pairs per list slot
+// (slot = query tile * lists_per_qt + j, j < sched[nq_tiles + query tile]).
+// On entry: part_idx all -1 (bytes 0xFF); qtau (nq_tiles * 128 words, the per-query shared
+// threshold) all bytes 0xFF; sched (2 * nq_tiles ints: chunks taken, lists started) all zero.
 // status: device int, set non-zero if a bounded wait inside the kernel ran out.
 int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
-                   int32_t *part_idx, int *status, int device, cudaStream_t stream);
+                   int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream);
 
 // ---- scan.cu -----------------------------------------------------------------------------
 // Exact-fp32 scan of row ranges with warp k-selection: one warp per (query, range)
 // item.  Item i scans rows [range_begin[i], range_end[i]) for query item_query[i] and
 // writes an unsorted list of k (key, row) at part_*[i * k ...].  Rows are read from
 // `x` (n x dp); when `xlo` is non-null the row is x + xlo (a split store).
-// key = squared L2 distance, or negated dot.
+// key = squared L2 distance, or negated dot.  qtau (optional, one word per query, all
+// bytes 0xFF on entry): items of the same query share their k-th best key through it,
+// so later items skip rows that cannot reach the query's final top-k.
 int launch_scan_items(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
                       const int32_t *item_query, const int64_t *range_begin, const int64_t *range_end,
-                      int64_t n_items, int k, int metric, float *part_key, int32_t *part_idx, int device,
-                      cudaStream_t stream);
+                      int64_t n_items, int k, int metric, float *part_key, int32_t *part_idx, uint32_t *qtau,
+                      int device, cudaStream_t stream);
 
 // Builds the (query, list) items of an IVF search from the coarse result:
 // probes (nq x nprobe) int32 list numbers (-1 = none); items are grouped by list so
@@ -72,11 +81,13 @@ int launch_build_ivf_items(const int32_t *probes, int64_t nq, int nprobe, int64_
 // ---- merge.cu ----------------------------------------------------------------------------
 // Per query: the k best of `nparts` unsorted lists, sorted best first.
 // The list of (query q, part p) starts at part_*[(p * part_stride_p + q_major(q)) * k].
-// Layout kinds: 0 = flat units (unit = p * nq_tiles + q / 128, row q % 128),
+// Layout kinds: 0 = flat list slots (slot = (q / 128) * nparts + p, row q % 128; only the first
+//                   min(nparts, lists_started[q / 128]) slots of a query tile are read),
 //               1 = item slots (slot_of[q * nparts + p], or q * nparts + p if null).
-int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layout, int nq_tiles,
-                       const int32_t *slot_of, int nparts, int64_t nq, int k, float *out_key, int32_t *out_idx,
-                       int device, cudaStream_t stream);
+// A list holds its k entries in the first k of `list_stride` slots.
+int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layout, const int *lists_started,
+                       const int32_t *slot_of, int nparts, int64_t nq, int k, int list_stride, float *out_key,
+                       int32_t *out_idx, int device, cudaStream_t stream);
 
 // Flat: recomputes the distance of every selected (query, row) pair in exact fp32
 // from the split store, sorts the k results best first and writes the user-facing

@@ -15,7 +15,7 @@ namespace anncuda {
 namespace {
 
 constexpr int kMergeThreads = 256;
-constexpr int kMaxCandidates = 8192;
+constexpr int kMaxCandidates = kMergeCandidates;
 
 __host__ __device__ inline int next_pow2(int v) {
     int p = 1;
@@ -48,13 +48,22 @@ __device__ void bitonic_sort(float *keys, int32_t *vals, int P) {
 
 __global__ void __launch_bounds__(kMergeThreads)
 merge_parts_kernel(const float *__restrict__ part_key, const int32_t *__restrict__ part_idx, int layout,
-                   int nq_tiles, const int32_t *__restrict__ slot_of, int nparts, int64_t nq, int k, int P,
+                   const int *__restrict__ lists_started, const int32_t *__restrict__ slot_of, int nparts, int64_t nq,
+                   int k, int list_stride, int P_max,
                    float *__restrict__ out_key, int32_t *__restrict__ out_idx) {
     extern __shared__ float smem_f[];
     float *keys = smem_f;
-    int32_t *vals = reinterpret_cast<int32_t *>(smem_f + P);
+    int32_t *vals = reinterpret_cast<int32_t *>(smem_f + P_max);
     const int64_t q = blockIdx.x;
-    const int total = nparts * k;
+    int nlists = nparts;
+    if (layout == 0) {
+        const int started = lists_started[q >> 7];
+        nlists = started < nparts ? started : nparts;
+    }
+    const int total = nlists * k;
+    int P = 2;  // sort only as many slots as this query has candidates
+    while (P < total) P <<= 1;
+    if (P > P_max) P = P_max;
     for (int t = threadIdx.x; t < P; t += blockDim.x) {
         float key = kInf;
         int32_t val = 0x7fffffff;
@@ -62,12 +71,12 @@ merge_parts_kernel(const float *__restrict__ part_key, const int32_t *__restrict
             const int p = t / k, j = t - p * k;
             int64_t list;
             if (layout == 0)
-                list = ((int64_t)p * nq_tiles + (q >> 7)) * 128 + (q & 127);
+                list = ((q >> 7) * (int64_t)nparts + p) * 128 + (q & 127);
             else
                 list = slot_of ? (int64_t)slot_of[q * nparts + p] : q * nparts + p;
-            const int32_t idx = part_idx[list * k + j];
+            const int32_t idx = part_idx[list * list_stride + j];
             if (idx >= 0) {
-                key = part_key[list * k + j];
+                key = part_key[list * list_stride + j];
                 val = idx;
             }
         }
@@ -76,7 +85,7 @@ merge_parts_kernel(const float *__restrict__ part_key, const int32_t *__restrict
     }
     bitonic_sort(keys, vals, P);
     for (int j = threadIdx.x; j < k; j += blockDim.x) {
-        const bool ok = vals[j] != 0x7fffffff;
+        const bool ok = j < P && vals[j] != 0x7fffffff;
         out_key[q * k + j] = ok ? keys[j] : kInf;
         out_idx[q * k + j] = ok ? vals[j] : -1;
     }
@@ -215,9 +224,9 @@ int opt_in_smem(K kernel, size_t smem) {
 
 }  // namespace
 
-int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layout, int nq_tiles,
-                       const int32_t *slot_of, int nparts, int64_t nq, int k, float *out_key, int32_t *out_idx,
-                       int device, cudaStream_t stream) {
+int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layout, const int *lists_started,
+                       const int32_t *slot_of, int nparts, int64_t nq, int k, int list_stride, float *out_key,
+                       int32_t *out_idx, int device, cudaStream_t stream) {
     (void)device;
     if (nq <= 0) return 0;
     const int total = nparts * k;
@@ -225,8 +234,8 @@ int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layou
     const int P = next_pow2(total < 2 ? 2 : total);
     const size_t smem = (size_t)P * 8;
     if (opt_in_smem(merge_parts_kernel, smem)) return -1;
-    merge_parts_kernel<<<(unsigned)nq, kMergeThreads, smem, stream>>>(part_key, part_idx, layout, nq_tiles, slot_of,
-                                                                      nparts, nq, k, P, out_key, out_idx);
+    merge_parts_kernel<<<(unsigned)nq, kMergeThreads, smem, stream>>>(part_key, part_idx, layout, lists_started, slot_of,
+                                                                      nparts, nq, k, list_stride, P, out_key, out_idx);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

@@ -35,7 +35,8 @@ __global__ void __launch_bounds__(kWarps * 32)
 scan_items_kernel(const float *__restrict__ x, const float *__restrict__ xlo, int dp, int d,
                   const float *__restrict__ queries, int q_stride, const int32_t *__restrict__ item_query,
                   const int64_t *__restrict__ range_begin, const int64_t *__restrict__ range_end, int64_t n_items,
-                  int k, int metric, float *__restrict__ part_key, int32_t *__restrict__ part_idx) {
+                  int k, int metric, float *__restrict__ part_key, int32_t *__restrict__ part_idx,
+                  uint32_t *__restrict__ qtau) {
     extern __shared__ float4 smem_q4[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float *myq = reinterpret_cast<float *>(smem_q4) + (size_t)warp * dp;
@@ -53,12 +54,20 @@ scan_items_kernel(const float *__restrict__ x, const float *__restrict__ xlo, in
         float m;
         int pos;
         list.argmax(lane, m, pos);
+        // thr: a key must be below it to matter.  It is the smaller of this list's current
+        // maximum and, when qtau is given, the best k-th key any other item of the same
+        // query has published (items of one query scan different lists at different times).
+        float thr = m, published = kInf;
         if (q >= 0 && begin < end) {
             __syncwarp();
             for (int c = lane; c < dp; c += 32) myq[c] = c < d ? queries[(int64_t)q * q_stride + c] : 0.f;
             __syncwarp();
             for (int64_t row0 = begin; row0 < end; row0 += kRows) {
                 const int nrows = (int)((end - row0) < kRows ? (end - row0) : kRows);
+                if (qtau) {
+                    const uint32_t tg = __ldcg(qtau + q);
+                    if (tg < float_to_ordered(thr)) thr = ordered_to_float(tg);
+                }
                 float acc[kRows];
 #pragma unroll
                 for (int r = 0; r < kRows; r++) acc[r] = 0.f;
@@ -100,12 +109,17 @@ scan_items_kernel(const float *__restrict__ x, const float *__restrict__ xlo, in
                 for (int r = 0; r < kRows; r++) {
                     if (r < nrows) {
                         const float key = l2 ? acc[r] : -acc[r];
-                        if (key < m) {  // warp-uniform: every lane holds the same sum
+                        if (key < thr) {  // warp-uniform: every lane holds the same sum
                             if (lane == (pos & 31)) li[pos] = (int32_t)(row0 + r);
                             list.set(pos, key, lane);
                             list.argmax(lane, m, pos);
+                            thr = fminf(thr, m);
                         }
                     }
+                }
+                if (qtau && m < published) {  // the list holds k rows: its maximum bounds the query's k-th best
+                    published = m;
+                    if (lane == 0) atomicMin(qtau + q, float_to_ordered(m));
                 }
             }
         }
@@ -176,7 +190,7 @@ __global__ void ivf_place_kernel(const int32_t *__restrict__ probes, int64_t n, 
 template <int KR>
 int launch_scan_kr(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
                    const int32_t *item_query, const int64_t *rb, const int64_t *re, int64_t n_items, int k,
-                   int metric, float *part_key, int32_t *part_idx, int device, cudaStream_t stream) {
+                   int metric, float *part_key, int32_t *part_idx, uint32_t *qtau, int device, cudaStream_t stream) {
     const size_t smem = (size_t)kWarps * dp * sizeof(float);
     if (smem > 48 * 1024) {
         ANN_CUDA_TRY(cudaFuncSetAttribute(scan_items_kernel<KR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -186,7 +200,7 @@ int launch_scan_kr(const float *x, const float *xlo, int dp, int d, const float 
     const int64_t cap = (int64_t)sm_count(device) * 16;
     if (blocks > cap) blocks = cap;
     scan_items_kernel<KR><<<(unsigned)blocks, kWarps * 32, smem, stream>>>(
-        x, xlo, dp, d, queries, q_stride, item_query, rb, re, n_items, k, metric, part_key, part_idx);
+        x, xlo, dp, d, queries, q_stride, item_query, rb, re, n_items, k, metric, part_key, part_idx, qtau);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -196,22 +210,22 @@ int launch_scan_kr(const float *x, const float *xlo, int dp, int d, const float 
 
 int launch_scan_items(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
                       const int32_t *item_query, const int64_t *range_begin, const int64_t *range_end,
-                      int64_t n_items, int k, int metric, float *part_key, int32_t *part_idx, int device,
-                      cudaStream_t stream) {
+                      int64_t n_items, int k, int metric, float *part_key, int32_t *part_idx, uint32_t *qtau,
+                      int device, cudaStream_t stream) {
     if (n_items <= 0) return 0;
     if (k <= 0 || k > kMaxK) return set_error("k must be in [1, %d]", kMaxK);
     if ((size_t)kWarps * dp * sizeof(float) > 200 * 1024) return set_error("dimension %d too large for the scan kernel", d);
     if (k <= 32)
         return launch_scan_kr<1>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k,
-                                 metric, part_key, part_idx, device, stream);
+                                 metric, part_key, part_idx, qtau, device, stream);
     if (k <= 128)
         return launch_scan_kr<4>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k,
-                                 metric, part_key, part_idx, device, stream);
+                                 metric, part_key, part_idx, qtau, device, stream);
     if (k <= 512)
         return launch_scan_kr<16>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k,
-                                  metric, part_key, part_idx, device, stream);
+                                  metric, part_key, part_idx, qtau, device, stream);
     return launch_scan_kr<64>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k, metric,
-                              part_key, part_idx, device, stream);
+                              part_key, part_idx, qtau, device, stream);
 }
 
 int launch_build_ivf_items(const int32_t *probes, int64_t nq, int nprobe, int64_t nlist, const int64_t *list_off,
