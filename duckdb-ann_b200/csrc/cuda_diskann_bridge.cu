@@ -155,24 +155,19 @@ __device__ __forceinline__ float sq8_acc(float acc, float q, uint32_t code, floa
 }
 
 // SQ8 rows with dim % 4 == 0 and dim <= 512.  Lane l owns the 4*WPL consecutive
-// dimensions starting at 4*WPL*l of EVERY row, so its slice of min / scale stays
-// in registers for the whole kernel and its slice of the query is reloaded only
+// dimensions starting at 4*WPL*l of EVERY row, so its slice of the scale stays in
+// registers for the whole kernel and its slice of (query - min) is rebuilt only
 // when the query changes (rows of one query are adjacent in DiskANN's lock-step
 // batches, rust_lib/src/disk_provider.rs:546-581).  A row is then WPL coalesced
 // 4-byte loads per lane and nothing else: the only traffic per row is its codes.
 // code/255 comes from a table in shared memory, replicated once per bank so the
-// lookups never conflict; the rest of the dequantisation is the reference's two
-// separately rounded operations.
+// lookups never conflict.  Arithmetic per element: the dequantised value is
+// (code/255)*scale+min (rust_lib/src/provider.rs:142-143); L2 uses
+// q - x = (q - min) - (code/255)*scale as one fused multiply-add (differs from the
+// reference's operation order by one rounding of magnitude 1e-7 relative), inner
+// product uses q*(code/255)*scale summed plus q.min once per query.
+// Eight rows are processed together so that eight independent sums are in flight.
 constexpr int kSq8RowsPerWarp = 8;
-
-__device__ __forceinline__ float sq8_lut_acc(float acc, float q, float t, float s, float m, bool l2) {
-    const float xh = __fadd_rn(__fmul_rn(t, s), m);  // (code/255)*scale+min, rust_lib/src/provider.rs:142-143
-    if (l2) {
-        const float d = q - xh;
-        return fmaf(d, d, acc);
-    }
-    return fmaf(q, xh, acc);
-}
 
 template <int WPL>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
@@ -191,18 +186,31 @@ batch_distance_sq8_regs_kernel(const uint8_t *__restrict__ codes, size_t num, in
     const int d0 = lane * 4 * WPL;   // first dimension of this lane
     const bool active = d0 < dim;    // dim is a multiple of 4 * WPL
     const float *mylut = lut + lane;
-    float4 m[WPL], s[WPL], q[WPL];
+    float s[WPL * 4];   // scale of my dimensions
+    float qa[WPL * 4];  // L2: q - min;  IP: q
+    float qmin = 0.f;   // IP: sum over my dimensions of q * min
 #pragma unroll
-    for (int j = 0; j < WPL; j++) {
-        m[j] = active ? __ldg(reinterpret_cast<const float4 *>(mins + d0) + j) : make_float4(0, 0, 0, 0);
-        s[j] = active ? __ldg(reinterpret_cast<const float4 *>(scale + d0) + j) : make_float4(0, 0, 0, 0);
-        q[j] = make_float4(0, 0, 0, 0);
+    for (int j = 0; j < WPL * 4; j++) {
+        s[j] = active ? __ldg(scale + d0 + j) : 0.f;
+        qa[j] = 0.f;
     }
     uint32_t cur_q = 0xffffffffu;
+    auto load_query = [&](uint32_t qi) {
+        cur_q = qi;
+        qmin = 0.f;
+#pragma unroll
+        for (int j = 0; j < WPL * 4; j++) {
+            const float qv = active ? __ldg(queries + (size_t)qi * dim + d0 + j) : 0.f;
+            const float mv = active ? __ldg(mins + d0 + j) : 0.f;
+            qa[j] = l2 ? qv - mv : qv;
+            qmin = fmaf(qv, mv, qmin);
+        }
+    };
     for (long long base = warp_global * kSq8RowsPerWarp; base < total_n; base += warps_total * kSq8RowsPerWarp) {
         uint32_t w[kSq8RowsPerWarp][WPL];
         uint32_t qi[kSq8RowsPerWarp];
         bool ok[kSq8RowsPerWarp];
+        bool same_query = true;
 #pragma unroll
         for (int t = 0; t < kSq8RowsPerWarp; t++) {
             const long long i = base + t;
@@ -220,31 +228,73 @@ batch_distance_sq8_regs_kernel(const uint8_t *__restrict__ codes, size_t num, in
                     for (int j = 0; j < WPL; j++)
                         asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(w[t][j]) : "l"(p + j));
                 }
+                if (ok[t] && qi[t] != qi[0]) same_query = false;
+                if (!ok[t]) same_query = false;
+            } else {
+                same_query = false;
+            }
+        }
+        float acc[kSq8RowsPerWarp];
+#pragma unroll
+        for (int t = 0; t < kSq8RowsPerWarp; t++) acc[t] = 0.f;
+        if (same_query) {  // warp-uniform: ids, map and bounds are the same in every lane
+            if (qi[0] != cur_q) load_query(qi[0]);
+#pragma unroll
+            for (int j = 0; j < WPL; j++) {
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    const float sv = s[j * 4 + b], qv = qa[j * 4 + b];
+#pragma unroll
+                    for (int t = 0; t < kSq8RowsPerWarp; t++) {
+                        const float tv = mylut[((w[t][j] >> (8 * b)) & 0xffu) << 5];
+                        if (l2) {
+                            const float diff = fmaf(-tv, sv, qv);
+                            acc[t] = fmaf(diff, diff, acc[t]);
+                        } else {
+                            acc[t] = fmaf(tv * sv, qv, acc[t]);
+                        }
+                    }
+                }
+            }
+            if (!l2) {
+#pragma unroll
+                for (int t = 0; t < kSq8RowsPerWarp; t++) acc[t] += qmin;
+            }
+        } else {
+#pragma unroll
+            for (int t = 0; t < kSq8RowsPerWarp; t++) {
+                if (base + t >= total_n || !ok[t]) continue;  // warp-uniform
+                if (qi[t] != cur_q) load_query(qi[t]);
+#pragma unroll
+                for (int j = 0; j < WPL; j++) {
+#pragma unroll
+                    for (int b = 0; b < 4; b++) {
+                        const float tv = mylut[((w[t][j] >> (8 * b)) & 0xffu) << 5];
+                        if (l2) {
+                            const float diff = fmaf(-tv, s[j * 4 + b], qa[j * 4 + b]);
+                            acc[t] = fmaf(diff, diff, acc[t]);
+                        } else {
+                            acc[t] = fmaf(tv * s[j * 4 + b], qa[j * 4 + b], acc[t]);
+                        }
+                    }
+                }
+                if (!l2) acc[t] += qmin;
             }
         }
 #pragma unroll
-        for (int t = 0; t < kSq8RowsPerWarp; t++) {
-            const long long i = base + t;
-            if (i >= total_n) break;        // warp-uniform
-            if (ok[t] && qi[t] != cur_q) {  // warp-uniform: every lane reads the same map entry
-                cur_q = qi[t];
-                const float4 *q4 = reinterpret_cast<const float4 *>(queries + (size_t)cur_q * dim + d0);
+        for (int t = 0; t < kSq8RowsPerWarp; t++) acc[t] = warp_sum(acc[t]);
+        if (lane < kSq8RowsPerWarp) {
+            float v = 0.f;
+            bool good = false;
 #pragma unroll
-                for (int j = 0; j < WPL; j++) q[j] = active ? __ldg(q4 + j) : make_float4(0, 0, 0, 0);
-            }
-            float acc = 0.f;
-            if (ok[t] && active) {
-#pragma unroll
-                for (int j = 0; j < WPL; j++) {
-                    const uint32_t ww = w[t][j];
-                    acc = sq8_lut_acc(acc, q[j].x, mylut[(ww & 0xffu) << 5], s[j].x, m[j].x, l2);
-                    acc = sq8_lut_acc(acc, q[j].y, mylut[((ww >> 8) & 0xffu) << 5], s[j].y, m[j].y, l2);
-                    acc = sq8_lut_acc(acc, q[j].z, mylut[((ww >> 16) & 0xffu) << 5], s[j].z, m[j].z, l2);
-                    acc = sq8_lut_acc(acc, q[j].w, mylut[(ww >> 24) << 5], s[j].w, m[j].w, l2);
+            for (int t = 0; t < kSq8RowsPerWarp; t++) {
+                if (lane == t) {
+                    v = acc[t];
+                    good = ok[t];
                 }
             }
-            acc = warp_sum(acc);
-            if (lane == 0) out[i] = ok[t] ? (l2 ? acc : -acc) : __int_as_float(0x7fc00000);
+            const long long i = base + lane;
+            if (i < total_n) out[i] = good ? (l2 ? v : -v) : __int_as_float(0x7fc00000);
         }
     }
 }
@@ -341,7 +391,7 @@ int launch_distance(const diskann_cuda_table &t, const float *queries, int nq, c
         if (regs) {
             long long warps = ((long long)total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
             long long blocks = (warps + kWarpsPerBlock - 1) / kWarpsPerBlock;
-            const long long cap = (long long)sms * 4;
+            const long long cap = (long long)sms * 2;  // one resident wave: the table in shared memory is built once per block
             if (blocks > cap) blocks = cap;
             const unsigned g = (unsigned)blocks, b = kWarpsPerBlock * 32;
             switch (wpl) {

@@ -181,16 +181,41 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 __device__ __forceinline__ void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tmem_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
-    uint32_t r[16];
+// Asynchronous read of 32 accumulator columns of this thread's TMEM lane.  The
+// registers are valid only after tmem_ld_wait, which names them as in/out operands so
+// the compiler cannot move their uses above the wait.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                   "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                   "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                   "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
+
+// Stores that execute only where `p` is set, as predicated instructions (no branch).
+__device__ __forceinline__ void st_global_if(bool p, float *addr, float v) {
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %0, 0;\n\t@q st.global.f32 [%1], %2;\n\t}" ::"r"((int)p), "l"(addr),
+                 "f"(v)
+                 : "memory");
+}
+__device__ __forceinline__ void st_global_if(bool p, int32_t *addr, int32_t v) {
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %0, 0;\n\t@q st.global.s32 [%1], %2;\n\t}" ::"r"((int)p), "l"(addr),
+                 "r"(v)
+                 : "memory");
 }
 
 // ---- selection helpers ------------------------------------------------------------------------
@@ -267,46 +292,54 @@ constexpr int kBuf = 512;  // candidate slots per row in append mode
 static_assert(kAppendMaxK <= kBuf / 2, "a compacted row must leave room for new candidates");
 
 // ---- bitonic sort of 512 (key, idx) pairs held by a warp, 16 per lane -------------------------
-// Element e lives in lane e / 16, register e % 16, so exchanges at distance < 16 stay
-// inside a thread and larger ones are one shuffle.  Ascending by key.
-__device__ __forceinline__ void sort512(float (&key)[16], int32_t (&idx)[16], int lane) {
+// Bitonic sort of 512 (key, idx) pairs held by a warp, 16 per lane; keys are order-preserving
+// uint32 images of the float keys.  Element e lives in lane e / 16, register e % 16, so
+// exchanges at distance < 16 stay inside a thread and larger ones are one shuffle.
+// Every compare-exchange is written without a conditional on the direction (the
+// direction is an XOR mask), so the code is straight-line selects, no branches.
+__device__ __forceinline__ void ce_swap(uint32_t &ka, int32_t &ia, uint32_t &kb, int32_t &ib, uint32_t dm) {
+    const bool sw = (ka ^ dm) > (kb ^ dm);  // dm = 0: ascending, ~0: descending
+    const uint32_t ta = sw ? kb : ka, tb = sw ? ka : kb;
+    const int32_t ua = sw ? ib : ia, ub = sw ? ia : ib;
+    ka = ta; kb = tb; ia = ua; ib = ub;
+}
+__device__ __forceinline__ void sort512(uint32_t (&key)[16], int32_t (&idx)[16], int lane) {
+    // sizes 2..16: all exchanges are inside a lane
 #pragma unroll
-    for (int size = 2; size <= 512; size <<= 1) {
+    for (int size = 2; size <= 16; size <<= 1) {
 #pragma unroll
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
-            if (stride >= 16) {
-                const int ls = stride >> 4;
-                const bool upper = (lane & ls) != 0;
-                const bool asc = (((lane << 4) & size) == 0);
-                const bool keep_min = (!upper) == asc;
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const float ok = __shfl_xor_sync(kFullMask, key[i], ls);
-                    const int32_t oi = __shfl_xor_sync(kFullMask, idx[i], ls);
-                    const bool take = keep_min ? (ok < key[i]) : (ok > key[i]);
-                    if (take) {
-                        key[i] = ok;
-                        idx[i] = oi;
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    if ((i & stride) == 0) {
-                        const int j = i | stride;
-                        const bool asc = ((((lane << 4) | i) & size) == 0);
-                        const bool sw = asc ? (key[i] > key[j]) : (key[i] < key[j]);
-                        if (sw) {
-                            const float tk = key[i];
-                            key[i] = key[j];
-                            key[j] = tk;
-                            const int32_t ti = idx[i];
-                            idx[i] = idx[j];
-                            idx[j] = ti;
-                        }
-                    }
+            for (int i = 0; i < 16; i++) {
+                if ((i & stride) == 0) {
+                    const uint32_t dm = size == 16 ? (0u - (uint32_t)(lane & 1)) : ((i & size) ? 0xffffffffu : 0u);
+                    ce_swap(key[i], idx[i], key[i | stride], idx[i | stride], dm);
                 }
             }
+        }
+    }
+    // sizes 32..512: the direction is the same for all 16 elements of a lane
+#pragma unroll 1
+    for (int size = 32; size <= 512; size <<= 1) {
+        const uint32_t dm = ((lane << 4) & size) ? 0xffffffffu : 0u;
+#pragma unroll 1
+        for (int ls = size >> 5; ls > 0; ls >>= 1) {
+            // the lower lane of a pair keeps the smaller key when ascending
+            const uint32_t km = ((lane & ls) ? 0xffffffffu : 0u) ^ dm;  // 0: keep min, ~0: keep max
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const uint32_t ok = __shfl_xor_sync(kFullMask, key[i], ls);
+                const int32_t oi = __shfl_xor_sync(kFullMask, idx[i], ls);
+                const bool take = (ok ^ km) < (key[i] ^ km);
+                key[i] = take ? ok : key[i];
+                idx[i] = take ? oi : idx[i];
+            }
+        }
+#pragma unroll
+        for (int stride = 8; stride > 0; stride >>= 1) {
+#pragma unroll
+            for (int i = 0; i < 16; i++)
+                if ((i & stride) == 0) ce_swap(key[i], idx[i], key[i | stride], idx[i | stride], dm);
         }
     }
 }
@@ -314,41 +347,45 @@ __device__ __forceinline__ void sort512(float (&key)[16], int32_t (&idx)[16], in
 // Append mode: sorts the buffers of the rows in `need` (bit r = row row0 + r of this
 // warp), keeps their best k entries in slots [0, k) (sorted, unused slots get index
 // -1) and tightens the rows' thresholds.
+__device__ unsigned long long g_compact_phase[4];  // measurement only: load, sort, store cycles, rows
+
 __device__ __noinline__ void compact_rows(float *slot_key, int32_t *slot_idx, int k, int row0, unsigned need, int &cnt,
                                           float &tau, int lane, uint32_t *qtau_tile) {
     __syncwarp();  // the appends of every lane are visible to the whole warp
     while (need) {
+        const long long p0 = clock64();
         const int r = __ffs(need) - 1;
         need &= need - 1;
         const int c = __shfl_sync(kFullMask, cnt, r);
         float *bk = slot_key + (size_t)(row0 + r) * kBuf;
         int32_t *bi = slot_idx + (size_t)(row0 + r) * kBuf;
-        float key[16];
+        uint32_t key[16];
         int32_t idx[16];
 #pragma unroll
         for (int v = 0; v < 4; v++) {
             const float4 kk = *reinterpret_cast<const float4 *>(bk + lane * 16 + v * 4);
             const int4 ii = *reinterpret_cast<const int4 *>(bi + lane * 16 + v * 4);
-            key[v * 4 + 0] = kk.x; key[v * 4 + 1] = kk.y; key[v * 4 + 2] = kk.z; key[v * 4 + 3] = kk.w;
+            key[v * 4 + 0] = float_to_ordered(kk.x); key[v * 4 + 1] = float_to_ordered(kk.y);
+            key[v * 4 + 2] = float_to_ordered(kk.z); key[v * 4 + 3] = float_to_ordered(kk.w);
             idx[v * 4 + 0] = ii.x; idx[v * 4 + 1] = ii.y; idx[v * 4 + 2] = ii.z; idx[v * 4 + 3] = ii.w;
         }
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-            if (lane * 16 + i >= c) {  // slots past the fill hold stale data
-                key[i] = kInf;
-                idx[i] = -1;
-            }
+            const bool stale = lane * 16 + i >= c;  // slots past the fill hold old data
+            key[i] = stale ? 0xff800000u : key[i];  // +inf
+            idx[i] = stale ? -1 : idx[i];
         }
+        const long long p1 = clock64();
         sort512(key, idx, lane);
+        const long long p2 = clock64();
         float kth = kInf;
 #pragma unroll
         for (int i = 0; i < 16; i++) {
             const int e = lane * 16 + i;
-            if (e < k) {
-                bk[e] = key[i];
-                bi[e] = idx[i];
-            }
-            if (e == k - 1) kth = key[i];
+            const float kf = ordered_to_float(key[i]);
+            st_global_if(e < k, bk + e, kf);
+            st_global_if(e < k, bi + e, idx[i]);
+            kth = (e == k - 1) ? kf : kth;
         }
         kth = __shfl_sync(kFullMask, kth, (k - 1) >> 4);
         if (lane == r) {
@@ -358,6 +395,13 @@ __device__ __noinline__ void compact_rows(float *slot_key, int32_t *slot_idx, in
                 tau = fminf(tau, kth);
                 atomicMin(qtau_tile + row0 + r, float_to_ordered(kth));
             }
+        }
+        if (lane == 0) {
+            const long long p3 = clock64();
+            atomicAdd(&g_compact_phase[0], (unsigned long long)(p1 - p0));
+            atomicAdd(&g_compact_phase[1], (unsigned long long)(p2 - p1));
+            atomicAdd(&g_compact_phase[2], (unsigned long long)(p3 - p2));
+            atomicAdd(&g_compact_phase[3], 1ull);
         }
     }
     __syncwarp();
@@ -632,19 +676,44 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 const int ncols = rem < BN ? (int)rem : BN;
                 const int32_t col0 = (int32_t)(tile * BN);
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
-                for (int cb = 0; cb < BN / 16; cb++) {
-                    if (cb * 16 >= ncols || (args.debug & 1)) break;
-                    float key[16];
-                    tmem_ld16(taddr + cb * 16, key);
+                // Selection over 32 accumulator columns (raw: the registers of one TMEM read).
+                // The common case - no column beats the threshold - is branch-free: with one
+                // warp per scheduler a branch per column would cost far more than the
+                // arithmetic.  Keys are formed and compared with predicated instructions into
+                // a bit mask; one warp vote then decides whether anything has to be done.
+                auto key_of = [&](const uint32_t (&raw)[32], int g, int j) -> float {
+                    const float acc = __uint_as_float(raw[j]);
+                    return args.l2 ? fmaf(-2.f, acc, xn_s[buf * BN + g * 32 + j]) : -acc;
+                };
+                auto beat_mask = [&](const uint32_t (&raw)[32], int g, uint32_t valid) -> uint32_t {
+                    uint32_t mask = 0;
 #pragma unroll
-                    for (int j = 0; j < 16; j++)
-                        key[j] = args.l2 ? fmaf(-2.f, key[j], xn_s[buf * BN + cb * 16 + j]) : -key[j];
-                    const int nvalid = ncols - cb * 16;  // >= 1
+                    for (int j = 0; j < 32; j++) mask |= (key_of(raw, g, j) < tau) ? (1u << j) : 0u;
+                    return mask & valid;
+                };
+                // key of column j, j known only at run time (rare path): predicated selects
+                auto pick = [&](const uint32_t (&raw)[32], int g, int j) -> float {
+                    float v = 0.f;
+#pragma unroll
+                    for (int jj = 0; jj < 32; jj++)
+                        if (jj == j) v = key_of(raw, g, jj);
+                    return v;
+                };
+                auto process32 = [&](const uint32_t (&raw)[32], int g) {
+                    const int nvalid = ncols - g * 32;
+                    if (nvalid <= 0) return;
+                    const uint32_t valid = nvalid >= 32 ? 0xffffffffu : ((1u << nvalid) - 1u);
+                    if (args.debug & 8) {  // measurement only: consume the registers, no selection
+                        uint32_t x = 0;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) x ^= raw[j];
+                        if (x == 0x12345678u) tau = 0.f;
+                        return;
+                    }
+                    uint32_t mask = beat_mask(raw, g, valid);
+                    if (!__any_sync(kFullMask, mask != 0)) return;
+                    const int32_t colg = col0 + g * 32;
                     if (APPEND) {
-                        uint32_t mask = 0;
-#pragma unroll
-                        for (int j = 0; j < 16; j++)
-                            if (j < nvalid && key[j] < tau) mask |= 1u << j;
                         const unsigned need = __ballot_sync(kFullMask, cnt + __popc(mask) > kBuf);
                         if (need) {
                             const long long c0 = args.stats ? clock64() : 0;
@@ -653,29 +722,28 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                                 atomicAdd(args.stats + kStatCompactCycles, (unsigned long long)(clock64() - c0));
                                 atomicAdd(args.stats + kStatCompactRows, (unsigned long long)__popc(need));
                             }
-                            mask = 0;
-#pragma unroll
-                            for (int j = 0; j < 16; j++)
-                                if (j < nvalid && key[j] < tau) mask |= 1u << j;
+                            mask = beat_mask(raw, g, valid);
                         }
                         if (args.debug & 4) mask = 0;
                         if (args.stats && mask) atomicAdd(args.stats + kStatAppends, (unsigned long long)__popc(mask));
+                        // predicated appends: no branch per column, nothing stored where the bit is clear
                         float *bk = unit_key + (size_t)row * kBuf;
                         int32_t *bi = unit_idx + (size_t)row * kBuf;
 #pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            if (mask & (1u << j)) {
-                                bk[cnt] = key[j];
-                                bi[cnt] = col0 + cb * 16 + j;
-                                cnt++;
-                            }
+                        for (int j = 0; j < 32; j++) {
+                            const bool p = (mask >> j) & 1u;
+                            st_global_if(p, bk + cnt, key_of(raw, g, j));
+                            st_global_if(p, bi + cnt, colg + j);
+                            cnt += p ? 1 : 0;
                         }
                     } else if (SMALLK) {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            if (j < nvalid && key[j] < tau) {
-                                qkey[pos * BM + row] = key[j];
-                                qidx[pos * BM + row] = col0 + cb * 16 + j;
+                        while (mask) {
+                            const int j = __ffs(mask) - 1;
+                            mask &= mask - 1;
+                            const float key = pick(raw, g, j);
+                            if (key < tau) {  // tau may have dropped since the mask was formed
+                                qkey[pos * BM + row] = key;
+                                qidx[pos * BM + row] = colg + j;
                                 float m = -kInf;
                                 for (int s = 0; s < k; s++) {
                                     const float v = qkey[s * BM + row];
@@ -689,26 +757,40 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             }
                         }
                     } else {
-                        uint32_t mask = 0;
-#pragma unroll
-                        for (int j = 0; j < 16; j++)
-                            if (j < nvalid && key[j] < tau) mask |= 1u << j;
-                        const bool overflow = cnt + __popc(mask) > kQueueDepth;
-                        if (__any_sync(kFullMask, overflow)) {
-                            flush_queues<KR>(unit_key, unit_idx, k, quarter * 32, qkey, qidx, cnt, tau, lane, qtau_tile);
-                            mask = 0;
-#pragma unroll
-                            for (int j = 0; j < 16; j++)
-                                if (j < nvalid && key[j] < tau) mask |= 1u << j;
-                        }
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            if (mask & (1u << j)) {
-                                qkey[cnt * BM + row] = key[j];
-                                qidx[cnt * BM + row] = col0 + cb * 16 + j;
+                        // the queue holds 16 entries: take the 32 columns in two halves
+#pragma unroll 1
+                        for (int half = 0; half < 2; half++) {
+                            uint32_t hm = (mask >> (16 * half)) & 0xffffu;
+                            const bool overflow = cnt + __popc(hm) > kQueueDepth;
+                            if (__any_sync(kFullMask, overflow)) {
+                                flush_queues<KR>(unit_key, unit_idx, k, quarter * 32, qkey, qidx, cnt, tau, lane,
+                                                 qtau_tile);
+                                mask = beat_mask(raw, g, valid);
+                                hm = (mask >> (16 * half)) & 0xffffu;
+                            }
+                            while (hm) {
+                                const int j = __ffs(hm) - 1 + 16 * half;
+                                hm &= hm - 1;
+                                qkey[cnt * BM + row] = pick(raw, g, j);
+                                qidx[cnt * BM + row] = colg + j;
                                 cnt++;
                             }
                         }
+                    }
+                };
+                if (!(args.debug & 1)) {
+                    // Two register buffers: the read of the next 32 columns is in flight while
+                    // the current 32 are scanned.
+                    uint32_t ra[32], rb[32];
+                    tmem_ld32_issue(taddr, ra);
+#pragma unroll 1
+                    for (int g = 0; g < BN / 32; g += 2) {
+                        tmem_ld_wait(ra);
+                        tmem_ld32_issue(taddr + (g + 1) * 32, rb);
+                        process32(ra, g);
+                        tmem_ld_wait(rb);
+                        if (g + 2 < BN / 32) tmem_ld32_issue(taddr + (g + 2) * 32, ra);
+                        process32(rb, g + 1);
                     }
                 }
                 tmem_fence_before();
@@ -853,6 +935,10 @@ int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, con
         unsigned long long h[8];
         ANN_CUDA_TRY(cudaStreamSynchronize(stream));
         ANN_CUDA_TRY(cudaMemcpy(h, a.stats, sizeof h, cudaMemcpyDeviceToHost));
+        unsigned long long ph[4] = {0, 0, 0, 0}, zero[4] = {0, 0, 0, 0};
+        cudaMemcpyFromSymbol(ph, g_compact_phase, sizeof ph);
+        cudaMemcpyToSymbol(g_compact_phase, zero, sizeof zero);
+        fprintf(stderr, "[flat_tc compact] rows %llu load %llu sort %llu store %llu cycles\n", ph[3], ph[0], ph[1], ph[2]);
         fprintf(stderr,
                 "[flat_tc stats] grid %d k %d tiles(x4 warps) %llu | compact rows %llu cycles %llu | appends %llu | "
                 "epilogue: wait %llu work %llu cycles | mma wait: tmem %llu smem %llu cycles\n",
