@@ -67,6 +67,7 @@ SIGNATURES = {
     "ann_cuda_index_reserve": (C.c_int, [_P, _I64]),
     "ann_cuda_index_search": (C.c_int, [_P, _I64, _P, _I64, _P, _P]),
     "ann_cuda_index_search_device": (C.c_int, [_P, _I64, _P, _I64, _P, _P, _I64, _P]),
+    "ann_cuda_flat_search_small_static": (C.c_int, [_P, _I64, _P, _I64, _P, _P, _I64, _P]),
     "ann_cuda_index_reset": (C.c_int, [_P]),
     "ann_cuda_index_reconstruct": (C.c_int, [_P, _I64, _P]),
     "ann_cuda_flat_get_rows": (C.c_int, [_P, _I64, _I64, _P]),

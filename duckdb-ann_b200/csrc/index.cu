@@ -939,3 +939,119 @@ int ann_cuda_merge_topk_device(int device, const float *parts_distances, const i
 }
 
 }  // extern "C"
+
+// =================================================================================================
+// Flat search without any allocation.
+//
+// Some hosts of this library may not allocate device memory while they search: a
+// database worker that runs under a fixed memory budget and treats any allocation
+// made behind its back as a leak, a caller that records its searches into a CUDA
+// graph (allocation calls are not permitted between begin and end of a capture),
+// or a latency-critical thread for which cudaMalloc / cudaFree - which can
+// synchronise the whole device - are off limits.  The regular search entry points
+// take their scratch from a growing pool, so their first call, and any call larger
+// than the ones before it, allocates.
+//
+// ann_cuda_flat_search_small_static runs the same kernels as
+// ann_cuda_index_search_device for a small query batch, with ALL scratch (the TF32
+// split of the queries, the per-CTA candidate lists, the shared thresholds, the
+// scheduler counters, the merged selection) carved out of one file-scope device
+// array of fixed size.  The array exists once per device that loads the library
+// (about 6 MB, held until the process exits) and is shared by every call: it keeps
+// whatever the last call left in it, so everything that has to start from a known
+// state is cleared on the stream at the start of each call, and two calls whose GPU
+// work overlaps (different streams, or different host threads) would trample each
+// other - callers must serialise them.
+namespace {
+
+constexpr int64_t kStaticMaxQueries = 128;  // one query tile
+constexpr int kStaticMaxDim = 1024;
+constexpr int kStaticMaxK = 16;             // the shared-memory selection mode
+constexpr int kStaticMaxLists = 304;        // k-lists the kernel may start for the one query tile
+
+constexpr size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+constexpr size_t kOffQhi = 0;
+constexpr size_t kOffQlo = kOffQhi + align256((size_t)kStaticMaxQueries * kStaticMaxDim * 4);
+constexpr size_t kOffQn = kOffQlo + align256((size_t)kStaticMaxQueries * kStaticMaxDim * 4);
+constexpr size_t kOffQtau = kOffQn + align256((size_t)kStaticMaxQueries * 4);
+constexpr size_t kOffSched = kOffQtau + align256(128 * 4);
+constexpr size_t kOffStatus = kOffSched + align256(2 * 4);
+constexpr size_t kOffPartKey = kOffStatus + align256(4);
+constexpr size_t kOffPartIdx = kOffPartKey + align256((size_t)kStaticMaxLists * 128 * kStaticMaxK * 4);
+constexpr size_t kOffSelKey = kOffPartIdx + align256((size_t)kStaticMaxLists * 128 * kStaticMaxK * 4);
+constexpr size_t kOffSelIdx = kOffSelKey + align256((size_t)kStaticMaxQueries * kStaticMaxK * 4);
+constexpr size_t kStaticScratchBytes = kOffSelIdx + align256((size_t)kStaticMaxQueries * kStaticMaxK * 4);
+
+// The scratch itself.  In host code this name is only a handle for the runtime, not a
+// device address: the address a kernel can use comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on `device` (which must be current); looked up
+// once per device and cached.
+int static_scratch_base(int device, unsigned char **out) {
+    static std::mutex mu;
+    static unsigned char *cached[64];
+    if (device < 0 || device >= 64) return set_error("device index %d out of range", device);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached[device]) {
+        void *p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p)
+            return set_error("cudaGetSymbolAddress(static scratch) failed on device %d: %s", device, cudaGetErrorString(e));
+        cached[device] = static_cast<unsigned char *>(p);
+    }
+    *out = cached[device];
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int ann_cuda_flat_search_small_static(const ann_cuda_index *ix, int64_t n, const float *x_device, int64_t k,
+                                                  float *distances_device, int64_t *labels_device,
+                                                  int64_t label_offset, void *stream) {
+    if (!ix || n < 0 || (n > 0 && (!x_device || !distances_device || !labels_device)))
+        return set_error("invalid arguments");
+    if (ix->ivf) return set_error("the allocation-free search exists for Flat indexes only");
+    if (k <= 0) return set_error("k must be > 0");
+    if (n > kStaticMaxQueries)
+        return set_error("allocation-free search: %lld queries exceed the limit of %lld per call", (long long)n,
+                         (long long)kStaticMaxQueries);
+    if (k > kStaticMaxK)
+        return set_error("allocation-free search: k = %lld exceeds the limit of %d", (long long)k, kStaticMaxK);
+    if (ix->dp > kStaticMaxDim)
+        return set_error("allocation-free search: dimension %d exceeds the limit of %d", ix->d, kStaticMaxDim);
+    if (n == 0) return 0;
+    DeviceGuard g(ix->device);
+    if (!g.ok) return set_error("cudaSetDevice(%d) failed", ix->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (ix->ntotal == 0 || ix->store.n == 0) return launch_fill_missing(distances_device, labels_device, n * k, ix->metric, s);
+    unsigned char *base = nullptr;
+    if (static_scratch_base(ix->device, &base)) return -1;  // first call on a device: looks the address up
+    const int k_sel = (int)std::min<int64_t>(k, ix->store.n);
+    const FlatPlan plan = make_flat_plan(n, ix->store.n, k_sel, sm_count(ix->device));
+    if (plan.nq_tiles != 1 || plan.lists_per_qt > kStaticMaxLists || plan.list_stride > kStaticMaxK)
+        return set_error("allocation-free search: this device needs %d candidate lists, the static scratch holds %d",
+                         plan.lists_per_qt, kStaticMaxLists);
+    float *qhi = reinterpret_cast<float *>(base + kOffQhi), *qlo = reinterpret_cast<float *>(base + kOffQlo);
+    float *qn = reinterpret_cast<float *>(base + kOffQn);
+    uint32_t *qtau = reinterpret_cast<uint32_t *>(base + kOffQtau);
+    int *sched = reinterpret_cast<int *>(base + kOffSched), *status = reinterpret_cast<int *>(base + kOffStatus);
+    float *part_key = reinterpret_cast<float *>(base + kOffPartKey);
+    int32_t *part_idx = reinterpret_cast<int32_t *>(base + kOffPartIdx);
+    float *sel_key = reinterpret_cast<float *>(base + kOffSelKey);
+    int32_t *sel_idx = reinterpret_cast<int32_t *>(base + kOffSelIdx);
+    // The array still holds the previous call's lists, thresholds and counters.
+    ANN_CUDA_TRY(cudaMemsetAsync(status, 0, 4, s));
+    ANN_CUDA_TRY(cudaMemsetAsync(qtau, 0xFF, 128 * 4, s));
+    ANN_CUDA_TRY(cudaMemsetAsync(sched, 0, 2 * 4, s));
+    ANN_CUDA_TRY(cudaMemsetAsync(part_idx, 0xFF, plan.part_entries * 4, s));
+    if (launch_split_rows(x_device, n, ix->d, ix->dp, qhi, qlo, qn, s)) return -1;
+    if (launch_flat_tc(plan, ix->store.hi, ix->store.lo, ix->store.norms, ix->store.n, qhi, qlo, n, ix->dp, k_sel,
+                       ix->metric, part_key, part_idx, qtau, sched, status, ix->device, s))
+        return -1;
+    if (launch_merge_parts(part_key, part_idx, 0, sched + plan.nq_tiles, nullptr, plan.lists_per_qt, n, k_sel,
+                           plan.list_stride, sel_key, sel_idx, ix->device, s))
+        return -1;
+    return launch_refine_finalize(ix->store.hi, ix->store.lo, ix->dp, ix->d, x_device, ix->d, sel_idx, n, k_sel, (int)k,
+                                  ix->metric, nullptr, label_offset, distances_device, labels_device, ix->device, s);
+}

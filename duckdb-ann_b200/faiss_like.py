@@ -135,6 +135,26 @@ class CudaIndexFlat(_CudaIndex):
         p = _pkg()
         p.check(p.lib().ann_cuda_flat_create(device, d, metric, C.byref(self._h)), "CudaIndexFlat")
 
+    def search_small_static(self, x, k: int, D=None, I=None, label_offset: int = 0, stream=None):
+        """search_device() for callers that may not allocate device memory (a worker under a
+        fixed memory budget, a search recorded into a CUDA graph): at most 128 queries, k <= 16,
+        d <= 1024, all scratch in a fixed device array.  Calls must not overlap on the GPU.
+        D and I must be passed in if torch itself must not allocate either."""
+        import torch
+        assert x.is_cuda and x.is_contiguous() and x.dtype == torch.float32 and x.shape[1] == self.d
+        n = x.shape[0]
+        if D is None:
+            D = torch.empty((n, k), dtype=torch.float32, device=x.device)
+        if I is None:
+            I = torch.empty((n, k), dtype=torch.int64, device=x.device)
+        s = stream if stream is not None else torch.cuda.current_stream(x.device)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_flat_search_small_static(self._h, n, C.c_void_p(x.data_ptr()), k,
+                                                          C.c_void_p(D.data_ptr()), C.c_void_p(I.data_ptr()),
+                                                          label_offset, C.c_void_p(s.cuda_stream)),
+                "search_small_static")
+        return D, I
+
     def get_rows(self, first: int, n: int):
         out = np.empty((n, self.d), np.float32)
         p = _pkg()

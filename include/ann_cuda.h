@@ -126,6 +126,24 @@ int ann_cuda_index_is_ivf(const ann_cuda_index *index);
 int ann_cuda_index_device(const ann_cuda_index *index);
 void ann_cuda_index_free(ann_cuda_index *index);
 
+/* Flat search that allocates nothing.  It has no counterpart in the reference.
+ * For hosts that must not allocate device memory while searching - a worker bound
+ * to a fixed memory budget, a caller recording its searches into a CUDA graph, a
+ * thread that cannot afford the device-wide stalls cudaMalloc / cudaFree may cause:
+ * the regular entry points grow a scratch pool on first use and whenever a call is
+ * larger than the ones before.  Same arguments and results as
+ * ann_cuda_index_search_device, Flat indexes only, with the limits n <= 128
+ * queries, k <= 16, dimension <= 1024; anything larger returns -1 with the limit
+ * in ann_cuda_last_error().  All scratch lives in one fixed device array of about
+ * 6 MB that every GPU loading the library holds until the process exits.  The first
+ * call on a device looks up that array's address (no allocation); make that first
+ * call before starting any stream capture.  Every call shares the array: calls
+ * whose GPU work may overlap (other streams, other host threads) race on it and
+ * must be serialised by the caller. */
+int ann_cuda_flat_search_small_static(const ann_cuda_index *index, int64_t n, const float *x_device, int64_t k,
+                                      float *distances_device, int64_t *labels_device, int64_t label_offset,
+                                      void *stream);
+
 /* ---- multi-GPU merge -------------------------------------------------------------
  * Final k-select over per-shard results.  parts_*: (nparts x nq x k) in DEVICE
  * memory, each (part, query) run sorted best first as search_device writes it;
