@@ -218,7 +218,8 @@ class FlatWorkload:
                 "metric": self.metric_name, "sharding": f"rows/{world}", "distribution": self.dist_kind,
                 "l2_flush": "database shard (>= 7 GB per GPU) is far larger than L2; no explicit flush"
                 if self.n * self.d * 8 / max(world, 1) > 1e9 else "database is L2-sized: see DESIGN.md",
-                "flat_kernel": self.pkg.lib().ann_cuda_flat_kernel_name().decode()}
+                "flat_kernel": self.pkg.lib().ann_cuda_flat_kernel_name().decode() if getattr(self, "pkg", None)
+                else "cpu"}
 
     def roofline(self, peaks, kernel_ms):
         local_rows = self.hi - self.lo
@@ -400,6 +401,23 @@ class BatchWorkload:
         self.it += 1
         return self.table.batch_distances_by_id_device(self.q_dev, ids, self.qmap, 0, out=self.out), None
 
+    def capture(self, torch, steps):
+        """Records `steps` back-to-back launches (each on a different id batch) into one CUDA
+        graph: the call is shorter than a few launch overheads, so the steady-state rate is
+        measured on a replayed stream of launches rather than on Python's call rate."""
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(s):
+            self.step()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, stream=s):
+                for _ in range(steps):
+                    self.step()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self.graph, self.graph_steps = g, steps
+
     def step_e2e(self, torch):
         ids = self.ids_host[self.it % len(self.ids_host)]
         self.it += 1
@@ -414,7 +432,8 @@ class BatchWorkload:
     def config(self, world):
         return {"workload": self.name, "table_rows": self.num, "dim": self.dim, "queries": self.nq,
                 "rows_per_query": self.per, "metric": "L2", "bytes_per_step": self.bytes_per_step(),
-                "l2_flush": f"{self.batches} id batches cycled; table ({self.num * self.row_bytes / 1e9:.1f} GB) >> L2"}
+                "l2_flush": f"{self.batches} id batches cycled; table ({self.num * self.row_bytes / 1e9:.1f} GB) >> L2",
+                "launch": "the K timed launches are replayed from one CUDA graph"}
 
     def roofline(self, peaks, kernel_ms):
         return {"bound": "hbm", "achieved": None, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None,
@@ -446,6 +465,14 @@ def run_reference(args, wl):
     rank, local, world = dist_info(args)
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every host core it can get
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    os.environ["OMP_NUM_THREADS"] = str(cores)
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=cores)
+    except Exception:
+        pass
     from oracle import oracle
     oracle.build()
     if not isinstance(wl, FlatWorkload):
@@ -464,7 +491,7 @@ def run_reference(args, wl):
     line = {"impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
             "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": wl.config(1) | {"flat_kernel": "cpu"},
+            "config": wl.config(max(args.gpus, 1)) | {"flat_kernel": "cpu"},
             "cpu_baseline": {"value": value, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
                              "sample": desc},
             "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -524,16 +551,26 @@ def main():
     launches0 = lib.ann_cuda_launch_count()
     kernel_ms = []
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    graph = None
+    if isinstance(wl, BatchWorkload):
+        wl.capture(torch, args.steps)
+        graph = wl.graph
+        graph.replay()  # warm replay
     barrier()
     t_begin = sampler.mark()
     ev0.record()
-    for _ in range(args.steps):
-        out = wl.step()
+    if graph is not None:
+        graph.replay()
+    else:
+        for _ in range(args.steps):
+            out = wl.step()
     ev1.record()
     barrier()
     t_end = sampler.mark()
     elapsed_ms = ev0.elapsed_time(ev1)
     launches = lib.ann_cuda_launch_count() - launches0
+    if graph is not None:
+        launches = args.steps  # replayed from the graph: one kernel per captured step
     clocks = sampler.stop(t_begin, t_end)
     if hasattr(wl, "index"):
         ms = lib.ann_cuda_index_last_flat_kernel_ms(wl.index._h)
