@@ -222,7 +222,7 @@ __device__ __forceinline__ void st_global_if(bool p, int32_t *addr, int32_t v) {
 // Folds the queues of this warp's 32 rows into their k-lists in global memory.
 template <int KR>
 __device__ __noinline__ void flush_queues(float *unit_key, int32_t *unit_idx, int k, int row0, const float *qkey,
-                                          const int32_t *qidx, int &cnt, float &tau, int lane, uint32_t *qtau_tile) {
+                                          const int32_t *qidx, int &cnt, float &tau, int lane, uint32_t *qtau_word) {
     for (int r = 0; r < 32; r++) {
         const int c = __shfl_sync(kFullMask, cnt, r);
         if (c == 0) continue;
@@ -248,7 +248,7 @@ __device__ __noinline__ void flush_queues(float *unit_key, int32_t *unit_idx, in
             // larger key can be in the query's final top-k, so it is published for all
             tau = fminf(tau, m);
             cnt = 0;
-            if (m < kInf) atomicMin(qtau_tile + row, float_to_ordered(m));
+            if (m < kInf) atomicMin(qtau_word, float_to_ordered(m));
         }
     }
     __syncwarp();
@@ -265,6 +265,11 @@ struct KernelArgs {
     int64_t ntiles;
     int *next_chunk;  // [nq_tiles] chunks handed out so far (zero on entry)
     int *nlists;      // [nq_tiles] lists started so far (zero on entry)
+    // Grouped mode (IVF list scan): work items are given, one per tile of gathered queries.
+    const int4 *items;          // {gathered query tile, first row, end row, unused}; null = flat mode
+    const int *n_items;         // device count of items
+    int *item_counter;          // zero on entry
+    const int32_t *qrow_query;  // gathered row -> query (its threshold word), -1 = padding row
     float *part_key;
     int32_t *part_idx;
     uint32_t *qtau;  // per query: smallest k-th-best key any chunk has published (ordered-uint form)
@@ -350,7 +355,7 @@ __device__ __forceinline__ void sort512(uint32_t (&key)[16], int32_t (&idx)[16],
 __device__ unsigned long long g_compact_phase[4];  // measurement only: load, sort, store cycles, rows
 
 __device__ __noinline__ void compact_rows(float *slot_key, int32_t *slot_idx, int k, int row0, unsigned need, int &cnt,
-                                          float &tau, int lane, uint32_t *qtau_tile) {
+                                          float &tau, int lane, uint32_t *qtau_word) {
     __syncwarp();  // the appends of every lane are visible to the whole warp
     while (need) {
         const long long p0 = clock64();
@@ -393,7 +398,7 @@ __device__ __noinline__ void compact_rows(float *slot_key, int32_t *slot_idx, in
             if (c >= k) {
                 // the k-th best key so far: nothing above it can reach the final top-k
                 tau = fminf(tau, kth);
-                atomicMin(qtau_tile + row0 + r, float_to_ordered(kth));
+                atomicMin(qtau_word, float_to_ordered(kth));
             }
         }
         if (lane == 0) {
@@ -459,7 +464,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
     const uint32_t tmem_base = *tmem_ptr_s;
 
     struct Work {
-        int qt, tile_begin, tile_end, slot, fresh, pad[3];
+        int qt, row_begin, row_end, slot, fresh, pad[3];
     };
     volatile Work *ring = reinterpret_cast<volatile Work *>(smem + SmemLayout::work_ring);
     const uint32_t bar_wfull = smem_base + SmemLayout::work_bars;
@@ -483,24 +488,41 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             };
             const int home = blockIdx.x % args.nq_tiles;
             bool have = false;
-            for (int i = 0; i < args.nq_tiles && !have; i++) have = adopt((home + i) % args.nq_tiles);
-            while (have) {
-                const int c = atomicAdd(args.next_chunk + cur, 1);
-                if (c >= args.nchunks) {  // this query tile is finished: look for another one
-                    have = false;
-                    const int from = cur;
-                    for (int i = 1; i < args.nq_tiles && !have; i++) have = adopt((from + i) % args.nq_tiles);
-                    continue;
+            if (!args.items)
+                for (int i = 0; i < args.nq_tiles && !have; i++) have = adopt((home + i) % args.nq_tiles);
+            const int n_items = args.items ? *args.n_items : 0;
+            for (;;) {
+                int64_t r_begin, r_end;
+                if (args.items) {
+                    // grouped mode: items are independent, each with its own lists
+                    const int i = atomicAdd(args.item_counter, 1);
+                    if (i >= n_items) break;
+                    const int4 it4 = args.items[i];
+                    cur = it4.x;
+                    slot = it4.x;
+                    fresh = 1;
+                    r_begin = it4.y;
+                    r_end = it4.z;
+                    if (r_end <= r_begin) continue;  // empty list: the slot stays empty
+                } else {
+                    if (!have) break;
+                    const int c = atomicAdd(args.next_chunk + cur, 1);
+                    if (c >= args.nchunks) {  // this query tile is finished: look for another one
+                        have = false;
+                        const int from = cur;
+                        for (int i = 1; i < args.nq_tiles && !have; i++) have = adopt((from + i) % args.nq_tiles);
+                        continue;
+                    }
+                    r_begin = (int64_t)c * args.tiles_per_chunk * BN;
+                    r_end = r_begin + (int64_t)args.tiles_per_chunk * BN;
+                    if (r_end > args.n) r_end = args.n;
                 }
-                const int64_t t_begin = (int64_t)c * args.tiles_per_chunk;
-                int64_t t_end = t_begin + args.tiles_per_chunk;
-                if (t_end > args.ntiles) t_end = args.ntiles;
                 {
                     const uint32_t w = wi % kWorkRing;
                     if (!mbar_wait(bar_wempty + 8 * w, ((wi / kWorkRing) & 1) ^ 1, abort_flag, args.status, 5)) goto done;
                     ring[w].qt = cur;
-                    ring[w].tile_begin = (int)t_begin;
-                    ring[w].tile_end = (int)t_end;
+                    ring[w].row_begin = (int)r_begin;
+                    ring[w].row_end = (int)r_end;
                     ring[w].slot = slot;
                     ring[w].fresh = fresh;
                     fresh = 0;
@@ -508,7 +530,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     mbar_arrive(bar_wfull + 8 * w);
                     wi++;
                 }
-                for (int64_t tile = t_begin; tile < t_end; tile++) {
+                for (int64_t trow = r_begin; trow < r_end; trow += BN) {
                     for (int kb = 0; kb < args.kblocks; kb++) {
                         if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, args.status, 1)) goto done;
                         const uint32_t full = bar_full + 8 * stage;
@@ -516,8 +538,8 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         mbar_expect_tx(full, kStageBytes);
                         tma_load_2d(base, &map_qhi, kb * BK, cur * BM, full);
                         tma_load_2d(base + kABytes, &map_qlo, kb * BK, cur * BM, full);
-                        tma_load_2d(base + 2 * kABytes, &map_xhi, kb * BK, (int32_t)(tile * BN), full);
-                        tma_load_2d(base + 2 * kABytes + kBBytes, &map_xlo, kb * BK, (int32_t)(tile * BN), full);
+                        tma_load_2d(base + 2 * kABytes, &map_xhi, kb * BK, (int32_t)trow, full);
+                        tma_load_2d(base + 2 * kABytes + kBBytes, &map_xlo, kb * BK, (int32_t)trow, full);
                         if (++stage == kStages) {
                             stage = 0;
                             phase ^= 1;
@@ -542,10 +564,10 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 const uint32_t w = wi % kWorkRing;
                 if (!mbar_wait(bar_wfull + 8 * w, (wi / kWorkRing) & 1, abort_flag, args.status, 6)) goto done;
                 const int qt = ring[w].qt;
-                const int64_t t_begin = ring[w].tile_begin, t_end = ring[w].tile_end;
+                const int64_t r_begin = ring[w].row_begin, r_end = ring[w].row_end;
                 mbar_arrive(bar_wempty + 8 * w);
                 if (qt < 0) break;
-                for (int64_t tile = t_begin; tile < t_end; tile++, it++) {
+                for (int64_t trow = r_begin; trow < r_end; trow += BN, it++) {
                     const uint32_t buf = it & 1;
                     long long t0 = args.stats ? clock64() : 0;
                     if (!mbar_wait(bar_tempty + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag, args.status, 2)) goto done;
@@ -592,7 +614,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
         // state of the current list (one per row, kept while the CTA stays with a query tile)
         float *unit_key = nullptr;
         int32_t *unit_idx = nullptr;
-        uint32_t *qtau_tile = nullptr;
+        uint32_t *qtau_word = nullptr;  // this row's shared-threshold word
         bool row_valid = false;
         float tau = -kInf;       // a key must be below this to matter
         float list_max = kInf;   // small k: current maximum of this row's list
@@ -604,7 +626,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             if (!unit_key) return;
             if (APPEND) {
                 const unsigned need = __ballot_sync(kFullMask, cnt > 0);
-                if (need) compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_tile);
+                if (need) compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word);
             } else if (SMALLK) {
                 for (int s = 0; s < k; s++) {
                     unit_key[(size_t)row * k + s] = qkey[s * BM + row];
@@ -612,14 +634,14 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 }
             } else {
                 if (__any_sync(kFullMask, cnt > 0))
-                    flush_queues<KR>(unit_key, unit_idx, k, quarter * 32, qkey, qidx, cnt, tau, lane, qtau_tile);
+                    flush_queues<KR>(unit_key, unit_idx, k, quarter * 32, qkey, qidx, cnt, tau, lane, qtau_word);
             }
         };
         for (uint32_t wi = 0;; wi++) {
             const uint32_t w = wi % kWorkRing;
             if (!mbar_wait(bar_wfull + 8 * w, (wi / kWorkRing) & 1, abort_flag, args.status, 7)) goto done;
             const int qt = ring[w].qt, slot = ring[w].slot, fresh = ring[w].fresh;
-            const int64_t t_begin = ring[w].tile_begin, t_end = ring[w].tile_end;
+            const int64_t r_begin = ring[w].row_begin, r_end = ring[w].row_end;
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_wempty + 8 * w);
             if (qt < 0) break;
@@ -627,8 +649,16 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 close_list();
                 unit_key = args.part_key + (size_t)slot * BM * stride;
                 unit_idx = args.part_idx + (size_t)slot * BM * stride;
-                qtau_tile = args.qtau + (size_t)qt * BM;
-                row_valid = (int64_t)qt * BM + row < args.nq;
+                if (args.items) {
+                    // grouped mode: the row's threshold word belongs to its query, shared by all
+                    // the lists that query probes; padding rows carry -1
+                    const int32_t q = args.qrow_query[(size_t)qt * BM + row];
+                    row_valid = q >= 0;
+                    qtau_word = args.qtau + (row_valid ? q : 0);
+                } else {
+                    row_valid = (int64_t)qt * BM + row < args.nq;
+                    qtau_word = args.qtau + (size_t)qt * BM + row;
+                }
                 tau = row_valid ? kInf : -kInf;
                 list_max = kInf;
                 published = kInf;
@@ -649,12 +679,12 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     }
                 }
             }
-            for (int64_t tile = t_begin; tile < t_end; tile++, it++) {
+            for (int64_t trow = r_begin; trow < r_end; trow += BN, it++) {
                 const uint32_t buf = it & 1;
                 if (args.l2) {
                     for (int j = lane; j < BN; j += 32) {
-                        const int64_t col = tile * BN + j;
-                        xn_s[buf * BN + j] = col < args.n ? __ldg(args.xnorm + col) : 0.f;
+                        const int64_t col = trow + j;
+                        xn_s[buf * BN + j] = col < r_end ? __ldg(args.xnorm + col) : 0.f;
                     }
                     __syncwarp();
                 }
@@ -669,12 +699,12 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 tmem_fence_after();
                 if (row_valid) {
                     // thresholds published by the other CTAs working on this query (L2-coherent read)
-                    const uint32_t tg = __ldcg(qtau_tile + row);
+                    const uint32_t tg = __ldcg(qtau_word);
                     if (tg < float_to_ordered(tau)) tau = ordered_to_float(tg);
                 }
-                const int64_t rem = args.n - tile * BN;
+                const int64_t rem = r_end - trow;
                 const int ncols = rem < BN ? (int)rem : BN;
-                const int32_t col0 = (int32_t)(tile * BN);
+                const int32_t col0 = (int32_t)trow;
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
                 // Selection over 32 accumulator columns (raw: the registers of one TMEM read).
                 // The common case - no column beats the threshold - is branch-free: with one
@@ -717,7 +747,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         const unsigned need = __ballot_sync(kFullMask, cnt + __popc(mask) > kBuf);
                         if (need) {
                             const long long c0 = args.stats ? clock64() : 0;
-                            compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_tile);
+                            compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word);
                             if (args.stats && lane == 0) {
                                 atomicAdd(args.stats + kStatCompactCycles, (unsigned long long)(clock64() - c0));
                                 atomicAdd(args.stats + kStatCompactRows, (unsigned long long)__popc(need));
@@ -764,7 +794,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             const bool overflow = cnt + __popc(hm) > kQueueDepth;
                             if (__any_sync(kFullMask, overflow)) {
                                 flush_queues<KR>(unit_key, unit_idx, k, quarter * 32, qkey, qidx, cnt, tau, lane,
-                                                 qtau_tile);
+                                                 qtau_word);
                                 mask = beat_mask(raw, g, valid);
                                 hm = (mask >> (16 * half)) & 0xffffu;
                             }
@@ -799,7 +829,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 if (args.stats && lane == 0) atomicAdd(args.stats + kStatEpiTileCycles, (unsigned long long)(clock64() - t1));
                 if (SMALLK && list_max < published) {
                     published = list_max;
-                    atomicMin(qtau_tile + row, float_to_ordered(list_max));
+                    atomicMin(qtau_word, float_to_ordered(list_max));
                 }
             }
         }
@@ -885,9 +915,23 @@ FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms) {
     return p;
 }
 
+FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms) {
+    FlatPlan p;
+    p.nq_tiles = (int)max_query_tiles;
+    p.tiles_per_chunk = 0;
+    p.nchunks = 0;
+    p.lists_per_qt = 1;  // a gathered query tile is scanned by exactly one CTA
+    p.grid = (int)(max_query_tiles < sms ? max_query_tiles : sms);
+    if (p.grid < 1) p.grid = 1;
+    p.list_stride = (k > kQueueDepth && k <= kAppendMaxK) ? kBuf : k;
+    p.part_entries = (size_t)max_query_tiles * BM * (size_t)p.list_stride;
+    return p;
+}
+
 int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
-                   int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream) {
+                   int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
+                   const GroupedWork *grouped) {
     (void)device;
     if (n <= 0 || nq <= 0) return 0;
     if (k <= 0 || k > kMaxK) return set_error("k must be in [1, %d]", kMaxK);
@@ -915,6 +959,10 @@ int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, con
     a.part_idx = part_idx;
     a.qtau = qtau;
     a.status = status;
+    a.items = grouped ? grouped->items : nullptr;
+    a.n_items = grouped ? grouped->n_items : nullptr;
+    a.item_counter = grouped ? grouped->item_counter : nullptr;
+    a.qrow_query = grouped ? grouped->qrow_query : nullptr;
     {
         const char *e = getenv("ANN_CUDA_TC_DEBUG");
         a.debug = e ? atoi(e) : 0;

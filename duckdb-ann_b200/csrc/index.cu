@@ -6,8 +6,8 @@
 //             to 32 floats), norms : ntotal fp32.  hi + lo is the original row, bit
 //             for bit, so reconstruct() needs no third copy.
 //   IVFFlat   centroids as a split store (nlist x dp) for the coarse quantiser;
-//             vectors : ntotal x dp fp32 grouped by list (CSR: list_off[nlist+1]),
-//             ids : ntotal int64.  The reference keeps the lists in host vectors and
+//             vectors as hi / lo : ntotal x dp fp32 each, grouped by list (CSR:
+//             list_off[nlist+1]), norms and ids (int64) : ntotal.  The reference keeps the lists in host vectors and
 //             gathers them per query (faiss-metal/src/MetalIndexIVFFlat.mm:32-37,158-194);
 //             here they never leave the device.
 // Searches draw their scratch from a per-index pool of workspaces, one per
@@ -99,7 +99,7 @@ struct Workspace {
     cudaStream_t own_stream = nullptr;
     cudaStream_t bound = nullptr;  // stream whose work may still use these buffers
     GrowBuf x, qhi, qlo, qn, part_key, part_idx, sel_key, sel_idx, status, out_d, out_i;
-    GrowBuf item_q, item_rb, item_re, item_slot, scratch, probes_key, probes, qtau, sched;
+    GrowBuf item_q, item_rb, item_re, item_slot, scratch, probes_key, probes, qtau, sched, gq, items;
     int *status_host = nullptr;  // pinned
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;  // bracket the flat kernel when timing is on
     bool timed = false;
@@ -107,7 +107,7 @@ struct Workspace {
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
         for (GrowBuf *b : {&x, &qhi, &qlo, &qn, &part_key, &part_idx, &sel_key, &sel_idx, &status, &out_d, &out_i,
-                           &item_q, &item_rb, &item_re, &item_slot, &scratch, &probes_key, &probes, &qtau, &sched})
+                           &item_q, &item_rb, &item_re, &item_slot, &scratch, &probes_key, &probes, &qtau, &sched, &gq, &items})
             b->release();
         if (status_host) cudaFreeHost(status_host);
         if (own_stream) cudaStreamDestroy(own_stream);
@@ -129,7 +129,8 @@ struct ann_cuda_index {
     // IVFFlat
     int64_t nlist = 0, nprobe = 1;
     int shard_rank = 0, shard_count = 1;
-    float *vecs = nullptr;    // rows x dp, plain fp32
+    float *vhi = nullptr, *vlo = nullptr;  // rows x dp each: TF32 split of the stored rows, grouped by list
+    float *vnorm = nullptr;                // rows: squared norms
     int64_t *ids = nullptr;   // rows
     int64_t rows = 0, rows_cap = 0;
     std::vector<int32_t> row_list;  // list of every stored row, physical order (host)
@@ -205,15 +206,22 @@ __global__ void kmeans_update_kernel(float *__restrict__ cent, const float *__re
     const int c = (int)(t / d);
     if (counts[c] > 0) cent[t] = sums[t] / (float)counts[c];  // an empty cluster keeps its centroid
 }
-__global__ void gather_rows_kernel(const float *__restrict__ src, const int64_t *__restrict__ src_ids,
-                                   const int64_t *__restrict__ perm, int64_t n, int dp, float *__restrict__ dst,
-                                   int64_t *__restrict__ dst_ids) {
+__global__ void gather_rows_kernel(const float *__restrict__ shi, const float *__restrict__ slo,
+                                   const float *__restrict__ snorm, const int64_t *__restrict__ src_ids,
+                                   const int64_t *__restrict__ perm, int64_t n, int dp, float *__restrict__ dhi,
+                                   float *__restrict__ dlo, float *__restrict__ dnorm, int64_t *__restrict__ dst_ids) {
     const int lane = threadIdx.x & 31;
     for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n;
          r += (int64_t)gridDim.x * (blockDim.x >> 5)) {
         const int64_t s = perm[r];
-        for (int c = lane; c < dp; c += 32) dst[r * (int64_t)dp + c] = src[s * (int64_t)dp + c];
-        if (lane == 0) dst_ids[r] = src_ids[s];
+        for (int c = lane; c < dp; c += 32) {
+            dhi[r * (int64_t)dp + c] = shi[s * (int64_t)dp + c];
+            dlo[r * (int64_t)dp + c] = slo[s * (int64_t)dp + c];
+        }
+        if (lane == 0) {
+            dst_ids[r] = src_ids[s];
+            dnorm[r] = snorm[s];
+        }
     }
 }
 __global__ void find_id_kernel(const int64_t *__restrict__ ids, int64_t n, int64_t key, long long *found) {
@@ -297,6 +305,27 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
                               ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream);
 }
 
+// Allocates the four row arrays of an IVF store for `cap` rows (all or nothing).
+int ivf_alloc_rows(int64_t cap, int dp, float **hi, float **lo, float **norm, int64_t **ids) {
+    *hi = *lo = *norm = nullptr;
+    *ids = nullptr;
+    if (cudaMalloc(hi, (size_t)cap * dp * 4) != cudaSuccess || cudaMalloc(lo, (size_t)cap * dp * 4) != cudaSuccess ||
+        cudaMalloc(norm, (size_t)cap * 4) != cudaSuccess || cudaMalloc(ids, (size_t)cap * 8) != cudaSuccess) {
+        cudaGetLastError();
+        for (void *p : {(void *)*hi, (void *)*lo, (void *)*norm, (void *)*ids})
+            if (p) cudaFree(p);
+        return set_error("out of device memory for %lld inverted-list rows of %d floats (x2 for the TF32 split)",
+                         (long long)cap, dp);
+    }
+    return 0;
+}
+void ivf_free_rows(ann_cuda_index &ix) {
+    for (void *p : {(void *)ix.vhi, (void *)ix.vlo, (void *)ix.vnorm, (void *)ix.ids})
+        if (p) cudaFree(p);
+    ix.vhi = ix.vlo = ix.vnorm = nullptr;
+    ix.ids = nullptr;
+}
+
 // ---- IVF: (re)build the CSR form after adds ------------------------------------------------------
 int ivf_finalize_lists(const ann_cuda_index &cix) {
     std::lock_guard<std::mutex> lock(cix.build_mu);
@@ -310,27 +339,26 @@ int ivf_finalize_lists(const ann_cuda_index &cix) {
         // stable counting sort by list: rows keep their add order inside a list
         std::vector<int64_t> cursor(off.begin(), off.end() - 1), perm((size_t)n);
         for (int64_t i = 0; i < n; i++) perm[(size_t)cursor[ix.row_list[i]]++] = i;
-        float *nv = nullptr;
+        float *nh = nullptr, *nl = nullptr, *nn = nullptr;
         int64_t *ni = nullptr, *dperm = nullptr;
         const int64_t cap = std::max<int64_t>(n, 1);
-        if (cudaMalloc(&nv, (size_t)cap * ix.dp * 4) != cudaSuccess || cudaMalloc(&ni, (size_t)cap * 8) != cudaSuccess ||
-            cudaMalloc(&dperm, (size_t)n * 8) != cudaSuccess) {
+        if (ivf_alloc_rows(cap, ix.dp, &nh, &nl, &nn, &ni)) return -1;
+        if (cudaMalloc(&dperm, (size_t)n * 8) != cudaSuccess) {
             cudaGetLastError();
-            if (nv) cudaFree(nv);
-            if (ni) cudaFree(ni);
-            if (dperm) cudaFree(dperm);
+            for (void *p : {(void *)nh, (void *)nl, (void *)nn, (void *)ni}) cudaFree(p);
             return set_error("out of device memory regrouping the inverted lists");
         }
         ANN_CUDA_TRY(cudaMemcpy(dperm, perm.data(), (size_t)n * 8, cudaMemcpyHostToDevice));
-        gather_rows_kernel<<<(unsigned)std::min<int64_t>((n + 7) / 8, 148 * 32), 256>>>(ix.vecs, ix.ids, dperm, n, ix.dp,
-                                                                                     nv, ni);
+        gather_rows_kernel<<<(unsigned)std::min<int64_t>((n + 7) / 8, 148 * 32), 256>>>(
+            ix.vhi, ix.vlo, ix.vnorm, ix.ids, dperm, n, ix.dp, nh, nl, nn, ni);
         count_launch();
         ANN_CUDA_TRY(cudaGetLastError());
         ANN_CUDA_TRY(cudaDeviceSynchronize());
         cudaFree(dperm);
-        cudaFree(ix.vecs);
-        cudaFree(ix.ids);
-        ix.vecs = nv;
+        ivf_free_rows(ix);
+        ix.vhi = nh;
+        ix.vlo = nl;
+        ix.vnorm = nn;
         ix.ids = ni;
         ix.rows_cap = cap;
         std::vector<int32_t> sorted_list((size_t)n);
@@ -349,21 +377,19 @@ int ivf_grow_rows(ann_cuda_index &ix, int64_t extra) {
     if (ix.rows + extra <= ix.rows_cap) return 0;
     int64_t want = std::max<int64_t>(ix.rows_cap * 2, 1024);
     while (want < ix.rows + extra) want *= 2;
-    float *nv = nullptr;
+    float *nh = nullptr, *nl = nullptr, *nn = nullptr;
     int64_t *ni = nullptr;
-    if (cudaMalloc(&nv, (size_t)want * ix.dp * 4) != cudaSuccess || cudaMalloc(&ni, (size_t)want * 8) != cudaSuccess) {
-        cudaGetLastError();
-        if (nv) cudaFree(nv);
-        if (ni) cudaFree(ni);
-        return set_error("out of device memory growing the inverted lists to %lld rows", (long long)want);
-    }
+    if (ivf_alloc_rows(want, ix.dp, &nh, &nl, &nn, &ni)) return -1;
     if (ix.rows > 0) {
-        ANN_CUDA_TRY(cudaMemcpy(nv, ix.vecs, (size_t)ix.rows * ix.dp * 4, cudaMemcpyDeviceToDevice));
+        ANN_CUDA_TRY(cudaMemcpy(nh, ix.vhi, (size_t)ix.rows * ix.dp * 4, cudaMemcpyDeviceToDevice));
+        ANN_CUDA_TRY(cudaMemcpy(nl, ix.vlo, (size_t)ix.rows * ix.dp * 4, cudaMemcpyDeviceToDevice));
+        ANN_CUDA_TRY(cudaMemcpy(nn, ix.vnorm, (size_t)ix.rows * 4, cudaMemcpyDeviceToDevice));
         ANN_CUDA_TRY(cudaMemcpy(ni, ix.ids, (size_t)ix.rows * 8, cudaMemcpyDeviceToDevice));
     }
-    if (ix.vecs) cudaFree(ix.vecs);
-    if (ix.ids) cudaFree(ix.ids);
-    ix.vecs = nv;
+    ivf_free_rows(ix);
+    ix.vhi = nh;
+    ix.vlo = nl;
+    ix.vnorm = nn;
     ix.ids = ni;
     ix.rows_cap = want;
     return 0;
@@ -413,7 +439,7 @@ int ivf_append(ann_cuda_index &ix, const float *x_dev, int64_t n, const int32_t 
     cudaError_t e = cudaMemcpy(ddst, dst.data(), (size_t)n * 8, cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(ix.ids + ix.rows, kept_ids.data(), (size_t)kept * 8, cudaMemcpyHostToDevice);
     int rc = 0;
-    if (e == cudaSuccess) rc = launch_scatter_rows(x_dev, n, ix.d, ix.dp, ddst, ix.vecs, nullptr);
+    if (e == cudaSuccess) rc = launch_scatter_rows(x_dev, n, ix.d, ix.dp, ddst, ix.vhi, ix.vlo, ix.vnorm, nullptr);
     if (e == cudaSuccess && rc == 0) e = cudaDeviceSynchronize();
     cudaFree(ddst);
     if (e != cudaSuccess) return set_error("appending rows failed: %s", cudaGetErrorString(e));
@@ -445,19 +471,71 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
     // coarse quantiser: nprobe nearest centroids under the index metric
     if (split_store_topk(ix, ix.store, ws, x_dev, nq, nprobe, stream)) return -1;
     const int64_t n_items = nq * nprobe;
-    if (ws.probes.ensure((size_t)n_items * 4) || ws.item_q.ensure(n_items * 4) || ws.item_rb.ensure(n_items * 8) ||
-        ws.item_re.ensure(n_items * 8) || ws.item_slot.ensure(n_items * 4) ||
-        ws.scratch.ensure((size_t)(ix.nlist + 1) * 2 * 4) || ws.part_key.ensure((size_t)n_items * k_sel * 4) ||
-        ws.part_idx.ensure((size_t)n_items * k_sel * 4))
+    if (ws.probes.ensure((size_t)n_items * 4) || ws.item_slot.ensure(n_items * 4) ||
+        ws.scratch.ensure((size_t)(ix.nlist + 1) * 2 * 4) || ws.qtau.ensure((size_t)nq * 4))
         return -1;
     ANN_CUDA_TRY(cudaMemcpyAsync(ws.probes.ptr, ws.sel_idx.ptr, (size_t)n_items * 4, cudaMemcpyDeviceToDevice, stream));
+    ANN_CUDA_TRY(cudaMemsetAsync(ws.qtau.ptr, 0xFF, (size_t)nq * 4, stream));
+    if (flat_kernel_choice() == FlatKernel::TC) {
+        // Tensor-core list scan: queries are grouped by the list they probe (padded to tiles
+        // of 128), every (list, query tile) pair is one work item of the flat kernel, and each
+        // list row is read once per query tile instead of once per query.
+        const int64_t max_tiles = n_items / 128 + ix.nlist + 1;
+        const int64_t max_rows = max_tiles * 128;
+        const FlatPlan plan = make_grouped_plan(max_tiles, k_sel, sm_count(ix.device));
+        if (ws.gq.ensure((size_t)max_rows * 4) || ws.items.ensure((size_t)max_tiles * 16) || ws.sched.ensure(64) ||
+            ws.qhi.ensure((size_t)max_rows * ix.dp * 4) || ws.qlo.ensure((size_t)max_rows * ix.dp * 4) ||
+            ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4) || ws.status.ensure(4))
+            return -1;
+        int *n_tiles = ws.sched.as<int>(), *item_counter = ws.sched.as<int>() + 1;
+        ANN_CUDA_TRY(cudaMemsetAsync(ws.sched.ptr, 0, 64, stream));
+        ANN_CUDA_TRY(cudaMemsetAsync(ws.gq.ptr, 0xFF, (size_t)max_rows * 4, stream));  // padding rows: no query
+        ANN_CUDA_TRY(cudaMemsetAsync(ws.status.ptr, 0, 4, stream));
+        ANN_CUDA_TRY(cudaMemset2DAsync(ws.part_idx.ptr, (size_t)plan.list_stride * 4, 0xFF, (size_t)k_sel * 4,
+                                       (size_t)max_rows, stream));
+        if (launch_group_probes(ws.probes.as<int32_t>(), nq, nprobe, ix.nlist, ix.list_off, ws.scratch.as<int>(), n_tiles,
+                                ws.items.as<int4>(), ws.gq.as<int32_t>(), ws.item_slot.as<int32_t>(), stream))
+            return -1;
+        if (launch_split_gathered(x_dev, ix.d, ix.dp, ws.gq.as<int32_t>(), n_tiles, max_rows, ws.qhi.as<float>(),
+                                  ws.qlo.as<float>(), stream))
+            return -1;
+        GroupedWork gw{ws.items.as<int4>(), n_tiles, item_counter, ws.gq.as<int32_t>()};
+        const bool timing = g_time_kernels.load(std::memory_order_relaxed) != 0;
+        if (timing) {
+            if (!ws.ev0) {
+                ANN_CUDA_TRY(cudaEventCreate(&ws.ev0));
+                ANN_CUDA_TRY(cudaEventCreate(&ws.ev1));
+            }
+            ANN_CUDA_TRY(cudaEventRecord(ws.ev0, stream));
+        }
+        if (launch_flat_tc(plan, ix.vhi, ix.vlo, ix.vnorm, ix.rows, ws.qhi.as<float>(), ws.qlo.as<float>(), max_rows, ix.dp,
+                           k_sel, ix.metric, ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.qtau.as<uint32_t>(),
+                           nullptr, ws.status.as<int>(), ix.device, stream, &gw))
+            return -1;
+        if (timing) {
+            ANN_CUDA_TRY(cudaEventRecord(ws.ev1, stream));
+            ws.timed = true;
+            ix.last_timed_ws = &ws;
+        }
+        ANN_CUDA_TRY(cudaMemcpyAsync(ws.status_host, ws.status.ptr, 4, cudaMemcpyDeviceToHost, stream));
+        if (ws.sel_key.ensure((size_t)nq * k_sel * 4) || ws.sel_idx.ensure((size_t)nq * k_sel * 4)) return -1;
+        if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, nullptr, ws.item_slot.as<int32_t>(),
+                               nprobe, nq, k_sel, plan.list_stride, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(),
+                               ix.device, stream))
+            return -1;
+        // the selected distances are recomputed exactly from hi + lo, as for Flat
+        return launch_refine_finalize(ix.vhi, ix.vlo, ix.dp, ix.d, x_dev, ix.d, ws.sel_idx.as<int32_t>(), nq, k_sel, (int)k,
+                                      ix.metric, ix.ids, label_offset, d_dev, i_dev, ix.device, stream);
+    }
+    // exact-fp32 cross-check path: one warp per (query, list)
+    if (ws.item_q.ensure(n_items * 4) || ws.item_rb.ensure(n_items * 8) || ws.item_re.ensure(n_items * 8) ||
+        ws.part_key.ensure((size_t)n_items * k_sel * 4) || ws.part_idx.ensure((size_t)n_items * k_sel * 4))
+        return -1;
     if (launch_build_ivf_items(ws.probes.as<int32_t>(), nq, nprobe, ix.nlist, ix.list_off, ws.item_q.as<int32_t>(),
                                ws.item_rb.as<int64_t>(), ws.item_re.as<int64_t>(), ws.item_slot.as<int32_t>(),
                                ws.scratch.as<int>(), stream))
         return -1;
-    if (ws.qtau.ensure((size_t)nq * 4)) return -1;
-    ANN_CUDA_TRY(cudaMemsetAsync(ws.qtau.ptr, 0xFF, (size_t)nq * 4, stream));
-    if (launch_scan_items(ix.vecs, nullptr, ix.dp, ix.d, x_dev, ix.d, ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(),
+    if (launch_scan_items(ix.vhi, ix.vlo, ix.dp, ix.d, x_dev, ix.d, ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(),
                           ws.item_re.as<int64_t>(), n_items, k_sel, ix.metric, ws.part_key.as<float>(),
                           ws.part_idx.as<int32_t>(), ws.qtau.as<uint32_t>(), ix.device, stream))
         return -1;
@@ -631,8 +709,7 @@ void ann_cuda_index_free(ann_cuda_index *ix) {
     DeviceGuard g(ix->device);
     cudaDeviceSynchronize();
     ix->store.release_buffers();
-    if (ix->vecs) cudaFree(ix->vecs);
-    if (ix->ids) cudaFree(ix->ids);
+    ivf_free_rows(*ix);
     if (ix->list_off) cudaFree(ix->list_off);
     for (Workspace *w : ix->ws_free) {
         w->release();
@@ -766,9 +843,15 @@ int ann_cuda_ivfflat_get_list(const ann_cuda_index *ix, int64_t list_no, int64_t
     const int64_t b = ix->list_off_host[list_no], n = ix->list_off_host[list_no + 1] - b;
     if (n == 0) return 0;
     if (ids) ANN_CUDA_TRY(cudaMemcpy(ids, ix->ids + b, (size_t)n * 8, cudaMemcpyDeviceToHost));
-    if (rows)
-        ANN_CUDA_TRY(cudaMemcpy2D(rows, (size_t)ix->d * 4, ix->vecs + b * ix->dp, (size_t)ix->dp * 4, (size_t)ix->d * 4,
-                                  (size_t)n, cudaMemcpyDeviceToHost));
+    if (rows) {
+        float *buf = nullptr;
+        ANN_CUDA_TRY(cudaMalloc(&buf, (size_t)n * ix->d * 4));
+        int rc = launch_join_rows(ix->vhi + b * ix->dp, ix->vlo + b * ix->dp, n, ix->d, ix->dp, buf, nullptr);
+        cudaError_t e = cudaMemcpy(rows, buf, (size_t)n * ix->d * 4, cudaMemcpyDeviceToHost);
+        cudaFree(buf);
+        if (rc) return -1;
+        if (e != cudaSuccess) return set_error("list download failed: %s", cudaGetErrorString(e));
+    }
     return 0;
 }
 
@@ -896,7 +979,13 @@ int ann_cuda_index_reconstruct(const ann_cuda_index *ix, int64_t key, float *rec
     cudaMemcpy(&h, found, 8, cudaMemcpyDeviceToHost);
     cudaFree(found);
     if (h == 0x7fffffffffffffffll) return set_error("reconstruct: key %lld not found", (long long)key);
-    ANN_CUDA_TRY(cudaMemcpy(recons, ix->vecs + h * ix->dp, (size_t)ix->d * 4, cudaMemcpyDeviceToHost));
+    float *buf = nullptr;
+    ANN_CUDA_TRY(cudaMalloc(&buf, (size_t)ix->d * 4));
+    int rc = launch_join_rows(ix->vhi + h * ix->dp, ix->vlo + h * ix->dp, 1, ix->d, ix->dp, buf, nullptr);
+    cudaError_t e = cudaMemcpy(recons, buf, (size_t)ix->d * 4, cudaMemcpyDeviceToHost);
+    cudaFree(buf);
+    if (rc) return -1;
+    if (e != cudaSuccess) return set_error("reconstruct failed: %s", cudaGetErrorString(e));
     return 0;
 }
 

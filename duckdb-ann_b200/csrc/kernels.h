@@ -52,9 +52,39 @@ FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms);
 // On entry: part_idx all -1 (bytes 0xFF); qtau (nq_tiles * 128 words, the per-query shared
 // threshold) all bytes 0xFF; sched (2 * nq_tiles ints: chunks taken, lists started) all zero.
 // status: device int, set non-zero if a bounded wait inside the kernel ran out.
+// Grouped mode (IVF list scan): `grouped` names device arrays of work items, one per tile
+// of 128 gathered queries: {query tile, first row, end row} of the inverted list those
+// queries probe.  The query stores then hold the GATHERED queries (query tile t = rows
+// 128 t ..), list slot = query tile, and qrow_query maps a gathered row to its query
+// (-1 = padding), whose word of `qtau` it shares with the query's other probes.
+struct GroupedWork {
+    const int4 *items;
+    const int *n_items;
+    int *item_counter;  // zero on entry
+    const int32_t *qrow_query;
+};
+FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms);
+
 int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
-                   int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream);
+                   int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
+                   const GroupedWork *grouped = nullptr);
+
+// IVF grouping: from probes (nq x nprobe list numbers, -1 = none) builds, on the device,
+//   tile_off[l]     first gathered query tile of list l (lists padded to whole tiles of 128),
+//   n_tiles         total gathered tiles (device int),
+//   items[t]        {t, list_off[l], list_off[l+1], l} for every gathered tile t,
+//   qrow_query[g]   query of gathered row g (-1 padding; caller pre-fills with 0xFF),
+//   gslot[q*nprobe+p] gathered row of probe p of query q (-1 if that probe is invalid).
+// scratch: 2 * (nlist + 1) ints.
+int launch_group_probes(const int32_t *probes, int64_t nq, int nprobe, int64_t nlist, const int64_t *list_off,
+                        int *scratch, int *n_tiles, int4 *items, int32_t *qrow_query, int32_t *gslot,
+                        cudaStream_t stream);
+
+// hi/lo split of gathered query rows: row g takes query qrow_query[g] of x (zeros if < 0),
+// for g < 128 * *n_tiles.
+int launch_split_gathered(const float *x, int d, int dp, const int32_t *qrow_query, const int *n_tiles,
+                          int64_t max_rows, float *hi, float *lo, cudaStream_t stream);
 
 // ---- scan.cu -----------------------------------------------------------------------------
 // Exact-fp32 scan of row ranges with warp k-selection: one warp per (query, range)
@@ -109,8 +139,8 @@ int launch_merge_results(const float *parts_d, const int64_t *parts_i, int npart
 // Fills n (distance, label) slots with the "missing" sentinel.
 int launch_fill_missing(float *d, int64_t *i, int64_t n, int metric, cudaStream_t stream);
 
-// IVF add: scatter rows into their lists.  dst_row[i] is the destination row (or -1 to drop).
-int launch_scatter_rows(const float *x, int64_t n, int d, int dp, const int64_t *dst_row, float *store,
-                        cudaStream_t stream);
+// IVF add: scatter rows into the split store.  dst_row[i] is the destination row (or -1 to drop).
+int launch_scatter_rows(const float *x, int64_t n, int d, int dp, const int64_t *dst_row, float *hi, float *lo,
+                        float *norms, cudaStream_t stream);
 
 }  // namespace anncuda

@@ -74,7 +74,7 @@ merge_parts_kernel(const float *__restrict__ part_key, const int32_t *__restrict
                 list = ((q >> 7) * (int64_t)nparts + p) * 128 + (q & 127);
             else
                 list = slot_of ? (int64_t)slot_of[q * nparts + p] : q * nparts + p;
-            const int32_t idx = part_idx[list * list_stride + j];
+            const int32_t idx = list >= 0 ? part_idx[list * list_stride + j] : -1;
             if (idx >= 0) {
                 key = part_key[list * list_stride + j];
                 val = idx;

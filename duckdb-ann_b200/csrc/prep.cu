@@ -62,12 +62,39 @@ join_rows_kernel(const float *__restrict__ hi, const float *__restrict__ lo, int
 
 __global__ void __launch_bounds__(kWarps * 32)
 scatter_rows_kernel(const float *__restrict__ x, int64_t n, int d, int dp, const int64_t *__restrict__ dst_row,
-                    float *__restrict__ store) {
+                    float *__restrict__ hi, float *__restrict__ lo, float *__restrict__ norms) {
     const int lane = threadIdx.x & 31;
     for (int64_t r = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); r < n; r += (int64_t)gridDim.x * kWarps) {
         const int64_t dst = dst_row[r];
-        if (dst < 0) continue;
-        for (int c = lane; c < dp; c += 32) store[dst * (int64_t)dp + c] = c < d ? x[r * (int64_t)d + c] : 0.f;
+        if (dst < 0) continue;  // warp-uniform
+        float acc = 0.f;
+        for (int c = lane; c < dp; c += 32) {
+            const float v = c < d ? x[r * (int64_t)d + c] : 0.f;
+            const float h = to_tf32(v);
+            acc = fmaf(v, v, acc);
+            hi[dst * (int64_t)dp + c] = h;
+            lo[dst * (int64_t)dp + c] = v - h;
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) norms[dst] = acc;
+    }
+}
+
+__global__ void __launch_bounds__(kWarps * 32)
+split_gathered_kernel(const float *__restrict__ x, int d, int dp, const int32_t *__restrict__ qrow_query,
+                      const int *__restrict__ n_tiles, int64_t max_rows, float *__restrict__ hi,
+                      float *__restrict__ lo) {
+    const int lane = threadIdx.x & 31;
+    int64_t rows = (int64_t)(*n_tiles) * 128;
+    if (rows > max_rows) rows = max_rows;
+    for (int64_t g = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); g < rows; g += (int64_t)gridDim.x * kWarps) {
+        const int32_t q = qrow_query[g];
+        for (int c = lane; c < dp; c += 32) {
+            const float v = (q >= 0 && c < d) ? x[q * (int64_t)d + c] : 0.f;
+            const float h = to_tf32(v);
+            hi[g * (int64_t)dp + c] = h;
+            lo[g * (int64_t)dp + c] = v - h;
+        }
     }
 }
 
@@ -105,10 +132,19 @@ int launch_join_rows(const float *hi, const float *lo, int64_t n, int d, int dp,
     return 0;
 }
 
-int launch_scatter_rows(const float *x, int64_t n, int d, int dp, const int64_t *dst_row, float *store,
-                        cudaStream_t stream) {
+int launch_split_gathered(const float *x, int d, int dp, const int32_t *qrow_query, const int *n_tiles,
+                          int64_t max_rows, float *hi, float *lo, cudaStream_t stream) {
+    if (max_rows <= 0) return 0;
+    split_gathered_kernel<<<grid_for(max_rows), kWarps * 32, 0, stream>>>(x, d, dp, qrow_query, n_tiles, max_rows, hi, lo);
+    count_launch();
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int launch_scatter_rows(const float *x, int64_t n, int d, int dp, const int64_t *dst_row, float *hi, float *lo,
+                        float *norms, cudaStream_t stream) {
     if (n <= 0) return 0;
-    scatter_rows_kernel<<<grid_for(n), kWarps * 32, 0, stream>>>(x, n, d, dp, dst_row, store);
+    scatter_rows_kernel<<<grid_for(n), kWarps * 32, 0, stream>>>(x, n, d, dp, dst_row, hi, lo, norms);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

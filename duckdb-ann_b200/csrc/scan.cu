@@ -187,6 +187,71 @@ __global__ void ivf_place_kernel(const int32_t *__restrict__ probes, int64_t n, 
     range_end[slot] = ok ? list_off[l + 1] : 0;
 }
 
+// ---- grouping of probes by list for the tensor-core list scan ---------------------------------
+// counts[l] = queries probing list l -> tiles[l] = ceil(counts / 128); exclusive scan of tiles.
+__global__ void group_tiles_kernel(const int *__restrict__ counts, int *__restrict__ tile_off, int64_t nlist,
+                                   int *__restrict__ n_tiles) {
+    __shared__ int carry;
+    __shared__ int warp_tot[32];
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int64_t base = 0; base < nlist; base += blockDim.x) {
+        const int64_t i = base + threadIdx.x;
+        const int v = i < nlist ? (counts[i] + 127) / 128 : 0;
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(kFullMask, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            const int w = lane < (int)(blockDim.x >> 5) ? warp_tot[lane] : 0;
+            int wi = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(kFullMask, wi, o);
+                if (lane >= o) wi += t;
+            }
+            warp_tot[lane] = wi - w;
+        }
+        __syncthreads();
+        const int excl = carry + warp_tot[warp] + incl - v;
+        if (i < nlist) tile_off[i] = excl;
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry = excl + v;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *n_tiles = carry;
+}
+
+__global__ void group_items_kernel(const int *__restrict__ counts, const int *__restrict__ tile_off, int64_t nlist,
+                                   const int64_t *__restrict__ list_off, int4 *__restrict__ items) {
+    const int64_t l = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (l >= nlist) return;
+    const int tiles = (counts[l] + 127) / 128;
+    for (int t = 0; t < tiles; t++)
+        items[tile_off[l] + t] = make_int4(tile_off[l] + t, (int)list_off[l], (int)list_off[l + 1], (int)l);
+}
+
+__global__ void group_place_kernel(const int32_t *__restrict__ probes, int64_t n, int nprobe, int64_t nlist,
+                                   const int *__restrict__ tile_off, int *cursors, int32_t *__restrict__ qrow_query,
+                                   int32_t *__restrict__ gslot) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int l = probes[i];
+    if (l < 0 || l >= nlist) {
+        gslot[i] = -1;
+        return;
+    }
+    const int pos = atomicAdd(&cursors[l], 1);
+    const int g = tile_off[l] * 128 + pos;
+    qrow_query[g] = (int32_t)(i / nprobe);
+    gslot[i] = g;
+}
+
 template <int KR>
 int launch_scan_kr(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
                    const int32_t *item_query, const int64_t *rb, const int64_t *re, int64_t n_items, int k,
@@ -241,6 +306,25 @@ int launch_build_ivf_items(const int32_t *probes, int64_t nq, int nprobe, int64_
     ivf_place_kernel<<<blocks, 256, 0, stream>>>(probes, n, nprobe, nlist, list_off, cursors, item_query,
                                                  range_begin, range_end, item_slot);
     count_launch(3);
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int launch_group_probes(const int32_t *probes, int64_t nq, int nprobe, int64_t nlist, const int64_t *list_off,
+                        int *scratch, int *n_tiles, int4 *items, int32_t *qrow_query, int32_t *gslot,
+                        cudaStream_t stream) {
+    const int64_t n = nq * nprobe;
+    if (n <= 0) return 0;
+    int *counts = scratch, *second = scratch + (nlist + 1);  // second: tile offsets, then placement cursors
+    ANN_CUDA_TRY(cudaMemsetAsync(scratch, 0, sizeof(int) * (size_t)(nlist + 1) * 2, stream));
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    ivf_count_kernel<<<blocks, 256, 0, stream>>>(probes, n, nlist, counts);
+    // tile offsets live in `second`; the placement cursors reuse `counts` after it is consumed
+    group_tiles_kernel<<<1, 1024, 0, stream>>>(counts, second, nlist, n_tiles);
+    group_items_kernel<<<(unsigned)((nlist + 255) / 256), 256, 0, stream>>>(counts, second, nlist, list_off, items);
+    ANN_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)(nlist + 1), stream));
+    group_place_kernel<<<blocks, 256, 0, stream>>>(probes, n, nprobe, nlist, second, counts, qrow_query, gslot);
+    count_launch(4);
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
 }
