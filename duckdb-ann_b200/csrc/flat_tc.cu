@@ -627,6 +627,9 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             if (APPEND) {
                 const unsigned need = __ballot_sync(kFullMask, cnt > 0);
                 if (need) compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word);
+                if (!((need >> lane) & 1u)) {  // no candidate ever reached this row: an empty list
+                    for (int s = 0; s < k; s++) unit_idx[(size_t)row * kBuf + s] = -1;
+                }
             } else if (SMALLK) {
                 for (int s = 0; s < k; s++) {
                     unit_key[(size_t)row * k + s] = qkey[s * BM + row];
@@ -672,10 +675,12 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         qidx[s * BM + row] = -1;
                     }
                 } else {
-                    // indices of every slot are -1 on entry (host memset); keys start at +inf
                     for (int r = 0; r < 32; r++) {
                         const size_t base = (size_t)(quarter * 32 + r) * k;
-                        for (int s = lane; s < k; s += 32) unit_key[base + s] = kInf;
+                        for (int s = lane; s < k; s += 32) {
+                            unit_key[base + s] = kInf;
+                            unit_idx[base + s] = -1;
+                        }
                     }
                 }
             }

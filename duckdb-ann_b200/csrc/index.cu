@@ -199,6 +199,47 @@ __global__ void kmeans_accumulate_kernel(const float *__restrict__ x, int64_t n,
         for (int j = lane; j < d; j += 32) atomicAdd(&sums[(int64_t)c * d + j], x[r * (int64_t)d + j]);
     }
 }
+// k-means++-style seeding, one step: every point updates its squared distance to the
+// nearest centre chosen so far (the newest is centre[step - 1]) and competes for being the
+// next centre with score D^2 / E^(1/4), E ~ Exp(1) drawn from a hash of (seed, step, point).
+// With E^1 the arg-max would be an exact draw with probability ~ D^2 (k-means++); the
+// fourth root tempers the noise to a factor of about three, so a group of points that has no
+// centre yet (D^2 orders of magnitude larger) always wins over groups that have one, and the
+// last few uncovered groups are not left to a hub centroid.
+__device__ __forceinline__ uint32_t hash32(uint32_t a) {
+    a ^= a >> 16; a *= 0x7feb352du; a ^= a >> 15; a *= 0x846ca68bu; a ^= a >> 16;
+    return a;
+}
+__global__ void kmeanspp_step_kernel(const float *__restrict__ x, int64_t n, int d, const float *__restrict__ newest,
+                                     float *__restrict__ dmin, uint32_t seed, int step,
+                                     unsigned long long *__restrict__ best) {
+    const int lane = threadIdx.x & 31;
+    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n;
+         r += (int64_t)gridDim.x * (blockDim.x >> 5)) {
+        float acc = 0.f;
+        for (int j = lane; j < d; j += 32) {
+            const float t = x[r * (int64_t)d + j] - newest[j];
+            acc = fmaf(t, t, acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            const float dm = step == 1 ? acc : fminf(dmin[r], acc);
+            dmin[r] = dm;
+            const uint32_t h = hash32(hash32((uint32_t)r ^ seed) + (uint32_t)step * 0x9E3779B9u);
+            const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);  // (0, 1)
+            const float score = dm / sqrtf(sqrtf(-__logf(u)));
+            if (score > 0.f)
+                atomicMax(best, ((unsigned long long)__float_as_uint(score) << 32) | (unsigned long long)(uint32_t)r);
+        }
+    }
+}
+__global__ void kmeanspp_take_kernel(const float *__restrict__ x, int d, float *__restrict__ dst,
+                                     unsigned long long *__restrict__ best) {
+    const int64_t r = (int64_t)(*best & 0xffffffffull);
+    for (int j = threadIdx.x; j < d; j += blockDim.x) dst[j] = x[r * (int64_t)d + j];
+    __syncthreads();
+    if (threadIdx.x == 0) *best = 0ull;
+}
 __global__ void kmeans_update_kernel(float *__restrict__ cent, const float *__restrict__ sums,
                                      const int *__restrict__ counts, int64_t nlist, int d) {
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -491,8 +532,8 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
         ANN_CUDA_TRY(cudaMemsetAsync(ws.sched.ptr, 0, 64, stream));
         ANN_CUDA_TRY(cudaMemsetAsync(ws.gq.ptr, 0xFF, (size_t)max_rows * 4, stream));  // padding rows: no query
         ANN_CUDA_TRY(cudaMemsetAsync(ws.status.ptr, 0, 4, stream));
-        ANN_CUDA_TRY(cudaMemset2DAsync(ws.part_idx.ptr, (size_t)plan.list_stride * 4, 0xFF, (size_t)k_sel * 4,
-                                       (size_t)max_rows, stream));
+        // no clearing of the list memory: every list a query refers to is written in full by
+        // the CTA that scans its (list, query tile) item, and empty lists are never referred to
         if (launch_group_probes(ws.probes.as<int32_t>(), nq, nprobe, ix.nlist, ix.list_off, ws.scratch.as<int>(), n_tiles,
                                 ws.items.as<int4>(), ws.gq.as<int32_t>(), ws.item_slot.as<int32_t>(), stream))
             return -1;
@@ -772,14 +813,48 @@ int ann_cuda_ivfflat_train(ann_cuda_index *ix, int64_t n, const float *x) {
         return set_error("out of device memory in train");
     }
     cudaMemcpy(dx, x, (size_t)n * d * 4, cudaMemcpyHostToDevice);
-    // initial centroids: nlist rows spread evenly over the training set
-    for (int64_t c = 0; c < nlist; c++)
-        cudaMemcpy(cent + c * d, dx + (c * n / nlist) * d, (size_t)d * 4, cudaMemcpyDeviceToDevice);
+    // initial centroids: k-means++ seeding (each next centre drawn with probability ~ squared
+    // distance to the nearest centre so far), so that well separated groups each get a centre
+    {
+        float *dmin = nullptr;
+        unsigned long long *best = nullptr;
+        if (cudaMalloc(&dmin, (size_t)n * 4) != cudaSuccess || cudaMalloc(&best, 8) != cudaSuccess) {
+            cudaGetLastError();
+            if (dmin) cudaFree(dmin);
+            cleanup();
+            return set_error("out of device memory in train");
+        }
+        cudaMemset(best, 0, 8);
+        cudaMemcpy(cent, dx, (size_t)d * 4, cudaMemcpyDeviceToDevice);  // first centre: the first training row
+        const unsigned blocks = (unsigned)std::min<int64_t>((n + 7) / 8, 148 * 16);
+        for (int64_t c = 1; c < nlist; c++) {
+            kmeanspp_step_kernel<<<blocks, 256>>>(dx, n, d, cent + (c - 1) * d, dmin, 0x1234567u, (int)c, best);
+            kmeanspp_take_kernel<<<1, 256>>>(dx, d, cent + c * d, best);
+        }
+        count_launch((int)(2 * (nlist - 1)));
+        const cudaError_t e = cudaDeviceSynchronize();
+        cudaFree(dmin);
+        cudaFree(best);
+        if (e != cudaSuccess) {
+            cleanup();
+            return set_error("device error in k-means++ seeding: %s", cudaGetErrorString(e));
+        }
+    }
     const int saved_metric = ix->metric;
     ix->metric = ANN_CUDA_METRIC_L2;  // Lloyd iterations assign by L2
     ix->trained = true;
     std::vector<int32_t> assign;
-    for (int it = 0; it < 10 && rc == 0; it++) {
+    std::vector<int> hcount((size_t)nlist);
+    std::vector<float> hcent;
+    uint64_t rng = 0x9E3779B97F4A7C15ull;  // fixed seed: training is deterministic
+    auto next_uniform = [&rng]() {
+        rng ^= rng << 13;
+        rng ^= rng >> 7;
+        rng ^= rng << 17;
+        return (double)(rng >> 11) / 9007199254740992.0;
+    };
+    const int kIterations = 20;
+    for (int it = 0; it < kIterations && rc == 0; it++) {
         ix->store.n = 0;
         rc = ix->store.append_device(cent, nlist, d, nullptr);
         if (rc == 0) rc = ivf_assign_device(*ix, dx, n, assign);
@@ -791,6 +866,36 @@ int ann_cuda_ivfflat_train(ann_cuda_index *ix, int64_t n, const float *x) {
         kmeans_update_kernel<<<(unsigned)((nlist * d + 255) / 256), 256>>>(cent, sums, counts, nlist, d);
         count_launch(2);
         if (cudaDeviceSynchronize() != cudaSuccess) rc = set_error("device error in train");
+        // Empty clusters are re-seeded by splitting large ones (the remedy k-means
+        // implementations such as FAISS's use): without it, clusters that start without a
+        // centroid all fall to one hub centroid and a single list swallows them.
+        if (rc == 0 && it + 1 < kIterations) {
+            cudaMemcpy(hcount.data(), counts, (size_t)nlist * 4, cudaMemcpyDeviceToHost);
+            int64_t empty = 0;
+            for (int64_t c = 0; c < nlist; c++) empty += hcount[c] == 0;
+            if (empty > 0) {
+                hcent.resize((size_t)nlist * d);
+                cudaMemcpy(hcent.data(), cent, (size_t)nlist * d * 4, cudaMemcpyDeviceToHost);
+                for (int64_t ci = 0; ci < nlist; ci++) {
+                    if (hcount[ci] != 0) continue;
+                    int64_t cj = 0;
+                    for (int tries = 0; tries < 1 << 20; tries++) {  // pick a cluster with probability ~ its size
+                        cj = (int64_t)(next_uniform() * nlist) % nlist;
+                        const double p = (hcount[cj] - 1.0) / (double)(n - nlist + 1);
+                        if (next_uniform() < p) break;
+                    }
+                    const float eps = 1.0f / 1024.0f;
+                    for (int j = 0; j < d; j++) {
+                        const float v = hcent[cj * d + j];
+                        hcent[ci * d + j] = v * ((j & 1) ? 1 + eps : 1 - eps);
+                        hcent[cj * d + j] = v * ((j & 1) ? 1 - eps : 1 + eps);
+                    }
+                    hcount[ci] = hcount[cj] / 2;
+                    hcount[cj] -= hcount[ci];
+                }
+                cudaMemcpy(cent, hcent.data(), (size_t)nlist * d * 4, cudaMemcpyHostToDevice);
+            }
+        }
     }
     ix->metric = saved_metric;
     if (rc == 0) {

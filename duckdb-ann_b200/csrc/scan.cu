@@ -237,12 +237,13 @@ __global__ void group_items_kernel(const int *__restrict__ counts, const int *__
 }
 
 __global__ void group_place_kernel(const int32_t *__restrict__ probes, int64_t n, int nprobe, int64_t nlist,
-                                   const int *__restrict__ tile_off, int *cursors, int32_t *__restrict__ qrow_query,
-                                   int32_t *__restrict__ gslot) {
+                                   const int64_t *__restrict__ list_off, const int *__restrict__ tile_off,
+                                   int *cursors, int32_t *__restrict__ qrow_query, int32_t *__restrict__ gslot) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int l = probes[i];
-    if (l < 0 || l >= nlist) {
+    // an invalid probe or an empty list contributes nothing: no list slot is ever written for it
+    if (l < 0 || l >= nlist || list_off[l + 1] == list_off[l]) {
         gslot[i] = -1;
         return;
     }
@@ -323,7 +324,7 @@ int launch_group_probes(const int32_t *probes, int64_t nq, int nprobe, int64_t n
     group_tiles_kernel<<<1, 1024, 0, stream>>>(counts, second, nlist, n_tiles);
     group_items_kernel<<<(unsigned)((nlist + 255) / 256), 256, 0, stream>>>(counts, second, nlist, list_off, items);
     ANN_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)(nlist + 1), stream));
-    group_place_kernel<<<blocks, 256, 0, stream>>>(probes, n, nprobe, nlist, second, counts, qrow_query, gslot);
+    group_place_kernel<<<blocks, 256, 0, stream>>>(probes, n, nprobe, nlist, list_off, second, counts, qrow_query, gslot);
     count_launch(4);
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
