@@ -960,6 +960,32 @@ int ann_cuda_ivfflat_get_list(const ann_cuda_index *ix, int64_t list_no, int64_t
     return 0;
 }
 
+int ann_cuda_ivfflat_coarse(const ann_cuda_index *ix, int64_t n, const float *x, int64_t nprobe, int64_t *lists) {
+    if (!ix || !ix->ivf || n < 0 || (n > 0 && (!x || !lists)) || nprobe <= 0) return set_error("invalid arguments");
+    if (!ix->trained) return set_error("index is not trained");
+    if (n == 0) return 0;
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    const int np = (int)std::min<int64_t>(nprobe, ix->nlist);
+    WsLease lease(ix, nullptr, true);
+    if (!lease.ws) return -1;
+    Workspace &ws = *lease.ws;
+    cudaStream_t s = ws.own_stream;
+    std::vector<int32_t> tmp;
+    for (int64_t q0 = 0; q0 < n; q0 += kQueryBlock) {
+        const int64_t nb = std::min(kQueryBlock, n - q0);
+        if (ws.x.ensure((size_t)nb * ix->d * 4)) return -1;
+        ANN_CUDA_TRY(cudaMemcpyAsync(ws.x.ptr, x + q0 * ix->d, (size_t)nb * ix->d * 4, cudaMemcpyHostToDevice, s));
+        if (split_store_topk(*ix, ix->store, ws, ws.x.as<float>(), nb, np, s)) return -1;
+        tmp.resize((size_t)nb * np);
+        ANN_CUDA_TRY(cudaMemcpyAsync(tmp.data(), ws.sel_idx.ptr, (size_t)nb * np * 4, cudaMemcpyDeviceToHost, s));
+        ANN_CUDA_TRY(cudaStreamSynchronize(s));
+        for (int64_t q = 0; q < nb; q++)
+            for (int64_t p = 0; p < nprobe; p++) lists[(q0 + q) * nprobe + p] = p < np ? tmp[q * np + p] : -1;
+    }
+    return 0;
+}
+
 int ann_cuda_ivfflat_set_nprobe(ann_cuda_index *ix, int64_t nprobe) {
     if (!ix || !ix->ivf) return set_error("not an IVFFlat index");
     ix->nprobe = std::max<int64_t>(1, std::min(nprobe, ix->nlist));  // MetalIndexIVFFlat.mm:275-279

@@ -205,6 +205,14 @@ class CudaIndexIVFFlat(_CudaIndex):
         p.check(p.lib().ann_cuda_ivfflat_get_list(self._h, list_no, _ptr(ids), _ptr(rows)), "get_list")
         return ids, rows
 
+    def coarse(self, x, nprobe: int):
+        """Coarse quantiser only: (n, nprobe) list numbers, nearest centroid first."""
+        x = _np_f32(x)
+        out = np.empty((x.shape[0], nprobe), np.int64)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_ivfflat_coarse(self._h, x.shape[0], _ptr(x), nprobe, _ptr(out)), "coarse")
+        return out
+
     def getNlist(self) -> int:
         return _pkg().lib().ann_cuda_ivfflat_nlist(self._h)
 

@@ -73,6 +73,11 @@ int64_t ann_cuda_ivfflat_list_size(const ann_cuda_index *index, int64_t list_no)
 int ann_cuda_ivfflat_get_list(const ann_cuda_index *index, int64_t list_no, int64_t *ids, float *rows);
 int ann_cuda_ivfflat_get_centroids(const ann_cuda_index *index, float *centroids);
 
+/* The coarse quantiser alone: the `nprobe` nearest centroids of each of n host queries
+ * under the index metric, nearest first, as list numbers (-1 past nlist) - the
+ * coarse_search step of MetalIndexIVFFlat::search (MetalIndexIVFFlat.mm:60-66, 155). */
+int ann_cuda_ivfflat_coarse(const ann_cuda_index *index, int64_t n, const float *x, int64_t nprobe, int64_t *lists);
+
 /* setNprobe / getNprobe (MetalIndexIVFFlat.mm:267-279): clamped to [1, nlist]. */
 int ann_cuda_ivfflat_set_nprobe(ann_cuda_index *index, int64_t nprobe);
 int64_t ann_cuda_ivfflat_get_nprobe(const ann_cuda_index *index);

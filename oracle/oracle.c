@@ -51,6 +51,16 @@ ORACLE_API int oracle_num_threads(void) {
 #endif
 }
 
+/* Lets the caller use every host core even when the environment said otherwise
+ * (torchrun exports OMP_NUM_THREADS=1 to its children). */
+ORACLE_API void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------------- */
 /* Batch distance: the scalar loop of ComputeDistancesCPU, same operation     */
 /* order, float accumulator (src/ann_search.cpp:702-720).                     */

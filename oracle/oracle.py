@@ -58,6 +58,10 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    lib().oracle_set_num_threads(C.c_int(int(n)))
+
+
 # --------------------------------------------------------------------------- batch distance
 def batch_distances(query, candidates, metric: int, exact: bool = False):
     """One query against n gathered rows (src/ann_search.cpp:702-720)."""
