@@ -155,19 +155,53 @@ __device__ __forceinline__ float sq8_acc(float acc, float q, uint32_t code, floa
 }
 
 // SQ8 rows with dim % 4 == 0 and dim <= 512.  Lane l owns the 4*WPL consecutive
-// dimensions starting at 4*WPL*l of EVERY row, so its slice of the scale stays in
+// dimensions starting at 4*WPL*l of EVERY row, so its slice of scale/255 stays in
 // registers for the whole kernel and its slice of (query - min) is rebuilt only
 // when the query changes (rows of one query are adjacent in DiskANN's lock-step
 // batches, rust_lib/src/disk_provider.rs:546-581).  A row is then WPL coalesced
 // 4-byte loads per lane and nothing else: the only traffic per row is its codes.
-// code/255 comes from a table in shared memory, replicated once per bank so the
-// lookups never conflict.  Arithmetic per element: the dequantised value is
-// (code/255)*scale+min (rust_lib/src/provider.rs:142-143); L2 uses
-// q - x = (q - min) - (code/255)*scale as one fused multiply-add (differs from the
-// reference's operation order by one rounding of magnitude 1e-7 relative), inner
-// product uses q*(code/255)*scale summed plus q.min once per query.
+//
+// The kernel is bound by instruction issue, not by HBM, so the per-element work is
+// cut to four instructions: a byte permute drops the code into the mantissa of
+// 2^23 (giving the float 2^23 + code), one subtraction yields the code as a float,
+// and two fused multiply-adds form (q - min) - code * (scale / 255) and its square.
+// The dequantised value code * (scale / 255) + min differs from the reference's
+// (code / 255) * scale + min (rust_lib/src/provider.rs:142-143) by at most an ulp
+// or two of the product, orders of magnitude inside the 1e-4 distance tolerance.
 // Eight rows are processed together so that eight independent sums are in flight.
 constexpr int kSq8RowsPerWarp = 8;
+
+// code byte `b` of word w as a float
+template <int B>
+__device__ __forceinline__ float code_as_float(uint32_t w) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | B)) - 8388608.0f;
+}
+
+// Sums eight per-lane values over the warp with 9 shuffles instead of 40: each exchange
+// halves the number of values a lane carries (the lane keeps the half its bit selects and
+// adds the partner's copy of it).  Afterwards every lane holds the total of row lane >> 2.
+__device__ __forceinline__ float warp_sum8(const float (&a)[8], int lane) {
+    float b[4], c[2];
+    const bool h4 = lane & 16, h3 = lane & 8, h2 = lane & 4;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float keep = h4 ? a[4 + i] : a[i];
+        const float send = h4 ? a[i] : a[4 + i];
+        b[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const float keep = h3 ? b[2 + i] : b[i];
+        const float send = h3 ? b[i] : b[2 + i];
+        c[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+    const float keep = h2 ? c[1] : c[0];
+    const float send = h2 ? c[0] : c[1];
+    float v = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v;
+}
 
 template <int WPL>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
@@ -176,22 +210,18 @@ batch_distance_sq8_regs_kernel(const uint8_t *__restrict__ codes, size_t num, in
                                const float *__restrict__ queries, int nq, const uint32_t *__restrict__ ids,
                                const uint32_t *__restrict__ qmap, int total_n, int metric,
                                float *__restrict__ out) {
-    __shared__ float lut[256 * 32];  // lut[c * 32 + lane] = c / 255
-    for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) lut[i] = code_over_255((float)(i >> 5));
-    __syncthreads();
     const int lane = threadIdx.x & 31;
     const long long warp_global = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const long long warps_total = (long long)gridDim.x * kWarpsPerBlock;
     const bool l2 = (metric == 0);
     const int d0 = lane * 4 * WPL;   // first dimension of this lane
     const bool active = d0 < dim;    // dim is a multiple of 4 * WPL
-    const float *mylut = lut + lane;
-    float s[WPL * 4];   // scale of my dimensions
-    float qa[WPL * 4];  // L2: q - min;  IP: q
+    float s[WPL * 4];   // scale / 255 of my dimensions
+    float qa[WPL * 4];  // L2: q - min;  IP: q * scale / 255
     float qmin = 0.f;   // IP: sum over my dimensions of q * min
 #pragma unroll
     for (int j = 0; j < WPL * 4; j++) {
-        s[j] = active ? __ldg(scale + d0 + j) : 0.f;
+        s[j] = active ? __fdiv_rn(__ldg(scale + d0 + j), 255.0f) : 0.f;
         qa[j] = 0.f;
     }
     uint32_t cur_q = 0xffffffffu;
@@ -202,11 +232,25 @@ batch_distance_sq8_regs_kernel(const uint8_t *__restrict__ codes, size_t num, in
         for (int j = 0; j < WPL * 4; j++) {
             const float qv = active ? __ldg(queries + (size_t)qi * dim + d0 + j) : 0.f;
             const float mv = active ? __ldg(mins + d0 + j) : 0.f;
-            qa[j] = l2 ? qv - mv : qv;
+            qa[j] = l2 ? qv - mv : qv * s[j];
             qmin = fmaf(qv, mv, qmin);
         }
     };
-    for (long long base = warp_global * kSq8RowsPerWarp; base < total_n; base += warps_total * kSq8RowsPerWarp) {
+    // one element of one row: acc += ((q - min) - c * s)^2   or   acc += c * (q * s)
+    auto step = [&](float acc, float c, int j) -> float {
+        if (l2) {
+            const float diff = fmaf(-c, s[j], qa[j]);
+            return fmaf(diff, diff, acc);
+        }
+        return fmaf(c, qa[j], acc);
+    };
+    // contiguous run of row groups per warp: consecutive groups mostly share their query
+    const long long n_groups = ((long long)total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
+    const long long per_warp = (n_groups + warps_total - 1) / warps_total;
+    const long long g_first = warp_global * per_warp;
+    const long long g_last = g_first + per_warp < n_groups ? g_first + per_warp : n_groups;
+    for (long long g = g_first; g < g_last; g++) {
+        const long long base = g * kSq8RowsPerWarp;
         uint32_t w[kSq8RowsPerWarp][WPL];
         uint32_t qi[kSq8RowsPerWarp];
         bool ok[kSq8RowsPerWarp];
@@ -242,21 +286,14 @@ batch_distance_sq8_regs_kernel(const uint8_t *__restrict__ codes, size_t num, in
 #pragma unroll
             for (int j = 0; j < WPL; j++) {
 #pragma unroll
-                for (int b = 0; b < 4; b++) {
-                    const float sv = s[j * 4 + b], qv = qa[j * 4 + b];
-#pragma unroll
-                    for (int t = 0; t < kSq8RowsPerWarp; t++) {
-                        const float tv = mylut[((w[t][j] >> (8 * b)) & 0xffu) << 5];
-                        if (l2) {
-                            const float diff = fmaf(-tv, sv, qv);
-                            acc[t] = fmaf(diff, diff, acc[t]);
-                        } else {
-                            acc[t] = fmaf(tv * sv, qv, acc[t]);
-                        }
-                    }
+                for (int t = 0; t < kSq8RowsPerWarp; t++) {
+                    acc[t] = step(acc[t], code_as_float<0>(w[t][j]), j * 4 + 0);
+                    acc[t] = step(acc[t], code_as_float<1>(w[t][j]), j * 4 + 1);
+                    acc[t] = step(acc[t], code_as_float<2>(w[t][j]), j * 4 + 2);
+                    acc[t] = step(acc[t], code_as_float<3>(w[t][j]), j * 4 + 3);
                 }
             }
-            if (!l2) {
+            if (!l2) {  // inner product: add this lane's share of q.min, the same for every row
 #pragma unroll
                 for (int t = 0; t < kSq8RowsPerWarp; t++) acc[t] += qmin;
             }
@@ -267,36 +304,254 @@ batch_distance_sq8_regs_kernel(const uint8_t *__restrict__ codes, size_t num, in
                 if (qi[t] != cur_q) load_query(qi[t]);
 #pragma unroll
                 for (int j = 0; j < WPL; j++) {
-#pragma unroll
-                    for (int b = 0; b < 4; b++) {
-                        const float tv = mylut[((w[t][j] >> (8 * b)) & 0xffu) << 5];
-                        if (l2) {
-                            const float diff = fmaf(-tv, s[j * 4 + b], qa[j * 4 + b]);
-                            acc[t] = fmaf(diff, diff, acc[t]);
-                        } else {
-                            acc[t] = fmaf(tv * s[j * 4 + b], qa[j * 4 + b], acc[t]);
-                        }
-                    }
+                    acc[t] = step(acc[t], code_as_float<0>(w[t][j]), j * 4 + 0);
+                    acc[t] = step(acc[t], code_as_float<1>(w[t][j]), j * 4 + 1);
+                    acc[t] = step(acc[t], code_as_float<2>(w[t][j]), j * 4 + 2);
+                    acc[t] = step(acc[t], code_as_float<3>(w[t][j]), j * 4 + 3);
                 }
                 if (!l2) acc[t] += qmin;
             }
         }
-#pragma unroll
-        for (int t = 0; t < kSq8RowsPerWarp; t++) acc[t] = warp_sum(acc[t]);
-        if (lane < kSq8RowsPerWarp) {
-            float v = 0.f;
+        static_assert(kSq8RowsPerWarp == 8, "warp_sum8 reduces eight rows");
+        const float v = warp_sum8(acc, lane);  // total of row lane >> 2
+        if ((lane & 3) == 0) {
             bool good = false;
 #pragma unroll
-            for (int t = 0; t < kSq8RowsPerWarp; t++) {
-                if (lane == t) {
-                    v = acc[t];
-                    good = ok[t];
-                }
-            }
-            const long long i = base + lane;
+            for (int t = 0; t < kSq8RowsPerWarp; t++)
+                if ((lane >> 2) == t) good = ok[t];
+            const long long i = base + (lane >> 2);
             if (i < total_n) out[i] = good ? (l2 ? v : -v) : __int_as_float(0x7fc00000);
         }
     }
+}
+
+// SQ8 rows with dim % 16 == 0 and dim <= 512, pipelined through shared memory.
+// The register kernel above is bound by latency: a warp must read ids, then (dependent)
+// the code rows, then compute, and has room for only eight rows in flight.  Here each warp
+// runs a four-stage cp.async ring of eight rows per stage (ids are read 32 rows at a time,
+// one block ahead; rows one to three groups ahead), so ~9 KB of codes per warp are always
+// in flight while it computes on the oldest stage.
+//
+// With the latency hidden the kernel is bound by instruction issue, so the arithmetic is
+// packed: lane l owns the 4-code words l, l + 32, ... of every row (conflict-free 4-byte
+// shared loads, 16-byte query loads), two codes at a time go through the two-wide fp32
+// instructions (add.f32x2 / fma.f32x2), 2.5 instructions per code instead of 4, and the
+// metric is a template parameter.  Per code the operations and their roundings are those
+// of the register kernel; only the order of the final sum differs (two partial sums per
+// lane).
+constexpr int kPipeStages = 4;
+constexpr int kPipeMaxDim = 512;
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// two fp32 values in one 64-bit register, for the packed instructions of sm_100
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_pack_bits(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ float f2_sum(uint64_t v) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    return lo + hi;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+template <int WPL, bool L2>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+batch_distance_sq8_pipe_kernel(const uint8_t *__restrict__ codes, size_t num, int dim,
+                               const float *__restrict__ mins, const float *__restrict__ scale,
+                               const float *__restrict__ queries, int nq, const uint32_t *__restrict__ ids,
+                               const uint32_t *__restrict__ qmap, int total_n, float *__restrict__ out) {
+    extern __shared__ __align__(16) uint8_t sq8_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // per warp: kPipeStages x (8 rows x dim bytes), then kPipeStages x 8 query numbers
+    uint8_t *ring = sq8_smem + (size_t)warp * kPipeStages * (kSq8RowsPerWarp * dim + kSq8RowsPerWarp * 4);
+    uint32_t *meta = reinterpret_cast<uint32_t *>(ring + (size_t)kPipeStages * kSq8RowsPerWarp * dim);
+    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+    const long long warp_global = (long long)blockIdx.x * kWarpsPerBlock + warp;
+    const long long warps_total = (long long)gridDim.x * kWarpsPerBlock;
+    const long long n_groups = ((long long)total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
+    const int words = dim >> 2;   // 4-code words per row
+    const int chunks = dim >> 4;  // 16-byte pieces per row
+    bool act[WPL];                // does word lane + 32 j exist?
+    uint64_t ns2[WPL * 2];        // L2: -(scale / 255) of my dimensions, in pairs
+    uint64_t qa2[WPL * 2];        // L2: q - min;  IP: q * scale / 255
+    float sc[L2 ? 1 : WPL * 4];   // IP: scale / 255, needed when the query changes
+    float qmin = 0.f;             // IP: sum over my dimensions of q * min
+#pragma unroll
+    for (int j = 0; j < WPL; j++) {
+        act[j] = lane + 32 * j < words;
+        float4 sv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (act[j]) sv = __ldg(reinterpret_cast<const float4 *>(scale) + lane + 32 * j);
+        sv.x = __fdiv_rn(sv.x, 255.0f);
+        sv.y = __fdiv_rn(sv.y, 255.0f);
+        sv.z = __fdiv_rn(sv.z, 255.0f);
+        sv.w = __fdiv_rn(sv.w, 255.0f);
+        ns2[2 * j] = f2_pack(-sv.x, -sv.y);
+        ns2[2 * j + 1] = f2_pack(-sv.z, -sv.w);
+        qa2[2 * j] = qa2[2 * j + 1] = 0ull;
+        if (!L2) {
+            sc[4 * j] = sv.x;
+            sc[4 * j + 1] = sv.y;
+            sc[4 * j + 2] = sv.z;
+            sc[4 * j + 3] = sv.w;
+        }
+    }
+    uint32_t cur_q = 0xffffffffu;
+    auto load_query = [&](uint32_t qi) {
+        cur_q = qi;
+        qmin = 0.f;
+#pragma unroll
+        for (int j = 0; j < WPL; j++) {
+            float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), mv = qv;
+            if (act[j]) {
+                qv = __ldg(reinterpret_cast<const float4 *>(queries + (size_t)qi * dim) + lane + 32 * j);
+                mv = __ldg(reinterpret_cast<const float4 *>(mins) + lane + 32 * j);
+            }
+            if (L2) {
+                qa2[2 * j] = f2_pack(qv.x - mv.x, qv.y - mv.y);
+                qa2[2 * j + 1] = f2_pack(qv.z - mv.z, qv.w - mv.w);
+            } else {
+                qa2[2 * j] = f2_pack(qv.x * sc[4 * j], qv.y * sc[4 * j + 1]);
+                qa2[2 * j + 1] = f2_pack(qv.z * sc[4 * j + 2], qv.w * sc[4 * j + 3]);
+                qmin = fmaf(qv.x, mv.x, qmin);
+                qmin = fmaf(qv.y, mv.y, qmin);
+                qmin = fmaf(qv.z, mv.z, qmin);
+                qmin = fmaf(qv.w, mv.w, qmin);
+            }
+        }
+    };
+    const uint64_t neg_magic = f2_pack(-8388608.0f, -8388608.0f);
+    // this lane's share of one row: sum of ((q - min) - c * s)^2   or of   c * (q * s)
+    auto row_sum = [&](const uint8_t *row) -> float {
+        uint64_t acc = 0ull;
+#pragma unroll
+        for (int j = 0; j < WPL; j++) {
+            uint32_t w = 0;
+            if (act[j]) w = reinterpret_cast<const uint32_t *>(row)[lane + 32 * j];
+            // a byte permute drops each code into the mantissa of 2^23: the float 2^23 + code
+            const uint64_t c01 = f2_add(f2_pack_bits(__byte_perm(w, 0x4B000000u, 0x7540u),
+                                                     __byte_perm(w, 0x4B000000u, 0x7541u)), neg_magic);
+            const uint64_t c23 = f2_add(f2_pack_bits(__byte_perm(w, 0x4B000000u, 0x7542u),
+                                                     __byte_perm(w, 0x4B000000u, 0x7543u)), neg_magic);
+            if (L2) {
+                const uint64_t d01 = f2_fma(c01, ns2[2 * j], qa2[2 * j]);
+                const uint64_t d23 = f2_fma(c23, ns2[2 * j + 1], qa2[2 * j + 1]);
+                acc = f2_fma(d01, d01, acc);
+                acc = f2_fma(d23, d23, acc);
+            } else {
+                acc = f2_fma(c01, qa2[2 * j], acc);
+                acc = f2_fma(c23, qa2[2 * j + 1], acc);
+            }
+        }
+        return f2_sum(acc) + (L2 ? 0.f : qmin);
+    };
+    // A warp takes a CONTIGUOUS run of groups, so that consecutive groups mostly share their
+    // query and its registers are rebuilt once per query, not once per group.
+    const long long per_warp = (n_groups + warps_total - 1) / warps_total;
+    const long long g_first = warp_global * per_warp;
+    const long long g_last = g_first + per_warp < n_groups ? g_first + per_warp : n_groups;
+    // ids and queries are read 32 rows (four groups) at a time, one coalesced load per block,
+    // one block ahead of the copies that need them: lane L holds row 32 b + L of the run.
+    auto fetch_block = [&](long long blk, uint32_t &rid, uint32_t &rq) {
+        rid = 0xffffffffu;
+        rq = 0xffffffffu;
+        const long long g = g_first + blk * 4 + (lane >> 3);
+        const long long i = g * kSq8RowsPerWarp + (lane & 7);
+        if (g < g_last && i < total_n) {
+            const uint32_t r = ids ? ids[i] : (uint32_t)i;
+            const uint32_t q = qmap ? qmap[i] : 0u;
+            if ((size_t)r < num && q < (uint32_t)nq) {
+                rid = r;
+                rq = q;
+            }
+        }
+    };
+    // starts the copies of group `sub` (0..3) of an id block into ring stage `st`
+    auto issue = [&](int st, int sub, uint32_t rid, uint32_t rq) {
+        const uint32_t myq = __shfl_sync(0xffffffffu, rq, sub * 8 + (lane & 7));
+        if (lane < kSq8RowsPerWarp) meta[st * kSq8RowsPerWarp + lane] = myq;
+#pragma unroll
+        for (int t = 0; t < kSq8RowsPerWarp; t++) {
+            const uint32_t r = __shfl_sync(0xffffffffu, rid, sub * 8 + t);
+            if (r != 0xffffffffu && lane < chunks)
+                cp_async16(ring_s + (uint32_t)((st * kSq8RowsPerWarp + t) * dim + lane * 16),
+                           codes + (size_t)r * dim + lane * 16);
+        }
+        cp_async_commit();
+    };
+    uint32_t rid_cur, rq_cur, rid_nxt, rq_nxt;
+    fetch_block(0, rid_cur, rq_cur);
+    fetch_block(1, rid_nxt, rq_nxt);
+    long long issued = 0;  // groups whose copies have been started (relative to g_first)
+    auto issue_next = [&]() {
+        const int sub = (int)(issued & 3);
+        issue((int)(issued % kPipeStages), sub, rid_cur, rq_cur);
+        issued++;
+        if ((issued & 3) == 0) {  // block used up: the prefetched one becomes current
+            rid_cur = rid_nxt;
+            rq_cur = rq_nxt;
+            fetch_block(issued / 4 + 1, rid_nxt, rq_nxt);
+        }
+    };
+    for (int st = 0; st < kPipeStages - 1; st++) issue_next();
+    int stage = 0;
+    for (long long g = g_first; g < g_last; g++) {
+        issue_next();  // keeps kPipeStages - 1 groups in flight behind the one computed below
+        cp_async_wait<kPipeStages - 1>();  // the oldest group has landed
+        __syncwarp();
+        const uint8_t *rows = ring + (size_t)stage * kSq8RowsPerWarp * dim;
+        const uint32_t mq = meta[stage * kSq8RowsPerWarp + (lane & 7)];  // query of row lane & 7
+        const uint32_t q0 = __shfl_sync(0xffffffffu, mq, 0);
+        float acc[kSq8RowsPerWarp];
+        if (q0 != 0xffffffffu && __all_sync(0xffffffffu, mq == q0)) {
+            // the usual case, eight valid rows of one query: straight-line code, eight
+            // independent sums for the scheduler to interleave
+            if (q0 != cur_q) load_query(q0);
+#pragma unroll
+            for (int t = 0; t < kSq8RowsPerWarp; t++) acc[t] = row_sum(rows + (size_t)t * dim);
+        } else {
+#pragma unroll
+            for (int t = 0; t < kSq8RowsPerWarp; t++) {
+                acc[t] = 0.f;
+                const uint32_t q = __shfl_sync(0xffffffffu, mq, t);
+                if (q == 0xffffffffu) continue;  // warp-uniform
+                if (q != cur_q) load_query(q);
+                acc[t] = row_sum(rows + (size_t)t * dim);
+            }
+        }
+        const float v = warp_sum8(acc, lane);  // total of row lane >> 2
+        const bool good = __shfl_sync(0xffffffffu, mq, lane >> 2) != 0xffffffffu;
+        if ((lane & 3) == 0) {
+            const long long i = g * kSq8RowsPerWarp + (lane >> 2);
+            if (i < total_n) out[i] = good ? (L2 ? v : -v) : __int_as_float(0x7fc00000);
+        }
+        __syncwarp();  // everyone is done with this stage before it is refilled
+        stage = (stage + 1) % kPipeStages;
+    }
+    cp_async_wait<0>();
 }
 
 // SQ8 rows, any dimension: one warp per row, byte loads.
@@ -388,10 +643,43 @@ int launch_distance(const diskann_cuda_table &t, const float *queries, int nq, c
             if (t.dim <= 128 * c && t.dim % (4 * c) == 0) wpl = c;
         const bool regs = wpl != 0 && ((reinterpret_cast<uintptr_t>(codes) & 3) == 0) &&
                           ((reinterpret_cast<uintptr_t>(queries) & 15) == 0);
-        if (regs) {
+        const bool pipe = (t.dim % 16 == 0) && t.dim <= kPipeMaxDim && total_n >= 4096 &&
+                          ((reinterpret_cast<uintptr_t>(codes) & 15) == 0) &&
+                          ((reinterpret_cast<uintptr_t>(queries) & 15) == 0);
+        if (pipe) {
+            const size_t smem = (size_t)kWarpsPerBlock * kPipeStages * (kSq8RowsPerWarp * t.dim + kSq8RowsPerWarp * 4);
             long long warps = ((long long)total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
             long long blocks = (warps + kWarpsPerBlock - 1) / kWarpsPerBlock;
-            const long long cap = (long long)sms * 2;  // one resident wave: the table in shared memory is built once per block
+            const long long cap = (long long)sms * 2;
+            if (blocks > cap) blocks = cap;
+            const unsigned g = (unsigned)blocks, b = kWarpsPerBlock * 32;
+#define ANN_LAUNCH_PIPE2(W, L2)                                                                                \
+    do {                                                                                                       \
+        ANN_CUDA_TRY(cudaFuncSetAttribute(batch_distance_sq8_pipe_kernel<W, L2>,                               \
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));            \
+        batch_distance_sq8_pipe_kernel<W, L2><<<g, b, smem, stream>>>(codes, t.num, t.dim, t.mins, t.scale,    \
+                                                                      queries, nq, ids, qmap, total_n, out);   \
+    } while (0)
+#define ANN_LAUNCH_PIPE(W)                \
+    do {                                  \
+        if (metric == 0)                  \
+            ANN_LAUNCH_PIPE2(W, true);    \
+        else                              \
+            ANN_LAUNCH_PIPE2(W, false);   \
+    } while (0)
+            // words per lane when lane l owns words l, l + 32, ...
+            switch ((t.dim / 4 + 31) / 32) {
+            case 1: ANN_LAUNCH_PIPE(1); break;
+            case 2: ANN_LAUNCH_PIPE(2); break;
+            case 3: ANN_LAUNCH_PIPE(3); break;
+            default: ANN_LAUNCH_PIPE(4); break;
+            }
+#undef ANN_LAUNCH_PIPE2
+#undef ANN_LAUNCH_PIPE
+        } else if (regs) {
+            long long warps = ((long long)total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
+            long long blocks = (warps + kWarpsPerBlock - 1) / kWarpsPerBlock;
+            const long long cap = (long long)sms * 4;
             if (blocks > cap) blocks = cap;
             const unsigned g = (unsigned)blocks, b = kWarpsPerBlock * 32;
             switch (wpl) {
