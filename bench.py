@@ -489,7 +489,7 @@ class BatchWorkload:
 
     def roofline(self, peaks, kernel_ms):
         return {"bound": "hbm", "achieved": None, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None,
-                "traffic": None, "kernel": "batch_distance_sq8_regs_kernel" if self.sq8 else "batch_distance_f32_kernel"}
+                "traffic": None, "kernel": "batch_distance_sq8_dp4a_kernel" if self.sq8 else "batch_distance_f32_kernel"}
 
     def verify(self, torch, D, I):
         assert torch.isfinite(D).all()

@@ -12,6 +12,7 @@
 
 #include <cstdlib>
 #include <memory>
+#include <type_traits>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -325,22 +326,37 @@ batch_distance_sq8_regs_kernel(const uint8_t *__restrict__ codes, size_t num, in
     }
 }
 
-// SQ8 rows with dim % 16 == 0 and dim <= 512, pipelined through shared memory.
-// The register kernel above is bound by latency: a warp must read ids, then (dependent)
-// the code rows, then compute, and has room for only eight rows in flight.  Here each warp
-// runs a four-stage cp.async ring of eight rows per stage (ids are read 32 rows at a time,
-// one block ahead; rows one to three groups ahead), so ~9 KB of codes per warp are always
-// in flight while it computes on the oldest stage.
+// SQ8 rows with dim % 16 == 0 and dim <= 512: integer dot products, pipelined through
+// shared memory.
 //
-// With the latency hidden the kernel is bound by instruction issue, so the arithmetic is
-// packed: lane l owns the 4-code words l, l + 32, ... of every row (conflict-free 4-byte
-// shared loads, 16-byte query loads), two codes at a time go through the two-wide fp32
-// instructions (add.f32x2 / fma.f32x2), 2.5 instructions per code instead of 4, and the
-// metric is a template parameter.  Per code the operations and their roundings are those
-// of the register kernel; only the order of the final sum differs (two partial sums per
-// lane).
+// Latency.  The register kernel above must read ids, then (dependent) the code rows, then
+// compute, with room for only eight rows in flight per warp.  Here each warp runs a
+// four-stage cp.async ring of eight rows per stage (ids are read 32 rows at a time, one
+// block ahead; rows one to three groups ahead), so ~9 KB of codes per warp are always in
+// flight while it computes on the oldest stage.
+//
+// Arithmetic.  With the latency hidden, converting every code to fp32 and doing two fused
+// multiply-adds on it (>= 4 instructions per code) is what bounds the kernel, not HBM.  The
+// distance is therefore split into the part that depends on the codes linearly and parts
+// that do not depend on the query:
+//     L2:  sum_d ((q_d - min_d) - s_d c_d)^2 = A - 2 sum_d w_d c_d + N_r,   w_d = (q_d - min_d) s_d
+//     IP:  sum_d q_d (min_d + s_d c_d)       = sum_d q_d min_d + sum_d w_d c_d,  w_d = q_d s_d
+// with s_d = scale_d / 255, A = sum_d (q_d - min_d)^2 once per query and N_r = sum_d (s_d c_d)^2
+// once per row, computed when the table is registered.  sum_d w_d c_d runs on the integer
+// dot-product instruction (dp4a, four codes per instruction): the weights of one query are
+// put on a common power-of-two scale as 23-bit signed integers and cut into three byte limbs
+// (two unsigned, the top one signed), so three dp4a per 4-code word give three exact integer
+// sums, 0.75 instructions per code.  The sums are accumulated straight into the mantissa of
+// 2^23 (resp. 2^23 + 2^22), which makes them floats without a conversion instruction.
+//
+// Accuracy.  The integer sums are exact; the weights carry 2^-23 of the largest weight of the
+// query, which is what fp32 accumulation loses as well.  What the split adds is cancellation
+// in A - 2 cross + N_r when a row almost coincides with the query, so a row whose distance
+// comes out below 2% of A + N_r is recomputed in the direct form (q - min - s c)^2 from the
+// codes still in shared memory.
 constexpr int kPipeStages = 4;
 constexpr int kPipeMaxDim = 512;
+constexpr float kSq8ExactBelow = 0.02f;  // redo a row directly if dist < this * (A + N_r)
 
 __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
@@ -350,79 +366,103 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
-
-// two fp32 values in one 64-bit register, for the packed instructions of sm_100
-__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ uint64_t f2_pack_bits(uint32_t lo, uint32_t hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
-    return r;
-}
-__device__ __forceinline__ float f2_sum(uint64_t v) {
-    float lo, hi;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-    return lo + hi;
-}
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+// d = c + sum of four products of the bytes of a (unsigned) and of b (unsigned / signed)
+__device__ __forceinline__ uint32_t dp4a_uu(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+__device__ __forceinline__ int32_t dp4a_us(uint32_t a, uint32_t b, int32_t c) {
+    int32_t d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
 
-template <int WPL, bool L2>
+// N_r = sum_d (s_d c_d)^2 of every row, for the kernel below
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-batch_distance_sq8_pipe_kernel(const uint8_t *__restrict__ codes, size_t num, int dim,
+sq8_row_norms_kernel(const uint8_t *__restrict__ codes, size_t num, int dim, const float *__restrict__ scale,
+                     float *__restrict__ norms) {
+    const int lane = threadIdx.x & 31;
+    const int words = dim >> 2;  // dim is a multiple of 16
+    for (size_t r = (size_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); r < num;
+         r += (size_t)gridDim.x * kWarpsPerBlock) {
+        const uint32_t *row = reinterpret_cast<const uint32_t *>(codes + r * (size_t)dim);
+        float acc = 0.f;
+        for (int wi = lane; wi < words; wi += 32) {
+            const uint32_t w = __ldg(row + wi);
+            const float4 sv = __ldg(reinterpret_cast<const float4 *>(scale) + wi);
+            const float v0 = (float)(w & 255u) * __fdiv_rn(sv.x, 255.0f);
+            const float v1 = (float)((w >> 8) & 255u) * __fdiv_rn(sv.y, 255.0f);
+            const float v2 = (float)((w >> 16) & 255u) * __fdiv_rn(sv.z, 255.0f);
+            const float v3 = (float)(w >> 24) * __fdiv_rn(sv.w, 255.0f);
+            acc = fmaf(v0, v0, acc);
+            acc = fmaf(v1, v1, acc);
+            acc = fmaf(v2, v2, acc);
+            acc = fmaf(v3, v3, acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) norms[r] = acc;
+    }
+}
+
+// WPL: 4-code words per lane (lane l owns words l, l + 32, ...); FULL: dim == 128 * WPL, so
+// every lane owns WPL words and no load needs a predicate.
+template <int WPL, bool L2, bool FULL>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+batch_distance_sq8_dp4a_kernel(const uint8_t *__restrict__ codes, const float *__restrict__ norms, size_t num, int dim,
                                const float *__restrict__ mins, const float *__restrict__ scale,
                                const float *__restrict__ queries, int nq, const uint32_t *__restrict__ ids,
                                const uint32_t *__restrict__ qmap, int total_n, float *__restrict__ out) {
+    static_assert(kPipeStages == 4 && kSq8RowsPerWarp == 8, "one id block of 32 rows fills the four stages");
     extern __shared__ __align__(16) uint8_t sq8_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // per warp: kPipeStages x (8 rows x dim bytes), then kPipeStages x 8 query numbers
-    uint8_t *ring = sq8_smem + (size_t)warp * kPipeStages * (kSq8RowsPerWarp * dim + kSq8RowsPerWarp * 4);
-    uint32_t *meta = reinterpret_cast<uint32_t *>(ring + (size_t)kPipeStages * kSq8RowsPerWarp * dim);
+    constexpr uint32_t kNone = 0xffffffffu;
+    constexpr uint32_t kFull = 0xffffffffu;
+    // A warp takes a CONTIGUOUS run of row groups, so that consecutive groups mostly share
+    // their query and its registers are rebuilt once per query, not once per group.
+    const int warps_total = (int)gridDim.x * kWarpsPerBlock;
+    const int n_groups = (total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
+    const int per_warp = (n_groups + warps_total - 1) / warps_total;
+    const int g_first = ((int)blockIdx.x * kWarpsPerBlock + warp) * per_warp;
+    if (g_first >= n_groups) return;  // whole warp; the kernel has no block-wide barrier
+    const int n_my = min(per_warp, n_groups - g_first);
+    const int row_first = g_first * kSq8RowsPerWarp;
+    const int row_end = min(total_n, row_first + n_my * kSq8RowsPerWarp);
+
+    const int stage_bytes = kSq8RowsPerWarp * dim;
+    uint8_t *ring = sq8_smem + (size_t)warp * kPipeStages * stage_bytes;  // this warp's four stages
     const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
-    const long long warp_global = (long long)blockIdx.x * kWarpsPerBlock + warp;
-    const long long warps_total = (long long)gridDim.x * kWarpsPerBlock;
-    const long long n_groups = ((long long)total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
-    const int words = dim >> 2;   // 4-code words per row
-    const int chunks = dim >> 4;  // 16-byte pieces per row
-    bool act[WPL];                // does word lane + 32 j exist?
-    uint64_t ns2[WPL * 2];        // L2: -(scale / 255) of my dimensions, in pairs
-    uint64_t qa2[WPL * 2];        // L2: q - min;  IP: q * scale / 255
-    float sc[L2 ? 1 : WPL * 4];   // IP: scale / 255, needed when the query changes
-    float qmin = 0.f;             // IP: sum over my dimensions of q * min
+    const int words = dim >> 2;            // 4-code words per row
+    const bool copier = lane < (dim >> 4);  // lane l copies 16-byte piece l of every row
+    const uint8_t *copy_src = codes + lane * 16;
+    const uint32_t copy_dst = ring_s + lane * 16;
+
+    bool act[WPL];       // does word lane + 32 j exist?
+    float sc[WPL * 4];   // scale / 255 of my dimensions
+    uint32_t wl[WPL], wm[WPL], wh[WPL];  // byte limbs of my weights, four dimensions per word
+    float back = 0.f;    // value of one unit of the integer weights
+    float qconst = 0.f;  // L2: A = sum (q - min)^2;  IP: sum q * min
 #pragma unroll
     for (int j = 0; j < WPL; j++) {
-        act[j] = lane + 32 * j < words;
+        act[j] = FULL || lane + 32 * j < words;
         float4 sv = make_float4(0.f, 0.f, 0.f, 0.f);
         if (act[j]) sv = __ldg(reinterpret_cast<const float4 *>(scale) + lane + 32 * j);
-        sv.x = __fdiv_rn(sv.x, 255.0f);
-        sv.y = __fdiv_rn(sv.y, 255.0f);
-        sv.z = __fdiv_rn(sv.z, 255.0f);
-        sv.w = __fdiv_rn(sv.w, 255.0f);
-        ns2[2 * j] = f2_pack(-sv.x, -sv.y);
-        ns2[2 * j + 1] = f2_pack(-sv.z, -sv.w);
-        qa2[2 * j] = qa2[2 * j + 1] = 0ull;
-        if (!L2) {
-            sc[4 * j] = sv.x;
-            sc[4 * j + 1] = sv.y;
-            sc[4 * j + 2] = sv.z;
-            sc[4 * j + 3] = sv.w;
-        }
+        sc[4 * j] = __fdiv_rn(sv.x, 255.0f);
+        sc[4 * j + 1] = __fdiv_rn(sv.y, 255.0f);
+        sc[4 * j + 2] = __fdiv_rn(sv.z, 255.0f);
+        sc[4 * j + 3] = __fdiv_rn(sv.w, 255.0f);
+        wl[j] = wm[j] = wh[j] = 0u;
     }
-    uint32_t cur_q = 0xffffffffu;
+    uint32_t cur_q = kNone;
     auto load_query = [&](uint32_t qi) {
         cur_q = qi;
-        qmin = 0.f;
+        float w[WPL * 4];
+        float part = 0.f, wmax = 0.f;
 #pragma unroll
         for (int j = 0; j < WPL; j++) {
             float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), mv = qv;
@@ -430,126 +470,184 @@ batch_distance_sq8_pipe_kernel(const uint8_t *__restrict__ codes, size_t num, in
                 qv = __ldg(reinterpret_cast<const float4 *>(queries + (size_t)qi * dim) + lane + 32 * j);
                 mv = __ldg(reinterpret_cast<const float4 *>(mins) + lane + 32 * j);
             }
-            if (L2) {
-                qa2[2 * j] = f2_pack(qv.x - mv.x, qv.y - mv.y);
-                qa2[2 * j + 1] = f2_pack(qv.z - mv.z, qv.w - mv.w);
-            } else {
-                qa2[2 * j] = f2_pack(qv.x * sc[4 * j], qv.y * sc[4 * j + 1]);
-                qa2[2 * j + 1] = f2_pack(qv.z * sc[4 * j + 2], qv.w * sc[4 * j + 3]);
-                qmin = fmaf(qv.x, mv.x, qmin);
-                qmin = fmaf(qv.y, mv.y, qmin);
-                qmin = fmaf(qv.z, mv.z, qmin);
-                qmin = fmaf(qv.w, mv.w, qmin);
+            const float qs[4] = {qv.x, qv.y, qv.z, qv.w}, ms[4] = {mv.x, mv.y, mv.z, mv.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                if (L2) {
+                    const float qa = qs[e] - ms[e];
+                    w[4 * j + e] = qa * sc[4 * j + e];
+                    part = fmaf(qa, qa, part);
+                } else {
+                    w[4 * j + e] = qs[e] * sc[4 * j + e];
+                    part = fmaf(qs[e], ms[e], part);
+                }
+                wmax = fmaxf(wmax, fabsf(w[4 * j + e]));
             }
         }
+        qconst = warp_sum(part);
+        wmax = warp_max(wmax);
+        // common scale: the power of two above the largest weight maps to 2^22
+        float inv = 0.f;
+        back = 0.f;
+        if (wmax > 1e-30f && wmax < 1e30f) {
+            const float top = __int_as_float((__float_as_int(wmax) & 0x7f800000) + 0x00800000);
+            inv = 4194304.0f / top;
+            back = top / 4194304.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < WPL; j++) {
+            uint32_t l = 0, m = 0, h = 0;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int v = __float2int_rn(w[4 * j + e] * inv);  // |v| <= 2^22
+                l |= ((uint32_t)v & 255u) << (8 * e);
+                m |= (((uint32_t)v >> 8) & 255u) << (8 * e);
+                h |= (((uint32_t)v >> 16) & 255u) << (8 * e);  // signed byte: v >> 16 in [-64, 64]
+            }
+            wl[j] = l;
+            wm[j] = m;
+            wh[j] = h;
+        }
     };
-    const uint64_t neg_magic = f2_pack(-8388608.0f, -8388608.0f);
-    // this lane's share of one row: sum of ((q - min) - c * s)^2   or of   c * (q * s)
-    auto row_sum = [&](const uint8_t *row) -> float {
-        uint64_t acc = 0ull;
+    // this lane's share of sum_d w_d c_d of one row, in integer weight units; `row` already
+    // points at this lane's first word
+    auto row_dot = [&](const uint32_t *row) -> float {
+        uint32_t al = 0x4B000000u, am = 0x4B000000u;  // the float 2^23: sums land in its mantissa
+        int32_t ah = 0x4B400000;                      // 2^23 + 2^22: room for a signed sum
 #pragma unroll
         for (int j = 0; j < WPL; j++) {
             uint32_t w = 0;
-            if (act[j]) w = reinterpret_cast<const uint32_t *>(row)[lane + 32 * j];
-            // a byte permute drops each code into the mantissa of 2^23: the float 2^23 + code
-            const uint64_t c01 = f2_add(f2_pack_bits(__byte_perm(w, 0x4B000000u, 0x7540u),
-                                                     __byte_perm(w, 0x4B000000u, 0x7541u)), neg_magic);
-            const uint64_t c23 = f2_add(f2_pack_bits(__byte_perm(w, 0x4B000000u, 0x7542u),
-                                                     __byte_perm(w, 0x4B000000u, 0x7543u)), neg_magic);
-            if (L2) {
-                const uint64_t d01 = f2_fma(c01, ns2[2 * j], qa2[2 * j]);
-                const uint64_t d23 = f2_fma(c23, ns2[2 * j + 1], qa2[2 * j + 1]);
-                acc = f2_fma(d01, d01, acc);
-                acc = f2_fma(d23, d23, acc);
-            } else {
-                acc = f2_fma(c01, qa2[2 * j], acc);
-                acc = f2_fma(c23, qa2[2 * j + 1], acc);
+            if (FULL || act[j]) w = row[32 * j];
+            al = dp4a_uu(w, wl[j], al);
+            am = dp4a_uu(w, wm[j], am);
+            ah = dp4a_us(w, wh[j], ah);
+        }
+        const float fl = __uint_as_float(al) - 8388608.0f;
+        const float fm = __uint_as_float(am) - 8388608.0f;
+        const float fh = __int_as_float(ah) - 12582912.0f;
+        return fmaf(fh, 65536.0f, fmaf(fm, 256.0f, fl));
+    };
+    // this lane's share of the L2 distance of one row in the direct form (rare path)
+    auto row_exact = [&](const uint32_t *row, uint32_t qi) -> float {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < WPL; j++) {
+            if (!act[j]) continue;
+            const uint32_t w = row[32 * j];
+            const float4 qv = __ldg(reinterpret_cast<const float4 *>(queries + (size_t)qi * dim) + lane + 32 * j);
+            const float4 mv = __ldg(reinterpret_cast<const float4 *>(mins) + lane + 32 * j);
+            const float qs[4] = {qv.x, qv.y, qv.z, qv.w}, ms[4] = {mv.x, mv.y, mv.z, mv.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float c = (float)((w >> (8 * e)) & 255u);
+                const float diff = fmaf(-c, sc[4 * j + e], qs[e] - ms[e]);
+                acc = fmaf(diff, diff, acc);
             }
         }
-        return f2_sum(acc) + (L2 ? 0.f : qmin);
+        return acc;
     };
-    // A warp takes a CONTIGUOUS run of groups, so that consecutive groups mostly share their
-    // query and its registers are rebuilt once per query, not once per group.
-    const long long per_warp = (n_groups + warps_total - 1) / warps_total;
-    const long long g_first = warp_global * per_warp;
-    const long long g_last = g_first + per_warp < n_groups ? g_first + per_warp : n_groups;
-    // ids and queries are read 32 rows (four groups) at a time, one coalesced load per block,
-    // one block ahead of the copies that need them: lane L holds row 32 b + L of the run.
-    auto fetch_block = [&](long long blk, uint32_t &rid, uint32_t &rq) {
-        rid = 0xffffffffu;
-        rq = 0xffffffffu;
-        const long long g = g_first + blk * 4 + (lane >> 3);
-        const long long i = g * kSq8RowsPerWarp + (lane & 7);
-        if (g < g_last && i < total_n) {
+    // distance from the reduced integer dot product `v` and the row's N_r
+    auto finish = [&](float v, float nrm) -> float {
+        return L2 ? fmaf(-2.0f * back, v, qconst + nrm) : -fmaf(back, v, qconst);
+    };
+
+    // Row ids, query numbers and row norms are read 32 rows (four groups, one per ring stage)
+    // at a time, one block ahead of the copies that need them: lane L holds row 32 b + L of
+    // the run; an unusable row (outside the run, id or query out of range) is kNone.
+    auto fetch_block = [&](int blk, uint32_t &rid, uint32_t &rq, float &nrm) {
+        rid = kNone;
+        rq = kNone;
+        nrm = 0.f;
+        const int i = row_first + blk * 32 + lane;
+        if (i < row_end) {
             const uint32_t r = ids ? ids[i] : (uint32_t)i;
             const uint32_t q = qmap ? qmap[i] : 0u;
             if ((size_t)r < num && q < (uint32_t)nq) {
                 rid = r;
                 rq = q;
+                if (L2) nrm = __ldg(norms + r);
             }
         }
     };
-    // starts the copies of group `sub` (0..3) of an id block into ring stage `st`
-    auto issue = [&](int st, int sub, uint32_t rid, uint32_t rq) {
-        const uint32_t myq = __shfl_sync(0xffffffffu, rq, sub * 8 + (lane & 7));
-        if (lane < kSq8RowsPerWarp) meta[st * kSq8RowsPerWarp + lane] = myq;
+    // starts the copies of group `sub` (0..3) of an id block into ring stage `sub`; always commits
+    auto issue = [&](int sub, uint32_t rid) {
+        const uint32_t dst = copy_dst + (uint32_t)(sub * stage_bytes);
 #pragma unroll
         for (int t = 0; t < kSq8RowsPerWarp; t++) {
-            const uint32_t r = __shfl_sync(0xffffffffu, rid, sub * 8 + t);
-            if (r != 0xffffffffu && lane < chunks)
-                cp_async16(ring_s + (uint32_t)((st * kSq8RowsPerWarp + t) * dim + lane * 16),
-                           codes + (size_t)r * dim + lane * 16);
+            const uint32_t r = __shfl_sync(kFull, rid, sub * 8 + t);
+            if (r != kNone && copier) cp_async16(dst + (uint32_t)(t * dim), copy_src + (size_t)r * (uint32_t)dim);
         }
         cp_async_commit();
     };
-    uint32_t rid_cur, rq_cur, rid_nxt, rq_nxt;
-    fetch_block(0, rid_cur, rq_cur);
-    fetch_block(1, rid_nxt, rq_nxt);
-    long long issued = 0;  // groups whose copies have been started (relative to g_first)
-    auto issue_next = [&]() {
-        const int sub = (int)(issued & 3);
-        issue((int)(issued % kPipeStages), sub, rid_cur, rq_cur);
-        issued++;
-        if ((issued & 3) == 0) {  // block used up: the prefetched one becomes current
-            rid_cur = rid_nxt;
-            rq_cur = rq_nxt;
-            fetch_block(issued / 4 + 1, rid_nxt, rq_nxt);
-        }
-    };
-    for (int st = 0; st < kPipeStages - 1; st++) issue_next();
-    int stage = 0;
-    for (long long g = g_first; g < g_last; g++) {
-        issue_next();  // keeps kPipeStages - 1 groups in flight behind the one computed below
-        cp_async_wait<kPipeStages - 1>();  // the oldest group has landed
-        __syncwarp();
-        const uint8_t *rows = ring + (size_t)stage * kSq8RowsPerWarp * dim;
-        const uint32_t mq = meta[stage * kSq8RowsPerWarp + (lane & 7)];  // query of row lane & 7
-        const uint32_t q0 = __shfl_sync(0xffffffffu, mq, 0);
-        float acc[kSq8RowsPerWarp];
-        if (q0 != 0xffffffffu && __all_sync(0xffffffffu, mq == q0)) {
+    // distances of group `sub` of the current id block; `row0` is the index of its first row
+    auto compute = [&](int sub, int row0, uint32_t rq, float nrm_reg) {
+        const uint32_t *rows = reinterpret_cast<const uint32_t *>(ring + sub * stage_bytes) + lane;
+        const uint32_t q0 = __shfl_sync(kFull, rq, sub * 8);
+        const uint32_t same = __ballot_sync(kFull, rq == q0) >> (sub * 8);
+        if (q0 != kNone && (same & 0xffu) == 0xffu) {
             // the usual case, eight valid rows of one query: straight-line code, eight
-            // independent sums for the scheduler to interleave
-            if (q0 != cur_q) load_query(q0);
+            // independent dot products for the scheduler to interleave
+            float acc[kSq8RowsPerWarp];  // q0's registers were built before the wait
 #pragma unroll
-            for (int t = 0; t < kSq8RowsPerWarp; t++) acc[t] = row_sum(rows + (size_t)t * dim);
+            for (int t = 0; t < kSq8RowsPerWarp; t++) acc[t] = row_dot(rows + t * words);
+            const float v = warp_sum8(acc, lane);  // total of row lane >> 2
+            const float nrm = __shfl_sync(kFull, nrm_reg, sub * 8 + (lane >> 2));
+            float dist = finish(v, nrm);
+            if (L2) {
+                uint32_t redo = __ballot_sync(kFull, (lane & 3) == 0 && !(dist >= kSq8ExactBelow * (qconst + nrm)));
+                while (redo) {  // warp-uniform, rare
+                    const int owner = __ffs(redo) - 1;
+                    redo &= redo - 1;
+                    const float ex = warp_sum(row_exact(rows + (owner >> 2) * words, q0));
+                    if (lane == owner) dist = ex;
+                }
+            }
+            if ((lane & 3) == 0) out[row0 + (lane >> 2)] = dist;
         } else {
-#pragma unroll
+#pragma unroll 1
             for (int t = 0; t < kSq8RowsPerWarp; t++) {
-                acc[t] = 0.f;
-                const uint32_t q = __shfl_sync(0xffffffffu, mq, t);
-                if (q == 0xffffffffu) continue;  // warp-uniform
-                if (q != cur_q) load_query(q);
-                acc[t] = row_sum(rows + (size_t)t * dim);
+                const uint32_t q = __shfl_sync(kFull, rq, sub * 8 + t);
+                const float nrm = __shfl_sync(kFull, nrm_reg, sub * 8 + t);
+                float dist = __int_as_float(0x7fc00000);
+                if (q != kNone) {  // warp-uniform
+                    if (q != cur_q) load_query(q);
+                    dist = finish(warp_sum(row_dot(rows + t * words)), nrm);
+                    if (L2 && !(dist >= kSq8ExactBelow * (qconst + nrm)))
+                        dist = warp_sum(row_exact(rows + t * words, q));
+                }
+                if (lane == 0 && row0 + t < total_n) out[row0 + t] = dist;
             }
         }
-        const float v = warp_sum8(acc, lane);  // total of row lane >> 2
-        const bool good = __shfl_sync(0xffffffffu, mq, lane >> 2) != 0xffffffffu;
-        if ((lane & 3) == 0) {
-            const long long i = g * kSq8RowsPerWarp + (lane >> 2);
-            if (i < total_n) out[i] = good ? (L2 ? v : -v) : __int_as_float(0x7fc00000);
+    };
+    uint32_t rid_a, rq_a, rid_b, rq_b;  // id blocks b and b + 1
+    float nrm_a, nrm_b;
+    fetch_block(0, rid_a, rq_a, nrm_a);
+    fetch_block(1, rid_b, rq_b, nrm_b);
+    issue(0, rid_a);
+    issue(1, rid_a);
+    issue(2, rid_a);
+    // One loop body for all four stages (the stage is a run-time value): the body is large,
+    // and four copies of it thrash the instruction cache for nothing.
+#pragma unroll 1
+    for (int n = 0; n < n_my; n++) {
+        const int sub = n & 3;
+        // start the copies of the group three ahead (stage (n + 3) & 3, freed by the last
+        // step), then wait for this step's own group
+        issue((sub + 3) & 3, sub == 0 ? rid_a : rid_b);
+        {   // a new query's registers are built while this step's rows are still in flight
+            const uint32_t q_next = __shfl_sync(kFull, rq_a, sub * 8);
+            if (q_next != kNone && q_next != cur_q) load_query(q_next);
         }
+        cp_async_wait<3>();
+        __syncwarp();
+        compute(sub, row_first + n * kSq8RowsPerWarp, rq_a, nrm_a);
         __syncwarp();  // everyone is done with this stage before it is refilled
-        stage = (stage + 1) % kPipeStages;
+        if (sub == 3) {
+            rid_a = rid_b;
+            rq_a = rq_b;
+            nrm_a = nrm_b;
+            fetch_block((n >> 2) + 2, rid_b, rq_b, nrm_b);
+        }
     }
     cp_async_wait<0>();
 }
@@ -601,6 +699,7 @@ struct diskann_cuda_table {
     void *rows = nullptr;  // float* or uint8_t*
     float *mins = nullptr;
     float *scale = nullptr;
+    float *norms = nullptr;  // SQ8 with dim % 16 == 0, dim <= 512: sum_d (scale_d / 255 * code_d)^2 per row
 };
 
 namespace {
@@ -643,29 +742,33 @@ int launch_distance(const diskann_cuda_table &t, const float *queries, int nq, c
             if (t.dim <= 128 * c && t.dim % (4 * c) == 0) wpl = c;
         const bool regs = wpl != 0 && ((reinterpret_cast<uintptr_t>(codes) & 3) == 0) &&
                           ((reinterpret_cast<uintptr_t>(queries) & 15) == 0);
-        const bool pipe = (t.dim % 16 == 0) && t.dim <= kPipeMaxDim && total_n >= 4096 &&
+        const bool pipe = t.norms && (t.dim % 16 == 0) && t.dim <= kPipeMaxDim && total_n >= 4096 &&
                           ((reinterpret_cast<uintptr_t>(codes) & 15) == 0) &&
                           ((reinterpret_cast<uintptr_t>(queries) & 15) == 0);
         if (pipe) {
-            const size_t smem = (size_t)kWarpsPerBlock * kPipeStages * (kSq8RowsPerWarp * t.dim + kSq8RowsPerWarp * 4);
+            const size_t smem = (size_t)kWarpsPerBlock * kPipeStages * kSq8RowsPerWarp * t.dim;
             long long warps = ((long long)total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
             long long blocks = (warps + kWarpsPerBlock - 1) / kWarpsPerBlock;
             const long long cap = (long long)sms * 2;
             if (blocks > cap) blocks = cap;
             const unsigned g = (unsigned)blocks, b = kWarpsPerBlock * 32;
-#define ANN_LAUNCH_PIPE2(W, L2)                                                                                \
+#define ANN_LAUNCH_PIPE3(W, L2, FULL)                                                                          \
     do {                                                                                                       \
-        ANN_CUDA_TRY(cudaFuncSetAttribute(batch_distance_sq8_pipe_kernel<W, L2>,                               \
+        ANN_CUDA_TRY(cudaFuncSetAttribute(batch_distance_sq8_dp4a_kernel<W, L2, FULL>,                         \
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));            \
-        batch_distance_sq8_pipe_kernel<W, L2><<<g, b, smem, stream>>>(codes, t.num, t.dim, t.mins, t.scale,    \
-                                                                      queries, nq, ids, qmap, total_n, out);   \
+        batch_distance_sq8_dp4a_kernel<W, L2, FULL><<<g, b, smem, stream>>>(                                   \
+            codes, t.norms, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, out);              \
     } while (0)
-#define ANN_LAUNCH_PIPE(W)                \
-    do {                                  \
-        if (metric == 0)                  \
-            ANN_LAUNCH_PIPE2(W, true);    \
-        else                              \
-            ANN_LAUNCH_PIPE2(W, false);   \
+#define ANN_LAUNCH_PIPE(W)                                         \
+    do {                                                           \
+        const bool full = t.dim == 128 * (W);                      \
+        if (metric == 0) {                                         \
+            if (full) ANN_LAUNCH_PIPE3(W, true, true);             \
+            else ANN_LAUNCH_PIPE3(W, true, false);                 \
+        } else {                                                   \
+            if (full) ANN_LAUNCH_PIPE3(W, false, true);            \
+            else ANN_LAUNCH_PIPE3(W, false, false);                \
+        }                                                          \
     } while (0)
             // words per lane when lane l owns words l, l + 32, ...
             switch ((t.dim / 4 + 31) / 32) {
@@ -674,7 +777,7 @@ int launch_distance(const diskann_cuda_table &t, const float *queries, int nq, c
             case 3: ANN_LAUNCH_PIPE(3); break;
             default: ANN_LAUNCH_PIPE(4); break;
             }
-#undef ANN_LAUNCH_PIPE2
+#undef ANN_LAUNCH_PIPE3
 #undef ANN_LAUNCH_PIPE
         } else if (regs) {
             long long warps = ((long long)total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
@@ -867,6 +970,26 @@ int make_table(int device, const void *rows, bool rows_on_device, const float *m
             diskann_cuda_unregister(t.release());
             return set_error("SQ8 parameter upload failed");
         }
+        if (dim % 16 == 0 && dim <= kPipeMaxDim && (reinterpret_cast<uintptr_t>(t->rows) & 15) == 0) {
+            // per-row constants of the integer dot-product kernel, 4 bytes per row
+            if (cudaMalloc(&t->norms, num * sizeof(float)) != cudaSuccess) {
+                cudaGetLastError();
+                diskann_cuda_unregister(t.release());
+                return set_error("out of device memory for the SQ8 row norms");
+            }
+            size_t blocks = (num + kWarpsPerBlock - 1) / kWarpsPerBlock;
+            const size_t cap = (size_t)sm_count(device) * 32;
+            if (blocks > cap) blocks = cap;
+            sq8_row_norms_kernel<<<(unsigned)blocks, kWarpsPerBlock * 32>>>(static_cast<const uint8_t *>(t->rows), num,
+                                                                           dim, t->scale, t->norms);
+            count_launch();
+            cudaError_t e = cudaGetLastError();
+            if (e == cudaSuccess) e = cudaDeviceSynchronize();
+            if (e != cudaSuccess) {
+                diskann_cuda_unregister(t.release());
+                return set_error("SQ8 row norms failed: %s", cudaGetErrorString(e));
+            }
+        }
     }
     *out = t.release();
     return 0;
@@ -920,6 +1043,7 @@ int diskann_cuda_unregister(diskann_cuda_table *t) {
     if (t->owns_rows && t->rows) cudaFree(t->rows);
     if (t->mins) cudaFree(t->mins);
     if (t->scale) cudaFree(t->scale);
+    if (t->norms) cudaFree(t->norms);
     delete t;
     return 0;
 }

@@ -140,6 +140,36 @@ def test_by_id_sq8_table(pkg, oracle, dim, metric):
     t.close()
 
 
+@pytest.mark.parametrize("dim", [384, 256, 80])
+def test_sq8_rows_that_almost_coincide_with_the_query(pkg, oracle, dim):
+    """L2 distances far below the norms of their operands (the query is a decoded row plus a
+    little noise): a kernel that expands (q - x)^2 into norms and a cross term must not lose
+    them to cancellation."""
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal((20000, dim)).astype(np.float32)
+    mins, scale = oracle.sq8_train(x)
+    codes = oracle.sq8_encode(x, mins, scale)
+    t = pkg.diskann_bridge.DeviceTable.sq8_from_host(codes, mins, scale)
+    nq, per = 64, 128
+    anchor = rng.integers(0, len(x), nq).astype(np.uint32)
+    noise = np.repeat(np.array([0.0, 1e-4, 1e-3, 1e-2], np.float32), nq // 4)[:, None]
+    q = (oracle.sq8_decode(codes[anchor], mins, scale) +
+         noise * rng.standard_normal((nq, dim))).astype(np.float32)
+    ids = rng.integers(0, len(x), nq * per).astype(np.uint32)
+    ids[::per] = anchor          # first candidate of every query: the row it was made from
+    ids[1::per] = anchor         # and once more
+    qm = np.repeat(np.arange(nq, dtype=np.uint32), per)
+    out = t.batch_distances_by_id(q, ids, qm, 0)
+    want = oracle.sq8_batch_distances_by_id(codes, mins, scale, q, ids, qm, 0, exact=True)
+    near = want < 1e-2 * want.max()
+    assert near.sum() >= nq
+    err = np.abs(out - want)
+    # the decoded value is formed as code * (scale / 255) + min, an ulp or two off the oracle's
+    # (code / 255) * scale + min: an absolute term of that size on top of the relative bound
+    assert (err <= 1e-4 * np.abs(want) + 1e-10 * dim).all(), (err / np.maximum(want, 1e-10 * dim)).max()
+    t.close()
+
+
 def test_sq8_nearest_neighbour_known_answer(pkg, oracle):
     import json, os
     with open(os.path.join(os.path.dirname(__file__), "golden", "reference_known_answers.json")) as f:
