@@ -226,8 +226,17 @@ class FlatWorkload:
         flops = 2.0 * self.nq * local_rows * self.d
         achieved = flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms and kernel_ms > 0 else None
         peak = peaks["bf16_tflops_sustained"] / 6.0
+        # DRAM traffic of one launch, from the ncu capture of this kernel on 400,000 rows
+        # (profiles/flat_tc_kernel__flat_ip_20m.md: 16.2-22.3 GB read + 0.47-0.49 GB written per
+        # launch with 4,096 queries of 768 dimensions), scaled by the rows and query tiles of this
+        # launch: every 128-query tile streams the shard once, L2 absorbs part of it.
+        traffic = None
+        if self.d == 768:
+            traffic = 19.7e9 * (local_rows / 400_000.0) * (((self.nq + 127) // 128) / 32.0)
         return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak if achieved else None, "traffic": None,
+                "frac": achieved / peak if achieved else None, "traffic": traffic,
+                "traffic_note": "bytes; ncu dram read+write of a 400,000-row launch scaled by rows and query tiles"
+                if traffic else "no capture for this shape",
                 "kernel": "flat_tc_kernel", "kernel_ms": kernel_ms,
                 "algorithmic_flops_per_launch": flops,
                 "peak_note": f"{peaks['_source']} bf16 sustained {peaks['bf16_tflops_sustained']} TFLOP/s / 2 (TF32 rate) "
@@ -254,8 +263,8 @@ class FlatWorkload:
 
     # ---- CPU baseline: blocked sgemm + heap on the host cores, on a bounded sample
     def cpu_sample(self, torch, device):
-        rows = min(self.n, 1_000_000 if self.n > 2_000_000 else self.n)
-        nq = min(self.nq, 256 if self.n > 2_000_000 else self.nq)
+        rows = min(self.n, 2_000_000 if self.n > 2_000_000 else self.n)
+        nq = min(self.nq, 1024 if self.n > 2_000_000 else self.nq)
         parts = []
         for c in range((rows + self.chunk - 1) // self.chunk):
             x = self.gen_chunk(c, device, torch)
@@ -274,6 +283,11 @@ class FlatWorkload:
         # queries/s over the FULL database: time scales with the number of rows scanned
         qps = nq / (dt * (self.n / rows))
         return qps, dt, f"{nq} queries x {rows:,} of {self.n:,} rows (blocked sgemm + heap), time scaled x{self.n / rows:g}"
+
+
+# DRAM read + write bytes of one grouped list-scan launch, keyed by (rows, queries, GPUs), from the
+# ncu capture summarised in profiles/flat_tc_kernel__ivf_1m.md
+IVF_SCAN_TRAFFIC = {}
 
 
 class IvfWorkload:
@@ -360,18 +374,23 @@ class IvfWorkload:
                 "l2_flush": "probed lists (3 GB of rows) exceed L2; no explicit flush"}
 
     def roofline(self, peaks, kernel_ms):
-        # list scan: algorithmic bytes = rows scanned x d x 4 (every query reads every row of its
-        # probed lists).  The kernel groups the queries of a list into tiles of 128 and reads each
-        # list row once per tile, so the algorithmic rate may exceed the HBM peak; the physical
-        # traffic of one launch is in profiles/.
-        alg_bytes = self.rows_scanned * self.d * 4 / max(self.world, 1)
-        achieved = alg_bytes / 1e9 / (kernel_ms * 1e-3) if kernel_ms and kernel_ms > 0 else None
-        return {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"] if achieved else None, "traffic": None,
+        # The list scan runs on the tensor cores: the queries probing a list are gathered into
+        # tiles of 128 and every (list, query tile) pair is one GEMM tile, so a list row is read
+        # once per tile, not once per query, and the kernel is bound by the MMA pipe like the flat
+        # search.  Useful work = one d-long dot product per (query, row of a probed list) pair.
+        pairs = self.rows_scanned / max(self.world, 1)
+        flops = 2.0 * pairs * self.d
+        achieved = flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms and kernel_ms > 0 else None
+        peak = peaks["bf16_tflops_sustained"] / 6.0
+        alg_bytes = pairs * self.d * 4
+        return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak if achieved else None, "traffic": IVF_SCAN_TRAFFIC.get((self.n, self.nq, self.world)),
                 "kernel": "flat_tc_kernel (grouped list scan)", "kernel_ms": kernel_ms,
-                "algorithmic_bytes_per_launch": alg_bytes,
-                "note": "algorithmic bytes (rows scanned x d x 4, per GPU) over the scan kernel's duration; "
-                        "queries probing one list share its rows through tensor-core tiles, so this can exceed 1"}
+                "algorithmic_flops_per_launch": flops,
+                "scan_bytes_if_read_per_query": alg_bytes,
+                "peak_note": f"{peaks['_source']} bf16 sustained {peaks['bf16_tflops_sustained']} TFLOP/s / 2 (TF32 rate) "
+                             "/ 3 (split-TF32); query tiles are padded to 128 rows per probed list, which the "
+                             "useful-flop count does not include"}
 
     def verify(self, torch, D, I):
         D = D.cpu().numpy()
@@ -381,7 +400,7 @@ class IvfWorkload:
 
     # ---- CPU baseline: per-query list scan with a heap, OpenMP over queries, same centroids and lists
     def cpu_sample(self, torch, device):
-        nq = min(self.nq, 400)
+        nq = min(self.nq, 4000)
         cent = self.index.get_centroids()
         xb = np.empty((self.n, self.d), np.float32)
         off = np.zeros(self.nlist + 1, np.int64)
@@ -488,8 +507,15 @@ class BatchWorkload:
                 "launch": "the K timed launches are replayed from one CUDA graph"}
 
     def roofline(self, peaks, kernel_ms):
+        # DRAM read + write of one launch at the default shapes, from the ncu captures summarised in
+        # profiles/batch_distance_f32_kernel__batch_c2.md and profiles/batch_distance_sq8_dp4a_kernel__sq8_c5.md
+        traffic = None
+        if self.sq8 and (self.nq, self.per, self.dim) == (1024, 128, 384):
+            traffic = 67.5e6
+        if not self.sq8 and (self.nq, self.per, self.dim) == (256, 128, 1536):
+            traffic = 204.5e6
         return {"bound": "hbm", "achieved": None, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None,
-                "traffic": None, "kernel": "batch_distance_sq8_dp4a_kernel" if self.sq8 else "batch_distance_f32_kernel"}
+                "traffic": traffic, "kernel": "batch_distance_sq8_dp4a_kernel" if self.sq8 else "batch_distance_f32_kernel"}
 
     def verify(self, torch, D, I):
         assert torch.isfinite(D).all()
@@ -504,7 +530,7 @@ class BatchWorkload:
     def cpu_run(self, oracle, sample):
         ids = self.ids_host[0]
         t0 = time.perf_counter()
-        reps = 5
+        reps = 300
         for _ in range(reps):
             if sample[0] == "sq8":
                 oracle.sq8_batch_distances_by_id(sample[1], sample[2], sample[3], self.q_host, ids, self.qmap_host, 0)
