@@ -222,7 +222,8 @@ __device__ __forceinline__ void st_global_if(bool p, int32_t *addr, int32_t v) {
 // Folds the queues of this warp's 32 rows into their k-lists in global memory.
 template <int KR>
 __device__ __noinline__ void flush_queues(float *unit_key, int32_t *unit_idx, int k, int row0, const float *qkey,
-                                          const int32_t *qidx, int &cnt, float &tau, int lane, uint32_t *qtau_word) {
+                                          const int32_t *qidx, int &cnt, float &tau, int lane, uint32_t *qtau_word,
+                                          float koff) {
     for (int r = 0; r < 32; r++) {
         const int c = __shfl_sync(kFullMask, cnt, r);
         if (c == 0) continue;
@@ -248,7 +249,7 @@ __device__ __noinline__ void flush_queues(float *unit_key, int32_t *unit_idx, in
             // larger key can be in the query's final top-k, so it is published for all
             tau = fminf(tau, m);
             cnt = 0;
-            if (m < kInf) atomicMin(qtau_word, float_to_ordered(m));
+            if (m < kInf) atomicMin(qtau_word, float_to_ordered(__fadd_ru(m, koff)));
         }
     }
     __syncwarp();
@@ -270,6 +271,9 @@ struct KernelArgs {
     const int *n_items;         // device count of items
     int *item_counter;          // zero on entry
     const int32_t *qrow_query;  // gathered row -> query (its threshold word), -1 = padding row
+    // Grouped L2 with residual queries (may be null): constant K of every gathered row such that
+    // key + K is comparable between the lists of one query; keys inside the kernel leave it out
+    const float *qrow_const;
     float *part_key;
     int32_t *part_idx;
     uint32_t *qtau;  // per query: smallest k-th-best key any chunk has published (ordered-uint form)
@@ -296,10 +300,9 @@ enum SelMode { kSelSmem = 0, kSelAppend = 1, kSelReplace = 2 };
 constexpr int kBuf = 512;  // candidate slots per row in append mode
 static_assert(kAppendMaxK <= kBuf / 2, "a compacted row must leave room for new candidates");
 
-// ---- bitonic sort of 512 (key, idx) pairs held by a warp, 16 per lane -------------------------
-// Bitonic sort of 512 (key, idx) pairs held by a warp, 16 per lane; keys are order-preserving
-// uint32 images of the float keys.  Element e lives in lane e / 16, register e % 16, so
-// exchanges at distance < 16 stay inside a thread and larger ones are one shuffle.
+// ---- bitonic sort of (key, idx) pairs held by a warp, E per lane ---------------------------------
+// Keys are order-preserving uint32 images of the float keys.  Element e lives in lane e / E,
+// register e % E, so exchanges at distance < E stay inside a thread and larger ones are one shuffle.
 // Every compare-exchange is written without a conditional on the direction (the
 // direction is an XOR mask), so the code is straight-line selects, no branches.
 __device__ __forceinline__ void ce_swap(uint32_t &ka, int32_t &ia, uint32_t &kb, int32_t &ib, uint32_t dm) {
@@ -308,31 +311,33 @@ __device__ __forceinline__ void ce_swap(uint32_t &ka, int32_t &ia, uint32_t &kb,
     const int32_t ua = sw ? ib : ia, ub = sw ? ia : ib;
     ka = ta; kb = tb; ia = ua; ib = ub;
 }
-__device__ __forceinline__ void sort512(uint32_t (&key)[16], int32_t (&idx)[16], int lane) {
-    // sizes 2..16: all exchanges are inside a lane
+// Sorts 32 * E pairs, E per lane (element e lives in lane e / E, register e % E).
+template <int E>
+__device__ __forceinline__ void warp_sort(uint32_t (&key)[E], int32_t (&idx)[E], int lane) {
+    // sizes 2..E: all exchanges are inside a lane
 #pragma unroll
-    for (int size = 2; size <= 16; size <<= 1) {
+    for (int size = 2; size <= E; size <<= 1) {
 #pragma unroll
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
+            for (int i = 0; i < E; i++) {
                 if ((i & stride) == 0) {
-                    const uint32_t dm = size == 16 ? (0u - (uint32_t)(lane & 1)) : ((i & size) ? 0xffffffffu : 0u);
+                    const uint32_t dm = size == E ? (0u - (uint32_t)(lane & 1)) : ((i & size) ? 0xffffffffu : 0u);
                     ce_swap(key[i], idx[i], key[i | stride], idx[i | stride], dm);
                 }
             }
         }
     }
-    // sizes 32..512: the direction is the same for all 16 elements of a lane
+    // sizes 2E..32E: the direction is the same for all elements of a lane
 #pragma unroll 1
-    for (int size = 32; size <= 512; size <<= 1) {
-        const uint32_t dm = ((lane << 4) & size) ? 0xffffffffu : 0u;
+    for (int size = 2 * E; size <= 32 * E; size <<= 1) {
+        const uint32_t dm = ((lane * E) & size) ? 0xffffffffu : 0u;
 #pragma unroll 1
-        for (int ls = size >> 5; ls > 0; ls >>= 1) {
+        for (int ls = size / (2 * E); ls > 0; ls >>= 1) {
             // the lower lane of a pair keeps the smaller key when ascending
             const uint32_t km = ((lane & ls) ? 0xffffffffu : 0u) ^ dm;  // 0: keep min, ~0: keep max
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
+            for (int i = 0; i < E; i++) {
                 const uint32_t ok = __shfl_xor_sync(kFullMask, key[i], ls);
                 const int32_t oi = __shfl_xor_sync(kFullMask, idx[i], ls);
                 const bool take = (ok ^ km) < (key[i] ^ km);
@@ -341,72 +346,85 @@ __device__ __forceinline__ void sort512(uint32_t (&key)[16], int32_t (&idx)[16],
             }
         }
 #pragma unroll
-        for (int stride = 8; stride > 0; stride >>= 1) {
+        for (int stride = E / 2; stride > 0; stride >>= 1) {
 #pragma unroll
-            for (int i = 0; i < 16; i++)
+            for (int i = 0; i < E; i++)
                 if ((i & stride) == 0) ce_swap(key[i], idx[i], key[i | stride], idx[i | stride], dm);
         }
     }
 }
 
-// Append mode: sorts the buffers of the rows in `need` (bit r = row row0 + r of this
-// warp), keeps their best k entries in slots [0, k) (sorted, unused slots get index
-// -1) and tightens the rows' thresholds.
-__device__ unsigned long long g_compact_phase[4];  // measurement only: load, sort, store cycles, rows
+// Sorts the first 32 * E slots of one row's append buffer (c <= 32 * E of them filled), writes
+// the best k back in order (index -1 past the end) and returns the k-th best key (+inf if c < k).
+template <int E>
+__device__ __forceinline__ float compact_one(float *bk, int32_t *bi, int c, int k, int lane) {
+    uint32_t key[E];
+    int32_t idx[E];
+    if (E >= 4) {
+#pragma unroll
+        for (int v = 0; v < E / 4; v++) {
+            const float4 kk = *reinterpret_cast<const float4 *>(bk + lane * E + v * 4);
+            const int4 ii = *reinterpret_cast<const int4 *>(bi + lane * E + v * 4);
+            key[v * 4 + 0] = float_to_ordered(kk.x); key[v * 4 + 1] = float_to_ordered(kk.y);
+            key[v * 4 + 2] = float_to_ordered(kk.z); key[v * 4 + 3] = float_to_ordered(kk.w);
+            idx[v * 4 + 0] = ii.x; idx[v * 4 + 1] = ii.y; idx[v * 4 + 2] = ii.z; idx[v * 4 + 3] = ii.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < E; i++) {
+            key[i] = float_to_ordered(bk[lane * E + i]);
+            idx[i] = bi[lane * E + i];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < E; i++) {
+        const bool stale = lane * E + i >= c;  // slots past the fill hold old data
+        key[i] = stale ? 0xff800000u : key[i];  // +inf
+        idx[i] = stale ? -1 : idx[i];
+    }
+    warp_sort<E>(key, idx, lane);
+    float kth = kInf;
+#pragma unroll
+    for (int i = 0; i < E; i++) {
+        const int e = lane * E + i;
+        const float kf = ordered_to_float(key[i]);
+        st_global_if(e < k, bk + e, kf);
+        st_global_if(e < k, bi + e, idx[i]);
+        kth = (e == k - 1) ? kf : kth;
+    }
+    if (32 * E < k) {  // the list is shorter than k: mark the rest empty
+        for (int e = 32 * E + lane; e < k; e += 32) bi[e] = -1;
+        return kInf;
+    }
+    return __shfl_sync(kFullMask, kth, (k - 1) / E);
+}
 
+// Compacts the append buffers of the rows in `need` (bit r = row row0 + r of this warp) down to
+// their best k, sorted.  The sort is as wide as the row's fill needs: a full buffer takes the
+// 512-wide network (~14k cycles); the few dozen entries typical when a list is closed behind a
+// tight threshold take the 32- or 64-wide one (a few hundred cycles).
 __device__ __noinline__ void compact_rows(float *slot_key, int32_t *slot_idx, int k, int row0, unsigned need, int &cnt,
-                                          float &tau, int lane, uint32_t *qtau_word) {
+                                          float &tau, int lane, uint32_t *qtau_word, float koff) {
     __syncwarp();  // the appends of every lane are visible to the whole warp
     while (need) {
-        const long long p0 = clock64();
         const int r = __ffs(need) - 1;
         need &= need - 1;
         const int c = __shfl_sync(kFullMask, cnt, r);
         float *bk = slot_key + (size_t)(row0 + r) * kBuf;
         int32_t *bi = slot_idx + (size_t)(row0 + r) * kBuf;
-        uint32_t key[16];
-        int32_t idx[16];
-#pragma unroll
-        for (int v = 0; v < 4; v++) {
-            const float4 kk = *reinterpret_cast<const float4 *>(bk + lane * 16 + v * 4);
-            const int4 ii = *reinterpret_cast<const int4 *>(bi + lane * 16 + v * 4);
-            key[v * 4 + 0] = float_to_ordered(kk.x); key[v * 4 + 1] = float_to_ordered(kk.y);
-            key[v * 4 + 2] = float_to_ordered(kk.z); key[v * 4 + 3] = float_to_ordered(kk.w);
-            idx[v * 4 + 0] = ii.x; idx[v * 4 + 1] = ii.y; idx[v * 4 + 2] = ii.z; idx[v * 4 + 3] = ii.w;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-            const bool stale = lane * 16 + i >= c;  // slots past the fill hold old data
-            key[i] = stale ? 0xff800000u : key[i];  // +inf
-            idx[i] = stale ? -1 : idx[i];
-        }
-        const long long p1 = clock64();
-        sort512(key, idx, lane);
-        const long long p2 = clock64();
-        float kth = kInf;
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-            const int e = lane * 16 + i;
-            const float kf = ordered_to_float(key[i]);
-            st_global_if(e < k, bk + e, kf);
-            st_global_if(e < k, bi + e, idx[i]);
-            kth = (e == k - 1) ? kf : kth;
-        }
-        kth = __shfl_sync(kFullMask, kth, (k - 1) >> 4);
+        float kth;
+        if (c > 256) kth = compact_one<16>(bk, bi, c, k, lane);
+        else if (c > 128) kth = compact_one<8>(bk, bi, c, k, lane);
+        else if (c > 64) kth = compact_one<4>(bk, bi, c, k, lane);
+        else if (c > 32) kth = compact_one<2>(bk, bi, c, k, lane);
+        else kth = compact_one<1>(bk, bi, c, k, lane);
         if (lane == r) {
             cnt = c < k ? c : k;
             if (c >= k) {
                 // the k-th best key so far: nothing above it can reach the final top-k
                 tau = fminf(tau, kth);
-                atomicMin(qtau_word, float_to_ordered(kth));
+                atomicMin(qtau_word, float_to_ordered(__fadd_ru(kth, koff)));
             }
-        }
-        if (lane == 0) {
-            const long long p3 = clock64();
-            atomicAdd(&g_compact_phase[0], (unsigned long long)(p1 - p0));
-            atomicAdd(&g_compact_phase[1], (unsigned long long)(p2 - p1));
-            atomicAdd(&g_compact_phase[2], (unsigned long long)(p3 - p2));
-            atomicAdd(&g_compact_phase[3], 1ull);
         }
     }
     __syncwarp();
@@ -615,6 +633,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
         float *unit_key = nullptr;
         int32_t *unit_idx = nullptr;
         uint32_t *qtau_word = nullptr;  // this row's shared-threshold word
+        float koff = 0.f;               // published key = key + koff (residual-query mode), else 0
         bool row_valid = false;
         float tau = -kInf;       // a key must be below this to matter
         float list_max = kInf;   // small k: current maximum of this row's list
@@ -626,7 +645,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             if (!unit_key) return;
             if (APPEND) {
                 const unsigned need = __ballot_sync(kFullMask, cnt > 0);
-                if (need) compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word);
+                if (need) compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word, koff);
                 if (!((need >> lane) & 1u)) {  // no candidate ever reached this row: an empty list
                     for (int s = 0; s < k; s++) unit_idx[(size_t)row * kBuf + s] = -1;
                 }
@@ -637,7 +656,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 }
             } else {
                 if (__any_sync(kFullMask, cnt > 0))
-                    flush_queues<KR>(unit_key, unit_idx, k, quarter * 32, qkey, qidx, cnt, tau, lane, qtau_word);
+                    flush_queues<KR>(unit_key, unit_idx, k, quarter * 32, qkey, qidx, cnt, tau, lane, qtau_word, koff);
             }
         };
         for (uint32_t wi = 0;; wi++) {
@@ -658,6 +677,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     const int32_t q = args.qrow_query[(size_t)qt * BM + row];
                     row_valid = q >= 0;
                     qtau_word = args.qtau + (row_valid ? q : 0);
+                    koff = (args.qrow_const && row_valid) ? args.qrow_const[(size_t)qt * BM + row] : 0.f;
                 } else {
                     row_valid = (int64_t)qt * BM + row < args.nq;
                     qtau_word = args.qtau + (size_t)qt * BM + row;
@@ -704,8 +724,9 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 tmem_fence_after();
                 if (row_valid) {
                     // thresholds published by the other CTAs working on this query (L2-coherent read)
-                    const uint32_t tg = __ldcg(qtau_word);
-                    if (tg < float_to_ordered(tau)) tau = ordered_to_float(tg);
+                    // (rounded up after taking the row's constant out: never tighter than published)
+                    const float tg = __fadd_ru(ordered_to_float(__ldcg(qtau_word)), -koff);
+                    if (tg < tau) tau = tg;
                 }
                 const int64_t rem = r_end - trow;
                 const int ncols = rem < BN ? (int)rem : BN;
@@ -752,7 +773,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         const unsigned need = __ballot_sync(kFullMask, cnt + __popc(mask) > kBuf);
                         if (need) {
                             const long long c0 = args.stats ? clock64() : 0;
-                            compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word);
+                            compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word, koff);
                             if (args.stats && lane == 0) {
                                 atomicAdd(args.stats + kStatCompactCycles, (unsigned long long)(clock64() - c0));
                                 atomicAdd(args.stats + kStatCompactRows, (unsigned long long)__popc(need));
@@ -799,7 +820,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             const bool overflow = cnt + __popc(hm) > kQueueDepth;
                             if (__any_sync(kFullMask, overflow)) {
                                 flush_queues<KR>(unit_key, unit_idx, k, quarter * 32, qkey, qidx, cnt, tau, lane,
-                                                 qtau_word);
+                                                 qtau_word, koff);
                                 mask = beat_mask(raw, g, valid);
                                 hm = (mask >> (16 * half)) & 0xffffu;
                             }
@@ -834,7 +855,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 if (args.stats && lane == 0) atomicAdd(args.stats + kStatEpiTileCycles, (unsigned long long)(clock64() - t1));
                 if (SMALLK && list_max < published) {
                     published = list_max;
-                    atomicMin(qtau_word, float_to_ordered(list_max));
+                    atomicMin(qtau_word, float_to_ordered(__fadd_ru(list_max, koff)));
                 }
             }
         }
@@ -916,6 +937,7 @@ FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms) {
     const int64_t work = (int64_t)p.nq_tiles * p.nchunks;
     p.grid = (int)(work < sms ? work : sms);
     p.list_stride = (k > kQueueDepth && k <= kAppendMaxK) ? kBuf : k;
+    p.lists_sorted = (k > kQueueDepth && k <= kAppendMaxK);
     p.part_entries = (size_t)p.nq_tiles * lists * BM * (size_t)p.list_stride;
     return p;
 }
@@ -929,6 +951,7 @@ FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms) {
     p.grid = (int)(max_query_tiles < sms ? max_query_tiles : sms);
     if (p.grid < 1) p.grid = 1;
     p.list_stride = (k > kQueueDepth && k <= kAppendMaxK) ? kBuf : k;
+    p.lists_sorted = (k > kQueueDepth && k <= kAppendMaxK);
     p.part_entries = (size_t)max_query_tiles * BM * (size_t)p.list_stride;
     return p;
 }
@@ -968,6 +991,7 @@ int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, con
     a.n_items = grouped ? grouped->n_items : nullptr;
     a.item_counter = grouped ? grouped->item_counter : nullptr;
     a.qrow_query = grouped ? grouped->qrow_query : nullptr;
+    a.qrow_const = grouped ? grouped->qrow_const : nullptr;
     {
         const char *e = getenv("ANN_CUDA_TC_DEBUG");
         a.debug = e ? atoi(e) : 0;
@@ -988,10 +1012,6 @@ int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, con
         unsigned long long h[8];
         ANN_CUDA_TRY(cudaStreamSynchronize(stream));
         ANN_CUDA_TRY(cudaMemcpy(h, a.stats, sizeof h, cudaMemcpyDeviceToHost));
-        unsigned long long ph[4] = {0, 0, 0, 0}, zero[4] = {0, 0, 0, 0};
-        cudaMemcpyFromSymbol(ph, g_compact_phase, sizeof ph);
-        cudaMemcpyToSymbol(g_compact_phase, zero, sizeof zero);
-        fprintf(stderr, "[flat_tc compact] rows %llu load %llu sort %llu store %llu cycles\n", ph[3], ph[0], ph[1], ph[2]);
         fprintf(stderr,
                 "[flat_tc stats] grid %d k %d tiles(x4 warps) %llu | compact rows %llu cycles %llu | appends %llu | "
                 "epilogue: wait %llu work %llu cycles | mma wait: tmem %llu smem %llu cycles\n",

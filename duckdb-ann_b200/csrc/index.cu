@@ -50,6 +50,11 @@ struct SplitStore {
     float *hi = nullptr, *lo = nullptr, *norms = nullptr;
     int64_t n = 0, cap = 0;
     int dp = 0;
+    // L2 stores: a reference point near the data (mean of the first rows added).  norms hold
+    // |x - mu|^2 and queries are searched as q - mu: distances are the same, the dot products
+    // the tensor cores form are smaller, and so is their absolute error.  Fixed while n > 0.
+    bool l2 = false;
+    float *mu = nullptr;
 
     int reserve(int64_t want) {
         if (want <= cap) return 0;
@@ -81,11 +86,18 @@ struct SplitStore {
     }
     // x: device rows (cnt x d)
     int append_device(const float *x, int64_t cnt, int d, cudaStream_t stream) {
+        if (cnt <= 0) return 0;
         if (grow_for(cnt)) return -1;
-        if (launch_split_rows(x, cnt, d, dp, hi + n * dp, lo + n * dp, norms + n, stream)) return -1;
+        if (l2 && n == 0) {
+            if (!mu) ANN_CUDA_TRY(cudaMalloc(&mu, (size_t)dp * sizeof(float)));
+            if (launch_column_mean(x, std::min<int64_t>(cnt, 16384), d, mu, stream)) return -1;
+        }
+        if (launch_split_rows(x, cnt, d, dp, hi + n * dp, lo + n * dp, norms + n, stream, l2 ? mu : nullptr, false))
+            return -1;
         n += cnt;
         return 0;
     }
+    const float *center() const { return l2 ? mu : nullptr; }
     void release_buffers() {
         if (hi) cudaFree(hi);
         if (lo) cudaFree(lo);
@@ -93,13 +105,18 @@ struct SplitStore {
         hi = lo = norms = nullptr;
         cap = 0;
     }
+    void release_all() {
+        release_buffers();
+        if (mu) cudaFree(mu);
+        mu = nullptr;
+    }
 };
 
 struct Workspace {
     cudaStream_t own_stream = nullptr;
     cudaStream_t bound = nullptr;  // stream whose work may still use these buffers
     GrowBuf x, qhi, qlo, qn, part_key, part_idx, sel_key, sel_idx, status, out_d, out_i;
-    GrowBuf item_q, item_rb, item_re, item_slot, scratch, probes_key, probes, qtau, sched, gq, items;
+    GrowBuf item_q, item_rb, item_re, item_slot, scratch, probes_key, probes, qtau, sched, gq, items, qconst;
     int *status_host = nullptr;  // pinned
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;  // bracket the flat kernel when timing is on
     bool timed = false;
@@ -107,7 +124,8 @@ struct Workspace {
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
         for (GrowBuf *b : {&x, &qhi, &qlo, &qn, &part_key, &part_idx, &sel_key, &sel_idx, &status, &out_d, &out_i,
-                           &item_q, &item_rb, &item_re, &item_slot, &scratch, &probes_key, &probes, &qtau, &sched, &gq, &items})
+                           &item_q, &item_rb, &item_re, &item_slot, &scratch, &probes_key, &probes, &qtau, &sched, &gq, &items,
+                           &qconst})
             b->release();
         if (status_host) cudaFreeHost(status_host);
         if (own_stream) cudaStreamDestroy(own_stream);
@@ -131,10 +149,13 @@ struct ann_cuda_index {
     int shard_rank = 0, shard_count = 1;
     float *vhi = nullptr, *vlo = nullptr;  // rows x dp each: TF32 split of the stored rows, grouped by list
     float *vnorm = nullptr;                // rows: squared norms
+    float *vrnorm = nullptr;               // rows: |x - centroid of its list|^2 (L2; rebuilt with the CSR form)
+    int64_t vrnorm_cap = 0;
     int64_t *ids = nullptr;   // rows
     int64_t rows = 0, rows_cap = 0;
     std::vector<int32_t> row_list;  // list of every stored row, physical order (host)
     bool rows_sorted = true;        // physical order is already grouped by list
+    bool coarse_exact = true;       // probe lists are re-ranked in exact fp32 (see ivf_update_coarse_policy)
     mutable bool csr_dirty = true;
     mutable int64_t *list_off = nullptr;  // device, nlist + 1
     mutable std::vector<int64_t> list_off_host;
@@ -280,7 +301,8 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         ws.sel_key.ensure((size_t)nq * k * 4) || ws.sel_idx.ensure((size_t)nq * k * 4) || ws.status.ensure(4))
         return -1;
     if (flat_kernel_choice() == FlatKernel::TC) {
-        if (launch_split_rows(x_dev, nq, d, dp, ws.qhi.as<float>(), ws.qlo.as<float>(), ws.qn.as<float>(), stream))
+        if (launch_split_rows(x_dev, nq, d, dp, ws.qhi.as<float>(), ws.qlo.as<float>(), ws.qn.as<float>(), stream,
+                              st.center(), true))
             return -1;
         const FlatPlan plan = make_flat_plan(nq, st.n, k, sm_count(ix.device));
         const size_t qtau_bytes = (size_t)plan.nq_tiles * 128 * 4, sched_bytes = (size_t)plan.nq_tiles * 2 * 4;
@@ -314,7 +336,8 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         ANN_CUDA_TRY(cudaMemcpyAsync(ws.status_host, ws.status.ptr, 4, cudaMemcpyDeviceToHost, stream));
         return launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 0,
                                   ws.sched.as<int>() + plan.nq_tiles, nullptr, plan.lists_per_qt, nq, k,
-                                  plan.list_stride, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream);
+                                  plan.list_stride, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream,
+                                  plan.lists_sorted);
     }
     // exact-fp32 cross-check kernel: items = (query, database chunk)
     int chunks = (int)std::max<int64_t>(1, std::min<int64_t>({(int64_t)kMergeCandidates / k, (st.n + 255) / 256,
@@ -365,6 +388,9 @@ void ivf_free_rows(ann_cuda_index &ix) {
         if (p) cudaFree(p);
     ix.vhi = ix.vlo = ix.vnorm = nullptr;
     ix.ids = nullptr;
+    if (ix.vrnorm) cudaFree(ix.vrnorm);
+    ix.vrnorm = nullptr;
+    ix.vrnorm_cap = 0;
 }
 
 // ---- IVF: (re)build the CSR form after adds ------------------------------------------------------
@@ -410,6 +436,21 @@ int ivf_finalize_lists(const ann_cuda_index &cix) {
     if (!ix.list_off) ANN_CUDA_TRY(cudaMalloc(&ix.list_off, (size_t)(ix.nlist + 1) * 8));
     ANN_CUDA_TRY(cudaMemcpy(ix.list_off, off.data(), (size_t)(ix.nlist + 1) * 8, cudaMemcpyHostToDevice));
     ix.list_off_host.swap(off);
+    if (ix.metric != 0 && n > 0) {
+        // L2: the list scan works with query residuals against the list centroid and needs
+        // |x - c|^2 of every row in place of |x|^2
+        if (ix.vrnorm_cap < n) {
+            if (ix.vrnorm) cudaFree(ix.vrnorm);
+            ix.vrnorm = nullptr;
+            ix.vrnorm_cap = 0;
+            ANN_CUDA_TRY(cudaMalloc(&ix.vrnorm, (size_t)ix.rows_cap * 4));
+            ix.vrnorm_cap = ix.rows_cap;
+        }
+        if (launch_residual_norms(ix.vhi, ix.vlo, n, ix.d, ix.dp, ix.list_off, (int)ix.nlist, ix.store.hi, ix.store.lo,
+                                  ix.vrnorm, nullptr))
+            return -1;
+        ANN_CUDA_TRY(cudaDeviceSynchronize());
+    }
     ix.csr_dirty = false;
     return 0;
 }
@@ -438,8 +479,87 @@ int ivf_grow_rows(ann_cuda_index &ix, int64_t extra) {
 
 bool ivf_owns(const ann_cuda_index &ix, int64_t list_no) { return list_no % ix.shard_count == ix.shard_rank; }
 
+// ---- coarse quantiser -----------------------------------------------------------------------------
+// The nprobe nearest centroids of every query, best first, as int32 list numbers in `probes`
+// (device, nq x nprobe).  The tensor-core pass selects a few more candidates than asked for and
+// they are re-ranked by their exact fp32 distance: centroids of neighbouring cells can differ by
+// less than the split-TF32 error of the first pass, and a wrong probe list loses whole lists.
+constexpr int kCoarseMargin = 8;
+constexpr int kSelectMargin = 8;
+int coarse_probes(const ann_cuda_index &ix, Workspace &ws, const float *x_dev, int64_t nq, int nprobe,
+                  int32_t *probes, cudaStream_t stream, bool exact) {
+    if (!exact) {
+        if (split_store_topk(ix, ix.store, ws, x_dev, nq, nprobe, stream)) return -1;
+        ANN_CUDA_TRY(cudaMemcpyAsync(probes, ws.sel_idx.ptr, (size_t)nq * nprobe * 4, cudaMemcpyDeviceToDevice, stream));
+        return 0;
+    }
+    const int k_c = (int)std::min<int64_t>(ix.nlist, (int64_t)nprobe + kCoarseMargin);
+    if (split_store_topk(ix, ix.store, ws, x_dev, nq, k_c, stream)) return -1;
+    return launch_refine_finalize(ix.store.hi, ix.store.lo, ix.dp, ix.d, x_dev, ix.d, ws.sel_idx.as<int32_t>(), nq, k_c,
+                                  nprobe, ix.metric, nullptr, 0, nullptr, nullptr, ix.device, stream, nullptr, nullptr,
+                                  nullptr, probes);
+}
+
+// Decides whether the tensor-core ranking of the centroids may pick the probe lists by itself.
+// Its keys are off by up to ~2^-20 |q - mu| |c| (mu = the centroid store's reference point); that
+// is harmless when it is far below the spacing of the centroids, and wrong lists otherwise
+// (several centroids inside one tight cluster far from the origin).  The spacing is taken as
+// the smallest exact distance between two centroids, |q - mu| as twice the largest |c - mu|.
+int ivf_update_coarse_policy(ann_cuda_index &ix) {
+    ix.coarse_exact = true;
+    if (ix.metric == 0 || ix.nlist < 2 || ix.store.n != ix.nlist) {
+        ix.coarse_exact = ix.metric != 0 && ix.nlist >= 2;  // inner product: no cancellation to guard against
+        return 0;
+    }
+    const int64_t nl = ix.nlist;
+    float *rows = nullptr;
+    ANN_CUDA_TRY(cudaMalloc(&rows, (size_t)nl * ix.d * 4));
+    int rc = 0;
+    std::vector<float> d2((size_t)nl * 2), norms((size_t)nl), mu((size_t)ix.dp, 0.f);
+    {
+        WsLease lease(&ix, nullptr, true);
+        if (!lease.ws) {
+            cudaFree(rows);
+            return -1;
+        }
+        Workspace &ws = *lease.ws;
+        cudaStream_t s = ws.own_stream;
+        rc = launch_join_rows(ix.store.hi, ix.store.lo, nl, ix.d, ix.dp, rows, s);
+        for (int64_t q0 = 0; q0 < nl && rc == 0; q0 += kQueryBlock) {
+            const int64_t nb = std::min(kQueryBlock, nl - q0);
+            if (ws.out_d.ensure((size_t)nb * 2 * 4) || ws.out_i.ensure((size_t)nb * 2 * 8)) rc = -1;
+            if (rc == 0) rc = split_store_topk(ix, ix.store, ws, rows + q0 * ix.d, nb, 2, s);
+            if (rc == 0)
+                rc = launch_refine_finalize(ix.store.hi, ix.store.lo, ix.dp, ix.d, rows + q0 * ix.d, ix.d,
+                                            ws.sel_idx.as<int32_t>(), nb, 2, 2, ix.metric, nullptr, 0, ws.out_d.as<float>(),
+                                            ws.out_i.as<int64_t>(), ix.device, s);
+            if (rc == 0 && cudaMemcpyAsync(d2.data() + q0 * 2, ws.out_d.ptr, (size_t)nb * 2 * 4, cudaMemcpyDeviceToHost, s) !=
+                               cudaSuccess)
+                rc = set_error("copy failed");
+            if (rc == 0 && cudaStreamSynchronize(s) != cudaSuccess) rc = set_error("device error ranking the centroids");
+        }
+    }
+    if (rc == 0 && (cudaMemcpy(norms.data(), ix.store.norms, (size_t)nl * 4, cudaMemcpyDeviceToHost) != cudaSuccess ||
+                    (ix.store.center() &&
+                     cudaMemcpy(mu.data(), ix.store.center(), (size_t)ix.dp * 4, cudaMemcpyDeviceToHost) != cudaSuccess)))
+        rc = set_error("copy failed");
+    cudaFree(rows);
+    if (rc) return -1;
+    double gap = INFINITY, r2 = 0, mu2 = 0;
+    for (int64_t i = 0; i < nl; i++) {
+        gap = std::min<double>(gap, std::max(d2[i * 2 + 1], 0.f));
+        r2 = std::max<double>(r2, norms[i]);
+    }
+    for (int j = 0; j < ix.d; j++) mu2 += (double)mu[j] * mu[j];
+    const double r = std::sqrt(r2), cmax = r + std::sqrt(mu2);
+    const double err = std::ldexp(1.0, -20) * 2.0 * r * cmax;
+    ix.coarse_exact = !(err <= 2.5e-5 * gap);
+    return 0;
+}
+
 // Nearest centroid of n device rows -> host vector.
-int ivf_assign_device(const ann_cuda_index &ix, const float *x_dev, int64_t n, std::vector<int32_t> &assign) {
+int ivf_assign_device(const ann_cuda_index &ix, const float *x_dev, int64_t n, std::vector<int32_t> &assign,
+                      bool exact) {
     assign.resize((size_t)n);
     WsLease lease(&ix, nullptr, true);
     if (!lease.ws) return -1;
@@ -447,8 +567,9 @@ int ivf_assign_device(const ann_cuda_index &ix, const float *x_dev, int64_t n, s
     cudaStream_t s = ws.own_stream;
     for (int64_t q0 = 0; q0 < n; q0 += kQueryBlock) {
         const int64_t nb = std::min(kQueryBlock, n - q0);
-        if (split_store_topk(ix, ix.store, ws, x_dev + q0 * ix.d, nb, 1, s)) return -1;
-        ANN_CUDA_TRY(cudaMemcpyAsync(assign.data() + q0, ws.sel_idx.ptr, (size_t)nb * 4, cudaMemcpyDeviceToHost, s));
+        if (ws.probes.ensure((size_t)nb * 4)) return -1;
+        if (coarse_probes(ix, ws, x_dev + q0 * ix.d, nb, 1, ws.probes.as<int32_t>(), s, exact)) return -1;
+        ANN_CUDA_TRY(cudaMemcpyAsync(assign.data() + q0, ws.probes.ptr, (size_t)nb * 4, cudaMemcpyDeviceToHost, s));
         ANN_CUDA_TRY(cudaStreamSynchronize(s));
         if (*ws.status_host) return set_error("flat kernel gave up on a wait (code %d)", *ws.status_host);
     }
@@ -505,17 +626,23 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
                                       k_sel, (int)k, ix.metric, nullptr, label_offset, d_dev, i_dev, ix.device, stream);
     }
     const int nprobe = (int)std::min<int64_t>(std::max<int64_t>(ix.nprobe, 1), ix.nlist);
-    const int k_sel = (int)std::min<int64_t>(k, kMaxK);
+    // The list scan ranks by split-TF32 keys, off by up to ~2^-20 |q - c||x|: a few more
+    // candidates than asked for are selected and the exact re-ranking at the end decides the
+    // k-th place, so a near tie at the boundary is settled in fp32.
+    int k_sel = (int)std::min<int64_t>(k, kMaxK);
+    if (flat_kernel_choice() == FlatKernel::TC && k_sel + kSelectMargin <= kMaxK &&
+        (int64_t)nprobe * (k_sel + kSelectMargin) <= kMergeCandidates)
+        k_sel += kSelectMargin;
     if ((int64_t)nprobe * k_sel > kMergeCandidates)
         return set_error("nprobe * k = %lld exceeds the %d candidates the merge step holds", (long long)nprobe * k_sel,
                          kMergeCandidates);
     // coarse quantiser: nprobe nearest centroids under the index metric
-    if (split_store_topk(ix, ix.store, ws, x_dev, nq, nprobe, stream)) return -1;
     const int64_t n_items = nq * nprobe;
     if (ws.probes.ensure((size_t)n_items * 4) || ws.item_slot.ensure(n_items * 4) ||
-        ws.scratch.ensure((size_t)(ix.nlist + 1) * 2 * 4) || ws.qtau.ensure((size_t)nq * 4))
+        ws.scratch.ensure((size_t)(ix.nlist + 1) * 2 * 4))
         return -1;
-    ANN_CUDA_TRY(cudaMemcpyAsync(ws.probes.ptr, ws.sel_idx.ptr, (size_t)n_items * 4, cudaMemcpyDeviceToDevice, stream));
+    if (coarse_probes(ix, ws, x_dev, nq, nprobe, ws.probes.as<int32_t>(), stream, ix.coarse_exact)) return -1;
+    if (ws.qtau.ensure((size_t)nq * 4)) return -1;
     ANN_CUDA_TRY(cudaMemsetAsync(ws.qtau.ptr, 0xFF, (size_t)nq * 4, stream));
     if (flat_kernel_choice() == FlatKernel::TC) {
         // Tensor-core list scan: queries are grouped by the list they probe (padded to tiles
@@ -537,10 +664,16 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
         if (launch_group_probes(ws.probes.as<int32_t>(), nq, nprobe, ix.nlist, ix.list_off, ws.scratch.as<int>(), n_tiles,
                                 ws.items.as<int4>(), ws.gq.as<int32_t>(), ws.item_slot.as<int32_t>(), stream))
             return -1;
+        // L2: residual queries (see split_gathered_kernel); keys carry the per-row constant
+        // only outside the scan kernel (shared thresholds, merge)
+        const bool residual = ix.metric != 0;
+        if (residual && ws.qconst.ensure((size_t)max_rows * 4)) return -1;
+        float *qconst = residual ? ws.qconst.as<float>() : nullptr;
         if (launch_split_gathered(x_dev, ix.d, ix.dp, ws.gq.as<int32_t>(), n_tiles, max_rows, ws.qhi.as<float>(),
-                                  ws.qlo.as<float>(), stream))
+                                  ws.qlo.as<float>(), stream, residual ? ws.items.as<int4>() : nullptr,
+                                  residual ? ix.store.hi : nullptr, residual ? ix.store.lo : nullptr, qconst))
             return -1;
-        GroupedWork gw{ws.items.as<int4>(), n_tiles, item_counter, ws.gq.as<int32_t>()};
+        GroupedWork gw{ws.items.as<int4>(), n_tiles, item_counter, ws.gq.as<int32_t>(), qconst};
         const bool timing = g_time_kernels.load(std::memory_order_relaxed) != 0;
         if (timing) {
             if (!ws.ev0) {
@@ -549,7 +682,8 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
             }
             ANN_CUDA_TRY(cudaEventRecord(ws.ev0, stream));
         }
-        if (launch_flat_tc(plan, ix.vhi, ix.vlo, ix.vnorm, ix.rows, ws.qhi.as<float>(), ws.qlo.as<float>(), max_rows, ix.dp,
+        if (launch_flat_tc(plan, ix.vhi, ix.vlo, residual ? ix.vrnorm : ix.vnorm, ix.rows, ws.qhi.as<float>(),
+                           ws.qlo.as<float>(), max_rows, ix.dp,
                            k_sel, ix.metric, ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.qtau.as<uint32_t>(),
                            nullptr, ws.status.as<int>(), ix.device, stream, &gw))
             return -1;
@@ -562,11 +696,14 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
         if (ws.sel_key.ensure((size_t)nq * k_sel * 4) || ws.sel_idx.ensure((size_t)nq * k_sel * 4)) return -1;
         if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, nullptr, ws.item_slot.as<int32_t>(),
                                nprobe, nq, k_sel, plan.list_stride, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(),
-                               ix.device, stream))
+                               ix.device, stream, plan.lists_sorted, qconst))
             return -1;
-        // the selected distances are recomputed exactly from hi + lo, as for Flat
+        // IP: the selected distances are recomputed exactly from hi + lo, as for Flat.  L2: the
+        // residual form keeps the scan's own distance accurate unless the row nearly coincides
+        // with the query; only those are recomputed.
         return launch_refine_finalize(ix.vhi, ix.vlo, ix.dp, ix.d, x_dev, ix.d, ws.sel_idx.as<int32_t>(), nq, k_sel, (int)k,
-                                      ix.metric, ix.ids, label_offset, d_dev, i_dev, ix.device, stream);
+                                      ix.metric, ix.ids, label_offset, d_dev, i_dev, ix.device, stream,
+                                      residual ? ws.sel_key.as<float>() : nullptr, ix.vrnorm, ix.vnorm);
     }
     // exact-fp32 cross-check path: one warp per (query, list)
     if (ws.item_q.ensure(n_items * 4) || ws.item_rb.ensure(n_items * 8) || ws.item_re.ensure(n_items * 8) ||
@@ -635,7 +772,7 @@ int add_device_impl(ann_cuda_index *ix, int64_t n, const float *x_dev) {
     }
     if (!ix->trained) return set_error("add: index must be trained first");  // MetalIndexIVFFlat.mm:103
     std::vector<int32_t> assign;
-    if (ivf_assign_device(*ix, x_dev, n, assign)) return -1;
+    if (ivf_assign_device(*ix, x_dev, n, assign, ix->coarse_exact)) return -1;
     std::vector<int64_t> labels((size_t)n);
     std::iota(labels.begin(), labels.end(), ix->ntotal);  // label = running ntotal (MetalIndexIVFFlat.mm:112)
     if (ivf_append(*ix, x_dev, n, assign.data(), labels.data())) return -1;
@@ -731,6 +868,7 @@ static int create_common(int device, int d, int metric, bool ivf, int64_t nlist,
     ix->metric = metric;
     ix->ivf = ivf;
     ix->store.dp = ix->dp;
+    ix->store.l2 = ix->metric != 0;
     ix->nlist = nlist;
     ix->trained = !ivf;
     *out = ix;
@@ -749,7 +887,7 @@ void ann_cuda_index_free(ann_cuda_index *ix) {
     if (!ix) return;
     DeviceGuard g(ix->device);
     cudaDeviceSynchronize();
-    ix->store.release_buffers();
+    ix->store.release_all();
     ivf_free_rows(*ix);
     if (ix->list_off) cudaFree(ix->list_off);
     for (Workspace *w : ix->ws_free) {
@@ -772,7 +910,8 @@ int ann_cuda_ivfflat_set_centroids(ann_cuda_index *ix, const float *centroids) {
     cudaFree(buf);
     if (rc) return -1;
     ix->trained = true;
-    return 0;
+    ix->csr_dirty = true;  // the rows' residual norms refer to the centroids
+    return ivf_update_coarse_policy(*ix);
 }
 
 int ann_cuda_ivfflat_get_centroids(const ann_cuda_index *ix, float *centroids) {
@@ -857,7 +996,7 @@ int ann_cuda_ivfflat_train(ann_cuda_index *ix, int64_t n, const float *x) {
     for (int it = 0; it < kIterations && rc == 0; it++) {
         ix->store.n = 0;
         rc = ix->store.append_device(cent, nlist, d, nullptr);
-        if (rc == 0) rc = ivf_assign_device(*ix, dx, n, assign);
+        if (rc == 0) rc = ivf_assign_device(*ix, dx, n, assign, false);  // Lloyd steps: the fast ranking will do
         if (rc) break;
         cudaMemcpy(dassign, assign.data(), (size_t)n * 4, cudaMemcpyHostToDevice);
         cudaMemset(sums, 0, (size_t)nlist * d * 4);
@@ -908,7 +1047,8 @@ int ann_cuda_ivfflat_train(ann_cuda_index *ix, int64_t n, const float *x) {
         ix->trained = false;
         return -1;
     }
-    return 0;
+    ix->csr_dirty = true;
+    return ivf_update_coarse_policy(*ix);
 }
 
 int ann_cuda_ivfflat_add_list(ann_cuda_index *ix, int64_t list_no, int64_t n, const int64_t *ids, const float *rows) {
@@ -976,9 +1116,10 @@ int ann_cuda_ivfflat_coarse(const ann_cuda_index *ix, int64_t n, const float *x,
         const int64_t nb = std::min(kQueryBlock, n - q0);
         if (ws.x.ensure((size_t)nb * ix->d * 4)) return -1;
         ANN_CUDA_TRY(cudaMemcpyAsync(ws.x.ptr, x + q0 * ix->d, (size_t)nb * ix->d * 4, cudaMemcpyHostToDevice, s));
-        if (split_store_topk(*ix, ix->store, ws, ws.x.as<float>(), nb, np, s)) return -1;
+        if (ws.probes.ensure((size_t)nb * np * 4)) return -1;
+        if (coarse_probes(*ix, ws, ws.x.as<float>(), nb, np, ws.probes.as<int32_t>(), s, ix->coarse_exact)) return -1;
         tmp.resize((size_t)nb * np);
-        ANN_CUDA_TRY(cudaMemcpyAsync(tmp.data(), ws.sel_idx.ptr, (size_t)nb * np * 4, cudaMemcpyDeviceToHost, s));
+        ANN_CUDA_TRY(cudaMemcpyAsync(tmp.data(), ws.probes.ptr, (size_t)nb * np * 4, cudaMemcpyDeviceToHost, s));
         ANN_CUDA_TRY(cudaStreamSynchronize(s));
         for (int64_t q = 0; q < nb; q++)
             for (int64_t p = 0; p < nprobe; p++) lists[(q0 + q) * nprobe + p] = p < np ? tmp[q * np + p] : -1;
@@ -1265,7 +1406,7 @@ extern "C" int ann_cuda_flat_search_small_static(const ann_cuda_index *ix, int64
     ANN_CUDA_TRY(cudaMemsetAsync(qtau, 0xFF, 128 * 4, s));
     ANN_CUDA_TRY(cudaMemsetAsync(sched, 0, 2 * 4, s));
     ANN_CUDA_TRY(cudaMemsetAsync(part_idx, 0xFF, plan.part_entries * 4, s));
-    if (launch_split_rows(x_device, n, ix->d, ix->dp, qhi, qlo, qn, s)) return -1;
+    if (launch_split_rows(x_device, n, ix->d, ix->dp, qhi, qlo, qn, s, ix->store.center(), true)) return -1;
     if (launch_flat_tc(plan, ix->store.hi, ix->store.lo, ix->store.norms, ix->store.n, qhi, qlo, n, ix->dp, k_sel,
                        ix->metric, part_key, part_idx, qtau, sched, status, ix->device, s))
         return -1;

@@ -22,8 +22,12 @@ void count_launch(int n = 1);
 // x (n x d, row stride d) -> hi, lo (n x dp each): hi = x rounded to TF32, lo = x - hi
 // (exact in fp32, so hi + lo reconstructs x bit for bit); pad columns are zero;
 // norms[i] = sum x^2 in fp32 (may be nullptr).
+// With `mu` (d floats, device) the norms are |x - mu|^2; with `center_rows` the planes hold
+// x - mu too (queries), otherwise x itself (database rows).
 int launch_split_rows(const float *x, int64_t n, int d, int dp, float *hi, float *lo, float *norms,
-                      cudaStream_t stream);
+                      cudaStream_t stream, const float *mu = nullptr, bool center_rows = false);
+// mu[c] = mean over the n rows of x[r][c]
+int launch_column_mean(const float *x, int64_t n, int d, float *mu, cudaStream_t stream);
 // x (n x d) -> out (n x dp) zero padded, norms (may be nullptr).
 int launch_pad_rows(const float *x, int64_t n, int d, int dp, float *out, float *norms, cudaStream_t stream);
 // out (n x d) <- hi + lo (n x dp)
@@ -41,6 +45,7 @@ struct FlatPlan {
     int grid = 0;
     int list_stride = 0;      // slots per row in the list memory (k, or the append buffer size)
     size_t part_entries = 0;  // nq_tiles * lists_per_qt * 128 * list_stride
+    bool lists_sorted = false;  // every finished k-list is sorted best first (append mode)
 };
 // Chooses the decomposition for nq queries against n rows on a device with `sms` SMs.
 FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms);
@@ -62,6 +67,7 @@ struct GroupedWork {
     const int *n_items;
     int *item_counter;  // zero on entry
     const int32_t *qrow_query;
+    const float *qrow_const = nullptr;  // per gathered row: add to a key to compare across lists (null = 0)
 };
 FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms);
 
@@ -83,8 +89,16 @@ int launch_group_probes(const int32_t *probes, int64_t nq, int nprobe, int64_t n
 
 // hi/lo split of gathered query rows: row g takes query qrow_query[g] of x (zeros if < 0),
 // for g < 128 * *n_tiles.
+// With `items` and the centroid planes given, gathered row g is written as the residual of its
+// query against the centroid of list items[g / 128].w and qconst[g] = |v|^2 + 2 v.c.
 int launch_split_gathered(const float *x, int d, int dp, const int32_t *qrow_query, const int *n_tiles,
-                          int64_t max_rows, float *hi, float *lo, cudaStream_t stream);
+                          int64_t max_rows, float *hi, float *lo, cudaStream_t stream, const int4 *items = nullptr,
+                          const float *cent_hi = nullptr, const float *cent_lo = nullptr, float *qconst = nullptr);
+
+// out[r] = |x_r - c|^2 for every row of a store grouped by list (CSR list_off), c = the
+// centroid (cent_hi + cent_lo) of the row's list.
+int launch_residual_norms(const float *xhi, const float *xlo, int64_t n, int d, int dp, const int64_t *list_off,
+                          int nlist, const float *cent_hi, const float *cent_lo, float *out, cudaStream_t stream);
 
 // ---- scan.cu -----------------------------------------------------------------------------
 // Exact-fp32 scan of row ranges with warp k-selection: one warp per (query, range)
@@ -114,19 +128,28 @@ int launch_build_ivf_items(const int32_t *probes, int64_t nq, int nprobe, int64_
 // Layout kinds: 0 = flat list slots (slot = (q / 128) * nparts + p, row q % 128; only the first
 //                   min(nparts, lists_started[q / 128]) slots of a query tile are read),
 //               1 = item slots (slot_of[q * nparts + p], or q * nparts + p if null).
-// A list holds its k entries in the first k of `list_stride` slots.
+// A list holds its k entries in the first k of `list_stride` slots.  With `lists_sorted` every
+// list is already sorted best first (entries past its end have index -1) and the lists are
+// merged pairwise instead of sorted from scratch.  `slot_key_offset[slot * 128-row index]`
+// (layout 1 only, may be null) is added to every key of that list as it is read.
 int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layout, const int *lists_started,
                        const int32_t *slot_of, int nparts, int64_t nq, int k, int list_stride, float *out_key,
-                       int32_t *out_idx, int device, cudaStream_t stream);
+                       int32_t *out_idx, int device, cudaStream_t stream, bool lists_sorted = false,
+                       const float *slot_key_offset = nullptr);
 
 // Flat: recomputes the distance of every selected (query, row) pair in exact fp32
 // from the split store, sorts the k results best first and writes the user-facing
 // distances (squared L2 / raw dot) and int64 labels (row + label_offset, or
 // ids[row] when ids is non-null).  Empty slots -> (+-inf, -1).
+// With approx_key (L2 list scan in residual form: approx_key[q * k_sel + j] is the scan's own
+// squared distance, rnorm[row] = |x - c|^2, xnorm[row] = |x|^2) a pair is recomputed only if its
+// distance is small against the error bound of the scan's dot product; the others keep approx_key.
+// With out_row the k_out best ROW NUMBERS (int32, -1 = none) are written there and nothing else.
 int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, const float *queries, int q_stride,
                            const int32_t *sel_idx, int64_t nq, int k_sel, int k_out, int metric,
                            const int64_t *ids, int64_t label_offset, float *out_d, int64_t *out_i, int device,
-                           cudaStream_t stream);
+                           cudaStream_t stream, const float *approx_key = nullptr, const float *rnorm = nullptr,
+                           const float *xnorm = nullptr, int32_t *out_row = nullptr);
 
 // Already-exact keys: just convert to user-facing values and labels, padding to k_out.
 int launch_finalize(const float *sel_key, const int32_t *sel_idx, int64_t nq, int k_sel, int k_out, int metric,

@@ -16,6 +16,8 @@ namespace {
 
 constexpr int kMergeThreads = 256;
 constexpr int kMaxCandidates = kMergeCandidates;
+// 2 * 2^-21 |v||x| <= 0.25e-4 * dist  <=>  dist >= 0.038 |v||x|
+constexpr float kRefineBelow = 0.04f;
 
 __host__ __device__ inline int next_pow2(int v) {
     int p = 1;
@@ -49,7 +51,7 @@ __device__ void bitonic_sort(float *keys, int32_t *vals, int P) {
 __global__ void __launch_bounds__(kMergeThreads)
 merge_parts_kernel(const float *__restrict__ part_key, const int32_t *__restrict__ part_idx, int layout,
                    const int *__restrict__ lists_started, const int32_t *__restrict__ slot_of, int nparts, int64_t nq,
-                   int k, int list_stride, int P_max,
+                   int k, int list_stride, int P_max, const float *__restrict__ slot_key_offset,
                    float *__restrict__ out_key, int32_t *__restrict__ out_idx) {
     extern __shared__ float smem_f[];
     float *keys = smem_f;
@@ -76,7 +78,7 @@ merge_parts_kernel(const float *__restrict__ part_key, const int32_t *__restrict
                 list = slot_of ? (int64_t)slot_of[q * nparts + p] : q * nparts + p;
             const int32_t idx = list >= 0 ? part_idx[list * list_stride + j] : -1;
             if (idx >= 0) {
-                key = part_key[list * list_stride + j];
+                key = part_key[list * list_stride + j] + (slot_key_offset ? slot_key_offset[list] : 0.f);
                 val = idx;
             }
         }
@@ -91,12 +93,99 @@ merge_parts_kernel(const float *__restrict__ part_key, const int32_t *__restrict
     }
 }
 
+// (key, val) order used by every merge here: smaller key first, ties by smaller val
+__device__ __forceinline__ bool pair_after(float a, int32_t va, float b, int32_t vb) {
+    return (a > b) || (a == b && va > vb);
+}
+
+// Same result as merge_parts_kernel when every input list is already sorted best first:
+// the lists are merged pairwise.  For two ascending lists A and B of K2 entries,
+// min(A[i], B[K2-1-i]) is a bitonic sequence holding the K2 smallest of their union; a
+// bitonic merge (log2 K2 steps, not log2^2) sorts it.  log2(lists) such rounds leave the
+// answer in list 0.  For 16 lists of 128 this is ~8k compare-exchanges instead of ~68k.
+__global__ void __launch_bounds__(kMergeThreads)
+merge_sorted_kernel(const float *__restrict__ part_key, const int32_t *__restrict__ part_idx, int layout,
+                    const int *__restrict__ lists_started, const int32_t *__restrict__ slot_of, int nparts, int64_t nq,
+                    int k, int list_stride, int K2, int L2n, const float *__restrict__ slot_key_offset,
+                    float *__restrict__ out_key, int32_t *__restrict__ out_idx) {
+    extern __shared__ float smem_f[];
+    float *keys = smem_f;                                              // [L2n][K2]
+    int32_t *vals = reinterpret_cast<int32_t *>(smem_f + L2n * K2);
+    const int64_t q = blockIdx.x;
+    int nlists = nparts;
+    if (layout == 0) {
+        const int started = lists_started[q >> 7];
+        nlists = started < nparts ? started : nparts;
+    }
+    int L = 1;  // lists that take part, rounded up to a power of two
+    while (L < nlists) L <<= 1;
+    const int kshift = 31 - __clz(K2);
+    for (int t = threadIdx.x; t < L * K2; t += blockDim.x) {
+        const int p = t >> kshift, j = t & (K2 - 1);
+        float key = kInf;
+        int32_t val = 0x7fffffff;
+        if (p < nlists && j < k) {
+            int64_t list;
+            if (layout == 0)
+                list = ((q >> 7) * (int64_t)nparts + p) * 128 + (q & 127);
+            else
+                list = slot_of ? (int64_t)slot_of[q * nparts + p] : q * nparts + p;
+            const int32_t idx = list >= 0 ? part_idx[list * list_stride + j] : -1;
+            if (idx >= 0) {
+                key = part_key[list * list_stride + j] + (slot_key_offset ? slot_key_offset[list] : 0.f);
+                val = idx;
+            }
+        }
+        keys[t] = key;
+        vals[t] = val;
+    }
+    __syncthreads();
+    // `step` = distance between surviving lists; the survivor of a pair stays in the left slot
+    for (int step = 1; step < L; step <<= 1) {
+        const int pairs = L / (2 * step);
+        for (int t = threadIdx.x; t < pairs * K2; t += blockDim.x) {
+            const int p = t >> kshift, i = t & (K2 - 1);
+            const int a = (2 * p * step) * K2 + i;
+            const int b = ((2 * p + 1) * step) * K2 + (K2 - 1 - i);
+            const float ka = keys[a], kb = keys[b];
+            const int32_t va = vals[a], vb = vals[b];
+            if (pair_after(ka, va, kb, vb)) {
+                keys[a] = kb;
+                vals[a] = vb;
+            }
+        }
+        __syncthreads();
+        for (int stride = K2 >> 1; stride > 0; stride >>= 1) {
+            const int sshift = 31 - __clz(stride);
+            for (int t = threadIdx.x; t < pairs * (K2 >> 1); t += blockDim.x) {
+                const int p = t >> (kshift - 1), c = t & ((K2 >> 1) - 1);
+                const int lo = (2 * p * step) * K2 + ((c >> sshift) << (sshift + 1)) + (c & (stride - 1));
+                const int hi = lo + stride;
+                const float ka = keys[lo], kb = keys[hi];
+                const int32_t va = vals[lo], vb = vals[hi];
+                if (pair_after(ka, va, kb, vb)) {
+                    keys[lo] = kb; keys[hi] = ka;
+                    vals[lo] = vb; vals[hi] = va;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    for (int j = threadIdx.x; j < k; j += blockDim.x) {
+        const bool ok = vals[j] != 0x7fffffff;
+        out_key[q * k + j] = ok ? keys[j] : kInf;
+        out_idx[q * k + j] = ok ? vals[j] : -1;
+    }
+}
+
 // Exact fp32 re-evaluation of the selected pairs, sort, and user-facing output.
 __global__ void __launch_bounds__(128)
 refine_finalize_kernel(const float *__restrict__ xhi, const float *__restrict__ xlo, int dp, int d,
                        const float *__restrict__ queries, int q_stride, const int32_t *__restrict__ sel_idx,
                        int k_sel, int k_out, int P, int metric, const int64_t *__restrict__ ids,
-                       int64_t label_offset, float *__restrict__ out_d, int64_t *__restrict__ out_i) {
+                       int64_t label_offset, const float *__restrict__ approx_key, const float *__restrict__ rnorm,
+                       const float *__restrict__ xnorm, float *__restrict__ out_d, int64_t *__restrict__ out_i,
+                       int32_t *__restrict__ out_row) {
     extern __shared__ float smem_f[];
     float *keys = smem_f;
     int32_t *vals = reinterpret_cast<int32_t *>(smem_f + P);
@@ -109,7 +198,21 @@ refine_finalize_kernel(const float *__restrict__ xhi, const float *__restrict__ 
         int32_t val = 0x7fffffff;
         if (j < k_sel) {
             const int32_t idx = sel_idx[q * k_sel + j];
-            if (idx >= 0) {
+            bool keep_approx = false;
+            if (idx >= 0 && approx_key) {
+                // The scan formed dist = |x - c|^2 - 2 v.x + const with v = q - c on split-TF32
+                // tensor cores: the dot product is off by at most ~2^-21 |v| |x|, the distance by
+                // twice that.  |v| <= |q - x| + |x - c| (triangle inequality), both known here.  Keep
+                // the scan's value when that error is below a quarter of the 1e-4 tolerance.
+                const float a = approx_key[q * k_sel + j];
+                const float vmax = sqrtf(fmaxf(a, 0.f)) + sqrtf(rnorm[idx]);
+                keep_approx = a >= kRefineBelow * vmax * sqrtf(xnorm[idx]);
+                if (keep_approx) {
+                    key = a;
+                    val = idx;
+                }
+            }
+            if (idx >= 0 && !keep_approx) {
                 const float *h = xhi + (int64_t)idx * dp;
                 const float *l = xlo ? xlo + (int64_t)idx * dp : nullptr;
                 float acc = 0.f;
@@ -136,6 +239,10 @@ refine_finalize_kernel(const float *__restrict__ xhi, const float *__restrict__ 
     bitonic_sort(keys, vals, P);
     for (int j = threadIdx.x; j < k_out; j += blockDim.x) {
         const bool ok = j < k_sel && vals[j] != 0x7fffffff;
+        if (out_row) {  // row numbers only (the coarse quantiser's probe lists)
+            out_row[q * k_out + j] = ok ? vals[j] : -1;
+            continue;
+        }
         float dist = l2 ? kInf : -kInf;
         int64_t label = -1;
         if (ok) {
@@ -226,16 +333,31 @@ int opt_in_smem(K kernel, size_t smem) {
 
 int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layout, const int *lists_started,
                        const int32_t *slot_of, int nparts, int64_t nq, int k, int list_stride, float *out_key,
-                       int32_t *out_idx, int device, cudaStream_t stream) {
+                       int32_t *out_idx, int device, cudaStream_t stream, bool lists_sorted,
+                       const float *slot_key_offset) {
     (void)device;
     if (nq <= 0) return 0;
     const int total = nparts * k;
     if (total > kMaxCandidates) return set_error("merge: %d candidates per query exceeds %d", total, kMaxCandidates);
+    if (lists_sorted) {
+        const int K2 = next_pow2(k < 2 ? 2 : k), L2n = next_pow2(nparts);
+        const size_t smem = (size_t)K2 * L2n * 8;
+        if (smem <= 200 * 1024) {
+            if (opt_in_smem(merge_sorted_kernel, smem)) return -1;
+            merge_sorted_kernel<<<(unsigned)nq, kMergeThreads, smem, stream>>>(
+                part_key, part_idx, layout, lists_started, slot_of, nparts, nq, k, list_stride, K2, L2n, slot_key_offset,
+                out_key, out_idx);
+            count_launch();
+            ANN_CUDA_TRY(cudaGetLastError());
+            return 0;
+        }
+    }
     const int P = next_pow2(total < 2 ? 2 : total);
     const size_t smem = (size_t)P * 8;
     if (opt_in_smem(merge_parts_kernel, smem)) return -1;
     merge_parts_kernel<<<(unsigned)nq, kMergeThreads, smem, stream>>>(part_key, part_idx, layout, lists_started, slot_of,
-                                                                      nparts, nq, k, list_stride, P, out_key, out_idx);
+                                                                      nparts, nq, k, list_stride, P, slot_key_offset, out_key,
+                                                                      out_idx);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -244,14 +366,16 @@ int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layou
 int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, const float *queries, int q_stride,
                            const int32_t *sel_idx, int64_t nq, int k_sel, int k_out, int metric,
                            const int64_t *ids, int64_t label_offset, float *out_d, int64_t *out_i, int device,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, const float *approx_key, const float *rnorm, const float *xnorm,
+                           int32_t *out_row) {
     (void)device;
     if (nq <= 0) return 0;
     const int P = next_pow2(k_sel < 2 ? 2 : k_sel);
     const size_t smem = (size_t)P * 8;
     if (opt_in_smem(refine_finalize_kernel, smem)) return -1;
     refine_finalize_kernel<<<(unsigned)nq, 128, smem, stream>>>(xhi, xlo, dp, d, queries, q_stride, sel_idx, k_sel,
-                                                                k_out, P, metric, ids, label_offset, out_d, out_i);
+                                                                k_out, P, metric, ids, label_offset, approx_key, rnorm, xnorm,
+                                                                out_d, out_i, out_row);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

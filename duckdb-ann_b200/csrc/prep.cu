@@ -27,17 +27,24 @@ __device__ __forceinline__ float to_tf32(float x) {
 }
 
 // MODE 0: split into hi/lo; MODE 1: pad only (out = hi).
+// With `mu` (d floats) the norm is taken about mu, |x - mu|^2, and with `center_rows` the
+// planes hold x - mu as well (queries); without it they hold x itself (database rows, so that
+// hi + lo stays the stored row bit for bit).  Squared L2 distances do not change when the same
+// vector is taken off both operands, but the dot product the tensor cores form then has the
+// magnitude |q - mu||x| instead of |q||x|, and with it its absolute error.
 template <int MODE>
 __global__ void __launch_bounds__(kWarps * 32)
 prep_rows_kernel(const float *__restrict__ x, int64_t n, int d, int dp, float *__restrict__ hi,
-                 float *__restrict__ lo, float *__restrict__ norms) {
+                 float *__restrict__ lo, float *__restrict__ norms, const float *__restrict__ mu, int center_rows) {
     const int lane = threadIdx.x & 31;
     for (int64_t r = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); r < n; r += (int64_t)gridDim.x * kWarps) {
         const float *src = x + r * (int64_t)d;
         float acc = 0.f;
         for (int c = lane; c < dp; c += 32) {
             float v = c < d ? src[c] : 0.f;
-            acc = fmaf(v, v, acc);
+            const float w = (mu && c < d) ? v - mu[c] : v;
+            acc = fmaf(w, w, acc);
+            if (center_rows) v = w;
             if (MODE == 0) {
                 float h = to_tf32(v);
                 hi[r * (int64_t)dp + c] = h;
@@ -49,6 +56,18 @@ prep_rows_kernel(const float *__restrict__ x, int64_t n, int d, int dp, float *_
         acc = warp_sum(acc);
         if (norms && lane == 0) norms[r] = acc;
     }
+}
+
+// mu[c] += (sum over this block's rows of x[r][c]) / n; mu zero on entry
+__global__ void __launch_bounds__(128)
+column_mean_kernel(const float *__restrict__ x, int64_t n, int d, float *__restrict__ mu) {
+    const int c = blockIdx.x * 128 + threadIdx.x;
+    if (c >= d) return;
+    const int64_t per = (n + gridDim.y - 1) / gridDim.y;
+    const int64_t r0 = blockIdx.y * per, r1 = r0 + per < n ? r0 + per : n;
+    float acc = 0.f;
+    for (int64_t r = r0; r < r1; r++) acc += x[r * (int64_t)d + c];
+    if (r1 > r0) atomicAdd(mu + c, acc / (float)n);
 }
 
 __global__ void __launch_bounds__(kWarps * 32)
@@ -80,21 +99,63 @@ scatter_rows_kernel(const float *__restrict__ x, int64_t n, int d, int dp, const
     }
 }
 
+// Gathered query rows of the grouped list scan.  With centroids given (L2), row g becomes the
+// residual v = q - c of its query against the centroid of the list its tile scans, and
+// qconst[g] = |v|^2 + 2 v.c, so that for a list row x
+//     |x - q|^2 = |x - c|^2 - 2 v.x + qconst[g]:
+// the dot product the tensor cores form has the magnitude |v||x| instead of |q||x|, which
+// takes an order of magnitude off its absolute error for clustered data.
 __global__ void __launch_bounds__(kWarps * 32)
 split_gathered_kernel(const float *__restrict__ x, int d, int dp, const int32_t *__restrict__ qrow_query,
-                      const int *__restrict__ n_tiles, int64_t max_rows, float *__restrict__ hi,
-                      float *__restrict__ lo) {
+                      const int *__restrict__ n_tiles, int64_t max_rows, const int4 *__restrict__ items,
+                      const float *__restrict__ chi, const float *__restrict__ clo, float *__restrict__ hi,
+                      float *__restrict__ lo, float *__restrict__ qconst) {
     const int lane = threadIdx.x & 31;
     int64_t rows = (int64_t)(*n_tiles) * 128;
     if (rows > max_rows) rows = max_rows;
     for (int64_t g = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); g < rows; g += (int64_t)gridDim.x * kWarps) {
         const int32_t q = qrow_query[g];
+        const int64_t list = (chi && q >= 0) ? items[g >> 7].w : -1;
+        float acc = 0.f;
         for (int c = lane; c < dp; c += 32) {
-            const float v = (q >= 0 && c < d) ? x[q * (int64_t)d + c] : 0.f;
+            float v = (q >= 0 && c < d) ? x[q * (int64_t)d + c] : 0.f;
+            if (list >= 0 && c < d) {
+                const float cen = chi[list * dp + c] + clo[list * dp + c];
+                v -= cen;
+                acc = fmaf(v, fmaf(2.f, cen, v), acc);  // v^2 + 2 v c
+            }
             const float h = to_tf32(v);
             hi[g * (int64_t)dp + c] = h;
             lo[g * (int64_t)dp + c] = v - h;
         }
+        if (qconst) {
+            acc = warp_sum(acc);
+            if (lane == 0) qconst[g] = acc;
+        }
+    }
+}
+
+// |x - c|^2 of every row of a list-grouped store, c = centroid of the row's list
+__global__ void __launch_bounds__(kWarps * 32)
+residual_norms_kernel(const float *__restrict__ xhi, const float *__restrict__ xlo, int64_t n, int d, int dp,
+                      const int64_t *__restrict__ list_off, int nlist, const float *__restrict__ chi,
+                      const float *__restrict__ clo, float *__restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    for (int64_t r = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); r < n; r += (int64_t)gridDim.x * kWarps) {
+        int lo_l = 0, hi_l = nlist;  // list_off[lo_l] <= r < list_off[hi_l]
+        while (hi_l - lo_l > 1) {
+            const int mid = (lo_l + hi_l) >> 1;
+            if (list_off[mid] <= r) lo_l = mid;
+            else hi_l = mid;
+        }
+        float acc = 0.f;
+        for (int c = lane; c < d; c += 32) {
+            const float v = (xhi[r * (int64_t)dp + c] + xlo[r * (int64_t)dp + c]) -
+                            (chi[(int64_t)lo_l * dp + c] + clo[(int64_t)lo_l * dp + c]);
+            acc = fmaf(v, v, acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) out[r] = acc;
     }
 }
 
@@ -108,9 +169,19 @@ unsigned grid_for(int64_t n) {
 }  // namespace
 
 int launch_split_rows(const float *x, int64_t n, int d, int dp, float *hi, float *lo, float *norms,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, const float *mu, bool center_rows) {
     if (n <= 0) return 0;
-    prep_rows_kernel<0><<<grid_for(n), kWarps * 32, 0, stream>>>(x, n, d, dp, hi, lo, norms);
+    prep_rows_kernel<0><<<grid_for(n), kWarps * 32, 0, stream>>>(x, n, d, dp, hi, lo, norms, mu, center_rows ? 1 : 0);
+    count_launch();
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int launch_column_mean(const float *x, int64_t n, int d, float *mu, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    ANN_CUDA_TRY(cudaMemsetAsync(mu, 0, (size_t)d * sizeof(float), stream));
+    dim3 grid((unsigned)((d + 127) / 128), (unsigned)(n < 64 ? n : 64));
+    column_mean_kernel<<<grid, 128, 0, stream>>>(x, n, d, mu);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -118,7 +189,7 @@ int launch_split_rows(const float *x, int64_t n, int d, int dp, float *hi, float
 
 int launch_pad_rows(const float *x, int64_t n, int d, int dp, float *out, float *norms, cudaStream_t stream) {
     if (n <= 0) return 0;
-    prep_rows_kernel<1><<<grid_for(n), kWarps * 32, 0, stream>>>(x, n, d, dp, out, nullptr, norms);
+    prep_rows_kernel<1><<<grid_for(n), kWarps * 32, 0, stream>>>(x, n, d, dp, out, nullptr, norms, nullptr, 0);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -133,9 +204,21 @@ int launch_join_rows(const float *hi, const float *lo, int64_t n, int d, int dp,
 }
 
 int launch_split_gathered(const float *x, int d, int dp, const int32_t *qrow_query, const int *n_tiles,
-                          int64_t max_rows, float *hi, float *lo, cudaStream_t stream) {
+                          int64_t max_rows, float *hi, float *lo, cudaStream_t stream, const int4 *items,
+                          const float *cent_hi, const float *cent_lo, float *qconst) {
     if (max_rows <= 0) return 0;
-    split_gathered_kernel<<<grid_for(max_rows), kWarps * 32, 0, stream>>>(x, d, dp, qrow_query, n_tiles, max_rows, hi, lo);
+    split_gathered_kernel<<<grid_for(max_rows), kWarps * 32, 0, stream>>>(x, d, dp, qrow_query, n_tiles, max_rows, items,
+                                                                          cent_hi, cent_lo, hi, lo, qconst);
+    count_launch();
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int launch_residual_norms(const float *xhi, const float *xlo, int64_t n, int d, int dp, const int64_t *list_off,
+                          int nlist, const float *cent_hi, const float *cent_lo, float *out, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    residual_norms_kernel<<<grid_for(n), kWarps * 32, 0, stream>>>(xhi, xlo, n, d, dp, list_off, nlist, cent_hi, cent_lo,
+                                                                   out);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

@@ -173,6 +173,23 @@ def test_gpu_train_gives_usable_centroids(pkg, oracle):
     idx.close()
 
 
+def test_tight_clusters_far_from_the_origin(pkg, oracle):
+    """Distances ~1e-4 of the operands' squared norms, several centroids inside one cluster,
+    some queries equal to stored rows: neither the choice of probe lists nor the list scan's
+    norm expansion may lose them to cancellation."""
+    rng = np.random.default_rng(11)
+    nc, d = 32, 96
+    centers = (rng.standard_normal((nc, d)) * 3 + 2).astype(np.float32)   # |c|^2 ~ 1.2e3, in-cluster d^2 ~ 0.5
+    xb = (centers[rng.integers(0, nc, 8000)] + 0.05 * rng.standard_normal((8000, d))).astype(np.float32)
+    xq = (centers[rng.integers(0, nc, 300)] + 0.05 * rng.standard_normal((300, d))).astype(np.float32)
+    xq[:40] = xb[rng.integers(0, len(xb), 40)]          # exact duplicates of stored rows
+    xq[40:80] = xb[rng.integers(0, len(xb), 40)] + np.float32(1e-3)
+    idx, cent, off, rows = _build(pkg, oracle, xb, nc, pkg.METRIC_L2, seed=5)
+    D, I = _check(pkg, oracle, idx, xb, cent, off, rows, xq, 20, 4, pkg.METRIC_L2, "tight clusters")
+    assert (D[:40, 0] == 0.0).all()
+    idx.close()
+
+
 def test_clustered_config_scaled_down(pkg, oracle):
     """Gaussian clusters (centres N(0,1), offsets N(0, 0.1^2)), d=768, k=100, nprobe=16, scaled 1/50."""
     rng = np.random.default_rng(45)
