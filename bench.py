@@ -478,22 +478,23 @@ class BatchWorkload:
         self.it += 1
         return self.table.batch_distances_by_id_device(self.q_dev, ids, self.qmap, 0, out=self.out), None
 
-    def capture(self, torch, steps):
-        """Records `steps` back-to-back launches (each on a different id batch) into one CUDA
-        graph: the call is shorter than a few launch overheads, so the steady-state rate is
-        measured on a replayed stream of launches rather than on Python's call rate."""
-        s = torch.cuda.Stream()
-        s.wait_stream(torch.cuda.current_stream())
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(s):
-            self.step()
-            torch.cuda.synchronize()
-            with torch.cuda.graph(g, stream=s):
-                for _ in range(steps):
-                    self.step()
-        torch.cuda.current_stream().wait_stream(s)
-        torch.cuda.synchronize()
-        self.graph, self.graph_steps = g, steps
+    def prepare_stream_of_batches(self, torch, steps):
+        """The timed region of this workload is ONE multi-batch launch of `steps` batches (each
+        on its own row ids and its own output): a single batch is shorter than a few launch
+        latencies, so the steady-state rate is measured on a stream of back-to-back batches."""
+        self.outs = [torch.empty(self.total, dtype=torch.float32, device=self.q_dev.device) for _ in range(min(steps, 8))]
+        # every batch of the launch gets row ids of its own: with repeated ids two batches in
+        # flight at once would share their rows through L2
+        g = torch.Generator(device=self.q_dev.device).manual_seed(4242)
+        while len(self.ids) < steps:
+            self.ids.append(torch.randint(0, self.num, (self.total,), generator=g, device=self.q_dev.device,
+                                          dtype=torch.int32))
+        self.multi = [(self.q_dev, self.ids[i], self.qmap, self.outs[i % len(self.outs)]) for i in range(steps)]
+        self.packed = self.table.pack_batches(self.multi)  # the C array of descriptors, built once
+
+    def run_stream_of_batches(self):
+        self.table.batch_distances_by_id_device_multi(self.packed, 0, device=self.q_dev.device)
+        return self.outs[0], None
 
     def step_e2e(self, torch):
         ids = self.ids_host[self.it % len(self.ids_host)]
@@ -544,7 +545,7 @@ class BatchWorkload:
         return {"workload": self.name, "table_rows": self.num, "dim": self.dim, "queries": self.nq,
                 "rows_per_query": self.per, "metric": "L2", "bytes_per_step": self.bytes_per_step(),
                 "l2_flush": f"{self.batches} id batches cycled; table ({self.num * self.row_bytes / 1e9:.1f} GB) >> L2",
-                "launch": "the K timed launches are replayed from one CUDA graph"}
+                "launch": "the K timed batches are submitted as ONE multi-batch launch (stream of back-to-back batches)"}
 
     def roofline(self, peaks, kernel_ms):
         # DRAM read + write of one launch at the default shapes, from the ncu captures summarised in
@@ -643,7 +644,7 @@ def run_reference(args, wl):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default 5; 100 for the batch-distance workloads)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="flat_ip_20m")
@@ -652,6 +653,9 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     wl = make_workload(args.workload, args.scale)
+    if args.steps is None:
+        # a batch-distance step is ~20-40 us: the steady-state rate needs a stream of >= 100 of them
+        args.steps = 100 if isinstance(wl, BatchWorkload) and args.impl == "ours" else 5
     if args.impl == "reference":
         run_reference(args, wl)
         return
@@ -693,16 +697,24 @@ def main():
     launches0 = lib.ann_cuda_launch_count()
     kernel_ms = []
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    graph = None
-    if isinstance(wl, BatchWorkload):
-        wl.capture(torch, args.steps)
-        graph = wl.graph
-        graph.replay()  # warm replay
+    stream_of_batches = isinstance(wl, BatchWorkload)
+    one_per_launch_ms = None
+    if stream_of_batches:
+        # for comparison: the same batches one launch each, back to back (launch gaps included)
+        ev0.record()
+        for _ in range(args.steps):
+            out = wl.step()
+        ev1.record()
+        torch.cuda.synchronize()
+        one_per_launch_ms = ev0.elapsed_time(ev1) / args.steps
+        wl.prepare_stream_of_batches(torch, args.steps)
+        wl.run_stream_of_batches()  # warm
+        launches0 = lib.ann_cuda_launch_count()
     barrier()
     t_begin = sampler.mark()
     ev0.record()
-    if graph is not None:
-        graph.replay()
+    if stream_of_batches:
+        out = wl.run_stream_of_batches()
     else:
         for _ in range(args.steps):
             out = wl.step()
@@ -711,8 +723,6 @@ def main():
     t_end = sampler.mark()
     elapsed_ms = ev0.elapsed_time(ev1)
     launches = lib.ann_cuda_launch_count() - launches0
-    if graph is not None:
-        launches = args.steps  # replayed from the graph: one kernel per captured step
     clocks = sampler.stop(t_begin, t_end)
     if hasattr(wl, "index"):
         ms = lib.ann_cuda_index_last_flat_kernel_ms(wl.index._h)
@@ -761,6 +771,9 @@ def main():
                     "ms_per_step": 1e3 * e2e_s / args.steps},
             "gpu_launches": int(launches), "roofline": roof, "setup_s": t_setup}
 
+    if one_per_launch_ms is not None:
+        line["one_batch_per_launch"] = {"ms_per_step": one_per_launch_ms,
+                                        "value": wl.units_per_step() / (one_per_launch_ms * 1e-3), "unit": wl.unit}
     if isinstance(wl, BatchWorkload) and not wl.sq8 and rank == 0:
         line["single_query"] = wl.single_query_shapes(torch)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -97,6 +97,7 @@ SIGNATURES = {
     "diskann_cuda_unregister": (C.c_int, [_P]),
     "diskann_cuda_batch_distances_by_id": (C.c_int, [_P, _P, C.c_int, _P, _P, C.c_int, C.c_int, _P]),
     "diskann_cuda_batch_distances_by_id_device": (C.c_int, [_P, _P, C.c_int, _P, _P, C.c_int, C.c_int, _P, _P]),
+    "diskann_cuda_batch_distances_by_id_device_multi": (C.c_int, [_P, _P, C.c_int, C.c_int, _P]),
 }
 
 

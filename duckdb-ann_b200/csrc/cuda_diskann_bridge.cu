@@ -10,7 +10,10 @@
 // warp, warp-shuffle reductions.  There is no CPU path in this file.
 #include "cuda_diskann_bridge.h"
 
+#include <algorithm>
 #include <cstdlib>
+#include <vector>
+#include <cstring>
 #include <memory>
 #include <type_traits>
 
@@ -67,7 +70,16 @@ template <int WPR, bool VEC4>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 batch_distance_f32_kernel(const float *__restrict__ table, size_t num, int dim, const float *__restrict__ queries,
                           int nq, const uint32_t *__restrict__ ids, const uint32_t *__restrict__ qmap, int total_n,
-                          int metric, float *__restrict__ out) {
+                          int metric, float *__restrict__ out, const diskann_cuda_batch *__restrict__ batches) {
+    if (batches) {  // several batches in one launch: blockIdx.y picks the batch
+        const diskann_cuda_batch b = batches[blockIdx.y];
+        queries = b.queries;
+        nq = b.nq;
+        ids = b.ids;
+        qmap = b.query_map;
+        total_n = b.total_n;
+        out = b.out_distances;
+    }
     constexpr int kRowsPerBlock = kWarpsPerBlock / WPR;
     __shared__ float partial[kWarpsPerBlock];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,6 +143,61 @@ batch_distance_f32_kernel(const float *__restrict__ table, size_t num, int dim, 
         if (sub == 0 && lane == 0 && i < total_n) {
             out[i] = valid ? (l2 ? acc : -acc) : __int_as_float(0x7fc00000);
         }
+    }
+}
+
+// Several batches in one launch, fp32 rows: the rows of all batches form one sequence
+// (row_off[b] = first row of batch b) that the warps of a grid sized to the GPU walk with a
+// stride, one row per warp at a time; a warp keeps its place in the batch list as it advances.
+template <bool VEC4>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+batch_distance_f32_multi_kernel(const float *__restrict__ table, size_t num, int dim,
+                                const diskann_cuda_batch *__restrict__ batches, const int *__restrict__ row_off,
+                                int nbatches, int metric) {
+    const int lane = threadIdx.x & 31;
+    const bool l2 = (metric == 0);
+    const long long warps_total = (long long)gridDim.x * kWarpsPerBlock;
+    const long long rows_all = row_off[nbatches];
+    int b = 0;
+    for (long long u = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); u < rows_all; u += warps_total) {
+        while (u >= row_off[b + 1]) b++;  // u only grows
+        const diskann_cuda_batch d = batches[b];
+        const int i = (int)(u - row_off[b]);
+        const size_t r = (size_t)d.ids[i];
+        const uint32_t qi = d.query_map ? d.query_map[i] : 0u;
+        const bool valid = r < num && qi < (uint32_t)d.nq;
+        float acc = 0.f;
+        if (valid) {
+            const float *x = table + r * (size_t)dim;
+            const float *q = d.queries + (size_t)qi * dim;
+            if (VEC4) {
+                const float4 *x4 = reinterpret_cast<const float4 *>(x);
+                const float4 *q4 = reinterpret_cast<const float4 *>(q);
+                const int n4 = dim >> 2;
+                int c = lane;
+                for (; c + 96 < n4; c += 128) {  // four independent 16-byte loads in flight per lane
+                    float4 a0 = ld_stream4(x4 + c), a1 = ld_stream4(x4 + c + 32);
+                    float4 a2 = ld_stream4(x4 + c + 64), a3 = ld_stream4(x4 + c + 96);
+                    acc = acc4(acc, __ldg(q4 + c), a0, l2);
+                    acc = acc4(acc, __ldg(q4 + c + 32), a1, l2);
+                    acc = acc4(acc, __ldg(q4 + c + 64), a2, l2);
+                    acc = acc4(acc, __ldg(q4 + c + 96), a3, l2);
+                }
+                for (; c < n4; c += 32) acc = acc4(acc, __ldg(q4 + c), ld_stream4(x4 + c), l2);
+            } else {
+                for (int c = lane; c < dim; c += 32) {
+                    const float xv = __ldg(x + c), qv = __ldg(q + c);
+                    if (l2) {
+                        const float t = qv - xv;
+                        acc = fmaf(t, t, acc);
+                    } else {
+                        acc = fmaf(qv, xv, acc);
+                    }
+                }
+            }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) d.out_distances[i] = valid ? (l2 ? acc : -acc) : __int_as_float(0x7fc00000);
     }
 }
 
@@ -210,7 +277,16 @@ batch_distance_sq8_regs_kernel(const uint8_t *__restrict__ codes, size_t num, in
                                const float *__restrict__ mins, const float *__restrict__ scale,
                                const float *__restrict__ queries, int nq, const uint32_t *__restrict__ ids,
                                const uint32_t *__restrict__ qmap, int total_n, int metric,
-                               float *__restrict__ out) {
+                               float *__restrict__ out, const diskann_cuda_batch *__restrict__ batches) {
+    if (batches) {
+        const diskann_cuda_batch b = batches[blockIdx.y];
+        queries = b.queries;
+        nq = b.nq;
+        ids = b.ids;
+        qmap = b.query_map;
+        total_n = b.total_n;
+        out = b.out_distances;
+    }
     const int lane = threadIdx.x & 31;
     const long long warp_global = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const long long warps_total = (long long)gridDim.x * kWarpsPerBlock;
@@ -417,22 +493,30 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 batch_distance_sq8_dp4a_kernel(const uint8_t *__restrict__ codes, const float *__restrict__ norms, size_t num, int dim,
                                const float *__restrict__ mins, const float *__restrict__ scale,
                                const float *__restrict__ queries, int nq, const uint32_t *__restrict__ ids,
-                               const uint32_t *__restrict__ qmap, int total_n, float *__restrict__ out) {
+                               const uint32_t *__restrict__ qmap, int total_n, float *__restrict__ out,
+                               const diskann_cuda_batch *__restrict__ batches, const int *__restrict__ group_off,
+                               int nbatches) {
     static_assert(kPipeStages == 4 && kSq8RowsPerWarp == 8, "one id block of 32 rows fills the four stages");
     extern __shared__ __align__(16) uint8_t sq8_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr uint32_t kNone = 0xffffffffu;
     constexpr uint32_t kFull = 0xffffffffu;
     // A warp takes a CONTIGUOUS run of row groups, so that consecutive groups mostly share
-    // their query and its registers are rebuilt once per query, not once per group.
+    // their query and its registers are rebuilt once per query, not once per group.  With
+    // several batches in one launch (batches != null) the groups of all batches form one
+    // sequence (group_off[b] = first group of batch b) that is cut evenly over the warps of a
+    // grid sized to the GPU; a run that crosses a batch boundary is worked off piece by piece.
     const int warps_total = (int)gridDim.x * kWarpsPerBlock;
-    const int n_groups = (total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
-    const int per_warp = (n_groups + warps_total - 1) / warps_total;
-    const int g_first = ((int)blockIdx.x * kWarpsPerBlock + warp) * per_warp;
-    if (g_first >= n_groups) return;  // whole warp; the kernel has no block-wide barrier
-    const int n_my = min(per_warp, n_groups - g_first);
-    const int row_first = g_first * kSq8RowsPerWarp;
-    const int row_end = min(total_n, row_first + n_my * kSq8RowsPerWarp);
+    const int warp_global = (int)blockIdx.x * kWarpsPerBlock + warp;
+    const int groups_all = batches ? group_off[nbatches] : (total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
+    const int per_warp = (groups_all + warps_total - 1) / warps_total;
+    const int run_first = warp_global * per_warp;
+    if (run_first >= groups_all) return;  // whole warp; the kernel has no block-wide barrier
+    const int run_end = min(groups_all, run_first + per_warp);
+    // the piece being worked on (one batch): set before every call of process_piece below
+    int n_my = run_end - run_first;
+    int row_first = run_first * kSq8RowsPerWarp;
+    int row_end = min(total_n, row_first + n_my * kSq8RowsPerWarp);
 
     const int stage_bytes = kSq8RowsPerWarp * dim;
     uint8_t *ring = sq8_smem + (size_t)warp * kPipeStages * stage_bytes;  // this warp's four stages
@@ -619,6 +703,7 @@ batch_distance_sq8_dp4a_kernel(const uint8_t *__restrict__ codes, const float *_
             }
         }
     };
+    auto process_piece = [&]() {
     uint32_t rid_a, rq_a, rid_b, rq_b;  // id blocks b and b + 1
     float nrm_a, nrm_b;
     fetch_block(0, rid_a, rq_a, nrm_a);
@@ -650,6 +735,40 @@ batch_distance_sq8_dp4a_kernel(const uint8_t *__restrict__ codes, const float *_
         }
     }
     cp_async_wait<0>();
+    __syncwarp();
+    };
+    if (!batches) {
+        process_piece();
+        return;
+    }
+    int b = 0;  // batch holding group run_first: the last b with group_off[b] <= run_first
+    {
+        int hi = nbatches;
+        while (hi - b > 1) {
+            const int mid = (b + hi) >> 1;
+            if (group_off[mid] <= run_first) b = mid;
+            else hi = mid;
+        }
+    }
+    for (int g = run_first; g < run_end; b++) {
+        const int b_first = group_off[b], b_end = group_off[b + 1];
+        const int piece_end = min(run_end, b_end);
+        if (piece_end > g) {
+            const diskann_cuda_batch d = batches[b];
+            queries = d.queries;
+            nq = d.nq;
+            ids = d.ids;
+            qmap = d.query_map;
+            total_n = d.total_n;
+            out = d.out_distances;
+            n_my = piece_end - g;
+            row_first = (g - b_first) * kSq8RowsPerWarp;
+            row_end = min(total_n, row_first + n_my * kSq8RowsPerWarp);
+            cur_q = kNone;  // query numbers of another batch mean other queries
+            process_piece();
+            g = piece_end;
+        }
+    }
 }
 
 // SQ8 rows, any dimension: one warp per row, byte loads.
@@ -658,7 +777,16 @@ batch_distance_sq8_generic_kernel(const uint8_t *__restrict__ codes, size_t num,
                                   const float *__restrict__ mins, const float *__restrict__ scale,
                                   const float *__restrict__ queries, int nq, const uint32_t *__restrict__ ids,
                                   const uint32_t *__restrict__ qmap, int total_n, int metric,
-                                  float *__restrict__ out) {
+                                  float *__restrict__ out, const diskann_cuda_batch *__restrict__ batches) {
+    if (batches) {
+        const diskann_cuda_batch b = batches[blockIdx.y];
+        queries = b.queries;
+        nq = b.nq;
+        ids = b.ids;
+        qmap = b.query_map;
+        total_n = b.total_n;
+        out = b.out_distances;
+    }
     const int lane = threadIdx.x & 31;
     const bool l2 = (metric == 0);
     for (long long i = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); i < total_n;
@@ -704,35 +832,64 @@ struct diskann_cuda_table {
 
 namespace {
 
+// One launch for one batch (batches == nullptr) or for nbatches of them (descriptors on the
+// device; total_n is then the largest batch and nq / queries / ids / qmap / out are unused).
 int launch_distance(const diskann_cuda_table &t, const float *queries, int nq, const uint32_t *ids,
-                    const uint32_t *qmap, int total_n, int metric, float *out, cudaStream_t stream) {
+                    const uint32_t *qmap, int total_n, int metric, float *out, cudaStream_t stream,
+                    const diskann_cuda_batch *batches = nullptr, int nbatches = 1, bool aligned16 = true,
+                    const int *group_off = nullptr, const int *row_off = nullptr, long long rows_all = 0) {
     const int sms = sm_count(t.device);
+    unsigned gy = (unsigned)(batches ? nbatches : 1);
+    // blocks per batch: enough to fill the GPU alone, fewer when many batches share it
+    auto blocks_for = [&](long long want, long long cap) -> unsigned {
+        if (batches) cap = std::max<long long>(1, std::min<long long>(cap, (2 * cap + nbatches - 1) / nbatches));
+        return (unsigned)std::max<long long>(1, std::min(want, cap));
+    };
+    const bool q16 = batches ? aligned16 : ((reinterpret_cast<uintptr_t>(queries) & 15) == 0);
     if (!t.sq8) {
         const float *rows = static_cast<const float *>(t.rows);
-        const bool vec = (t.dim % 4 == 0) && ((reinterpret_cast<uintptr_t>(rows) & 15) == 0) &&
-                         ((reinterpret_cast<uintptr_t>(queries) & 15) == 0);
+        const bool vec = (t.dim % 4 == 0) && ((reinterpret_cast<uintptr_t>(rows) & 15) == 0) && q16;
         // fewer rows than resident warps: put four warps on each row
-        const bool small = total_n < sms * 16;
+        const bool small = (batches ? rows_all : (long long)total_n) < sms * 16;
+        if (batches && !small) {
+            // exactly one wave of blocks for all batches together
+            int per_sm = 0;
+            if (vec)
+                ANN_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, batch_distance_f32_multi_kernel<true>,
+                                                                           kWarpsPerBlock * 32, 0));
+            else
+                ANN_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, batch_distance_f32_multi_kernel<false>,
+                                                                           kWarpsPerBlock * 32, 0));
+            const dim3 grid((unsigned)std::min<long long>((rows_all + kWarpsPerBlock - 1) / kWarpsPerBlock,
+                                                          (long long)sms * std::max(per_sm, 1)));
+            if (vec)
+                batch_distance_f32_multi_kernel<true><<<grid, kWarpsPerBlock * 32, 0, stream>>>(rows, t.num, t.dim, batches,
+                                                                                                row_off, nbatches, metric);
+            else
+                batch_distance_f32_multi_kernel<false><<<grid, kWarpsPerBlock * 32, 0, stream>>>(rows, t.num, t.dim, batches,
+                                                                                                 row_off, nbatches, metric);
+            count_launch();
+            ANN_CUDA_TRY(cudaGetLastError());
+            return 0;
+        }
         const int wpr = small ? 4 : 1;
         const int rows_per_block = kWarpsPerBlock / wpr;
-        long long blocks = ((long long)total_n + rows_per_block - 1) / rows_per_block;
-        const long long cap = (long long)sms * 32;
-        if (blocks > cap) blocks = cap;
-        dim3 grid((unsigned)blocks), block(kWarpsPerBlock * 32);
+        dim3 grid(blocks_for(((long long)total_n + rows_per_block - 1) / rows_per_block, (long long)sms * 32), gy);
+        dim3 block(kWarpsPerBlock * 32);
         if (small) {
             if (vec)
-                batch_distance_f32_kernel<4, true><<<grid, block, 0, stream>>>(rows, t.num, t.dim, queries, nq, ids,
-                                                                                qmap, total_n, metric, out);
+                batch_distance_f32_kernel<4, true><<<grid, block, 0, stream>>>(rows, t.num, t.dim, queries, nq, ids, qmap,
+                                                                                total_n, metric, out, batches);
             else
                 batch_distance_f32_kernel<4, false><<<grid, block, 0, stream>>>(rows, t.num, t.dim, queries, nq, ids,
-                                                                                 qmap, total_n, metric, out);
+                                                                                 qmap, total_n, metric, out, batches);
         } else {
             if (vec)
-                batch_distance_f32_kernel<1, true><<<grid, block, 0, stream>>>(rows, t.num, t.dim, queries, nq, ids,
-                                                                                qmap, total_n, metric, out);
+                batch_distance_f32_kernel<1, true><<<grid, block, 0, stream>>>(rows, t.num, t.dim, queries, nq, ids, qmap,
+                                                                                total_n, metric, out, batches);
             else
                 batch_distance_f32_kernel<1, false><<<grid, block, 0, stream>>>(rows, t.num, t.dim, queries, nq, ids,
-                                                                                 qmap, total_n, metric, out);
+                                                                                 qmap, total_n, metric, out, batches);
         }
     } else {
         const uint8_t *codes = static_cast<const uint8_t *>(t.rows);
@@ -740,24 +897,23 @@ int launch_distance(const diskann_cuda_table &t, const float *queries, int nq, c
         int wpl = 0;
         for (int c = 1; c <= 4 && !wpl; c++)
             if (t.dim <= 128 * c && t.dim % (4 * c) == 0) wpl = c;
-        const bool regs = wpl != 0 && ((reinterpret_cast<uintptr_t>(codes) & 3) == 0) &&
-                          ((reinterpret_cast<uintptr_t>(queries) & 15) == 0);
+        const bool regs = wpl != 0 && ((reinterpret_cast<uintptr_t>(codes) & 3) == 0) && q16;
         const bool pipe = t.norms && (t.dim % 16 == 0) && t.dim <= kPipeMaxDim && total_n >= 4096 &&
-                          ((reinterpret_cast<uintptr_t>(codes) & 15) == 0) &&
-                          ((reinterpret_cast<uintptr_t>(queries) & 15) == 0);
+                          ((reinterpret_cast<uintptr_t>(codes) & 15) == 0) && q16;
+        const long long groups = ((long long)total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
+        const long long group_blocks = (groups + kWarpsPerBlock - 1) / kWarpsPerBlock;
         if (pipe) {
             const size_t smem = (size_t)kWarpsPerBlock * kPipeStages * kSq8RowsPerWarp * t.dim;
-            long long warps = ((long long)total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
-            long long blocks = (warps + kWarpsPerBlock - 1) / kWarpsPerBlock;
-            const long long cap = (long long)sms * 2;
-            if (blocks > cap) blocks = cap;
-            const unsigned g = (unsigned)blocks, b = kWarpsPerBlock * 32;
+            // several batches: one grid of two blocks per SM walks the groups of all of them
+            const dim3 g(batches ? (unsigned)(sms * 2) : blocks_for(group_blocks, (long long)sms * 2), 1);
+            const unsigned b = kWarpsPerBlock * 32;
 #define ANN_LAUNCH_PIPE3(W, L2, FULL)                                                                          \
     do {                                                                                                       \
         ANN_CUDA_TRY(cudaFuncSetAttribute(batch_distance_sq8_dp4a_kernel<W, L2, FULL>,                         \
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));            \
         batch_distance_sq8_dp4a_kernel<W, L2, FULL><<<g, b, smem, stream>>>(                                   \
-            codes, t.norms, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, out);              \
+            codes, t.norms, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, out, batches,      \
+            group_off, nbatches);                                                                              \
     } while (0)
 #define ANN_LAUNCH_PIPE(W)                                         \
     do {                                                           \
@@ -780,23 +936,18 @@ int launch_distance(const diskann_cuda_table &t, const float *queries, int nq, c
 #undef ANN_LAUNCH_PIPE3
 #undef ANN_LAUNCH_PIPE
         } else if (regs) {
-            long long warps = ((long long)total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
-            long long blocks = (warps + kWarpsPerBlock - 1) / kWarpsPerBlock;
-            const long long cap = (long long)sms * 4;
-            if (blocks > cap) blocks = cap;
-            const unsigned g = (unsigned)blocks, b = kWarpsPerBlock * 32;
+            const dim3 g(blocks_for(group_blocks, (long long)sms * 4), gy);
+            const unsigned b = kWarpsPerBlock * 32;
             switch (wpl) {
-            case 1: batch_distance_sq8_regs_kernel<1><<<g, b, 0, stream>>>(codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out); break;
-            case 2: batch_distance_sq8_regs_kernel<2><<<g, b, 0, stream>>>(codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out); break;
-            case 3: batch_distance_sq8_regs_kernel<3><<<g, b, 0, stream>>>(codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out); break;
-            default: batch_distance_sq8_regs_kernel<4><<<g, b, 0, stream>>>(codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out); break;
+            case 1: batch_distance_sq8_regs_kernel<1><<<g, b, 0, stream>>>(codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out, batches); break;
+            case 2: batch_distance_sq8_regs_kernel<2><<<g, b, 0, stream>>>(codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out, batches); break;
+            case 3: batch_distance_sq8_regs_kernel<3><<<g, b, 0, stream>>>(codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out, batches); break;
+            default: batch_distance_sq8_regs_kernel<4><<<g, b, 0, stream>>>(codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out, batches); break;
             }
         } else {
-            long long blocks = ((long long)total_n + kWarpsPerBlock - 1) / kWarpsPerBlock;
-            const long long cap = (long long)sms * 32;
-            if (blocks > cap) blocks = cap;
-            batch_distance_sq8_generic_kernel<<<(unsigned)blocks, kWarpsPerBlock * 32, 0, stream>>>(
-                codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out);
+            const dim3 g(blocks_for(((long long)total_n + kWarpsPerBlock - 1) / kWarpsPerBlock, (long long)sms * 32), gy);
+            batch_distance_sq8_generic_kernel<<<g, kWarpsPerBlock * 32, 0, stream>>>(
+                codes, t.num, t.dim, t.mins, t.scale, queries, nq, ids, qmap, total_n, metric, out, batches);
         }
     }
     count_launch();
@@ -812,6 +963,8 @@ struct CallCtx {
     int device = 0;
     cudaStream_t stream = nullptr;
     GrowBuf q, cand, ids, map, out, flag;
+    GrowBuf desc;                // descriptor image of an asynchronous multi-batch launch
+    cudaEvent_t done = nullptr;  // recorded after the launch that last read `desc`
 };
 
 struct BridgeState {
@@ -1067,6 +1220,67 @@ int diskann_cuda_batch_distances_by_id_device(const diskann_cuda_table *table, c
     if (!guard.ok) return set_error("cudaSetDevice(%d) failed", table->device);
     return launch_distance(*table, queries, nq, ids, query_map, total_n, metric, out_distances,
                            static_cast<cudaStream_t>(stream));
+}
+
+int diskann_cuda_batch_distances_by_id_device_multi(const diskann_cuda_table *table, const diskann_cuda_batch *batches,
+                                                    int nbatches, int metric, void *stream) {
+    if (!table || !batches || nbatches <= 0) return set_error("invalid arguments");
+    if (nbatches > 65535) return set_error("at most 65535 batches per call");
+    int max_n = 0;
+    bool aligned16 = true;
+    for (int i = 0; i < nbatches; i++) {
+        const diskann_cuda_batch &b = batches[i];
+        if (!b.queries || !b.ids || !b.out_distances || b.total_n <= 0 || b.nq <= 0)
+            return set_error("batch %d: invalid arguments", i);
+        if (!b.query_map && b.nq != 1) return set_error("batch %d: query_map may be NULL only when nq == 1", i);
+        max_n = std::max(max_n, b.total_n);
+        aligned16 = aligned16 && (reinterpret_cast<uintptr_t>(b.queries) & 15) == 0;
+    }
+    DeviceGuard guard(table->device);
+    if (!guard.ok) return set_error("cudaSetDevice(%d) failed", table->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // stream-ordered copy of the descriptors: the host array is free on return, the device
+    // copy is released after the kernel
+    // device image: descriptors, then first group (8 rows) and first row of every batch in the
+    // sequence of all batches
+    const size_t desc_bytes = (size_t)nbatches * sizeof(diskann_cuda_batch);
+    const size_t bytes = desc_bytes + 2 * (size_t)(nbatches + 1) * sizeof(int);
+    std::vector<unsigned char> image(bytes);
+    std::memcpy(image.data(), batches, desc_bytes);
+    int *group_off = reinterpret_cast<int *>(image.data() + desc_bytes), *row_off = group_off + nbatches + 1;
+    long long groups = 0, rows = 0;
+    for (int i = 0; i < nbatches; i++) {
+        group_off[i] = (int)groups;
+        row_off[i] = (int)rows;
+        groups += (batches[i].total_n + kSq8RowsPerWarp - 1) / kSq8RowsPerWarp;
+        rows += batches[i].total_n;
+    }
+    if (rows > 0x7fffffffLL) return set_error("more than 2^31 rows in one call");
+    group_off[nbatches] = (int)groups;
+    row_off[nbatches] = (int)rows;
+    // The device copy lives in a pooled per-call context (no allocation in the steady state);
+    // an event recorded behind the launch keeps the next user of that context from overwriting
+    // the image while this launch may still read it.
+    CallCtx *c = state().acquire(table->device);
+    if (!c) return set_error("could not create a call context");
+    int rc = 0;
+    if (c->done && cudaEventSynchronize(c->done) != cudaSuccess) rc = set_error("device error before the launch");
+    if (rc == 0 && !c->done && cudaEventCreateWithFlags(&c->done, cudaEventDisableTiming) != cudaSuccess)
+        rc = set_error("could not create an event");
+    if (rc == 0 && c->desc.ensure(bytes)) rc = -1;
+    if (rc == 0) {
+        unsigned char *dev = static_cast<unsigned char *>(c->desc.ptr);
+        const cudaError_t e = cudaMemcpyAsync(dev, image.data(), bytes, cudaMemcpyHostToDevice, s);
+        if (e != cudaSuccess) rc = set_error("descriptor upload failed: %s", cudaGetErrorString(e));
+        if (rc == 0)
+            rc = launch_distance(*table, nullptr, 0, nullptr, nullptr, max_n, metric, nullptr, s,
+                                 reinterpret_cast<const diskann_cuda_batch *>(dev), nbatches, aligned16,
+                                 reinterpret_cast<const int *>(dev + desc_bytes),
+                                 reinterpret_cast<const int *>(dev + desc_bytes) + nbatches + 1, rows);
+        cudaEventRecord(c->done, s);
+    }
+    state().release(c);
+    return rc;
 }
 
 }  // extern "C"

@@ -80,6 +80,26 @@ extern "C" {
         out_distances: *mut f32,
         stream: *mut c_void,
     ) -> c_int;
+    #[allow(dead_code)]
+    fn diskann_cuda_batch_distances_by_id_device_multi(
+        table: *const DiskannCudaTable,
+        batches: *const DiskannCudaBatch,
+        nbatches: c_int,
+        metric: c_int,
+        stream: *mut c_void,
+    ) -> c_int;
+}
+
+/// `struct diskann_cuda_batch`: one batch of a multi-batch launch, device pointers.
+#[repr(C)]
+#[allow(dead_code)]
+pub struct DiskannCudaBatch {
+    pub queries: *const f32,
+    pub ids: *const u32,
+    pub query_map: *const u32,
+    pub out_distances: *mut f32,
+    pub nq: c_int,
+    pub total_n: c_int,
 }
 
 /// -1 = not probed yet, 0 = no usable GPU, 1 = available.

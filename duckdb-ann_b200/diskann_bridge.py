@@ -74,6 +74,12 @@ def multi_batch_distances_raw(queries, candidates, query_map, total_n, nq, dim, 
                                                                _p(out)))
 
 
+class _BatchDesc(C.Structure):
+    """struct diskann_cuda_batch of include/cuda_diskann_bridge.h"""
+    _fields_ = [("queries", C.c_void_p), ("ids", C.c_void_p), ("query_map", C.c_void_p),
+                ("out_distances", C.c_void_p), ("nq", C.c_int), ("total_n", C.c_int)]
+
+
 class DeviceTable:
     """A vector table resident in GPU memory (fp32 rows, or SQ8 codes + min/scale),
     scored by row id: diskann_cuda_register_* / diskann_cuda_batch_distances_by_id."""
@@ -151,6 +157,35 @@ class DeviceTable:
             C.c_void_p(query_map.data_ptr()) if query_map is not None else None, total_n, metric,
             C.c_void_p(out.data_ptr()), C.c_void_p(s.cuda_stream)), "batch_distances_by_id_device")
         return out
+
+    @staticmethod
+    def pack_batches(batches):
+        """The descriptor array of a multi-batch launch (struct diskann_cuda_batch[]), built once
+        and reusable: `batches` is a list of (queries, ids, query_map, out) torch CUDA tensors,
+        query_map None for a single query.  The tensors must outlive the launches."""
+        arr = (_BatchDesc * len(batches))()
+        for d, (q, ids, qm, out) in zip(arr, batches):
+            d.queries = q.data_ptr()
+            d.ids = ids.data_ptr()
+            d.query_map = qm.data_ptr() if qm is not None else None
+            d.out_distances = out.data_ptr()
+            d.nq = q.shape[0]
+            d.total_n = ids.shape[0]
+        return arr
+
+    def batch_distances_by_id_device_multi(self, batches, metric: int, stream=None, device=None):
+        """Several batches in one launch.  `batches` is a list of (queries, ids, query_map, out)
+        torch CUDA tensors or the result of pack_batches(); enqueued on `stream`."""
+        import torch
+        arr = batches if isinstance(batches, C.Array) else self.pack_batches(batches)
+        if stream is None:
+            if device is None and not isinstance(batches, C.Array):
+                device = batches[0][0].device
+            stream = torch.cuda.current_stream(device)
+        p = _pkg()
+        p.check(p.lib().diskann_cuda_batch_distances_by_id_device_multi(self._h, arr, len(arr), metric,
+                                                                         C.c_void_p(stream.cuda_stream)),
+                "batch_distances_by_id_device_multi")
 
     def close(self) -> None:
         if self._h:

@@ -98,6 +98,29 @@ int diskann_cuda_batch_distances_by_id_device(const diskann_cuda_table *table, c
                                               const uint32_t *ids, const uint32_t *query_map, int total_n,
                                               int metric, float *out_distances, void *stream);
 
+/* One batch of the call below: DEVICE pointers, same meaning as the arguments of
+ * diskann_cuda_batch_distances_by_id_device. */
+typedef struct diskann_cuda_batch {
+    const float *queries;        /* nq x dim */
+    const uint32_t *ids;         /* total_n row ids */
+    const uint32_t *query_map;   /* total_n query numbers, NULL when nq == 1 */
+    float *out_distances;        /* total_n results */
+    int nq;
+    int total_n;
+} diskann_cuda_batch;
+
+/* Several independent batches against one table in ONE launch (the batches of
+ * concurrent searches, or the lock-step batches of several query groups,
+ * rust_lib/src/disk_provider.rs:546-610).  A single batch of ~100 rows per query is
+ * shorter than a few kernel-launch latencies; submitted together the batches fill
+ * the GPU back to back and the kernel runs at its streaming rate.  `batches` is a
+ * HOST array of `nbatches` descriptors holding device pointers; it is copied
+ * during the call and may be reused on return.  Enqueued on `stream` without
+ * synchronising; results and error behaviour per batch as for the single call.
+ * No counterpart in the reference. */
+int diskann_cuda_batch_distances_by_id_device_multi(const diskann_cuda_table *table, const diskann_cuda_batch *batches,
+                                                    int nbatches, int metric, void *stream);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

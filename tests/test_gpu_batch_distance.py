@@ -170,6 +170,42 @@ def test_sq8_rows_that_almost_coincide_with_the_query(pkg, oracle, dim):
     t.close()
 
 
+@pytest.mark.parametrize("kind", ["f32", "sq8", "sq8_odd_dim"])
+@pytest.mark.parametrize("metric", [0, 1])
+def test_multi_batch_launch_equals_single_launches(pkg, oracle, kind, metric):
+    """Several batches of different sizes in one launch: every batch gets the result of its own
+    single-batch call (same kernels; only the summation order of a row may differ)."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(3)
+    dim = {"f32": 200, "sq8": 256, "sq8_odd_dim": 72}[kind]
+    num = 60000
+    if kind == "f32":
+        table = torch.randn((num, dim), generator=g, device="cuda")
+        t = pkg.diskann_bridge.DeviceTable.from_device(table)
+    else:
+        codes = torch.randint(0, 256, (num, dim), generator=g, device="cuda", dtype=torch.uint8)
+        mins = np.linspace(-2, -1, dim).astype(np.float32)
+        scale = np.linspace(2, 4, dim).astype(np.float32)
+        t = pkg.diskann_bridge.DeviceTable.sq8_from_device(codes, mins, scale)
+    shapes = [(64, 128), (1, 77), (33, 100), (64, 128), (5, 3)]   # (queries, rows per query)
+    batches, singles = [], []
+    for nq, per in shapes:
+        q = torch.randn((nq, dim), generator=g, device="cuda")
+        ids = torch.randint(0, num, (nq * per,), generator=g, device="cuda", dtype=torch.int32)
+        qm = None if nq == 1 else torch.arange(nq, device="cuda", dtype=torch.int32).repeat_interleave(per)
+        out = torch.full((nq * per,), float("nan"), device="cuda")
+        batches.append((q, ids, qm, out))
+        singles.append(t.batch_distances_by_id_device(q, ids, qm, metric).clone())
+    t.batch_distances_by_id_device_multi(batches, metric)
+    torch.cuda.synchronize()
+    for (q, ids, qm, out), want in zip(batches, singles):
+        # not bit for bit: a small single batch puts four warps on a row, which sums in another order
+        assert torch.allclose(out, want, rtol=3e-6, atol=1e-4 if metric else 0) and torch.isfinite(out).all()
+    with pytest.raises(pkg.AnnCudaError):
+        t.batch_distances_by_id_device_multi([(batches[0][0], batches[0][1], None, batches[0][3])], metric)
+    t.close()
+
+
 def test_sq8_nearest_neighbour_known_answer(pkg, oracle):
     import json, os
     with open(os.path.join(os.path.dirname(__file__), "golden", "reference_known_answers.json")) as f:
