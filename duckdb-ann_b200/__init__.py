@@ -95,6 +95,9 @@ SIGNATURES = {
     "diskann_cuda_register_sq8": (C.c_int, [C.c_int, _P, _P, _P, C.c_size_t, C.c_int, C.POINTER(_P)]),
     "diskann_cuda_register_sq8_device": (C.c_int, [C.c_int, _P, _P, _P, C.c_size_t, C.c_int, C.POINTER(_P)]),
     "diskann_cuda_unregister": (C.c_int, [_P]),
+    "diskann_cuda_parse_index": (C.c_int, [_P, C.c_size_t, _P]),
+    "diskann_cuda_load_index": (C.c_int, [C.c_int, _P, C.c_size_t, _P, _P, _P]),
+    "diskann_cuda_load_index_file": (C.c_int, [C.c_int, C.c_char_p, _P, _P, _P]),
     "diskann_cuda_batch_distances_by_id": (C.c_int, [_P, _P, C.c_int, _P, _P, C.c_int, C.c_int, _P]),
     "diskann_cuda_batch_distances_by_id_device": (C.c_int, [_P, _P, C.c_int, _P, _P, C.c_int, C.c_int, _P, _P]),
     "diskann_cuda_batch_distances_by_id_device_multi": (C.c_int, [_P, _P, C.c_int, C.c_int, _P]),

@@ -11,6 +11,7 @@
 #include "cuda_diskann_bridge.h"
 
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <vector>
 #include <cstring>
@@ -1281,6 +1282,101 @@ int diskann_cuda_batch_distances_by_id_device_multi(const diskann_cuda_table *ta
     }
     state().release(c);
     return rc;
+}
+
+int diskann_cuda_parse_index(const void *image, size_t len, diskann_cuda_index_info *info) {
+    if (!image || !info) return set_error("invalid arguments");
+    const unsigned char *p = static_cast<const unsigned char *>(image);
+    auto u32 = [&](size_t off) -> uint32_t {
+        return (uint32_t)p[off] | ((uint32_t)p[off + 1] << 8) | ((uint32_t)p[off + 2] << 16) | ((uint32_t)p[off + 3] << 24);
+    };
+    std::memset(info, 0, sizeof *info);
+    if (len < 32) return set_error("index image too small: %zu bytes, the header alone is 32", len);
+    if (std::memcmp(p, "DANN", 4) != 0) return set_error("bad magic: not a .diskann image");
+    if (u32(4) != 2) return set_error("unsupported .diskann version %u (2 expected)", u32(4));
+    info->num_vectors = u32(8);
+    info->dimension = u32(12);
+    info->max_degree = u32(16);
+    info->num_entry_points = u32(20);
+    info->metric = p[24];
+    info->build_complexity = u32(28);
+    if (info->dimension == 0) return set_error("dimension 0 in the header");
+    if (info->metric > 1) return set_error("unknown metric %u in the header", info->metric);
+    info->entry_points_offset = 32;
+    info->vectors_offset = 32 + (uint64_t)info->num_entry_points * 4;
+    const uint64_t vec_bytes = (uint64_t)info->num_vectors * info->dimension * 4;
+    info->adjacency_offset = info->vectors_offset + vec_bytes;
+    info->standard_size = info->adjacency_offset + (uint64_t)info->num_vectors * info->max_degree * 4;
+    if (info->standard_size > len)
+        return set_error("index image truncated: %llu bytes needed, %zu given", (unsigned long long)info->standard_size, len);
+    // optional SQ8 trailer
+    const uint64_t t = info->standard_size;
+    if (len > t + 4 && std::memcmp(p + t, "SQ8\0", 4) == 0) {
+        if (len < t + 16) return set_error("SQ8 trailer truncated");
+        const uint32_t sq_dim = u32(t + 4);
+        const uint64_t qlen = (uint64_t)u32(t + 8) | ((uint64_t)u32(t + 12) << 32);
+        if (sq_dim != info->dimension)
+            return set_error("SQ8 trailer has dimension %u, the header %u", sq_dim, info->dimension);
+        if (qlen != (uint64_t)info->num_vectors * info->dimension)
+            return set_error("SQ8 trailer holds %llu code bytes, %llu expected", (unsigned long long)qlen,
+                             (unsigned long long)info->num_vectors * info->dimension);
+        info->sq8_min_offset = t + 16;
+        info->sq8_scale_offset = info->sq8_min_offset + (uint64_t)sq_dim * 4;
+        info->sq8_codes_offset = info->sq8_scale_offset + (uint64_t)sq_dim * 4;
+        info->sq8_codes_size = qlen;
+        if (info->sq8_codes_offset + qlen > len)
+            return set_error("SQ8 section truncated: need %llu bytes, have %zu",
+                             (unsigned long long)(info->sq8_codes_offset + qlen), len);
+        info->has_sq8 = 1;
+    }
+    return 0;
+}
+
+int diskann_cuda_load_index(int device, const void *image, size_t len, diskann_cuda_index_info *info,
+                            diskann_cuda_table **vectors, diskann_cuda_table **sq8) {
+    if (!vectors) return set_error("null output handle");
+    *vectors = nullptr;
+    if (sq8) *sq8 = nullptr;
+    diskann_cuda_index_info local;
+    if (!info) info = &local;
+    if (diskann_cuda_parse_index(image, len, info)) return -1;
+    if (info->num_vectors == 0) return set_error("the index holds no vectors");
+    if (info->dimension > 0x7fffffffu) return set_error("dimension too large");
+    const unsigned char *p = static_cast<const unsigned char *>(image);
+    // the segments sit at arbitrary byte offsets: copy through aligned host vectors
+    std::vector<float> rows((size_t)info->num_vectors * info->dimension);
+    std::memcpy(rows.data(), p + info->vectors_offset, rows.size() * 4);
+    if (make_table(device, rows.data(), false, nullptr, nullptr, info->num_vectors, (int)info->dimension, false, vectors))
+        return -1;
+    if (sq8 && info->has_sq8) {
+        std::vector<float> mins(info->dimension), scale(info->dimension);
+        std::memcpy(mins.data(), p + info->sq8_min_offset, mins.size() * 4);
+        std::memcpy(scale.data(), p + info->sq8_scale_offset, scale.size() * 4);
+        if (make_table(device, p + info->sq8_codes_offset, false, mins.data(), scale.data(), info->num_vectors,
+                       (int)info->dimension, true, sq8)) {
+            diskann_cuda_unregister(*vectors);
+            *vectors = nullptr;
+            return -1;
+        }
+    }
+    return 0;
+}
+
+int diskann_cuda_load_index_file(int device, const char *path, diskann_cuda_index_info *info,
+                                 diskann_cuda_table **vectors, diskann_cuda_table **sq8) {
+    if (!path) return set_error("null path");
+    FILE *f = std::fopen(path, "rb");
+    if (!f) return set_error("cannot open %s", path);
+    std::vector<unsigned char> buf;
+    if (std::fseek(f, 0, SEEK_END) == 0) {
+        const long size = std::ftell(f);
+        if (size > 0) buf.resize((size_t)size);
+        std::rewind(f);
+    }
+    const size_t got = buf.empty() ? 0 : std::fread(buf.data(), 1, buf.size(), f);
+    std::fclose(f);
+    if (got != buf.size() || buf.empty()) return set_error("cannot read %s", path);
+    return diskann_cuda_load_index(device, buf.data(), buf.size(), info, vectors, sq8);
 }
 
 }  // extern "C"

@@ -90,6 +90,42 @@ extern "C" {
     ) -> c_int;
 }
 
+/// `struct diskann_cuda_index_info`: header and segment offsets of a serialized index.
+#[repr(C)]
+#[derive(Default, Debug, Clone)]
+#[allow(dead_code)]
+pub struct DiskannCudaIndexInfo {
+    pub num_vectors: u32,
+    pub dimension: u32,
+    pub max_degree: u32,
+    pub num_entry_points: u32,
+    pub build_complexity: u32,
+    pub metric: u32,
+    pub entry_points_offset: u64,
+    pub vectors_offset: u64,
+    pub adjacency_offset: u64,
+    pub standard_size: u64,
+    pub has_sq8: c_int,
+    pub sq8_min_offset: u64,
+    pub sq8_scale_offset: u64,
+    pub sq8_codes_offset: u64,
+    pub sq8_codes_size: u64,
+}
+
+extern "C" {
+    /// Registers the vector segment (and the SQ8 trailer, if present) of the bytes written by
+    /// `InMemoryIndex::serialize_to_bytes` / `file_format::write_index` as device tables.
+    #[allow(dead_code)]
+    fn diskann_cuda_load_index(
+        device: c_int,
+        image: *const u8,
+        len: usize,
+        info: *mut DiskannCudaIndexInfo,
+        vectors: *mut *mut DiskannCudaTable,
+        sq8: *mut *mut DiskannCudaTable,
+    ) -> c_int;
+}
+
 /// `struct diskann_cuda_batch`: one batch of a multi-batch launch, device pointers.
 #[repr(C)]
 #[allow(dead_code)]

@@ -74,6 +74,41 @@ def multi_batch_distances_raw(queries, candidates, query_map, total_n, nq, dim, 
                                                                _p(out)))
 
 
+class IndexInfo(C.Structure):
+    """struct diskann_cuda_index_info of include/cuda_diskann_bridge.h"""
+    _fields_ = [("num_vectors", C.c_uint32), ("dimension", C.c_uint32), ("max_degree", C.c_uint32),
+                ("num_entry_points", C.c_uint32), ("build_complexity", C.c_uint32), ("metric", C.c_uint32),
+                ("entry_points_offset", C.c_uint64), ("vectors_offset", C.c_uint64), ("adjacency_offset", C.c_uint64),
+                ("standard_size", C.c_uint64), ("has_sq8", C.c_int), ("sq8_min_offset", C.c_uint64),
+                ("sq8_scale_offset", C.c_uint64), ("sq8_codes_offset", C.c_uint64), ("sq8_codes_size", C.c_uint64)]
+
+
+def parse_index(image: bytes) -> IndexInfo:
+    """Header and segment offsets of a serialized DiskANN index (no GPU needed)."""
+    info = IndexInfo()
+    p = _pkg()
+    p.check(p.lib().diskann_cuda_parse_index(image, len(image), C.byref(info)), "parse_index")
+    return info
+
+
+def load_index(image_or_path, device: int = 0):
+    """Registers the vector segment (and the SQ8 codes, if the image carries them) of a
+    serialized DiskANN index.  Returns (info, fp32 DeviceTable, SQ8 DeviceTable or None)."""
+    info = IndexInfo()
+    hv, hq = C.c_void_p(), C.c_void_p()
+    p = _pkg()
+    if isinstance(image_or_path, (bytes, bytearray, memoryview)):
+        image = bytes(image_or_path)
+        rc = p.lib().diskann_cuda_load_index(device, image, len(image), C.byref(info), C.byref(hv), C.byref(hq))
+    else:
+        rc = p.lib().diskann_cuda_load_index_file(device, str(image_or_path).encode(), C.byref(info), C.byref(hv),
+                                                  C.byref(hq))
+    p.check(rc, "load_index")
+    vec = DeviceTable(hv, info.num_vectors, info.dimension, False)
+    sq8 = DeviceTable(hq, info.num_vectors, info.dimension, True) if hq.value else None
+    return info, vec, sq8
+
+
 class _BatchDesc(C.Structure):
     """struct diskann_cuda_batch of include/cuda_diskann_bridge.h"""
     _fields_ = [("queries", C.c_void_p), ("ids", C.c_void_p), ("query_map", C.c_void_p),

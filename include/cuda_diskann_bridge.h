@@ -121,6 +121,40 @@ typedef struct diskann_cuda_batch {
 int diskann_cuda_batch_distances_by_id_device_multi(const diskann_cuda_table *table, const diskann_cuda_batch *batches,
                                                     int nbatches, int metric, void *stream);
 
+/* ---- serialized indexes -------------------------------------------------------------------
+ * The reference stores a DiskANN index as the ".diskann" v2 image
+ * (rust_lib/src/file_format.rs:3-18: 32-byte header "DANN", version 2, num_vectors,
+ * dimension, max_degree, num_entry_points, metric u8 (0 = L2, 1 = IP), 3 pad bytes,
+ * build_complexity; entry point ids; the fp32 vector segment; the u32 adjacency
+ * segment; all little-endian), optionally followed by the SQ8 trailer
+ * (rust_lib/src/index_manager.rs:513-533, read back at :629-668: "SQ8\0", dim u32,
+ * qlen u64, min[dim] f32, scale[dim] f32, qlen code bytes).  The calls below take
+ * such an image and put its vector segment (and its codes) on the device as tables
+ * for the by-id entry points, so a persisted index can be searched without the
+ * host gathering rows.  The graph (adjacency) stays with the caller. */
+typedef struct diskann_cuda_index_info {
+    uint32_t num_vectors, dimension, max_degree, num_entry_points, build_complexity;
+    uint32_t metric;            /* 0 = L2, 1 = inner product */
+    uint64_t entry_points_offset, vectors_offset, adjacency_offset;  /* byte offsets in the image */
+    uint64_t standard_size;     /* bytes of the image up to the end of the adjacency segment */
+    int has_sq8;                /* 1 when a well-formed SQ8 trailer follows */
+    uint64_t sq8_min_offset, sq8_scale_offset, sq8_codes_offset, sq8_codes_size;
+} diskann_cuda_index_info;
+
+/* Validates the image and fills `info`.  Pure host code (no GPU needed).  -1 for a bad
+ * magic / version, a truncated segment, a trailer whose dimension or length does not
+ * match the header. */
+int diskann_cuda_parse_index(const void *image, size_t len, diskann_cuda_index_info *info);
+
+/* Parses and registers: `*vectors` gets the fp32 table; `*sq8` (may be NULL if the
+ * caller does not want it) gets the SQ8 table, or NULL when the image has no trailer. */
+int diskann_cuda_load_index(int device, const void *image, size_t len, diskann_cuda_index_info *info,
+                            diskann_cuda_table **vectors, diskann_cuda_table **sq8);
+
+/* Same, reading the image from a file. */
+int diskann_cuda_load_index_file(int device, const char *path, diskann_cuda_index_info *info,
+                                 diskann_cuda_table **vectors, diskann_cuda_table **sq8);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -291,3 +291,60 @@ def ivf_search_given_probes(xb, list_off, list_rows, xq, k: int, probes, metric:
     if rc != 0:
         raise ValueError("oracle_ivf_search_given_probes: invalid arguments")
     return D, I
+
+
+# ---- serialized DiskANN index (".diskann" v2 image, rust_lib/src/file_format.rs:3-18, with the
+# ---- optional SQ8 trailer of rust_lib/src/index_manager.rs:513-533) ---------------------------
+def write_diskann_image(vectors, adjacency, entry_points, metric: int = 0, build_complexity: int = 64, sq8=None) -> bytes:
+    """vectors (n, d) float32; adjacency (n, max_degree) uint32 with 0xFFFFFFFF in unused slots;
+    entry_points: ids; sq8 = (mins, scale, codes) appends the trailer.  All little-endian."""
+    import struct
+    v = np.ascontiguousarray(vectors, "<f4")
+    a = np.ascontiguousarray(adjacency, "<u4")
+    e = np.ascontiguousarray(entry_points, "<u4")
+    out = bytearray()
+    out += b"DANN" + struct.pack("<IIIII", 2, v.shape[0], v.shape[1], a.shape[1], len(e))
+    out += struct.pack("<B3xI", metric, build_complexity)
+    assert len(out) == 32
+    out += e.tobytes() + v.tobytes() + a.tobytes()
+    if sq8 is not None:
+        mins, scale, codes = sq8
+        codes = np.ascontiguousarray(codes, np.uint8)
+        out += b"SQ8\0" + struct.pack("<IQ", v.shape[1], codes.size)
+        out += np.ascontiguousarray(mins, "<f4").tobytes() + np.ascontiguousarray(scale, "<f4").tobytes()
+        out += codes.tobytes()
+    return bytes(out)
+
+
+def parse_diskann_image(image: bytes) -> dict:
+    """Restates FileHeader::read and InMemoryIndex::from_bytes (rust_lib/src/index_manager.rs:560-668):
+    returns the header fields, the segments as arrays and, if present, the SQ8 section."""
+    import struct
+    if len(image) < 32 or image[:4] != b"DANN":
+        raise ValueError("not a .diskann image")
+    version, n, d, deg, ne = struct.unpack_from("<IIIII", image, 4)
+    metric = image[24]
+    (bc,) = struct.unpack_from("<I", image, 28)
+    if version != 2:
+        raise ValueError("unsupported version")
+    off = 32
+    entry = np.frombuffer(image, "<u4", ne, off)
+    off += ne * 4
+    if off + n * d * 4 + n * deg * 4 > len(image):
+        raise ValueError("truncated")
+    vec = np.frombuffer(image, "<f4", n * d, off).reshape(n, d)
+    off += n * d * 4
+    adj = np.frombuffer(image, "<u4", n * deg, off).reshape(n, deg)
+    off += n * deg * 4
+    res = {"num_vectors": n, "dimension": d, "max_degree": deg, "metric": metric, "build_complexity": bc,
+           "entry_points": entry, "vectors": vec, "adjacency": adj, "standard_size": off, "sq8": None}
+    if len(image) > off + 4 and image[off:off + 4] == b"SQ8\0":
+        sq_dim, qlen = struct.unpack_from("<IQ", image, off + 4)
+        p = off + 16
+        if p + sq_dim * 8 + qlen > len(image):
+            raise ValueError("SQ8 section truncated")
+        mins = np.frombuffer(image, "<f4", sq_dim, p)
+        scale = np.frombuffer(image, "<f4", sq_dim, p + sq_dim * 4)
+        codes = np.frombuffer(image, np.uint8, qlen, p + sq_dim * 8).reshape(n, sq_dim)
+        res["sq8"] = (mins, scale, codes)
+    return res
