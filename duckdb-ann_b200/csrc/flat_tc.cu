@@ -274,6 +274,9 @@ struct KernelArgs {
     // Grouped L2 with residual queries (may be null): constant K of every gathered row such that
     // key + K is comparable between the lists of one query; keys inside the kernel leave it out
     const float *qrow_const;
+    // Grouped append mode (may be null): a finished row leaves its append buffer unsorted and
+    // writes its fill count here (index = slot * 128 + row); the merge filters and sorts
+    int32_t *part_cnt;
     float *part_key;
     int32_t *part_idx;
     uint32_t *qtau;  // per query: smallest k-th-best key any chunk has published (ordered-uint form)
@@ -297,7 +300,7 @@ enum { kStatCompactRows = 0, kStatAppends = 1, kStatCompactCycles = 2, kStatEpiW
        kStatMmaWaitSmem = 5, kStatEpiTileCycles = 6, kStatTiles = 7 };
 
 enum SelMode { kSelSmem = 0, kSelAppend = 1, kSelReplace = 2 };
-constexpr int kBuf = 512;  // candidate slots per row in append mode
+constexpr int kBuf = kAppendBuffer;  // candidate slots per row in append mode
 static_assert(kAppendMaxK <= kBuf / 2, "a compacted row must leave room for new candidates");
 
 // ---- bitonic sort of (key, idx) pairs held by a warp, E per lane ---------------------------------
@@ -641,9 +644,14 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
         int cnt = 0;             // queue fill (large k)
         int pos = 0;             // slot of the current maximum (small k)
         const int stride = APPEND ? kBuf : k;  // slots per row in the list memory
+        int cur_slot = 0;
         auto close_list = [&]() {
             if (!unit_key) return;
-            if (APPEND) {
+            if (APPEND && args.part_cnt) {
+                // the per-query merge sees the final threshold of the query and throws most of
+                // these entries away before it sorts: nothing to do here but say how many there are
+                args.part_cnt[(size_t)cur_slot * BM + row] = row_valid ? cnt : 0;
+            } else if (APPEND) {
                 const unsigned need = __ballot_sync(kFullMask, cnt > 0);
                 if (need) compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word, koff);
                 if (!((need >> lane) & 1u)) {  // no candidate ever reached this row: an empty list
@@ -669,6 +677,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             if (qt < 0) break;
             if (fresh) {
                 close_list();
+                cur_slot = slot;
                 unit_key = args.part_key + (size_t)slot * BM * stride;
                 unit_idx = args.part_idx + (size_t)slot * BM * stride;
                 if (args.items) {
@@ -992,6 +1001,7 @@ int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, con
     a.item_counter = grouped ? grouped->item_counter : nullptr;
     a.qrow_query = grouped ? grouped->qrow_query : nullptr;
     a.qrow_const = grouped ? grouped->qrow_const : nullptr;
+    a.part_cnt = grouped ? grouped->part_cnt : nullptr;
     {
         const char *e = getenv("ANN_CUDA_TC_DEBUG");
         a.debug = e ? atoi(e) : 0;

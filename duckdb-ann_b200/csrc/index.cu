@@ -116,7 +116,7 @@ struct Workspace {
     cudaStream_t own_stream = nullptr;
     cudaStream_t bound = nullptr;  // stream whose work may still use these buffers
     GrowBuf x, qhi, qlo, qn, part_key, part_idx, sel_key, sel_idx, status, out_d, out_i;
-    GrowBuf item_q, item_rb, item_re, item_slot, scratch, probes_key, probes, qtau, sched, gq, items, qconst;
+    GrowBuf item_q, item_rb, item_re, item_slot, scratch, probes_key, probes, qtau, sched, gq, items, qconst, part_cnt;
     int *status_host = nullptr;  // pinned
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;  // bracket the flat kernel when timing is on
     bool timed = false;
@@ -125,7 +125,7 @@ struct Workspace {
         if (ev1) cudaEventDestroy(ev1);
         for (GrowBuf *b : {&x, &qhi, &qlo, &qn, &part_key, &part_idx, &sel_key, &sel_idx, &status, &out_d, &out_i,
                            &item_q, &item_rb, &item_re, &item_slot, &scratch, &probes_key, &probes, &qtau, &sched, &gq, &items,
-                           &qconst})
+                           &qconst, &part_cnt})
             b->release();
         if (status_host) cudaFreeHost(status_host);
         if (own_stream) cudaStreamDestroy(own_stream);
@@ -673,7 +673,12 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
                                   ws.qlo.as<float>(), stream, residual ? ws.items.as<int4>() : nullptr,
                                   residual ? ix.store.hi : nullptr, residual ? ix.store.lo : nullptr, qconst))
             return -1;
-        GroupedWork gw{ws.items.as<int4>(), n_tiles, item_counter, ws.gq.as<int32_t>(), qconst};
+        // append mode: finished rows stay unsorted, the per-query merge filters them by the
+        // query's final threshold before it sorts (see merge_filtered_kernel)
+        const bool filtered = plan.lists_sorted && (int64_t)k_sel * 2 <= 2048;
+        if (filtered && ws.part_cnt.ensure((size_t)max_rows * 4)) return -1;
+        GroupedWork gw{ws.items.as<int4>(), n_tiles, item_counter, ws.gq.as<int32_t>(), qconst,
+                       filtered ? ws.part_cnt.as<int32_t>() : nullptr};
         const bool timing = g_time_kernels.load(std::memory_order_relaxed) != 0;
         if (timing) {
             if (!ws.ev0) {
@@ -694,9 +699,15 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
         }
         ANN_CUDA_TRY(cudaMemcpyAsync(ws.status_host, ws.status.ptr, 4, cudaMemcpyDeviceToHost, stream));
         if (ws.sel_key.ensure((size_t)nq * k_sel * 4) || ws.sel_idx.ensure((size_t)nq * k_sel * 4)) return -1;
-        if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, nullptr, ws.item_slot.as<int32_t>(),
-                               nprobe, nq, k_sel, plan.list_stride, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(),
-                               ix.device, stream, plan.lists_sorted, qconst))
+        if (filtered) {
+            if (launch_merge_filtered(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.part_cnt.as<int32_t>(),
+                                      ws.item_slot.as<int32_t>(), qconst, ws.qtau.as<uint32_t>(), nprobe, nq, k_sel,
+                                      ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), stream))
+                return -1;
+        } else if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, nullptr,
+                                      ws.item_slot.as<int32_t>(), nprobe, nq, k_sel, plan.list_stride,
+                                      ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream,
+                                      plan.lists_sorted, qconst))
             return -1;
         // IP: the selected distances are recomputed exactly from hi + lo, as for Flat.  L2: the
         // residual form keeps the scan's own distance accurate unless the row nearly coincides

@@ -68,6 +68,9 @@ struct GroupedWork {
     int *item_counter;  // zero on entry
     const int32_t *qrow_query;
     const float *qrow_const = nullptr;  // per gathered row: add to a key to compare across lists (null = 0)
+    // append mode only (16 < k <= kAppendMaxK), may be null: finished rows keep their append
+    // buffer unsorted and write its fill count to part_cnt[gathered row]; use launch_merge_filtered
+    int32_t *part_cnt = nullptr;
 };
 FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms);
 
@@ -136,6 +139,16 @@ int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layou
                        const int32_t *slot_of, int nparts, int64_t nq, int k, int list_stride, float *out_key,
                        int32_t *out_idx, int device, cudaStream_t stream, bool lists_sorted = false,
                        const float *slot_key_offset = nullptr);
+
+// Grouped list scan with GroupedWork::part_cnt: per query, the k best of the append buffers of
+// its nparts lists (gathered row slot_of[q * nparts + p], -1 = none; buffer = the first
+// part_cnt[row] of kAppendBuffer slots at part_*[row * kAppendBuffer]), sorted best first.
+// Entries above the query's final threshold qtau[q] (ordered-uint form, key + slot_key_offset[row])
+// are dropped before anything is sorted.
+constexpr int kAppendBuffer = 512;
+int launch_merge_filtered(const float *part_key, const int32_t *part_idx, const int32_t *part_cnt,
+                          const int32_t *slot_of, const float *slot_key_offset, const uint32_t *qtau, int nparts,
+                          int64_t nq, int k, float *out_key, int32_t *out_idx, cudaStream_t stream);
 
 // Flat: recomputes the distance of every selected (query, row) pair in exact fp32
 // from the split store, sorts the k results best first and writes the user-facing

@@ -178,6 +178,72 @@ merge_sorted_kernel(const float *__restrict__ part_key, const int32_t *__restric
     }
 }
 
+// Streaming top-k over the unsorted append buffers of one query's lists.  Candidates above the
+// query's final threshold are dropped as they are read; the survivors collect in a shared
+// buffer of kFilterCap pairs; when the next round of reads might not fit, the buffer is sorted,
+// cut to its best k and its k-th key becomes the threshold.  Exact for any input; with the
+// threshold the scan kernel leaves behind, the usual case is one small sort at the end.
+constexpr int kFilterCap = 2048;
+__global__ void __launch_bounds__(kMergeThreads)
+merge_filtered_kernel(const float *__restrict__ part_key, const int32_t *__restrict__ part_idx,
+                      const int32_t *__restrict__ part_cnt, const int32_t *__restrict__ slot_of,
+                      const float *__restrict__ slot_key_offset, const uint32_t *__restrict__ qtau, int nparts,
+                      int k, float *__restrict__ out_key, int32_t *__restrict__ out_idx) {
+    __shared__ float keys[kFilterCap];
+    __shared__ int32_t vals[kFilterCap];
+    __shared__ int count;
+    const int64_t q = blockIdx.x;
+    if (threadIdx.x == 0) count = 0;
+    // the scan's threshold was rounded up when it was published: a key equal to it stays in
+    float tau = ordered_to_float(qtau[q]);
+    if (!(tau == tau)) tau = kInf;  // nothing published
+    __syncthreads();
+    auto shrink = [&]() {  // sort what is there, keep the best k, tighten the threshold
+        __syncthreads();
+        const int c = count;
+        int P = 2;
+        while (P < c) P <<= 1;
+        for (int t = c + threadIdx.x; t < P; t += blockDim.x) {
+            keys[t] = kInf;
+            vals[t] = 0x7fffffff;
+        }
+        bitonic_sort(keys, vals, P);
+        if (c > k) {
+            tau = fminf(tau, keys[k - 1]);
+            __syncthreads();
+            if (threadIdx.x == 0) count = k;
+        }
+        __syncthreads();
+    };
+    for (int p = 0; p < nparts; p++) {
+        const int32_t g = slot_of[q * nparts + p];
+        if (g < 0) continue;  // block-uniform
+        const int c = part_cnt[g];
+        const float off = slot_key_offset ? slot_key_offset[g] : 0.f;
+        for (int j0 = 0; j0 < c; j0 += blockDim.x) {
+            if (count + (int)blockDim.x > kFilterCap) shrink();  // block-uniform: count is read after a barrier
+            const int j = j0 + threadIdx.x;
+            if (j < c) {
+                const int32_t idx = part_idx[(size_t)g * kAppendBuffer + j];
+                const float key = part_key[(size_t)g * kAppendBuffer + j] + off;
+                if (idx >= 0 && key <= tau) {
+                    const int pos = atomicAdd(&count, 1);
+                    keys[pos] = key;
+                    vals[pos] = idx;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    shrink();
+    const int c = count;
+    for (int j = threadIdx.x; j < k; j += blockDim.x) {
+        const bool ok = j < c && vals[j] != 0x7fffffff;
+        out_key[q * k + j] = ok ? keys[j] : kInf;
+        out_idx[q * k + j] = ok ? vals[j] : -1;
+    }
+}
+
 // Exact fp32 re-evaluation of the selected pairs, sort, and user-facing output.
 __global__ void __launch_bounds__(128)
 refine_finalize_kernel(const float *__restrict__ xhi, const float *__restrict__ xlo, int dp, int d,
@@ -358,6 +424,18 @@ int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layou
     merge_parts_kernel<<<(unsigned)nq, kMergeThreads, smem, stream>>>(part_key, part_idx, layout, lists_started, slot_of,
                                                                       nparts, nq, k, list_stride, P, slot_key_offset, out_key,
                                                                       out_idx);
+    count_launch();
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int launch_merge_filtered(const float *part_key, const int32_t *part_idx, const int32_t *part_cnt,
+                          const int32_t *slot_of, const float *slot_key_offset, const uint32_t *qtau, int nparts,
+                          int64_t nq, int k, float *out_key, int32_t *out_idx, cudaStream_t stream) {
+    if (nq <= 0) return 0;
+    if (k > kFilterCap / 2) return set_error("merge: k = %d is too large for the filtered merge", k);
+    merge_filtered_kernel<<<(unsigned)nq, kMergeThreads, 0, stream>>>(part_key, part_idx, part_cnt, slot_of,
+                                                                     slot_key_offset, qtau, nparts, k, out_key, out_idx);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
