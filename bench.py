@@ -287,7 +287,7 @@ class FlatWorkload:
 
 # DRAM read + write bytes of one grouped list-scan launch, keyed by (rows, queries, GPUs), from the
 # ncu capture summarised in profiles/flat_tc_kernel__ivf_1m.md
-IVF_SCAN_TRAFFIC = {}
+IVF_SCAN_TRAFFIC = {(1_000_000, 10_000, 1): 16.28e9}
 
 
 class IvfWorkload:
@@ -552,9 +552,9 @@ class BatchWorkload:
         # profiles/batch_distance_f32_kernel__batch_c2.md and profiles/batch_distance_sq8_dp4a_kernel__sq8_c5.md
         traffic = None
         if self.sq8 and (self.nq, self.per, self.dim) == (1024, 128, 384):
-            traffic = 67.5e6
+            traffic = 61.1e6   # per batch of the multi-batch launch
         if not self.sq8 and (self.nq, self.per, self.dim) == (256, 128, 1536):
-            traffic = 204.5e6
+            traffic = 199.0e6  # per batch of the multi-batch launch
         return {"bound": "hbm", "achieved": None, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None,
                 "traffic": traffic, "kernel": "batch_distance_sq8_dp4a_kernel" if self.sq8 else "batch_distance_f32_kernel"}
 

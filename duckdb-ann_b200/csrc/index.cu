@@ -210,14 +210,16 @@ constexpr int64_t kQueryBlock = 16384;  // queries per pass, bounds the scratch 
 
 // ---- k-means helper kernels (index build, not the search path) -------------------------------
 __global__ void kmeans_accumulate_kernel(const float *__restrict__ x, int64_t n, int d, const int32_t *__restrict__ assign,
-                                         float *__restrict__ sums, int *__restrict__ counts) {
+                                         double *__restrict__ sums, int *__restrict__ counts) {
     const int lane = threadIdx.x & 31;
     for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n;
          r += (int64_t)gridDim.x * (blockDim.x >> 5)) {
         const int c = assign[r];
         if (c < 0) continue;
         if (lane == 0) atomicAdd(&counts[c], 1);
-        for (int j = lane; j < d; j += 32) atomicAdd(&sums[(int64_t)c * d + j], x[r * (int64_t)d + j]);
+        // double sums: the order of the atomic adds then cannot change the rounded centroid, so
+        // training gives the same lists on every run
+        for (int j = lane; j < d; j += 32) atomicAdd(&sums[(int64_t)c * d + j], (double)x[r * (int64_t)d + j]);
     }
 }
 // k-means++-style seeding, one step: every point updates its squared distance to the
@@ -261,12 +263,12 @@ __global__ void kmeanspp_take_kernel(const float *__restrict__ x, int d, float *
     __syncthreads();
     if (threadIdx.x == 0) *best = 0ull;
 }
-__global__ void kmeans_update_kernel(float *__restrict__ cent, const float *__restrict__ sums,
+__global__ void kmeans_update_kernel(float *__restrict__ cent, const double *__restrict__ sums,
                                      const int *__restrict__ counts, int64_t nlist, int d) {
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= nlist * d) return;
     const int c = (int)(t / d);
-    if (counts[c] > 0) cent[t] = sums[t] / (float)counts[c];  // an empty cluster keeps its centroid
+    if (counts[c] > 0) cent[t] = (float)(sums[t] / (double)counts[c]);  // an empty cluster keeps its centroid
 }
 __global__ void gather_rows_kernel(const float *__restrict__ shi, const float *__restrict__ slo,
                                    const float *__restrict__ snorm, const int64_t *__restrict__ src_ids,
@@ -947,7 +949,8 @@ int ann_cuda_ivfflat_train(ann_cuda_index *ix, int64_t n, const float *x) {
     if (ensure_device(ix, g)) return -1;
     const int d = ix->d;
     const int64_t nlist = ix->nlist;
-    float *dx = nullptr, *cent = nullptr, *sums = nullptr;
+    float *dx = nullptr, *cent = nullptr;
+    double *sums = nullptr;
     int *counts = nullptr;
     int32_t *dassign = nullptr;
     int rc = 0;
@@ -956,7 +959,7 @@ int ann_cuda_ivfflat_train(ann_cuda_index *ix, int64_t n, const float *x) {
             if (p) cudaFree(p);
     };
     if (cudaMalloc(&dx, (size_t)n * d * 4) != cudaSuccess || cudaMalloc(&cent, (size_t)nlist * d * 4) != cudaSuccess ||
-        cudaMalloc(&sums, (size_t)nlist * d * 4) != cudaSuccess || cudaMalloc(&counts, (size_t)nlist * 4) != cudaSuccess ||
+        cudaMalloc(&sums, (size_t)nlist * d * 8) != cudaSuccess || cudaMalloc(&counts, (size_t)nlist * 4) != cudaSuccess ||
         cudaMalloc(&dassign, (size_t)n * 4) != cudaSuccess) {
         cudaGetLastError();
         cleanup();
@@ -1010,7 +1013,7 @@ int ann_cuda_ivfflat_train(ann_cuda_index *ix, int64_t n, const float *x) {
         if (rc == 0) rc = ivf_assign_device(*ix, dx, n, assign, false);  // Lloyd steps: the fast ranking will do
         if (rc) break;
         cudaMemcpy(dassign, assign.data(), (size_t)n * 4, cudaMemcpyHostToDevice);
-        cudaMemset(sums, 0, (size_t)nlist * d * 4);
+        cudaMemset(sums, 0, (size_t)nlist * d * 8);
         cudaMemset(counts, 0, (size_t)nlist * 4);
         kmeans_accumulate_kernel<<<(unsigned)std::min<int64_t>((n + 7) / 8, 148 * 16), 256>>>(dx, n, d, dassign, sums, counts);
         kmeans_update_kernel<<<(unsigned)((nlist * d + 255) / 256), 256>>>(cent, sums, counts, nlist, d);
