@@ -238,8 +238,7 @@ __global__ void group_items_kernel(const int *__restrict__ counts, const int *__
 
 __global__ void group_place_kernel(const int32_t *__restrict__ probes, int64_t n, int nprobe, int64_t nlist,
                                    const int64_t *__restrict__ list_off, const int *__restrict__ tile_off,
-                                   const int *__restrict__ n_tiles, int *cursors, int32_t *__restrict__ qrow_query,
-                                   int32_t *__restrict__ gslot) {
+                                   int *cursors, int32_t *__restrict__ qrow_query, int32_t *__restrict__ gslot) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int l = probes[i];
@@ -248,12 +247,8 @@ __global__ void group_place_kernel(const int32_t *__restrict__ probes, int64_t n
         gslot[i] = -1;
         return;
     }
-    // The queries of a list are dealt round-robin over its tiles, so the tiles are equally
-    // full: the CTAs scanning the same list for different query tiles then do the same amount
-    // of selection work, stay in step, and the second one finds the list rows in L2.
     const int pos = atomicAdd(&cursors[l], 1);
-    const int tiles = (l + 1 < nlist ? tile_off[l + 1] : *n_tiles) - tile_off[l];
-    const int g = (tile_off[l] + pos % tiles) * 128 + pos / tiles;
+    const int g = tile_off[l] * 128 + pos;
     qrow_query[g] = (int32_t)(i / nprobe);
     gslot[i] = g;
 }
@@ -329,8 +324,7 @@ int launch_group_probes(const int32_t *probes, int64_t nq, int nprobe, int64_t n
     group_tiles_kernel<<<1, 1024, 0, stream>>>(counts, second, nlist, n_tiles);
     group_items_kernel<<<(unsigned)((nlist + 255) / 256), 256, 0, stream>>>(counts, second, nlist, list_off, items);
     ANN_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)(nlist + 1), stream));
-    group_place_kernel<<<blocks, 256, 0, stream>>>(probes, n, nprobe, nlist, list_off, second, n_tiles, counts, qrow_query,
-                                                   gslot);
+    group_place_kernel<<<blocks, 256, 0, stream>>>(probes, n, nprobe, nlist, list_off, second, counts, qrow_query, gslot);
     count_launch(4);
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
