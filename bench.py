@@ -217,7 +217,7 @@ class FlatWorkload:
         return {"workload": self.name, "rows": self.n, "dim": self.d, "queries": self.nq, "k": self.k,
                 "metric": self.metric_name, "sharding": f"rows/{world}", "distribution": self.dist_kind,
                 "l2_flush": "database shard (>= 7 GB per GPU) is far larger than L2; no explicit flush"
-                if self.n * self.d * 8 / max(world, 1) > 1e9 else "database is L2-sized: see DESIGN.md",
+                if self.n * self.d * 8 / max(world, 1) > 1e9 else "database is L2-sized (a warm-cache figure; the full-size workload is the headline)",
                 "flat_kernel": self.pkg.lib().ann_cuda_flat_kernel_name().decode() if getattr(self, "pkg", None)
                 else "cpu"}
 
