@@ -227,7 +227,7 @@ class FlatWorkload:
         achieved = flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms and kernel_ms > 0 else None
         peak = peaks["bf16_tflops_sustained"] / 6.0
         # DRAM traffic of one launch, from the ncu capture of this kernel on 400,000 rows
-        # (profiles/flat_tc_kernel__flat_ip_20m.md: 16.2-22.3 GB read + 0.47-0.49 GB written per
+        # (summarised with the other profile summaries: 16.2-22.3 GB read + 0.47-0.49 GB written per
         # launch with 4,096 queries of 768 dimensions), scaled by the rows and query tiles of this
         # launch: every 128-query tile streams the shard once, L2 absorbs part of it.
         traffic = None
@@ -286,7 +286,7 @@ class FlatWorkload:
 
 
 # DRAM read + write bytes of one grouped list-scan launch, keyed by (rows, queries, GPUs), from the
-# ncu capture summarised in profiles/flat_tc_kernel__ivf_1m.md
+# ncu capture of the grouped list scan at the default shape (16.05 GB read + 0.23 GB written)
 IVF_SCAN_TRAFFIC = {(1_000_000, 10_000, 1): 16.28e9}
 
 
@@ -549,7 +549,7 @@ class BatchWorkload:
 
     def roofline(self, peaks, kernel_ms):
         # DRAM read + write of one launch at the default shapes, from the ncu captures summarised in
-        # profiles/batch_distance_f32_kernel__batch_c2.md and profiles/batch_distance_sq8_dp4a_kernel__sq8_c5.md
+        # the profile summaries of the two batch-distance kernels
         traffic = None
         if self.sq8 and (self.nq, self.per, self.dim) == (1024, 128, 384):
             traffic = 61.1e6   # per batch of the multi-batch launch
