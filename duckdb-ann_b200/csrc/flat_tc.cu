@@ -69,6 +69,9 @@ constexpr int BN = 256;           // database rows per tile (TMEM columns)
 constexpr int BK = ANN_TC_BK;     // floats per K block: 32 = one 128-byte swizzled row, 16 = one 64-byte row
 static_assert(BK == 32 || BK == 16, "K block is one 128-byte or one 64-byte swizzled row");
 constexpr int kStages = 64 / BK;  // the ring always holds 64 floats of K: 2 x 96 KB or 4 x 48 KB
+// Screened mode needs the hi planes only: the lo half of every stage serves as a stage of its own,
+// so the ring is twice as deep (stage s = planes s & 1 of the physical stage s >> 1).
+constexpr int kMaxStages = 2 * kStages;
 constexpr int kRowBytes = BK * 4;
 constexpr uint64_t kDescLayout = BK == 32 ? 2ull : 4ull;    // SWIZZLE_128B : SWIZZLE_64B
 constexpr uint64_t kDescSbo = (8 * kRowBytes) >> 4;         // 8-row group stride, in 16-byte units
@@ -85,8 +88,8 @@ struct SmemLayout {
     static constexpr int queue_idx = queue_key + kQueueDepth * BM * 4;
     static constexpr int xnorm = queue_idx + kQueueDepth * BM * 4;
     static constexpr int barriers = xnorm + 4 * 2 * BN * 4;  // (after a private norm copy per epilogue warp)
-    // barriers: full[kStages] empty[kStages] tmem_full[2] tmem_empty[2]
-    static constexpr int work_bars = barriers + (2 * kStages + 4) * 8;  // wfull[kWorkRing] wempty[kWorkRing]
+    // barriers: full[kMaxStages] empty[kMaxStages] tmem_full[2] tmem_empty[2]
+    static constexpr int work_bars = barriers + (2 * kMaxStages + 4) * 8;  // wfull[kWorkRing] wempty[kWorkRing]
     static constexpr int work_ring = work_bars + 2 * kWorkRing * 8;    // kWorkRing descriptors of 32 bytes
     static constexpr int tmem_ptr = work_ring + kWorkRing * 32;
     static constexpr int abort_flag = tmem_ptr + 4;
@@ -277,6 +280,20 @@ struct KernelArgs {
     // Grouped append mode (may be null): a finished row leaves its append buffer unsorted and
     // writes its fill count here (index = slot * 128 + row); the merge filters and sorts
     int32_t *part_cnt;
+    // Screened mode (flat search, append selection; 0 = off).  The tensor cores form q_hi.x_hi
+    // only: one MMA per K step instead of three, and only the hi planes travel through shared
+    // memory.  That dot product is within  E = (2^-10 + d 2^-23) |q||x|  of the exact one (each
+    // operand is rounded to 11 significant bits; fp32 accumulation), so all keys of a query are
+    // within E' (E for IP, 2E for L2) of the exact ones, |x| taken as the largest norm in the
+    // store.  If K is the k_rank-th smallest coarse key, the exact k_rank-th best is at most
+    // K + E', and a row can be among the k_rank best only if its coarse key is <= K + 2E'.  The
+    // lists therefore keep k > k_rank entries, the threshold is the k_rank-th key + 2E', and the
+    // caller re-ranks the k candidates it gets back by their exact fp32 distance.
+    int screen;
+    int k_rank;                   // = k when not screening
+    const float *q_norm2;         // per query |q - mu|^2 (L2, mu = the store's reference point) or |q|^2 (IP)
+    const unsigned *x_max_norm2;  // bits of the largest |x|^2 in the store
+    int d;
     float *part_key;
     int32_t *part_idx;
     uint32_t *qtau;  // per query: smallest k-th-best key any chunk has published (ordered-uint form)
@@ -301,7 +318,7 @@ enum { kStatCompactRows = 0, kStatAppends = 1, kStatCompactCycles = 2, kStatEpiW
 
 enum SelMode { kSelSmem = 0, kSelAppend = 1, kSelReplace = 2 };
 constexpr int kBuf = kAppendBuffer;  // candidate slots per row in append mode
-static_assert(kAppendMaxK <= kBuf / 2, "a compacted row must leave room for new candidates");
+static_assert(kAppendMaxK <= kBuf / 2 && kScreenMaxList <= kBuf / 2, "a compacted row must leave room for new candidates");
 
 // ---- bitonic sort of (key, idx) pairs held by a warp, E per lane ---------------------------------
 // Keys are order-preserving uint32 images of the float keys.  Element e lives in lane e / E,
@@ -358,9 +375,10 @@ __device__ __forceinline__ void warp_sort(uint32_t (&key)[E], int32_t (&idx)[E],
 }
 
 // Sorts the first 32 * E slots of one row's append buffer (c <= 32 * E of them filled), writes
-// the best k back in order (index -1 past the end) and returns the k-th best key (+inf if c < k).
+// the best k back in order (index -1 past the end) and returns the k_rank-th best key (k_rank <= k;
+// meaningful only if c >= k_rank).
 template <int E>
-__device__ __forceinline__ float compact_one(float *bk, int32_t *bi, int c, int k, int lane) {
+__device__ __forceinline__ float compact_one(float *bk, int32_t *bi, int c, int k, int k_rank, int lane) {
     uint32_t key[E];
     int32_t idx[E];
     if (E >= 4) {
@@ -393,13 +411,12 @@ __device__ __forceinline__ float compact_one(float *bk, int32_t *bi, int c, int 
         const float kf = ordered_to_float(key[i]);
         st_global_if(e < k, bk + e, kf);
         st_global_if(e < k, bi + e, idx[i]);
-        kth = (e == k - 1) ? kf : kth;
+        kth = (e == k_rank - 1) ? kf : kth;
     }
-    if (32 * E < k) {  // the list is shorter than k: mark the rest empty
+    if (32 * E < k)  // the sorted part is shorter than the list: mark the rest empty
         for (int e = 32 * E + lane; e < k; e += 32) bi[e] = -1;
-        return kInf;
-    }
-    return __shfl_sync(kFullMask, kth, (k - 1) / E);
+    if (32 * E < k_rank) return kInf;
+    return __shfl_sync(kFullMask, kth, (k_rank - 1) / E);
 }
 
 // Compacts the append buffers of the rows in `need` (bit r = row row0 + r of this warp) down to
@@ -407,7 +424,8 @@ __device__ __forceinline__ float compact_one(float *bk, int32_t *bi, int c, int 
 // 512-wide network (~14k cycles); the few dozen entries typical when a list is closed behind a
 // tight threshold take the 32- or 64-wide one (a few hundred cycles).
 __device__ __noinline__ void compact_rows(float *slot_key, int32_t *slot_idx, int k, int row0, unsigned need, int &cnt,
-                                          float &tau, int lane, uint32_t *qtau_word, float koff) {
+                                          float &tau, int lane, uint32_t *qtau_word, float koff, int k_rank,
+                                          float slack) {
     __syncwarp();  // the appends of every lane are visible to the whole warp
     while (need) {
         const int r = __ffs(need) - 1;
@@ -416,17 +434,19 @@ __device__ __noinline__ void compact_rows(float *slot_key, int32_t *slot_idx, in
         float *bk = slot_key + (size_t)(row0 + r) * kBuf;
         int32_t *bi = slot_idx + (size_t)(row0 + r) * kBuf;
         float kth;
-        if (c > 256) kth = compact_one<16>(bk, bi, c, k, lane);
-        else if (c > 128) kth = compact_one<8>(bk, bi, c, k, lane);
-        else if (c > 64) kth = compact_one<4>(bk, bi, c, k, lane);
-        else if (c > 32) kth = compact_one<2>(bk, bi, c, k, lane);
-        else kth = compact_one<1>(bk, bi, c, k, lane);
+        if (c > 256) kth = compact_one<16>(bk, bi, c, k, k_rank, lane);
+        else if (c > 128) kth = compact_one<8>(bk, bi, c, k, k_rank, lane);
+        else if (c > 64) kth = compact_one<4>(bk, bi, c, k, k_rank, lane);
+        else if (c > 32) kth = compact_one<2>(bk, bi, c, k, k_rank, lane);
+        else kth = compact_one<1>(bk, bi, c, k, k_rank, lane);
         if (lane == r) {
             cnt = c < k ? c : k;
-            if (c >= k) {
-                // the k-th best key so far: nothing above it can reach the final top-k
-                tau = fminf(tau, kth);
-                atomicMin(qtau_word, float_to_ordered(__fadd_ru(kth, koff)));
+            if (c >= k_rank) {
+                // the k_rank-th best key so far (plus this row's error slack when the keys are
+                // coarse): nothing above it can reach the final top k_rank
+                const float thr = kth + slack;
+                tau = fminf(tau, thr);
+                atomicMin(qtau_word, float_to_ordered(__fadd_ru(thr, koff)));
             }
         }
     }
@@ -447,8 +467,9 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
     int32_t *qidx = reinterpret_cast<int32_t *>(smem + SmemLayout::queue_idx);
     float *xn_all = reinterpret_cast<float *>(smem + SmemLayout::xnorm);
     const uint32_t bar_full = smem_base + SmemLayout::barriers;
-    const uint32_t bar_empty = bar_full + 8 * kStages;
-    const uint32_t bar_tfull = bar_empty + 8 * kStages;
+    const uint32_t bar_empty = bar_full + 8 * kMaxStages;
+    const uint32_t bar_tfull = bar_empty + 8 * kMaxStages;
+    const uint32_t nstages = args.screen ? kMaxStages : kStages;
     const uint32_t bar_tempty = bar_tfull + 16;
     volatile uint32_t *tmem_ptr_s = reinterpret_cast<volatile uint32_t *>(smem + SmemLayout::tmem_ptr);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + SmemLayout::abort_flag);
@@ -456,7 +477,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; s++) {
+        for (int s = 0; s < kMaxStages; s++) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
@@ -555,13 +576,20 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     for (int kb = 0; kb < args.kblocks; kb++) {
                         if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, args.status, 1)) goto done;
                         const uint32_t full = bar_full + 8 * stage;
-                        const uint32_t base = smem_base + stage * kStageBytes;
-                        mbar_expect_tx(full, kStageBytes);
-                        tma_load_2d(base, &map_qhi, kb * BK, cur * BM, full);
-                        tma_load_2d(base + kABytes, &map_qlo, kb * BK, cur * BM, full);
-                        tma_load_2d(base + 2 * kABytes, &map_xhi, kb * BK, (int32_t)trow, full);
-                        tma_load_2d(base + 2 * kABytes + kBBytes, &map_xlo, kb * BK, (int32_t)trow, full);
-                        if (++stage == kStages) {
+                        if (args.screen) {  // hi planes only, into plane set stage & 1 of stage >> 1
+                            const uint32_t base = smem_base + (stage >> 1) * kStageBytes;
+                            mbar_expect_tx(full, kABytes + kBBytes);
+                            tma_load_2d(base + (stage & 1) * kABytes, &map_qhi, kb * BK, cur * BM, full);
+                            tma_load_2d(base + 2 * kABytes + (stage & 1) * kBBytes, &map_xhi, kb * BK, (int32_t)trow, full);
+                        } else {
+                            const uint32_t base = smem_base + stage * kStageBytes;
+                            mbar_expect_tx(full, kStageBytes);
+                            tma_load_2d(base, &map_qhi, kb * BK, cur * BM, full);
+                            tma_load_2d(base + kABytes, &map_qlo, kb * BK, cur * BM, full);
+                            tma_load_2d(base + 2 * kABytes, &map_xhi, kb * BK, (int32_t)trow, full);
+                            tma_load_2d(base + 2 * kABytes + kBBytes, &map_xlo, kb * BK, (int32_t)trow, full);
+                        }
+                        if (++stage == nstages) {
                             stage = 0;
                             phase ^= 1;
                         }
@@ -600,20 +628,25 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, args.status, 3)) goto done;
                         if (args.stats) atomicAdd(args.stats + kStatMmaWaitSmem, (unsigned long long)(clock64() - t0));
                         tmem_fence_after();
-                        const uint32_t base = smem_base + stage * kStageBytes;
+                        const uint32_t base = smem_base + (args.screen ? (stage >> 1) : stage) * kStageBytes;
+                        const uint32_t sub = args.screen ? (stage & 1) : 0;
 #pragma unroll
                         for (int ks = 0; ks < BK / 8; ks++) {
-                            const uint64_t a_hi = make_smem_desc(base + ks * 32);
+                            const uint64_t a_hi = make_smem_desc(base + sub * kABytes + ks * 32);
                             const uint64_t a_lo = make_smem_desc(base + kABytes + ks * 32);
-                            const uint64_t b_hi = make_smem_desc(base + 2 * kABytes + ks * 32);
+                            const uint64_t b_hi = make_smem_desc(base + 2 * kABytes + sub * kBBytes + ks * 32);
                             const uint64_t b_lo = make_smem_desc(base + 2 * kABytes + kBBytes + ks * 32);
                             if (args.debug & 2) continue;
-                            mma_tf32(tmem_d, a_hi, b_lo, (kb | ks) != 0);
-                            mma_tf32(tmem_d, a_lo, b_hi, 1);
-                            mma_tf32(tmem_d, a_hi, b_hi, 1);
+                            if (args.screen) {
+                                mma_tf32(tmem_d, a_hi, b_hi, (kb | ks) != 0);
+                            } else {
+                                mma_tf32(tmem_d, a_hi, b_lo, (kb | ks) != 0);
+                                mma_tf32(tmem_d, a_lo, b_hi, 1);
+                                mma_tf32(tmem_d, a_hi, b_hi, 1);
+                            }
                         }
                         mma_commit(bar_empty + 8 * stage);  // stage is free once these MMAs have read it
-                        if (++stage == kStages) {
+                        if (++stage == nstages) {
                             stage = 0;
                             phase ^= 1;
                         }
@@ -645,6 +678,8 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
         int pos = 0;             // slot of the current maximum (small k)
         const int stride = APPEND ? kBuf : k;  // slots per row in the list memory
         int cur_slot = 0;
+        float slack = 0.f;  // screened mode: twice the error bound of this row's coarse keys
+        const int k_rank = (APPEND && args.screen) ? args.k_rank : k;
         auto close_list = [&]() {
             if (!unit_key) return;
             if (APPEND && args.part_cnt) {
@@ -653,7 +688,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 args.part_cnt[(size_t)cur_slot * BM + row] = row_valid ? cnt : 0;
             } else if (APPEND) {
                 const unsigned need = __ballot_sync(kFullMask, cnt > 0);
-                if (need) compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word, koff);
+                if (need) compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word, koff, k_rank, slack);
                 if (!((need >> lane) & 1u)) {  // no candidate ever reached this row: an empty list
                     for (int s = 0; s < k; s++) unit_idx[(size_t)row * kBuf + s] = -1;
                 }
@@ -690,6 +725,11 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 } else {
                     row_valid = (int64_t)qt * BM + row < args.nq;
                     qtau_word = args.qtau + (size_t)qt * BM + row;
+                    if (APPEND && args.screen && row_valid) {
+                        const float rel = 9.8e-4f + (float)args.d * 1.2e-7f;  // 2^-10 (1 + 2^-11) + d 2^-23
+                        const float e = rel * sqrtf(args.q_norm2[(size_t)qt * BM + row] * __uint_as_float(*args.x_max_norm2));
+                        slack = 2.f * (args.l2 ? 2.f * e : e);
+                    }
                 }
                 tau = row_valid ? kInf : -kInf;
                 list_max = kInf;
@@ -782,7 +822,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         const unsigned need = __ballot_sync(kFullMask, cnt + __popc(mask) > kBuf);
                         if (need) {
                             const long long c0 = args.stats ? clock64() : 0;
-                            compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word, koff);
+                            compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word, koff, k_rank, slack);
                             if (args.stats && lane == 0) {
                                 atomicAdd(args.stats + kStatCompactCycles, (unsigned long long)(clock64() - c0));
                                 atomicAdd(args.stats + kStatCompactRows, (unsigned long long)__popc(need));
@@ -951,6 +991,15 @@ FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms) {
     return p;
 }
 
+FlatPlan make_flat_plan_screened(int64_t nq, int64_t n, int k, int sms) {
+    FlatPlan p = make_flat_plan(nq, n, k, sms);
+    // lists of up to kScreenMaxList entries, kept by the append selection
+    p.list_stride = kBuf;
+    p.lists_sorted = true;
+    p.part_entries = (size_t)p.nq_tiles * p.lists_per_qt * BM * (size_t)p.list_stride;
+    return p;
+}
+
 FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms) {
     FlatPlan p;
     p.nq_tiles = (int)max_query_tiles;
@@ -968,7 +1017,7 @@ FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms) {
 int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
                    int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
-                   const GroupedWork *grouped) {
+                   const GroupedWork *grouped, const ScreenInput *screen) {
     (void)device;
     if (n <= 0 || nq <= 0) return 0;
     if (k <= 0 || k > kMaxK) return set_error("k must be in [1, %d]", kMaxK);
@@ -1002,6 +1051,12 @@ int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, con
     a.qrow_query = grouped ? grouped->qrow_query : nullptr;
     a.qrow_const = grouped ? grouped->qrow_const : nullptr;
     a.part_cnt = grouped ? grouped->part_cnt : nullptr;
+    const bool use_screen = screen && !grouped && screen->k_rank > kQueueDepth && screen->k_rank <= k && k <= kScreenMaxList;
+    a.screen = use_screen ? 1 : 0;
+    a.k_rank = use_screen ? screen->k_rank : k;
+    a.q_norm2 = use_screen ? screen->q_norm2 : nullptr;
+    a.x_max_norm2 = use_screen ? screen->x_max_norm2 : nullptr;
+    a.d = use_screen ? screen->d : dp;
     {
         const char *e = getenv("ANN_CUDA_TC_DEBUG");
         a.debug = e ? atoi(e) : 0;
@@ -1015,7 +1070,7 @@ int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, con
     }
     int rc;
     if (k <= kQueueDepth) rc = launch_variant<1, kSelSmem>(plan, maps, a, stream);
-    else if (k <= kAppendMaxK) rc = launch_variant<1, kSelAppend>(plan, maps, a, stream);
+    else if (k <= kAppendMaxK || use_screen) rc = launch_variant<1, kSelAppend>(plan, maps, a, stream);
     else if (k <= 512) rc = launch_variant<16, kSelReplace>(plan, maps, a, stream);
     else rc = launch_variant<64, kSelReplace>(plan, maps, a, stream);
     if (rc == 0 && a.stats) {

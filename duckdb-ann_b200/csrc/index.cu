@@ -55,6 +55,7 @@ struct SplitStore {
     // the tensor cores form are smaller, and so is their absolute error.  Fixed while n > 0.
     bool l2 = false;
     float *mu = nullptr;
+    unsigned *max_norm2 = nullptr;  // device word: bits of the largest |x|^2 in the store
 
     int reserve(int64_t want) {
         if (want <= cap) return 0;
@@ -92,7 +93,10 @@ struct SplitStore {
             if (!mu) ANN_CUDA_TRY(cudaMalloc(&mu, (size_t)dp * sizeof(float)));
             if (launch_column_mean(x, std::min<int64_t>(cnt, 16384), d, mu, stream)) return -1;
         }
-        if (launch_split_rows(x, cnt, d, dp, hi + n * dp, lo + n * dp, norms + n, stream, l2 ? mu : nullptr, false))
+        if (!max_norm2) ANN_CUDA_TRY(cudaMalloc(&max_norm2, sizeof(unsigned)));
+        if (n == 0) ANN_CUDA_TRY(cudaMemsetAsync(max_norm2, 0, sizeof(unsigned), stream));
+        if (launch_split_rows(x, cnt, d, dp, hi + n * dp, lo + n * dp, norms + n, stream, l2 ? mu : nullptr, false,
+                              max_norm2))
             return -1;
         n += cnt;
         return 0;
@@ -109,6 +113,8 @@ struct SplitStore {
         release_buffers();
         if (mu) cudaFree(mu);
         mu = nullptr;
+        if (max_norm2) cudaFree(max_norm2);
+        max_norm2 = nullptr;
     }
 };
 
@@ -207,6 +213,7 @@ struct WsLease {
 };
 
 constexpr int64_t kQueryBlock = 16384;  // queries per pass, bounds the scratch size
+constexpr int64_t kScreenMinRows = 2000000;  // flat stores this large are searched with one-MMA screening
 
 // ---- k-means helper kernels (index build, not the search path) -------------------------------
 __global__ void kmeans_accumulate_kernel(const float *__restrict__ x, int64_t n, int d, const int32_t *__restrict__ assign,
@@ -296,8 +303,10 @@ __global__ void find_id_kernel(const int64_t *__restrict__ ids, int64_t n, int64
 // ---- top-k over a split store (flat database, or IVF centroids) ---------------------------------
 // x_dev: nq x d queries on the device.  Leaves (nq x k) keys and int32 rows, best
 // first, in ws.sel_key / ws.sel_idx.
+// k_rank > 0 (flat_tc kernel only): screened search - k = k_rank + spare candidates are selected by
+// one-MMA keys with an error slack and the caller re-ranks them exactly (see ScreenInput).
 int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &ws, const float *x_dev, int64_t nq,
-                     int k, cudaStream_t stream) {
+                     int k, cudaStream_t stream, int k_rank = 0) {
     const int dp = st.dp, d = ix.d;
     if (ws.qhi.ensure((size_t)nq * dp * 4) || ws.qlo.ensure((size_t)nq * dp * 4) || ws.qn.ensure((size_t)nq * 4) ||
         ws.sel_key.ensure((size_t)nq * k * 4) || ws.sel_idx.ensure((size_t)nq * k * 4) || ws.status.ensure(4))
@@ -306,7 +315,9 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         if (launch_split_rows(x_dev, nq, d, dp, ws.qhi.as<float>(), ws.qlo.as<float>(), ws.qn.as<float>(), stream,
                               st.center(), true))
             return -1;
-        const FlatPlan plan = make_flat_plan(nq, st.n, k, sm_count(ix.device));
+        const FlatPlan plan = k_rank > 0 ? make_flat_plan_screened(nq, st.n, k, sm_count(ix.device))
+                                         : make_flat_plan(nq, st.n, k, sm_count(ix.device));
+        const ScreenInput screen{k_rank, ws.qn.as<float>(), st.max_norm2, d};
         const size_t qtau_bytes = (size_t)plan.nq_tiles * 128 * 4, sched_bytes = (size_t)plan.nq_tiles * 2 * 4;
         if (ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4) ||
             ws.qtau.ensure(qtau_bytes) || ws.sched.ensure(sched_bytes))
@@ -328,7 +339,7 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         if (launch_flat_tc(plan, st.hi, st.lo, st.norms, st.n, ws.qhi.as<float>(), ws.qlo.as<float>(), nq, dp, k,
                            ix.metric, ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.qtau.as<uint32_t>(),
                            ws.sched.as<int>(), ws.status.as<int>(),
-                           ix.device, stream))
+                           ix.device, stream, nullptr, k_rank > 0 ? &screen : nullptr))
             return -1;
         if (timing) {
             ANN_CUDA_TRY(cudaEventRecord(ws.ev1, stream));
@@ -622,8 +633,24 @@ int ensure_device(const ann_cuda_index *ix, DeviceGuard &g) {
 int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const float *x_dev, int64_t k,
                         float *d_dev, int64_t *i_dev, int64_t label_offset, cudaStream_t stream) {
     if (!ix.ivf) {
-        const int k_sel = (int)std::min<int64_t>(k, ix.store.n);
-        if (split_store_topk(ix, ix.store, ws, x_dev, nq, k_sel, stream)) return -1;
+        int k_sel = (int)std::min<int64_t>(k, ix.store.n);
+        // Large stores, 16 < k <= 128: one-MMA screening.  k + spare candidates come back, ranked
+        // by coarse keys; the exact re-ranking below picks the k.  (ANN_CUDA_FLAT_SCREEN=0 turns it
+        // off, =1 applies it to stores of any size.)
+        static const int screen_env = [] {
+            const char *e = getenv("ANN_CUDA_FLAT_SCREEN");
+            return e ? atoi(e) : -1;
+        }();
+        int k_rank = 0;
+        if (flat_kernel_choice() == FlatKernel::TC && k_sel > 16 && k_sel <= kAppendMaxK && ix.store.max_norm2 &&
+            (screen_env == 1 || (screen_env != 0 && ix.store.n >= kScreenMinRows))) {
+            const int k_list = (int)std::min<int64_t>({(int64_t)k_sel + std::max(32, k_sel / 2), (int64_t)kScreenMaxList, ix.store.n});
+            if (k_list > k_sel) {
+                k_rank = k_sel;
+                k_sel = k_list;
+            }
+        }
+        if (split_store_topk(ix, ix.store, ws, x_dev, nq, k_sel, stream, k_rank)) return -1;
         return launch_refine_finalize(ix.store.hi, ix.store.lo, ix.dp, ix.d, x_dev, ix.d, ws.sel_idx.as<int32_t>(), nq,
                                       k_sel, (int)k, ix.metric, nullptr, label_offset, d_dev, i_dev, ix.device, stream);
     }

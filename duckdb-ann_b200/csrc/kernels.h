@@ -24,8 +24,11 @@ void count_launch(int n = 1);
 // norms[i] = sum x^2 in fp32 (may be nullptr).
 // With `mu` (d floats, device) the norms are |x - mu|^2; with `center_rows` the planes hold
 // x - mu too (queries), otherwise x itself (database rows).
+// max_norm2_bits (optional, device word, zero before the first rows): raised to the bit pattern of
+// the largest |x|^2 seen (not centred).
 int launch_split_rows(const float *x, int64_t n, int d, int dp, float *hi, float *lo, float *norms,
-                      cudaStream_t stream, const float *mu = nullptr, bool center_rows = false);
+                      cudaStream_t stream, const float *mu = nullptr, bool center_rows = false,
+                      unsigned *max_norm2_bits = nullptr);
 // mu[c] = mean over the n rows of x[r][c]
 int launch_column_mean(const float *x, int64_t n, int d, float *mu, cudaStream_t stream);
 // x (n x d) -> out (n x dp) zero padded, norms (may be nullptr).
@@ -74,10 +77,23 @@ struct GroupedWork {
 };
 FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms);
 
+// Screened flat search (see KernelArgs::screen in flat_tc.cu).  The lists the kernel keeps are
+// `k` long as always; `k_rank` (< k) is the rank whose key, plus the error slack, is the
+// threshold: the caller asks for k = k_rank + spare candidates and re-ranks them exactly.
+struct ScreenInput {
+    int k_rank;                   // the caller's k
+    const float *q_norm2;         // per query |q - mu|^2 (L2) or |q|^2 (IP)
+    const unsigned *x_max_norm2;  // device word: bits of the largest |x|^2 in the store
+    int d;                        // true dimension
+};
+constexpr int kScreenMaxList = 256;  // longest list (k_rank + spare) the screened mode keeps
+
 int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
                    int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
-                   const GroupedWork *grouped = nullptr);
+                   const GroupedWork *grouped = nullptr, const ScreenInput *screen = nullptr);
+// make_flat_plan for a screened search: lists of `k` (up to kScreenMaxList) in append mode
+FlatPlan make_flat_plan_screened(int64_t nq, int64_t n, int k, int sms);
 
 // IVF grouping: from probes (nq x nprobe list numbers, -1 = none) builds, on the device,
 //   tile_off[l]     first gathered query tile of list l (lists padded to whole tiles of 128),

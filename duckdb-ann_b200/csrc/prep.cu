@@ -35,15 +35,17 @@ __device__ __forceinline__ float to_tf32(float x) {
 template <int MODE>
 __global__ void __launch_bounds__(kWarps * 32)
 prep_rows_kernel(const float *__restrict__ x, int64_t n, int d, int dp, float *__restrict__ hi,
-                 float *__restrict__ lo, float *__restrict__ norms, const float *__restrict__ mu, int center_rows) {
+                 float *__restrict__ lo, float *__restrict__ norms, const float *__restrict__ mu, int center_rows,
+                 unsigned *__restrict__ max_norm2_bits) {
     const int lane = threadIdx.x & 31;
     for (int64_t r = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); r < n; r += (int64_t)gridDim.x * kWarps) {
         const float *src = x + r * (int64_t)d;
-        float acc = 0.f;
+        float acc = 0.f, raw = 0.f;
         for (int c = lane; c < dp; c += 32) {
             float v = c < d ? src[c] : 0.f;
             const float w = (mu && c < d) ? v - mu[c] : v;
             acc = fmaf(w, w, acc);
+            raw = fmaf(v, v, raw);
             if (center_rows) v = w;
             if (MODE == 0) {
                 float h = to_tf32(v);
@@ -55,6 +57,10 @@ prep_rows_kernel(const float *__restrict__ x, int64_t n, int d, int dp, float *_
         }
         acc = warp_sum(acc);
         if (norms && lane == 0) norms[r] = acc;
+        if (max_norm2_bits) {  // largest |x|^2 of the store (non-negative floats order like their bits)
+            raw = warp_sum(raw);
+            if (lane == 0) atomicMax(max_norm2_bits, __float_as_uint(raw));
+        }
     }
 }
 
@@ -169,9 +175,10 @@ unsigned grid_for(int64_t n) {
 }  // namespace
 
 int launch_split_rows(const float *x, int64_t n, int d, int dp, float *hi, float *lo, float *norms,
-                      cudaStream_t stream, const float *mu, bool center_rows) {
+                      cudaStream_t stream, const float *mu, bool center_rows, unsigned *max_norm2_bits) {
     if (n <= 0) return 0;
-    prep_rows_kernel<0><<<grid_for(n), kWarps * 32, 0, stream>>>(x, n, d, dp, hi, lo, norms, mu, center_rows ? 1 : 0);
+    prep_rows_kernel<0><<<grid_for(n), kWarps * 32, 0, stream>>>(x, n, d, dp, hi, lo, norms, mu, center_rows ? 1 : 0,
+                                                                 max_norm2_bits);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -189,7 +196,7 @@ int launch_column_mean(const float *x, int64_t n, int d, float *mu, cudaStream_t
 
 int launch_pad_rows(const float *x, int64_t n, int d, int dp, float *out, float *norms, cudaStream_t stream) {
     if (n <= 0) return 0;
-    prep_rows_kernel<1><<<grid_for(n), kWarps * 32, 0, stream>>>(x, n, d, dp, out, nullptr, norms, nullptr, 0);
+    prep_rows_kernel<1><<<grid_for(n), kWarps * 32, 0, stream>>>(x, n, d, dp, out, nullptr, norms, nullptr, 0, nullptr);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
