@@ -21,7 +21,7 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libann_cuda.so")
 DRIVER = os.path.join(HERE, "backend_driver")
 
-LIB_SOURCES = ["prep.cu", "scan.cu", "merge.cu", "flat_tc.cu", "index.cu", "cuda_diskann_bridge.cu",
+LIB_SOURCES = ["prep.cu", "scan.cu", "merge.cu", "flat_tc.cu", "flat_tc_bk32.cu", "index.cu", "cuda_diskann_bridge.cu",
                "gpu_backend_cuda.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # /usr/bin/g++ is the system compiler; the image's $CXX points at a gcc without OpenMP support files
@@ -46,6 +46,7 @@ def _newer(target: str, deps: list[str]) -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".hpp"))]
+    headers.append(os.path.join(CSRC, "flat_tc.cu"))  # flat_tc_bk32.cu includes it
     headers += [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
     headers += [os.path.join(INCLUDE, "faiss", f) for f in os.listdir(os.path.join(INCLUDE, "faiss"))]
     headers.append(os.path.abspath(__file__))

@@ -63,6 +63,16 @@ namespace {
 
 constexpr int BM = 128;           // queries per tile (TMEM lanes)
 constexpr int BN = 256;           // database rows per tile (TMEM columns)
+// This file is compiled twice: as it stands (K blocks of 16 floats, four 48 KB stages: best for
+// the three-MMA product and for the list scan, which want a deep ring) and, through
+// flat_tc_bk32.cu, with K blocks of 32 floats for the screened search, whose single MMA per K
+// step is otherwise dominated by the per-block bookkeeping of the issuing thread.
+#ifdef ANN_TC_VARIANT_BK32
+#define ANN_TC_BK 32
+#define ANN_TC_LAUNCH launch_flat_tc_bk32
+#else
+#define ANN_TC_LAUNCH launch_flat_tc
+#endif
 #ifndef ANN_TC_BK
 #define ANN_TC_BK 16
 #endif
@@ -727,8 +737,11 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     qtau_word = args.qtau + (size_t)qt * BM + row;
                     if (APPEND && args.screen && row_valid) {
                         const float rel = 9.8e-4f + (float)args.d * 1.2e-7f;  // 2^-10 (1 + 2^-11) + d 2^-23
-                        const float e = rel * sqrtf(args.q_norm2[(size_t)qt * BM + row] * __uint_as_float(*args.x_max_norm2));
-                        slack = 2.f * (args.l2 ? 2.f * e : e);
+                        const float xm2 = __uint_as_float(*args.x_max_norm2);
+                        const float e = rel * sqrtf(args.q_norm2[(size_t)qt * BM + row] * xm2);
+                        // L2 keys are |x - mu|^2 - 2 (q - mu).x: twice the dot error, plus the fp32 rounding
+                        // of the stored norm (<= (d / 32 + 6) 2^-24 of a value that is at most 4 |x|max^2)
+                        slack = 2.f * (args.l2 ? 2.f * e + ((float)args.d * (1.f / 32.f) + 6.f) * 6e-8f * 4.f * xm2 : e);
                     }
                 }
                 tau = row_valid ? kInf : -kInf;
@@ -965,6 +978,7 @@ int launch_variant(const FlatPlan &plan, const CUtensorMap maps[4], const Kernel
 
 }  // namespace
 
+#ifndef ANN_TC_VARIANT_BK32
 FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms) {
     FlatPlan p;
     p.nq_tiles = (int)((nq + BM - 1) / BM);
@@ -1014,13 +1028,21 @@ FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms) {
     return p;
 }
 
-int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
+#endif  // !ANN_TC_VARIANT_BK32
+
+int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
                    int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
                    const GroupedWork *grouped, const ScreenInput *screen) {
     (void)device;
     if (n <= 0 || nq <= 0) return 0;
     if (k <= 0 || k > kMaxK) return set_error("k must be in [1, %d]", kMaxK);
+#ifndef ANN_TC_VARIANT_BK32
+    // the screened search runs in the build of this file with K blocks of 32 floats
+    if (screen && !grouped && screen->k_rank > kQueueDepth && screen->k_rank <= k && k <= kScreenMaxList && dp % 32 == 0)
+        return launch_flat_tc_bk32(plan, xhi, xlo, xnorm, n, qhi, qlo, nq, dp, k, metric, part_key, part_idx, qtau, sched,
+                                   status, device, stream, grouped, screen);
+#endif
     if (dp % BK != 0) return set_error("padded dimension must be a multiple of %d", BK);
     if (n > 0x7fffffffll - BN) return set_error("a flat shard holds at most 2^31 rows");
     CUtensorMap maps[4];

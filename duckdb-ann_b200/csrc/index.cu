@@ -32,6 +32,12 @@ namespace {
 enum class FlatKernel { TC, SIMT };
 
 std::atomic<int> g_flat_kernel{-1};  // -1 = not chosen yet
+// one-MMA screening of the flat search: -1 = by store size, 0 = never, 1 = always (tests);
+// ANN_CUDA_FLAT_SCREEN sets the initial value
+std::atomic<int> g_flat_screen{[] {
+    const char *e = getenv("ANN_CUDA_FLAT_SCREEN");
+    return e ? (atoi(e) != 0 ? 1 : 0) : -1;
+}()};
 std::atomic<int> g_time_kernels{0};
 
 FlatKernel flat_kernel_choice() {
@@ -637,10 +643,7 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
         // Large stores, 16 < k <= 128: one-MMA screening.  k + spare candidates come back, ranked
         // by coarse keys; the exact re-ranking below picks the k.  (ANN_CUDA_FLAT_SCREEN=0 turns it
         // off, =1 applies it to stores of any size.)
-        static const int screen_env = [] {
-            const char *e = getenv("ANN_CUDA_FLAT_SCREEN");
-            return e ? atoi(e) : -1;
-        }();
+        const int screen_env = g_flat_screen.load(std::memory_order_relaxed);
         int k_rank = 0;
         if (flat_kernel_choice() == FlatKernel::TC && k_sel > 16 && k_sel <= kAppendMaxK && ix.store.max_norm2 &&
             (screen_env == 1 || (screen_env != 0 && ix.store.n >= kScreenMinRows))) {
@@ -868,13 +871,24 @@ const char *ann_cuda_flat_kernel_name(void) { return flat_kernel_choice() == Fla
 int ann_cuda_set_flat_kernel(const char *name) {
     if (name && strcmp(name, "tcgen05") == 0) {
         g_flat_kernel.store(0);
+        g_flat_screen.store(-1);
+        return 0;
+    }
+    if (name && strcmp(name, "tcgen05-screened") == 0) {  // one-MMA screening for stores of any size
+        g_flat_kernel.store(0);
+        g_flat_screen.store(1);
+        return 0;
+    }
+    if (name && strcmp(name, "tcgen05-split") == 0) {  // three-MMA split product for every pair
+        g_flat_kernel.store(0);
+        g_flat_screen.store(0);
         return 0;
     }
     if (name && strcmp(name, "simt") == 0) {
         g_flat_kernel.store(1);
         return 0;
     }
-    return set_error("unknown flat kernel name (tcgen05 | simt)");
+    return set_error("unknown flat kernel name (tcgen05 | tcgen05-screened | tcgen05-split | simt)");
 }
 
 void ann_cuda_set_kernel_timing(int on) { g_time_kernels.store(on ? 1 : 0); }

@@ -92,6 +92,12 @@ int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, con
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
                    int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
                    const GroupedWork *grouped = nullptr, const ScreenInput *screen = nullptr);
+// The same kernel built with K blocks of 32 floats (flat_tc_bk32.cu); launch_flat_tc hands the
+// screened searches to it.
+int launch_flat_tc_bk32(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
+                        const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
+                        int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
+                        const GroupedWork *grouped, const ScreenInput *screen);
 // make_flat_plan for a screened search: lists of `k` (up to kScreenMaxList) in append mode
 FlatPlan make_flat_plan_screened(int64_t nq, int64_t n, int k, int sms);
 

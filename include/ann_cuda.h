@@ -162,8 +162,12 @@ int ann_cuda_merge_topk_device(int device, const float *parts_distances, const i
  * product path) or "simt" (exact-fp32 cross-check kernel).  Selected by the
  * environment variable ANN_CUDA_FLAT_KERNEL; default tcgen05. */
 const char *ann_cuda_flat_kernel_name(void);
-/* Overrides that choice for the whole process ("tcgen05" | "simt"); used by the
- * tests to cross-check one kernel against the other. */
+/* Overrides that choice for the whole process; used by the tests to cross-check one
+ * kernel against the other.  "tcgen05": tensor-core kernel; flat stores of two
+ * million rows or more are searched with one-MMA screening (candidates chosen by
+ * q_hi.x_hi keys under a proven error slack, then re-ranked in exact fp32), smaller
+ * ones with the three-MMA split product.  "tcgen05-screened" / "tcgen05-split":
+ * screening always / never.  "simt": the exact-fp32 cross-check kernels. */
 int ann_cuda_set_flat_kernel(const char *name);
 
 /* Measurement hook.  With timing on, every search records CUDA events around

@@ -30,7 +30,7 @@ def _metric(pkg, name):
     return pkg.METRIC_L2 if name == "L2" else pkg.METRIC_INNER_PRODUCT
 
 
-@pytest.fixture(params=["tcgen05", "simt"])
+@pytest.fixture(params=["tcgen05", "tcgen05-screened", "simt"])
 def kernel(request, pkg):
     assert pkg.lib().ann_cuda_set_flat_kernel(request.param.encode()) == 0
     yield request.param
@@ -50,6 +50,29 @@ def test_flat_matches_oracle(pkg, oracle, kernel, shape, metric_name):
     Dref, Iref = oracle.flat_search(xb, xq, k, m)
     assert_topk_matches(oracle, xb, xq, m, D, I, Dref, Iref, f"{kernel} {metric_name} {shape}")
     idx.close()
+
+
+@pytest.mark.parametrize("metric_name", ["L2", "IP"])
+def test_screened_search_with_norms_over_four_decades(pkg, oracle, metric_name):
+    """One-MMA screening bounds its error with the LARGEST row norm of the store: rows whose
+    norms span 1e-2 .. 1e2 and queries of all sizes must still give the oracle's answer."""
+    rng = np.random.default_rng(5)
+    nv, nq, d, k = 30000, 64, 96, 50
+    xb = rng.standard_normal((nv, d)).astype(np.float32)
+    xb *= (10.0 ** rng.uniform(-2, 2, (nv, 1))).astype(np.float32)
+    xq = rng.standard_normal((nq, d)).astype(np.float32) * (10.0 ** rng.uniform(-2, 2, (nq, 1))).astype(np.float32)
+    m = _metric(pkg, metric_name)
+    assert pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05-screened") == 0
+    try:
+        idx = pkg.CudaIndexFlat(d, m)
+        idx.add(xb[:10000])
+        idx.add(xb[10000:])
+        D, I = idx.search(xq, k)
+        Dref, Iref = oracle.flat_search(xb, xq, k, m)
+        assert_topk_matches(oracle, xb, xq, m, D, I, Dref, Iref, f"screened {metric_name}")
+        idx.close()
+    finally:
+        pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05")
 
 
 def test_known_answers_from_reference_sql(pkg, kernel):
