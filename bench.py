@@ -151,7 +151,7 @@ class FlatWorkload:
         self.chunk = 250_000
         self.metric = "flat_topk_queries_per_s"
         self.unit = "queries/s"
-        self.dtype = "f32 (split-TF32 tensor cores, fp32 accumulate)"
+        self.dtype = "f32 (TF32 tensor cores with fp32 accumulate for candidate selection, exact fp32 re-ranking)"
         self.scaling = "strong"
 
     def gen_chunk(self, c, device, torch):
@@ -219,28 +219,36 @@ class FlatWorkload:
                 "l2_flush": "database shard (>= 7 GB per GPU) is far larger than L2; no explicit flush"
                 if self.n * self.d * 8 / max(world, 1) > 1e9 else "database is L2-sized (a warm-cache figure; the full-size workload is the headline)",
                 "flat_kernel": self.pkg.lib().ann_cuda_flat_kernel_name().decode() if getattr(self, "pkg", None)
-                else "cpu"}
+                else "cpu",
+                "search": "one-MMA screening + exact re-ranking (stores >= 2M rows, 16 < k <= 128), else three-MMA split product"}
 
     def roofline(self, peaks, kernel_ms):
         local_rows = self.hi - self.lo
         flops = 2.0 * self.nq * local_rows * self.d
         achieved = flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms and kernel_ms > 0 else None
-        peak = peaks["bf16_tflops_sustained"] / 6.0
-        # DRAM traffic of one launch, from the ncu capture of this kernel on 400,000 rows
-        # (summarised with the other profile summaries: 16.2-22.3 GB read + 0.47-0.49 GB written per
-        # launch with 4,096 queries of 768 dimensions), scaled by the rows and query tiles of this
-        # launch: every 128-query tile streams the shard once, L2 absorbs part of it.
+        # Stores of two million rows or more are searched with one-MMA screening (one TF32 MMA per
+        # product, candidates re-ranked exactly); smaller ones with the three-MMA split product.
+        screened = local_rows >= 2_000_000 and 16 < self.k <= 128 and self.pkg.lib().ann_cuda_flat_kernel_name().decode() == "tcgen05"
+        mmas = 1 if screened else 3
+        peak = peaks["bf16_tflops_sustained"] / 2.0 / mmas
+        # DRAM traffic of one launch, from ncu captures of this kernel on 400,000 rows with 4,096
+        # queries of 768 dimensions (screened: 11.1-11.2 GB read + 0.44 GB written; split product:
+        # 16.2-22.3 GB + 0.47-0.49 GB), scaled by the rows and query tiles of this launch: every
+        # 128-query tile streams the shard once, L2 absorbs part of it.
         traffic = None
         if self.d == 768:
-            traffic = 19.7e9 * (local_rows / 400_000.0) * (((self.nq + 127) // 128) / 32.0)
+            per_launch = 11.6e9 if screened else 19.7e9
+            traffic = per_launch * (local_rows / 400_000.0) * (((self.nq + 127) // 128) / 32.0)
         return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak if achieved else None, "traffic": traffic,
                 "traffic_note": "bytes; ncu dram read+write of a 400,000-row launch scaled by rows and query tiles"
                 if traffic else "no capture for this shape",
-                "kernel": "flat_tc_kernel", "kernel_ms": kernel_ms,
-                "algorithmic_flops_per_launch": flops,
-                "peak_note": f"{peaks['_source']} bf16 sustained {peaks['bf16_tflops_sustained']} TFLOP/s / 2 (TF32 rate) "
-                             "/ 3 (split-TF32 issues three MMAs per product); 'achieved' counts 2*Q*N*d once"}
+                "kernel": "flat_tc_kernel" + (" (screened, 32-float K blocks)" if screened else ""),
+                "kernel_ms": kernel_ms, "algorithmic_flops_per_launch": flops, "mma_per_product": mmas,
+                "peak_note": f"{peaks['_source']} bf16 sustained {peaks['bf16_tflops_sustained']} TFLOP/s / 2 (TF32 rate)"
+                             + (" (screened search: one TF32 MMA per product)" if screened else
+                                " / 3 (split-TF32 issues three MMAs per product)")
+                             + "; 'achieved' counts 2*Q*N*d once"}
 
     def verify(self, torch, D, I):
         """Size-independent properties: sorted best first, labels valid and distinct, and the
