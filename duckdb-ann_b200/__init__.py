@@ -85,6 +85,7 @@ SIGNATURES = {
     "ann_cuda_set_kernel_timing": (None, [C.c_int]),
     "ann_cuda_index_last_flat_kernel_ms": (C.c_float, [_P]),
     "ann_cuda_launch_count": (C.c_uint64, []),
+    "ann_cuda_screen_fallbacks": (C.c_uint64, []),
     # include/cuda_diskann_bridge.h
     "diskann_metal_available": (C.c_int, []),
     "diskann_metal_batch_distances": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P]),

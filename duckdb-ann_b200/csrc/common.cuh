@@ -100,4 +100,15 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 constexpr float kInf = __builtin_huge_valf();
 
+// Screened flat search: twice the bound E' on |coarse key - exact key| for a query with
+// qn = |q - mu|^2 (L2) or |q|^2 (IP) against a store whose largest row norm squared is xm2.
+// The one-MMA dot product q_hi.x_hi is within (2^-10 (1 + 2^-11) + d 2^-23) |q||x| of the exact
+// one; an L2 key is |x - mu|^2 - 2 (q - mu).x, so it carries twice that plus the fp32 rounding of
+// the stored norm (<= (d / 32 + 6) 2^-24 of a value that is at most 4 xm2).
+__host__ __device__ inline float screen_slack(float qn, float xm2, int d, bool l2) {
+    const float rel = 9.8e-4f + (float)d * 1.2e-7f;
+    const float e = rel * sqrtf(qn * xm2);
+    return 2.f * (l2 ? 2.f * e + ((float)d * (1.f / 32.f) + 6.f) * 6e-8f * 4.f * xm2 : e);
+}
+
 }  // namespace anncuda

@@ -736,12 +736,8 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     row_valid = (int64_t)qt * BM + row < args.nq;
                     qtau_word = args.qtau + (size_t)qt * BM + row;
                     if (APPEND && args.screen && row_valid) {
-                        const float rel = 9.8e-4f + (float)args.d * 1.2e-7f;  // 2^-10 (1 + 2^-11) + d 2^-23
-                        const float xm2 = __uint_as_float(*args.x_max_norm2);
-                        const float e = rel * sqrtf(args.q_norm2[(size_t)qt * BM + row] * xm2);
-                        // L2 keys are |x - mu|^2 - 2 (q - mu).x: twice the dot error, plus the fp32 rounding
-                        // of the stored norm (<= (d / 32 + 6) 2^-24 of a value that is at most 4 |x|max^2)
-                        slack = 2.f * (args.l2 ? 2.f * e + ((float)args.d * (1.f / 32.f) + 6.f) * 6e-8f * 4.f * xm2 : e);
+                        slack = screen_slack(args.q_norm2[(size_t)qt * BM + row], __uint_as_float(*args.x_max_norm2), args.d,
+                                             args.l2 != 0);
                     }
                 }
                 tau = row_valid ? kInf : -kInf;

@@ -34,6 +34,8 @@ enum class FlatKernel { TC, SIMT };
 std::atomic<int> g_flat_kernel{-1};  // -1 = not chosen yet
 // one-MMA screening of the flat search: -1 = by store size, 0 = never, 1 = always (tests);
 // ANN_CUDA_FLAT_SCREEN sets the initial value
+thread_local bool t_no_screen = false;  // set while a host entry point repeats a block unscreened
+std::atomic<uint64_t> g_screen_fallbacks{0};
 std::atomic<int> g_flat_screen{[] {
     const char *e = getenv("ANN_CUDA_FLAT_SCREEN");
     return e ? (atoi(e) != 0 ? 1 : 0) : -1;
@@ -352,11 +354,15 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
             ws.timed = true;
             ix.last_timed_ws = &ws;
         }
+        if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 0, ws.sched.as<int>() + plan.nq_tiles,
+                               nullptr, plan.lists_per_qt, nq, k, plan.list_stride, ws.sel_key.as<float>(),
+                               ws.sel_idx.as<int32_t>(), ix.device, stream, plan.lists_sorted))
+            return -1;
+        if (k_rank > 0 && launch_screen_check(ws.sel_key.as<float>(), nq, k, k_rank, ws.qn.as<float>(), st.max_norm2, d,
+                                              ix.metric, ws.status.as<int>(), stream))
+            return -1;
         ANN_CUDA_TRY(cudaMemcpyAsync(ws.status_host, ws.status.ptr, 4, cudaMemcpyDeviceToHost, stream));
-        return launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 0,
-                                  ws.sched.as<int>() + plan.nq_tiles, nullptr, plan.lists_per_qt, nq, k,
-                                  plan.list_stride, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream,
-                                  plan.lists_sorted);
+        return 0;
     }
     // exact-fp32 cross-check kernel: items = (query, database chunk)
     int chunks = (int)std::max<int64_t>(1, std::min<int64_t>({(int64_t)kMergeCandidates / k, (st.n + 255) / 256,
@@ -640,14 +646,16 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
                         float *d_dev, int64_t *i_dev, int64_t label_offset, cudaStream_t stream) {
     if (!ix.ivf) {
         int k_sel = (int)std::min<int64_t>(k, ix.store.n);
-        // Large stores, 16 < k <= 128: one-MMA screening.  k + spare candidates come back, ranked
-        // by coarse keys; the exact re-ranking below picks the k.  (ANN_CUDA_FLAT_SCREEN=0 turns it
+        // Large stores, 16 < k <= 128: one-MMA screening.  kScreenMaxList candidates come back, ranked
+        // by coarse keys; the exact re-ranking below picks the k.  Should more rows than the spare
+        // holds fall inside the error band of some query, the status word says so and the host entry
+        // point repeats the block without screening.  (ANN_CUDA_FLAT_SCREEN=0 turns it
         // off, =1 applies it to stores of any size.)
-        const int screen_env = g_flat_screen.load(std::memory_order_relaxed);
+        const int screen_env = t_no_screen ? 0 : g_flat_screen.load(std::memory_order_relaxed);
         int k_rank = 0;
         if (flat_kernel_choice() == FlatKernel::TC && k_sel > 16 && k_sel <= kAppendMaxK && ix.store.max_norm2 &&
             (screen_env == 1 || (screen_env != 0 && ix.store.n >= kScreenMinRows))) {
-            const int k_list = (int)std::min<int64_t>({(int64_t)k_sel + std::max(32, k_sel / 2), (int64_t)kScreenMaxList, ix.store.n});
+            const int k_list = (int)std::min<int64_t>((int64_t)kScreenMaxList, ix.store.n);
             if (k_list > k_sel) {
                 k_rank = k_sel;
                 k_sel = k_list;
@@ -890,6 +898,8 @@ int ann_cuda_set_flat_kernel(const char *name) {
     }
     return set_error("unknown flat kernel name (tcgen05 | tcgen05-screened | tcgen05-split | simt)");
 }
+
+uint64_t ann_cuda_screen_fallbacks(void) { return g_screen_fallbacks.load(std::memory_order_relaxed); }
 
 void ann_cuda_set_kernel_timing(int on) { g_time_kernels.store(on ? 1 : 0); }
 
@@ -1236,6 +1246,10 @@ int ann_cuda_index_search_device(const ann_cuda_index *ix, int64_t n, const floa
     if (*lease.ws->status_host) {
         const int code = *lease.ws->status_host;
         *lease.ws->status_host = 0;
+        if (code == kScreenOverflow)
+            return set_error("an earlier screened search on this stream had more rows inside its error band than spare "
+                             "candidates: its results may miss near ties; use the host entry point or "
+                             "ann_cuda_set_flat_kernel(\"tcgen05-split\") for such data");
         return set_error("an earlier search on this stream gave up on a wait inside the flat kernel (code %d)", code);
     }
     return search_device_impl(*ix, *lease.ws, n, x_device, k, distances_device, labels_device, label_offset, s);
@@ -1264,6 +1278,16 @@ int ann_cuda_index_search(const ann_cuda_index *ix, int64_t n, const float *x, i
         ANN_CUDA_TRY(cudaMemcpyAsync(distances + q0 * k, ws.out_d.ptr, (size_t)nb * k * 4, cudaMemcpyDeviceToHost, s));
         ANN_CUDA_TRY(cudaMemcpyAsync(labels + q0 * k, ws.out_i.ptr, (size_t)nb * k * 8, cudaMemcpyDeviceToHost, s));
         ANN_CUDA_TRY(cudaStreamSynchronize(s));
+        if (*ws.status_host == kScreenOverflow && !t_no_screen) {
+            // too many rows inside the screening band of some query: this block once more with the
+            // three-MMA product, which needs no spare candidates
+            *ws.status_host = 0;
+            t_no_screen = true;
+            g_screen_fallbacks.fetch_add(1, std::memory_order_relaxed);
+            q0 -= kQueryBlock;
+            continue;
+        }
+        t_no_screen = false;
         if (*ws.status_host) {
             const int code = *ws.status_host;
             *ws.status_host = 0;

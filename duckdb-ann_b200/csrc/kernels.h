@@ -87,6 +87,11 @@ struct ScreenInput {
     int d;                        // true dimension
 };
 constexpr int kScreenMaxList = 256;  // longest list (k_rank + spare) the screened mode keeps
+constexpr int kScreenOverflow = 100;  // status code: more rows inside the error band than the spare holds
+// Sets *status (if still 0) to kScreenOverflow when the last of the k_list merged candidates of
+// some query is still within the slack of its k_rank-th key.
+int launch_screen_check(const float *sel_key, int64_t nq, int k_list, int k_rank, const float *q_norm2,
+                        const unsigned *x_max_norm2, int d, int metric, int *status, cudaStream_t stream);
 
 int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,

@@ -244,6 +244,20 @@ merge_filtered_kernel(const float *__restrict__ part_key, const int32_t *__restr
     }
 }
 
+// Screened flat search: the guarantee holds while fewer than k_list - k_rank rows sit within the
+// slack above the k_rank-th coarse key.  If the LAST candidate of a query is still inside that
+// band, rows may have been left out: status (0 so far) becomes kScreenOverflow and the host entry
+// points repeat the search with the three-MMA product.
+__global__ void screen_check_kernel(const float *__restrict__ sel_key, int64_t nq, int k_list, int k_rank,
+                                    const float *__restrict__ q_norm2, const unsigned *__restrict__ x_max_norm2, int d,
+                                    int l2, int *__restrict__ status) {
+    const int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= nq) return;
+    const float last = sel_key[q * k_list + k_list - 1], kth = sel_key[q * k_list + k_rank - 1];
+    if (last < kInf && last <= kth + screen_slack(q_norm2[q], __uint_as_float(*x_max_norm2), d, l2 != 0))
+        atomicCAS(status, 0, kScreenOverflow);
+}
+
 // Exact fp32 re-evaluation of the selected pairs, sort, and user-facing output.
 __global__ void __launch_bounds__(128)
 refine_finalize_kernel(const float *__restrict__ xhi, const float *__restrict__ xlo, int dp, int d,
@@ -436,6 +450,16 @@ int launch_merge_filtered(const float *part_key, const int32_t *part_idx, const 
     if (k > kFilterCap / 2) return set_error("merge: k = %d is too large for the filtered merge", k);
     merge_filtered_kernel<<<(unsigned)nq, kMergeThreads, 0, stream>>>(part_key, part_idx, part_cnt, slot_of,
                                                                      slot_key_offset, qtau, nparts, k, out_key, out_idx);
+    count_launch();
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int launch_screen_check(const float *sel_key, int64_t nq, int k_list, int k_rank, const float *q_norm2,
+                        const unsigned *x_max_norm2, int d, int metric, int *status, cudaStream_t stream) {
+    if (nq <= 0 || k_list <= k_rank) return 0;
+    screen_check_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, stream>>>(sel_key, nq, k_list, k_rank, q_norm2, x_max_norm2,
+                                                                          d, metric != 0, status);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

@@ -137,7 +137,7 @@ class CudaIndexFlat(_CudaIndex):
 
     def search_small_static(self, x, k: int, D=None, I=None, label_offset: int = 0, stream=None):
         """search_device() for callers that may not allocate device memory (a worker under a
-        fixed memory budget, a search recorded into a CUDA graph): at most 128 queries, k <= 16,
+        fixed memory budget): at most 128 queries, k <= 16,
         d <= 1024, all scratch in a fixed device array.  Calls must not overlap on the GPU.
         D and I must be passed in if torch itself must not allocate either."""
         import torch

@@ -167,8 +167,18 @@ const char *ann_cuda_flat_kernel_name(void);
  * million rows or more are searched with one-MMA screening (candidates chosen by
  * q_hi.x_hi keys under a proven error slack, then re-ranked in exact fp32), smaller
  * ones with the three-MMA split product.  "tcgen05-screened" / "tcgen05-split":
- * screening always / never.  "simt": the exact-fp32 cross-check kernels. */
+ * screening always / never.  "simt": the exact-fp32 cross-check kernels.
+ * Screening returns exactly the split product's answer as long as fewer than 256 - k
+ * rows lie within its error band (about 0.2 % of |q||x|max) above the k-th best; the
+ * library checks that for every query.  ann_cuda_index_search then repeats the
+ * block with the split product by itself; ann_cuda_index_search_device, which
+ * returns before the search has run, reports it as an error of the NEXT call on
+ * that stream. */
 int ann_cuda_set_flat_kernel(const char *name);
+
+/* How many query blocks ann_cuda_index_search has repeated with the split product
+ * because the screened search ran out of spare candidates (process-wide, since load). */
+uint64_t ann_cuda_screen_fallbacks(void);
 
 /* Measurement hook.  With timing on, every search records CUDA events around
  * its flat-search kernel on the stream the kernel is launched on;

@@ -75,6 +75,42 @@ def test_screened_search_with_norms_over_four_decades(pkg, oracle, metric_name):
         pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05")
 
 
+def test_screening_falls_back_when_its_spare_candidates_run_out(pkg, oracle):
+    """600 rows whose distances to the query are 1e-4 apart (resolved by the split product, far
+    inside the error band of the one-MMA keys, whose size is set by the largest norm in the
+    store): more than the screened search keeps in reserve.  The host entry point must notice
+    and answer with the split product."""
+    rng = np.random.default_rng(17)
+    d, k = 64, 40
+    q = rng.standard_normal(d)
+    q /= np.linalg.norm(q)
+    u = rng.standard_normal((600, d))
+    u /= np.linalg.norm(u, axis=1, keepdims=True)
+    far = rng.standard_normal((20000, d)).astype(np.float32)        # norms ~8: they set the band
+    xq = q[None, :].astype(np.float32)
+    assert pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05-screened") == 0
+    try:
+        for metric_name in ("L2", "IP"):
+            if metric_name == "L2":     # squared distances 0.5, 0.5001, 0.5002, ...
+                near = q[None, :] + np.sqrt(0.5 + 1e-4 * np.arange(600))[:, None] * u
+            else:                       # dot products 50, 49.9998, 49.9996, ... (the other rows: |q.x| < 5)
+                r = u - (u @ q)[:, None] * q[None, :]
+                near = (50.0 - 2e-4 * np.arange(600))[:, None] * q[None, :] + 0.1 * r
+            xb = np.concatenate([far, near.astype(np.float32)])
+            xb = xb[np.random.default_rng(3).permutation(len(xb))]
+            m = _metric(pkg, metric_name)
+            idx = pkg.CudaIndexFlat(d, m)
+            idx.add(xb)
+            before = pkg.lib().ann_cuda_screen_fallbacks()
+            D, I = idx.search(xq, k)
+            assert pkg.lib().ann_cuda_screen_fallbacks() == before + 1, "the overflow went unnoticed"
+            Dref, Iref = oracle.flat_search(xb, xq, k, m)
+            assert_topk_matches(oracle, xb, xq, m, D, I, Dref, Iref, f"screen overflow {metric_name}")
+            idx.close()
+    finally:
+        pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05")
+
+
 def test_known_answers_from_reference_sql(pkg, kernel):
     with open(os.path.join(os.path.dirname(__file__), "golden", "reference_known_answers.json")) as f:
         golden = json.load(f)
