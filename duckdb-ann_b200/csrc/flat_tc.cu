@@ -638,18 +638,27 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, args.status, 3)) goto done;
                         if (args.stats) atomicAdd(args.stats + kStatMmaWaitSmem, (unsigned long long)(clock64() - t0));
                         tmem_fence_after();
-                        const uint32_t base = smem_base + (args.screen ? (stage >> 1) : stage) * kStageBytes;
-                        const uint32_t sub = args.screen ? (stage & 1) : 0;
+                        if (args.screen) {
+                            // One MMA per K step: the loop of this single thread is what paces the
+                            // tensor pipe, so the descriptors are formed once per K block and only
+                            // their address field moves (32 bytes = 2 units of 16 per K step).
+                            const uint32_t base = smem_base + (stage >> 1) * kStageBytes;
+                            const uint64_t a0 = make_smem_desc(base + (stage & 1) * kABytes);
+                            const uint64_t b0 = make_smem_desc(base + 2 * kABytes + (stage & 1) * kBBytes);
+                            if (!(args.debug & 2)) {
+                                mma_tf32(tmem_d, a0, b0, kb != 0);
 #pragma unroll
-                        for (int ks = 0; ks < BK / 8; ks++) {
-                            const uint64_t a_hi = make_smem_desc(base + sub * kABytes + ks * 32);
-                            const uint64_t a_lo = make_smem_desc(base + kABytes + ks * 32);
-                            const uint64_t b_hi = make_smem_desc(base + 2 * kABytes + sub * kBBytes + ks * 32);
-                            const uint64_t b_lo = make_smem_desc(base + 2 * kABytes + kBBytes + ks * 32);
-                            if (args.debug & 2) continue;
-                            if (args.screen) {
-                                mma_tf32(tmem_d, a_hi, b_hi, (kb | ks) != 0);
-                            } else {
+                                for (int ks = 1; ks < BK / 8; ks++) mma_tf32(tmem_d, a0 + 2 * ks, b0 + 2 * ks, 1);
+                            }
+                        } else {
+                            const uint32_t base = smem_base + stage * kStageBytes;
+#pragma unroll
+                            for (int ks = 0; ks < BK / 8; ks++) {
+                                const uint64_t a_hi = make_smem_desc(base + ks * 32);
+                                const uint64_t a_lo = make_smem_desc(base + kABytes + ks * 32);
+                                const uint64_t b_hi = make_smem_desc(base + 2 * kABytes + ks * 32);
+                                const uint64_t b_lo = make_smem_desc(base + 2 * kABytes + kBBytes + ks * 32);
+                                if (args.debug & 2) continue;
                                 mma_tf32(tmem_d, a_hi, b_lo, (kb | ks) != 0);
                                 mma_tf32(tmem_d, a_lo, b_hi, 1);
                                 mma_tf32(tmem_d, a_hi, b_hi, 1);
