@@ -68,6 +68,10 @@ SIGNATURES = {
     "ann_cuda_index_reserve": (C.c_int, [_P, _I64]),
     "ann_cuda_index_search": (C.c_int, [_P, _I64, _P, _I64, _P, _P]),
     "ann_cuda_index_search_device": (C.c_int, [_P, _I64, _P, _I64, _P, _P, _I64, _P]),
+    "ann_cuda_index_search_async": (C.c_int, [_P, _I64, _P, _I64, _P, _P, _P]),
+    "ann_cuda_search_token_ready": (C.c_int, [_P]),
+    "ann_cuda_search_token_wait": (C.c_int, [_P]),
+    "ann_cuda_search_token_free": (None, [_P]),
     "ann_cuda_flat_search_small_static": (C.c_int, [_P, _I64, _P, _I64, _P, _P, _I64, _P]),
     "ann_cuda_index_reset": (C.c_int, [_P]),
     "ann_cuda_index_reconstruct": (C.c_int, [_P, _I64, _P]),
@@ -125,7 +129,7 @@ def check(rc: int, what: str) -> None:
 
 
 from .faiss_like import (METRIC_INNER_PRODUCT, METRIC_L2, CudaGpuBackend, CudaIndexFlat,  # noqa: E402
-                         CudaIndexIVFFlat, get_gpu_backend, merge_topk_device)
+                         CudaIndexIVFFlat, SearchToken, get_gpu_backend, merge_topk_device)
 from . import diskann_bridge  # noqa: E402
 from . import sharded  # noqa: E402
 

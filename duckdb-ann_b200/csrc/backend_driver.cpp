@@ -79,6 +79,22 @@ int main(int argc, char **argv) {
         gpu->search(nq, xq.data(), k, D.data(), I.data());
         for (int64_t q = 0; q < nq; q++) gpu->search(1, xq.data() + q * d, k, D1.data() + q * k, I1.data() + q * k);
 
+        // searchAsync (MetalIndexFlat.h:71-76): one token per query, all in flight, then waited
+        // on in reverse order; the answers are those of the synchronous calls
+        int async_ok = 1;
+        if (!ivf) {  // CpuToGpu hands out a CudaIndexFlat for an IndexFlat
+            auto *gf = static_cast<faiss_cuda::CudaIndexFlat *>(gpu.get());
+            std::vector<float> D2((size_t)(nq * k));
+            std::vector<int64_t> I2((size_t)(nq * k));
+            std::vector<faiss_cuda::CudaSearchToken> tokens;
+            for (int64_t q = 0; q < nq; q++)
+                tokens.push_back(gf->searchAsync(1, xq.data() + q * d, k, D2.data() + q * k, I2.data() + q * k));
+            for (int64_t q = nq - 1; q >= 0; q--) tokens[(size_t)q].wait();
+            for (auto &t : tokens) async_ok = async_ok && t.isReady();
+            async_ok = async_ok && memcmp(D2.data(), D1.data(), D1.size() * 4) == 0 &&
+                       memcmp(I2.data(), I1.data(), I1.size() * 8) == 0;
+        }
+
         // round trip: every row comes back bit for bit
         std::unique_ptr<faiss::Index> back = backend.GpuToCpu(gpu.get());
         int roundtrip_ok = back->ntotal == n;
@@ -121,8 +137,8 @@ int main(int argc, char **argv) {
         fwrite(D1.data(), 4, D1.size(), o);
         fwrite(I1.data(), 8, I1.size(), o);
         fclose(o);
-        printf("{\"backend\": \"%s\", \"roundtrip_ok\": %d, \"rejects_unknown\": %d}\n", backend.BackendName().c_str(),
-               roundtrip_ok, rejects_unknown);
+        printf("{\"backend\": \"%s\", \"roundtrip_ok\": %d, \"rejects_unknown\": %d, \"async_ok\": %d}\n",
+               backend.BackendName().c_str(), roundtrip_ok, rejects_unknown, async_ok);
         return 0;
     } catch (const std::exception &e) {
         fprintf(stderr, "error: %s\n", e.what());

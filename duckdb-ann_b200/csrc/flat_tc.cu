@@ -984,6 +984,8 @@ int launch_variant(const FlatPlan &plan, const CUtensorMap maps[4], const Kernel
 }  // namespace
 
 #ifndef ANN_TC_VARIANT_BK32
+constexpr int64_t kMaxTilesPerChunk = 2;
+
 FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms) {
     FlatPlan p;
     p.nq_tiles = (int)((nq + BM - 1) / BM);
@@ -992,7 +994,15 @@ FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms) {
     const int ctas_per_qt = (sms + p.nq_tiles - 1) / p.nq_tiles;
     int64_t tpc = ntiles / ((int64_t)ctas_per_qt * 8);
     if (tpc < 1) tpc = 1;
-    if (tpc > 512) tpc = 512;
+    // ... and short enough that all CTAs stay within a few MB of one another in the store: the
+    // CTAs of one query tile pull consecutive chunks and every query tile starts at row 0, so a row
+    // tile is fetched from DRAM by the first CTA that needs it and from L2 by the others, as long
+    // as they are no more than a few tens of microseconds apart.  With long chunks (hundreds of
+    // tiles) the 148 CTAs spread over gigabytes and every query tile streamed the store from DRAM
+    // by itself (measured on 20M x 768 rows, 4096 queries: 14.0k queries/s with chunks of up to
+    // 512 tiles, 14.4k with 4, 15.3k with 3, 16.0-16.5k with 2 or 1; the SM clock under the power
+    // cap rises with every byte that does not come from DRAM).
+    if (tpc > kMaxTilesPerChunk) tpc = kMaxTilesPerChunk;
     p.tiles_per_chunk = (int)tpc;
     p.nchunks = (int)((ntiles + tpc - 1) / tpc);
     // one k-list per CTA that ever works on a query tile; the merge sorts lists * k candidates

@@ -56,6 +56,27 @@ ANN_CUDA_EXPORT void CudaIndexFlat::reset() {
     if (ann_cuda_index_reset(handle_)) fail("CudaIndexFlat::reset");
     ntotal = 0;
 }
+ANN_CUDA_EXPORT CudaSearchToken CudaIndexFlat::searchAsync(faiss::idx_t n, const float *x, faiss::idx_t k,
+                                                           float *distances, faiss::idx_t *labels,
+                                                           const faiss::SearchParameters *) const {
+    ann_cuda_search_token *t = nullptr;
+    if (ann_cuda_index_search_async(handle_, n, x, k, distances, labels, &t)) fail("CudaIndexFlat::searchAsync");
+    return CudaSearchToken(t);
+}
+ANN_CUDA_EXPORT CudaSearchToken &CudaSearchToken::operator=(CudaSearchToken &&o) noexcept {
+    if (this != &o) {
+        ann_cuda_search_token_free(token_);
+        token_ = o.token_;
+        o.token_ = nullptr;
+    }
+    return *this;
+}
+ANN_CUDA_EXPORT CudaSearchToken::~CudaSearchToken() { ann_cuda_search_token_free(token_); }
+ANN_CUDA_EXPORT void CudaSearchToken::wait() {
+    if (token_ && ann_cuda_search_token_wait(token_)) fail("CudaSearchToken::wait");
+}
+ANN_CUDA_EXPORT bool CudaSearchToken::isReady() const { return !token_ || ann_cuda_search_token_ready(token_) == 1; }
+
 ANN_CUDA_EXPORT void CudaIndexFlat::reconstruct(faiss::idx_t key, float *recons) const {
     if (ann_cuda_index_reconstruct(handle_, key, recons)) fail("CudaIndexFlat::reconstruct");
 }

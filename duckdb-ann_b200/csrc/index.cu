@@ -1297,6 +1297,122 @@ int ann_cuda_index_search(const ann_cuda_index *ix, int64_t n, const float *x, i
     return 0;
 }
 
+// ---- asynchronous search (MetalIndexFlat.h:15-36, MetalIndexFlat.mm:371-443) --------------------
+// The token keeps one workspace (its stream and staging buffers) leased until it is waited on or
+// freed, so several searches can be in flight on one index.
+struct ann_cuda_search_token {
+    const ann_cuda_index *ix = nullptr;
+    WsLease *lease = nullptr;
+    cudaEvent_t done = nullptr;
+    int64_t n = 0, k = 0;
+    float *distances = nullptr;
+    int64_t *labels = nullptr;
+    bool waited = false;
+    int rc = 0;
+};
+
+int ann_cuda_index_search_async(const ann_cuda_index *ix, int64_t n, const float *x, int64_t k, float *distances,
+                                int64_t *labels, ann_cuda_search_token **out) {
+    if (!out) return set_error("invalid arguments");
+    *out = nullptr;
+    if (!ix || n < 0 || (n > 0 && (!x || !distances || !labels))) return set_error("invalid arguments");
+    if (k <= 0) return set_error("k must be > 0");
+    auto *t = new ann_cuda_search_token();
+    t->ix = ix;
+    t->n = n;
+    t->k = k;
+    t->distances = distances;
+    t->labels = labels;
+    if (n == 0) {
+        t->waited = true;
+        *out = t;
+        return 0;
+    }
+    DeviceGuard g(ix->device);
+    int rc = ensure_device(ix, g);
+    if (!rc) {
+        t->lease = new WsLease(ix, nullptr, true);
+        if (!t->lease->ws) rc = -1;
+    }
+    if (!rc) {
+        Workspace &ws = *t->lease->ws;
+        cudaStream_t s = ws.own_stream;
+        rc = ws.x.ensure((size_t)n * ix->d * 4) || ws.out_d.ensure((size_t)n * k * 4) || ws.out_i.ensure((size_t)n * k * 8);
+        // the copy out of pageable memory is staged before the call returns: x may be reused at once
+        if (!rc && cudaMemcpyAsync(ws.x.ptr, x, (size_t)n * ix->d * 4, cudaMemcpyHostToDevice, s) != cudaSuccess)
+            rc = set_error("query upload failed");
+        if (!rc) {
+            *ws.status_host = 0;
+            rc = search_device_impl(*ix, ws, n, ws.x.as<float>(), k, ws.out_d.as<float>(), ws.out_i.as<int64_t>(), 0, s);
+        }
+        if (!rc && (cudaEventCreateWithFlags(&t->done, cudaEventDisableTiming) != cudaSuccess ||
+                    cudaEventRecord(t->done, s) != cudaSuccess))
+            rc = set_error("event record failed");
+    }
+    if (rc) {
+        ann_cuda_search_token_free(t);
+        return -1;
+    }
+    *out = t;
+    return 0;
+}
+
+int ann_cuda_search_token_ready(const ann_cuda_search_token *t) {
+    if (!t) return set_error("null token");
+    if (t->waited || !t->done) return 1;
+    return cudaEventQuery(t->done) == cudaSuccess ? 1 : 0;
+}
+
+int ann_cuda_search_token_wait(ann_cuda_search_token *t) {
+    if (!t) return set_error("null token");
+    if (t->waited) return t->rc;
+    t->waited = true;
+    const ann_cuda_index *ix = t->ix;
+    DeviceGuard g(ix->device);
+    Workspace &ws = *t->lease->ws;
+    cudaStream_t s = ws.own_stream;
+    auto finish = [&](int rc) {
+        t->rc = rc;
+        delete t->lease;
+        t->lease = nullptr;
+        return rc;
+    };
+    for (int pass = 0; pass < 2; pass++) {
+        if (cudaMemcpyAsync(t->distances, ws.out_d.ptr, (size_t)t->n * t->k * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+            cudaMemcpyAsync(t->labels, ws.out_i.ptr, (size_t)t->n * t->k * 8, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+            cudaStreamSynchronize(s) != cudaSuccess)
+            return finish(set_error("asynchronous search failed: %s", cudaGetErrorString(cudaGetLastError())));
+        const int code = *ws.status_host;
+        *ws.status_host = 0;
+        if (code == 0) break;
+        if (code != kScreenOverflow || pass == 1) return finish(set_error("flat kernel gave up on a wait (code %d)", code));
+        // some query had more rows inside its screening band than spare candidates: once more,
+        // with the three-MMA product, from the queries still held in the workspace
+        g_screen_fallbacks.fetch_add(1, std::memory_order_relaxed);
+        t_no_screen = true;
+        const int rc = search_device_impl(*ix, ws, t->n, ws.x.as<float>(), t->k, ws.out_d.as<float>(),
+                                          ws.out_i.as<int64_t>(), 0, s);
+        t_no_screen = false;
+        if (rc) return finish(-1);
+    }
+    return finish(0);
+}
+
+void ann_cuda_search_token_free(ann_cuda_search_token *t) {
+    if (!t) return;
+    if (t->lease) {
+        // never hand a workspace back while its stream still writes into it
+        if (t->lease->ws) {
+            DeviceGuard g(t->ix->device);
+            cudaStreamSynchronize(t->lease->ws->own_stream);
+            *t->lease->ws->status_host = 0;
+        }
+        delete t->lease;
+    }
+    if (t->done) cudaEventDestroy(t->done);
+    delete t;
+}
+
 int ann_cuda_index_reset(ann_cuda_index *ix) {
     if (!ix) return set_error("null index");
     DeviceGuard g(ix->device);

@@ -30,6 +30,37 @@ def _ptr(a):
     return C.c_void_p(a.ctypes.data) if a is not None else None
 
 
+class SearchToken:
+    """MetalSearchToken (MetalIndexFlat.h:15-36): owns one in-flight search."""
+
+    def __init__(self, handle, D, I, index):
+        self._t, self._D, self._I, self._index = handle, D, I, index  # the index outlives its tokens
+
+    def is_ready(self) -> bool:
+        """Non-blocking: True once the device work has finished."""
+        return not self._t or _pkg().lib().ann_cuda_search_token_ready(self._t) == 1
+
+    def wait(self):
+        """Blocks until the search has finished; returns (D, I)."""
+        if self._t:
+            p = _pkg()
+            rc = p.lib().ann_cuda_search_token_wait(self._t)
+            self.close()
+            p.check(rc, "search_async wait")
+        return self._D, self._I
+
+    def close(self) -> None:
+        if self._t:
+            _pkg().lib().ann_cuda_search_token_free(self._t)
+            self._t = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class _CudaIndex:
     """Common faiss::Index surface: d, ntotal, metric_type, is_trained, add,
     search, reset, reconstruct."""
@@ -87,6 +118,21 @@ class _CudaIndex:
         p = _pkg()
         p.check(p.lib().ann_cuda_index_search(self._h, n, _ptr(x), k, _ptr(D), _ptr(I)), "search")
         return D, I
+
+    def search_async(self, x, k: int) -> "SearchToken":
+        """MetalIndexFlat::searchAsync (MetalIndexFlat.h:71-76): enqueue the search and return
+        a token; token.wait() -> (D, I).  Several tokens may be in flight on one index."""
+        x = _np_f32(x)
+        if x.ndim != 2 or x.shape[1] != self.d:
+            raise ValueError(f"search_async: expected (n, {self.d}) queries")
+        n = x.shape[0]
+        D = np.empty((n, max(k, 0)), np.float32)
+        I = np.empty((n, max(k, 0)), np.int64)
+        tok = C.c_void_p()
+        p = _pkg()
+        p.check(p.lib().ann_cuda_index_search_async(self._h, n, _ptr(x), k, _ptr(D), _ptr(I), C.byref(tok)),
+                "search_async")
+        return SearchToken(tok, D, I, self)
 
     def search_device(self, x, k: int, D=None, I=None, label_offset: int = 0, stream=None):
         """search() on device buffers (torch CUDA tensors), enqueued on `stream`

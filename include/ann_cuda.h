@@ -114,6 +114,21 @@ int ann_cuda_index_search_device(const ann_cuda_index *index, int64_t n, const f
                                  float *distances_device, int64_t *labels_device, int64_t label_offset,
                                  void *stream);
 
+/* MetalIndexFlat::searchAsync and its MetalSearchToken (MetalIndexFlat.h:15-36,
+ * MetalIndexFlat.mm:371-443): the search is enqueued and the call returns; `x` may be reused
+ * at once, `distances` / `labels` (host) are written by ann_cuda_search_token_wait.  Each token
+ * holds its own stream and staging buffers until it is waited on or freed, so several searches
+ * can be in flight on one index.  _ready: 1 when the device work has finished, 0 while it
+ * runs, -1 on a null token.  _wait: blocks, copies the results out, returns 0 or -1; a second
+ * wait returns the first one's result.  _free may be called without a wait (the results are
+ * then dropped).  Works for Flat and IVFFlat indexes. */
+typedef struct ann_cuda_search_token ann_cuda_search_token;
+int ann_cuda_index_search_async(const ann_cuda_index *index, int64_t n, const float *x, int64_t k, float *distances,
+                                int64_t *labels, ann_cuda_search_token **token);
+int ann_cuda_search_token_ready(const ann_cuda_search_token *token);
+int ann_cuda_search_token_wait(ann_cuda_search_token *token);
+void ann_cuda_search_token_free(ann_cuda_search_token *token);
+
 /* faiss::Index::reset / reconstruct (MetalIndexFlat.mm:445-478). reconstruct is
  * bit-exact; for IVFFlat `key` is the label given at add time. */
 int ann_cuda_index_reset(ann_cuda_index *index);

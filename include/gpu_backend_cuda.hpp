@@ -14,8 +14,28 @@
 #include <memory>
 
 struct ann_cuda_index;
+struct ann_cuda_search_token;
 
 namespace faiss_cuda {
+
+// Move-only handle of one in-flight search (the role of faiss_metal::MetalSearchToken,
+// faiss-metal/include/faiss-metal/MetalIndexFlat.h:15-36).
+class CudaSearchToken {
+public:
+    CudaSearchToken(CudaSearchToken &&o) noexcept : token_(o.token_) { o.token_ = nullptr; }
+    CudaSearchToken &operator=(CudaSearchToken &&o) noexcept;
+    ~CudaSearchToken();
+    CudaSearchToken(const CudaSearchToken &) = delete;
+    CudaSearchToken &operator=(const CudaSearchToken &) = delete;
+
+    void wait();           // blocks, then the caller's distances / labels are filled; throws on a device error
+    bool isReady() const;  // non-blocking
+
+private:
+    friend class CudaIndexFlat;
+    explicit CudaSearchToken(ann_cuda_search_token *t) : token_(t) {}
+    ann_cuda_search_token *token_ = nullptr;
+};
 
 class CudaIndexFlat : public faiss::Index {
 public:
@@ -29,6 +49,11 @@ public:
                 const faiss::SearchParameters *params = nullptr) const override;
     void reset() override;
     void reconstruct(faiss::idx_t key, float *recons) const override;
+
+    // Enqueues the search and returns; token.wait() fills distances / labels
+    // (MetalIndexFlat.h:71-76).  x may be reused as soon as this returns.
+    CudaSearchToken searchAsync(faiss::idx_t n, const float *x, faiss::idx_t k, float *distances, faiss::idx_t *labels,
+                                const faiss::SearchParameters *params = nullptr) const;
 
     // Copies rows [first, first + n) to host memory (the role of getVectorsData()).
     void getRows(faiss::idx_t first, faiss::idx_t n, float *rows) const;

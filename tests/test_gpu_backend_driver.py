@@ -45,7 +45,7 @@ def test_flat_through_gpu_backend(tmp_path, oracle, metric):
     xb = rng.uniform(-1, 1, (3000, 96)).astype(np.float32)
     xq = rng.uniform(-1, 1, (12, 96)).astype(np.float32)
     info, D, I, D1, I1 = _run(tmp_path, "flat", 96, 7, metric, xb, xq)
-    assert info == {"backend": "cuda", "roundtrip_ok": 1, "rejects_unknown": 1}
+    assert info == {"backend": "cuda", "roundtrip_ok": 1, "rejects_unknown": 1, "async_ok": 1}
     Dref, Iref = oracle.flat_search(xb, xq, 7, metric)
     assert_topk_matches(oracle, xb, xq, metric, D, I, Dref, Iref, "batch")
     assert_topk_matches(oracle, xb, xq, metric, D1, I1, Dref, Iref, "one query per call")

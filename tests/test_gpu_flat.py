@@ -106,6 +106,10 @@ def test_screening_falls_back_when_its_spare_candidates_run_out(pkg, oracle):
             assert pkg.lib().ann_cuda_screen_fallbacks() == before + 1, "the overflow went unnoticed"
             Dref, Iref = oracle.flat_search(xb, xq, k, m)
             assert_topk_matches(oracle, xb, xq, m, D, I, Dref, Iref, f"screen overflow {metric_name}")
+            Da, Ia = idx.search_async(xq, k).wait()      # the token's wait repeats the search the same way
+            assert pkg.lib().ann_cuda_screen_fallbacks() == before + 2
+            np.testing.assert_array_equal(Ia, I)
+            np.testing.assert_array_equal(Da, D)
             idx.close()
     finally:
         pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05")
@@ -207,6 +211,37 @@ def test_unit_norm_inner_product_k100(pkg, oracle):
     Dref, Iref = oracle.flat_search(xb, xq, 100, oracle.METRIC_IP)
     assert_topk_matches(oracle, xb, xq, oracle.METRIC_IP, D, I, Dref, Iref, "C4 scaled")
     idx.close()
+
+
+def test_search_async_tokens(pkg, oracle, kernel):
+    """searchAsync (faiss-metal/src/MetalIndexFlat.mm:371-443): several tokens in flight on one
+    index, waited on out of order, give what search() gives; n == 0 and an empty index answer at
+    once; a token may be dropped without a wait."""
+    xb, xq = _data(11, 6000, 40, 96)
+    for metric_name in ("L2", "IP"):
+        m = _metric(pkg, metric_name)
+        idx = pkg.CudaIndexFlat(96, m)
+        empty = idx.search_async(xq[:2], 3)            # ntotal == 0: sentinels (MetalIndexFlat.mm:385-395)
+        De, Ie = empty.wait()
+        assert (Ie == -1).all() and np.isinf(De).all()
+        idx.add(xb)
+        Dsync, Isync = idx.search(xq, 20)
+        tokens = [idx.search_async(xq[i:i + 8], 20) for i in range(0, 40, 8)]
+        dropped = idx.search_async(xq, 20)
+        dropped.close()
+        for j in (3, 0, 4, 1, 2):
+            D, I = tokens[j].wait()
+            assert tokens[j].is_ready()
+            np.testing.assert_array_equal(I, Isync[8 * j:8 * j + 8])
+            np.testing.assert_array_equal(D, Dsync[8 * j:8 * j + 8])
+            assert tokens[j].wait()[1] is I            # a second wait is a no-op
+        none = idx.search_async(xq[:0], 20)
+        assert none.is_ready() and none.wait()[0].shape == (0, 20)
+        Dref, Iref = oracle.flat_search(xb, xq, 20, m)
+        assert_topk_matches(oracle, xb, xq, m, Dsync, Isync, Dref, Iref, f"async {metric_name}")
+        with pytest.raises(RuntimeError):
+            idx.search_async(xq, 0)
+        idx.close()
 
 
 def test_concurrent_search(pkg, oracle):

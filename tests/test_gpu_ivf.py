@@ -93,6 +93,22 @@ def test_ip_reference_shape(pkg, oracle):
     idx.close()
 
 
+def test_search_async_on_an_ivf_index(pkg, oracle):
+    """The token interface of the flat index also serves IVFFlat: same answers as search()."""
+    rng = np.random.default_rng(7)
+    xb = rng.uniform(-1, 1, (3000, 48)).astype(np.float32)
+    xq = rng.uniform(-1, 1, (24, 48)).astype(np.float32)
+    idx, cent, off, rows = _build(pkg, oracle, xb, 12, pkg.METRIC_L2)
+    idx.setNprobe(3)
+    D, I = idx.search(xq, 9)
+    tokens = [idx.search_async(xq[i:i + 6], 9) for i in range(0, 24, 6)]
+    for j in (2, 3, 0, 1):
+        Da, Ia = tokens[j].wait()
+        np.testing.assert_array_equal(Ia, I[6 * j:6 * j + 6])
+        np.testing.assert_array_equal(Da, D[6 * j:6 * j + 6])
+    idx.close()
+
+
 def test_known_answer_from_reference_sql(pkg, oracle):
     with open(os.path.join(os.path.dirname(__file__), "golden", "reference_known_answers.json")) as f:
         case = json.load(f)["ivfflat"][0]
