@@ -220,7 +220,7 @@ class FlatWorkload:
                 if self.n * self.d * 8 / max(world, 1) > 1e9 else "database is L2-sized (a warm-cache figure; the full-size workload is the headline)",
                 "flat_kernel": self.pkg.lib().ann_cuda_flat_kernel_name().decode() if getattr(self, "pkg", None)
                 else "cpu",
-                "search": "one-MMA screening + exact re-ranking (stores >= 2M rows, 16 < k <= 128), else three-MMA split product"}
+                "search": "one-MMA screening + exact re-ranking (stores >= 2M rows, k <= 128), else three-MMA split product"}
 
     def roofline(self, peaks, kernel_ms):
         local_rows = self.hi - self.lo
@@ -228,7 +228,7 @@ class FlatWorkload:
         achieved = flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms and kernel_ms > 0 else None
         # Stores of two million rows or more are searched with one-MMA screening (one TF32 MMA per
         # product, candidates re-ranked exactly); smaller ones with the three-MMA split product.
-        screened = local_rows >= 2_000_000 and 16 < self.k <= 128 and self.pkg.lib().ann_cuda_flat_kernel_name().decode() == "tcgen05"
+        screened = local_rows >= 2_000_000 and self.k <= 128 and self.pkg.lib().ann_cuda_flat_kernel_name().decode() == "tcgen05"
         mmas = 1 if screened else 3
         peak = peaks["bf16_tflops_sustained"] / 2.0 / mmas
         # DRAM traffic of one launch, from ncu captures of this kernel on 400,000 rows with 4,096
@@ -294,8 +294,8 @@ class FlatWorkload:
 
 
 # DRAM read + write bytes of one grouped list-scan launch, keyed by (rows, queries, GPUs), from the
-# ncu capture of the grouped list scan at the default shape (16.05 GB read + 0.23 GB written)
-IVF_SCAN_TRAFFIC = {(1_000_000, 10_000, 1): 16.28e9}
+# ncu capture of the grouped list scan at the default shape (14.6-14.8 GB read + 0.2 GB written)
+IVF_SCAN_TRAFFIC = {(1_000_000, 10_000, 1): 14.8e9}
 
 
 class IvfWorkload:
@@ -386,8 +386,9 @@ class IvfWorkload:
         # (rows scanned x d x 4, per GPU).  The kernel gathers the queries probing a list into
         # tiles of 128 and reads a list row once per tile, on the tensor cores, so the
         # algorithmic rate EXCEEDS the HBM peak by design (frac > 1); `traffic` is what DRAM
-        # really moved, and `tensor` restates the same launch against the MMA roofline that
-        # actually bounds it (useful flops = 2 d per (query, row) pair; tile padding not counted).
+        # really moved (the physical bound: ~5.5 TB/s of it at the full size), and `tensor` restates
+        # the same launch against the MMA roofline (useful flops = 2 d per (query, row) pair; tile
+        # padding not counted).
         pairs = self.rows_scanned / max(self.world, 1)
         alg_bytes = pairs * self.d * 4
         secs = kernel_ms * 1e-3 if kernel_ms and kernel_ms > 0 else None
@@ -404,7 +405,10 @@ class IvfWorkload:
                            "frac": tflops / tpeak if tflops else None,
                            "peak_note": f"{peaks['_source']} bf16 sustained / 2 (TF32) / 3 (split-TF32)"},
                 "note": "queries probing one list share its rows through 128-query tensor-core tiles, so the "
-                        "algorithmic figure exceeds 1; the kernel is bound by the MMA pipe (see tensor)"}
+                        "algorithmic figure exceeds 1; physically the launch is bound by its DRAM traffic "
+                        "(`traffic` / kernel time, against the same peak)",
+                "traffic_gbs": (IVF_SCAN_TRAFFIC.get((self.n, self.nq, self.world), 0) / 1e9 / secs
+                                if secs and IVF_SCAN_TRAFFIC.get((self.n, self.nq, self.world)) else None)}
 
     def verify(self, torch, D, I):
         D = D.cpu().numpy()

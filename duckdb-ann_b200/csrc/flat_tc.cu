@@ -26,11 +26,20 @@
 // chunks of it one by one with atomicAdd, and keeps ONE k-list per row for as long
 // as it stays with that query tile, so a list sees a long stream of rows and
 // settles after the first few tiles.  When a query tile has no chunks left the CTA
-// moves to another one and starts a new list there.  All query tiles advance
-// through the chunks in the same order at the same rate, so the CTAs running at
-// any moment read the same database rows and share them through L2.  At the end
-// each query has one unsorted k-list per CTA that worked on its tile (at most
-// lists_per_qt); merge.cu reduces them to the final top-k.
+// moves to another one and starts a new list there.  At the end each query has
+// one k-list per CTA that worked on its tile (at most lists_per_qt); merge.cu
+// reduces them to the final top-k.
+//
+// The screened search of a large store is walked with a STATIC schedule instead (see
+// choose_static): every CTA owns the same share of each chunk of the store, so all
+// CTAs stay within two chunks of one another (an arrival counter per chunk paces
+// them) and a row tile comes from DRAM once, from L2 for the other query tiles.
+// Handing chunks out per query tile cannot do that: 148 CTAs do not divide evenly
+// over the query tiles, the tiles with one CTA more run ahead, and a 20M x 768
+// store was read from DRAM ~11 times per search (3 TB/s) - power the SMs then did
+// not get under the board's cap.  A CTA's share touches at most two query tiles;
+// it alternates between their two lists, keeping the one it is not working on
+// parked (its fill counts in global memory).
 //
 // CTA layout (192 threads, one CTA per SM):
 //   warp 0     scheduler + TMA producer: takes the next chunk, announces it to the
@@ -283,6 +292,12 @@ struct KernelArgs {
     const int4 *items;          // {gathered query tile, first row, end row, unused}; null = flat mode
     const int *n_items;         // device count of items
     int *item_counter;          // zero on entry
+    // Static schedule (see FlatPlan::static_g): arrivals[c] counts the CTAs that have started
+    // chunk c (zero on entry); slot_cnt[list * 128 + row] keeps the fill count of a row's append
+    // buffer while its CTA works for its other query tile
+    int static_g, static_chunks;
+    int *arrivals;
+    int *slot_cnt;
     const int32_t *qrow_query;  // gathered row -> query (its threshold word), -1 = padding row
     // Grouped L2 with residual queries (may be null): constant K of every gathered row such that
     // key + K is comparable between the lists of one query; keys inside the kernel leave it out
@@ -540,12 +555,78 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             };
             const int home = blockIdx.x % args.nq_tiles;
             bool have = false;
-            if (!args.items)
+            if (!args.items && !args.static_g)
                 for (int i = 0; i < args.nq_tiles && !have; i++) have = adopt((home + i) % args.nq_tiles);
             const int n_items = args.items ? *args.n_items : 0;
+            // static schedule: this CTA's share [ulo, uhi) of the units of every chunk, the (at
+            // most two) query tiles it falls into, their list slots
+            const int G = args.static_g;
+            const long long U = (long long)args.nq_tiles * G;
+            const int ulo = G ? (int)(blockIdx.x * U / gridDim.x) : 0;
+            const int uhi = G ? (int)((blockIdx.x + 1) * U / gridDim.x) : 0;
+            const int t_first = G ? ulo / G : 0, t_last = G ? (uhi - 1) / G : -1;
+            int st_slot[2] = {-1, -1};
+            int st_chunk = 0, st_tile = t_first, st_active = -1, st_close = 0;
+            bool st_arrived = false;
             for (;;) {
                 int64_t r_begin, r_end;
-                if (args.items) {
+                if (G) {
+                    bool got = false;
+                    while (!got && st_chunk < args.static_chunks) {
+                        if (st_tile > t_last) {
+                            st_chunk++;
+                            st_tile = t_first;
+                            st_arrived = false;
+                            continue;
+                        }
+                        if (!st_arrived) {
+                            // nobody starts chunk c before everybody has started chunk c - 1: the
+                            // CTAs stay within two chunks of one another in the store.  Bounded:
+                            // pacing is an optimisation, never a condition for progress.
+                            if (st_chunk > 0) {
+                                const volatile int *prev = args.arrivals + (st_chunk - 1);
+                                for (int spins = 0; *prev < (int)gridDim.x && spins < 20000; spins++) __nanosleep(100);
+                            }
+                            atomicAdd(args.arrivals + st_chunk, 1);
+                            st_arrived = true;
+                        }
+                        const int t = st_tile++;
+                        const int a = ulo > t * G ? ulo : t * G, b = uhi < (t + 1) * G ? uhi : (t + 1) * G;
+                        if (a >= b) continue;
+                        r_begin = ((int64_t)st_chunk * G + (a - t * G)) * BN;
+                        r_end = ((int64_t)st_chunk * G + (b - t * G)) * BN;
+                        if (r_begin >= args.n) continue;
+                        if (r_end > args.n) r_end = args.n;
+                        const int si = t - t_first;
+                        if (st_slot[si] < 0) {
+                            const int j = atomicAdd(args.nlists + t, 1);
+                            if (j >= args.lists_per_qt) {  // cannot happen with the plan's list count
+                                atomicExch(args.status, 9);
+                                *abort_flag = 1;
+                                goto done;
+                            }
+                            st_slot[si] = t * args.lists_per_qt + j;
+                            fresh = 1;
+                        } else {
+                            fresh = st_active != t ? 2 : 0;
+                        }
+                        st_active = t;
+                        cur = t;
+                        slot = st_slot[si];
+                        got = true;
+                    }
+                    if (!got) {
+                        // all chunks done: one empty item per list, which closes it
+                        while (st_close < 2 && st_slot[st_close] < 0) st_close++;
+                        if (st_close >= 2) break;
+                        cur = t_first + st_close;
+                        slot = st_slot[st_close];
+                        fresh = (st_active != cur ? 2 : 0) | 4;
+                        st_active = cur;
+                        st_close++;
+                        r_begin = r_end = 0;
+                    }
+                } else if (args.items) {
                     // grouped mode: items are independent, each with its own lists
                     const int i = atomicAdd(args.item_counter, 1);
                     if (i >= n_items) break;
@@ -729,8 +810,14 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_wempty + 8 * w);
             if (qt < 0) break;
-            if (fresh) {
-                close_list();
+            if (fresh & 3) {
+                if (args.static_g) {
+                    // static schedule: the list left behind is taken up again later; only its fill
+                    // count has to survive (the buffer is in global memory, thresholds are shared)
+                    if (APPEND && unit_key) args.slot_cnt[(size_t)cur_slot * BM + row] = cnt;
+                } else {
+                    close_list();
+                }
                 cur_slot = slot;
                 unit_key = args.part_key + (size_t)slot * BM * stride;
                 unit_idx = args.part_idx + (size_t)slot * BM * stride;
@@ -752,7 +839,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 tau = row_valid ? kInf : -kInf;
                 list_max = kInf;
                 published = kInf;
-                cnt = 0;
+                cnt = (APPEND && (fresh & 2)) ? args.slot_cnt[(size_t)slot * BM + row] : 0;
                 pos = 0;
                 if (APPEND) {
                     // nothing to initialise: a row's buffer is valid up to its fill count
@@ -925,6 +1012,10 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     atomicMin(qtau_word, float_to_ordered(__fadd_ru(list_max, koff)));
                 }
             }
+            if (fresh & 4) {  // static schedule, after the last chunk: this list is complete
+                close_list();
+                unit_key = nullptr;
+            }
         }
         close_list();
     }
@@ -986,6 +1077,38 @@ int launch_variant(const FlatPlan &plan, const CUtensorMap maps[4], const Kernel
 #ifndef ANN_TC_VARIANT_BK32
 constexpr int64_t kMaxTilesPerChunk = 2;
 
+namespace {
+int gcd_int(int a, int b) { return b ? gcd_int(b, a % b) : a; }
+
+// Static schedule for the screened search of a large store.  (Measured with the three-MMA product
+// as well, 5M x 768 rows, 4096 queries, k = 10: 149 ms against 126 ms with dynamic chunks - that
+// kernel is bound by the tensor pipe and gains nothing from the saved DRAM reads - so it is not
+// used there.)  A chunk is G row tiles; its
+// nq_tiles * G units (query tile t = u / G, row tile u % G) are dealt to the CTAs in equal
+// contiguous shares, the same for every chunk, so that
+//  - every CTA does the same work per chunk and all of them walk the store together: a row tile
+//    comes from DRAM once and from L2 for the other query tiles (with chunks handed out per query
+//    tile the tiles that have one CTA more run ahead, and the store was read ~11 times);
+//  - a CTA works for at most two query tiles, alternating between their two lists.
+// G = sms / gcd(sms, nq_tiles) makes the shares exact.
+void choose_static(FlatPlan &p, int64_t n, int sms, bool screened) {
+    p.static_g = 0;
+    p.static_chunks = 0;
+    p.sched_ints = (size_t)p.nq_tiles * 2;
+    static const bool off = [] { const char *e = getenv("ANN_CUDA_STATIC"); return e && atoi(e) == 0; }();
+    if (!screened || off || p.nq_tiles > sms) return;
+    const int64_t ntiles = (n + BN - 1) / BN;
+    const int g = sms / gcd_int(sms, p.nq_tiles);
+    const int ctas_per_qt = (sms + p.nq_tiles - 1) / p.nq_tiles;
+    if (ntiles < 16 * (int64_t)g || p.lists_per_qt < ctas_per_qt + 1) return;  // short stores: the ragged last chunk would cost more
+    p.static_g = g;
+    p.static_chunks = (int)((ntiles + g - 1) / g);
+    p.grid = sms;
+    // + one arrival counter per chunk, + one fill count per (list, row)
+    p.sched_ints += (size_t)p.static_chunks + (size_t)p.nq_tiles * p.lists_per_qt * BM;
+}
+}  // namespace
+
 FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms) {
     FlatPlan p;
     p.nq_tiles = (int)((nq + BM - 1) / BM);
@@ -1017,6 +1140,7 @@ FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms) {
     p.list_stride = (k > kQueueDepth && k <= kAppendMaxK) ? kBuf : k;
     p.lists_sorted = (k > kQueueDepth && k <= kAppendMaxK);
     p.part_entries = (size_t)p.nq_tiles * lists * BM * (size_t)p.list_stride;
+    choose_static(p, n, sms, false);
     return p;
 }
 
@@ -1026,6 +1150,7 @@ FlatPlan make_flat_plan_screened(int64_t nq, int64_t n, int k, int sms) {
     p.list_stride = kBuf;
     p.lists_sorted = true;
     p.part_entries = (size_t)p.nq_tiles * p.lists_per_qt * BM * (size_t)p.list_stride;
+    choose_static(p, n, sms, true);
     return p;
 }
 
@@ -1040,6 +1165,7 @@ FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms) {
     p.list_stride = (k > kQueueDepth && k <= kAppendMaxK) ? kBuf : k;
     p.lists_sorted = (k > kQueueDepth && k <= kAppendMaxK);
     p.part_entries = (size_t)max_query_tiles * BM * (size_t)p.list_stride;
+    p.sched_ints = 16;
     return p;
 }
 
@@ -1054,7 +1180,7 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     if (k <= 0 || k > kMaxK) return set_error("k must be in [1, %d]", kMaxK);
 #ifndef ANN_TC_VARIANT_BK32
     // the screened search runs in the build of this file with K blocks of 32 floats
-    if (screen && !grouped && screen->k_rank > kQueueDepth && screen->k_rank <= k && k <= kScreenMaxList && dp % 32 == 0)
+    if (screen && !grouped && screen->k_rank >= 1 && screen->k_rank <= k && k <= kScreenMaxList && dp % 32 == 0)
         return launch_flat_tc_bk32(plan, xhi, xlo, xnorm, n, qhi, qlo, nq, dp, k, metric, part_key, part_idx, qtau, sched,
                                    status, device, stream, grouped, screen);
 #endif
@@ -1085,11 +1211,16 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     a.items = grouped ? grouped->items : nullptr;
     a.n_items = grouped ? grouped->n_items : nullptr;
     a.item_counter = grouped ? grouped->item_counter : nullptr;
+    a.static_chunks = plan.static_chunks;
+    a.arrivals = sched + 2 * plan.nq_tiles;
+    a.slot_cnt = a.arrivals + plan.static_chunks;
     a.qrow_query = grouped ? grouped->qrow_query : nullptr;
     a.qrow_const = grouped ? grouped->qrow_const : nullptr;
     a.part_cnt = grouped ? grouped->part_cnt : nullptr;
-    const bool use_screen = screen && !grouped && screen->k_rank > kQueueDepth && screen->k_rank <= k && k <= kScreenMaxList;
+    const bool use_screen = screen && !grouped && screen->k_rank >= 1 && screen->k_rank <= k && k <= kScreenMaxList;
     a.screen = use_screen ? 1 : 0;
+    // the static schedule parks and resumes append buffers; it pays for the screened search only
+    a.static_g = use_screen ? plan.static_g : 0;
     a.k_rank = use_screen ? screen->k_rank : k;
     a.q_norm2 = use_screen ? screen->q_norm2 : nullptr;
     a.x_max_norm2 = use_screen ? screen->x_max_norm2 : nullptr;

@@ -326,7 +326,7 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         const FlatPlan plan = k_rank > 0 ? make_flat_plan_screened(nq, st.n, k, sm_count(ix.device))
                                          : make_flat_plan(nq, st.n, k, sm_count(ix.device));
         const ScreenInput screen{k_rank, ws.qn.as<float>(), st.max_norm2, d};
-        const size_t qtau_bytes = (size_t)plan.nq_tiles * 128 * 4, sched_bytes = (size_t)plan.nq_tiles * 2 * 4;
+        const size_t qtau_bytes = (size_t)plan.nq_tiles * 128 * 4, sched_bytes = plan.sched_ints * 4;
         if (ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4) ||
             ws.qtau.ensure(qtau_bytes) || ws.sched.ensure(sched_bytes))
             return -1;
@@ -646,14 +646,14 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
                         float *d_dev, int64_t *i_dev, int64_t label_offset, cudaStream_t stream) {
     if (!ix.ivf) {
         int k_sel = (int)std::min<int64_t>(k, ix.store.n);
-        // Large stores, 16 < k <= 128: one-MMA screening.  kScreenMaxList candidates come back, ranked
+        // Large stores, k <= 128: one-MMA screening.  kScreenMaxList candidates come back, ranked
         // by coarse keys; the exact re-ranking below picks the k.  Should more rows than the spare
         // holds fall inside the error band of some query, the status word says so and the host entry
         // point repeats the block without screening.  (ANN_CUDA_FLAT_SCREEN=0 turns it
         // off, =1 applies it to stores of any size.)
         const int screen_env = t_no_screen ? 0 : g_flat_screen.load(std::memory_order_relaxed);
         int k_rank = 0;
-        if (flat_kernel_choice() == FlatKernel::TC && k_sel > 16 && k_sel <= kAppendMaxK && ix.store.max_norm2 &&
+        if (flat_kernel_choice() == FlatKernel::TC && k_sel <= kAppendMaxK && ix.store.max_norm2 &&
             (screen_env == 1 || (screen_env != 0 && ix.store.n >= kScreenMinRows))) {
             const int k_list = (int)std::min<int64_t>((int64_t)kScreenMaxList, ix.store.n);
             if (k_list > k_sel) {

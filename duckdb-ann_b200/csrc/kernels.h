@@ -49,6 +49,11 @@ struct FlatPlan {
     int list_stride = 0;      // slots per row in the list memory (k, or the append buffer size)
     size_t part_entries = 0;  // nq_tiles * lists_per_qt * 128 * list_stride
     bool lists_sorted = false;  // every finished k-list is sorted best first (append mode)
+    // Static schedule (append selection on large stores; 0 = chunks are handed out dynamically):
+    // the store is walked in chunks of static_g row tiles and every CTA owns a fixed share of the
+    // nq_tiles * static_g (query tile, row tile) units of each chunk.
+    int static_g = 0, static_chunks = 0;
+    size_t sched_ints = 0;    // ints of scheduler memory (zero on entry)
 };
 // Chooses the decomposition for nq queries against n rows on a device with `sms` SMs.
 FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms);

@@ -213,6 +213,30 @@ def test_unit_norm_inner_product_k100(pkg, oracle):
     idx.close()
 
 
+@pytest.mark.parametrize("flat_kernel", ["tcgen05", "tcgen05-screened"])
+@pytest.mark.parametrize("shape", [(160_000, 4096, 32, 24), (620_000, 300, 16, 100), (310_000, 200, 24, 17), (310_000, 200, 24, 10)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_large_store_static_schedule(pkg, oracle, flat_kernel, shape):
+    """Stores of several hundred row tiles and more, k <= 128: every CTA owns a fixed share of each
+    chunk of the store and alternates between the lists of two query tiles (32 query tiles: shares
+    of 8 units out of 37 per tile; 3 and 2 query tiles: one CTA in 49 / 74 straddles two tiles).
+    Ragged last chunk, ragged last query tile."""
+    nv, nq, d, k = shape
+    xb, xq = _data(7, nv, nq, d)
+    assert pkg.lib().ann_cuda_set_flat_kernel(flat_kernel.encode()) == 0
+    try:
+        for metric_name in ("L2", "IP"):
+            m = _metric(pkg, metric_name)
+            idx = pkg.CudaIndexFlat(d, m)
+            idx.add(xb)
+            D, I = idx.search(xq, k)
+            idx.close()
+            Dref, Iref = oracle.flat_search(xb, xq, k, m)
+            assert_topk_matches(oracle, xb, xq, m, D, I, Dref, Iref, f"{flat_kernel} {metric_name} {shape}")
+    finally:
+        pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05")
+
+
 def test_search_async_tokens(pkg, oracle, kernel):
     """searchAsync (faiss-metal/src/MetalIndexFlat.mm:371-443): several tokens in flight on one
     index, waited on out of order, give what search() gives; n == 0 and an empty index answer at
