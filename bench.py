@@ -231,18 +231,21 @@ class FlatWorkload:
         screened = local_rows >= 2_000_000 and self.k <= 128 and self.pkg.lib().ann_cuda_flat_kernel_name().decode() == "tcgen05"
         mmas = 1 if screened else 3
         peak = peaks["bf16_tflops_sustained"] / 2.0 / mmas
-        # DRAM traffic of one launch, from ncu captures of this kernel on 400,000 rows with 4,096
-        # queries of 768 dimensions (screened: 11.1-11.2 GB read + 0.44 GB written; split product:
-        # 16.2-22.3 GB + 0.47-0.49 GB), scaled by the rows and query tiles of this launch: every
-        # 128-query tile streams the shard once, L2 absorbs part of it.
-        traffic = None
-        if self.d == 768:
-            per_launch = 11.6e9 if screened else 19.7e9
-            traffic = per_launch * (local_rows / 400_000.0) * (((self.nq + 127) // 128) / 32.0)
+        # DRAM traffic of one launch.  Screened search: ncu capture of the full-size launch (20M rows of
+        # 768 floats, 4,096 queries: 67.5 GB read + 1.2 GB written; the hi planes are 61.4 GB and are
+        # read once for all query tiles), scaled by the rows of this launch.  Split product: captures
+        # on 400,000 rows with 4,096 queries (16.2-22.3 GB + 0.47-0.49 GB), scaled by rows and query
+        # tiles: there every 128-query tile streams the shard and L2 absorbs part of it.
+        traffic, note = None, "no capture for this shape"
+        if self.d == 768 and screened:
+            traffic = 68.7e9 * (local_rows / 20_000_000.0)
+            note = "bytes; ncu dram read+write of the 20M-row launch scaled by rows"
+        elif self.d == 768:
+            traffic = 19.7e9 * (local_rows / 400_000.0) * (((self.nq + 127) // 128) / 32.0)
+            note = "bytes; ncu dram read+write of a 400,000-row launch scaled by rows and query tiles"
         return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak if achieved else None, "traffic": traffic,
-                "traffic_note": "bytes; ncu dram read+write of a 400,000-row launch scaled by rows and query tiles"
-                if traffic else "no capture for this shape",
+                "traffic_note": note,
                 "kernel": "flat_tc_kernel" + (" (screened, 32-float K blocks)" if screened else ""),
                 "kernel_ms": kernel_ms, "algorithmic_flops_per_launch": flops, "mma_per_product": mmas,
                 "peak_note": f"{peaks['_source']} bf16 sustained {peaks['bf16_tflops_sustained']} TFLOP/s / 2 (TF32 rate)"
