@@ -99,6 +99,7 @@ constexpr int kBBytes = BN * BK * 4;                    // 32 KB
 constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;  // hi + lo of both operands: 96 KB
 constexpr int kQueueDepth = 16;   // per-row candidate queue, also the small-k list capacity
 constexpr int kThreads = 192;
+constexpr int kPaceSpins = 10000;  // polls of ~100 ns a CTA of the static schedule waits for the others, once
 constexpr int kWorkRing = 4;       // chunk descriptors in flight between the scheduler and the other roles
 
 struct SmemLayout {
@@ -567,7 +568,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             const int t_first = G ? ulo / G : 0, t_last = G ? (uhi - 1) / G : -1;
             int st_slot[2] = {-1, -1};
             int st_chunk = 0, st_tile = t_first, st_active = -1, st_close = 0;
-            bool st_arrived = false;
+            bool st_arrived = false, st_paced = true;
             for (;;) {
                 int64_t r_begin, r_end;
                 if (G) {
@@ -583,9 +584,16 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             // nobody starts chunk c before everybody has started chunk c - pace_window:
                             // the CTAs stay within two chunks of one another in the store.  Bounded:
                             // pacing is an optimisation, never a condition for progress.
-                            if (st_chunk >= args.pace_window) {
+                            if (st_paced && st_chunk >= args.pace_window) {
                                 const volatile int *prev = args.arrivals + (st_chunk - args.pace_window);
-                                for (int spins = 0; *prev < (int)gridDim.x && spins < 20000; spins++) __nanosleep(100);
+                                int spins = 0;
+                                while (*prev < (int)gridDim.x && spins < kPaceSpins) {
+                                    __nanosleep(100);
+                                    spins++;
+                                }
+                                // a CTA of this grid that is a millisecond late is not running (its SM
+                                // is held by another kernel): stop waiting for good, not chunk by chunk
+                                if (spins >= kPaceSpins) st_paced = false;
                             }
                             atomicAdd(args.arrivals + st_chunk, 1);
                             st_arrived = true;

@@ -237,6 +237,28 @@ def test_large_store_static_schedule(pkg, oracle, flat_kernel, shape):
         pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05")
 
 
+def test_static_schedule_with_searches_in_flight(pkg, oracle):
+    """Three screened searches of a large store enqueued at once on their own streams: their CTAs
+    compete for the SMs, so the CTAs of one launch are not all running together and its pacing has
+    to give way.  Same answers as the synchronous search."""
+    xb, xq = _data(19, 200_000, 1024, 32)
+    assert pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05-screened") == 0
+    try:
+        idx = pkg.CudaIndexFlat(32, pkg.METRIC_L2)
+        idx.add(xb)
+        D, I = idx.search(xq, 30)
+        tokens = [idx.search_async(xq, 30) for _ in range(3)]
+        for t in tokens:
+            Da, Ia = t.wait()
+            np.testing.assert_array_equal(Ia, I)
+            np.testing.assert_array_equal(Da, D)
+        Dref, Iref = oracle.flat_search(xb, xq, 30, pkg.METRIC_L2)
+        assert_topk_matches(oracle, xb, xq, pkg.METRIC_L2, D, I, Dref, Iref, "static schedule, searches in flight")
+        idx.close()
+    finally:
+        pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05")
+
+
 def test_search_async_tokens(pkg, oracle, kernel):
     """searchAsync (faiss-metal/src/MetalIndexFlat.mm:371-443): several tokens in flight on one
     index, waited on out of order, give what search() gives; n == 0 and an empty index answer at
