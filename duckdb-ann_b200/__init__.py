@@ -73,6 +73,10 @@ SIGNATURES = {
     "ann_cuda_search_token_wait": (C.c_int, [_P]),
     "ann_cuda_search_token_free": (None, [_P]),
     "ann_cuda_flat_search_small_static": (C.c_int, [_P, _I64, _P, _I64, _P, _P, _I64, _P]),
+    "ann_cuda_flat_search_small_static_status": (C.c_int, [C.c_int, _P]),
+    "ann_cuda_index_search_status": (C.c_int, [_P, _P]),
+    "ann_cuda_set_wait_limit_ms": (None, [C.c_int]),
+    "ann_cuda_test_withhold_loads": (None, [C.c_int]),
     "ann_cuda_index_reset": (C.c_int, [_P]),
     "ann_cuda_index_reconstruct": (C.c_int, [_P, _I64, _P]),
     "ann_cuda_flat_get_rows": (C.c_int, [_P, _I64, _I64, _P]),

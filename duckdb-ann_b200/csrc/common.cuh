@@ -100,15 +100,27 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 constexpr float kInf = __builtin_huge_valf();
 
-// Screened flat search: twice the bound E' on |coarse key - exact key| for a query with
-// qn = |q - mu|^2 (L2) or |q|^2 (IP) against a store whose largest row norm squared is xm2.
-// The one-MMA dot product q_hi.x_hi is within (2^-10 (1 + 2^-11) + d 2^-23) |q||x| of the exact
-// one; an L2 key is |x - mu|^2 - 2 (q - mu).x, so it carries twice that plus the fp32 rounding of
+// Error slack of tensor-core ranking keys.  Twice the bound E' on |ranking key - exact key| for a
+// query with qn = |q - mu|^2 (L2) or |q|^2 (IP) against a store whose largest row norm squared is
+// xm2.  The dot product the tensor cores form differs from the exact one by at most rel |q||x|:
+//   screened search (q_hi.x_hi only): each operand rounded to 11 significant bits,
+//       rel = 2^-10 (1 + 2^-11) + d 2^-23;
+//   split product (q_hi.x_hi + q_hi.x_lo + q_lo.x_hi): the dropped q_lo.x_lo term is <= 2^-22, the
+//       lo operands lose up to 2^-10 of themselves when the MMA reads them as TF32 (2 x 2^-21),
+//       rel = 1.25 2^-20 + 3 d 2^-23.
+// The d 2^-23 terms bound the fp32 accumulation in tensor memory (one rounding of at most one ulp
+// of |q||x| per product added, three products per element for the split form).  An L2 key is
+// |x - mu|^2 - 2 (q - mu).x, so it carries twice the dot-product error plus the fp32 rounding of
 // the stored norm (<= (d / 32 + 6) 2^-24 of a value that is at most 4 xm2).
-__host__ __device__ inline float screen_slack(float qn, float xm2, int d, bool l2) {
-    const float rel = 9.8e-4f + (float)d * 1.2e-7f;
+// If K is the k-th smallest ranking key of a query, its exact k-th best key is <= K + E' and a row
+// can be among the exact k best only if its ranking key is <= K + 2E' = K + slack.
+__host__ __device__ inline float key_slack(float qn, float xm2, int d, bool l2, bool screened) {
+    const float rel = screened ? 9.8e-4f + (float)d * 1.2e-7f : 1.2e-6f + (float)d * 3.6e-7f;
     const float e = rel * sqrtf(qn * xm2);
     return 2.f * (l2 ? 2.f * e + ((float)d * (1.f / 32.f) + 6.f) * 6e-8f * 4.f * xm2 : e);
+}
+__host__ __device__ inline float screen_slack(float qn, float xm2, int d, bool l2) {
+    return key_slack(qn, xm2, d, l2, true);
 }
 
 }  // namespace anncuda

@@ -153,15 +153,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 
 // Bounded wait.  Returns false when another role has already given up or when
-// this wait itself runs out (~2 s); the caller then leaves its loop.
+// this wait itself runs out (limit_ns, 2 s unless the host lowered it); the caller then
+// leaves its loop.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
-                                            int code) {
+                                            uint64_t limit_ns, int code) {
     const uint64_t t0 = global_timer_ns();
     for (;;) {
         for (int i = 0; i < 256; i++)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > 2000000000ull) {
+        if (global_timer_ns() - t0 > limit_ns) {
             *abort_flag = 1;
             atomicCAS(status, 0, code);
             return false;
@@ -169,9 +170,9 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
     }
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
-                                          int code) {
+                                          uint64_t limit_ns, int code) {
     if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, status, code);
+    return mbar_wait_slow(bar, parity, abort_flag, status, limit_ns, code);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int32_t c0, int32_t c1,
@@ -324,9 +325,24 @@ struct KernelArgs {
     int32_t *part_idx;
     uint32_t *qtau;  // per query: smallest k-th-best key any chunk has published (ordered-uint form)
     int *status;
-    unsigned long long *stats;  // measurement only (may be null): see kStat* below
-    int debug;  // measurement only: bit 0 = epilogue skips selection, bit 1 = MMA issuer skips the MMAs
+    uint64_t wait_ns;     // limit of every bounded wait
+    int withhold_after;   // test hook (-1 = off): see flat_test_withhold_after in kernels.h
+    const int *gate;      // may be null: run only if *gate == kScreenOverflow (a fallback pass)
+#ifdef ANN_CUDA_MEASURE
+    unsigned long long *stats;  // see kStat* below
+    int debug;  // bit 0 = epilogue skips selection, bit 1 = MMA issuer skips the MMAs, bit 2 = no appends, bit 3 = consume only
+#endif
 };
+
+// Counters and stage switches for profiling exist only in builds with -DANN_CUDA_MEASURE; in the
+// product build both read as constants and the code behind them is dropped.
+#ifdef ANN_CUDA_MEASURE
+__device__ __forceinline__ unsigned long long *kstats(const KernelArgs &a) { return a.stats; }
+__device__ __forceinline__ int kdebug(const KernelArgs &a) { return a.debug; }
+#else
+__device__ __forceinline__ unsigned long long *kstats(const KernelArgs &) { return nullptr; }
+__device__ __forceinline__ int kdebug(const KernelArgs &) { return 0; }
+#endif
 
 // How the epilogue keeps the k best keys of a row:
 //   kSelSmem    k <= 16: the list sits in shared memory, one column per thread;
@@ -487,6 +503,8 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
     constexpr bool SMALLK = (MODE == kSelSmem);
     constexpr bool APPEND = (MODE == kSelAppend);
     extern __shared__ uint8_t smem_raw[];
+    // a fallback pass whose predecessor found nothing to repair: leave before anything is set up
+    if (args.gate && *args.gate != kScreenOverflow) return;
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
     float *qkey = reinterpret_cast<float *>(smem + SmemLayout::queue_key);
@@ -542,6 +560,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
         // ---------------------------------------------------------------- scheduler + TMA producer
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
+            int issued = 0;   // K blocks loaded so far (test hook only)
             uint32_t wi = 0;  // work items announced
             int cur = -1, slot = -1, fresh = 0;
             // Adopts query tile t if it still has chunks and a free list slot.
@@ -660,7 +679,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 }
                 {
                     const uint32_t w = wi % kWorkRing;
-                    if (!mbar_wait(bar_wempty + 8 * w, ((wi / kWorkRing) & 1) ^ 1, abort_flag, args.status, 5)) goto done;
+                    if (!mbar_wait(bar_wempty + 8 * w, ((wi / kWorkRing) & 1) ^ 1, abort_flag, args.status, args.wait_ns, 5)) goto done;
                     ring[w].qt = cur;
                     ring[w].row_begin = (int)r_begin;
                     ring[w].row_end = (int)r_end;
@@ -673,7 +692,10 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 }
                 for (int64_t trow = r_begin; trow < r_end; trow += BN) {
                     for (int kb = 0; kb < args.kblocks; kb++) {
-                        if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, args.status, 1)) goto done;
+                        if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, args.status, args.wait_ns, 1)) goto done;
+                        // test hook: from this K block on nothing is loaded, so the MMA issuer's
+                        // wait for the stage runs out and the give-up path is exercised
+                        if (args.withhold_after >= 0 && issued++ >= args.withhold_after) goto done;
                         const uint32_t full = bar_full + 8 * stage;
                         if (args.screen) {  // hi planes only, into plane set stage & 1 of stage >> 1
                             const uint32_t base = smem_base + (stage >> 1) * kStageBytes;
@@ -697,7 +719,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             }
             {  // end marker
                 const uint32_t w = wi % kWorkRing;
-                if (!mbar_wait(bar_wempty + 8 * w, ((wi / kWorkRing) & 1) ^ 1, abort_flag, args.status, 5)) goto done;
+                if (!mbar_wait(bar_wempty + 8 * w, ((wi / kWorkRing) & 1) ^ 1, abort_flag, args.status, args.wait_ns, 5)) goto done;
                 ring[w].qt = -1;
                 __threadfence_block();
                 mbar_arrive(bar_wfull + 8 * w);
@@ -710,22 +732,22 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             uint32_t it = 0;  // tiles issued by this CTA
             for (uint32_t wi = 0;; wi++) {
                 const uint32_t w = wi % kWorkRing;
-                if (!mbar_wait(bar_wfull + 8 * w, (wi / kWorkRing) & 1, abort_flag, args.status, 6)) goto done;
+                if (!mbar_wait(bar_wfull + 8 * w, (wi / kWorkRing) & 1, abort_flag, args.status, args.wait_ns, 6)) goto done;
                 const int qt = ring[w].qt;
                 const int64_t r_begin = ring[w].row_begin, r_end = ring[w].row_end;
                 mbar_arrive(bar_wempty + 8 * w);
                 if (qt < 0) break;
                 for (int64_t trow = r_begin; trow < r_end; trow += BN, it++) {
                     const uint32_t buf = it & 1;
-                    long long t0 = args.stats ? clock64() : 0;
-                    if (!mbar_wait(bar_tempty + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag, args.status, 2)) goto done;
-                    if (args.stats) atomicAdd(args.stats + kStatMmaWaitTmem, (unsigned long long)(clock64() - t0));
+                    long long t0 = kstats(args) ? clock64() : 0;
+                    if (!mbar_wait(bar_tempty + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag, args.status, args.wait_ns, 2)) goto done;
+                    if (kstats(args)) atomicAdd(kstats(args) + kStatMmaWaitTmem, (unsigned long long)(clock64() - t0));
                     tmem_fence_after();
                     const uint32_t tmem_d = tmem_base + buf * BN;
                     for (int kb = 0; kb < args.kblocks; kb++) {
-                        t0 = args.stats ? clock64() : 0;
-                        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, args.status, 3)) goto done;
-                        if (args.stats) atomicAdd(args.stats + kStatMmaWaitSmem, (unsigned long long)(clock64() - t0));
+                        t0 = kstats(args) ? clock64() : 0;
+                        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, args.status, args.wait_ns, 3)) goto done;
+                        if (kstats(args)) atomicAdd(kstats(args) + kStatMmaWaitSmem, (unsigned long long)(clock64() - t0));
                         tmem_fence_after();
                         if (args.screen) {
                             // One MMA per K step: the loop of this single thread is what paces the
@@ -734,7 +756,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             const uint32_t base = smem_base + (stage >> 1) * kStageBytes;
                             const uint64_t a0 = make_smem_desc(base + (stage & 1) * kABytes);
                             const uint64_t b0 = make_smem_desc(base + 2 * kABytes + (stage & 1) * kBBytes);
-                            if (!(args.debug & 2)) {
+                            if (!(kdebug(args) & 2)) {
                                 mma_tf32(tmem_d, a0, b0, kb != 0);
 #pragma unroll
                                 for (int ks = 1; ks < BK / 8; ks++) mma_tf32(tmem_d, a0 + 2 * ks, b0 + 2 * ks, 1);
@@ -747,7 +769,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                                 const uint64_t a_lo = make_smem_desc(base + kABytes + ks * 32);
                                 const uint64_t b_hi = make_smem_desc(base + 2 * kABytes + ks * 32);
                                 const uint64_t b_lo = make_smem_desc(base + 2 * kABytes + kBBytes + ks * 32);
-                                if (args.debug & 2) continue;
+                                if (kdebug(args) & 2) continue;
                                 mma_tf32(tmem_d, a_hi, b_lo, (kb | ks) != 0);
                                 mma_tf32(tmem_d, a_lo, b_hi, 1);
                                 mma_tf32(tmem_d, a_hi, b_hi, 1);
@@ -812,7 +834,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
         };
         for (uint32_t wi = 0;; wi++) {
             const uint32_t w = wi % kWorkRing;
-            if (!mbar_wait(bar_wfull + 8 * w, (wi / kWorkRing) & 1, abort_flag, args.status, 7)) goto done;
+            if (!mbar_wait(bar_wfull + 8 * w, (wi / kWorkRing) & 1, abort_flag, args.status, args.wait_ns, 7)) goto done;
             const int qt = ring[w].qt, slot = ring[w].slot, fresh = ring[w].fresh;
             const int64_t r_begin = ring[w].row_begin, r_end = ring[w].row_end;
             __syncwarp();
@@ -875,13 +897,13 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     }
                     __syncwarp();
                 }
-                long long t0 = (args.stats && lane == 0) ? clock64() : 0;
-                if (!mbar_wait(bar_tfull + 8 * buf, (it >> 1) & 1, abort_flag, args.status, 4)) goto done;
+                long long t0 = (kstats(args) && lane == 0) ? clock64() : 0;
+                if (!mbar_wait(bar_tfull + 8 * buf, (it >> 1) & 1, abort_flag, args.status, args.wait_ns, 4)) goto done;
                 long long t1 = 0;
-                if (args.stats && lane == 0) {
+                if (kstats(args) && lane == 0) {
                     t1 = clock64();
-                    atomicAdd(args.stats + kStatEpiWaitCycles, (unsigned long long)(t1 - t0));
-                    atomicAdd(args.stats + kStatTiles, 1ull);
+                    atomicAdd(kstats(args) + kStatEpiWaitCycles, (unsigned long long)(t1 - t0));
+                    atomicAdd(kstats(args) + kStatTiles, 1ull);
                 }
                 tmem_fence_after();
                 if (row_valid) {
@@ -921,7 +943,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     const int nvalid = ncols - g * 32;
                     if (nvalid <= 0) return;
                     const uint32_t valid = nvalid >= 32 ? 0xffffffffu : ((1u << nvalid) - 1u);
-                    if (args.debug & 8) {  // measurement only: consume the registers, no selection
+                    if (kdebug(args) & 8) {  // measurement only: consume the registers, no selection
                         uint32_t x = 0;
 #pragma unroll
                         for (int j = 0; j < 32; j++) x ^= raw[j];
@@ -934,16 +956,16 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     if (APPEND) {
                         const unsigned need = __ballot_sync(kFullMask, cnt + __popc(mask) > kBuf);
                         if (need) {
-                            const long long c0 = args.stats ? clock64() : 0;
+                            const long long c0 = kstats(args) ? clock64() : 0;
                             compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word, koff, k_rank, slack);
-                            if (args.stats && lane == 0) {
-                                atomicAdd(args.stats + kStatCompactCycles, (unsigned long long)(clock64() - c0));
-                                atomicAdd(args.stats + kStatCompactRows, (unsigned long long)__popc(need));
+                            if (kstats(args) && lane == 0) {
+                                atomicAdd(kstats(args) + kStatCompactCycles, (unsigned long long)(clock64() - c0));
+                                atomicAdd(kstats(args) + kStatCompactRows, (unsigned long long)__popc(need));
                             }
                             mask = beat_mask(raw, g, valid);
                         }
-                        if (args.debug & 4) mask = 0;
-                        if (args.stats && mask) atomicAdd(args.stats + kStatAppends, (unsigned long long)__popc(mask));
+                        if (kdebug(args) & 4) mask = 0;
+                        if (kstats(args) && mask) atomicAdd(kstats(args) + kStatAppends, (unsigned long long)__popc(mask));
                         // predicated appends: no branch per column, nothing stored where the bit is clear
                         float *bk = unit_key + (size_t)row * kBuf;
                         int32_t *bi = unit_idx + (size_t)row * kBuf;
@@ -996,7 +1018,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         }
                     }
                 };
-                if (!(args.debug & 1)) {
+                if (!(kdebug(args) & 1)) {
                     // Two register buffers: the read of the next 32 columns is in flight while
                     // the current 32 are scanned.
                     uint32_t ra[32], rb[32];
@@ -1014,7 +1036,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 tmem_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
-                if (args.stats && lane == 0) atomicAdd(args.stats + kStatEpiTileCycles, (unsigned long long)(clock64() - t1));
+                if (kstats(args) && lane == 0) atomicAdd(kstats(args) + kStatEpiTileCycles, (unsigned long long)(clock64() - t1));
                 if (SMALLK && list_max < published) {
                     published = list_max;
                     atomicMin(qtau_word, float_to_ordered(__fadd_ru(list_max, koff)));
@@ -1182,15 +1204,16 @@ FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms) {
 int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
                    int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
-                   const GroupedWork *grouped, const ScreenInput *screen) {
+                   const GroupedWork *grouped, const ScreenInput *screen, const int *gate) {
     (void)device;
     if (n <= 0 || nq <= 0) return 0;
-    if (k <= 0 || k > kMaxK) return set_error("k must be in [1, %d]", kMaxK);
+    static_assert(kMaxListK <= 66 * 32, "the widest replace-max list covers every list length");
+    if (k <= 0 || k > kMaxListK) return set_error("k must be in [1, %d]", kMaxListK);
 #ifndef ANN_TC_VARIANT_BK32
     // the screened search runs in the build of this file with K blocks of 32 floats
     if (screen && !grouped && screen->k_rank >= 1 && screen->k_rank <= k && k <= kScreenMaxList && dp % 32 == 0)
         return launch_flat_tc_bk32(plan, xhi, xlo, xnorm, n, qhi, qlo, nq, dp, k, metric, part_key, part_idx, qtau, sched,
-                                   status, device, stream, grouped, screen);
+                                   status, device, stream, grouped, screen, gate);
 #endif
     if (dp % BK != 0) return set_error("padded dimension must be a multiple of %d", BK);
     if (n > 0x7fffffffll - BN) return set_error("a flat shard holds at most 2^31 rows");
@@ -1234,22 +1257,30 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     a.q_norm2 = use_screen ? screen->q_norm2 : nullptr;
     a.x_max_norm2 = use_screen ? screen->x_max_norm2 : nullptr;
     a.d = use_screen ? screen->d : dp;
+    a.wait_ns = flat_wait_limit_ns();
+    a.withhold_after = flat_test_withhold_after();
+    a.gate = gate;
+#ifdef ANN_CUDA_MEASURE
     {
-        const char *e = getenv("ANN_CUDA_TC_DEBUG");
-        a.debug = e ? atoi(e) : 0;
+        static const int debug_bits = [] { const char *e = getenv("ANN_CUDA_TC_DEBUG"); return e ? atoi(e) : 0; }();
+        a.debug = debug_bits;
     }
     a.stats = nullptr;
     static unsigned long long *stats_dev = nullptr;
-    if (getenv("ANN_CUDA_TC_STATS")) {  // measurement only: synchronises and prints
+    static const bool want_stats = getenv("ANN_CUDA_TC_STATS") != nullptr;
+    if (want_stats) {  // synchronises and prints
         if (!stats_dev) ANN_CUDA_TRY(cudaMalloc(&stats_dev, 8 * sizeof(unsigned long long)));
         ANN_CUDA_TRY(cudaMemsetAsync(stats_dev, 0, 8 * sizeof(unsigned long long), stream));
         a.stats = stats_dev;
     }
+#endif
     int rc;
     if (k <= kQueueDepth) rc = launch_variant<1, kSelSmem>(plan, maps, a, stream);
     else if (k <= kAppendMaxK || use_screen) rc = launch_variant<1, kSelAppend>(plan, maps, a, stream);
-    else if (k <= 512) rc = launch_variant<16, kSelReplace>(plan, maps, a, stream);
-    else rc = launch_variant<64, kSelReplace>(plan, maps, a, stream);
+    else if (k <= 17 * 32) rc = launch_variant<17, kSelReplace>(plan, maps, a, stream);
+    else if (k <= 33 * 32) rc = launch_variant<33, kSelReplace>(plan, maps, a, stream);
+    else rc = launch_variant<66, kSelReplace>(plan, maps, a, stream);
+#ifdef ANN_CUDA_MEASURE
     if (rc == 0 && a.stats) {
         unsigned long long h[8];
         ANN_CUDA_TRY(cudaStreamSynchronize(stream));
@@ -1260,6 +1291,7 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
                 plan.grid, k, h[kStatTiles], h[kStatCompactRows], h[kStatCompactCycles], h[kStatAppends],
                 h[kStatEpiWaitCycles], h[kStatEpiTileCycles], h[kStatMmaWaitTmem], h[kStatMmaWaitSmem]);
     }
+#endif
     return rc;
 }
 

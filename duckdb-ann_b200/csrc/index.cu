@@ -34,7 +34,6 @@ enum class FlatKernel { TC, SIMT };
 std::atomic<int> g_flat_kernel{-1};  // -1 = not chosen yet
 // one-MMA screening of the flat search: -1 = by store size, 0 = never, 1 = always (tests);
 // ANN_CUDA_FLAT_SCREEN sets the initial value
-thread_local bool t_no_screen = false;  // set while a host entry point repeats a block unscreened
 std::atomic<uint64_t> g_screen_fallbacks{0};
 std::atomic<int> g_flat_screen{[] {
     const char *e = getenv("ANN_CUDA_FLAT_SCREEN");
@@ -126,12 +125,21 @@ struct SplitStore {
     }
 };
 
+constexpr int kStatusWords = 8;
+constexpr int kStatusWait = 0, kStatusTier0 = 1, kStatusFallbacks = 4;
+
 struct Workspace {
     cudaStream_t own_stream = nullptr;
     cudaStream_t bound = nullptr;  // stream whose work may still use these buffers
     GrowBuf x, qhi, qlo, qn, part_key, part_idx, sel_key, sel_idx, status, out_d, out_i;
     GrowBuf item_q, item_rb, item_re, item_slot, scratch, probes_key, probes, qtau, sched, gq, items, qconst, part_cnt;
+    // Status words (device: `status`, pinned host copy: `status_host`), kStatusWords ints:
+    //   [0]      first give-up code of a bounded wait inside a kernel; sticky for one API call
+    //   [1 + t]  tier t of the flat search (0 screened, 1 split product, 2 exact) found more rows
+    //            inside its error band than it kept candidates for: kScreenOverflow; per query block
+    //   [4]      how often a tier flagged such an overflow during the API call
     int *status_host = nullptr;  // pinned
+    int fallbacks_seen = 0;      // part of status_host[4] already added to the process-wide counter
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;  // bracket the flat kernel when timing is on
     bool timed = false;
     void release() {
@@ -192,14 +200,14 @@ struct ann_cuda_index {
         }
         Workspace *w = new Workspace();
         if (cudaStreamCreateWithFlags(&w->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
-            cudaMallocHost(&w->status_host, sizeof(int)) != cudaSuccess) {
+            cudaMallocHost(&w->status_host, kStatusWords * sizeof(int)) != cudaSuccess) {
             cudaGetLastError();
             w->release();
             delete w;
             set_error("could not create a search workspace");
             return nullptr;
         }
-        *w->status_host = 0;
+        memset(w->status_host, 0, kStatusWords * sizeof(int));
         w->bound = internal ? w->own_stream : user_stream;
         return w;
     }
@@ -308,35 +316,66 @@ __global__ void find_id_kernel(const int64_t *__restrict__ ids, int64_t n, int64
     if (t < n && ids[t] == key) atomicMin(found, (long long)t);
 }
 
+// ---- status words -----------------------------------------------------------------------------------
+int ws_status_ready(Workspace &ws) {
+    if (ws.status.ensure(kStatusWords * sizeof(int))) return -1;
+    return 0;
+}
+// All status words to zero, in stream order.
+int ws_clear_status(Workspace &ws, cudaStream_t stream) {
+    if (ws_status_ready(ws)) return -1;
+    ANN_CUDA_TRY(cudaMemsetAsync(ws.status.ptr, 0, kStatusWords * sizeof(int), stream));
+    return 0;
+}
+int ws_publish_status(Workspace &ws, cudaStream_t stream) {
+    ANN_CUDA_TRY(cudaMemcpyAsync(ws.status_host, ws.status.ptr, kStatusWords * sizeof(int), cudaMemcpyDeviceToHost, stream));
+    return 0;
+}
+// Adds the overflows the device counted since the last look to the process-wide counter.  Only
+// meaningful after the stream has been synchronised.
+void ws_absorb_fallbacks(Workspace &ws) {
+    const int seen = ws.status_host[kStatusFallbacks];
+    if (seen > ws.fallbacks_seen) g_screen_fallbacks.fetch_add((uint64_t)(seen - ws.fallbacks_seen), std::memory_order_relaxed);
+    ws.fallbacks_seen = seen;
+}
+
 // ---- top-k over a split store (flat database, or IVF centroids) ---------------------------------
+struct TopkOpts {
+    int k_rank = 0;      // > 0: screened search - the kernel forms one-MMA keys and keeps the k candidates
+                         // around rank k_rank that its error slack cannot rule out (see ScreenInput)
+    int check_rank = 0;  // > 0: band check - is the last of the k candidates beyond the slack above the
+                         // check_rank-th?  If not, status word kStatusTier0 + tier becomes kScreenOverflow
+    int tier = 0;
+    bool exact = false;  // exact-fp32 scan instead of the tensor cores
+    const int *gate = nullptr;  // device word: run only if it holds kScreenOverflow (a fallback pass)
+};
 // x_dev: nq x d queries on the device.  Leaves (nq x k) keys and int32 rows, best
-// first, in ws.sel_key / ws.sel_idx.
-// k_rank > 0 (flat_tc kernel only): screened search - k = k_rank + spare candidates are selected by
-// one-MMA keys with an error slack and the caller re-ranks them exactly (see ScreenInput).
+// first, in ws.sel_key / ws.sel_idx.  The status words must have been cleared by the caller.
 int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &ws, const float *x_dev, int64_t nq,
-                     int k, cudaStream_t stream, int k_rank = 0) {
+                     int k, cudaStream_t stream, const TopkOpts &o = TopkOpts()) {
     const int dp = st.dp, d = ix.d;
     if (ws.qhi.ensure((size_t)nq * dp * 4) || ws.qlo.ensure((size_t)nq * dp * 4) || ws.qn.ensure((size_t)nq * 4) ||
-        ws.sel_key.ensure((size_t)nq * k * 4) || ws.sel_idx.ensure((size_t)nq * k * 4) || ws.status.ensure(4))
+        ws.sel_key.ensure((size_t)nq * k * 4) || ws.sel_idx.ensure((size_t)nq * k * 4) || ws_status_ready(ws))
         return -1;
-    if (flat_kernel_choice() == FlatKernel::TC) {
+    int *status = ws.status.as<int>();
+    if (!o.exact && flat_kernel_choice() == FlatKernel::TC) {
+        // the split of the queries is the same in every tier: rewriting it in a fallback pass is harmless
         if (launch_split_rows(x_dev, nq, d, dp, ws.qhi.as<float>(), ws.qlo.as<float>(), ws.qn.as<float>(), stream,
                               st.center(), true))
             return -1;
-        const FlatPlan plan = k_rank > 0 ? make_flat_plan_screened(nq, st.n, k, sm_count(ix.device))
-                                         : make_flat_plan(nq, st.n, k, sm_count(ix.device));
-        const ScreenInput screen{k_rank, ws.qn.as<float>(), st.max_norm2, d};
+        const FlatPlan plan = o.k_rank > 0 ? make_flat_plan_screened(nq, st.n, k, sm_count(ix.device))
+                                           : make_flat_plan(nq, st.n, k, sm_count(ix.device));
+        const ScreenInput screen{o.k_rank, ws.qn.as<float>(), st.max_norm2, d};
         const size_t qtau_bytes = (size_t)plan.nq_tiles * 128 * 4, sched_bytes = plan.sched_ints * 4;
         if (ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4) ||
             ws.qtau.ensure(qtau_bytes) || ws.sched.ensure(sched_bytes))
             return -1;
-        ANN_CUDA_TRY(cudaMemsetAsync(ws.status.ptr, 0, 4, stream));
         ANN_CUDA_TRY(cudaMemsetAsync(ws.qtau.ptr, 0xFF, qtau_bytes, stream));  // "no threshold yet"
         ANN_CUDA_TRY(cudaMemsetAsync(ws.sched.ptr, 0, sched_bytes, stream));
         // every list empty: index -1 in the k slots the merge reads of each row
         ANN_CUDA_TRY(cudaMemset2DAsync(ws.part_idx.ptr, (size_t)plan.list_stride * 4, 0xFF, (size_t)k * 4,
                                        plan.part_entries / plan.list_stride, stream));
-        const bool timing = g_time_kernels.load(std::memory_order_relaxed) != 0;
+        const bool timing = !o.gate && g_time_kernels.load(std::memory_order_relaxed) != 0;
         if (timing) {
             if (!ws.ev0) {
                 ANN_CUDA_TRY(cudaEventCreate(&ws.ev0));
@@ -346,8 +385,8 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         }
         if (launch_flat_tc(plan, st.hi, st.lo, st.norms, st.n, ws.qhi.as<float>(), ws.qlo.as<float>(), nq, dp, k,
                            ix.metric, ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.qtau.as<uint32_t>(),
-                           ws.sched.as<int>(), ws.status.as<int>(),
-                           ix.device, stream, nullptr, k_rank > 0 ? &screen : nullptr))
+                           ws.sched.as<int>(), status + kStatusWait, ix.device, stream, nullptr,
+                           o.k_rank > 0 ? &screen : nullptr, o.gate))
             return -1;
         if (timing) {
             ANN_CUDA_TRY(cudaEventRecord(ws.ev1, stream));
@@ -356,42 +395,35 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         }
         if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 0, ws.sched.as<int>() + plan.nq_tiles,
                                nullptr, plan.lists_per_qt, nq, k, plan.list_stride, ws.sel_key.as<float>(),
-                               ws.sel_idx.as<int32_t>(), ix.device, stream, plan.lists_sorted))
+                               ws.sel_idx.as<int32_t>(), ix.device, stream, plan.lists_sorted, nullptr, o.gate))
             return -1;
-        if (k_rank > 0 && launch_screen_check(ws.sel_key.as<float>(), nq, k, k_rank, ws.qn.as<float>(), st.max_norm2, d,
-                                              ix.metric, ws.status.as<int>(), stream))
+        // (a list that holds every row of the store has left nothing out)
+        if (o.check_rank > 0 && k < st.n &&
+            launch_screen_check(ws.sel_key.as<float>(), nq, k, o.check_rank, ws.qn.as<float>(), st.max_norm2, d, ix.metric,
+                                o.k_rank > 0, status + kStatusTier0 + o.tier, status + kStatusFallbacks, stream, o.gate))
             return -1;
-        ANN_CUDA_TRY(cudaMemcpyAsync(ws.status_host, ws.status.ptr, 4, cudaMemcpyDeviceToHost, stream));
-        return 0;
+        return ws_publish_status(ws, stream);
     }
-    // exact-fp32 cross-check kernel: items = (query, database chunk)
+    // exact-fp32 scan: items = (query, database chunk), laid out on the device
     int chunks = (int)std::max<int64_t>(1, std::min<int64_t>({(int64_t)kMergeCandidates / k, (st.n + 255) / 256,
                                                              (int64_t)sm_count(ix.device) * 32 / std::max<int64_t>(nq, 1) + 1}));
     const int64_t per = (st.n + chunks - 1) / chunks;
     chunks = (int)((st.n + per - 1) / per);
     const int64_t n_items = nq * chunks;
-    std::vector<int32_t> iq((size_t)n_items);
-    std::vector<int64_t> rb((size_t)n_items), re((size_t)n_items);
-    for (int64_t q = 0; q < nq; q++)
-        for (int c = 0; c < chunks; c++) {
-            const int64_t i = q * chunks + c;
-            iq[i] = (int32_t)q;
-            rb[i] = c * per;
-            re[i] = std::min<int64_t>(st.n, (c + 1) * per);
-        }
     if (ws.item_q.ensure(n_items * 4) || ws.item_rb.ensure(n_items * 8) || ws.item_re.ensure(n_items * 8) ||
         ws.part_key.ensure((size_t)n_items * k * 4) || ws.part_idx.ensure((size_t)n_items * k * 4))
         return -1;
-    ANN_CUDA_TRY(cudaMemcpyAsync(ws.item_q.ptr, iq.data(), n_items * 4, cudaMemcpyHostToDevice, stream));
-    ANN_CUDA_TRY(cudaMemcpyAsync(ws.item_rb.ptr, rb.data(), n_items * 8, cudaMemcpyHostToDevice, stream));
-    ANN_CUDA_TRY(cudaMemcpyAsync(ws.item_re.ptr, re.data(), n_items * 8, cudaMemcpyHostToDevice, stream));
-    ANN_CUDA_TRY(cudaStreamSynchronize(stream));  // the host vectors go out of scope
+    if (launch_fill_chunk_items(ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(), ws.item_re.as<int64_t>(), nq, chunks, per,
+                                st.n, stream))
+        return -1;
     if (launch_scan_items(st.hi, st.lo, dp, d, x_dev, d, ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(),
                           ws.item_re.as<int64_t>(), n_items, k, ix.metric, ws.part_key.as<float>(),
-                          ws.part_idx.as<int32_t>(), nullptr, ix.device, stream))
+                          ws.part_idx.as<int32_t>(), nullptr, ix.device, stream, o.gate))
         return -1;
-    return launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, nullptr, nullptr, chunks, nq, k, k,
-                              ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream);
+    if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, nullptr, nullptr, chunks, nq, k, k,
+                           ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream, false, nullptr, o.gate))
+        return -1;
+    return ws_publish_status(ws, stream);
 }
 
 // Allocates the four row arrays of an IVF store for `cap` rows (all or nothing).
@@ -441,7 +473,7 @@ int ivf_finalize_lists(const ann_cuda_index &cix) {
             return set_error("out of device memory regrouping the inverted lists");
         }
         ANN_CUDA_TRY(cudaMemcpy(dperm, perm.data(), (size_t)n * 8, cudaMemcpyHostToDevice));
-        gather_rows_kernel<<<(unsigned)std::min<int64_t>((n + 7) / 8, 148 * 32), 256>>>(
+        gather_rows_kernel<<<(unsigned)std::min<int64_t>((n + 7) / 8, (int64_t)sm_count(ix.device) * 32), 256>>>(
             ix.vhi, ix.vlo, ix.vnorm, ix.ids, dperm, n, ix.dp, nh, nl, nn, ni);
         count_launch();
         ANN_CUDA_TRY(cudaGetLastError());
@@ -553,6 +585,7 @@ int ivf_update_coarse_policy(ann_cuda_index &ix) {
         for (int64_t q0 = 0; q0 < nl && rc == 0; q0 += kQueryBlock) {
             const int64_t nb = std::min(kQueryBlock, nl - q0);
             if (ws.out_d.ensure((size_t)nb * 2 * 4) || ws.out_i.ensure((size_t)nb * 2 * 8)) rc = -1;
+            if (rc == 0) rc = ws_clear_status(ws, s);
             if (rc == 0) rc = split_store_topk(ix, ix.store, ws, rows + q0 * ix.d, nb, 2, s);
             if (rc == 0)
                 rc = launch_refine_finalize(ix.store.hi, ix.store.lo, ix.dp, ix.d, rows + q0 * ix.d, ix.d,
@@ -592,11 +625,12 @@ int ivf_assign_device(const ann_cuda_index &ix, const float *x_dev, int64_t n, s
     cudaStream_t s = ws.own_stream;
     for (int64_t q0 = 0; q0 < n; q0 += kQueryBlock) {
         const int64_t nb = std::min(kQueryBlock, n - q0);
-        if (ws.probes.ensure((size_t)nb * 4)) return -1;
+        if (ws.probes.ensure((size_t)nb * 4) || ws_clear_status(ws, s)) return -1;
         if (coarse_probes(ix, ws, x_dev + q0 * ix.d, nb, 1, ws.probes.as<int32_t>(), s, exact)) return -1;
         ANN_CUDA_TRY(cudaMemcpyAsync(assign.data() + q0, ws.probes.ptr, (size_t)nb * 4, cudaMemcpyDeviceToHost, s));
         ANN_CUDA_TRY(cudaStreamSynchronize(s));
-        if (*ws.status_host) return set_error("flat kernel gave up on a wait (code %d)", *ws.status_host);
+        if (ws.status_host[kStatusWait])
+            return set_error("flat kernel gave up on a wait (code %d)", ws.status_host[kStatusWait]);
     }
     return 0;
 }
@@ -615,12 +649,8 @@ int ivf_append(ann_cuda_index &ix, const float *x_dev, int64_t n, const int32_t 
     if (kept == 0) return 0;
     if (ivf_grow_rows(ix, kept)) return -1;
     kept_ids.reserve((size_t)kept);
-    for (int64_t i = 0; i < n; i++) {
-        if (dst[i] < 0) continue;
-        kept_ids.push_back(labels[i]);
-        if (!ix.row_list.empty() && lists[i] < ix.row_list.back()) ix.rows_sorted = false;
-        ix.row_list.push_back(lists[i]);
-    }
+    for (int64_t i = 0; i < n; i++)
+        if (dst[i] >= 0) kept_ids.push_back(labels[i]);
     int64_t *ddst = nullptr;
     ANN_CUDA_TRY(cudaMalloc(&ddst, (size_t)n * 8));
     cudaError_t e = cudaMemcpy(ddst, dst.data(), (size_t)n * 8, cudaMemcpyHostToDevice);
@@ -631,6 +661,13 @@ int ivf_append(ann_cuda_index &ix, const float *x_dev, int64_t n, const int32_t 
     cudaFree(ddst);
     if (e != cudaSuccess) return set_error("appending rows failed: %s", cudaGetErrorString(e));
     if (rc) return -1;
+    // the host-side list of every stored row grows only now that the rows are in place: a failed
+    // append leaves row_list as long as ix.rows
+    for (int64_t i = 0; i < n; i++) {
+        if (dst[i] < 0) continue;
+        if (!ix.row_list.empty() && lists[i] < ix.row_list.back()) ix.rows_sorted = false;
+        ix.row_list.push_back(lists[i]);
+    }
     ix.rows += kept;
     ix.csr_dirty = true;
     return 0;
@@ -641,41 +678,80 @@ int ensure_device(const ann_cuda_index *ix, DeviceGuard &g) {
     return 0;
 }
 
+// ---- flat search: tiers ---------------------------------------------------------------------------
+// A flat search runs in up to three tiers, each exact within its own proof:
+//   0  screened       one-MMA keys, kScreenMaxList candidates kept under the one-MMA error slack;
+//   1  split product  three-MMA keys, k + kSplitSpare candidates (16 for k <= 12);
+//   2  exact          direct-form fp32 scan (scan_items_kernel), no tensor cores.
+// Tiers 0 and 1 end with the band check of key_slack: if the last candidate of some query is still
+// within the slack above the k-th, rows that belong among the exact k best may be missing and the
+// tier's overflow word is set; the block is then searched again one tier up.  All tiers re-rank
+// their candidates by the exact fp32 distance, so the answer never depends on the tier.
+enum { kTierScreen = 0, kTierSplit = 1, kTierExact = 2 };
+
+int flat_first_tier(const ann_cuda_index &ix, int k_sel) {
+    if (flat_kernel_choice() != FlatKernel::TC) return kTierExact;
+    // (ANN_CUDA_FLAT_SCREEN=0 turns screening off, =1 applies it to stores of any size)
+    const int screen_env = g_flat_screen.load(std::memory_order_relaxed);
+    if (k_sel <= kScreenMaxK && ix.store.max_norm2 && std::min<int64_t>(kScreenMaxList, ix.store.n) > k_sel &&
+        (screen_env == 1 || (screen_env != 0 && ix.store.n >= kScreenMinRows)))
+        return kTierScreen;
+    return kTierSplit;
+}
+
+// Candidates the split-product tier selects for a search that needs k_sel results: the shared-memory
+// selection holds 16, longer lists get kSplitSpare extra.
+int split_list_len(int k_sel, int64_t n) {
+    const int64_t k_list = k_sel <= 12 ? 16 : (int64_t)k_sel + kSplitSpare;
+    return (int)std::min<int64_t>(k_list, n);
+}
+
+int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const float *x_dev, int64_t k, float *d_dev,
+                     int64_t *i_dev, int64_t label_offset, cudaStream_t stream, int tier, const int *gate) {
+    const int k_sel = (int)std::min<int64_t>(k, ix.store.n);
+    TopkOpts o;
+    o.tier = tier;
+    o.gate = gate;
+    int k_list = k_sel;
+    if (tier == kTierScreen) {
+        k_list = (int)std::min<int64_t>((int64_t)kScreenMaxList, ix.store.n);
+        o.k_rank = o.check_rank = k_sel;
+    } else if (tier == kTierSplit) {
+        k_list = split_list_len(k_sel, ix.store.n);
+        o.check_rank = k_list > k_sel ? k_sel : 0;
+    } else {
+        o.exact = true;
+    }
+    if (split_store_topk(ix, ix.store, ws, x_dev, nq, k_list, stream, o)) return -1;
+    return launch_refine_finalize(ix.store.hi, ix.store.lo, ix.dp, ix.d, x_dev, ix.d, ws.sel_idx.as<int32_t>(), nq, k_list,
+                                  (int)k, ix.metric, nullptr, label_offset, d_dev, i_dev, ix.device, stream, nullptr, nullptr,
+                                  nullptr, nullptr, gate);
+}
+
 // The whole search for one block of queries, all pointers on the device.
+// Flat: tier_hint = lowest tier to start from.  gated = false runs that one tier and leaves the
+// verdict of its band check in the status words for the host to act on; gated = true enqueues the
+// higher tiers behind it, each running only if the tier before it flagged an overflow.
 int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const float *x_dev, int64_t k,
-                        float *d_dev, int64_t *i_dev, int64_t label_offset, cudaStream_t stream) {
+                        float *d_dev, int64_t *i_dev, int64_t label_offset, cudaStream_t stream, int tier_hint,
+                        bool gated) {
     if (!ix.ivf) {
-        int k_sel = (int)std::min<int64_t>(k, ix.store.n);
-        // Large stores, k <= 128: one-MMA screening.  kScreenMaxList candidates come back, ranked
-        // by coarse keys; the exact re-ranking below picks the k.  Should more rows than the spare
-        // holds fall inside the error band of some query, the status word says so and the host entry
-        // point repeats the block without screening.  (ANN_CUDA_FLAT_SCREEN=0 turns it
-        // off, =1 applies it to stores of any size.)
-        const int screen_env = t_no_screen ? 0 : g_flat_screen.load(std::memory_order_relaxed);
-        int k_rank = 0;
-        if (flat_kernel_choice() == FlatKernel::TC && k_sel <= kAppendMaxK && ix.store.max_norm2 &&
-            (screen_env == 1 || (screen_env != 0 && ix.store.n >= kScreenMinRows))) {
-            const int k_list = (int)std::min<int64_t>((int64_t)kScreenMaxList, ix.store.n);
-            if (k_list > k_sel) {
-                k_rank = k_sel;
-                k_sel = k_list;
-            }
+        int tier = std::max(tier_hint, flat_first_tier(ix, (int)std::min<int64_t>(k, ix.store.n)));
+        if (tier > kTierExact) tier = kTierExact;
+        const int *gate = nullptr;
+        for (;; tier++) {
+            if (flat_tier_search(ix, ws, nq, x_dev, k, d_dev, i_dev, label_offset, stream, tier, gate)) return -1;
+            if (!gated || tier == kTierExact) return 0;
+            gate = ws.status.as<int>() + kStatusTier0 + tier;
         }
-        if (split_store_topk(ix, ix.store, ws, x_dev, nq, k_sel, stream, k_rank)) return -1;
-        return launch_refine_finalize(ix.store.hi, ix.store.lo, ix.dp, ix.d, x_dev, ix.d, ws.sel_idx.as<int32_t>(), nq,
-                                      k_sel, (int)k, ix.metric, nullptr, label_offset, d_dev, i_dev, ix.device, stream);
     }
     const int nprobe = (int)std::min<int64_t>(std::max<int64_t>(ix.nprobe, 1), ix.nlist);
     // The list scan ranks by split-TF32 keys, off by up to ~2^-20 |q - c||x|: a few more
     // candidates than asked for are selected and the exact re-ranking at the end decides the
     // k-th place, so a near tie at the boundary is settled in fp32.
-    int k_sel = (int)std::min<int64_t>(k, kMaxK);
-    if (flat_kernel_choice() == FlatKernel::TC && k_sel + kSelectMargin <= kMaxK &&
-        (int64_t)nprobe * (k_sel + kSelectMargin) <= kMergeCandidates)
-        k_sel += kSelectMargin;
-    if ((int64_t)nprobe * k_sel > kMergeCandidates)
-        return set_error("nprobe * k = %lld exceeds the %d candidates the merge step holds", (long long)nprobe * k_sel,
-                         kMergeCandidates);
+    if (k > kMaxK) return set_error("k is limited to %d", kMaxK);
+    int k_sel = (int)k;
+    if (flat_kernel_choice() == FlatKernel::TC) k_sel += kSelectMargin;
     // coarse quantiser: nprobe nearest centroids under the index metric
     const int64_t n_items = nq * nprobe;
     if (ws.probes.ensure((size_t)n_items * 4) || ws.item_slot.ensure(n_items * 4) ||
@@ -693,12 +769,11 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
         const FlatPlan plan = make_grouped_plan(max_tiles, k_sel, sm_count(ix.device));
         if (ws.gq.ensure((size_t)max_rows * 4) || ws.items.ensure((size_t)max_tiles * 16) || ws.sched.ensure(64) ||
             ws.qhi.ensure((size_t)max_rows * ix.dp * 4) || ws.qlo.ensure((size_t)max_rows * ix.dp * 4) ||
-            ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4) || ws.status.ensure(4))
+            ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4) || ws_status_ready(ws))
             return -1;
         int *n_tiles = ws.sched.as<int>(), *item_counter = ws.sched.as<int>() + 1;
         ANN_CUDA_TRY(cudaMemsetAsync(ws.sched.ptr, 0, 64, stream));
         ANN_CUDA_TRY(cudaMemsetAsync(ws.gq.ptr, 0xFF, (size_t)max_rows * 4, stream));  // padding rows: no query
-        ANN_CUDA_TRY(cudaMemsetAsync(ws.status.ptr, 0, 4, stream));
         // no clearing of the list memory: every list a query refers to is written in full by
         // the CTA that scans its (list, query tile) item, and empty lists are never referred to
         if (launch_group_probes(ws.probes.as<int32_t>(), nq, nprobe, ix.nlist, ix.list_off, ws.scratch.as<int>(), n_tiles,
@@ -713,9 +788,10 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
                                   ws.qlo.as<float>(), stream, residual ? ws.items.as<int4>() : nullptr,
                                   residual ? ix.store.hi : nullptr, residual ? ix.store.lo : nullptr, qconst))
             return -1;
-        // append mode: finished rows stay unsorted, the per-query merge filters them by the
-        // query's final threshold before it sorts (see merge_filtered_kernel)
-        const bool filtered = plan.lists_sorted && (int64_t)k_sel * 2 <= 2048;
+        // append mode: finished rows stay unsorted with their fill count; in every mode the per-query
+        // merge streams the lists of all probes and filters them by the query's final threshold
+        // before it sorts (see merge_filtered_kernel), so nprobe * k is not limited
+        const bool filtered = plan.lists_sorted;
         if (filtered && ws.part_cnt.ensure((size_t)max_rows * 4)) return -1;
         GroupedWork gw{ws.items.as<int4>(), n_tiles, item_counter, ws.gq.as<int32_t>(), qconst,
                        filtered ? ws.part_cnt.as<int32_t>() : nullptr};
@@ -730,24 +806,19 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
         if (launch_flat_tc(plan, ix.vhi, ix.vlo, residual ? ix.vrnorm : ix.vnorm, ix.rows, ws.qhi.as<float>(),
                            ws.qlo.as<float>(), max_rows, ix.dp,
                            k_sel, ix.metric, ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.qtau.as<uint32_t>(),
-                           nullptr, ws.status.as<int>(), ix.device, stream, &gw))
+                           nullptr, ws.status.as<int>() + kStatusWait, ix.device, stream, &gw))
             return -1;
         if (timing) {
             ANN_CUDA_TRY(cudaEventRecord(ws.ev1, stream));
             ws.timed = true;
             ix.last_timed_ws = &ws;
         }
-        ANN_CUDA_TRY(cudaMemcpyAsync(ws.status_host, ws.status.ptr, 4, cudaMemcpyDeviceToHost, stream));
+        if (ws_publish_status(ws, stream)) return -1;
         if (ws.sel_key.ensure((size_t)nq * k_sel * 4) || ws.sel_idx.ensure((size_t)nq * k_sel * 4)) return -1;
-        if (filtered) {
-            if (launch_merge_filtered(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.part_cnt.as<int32_t>(),
-                                      ws.item_slot.as<int32_t>(), qconst, ws.qtau.as<uint32_t>(), nprobe, nq, k_sel,
-                                      ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), stream))
-                return -1;
-        } else if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, nullptr,
-                                      ws.item_slot.as<int32_t>(), nprobe, nq, k_sel, plan.list_stride,
-                                      ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream,
-                                      plan.lists_sorted, qconst))
+        if (launch_merge_filtered(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(),
+                                  filtered ? ws.part_cnt.as<int32_t>() : nullptr, ws.item_slot.as<int32_t>(), qconst,
+                                  ws.qtau.as<uint32_t>(), nprobe, nq, k_sel, plan.list_stride, ws.sel_key.as<float>(),
+                                  ws.sel_idx.as<int32_t>(), stream))
             return -1;
         // IP: the selected distances are recomputed exactly from hi + lo, as for Flat.  L2: the
         // residual form keeps the scan's own distance accurate unless the row nearly coincides
@@ -769,28 +840,42 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
                           ws.part_idx.as<int32_t>(), ws.qtau.as<uint32_t>(), ix.device, stream))
         return -1;
     if (ws.sel_key.ensure((size_t)nq * k_sel * 4) || ws.sel_idx.ensure((size_t)nq * k_sel * 4)) return -1;
-    if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, nullptr, ws.item_slot.as<int32_t>(), nprobe,
-                           nq, k_sel, k_sel, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream))
+    if (launch_merge_filtered(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), nullptr, ws.item_slot.as<int32_t>(), nullptr,
+                              ws.qtau.as<uint32_t>(), nprobe, nq, k_sel, k_sel, ws.sel_key.as<float>(),
+                              ws.sel_idx.as<int32_t>(), stream))
         return -1;
     return launch_finalize(ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), nq, k_sel, (int)k, ix.metric, ix.ids,
                            label_offset, d_dev, i_dev, stream);
 }
 
+// keep_sticky: leave the wait word and the fallback counter as they are (they accumulate over the
+// calls on a caller's stream until ann_cuda_index_search_status collects them).
 int search_device_impl(const ann_cuda_index &ix, Workspace &ws, int64_t n, const float *x_dev, int64_t k, float *d_dev,
-                       int64_t *i_dev, int64_t label_offset, cudaStream_t stream) {
+                       int64_t *i_dev, int64_t label_offset, cudaStream_t stream, int tier_hint, bool gated,
+                       bool keep_sticky = false) {
     if (k <= 0) return set_error("k must be > 0");  // MetalIndexFlat.mm:297
     if (n <= 0) return 0;
     if (!ix.trained) return set_error("search: index must be trained first");  // MetalIndexIVFFlat.mm:125
     const int64_t stored = ix.ivf ? ix.rows : ix.store.n;
     if (ix.ntotal == 0 || stored == 0) return launch_fill_missing(d_dev, i_dev, n * k, ix.metric, stream);
-    if (!ix.ivf && std::min<int64_t>(k, ix.store.n) > kMaxK) return set_error("k is limited to %d", kMaxK);
+    if (k > kMaxK && (ix.ivf || ix.store.n > kMaxK)) return set_error("k is limited to %d", kMaxK);
     if (ix.ivf && ivf_finalize_lists(ix)) return -1;
+    const bool fresh = ws.status.ptr == nullptr;
+    if (ws_status_ready(ws)) return -1;
+    if (fresh || !keep_sticky) {
+        if (ws_clear_status(ws, stream)) return -1;
+        ws.fallbacks_seen = 0;
+    }
     for (int64_t q0 = 0; q0 < n; q0 += kQueryBlock) {
         const int64_t nb = std::min(kQueryBlock, n - q0);
-        if (search_block_device(ix, ws, nb, x_dev + q0 * ix.d, k, d_dev + q0 * k, i_dev + q0 * k, label_offset, stream))
+        // the overflow words speak of one block of queries
+        if (q0 > 0 || keep_sticky)
+            ANN_CUDA_TRY(cudaMemsetAsync(ws.status.as<int>() + kStatusTier0, 0, 3 * sizeof(int), stream));
+        if (search_block_device(ix, ws, nb, x_dev + q0 * ix.d, k, d_dev + q0 * k, i_dev + q0 * k, label_offset, stream,
+                                tier_hint, gated))
             return -1;
     }
-    return 0;
+    return ws_publish_status(ws, stream);
 }
 
 int upload_and(ann_cuda_index *ix, int64_t n, const float *x_host,
@@ -900,6 +985,9 @@ int ann_cuda_set_flat_kernel(const char *name) {
 }
 
 uint64_t ann_cuda_screen_fallbacks(void) { return g_screen_fallbacks.load(std::memory_order_relaxed); }
+
+void ann_cuda_set_wait_limit_ms(int ms) { set_flat_wait_limit_ns(ms > 0 ? (uint64_t)ms * 1000000ull : 0); }
+void ann_cuda_test_withhold_loads(int after_k_blocks) { set_flat_test_withhold_after(after_k_blocks < 0 ? -1 : after_k_blocks); }
 
 void ann_cuda_set_kernel_timing(int on) { g_time_kernels.store(on ? 1 : 0); }
 
@@ -1181,7 +1269,7 @@ int ann_cuda_ivfflat_coarse(const ann_cuda_index *ix, int64_t n, const float *x,
         const int64_t nb = std::min(kQueryBlock, n - q0);
         if (ws.x.ensure((size_t)nb * ix->d * 4)) return -1;
         ANN_CUDA_TRY(cudaMemcpyAsync(ws.x.ptr, x + q0 * ix->d, (size_t)nb * ix->d * 4, cudaMemcpyHostToDevice, s));
-        if (ws.probes.ensure((size_t)nb * np * 4)) return -1;
+        if (ws.probes.ensure((size_t)nb * np * 4) || ws_clear_status(ws, s)) return -1;
         if (coarse_probes(*ix, ws, ws.x.as<float>(), nb, np, ws.probes.as<int32_t>(), s, ix->coarse_exact)) return -1;
         tmp.resize((size_t)nb * np);
         ANN_CUDA_TRY(cudaMemcpyAsync(tmp.data(), ws.probes.ptr, (size_t)nb * np * 4, cudaMemcpyDeviceToHost, s));
@@ -1243,16 +1331,50 @@ int ann_cuda_index_search_device(const ann_cuda_index *ix, int64_t n, const floa
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     WsLease lease(ix, s, false);
     if (!lease.ws) return -1;
-    if (*lease.ws->status_host) {
-        const int code = *lease.ws->status_host;
-        *lease.ws->status_host = 0;
-        if (code == kScreenOverflow)
-            return set_error("an earlier screened search on this stream had more rows inside its error band than spare "
-                             "candidates: its results may miss near ties; use the host entry point or "
-                             "ann_cuda_set_flat_kernel(\"tcgen05-split\") for such data");
-        return set_error("an earlier search on this stream gave up on a wait inside the flat kernel (code %d)", code);
+    // Nothing is waited for here, so every fallback tier is enqueued behind the first one, gated on
+    // the device by the band check of the tier before it: the results are complete when the stream
+    // gets there, whatever the data.  Give-up codes of bounded waits accumulate in the workspace of
+    // this stream until ann_cuda_index_search_status collects them.
+    return search_device_impl(*ix, *lease.ws, n, x_device, k, distances_device, labels_device, label_offset, s, 0, true,
+                              true);
+}
+
+int ann_cuda_index_search_status(const ann_cuda_index *ix, void *stream) {
+    if (!ix) return set_error("null index");
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    ANN_CUDA_TRY(cudaStreamSynchronize(s));
+    // every idle workspace that served this stream
+    std::vector<Workspace *> mine;
+    {
+        std::lock_guard<std::mutex> lock(ix->ws_mu);
+        for (size_t i = 0; i < ix->ws_free.size();) {
+            Workspace *w = ix->ws_free[i];
+            if (w->bound == s && w->bound != w->own_stream) {
+                mine.push_back(w);
+                ix->ws_free.erase(ix->ws_free.begin() + i);
+            } else {
+                i++;
+            }
+        }
     }
-    return search_device_impl(*ix, *lease.ws, n, x_device, k, distances_device, labels_device, label_offset, s);
+    int code = 0, rc = 0;
+    for (Workspace *w : mine) {
+        if (!w->status.ptr) continue;  // never searched
+        ws_absorb_fallbacks(*w);
+        if (!code) code = w->status_host[kStatusWait];
+        // start over: the wait word and the fallback counter are sticky until collected here
+        if (ws_clear_status(*w, s) || ws_publish_status(*w, s)) rc = -1;
+        w->fallbacks_seen = 0;
+    }
+    if (cudaStreamSynchronize(s) != cudaSuccess) rc = set_error("device error while collecting the search status");
+    for (Workspace *w : mine) ix->release_ws(w);
+    if (rc) return -1;
+    if (code)
+        return set_error("a search on this stream gave up on a wait inside the flat kernel (code %d): its results are not valid",
+                         code);
+    return 0;
 }
 
 int ann_cuda_index_search(const ann_cuda_index *ix, int64_t n, const float *x, int64_t k, float *distances,
@@ -1272,26 +1394,25 @@ int ann_cuda_index_search(const ann_cuda_index *ix, int64_t n, const float *x, i
         if (ws.x.ensure((size_t)nb * ix->d * 4) || ws.out_d.ensure((size_t)nb * k * 4) || ws.out_i.ensure((size_t)nb * k * 8))
             return -1;
         ANN_CUDA_TRY(cudaMemcpyAsync(ws.x.ptr, x + q0 * ix->d, (size_t)nb * ix->d * 4, cudaMemcpyHostToDevice, s));
-        *ws.status_host = 0;
-        if (search_device_impl(*ix, ws, nb, ws.x.as<float>(), k, ws.out_d.as<float>(), ws.out_i.as<int64_t>(), 0, s))
-            return -1;
-        ANN_CUDA_TRY(cudaMemcpyAsync(distances + q0 * k, ws.out_d.ptr, (size_t)nb * k * 4, cudaMemcpyDeviceToHost, s));
-        ANN_CUDA_TRY(cudaMemcpyAsync(labels + q0 * k, ws.out_i.ptr, (size_t)nb * k * 8, cudaMemcpyDeviceToHost, s));
-        ANN_CUDA_TRY(cudaStreamSynchronize(s));
-        if (*ws.status_host == kScreenOverflow && !t_no_screen) {
-            // too many rows inside the screening band of some query: this block once more with the
-            // three-MMA product, which needs no spare candidates
-            *ws.status_host = 0;
-            t_no_screen = true;
+        // This call waits for its results anyway, so a tier whose band check flags an overflow is
+        // repeated one tier up from here (no gated launches on the common path: one query per call
+        // is how the extension searches, src/faiss_index.cpp:737).
+        for (int tier = 0;;) {
+            if (search_device_impl(*ix, ws, nb, ws.x.as<float>(), k, ws.out_d.as<float>(), ws.out_i.as<int64_t>(), 0, s, tier,
+                                   false))
+                return -1;
+            ANN_CUDA_TRY(cudaMemcpyAsync(distances + q0 * k, ws.out_d.ptr, (size_t)nb * k * 4, cudaMemcpyDeviceToHost, s));
+            ANN_CUDA_TRY(cudaMemcpyAsync(labels + q0 * k, ws.out_i.ptr, (size_t)nb * k * 8, cudaMemcpyDeviceToHost, s));
+            ANN_CUDA_TRY(cudaStreamSynchronize(s));
+            if (ws.status_host[kStatusWait])
+                return set_error("flat kernel gave up on a wait (code %d)", ws.status_host[kStatusWait]);
+            int flagged = -1;
+            for (int t = kTierScreen; t <= kTierExact; t++)
+                if (ws.status_host[kStatusTier0 + t] == kScreenOverflow) flagged = t;
+            if (flagged < 0) break;
+            if (flagged >= kTierExact) return set_error("the exact tier reported an overflow");  // it has no band check
             g_screen_fallbacks.fetch_add(1, std::memory_order_relaxed);
-            q0 -= kQueryBlock;
-            continue;
-        }
-        t_no_screen = false;
-        if (*ws.status_host) {
-            const int code = *ws.status_host;
-            *ws.status_host = 0;
-            return set_error("flat kernel gave up on a wait (code %d)", code);
+            tier = flagged + 1;
         }
     }
     return 0;
@@ -1341,10 +1462,8 @@ int ann_cuda_index_search_async(const ann_cuda_index *ix, int64_t n, const float
         // the copy out of pageable memory is staged before the call returns: x may be reused at once
         if (!rc && cudaMemcpyAsync(ws.x.ptr, x, (size_t)n * ix->d * 4, cudaMemcpyHostToDevice, s) != cudaSuccess)
             rc = set_error("query upload failed");
-        if (!rc) {
-            *ws.status_host = 0;
-            rc = search_device_impl(*ix, ws, n, ws.x.as<float>(), k, ws.out_d.as<float>(), ws.out_i.as<int64_t>(), 0, s);
-        }
+        // all tiers are enqueued now, gated on the device: the wait only has to collect the results
+        if (!rc) rc = search_device_impl(*ix, ws, n, ws.x.as<float>(), k, ws.out_d.as<float>(), ws.out_i.as<int64_t>(), 0, s, 0, true);
         if (!rc && (cudaEventCreateWithFlags(&t->done, cudaEventDisableTiming) != cudaSuccess ||
                     cudaEventRecord(t->done, s) != cudaSuccess))
             rc = set_error("event record failed");
@@ -1377,24 +1496,12 @@ int ann_cuda_search_token_wait(ann_cuda_search_token *t) {
         t->lease = nullptr;
         return rc;
     };
-    for (int pass = 0; pass < 2; pass++) {
-        if (cudaMemcpyAsync(t->distances, ws.out_d.ptr, (size_t)t->n * t->k * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
-            cudaMemcpyAsync(t->labels, ws.out_i.ptr, (size_t)t->n * t->k * 8, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
-            cudaStreamSynchronize(s) != cudaSuccess)
-            return finish(set_error("asynchronous search failed: %s", cudaGetErrorString(cudaGetLastError())));
-        const int code = *ws.status_host;
-        *ws.status_host = 0;
-        if (code == 0) break;
-        if (code != kScreenOverflow || pass == 1) return finish(set_error("flat kernel gave up on a wait (code %d)", code));
-        // some query had more rows inside its screening band than spare candidates: once more,
-        // with the three-MMA product, from the queries still held in the workspace
-        g_screen_fallbacks.fetch_add(1, std::memory_order_relaxed);
-        t_no_screen = true;
-        const int rc = search_device_impl(*ix, ws, t->n, ws.x.as<float>(), t->k, ws.out_d.as<float>(),
-                                          ws.out_i.as<int64_t>(), 0, s);
-        t_no_screen = false;
-        if (rc) return finish(-1);
-    }
+    if (cudaMemcpyAsync(t->distances, ws.out_d.ptr, (size_t)t->n * t->k * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaMemcpyAsync(t->labels, ws.out_i.ptr, (size_t)t->n * t->k * 8, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess)
+        return finish(set_error("asynchronous search failed: %s", cudaGetErrorString(cudaGetLastError())));
+    ws_absorb_fallbacks(ws);
+    if (ws.status_host[kStatusWait]) return finish(set_error("flat kernel gave up on a wait (code %d)", ws.status_host[kStatusWait]));
     return finish(0);
 }
 
@@ -1405,7 +1512,6 @@ void ann_cuda_search_token_free(ann_cuda_search_token *t) {
         if (t->lease->ws) {
             DeviceGuard g(t->ix->device);
             cudaStreamSynchronize(t->lease->ws->own_stream);
-            *t->lease->ws->status_host = 0;
         }
         delete t->lease;
     }
@@ -1584,8 +1690,13 @@ extern "C" int ann_cuda_flat_search_small_static(const ann_cuda_index *ix, int64
     unsigned char *base = nullptr;
     if (static_scratch_base(ix->device, &base)) return -1;  // first call on a device: looks the address up
     const int k_sel = (int)std::min<int64_t>(k, ix->store.n);
-    const FlatPlan plan = make_flat_plan(n, ix->store.n, k_sel, sm_count(ix->device));
-    if (plan.nq_tiles != 1 || plan.lists_per_qt > kStaticMaxLists || plan.list_stride > kStaticMaxK)
+    // like the regular split-product search: 16 candidates for k <= 12, so that near ties at the
+    // k-th place are settled by the exact re-ranking below (k = 13..16: no spare, no band check)
+    const int k_list = split_list_len(k_sel, ix->store.n) <= kStaticMaxK ? split_list_len(k_sel, ix->store.n) : k_sel;
+    const FlatPlan plan = make_flat_plan(n, ix->store.n, k_list, sm_count(ix->device));
+    if (plan.list_stride > kStaticMaxK)
+        return set_error("allocation-free search: lists of %d entries exceed the limit of %d", plan.list_stride, kStaticMaxK);
+    if (plan.nq_tiles != 1 || plan.lists_per_qt > kStaticMaxLists)
         return set_error("allocation-free search: this device needs %d candidate lists, the static scratch holds %d",
                          plan.lists_per_qt, kStaticMaxLists);
     float *qhi = reinterpret_cast<float *>(base + kOffQhi), *qlo = reinterpret_cast<float *>(base + kOffQlo);
@@ -1596,18 +1707,36 @@ extern "C" int ann_cuda_flat_search_small_static(const ann_cuda_index *ix, int64
     int32_t *part_idx = reinterpret_cast<int32_t *>(base + kOffPartIdx);
     float *sel_key = reinterpret_cast<float *>(base + kOffSelKey);
     int32_t *sel_idx = reinterpret_cast<int32_t *>(base + kOffSelIdx);
-    // The array still holds the previous call's lists, thresholds and counters.
-    ANN_CUDA_TRY(cudaMemsetAsync(status, 0, 4, s));
+    // The array still holds the previous call's lists, thresholds and counters.  The two status
+    // words (wait give-up code, band overflow) are sticky until ..._static_status reads them.
     ANN_CUDA_TRY(cudaMemsetAsync(qtau, 0xFF, 128 * 4, s));
     ANN_CUDA_TRY(cudaMemsetAsync(sched, 0, 2 * 4, s));
     ANN_CUDA_TRY(cudaMemsetAsync(part_idx, 0xFF, plan.part_entries * 4, s));
     if (launch_split_rows(x_device, n, ix->d, ix->dp, qhi, qlo, qn, s, ix->store.center(), true)) return -1;
-    if (launch_flat_tc(plan, ix->store.hi, ix->store.lo, ix->store.norms, ix->store.n, qhi, qlo, n, ix->dp, k_sel,
+    if (launch_flat_tc(plan, ix->store.hi, ix->store.lo, ix->store.norms, ix->store.n, qhi, qlo, n, ix->dp, k_list,
                        ix->metric, part_key, part_idx, qtau, sched, status, ix->device, s))
         return -1;
-    if (launch_merge_parts(part_key, part_idx, 0, sched + plan.nq_tiles, nullptr, plan.lists_per_qt, n, k_sel,
+    if (launch_merge_parts(part_key, part_idx, 0, sched + plan.nq_tiles, nullptr, plan.lists_per_qt, n, k_list,
                            plan.list_stride, sel_key, sel_idx, ix->device, s))
         return -1;
-    return launch_refine_finalize(ix->store.hi, ix->store.lo, ix->dp, ix->d, x_device, ix->d, sel_idx, n, k_sel, (int)k,
+    if (k_list > k_sel && k_list < ix->store.n &&
+        launch_screen_check(sel_key, n, k_list, k_sel, qn, ix->store.max_norm2, ix->d, ix->metric, false, status + 1, nullptr, s))
+        return -1;
+    return launch_refine_finalize(ix->store.hi, ix->store.lo, ix->dp, ix->d, x_device, ix->d, sel_idx, n, k_list, (int)k,
                                   ix->metric, nullptr, label_offset, distances_device, labels_device, ix->device, s);
+}
+
+extern "C" int ann_cuda_flat_search_small_static_status(int device, void *stream) {
+    DeviceGuard g(device);
+    if (!g.ok) return set_error("cudaSetDevice(%d) failed", device);
+    unsigned char *base = nullptr;
+    if (static_scratch_base(device, &base)) return -1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    ANN_CUDA_TRY(cudaStreamSynchronize(s));
+    int words[2] = {0, 0};
+    ANN_CUDA_TRY(cudaMemcpy(words, base + kOffStatus, sizeof words, cudaMemcpyDeviceToHost));  // pageable target: no allocation
+    ANN_CUDA_TRY(cudaMemset(base + kOffStatus, 0, sizeof words));
+    if (words[0]) return set_error("allocation-free search: the flat kernel gave up on a wait (code %d); results are not valid", words[0]);
+    if (words[1] == kScreenOverflow) return 1;
+    return 0;
 }

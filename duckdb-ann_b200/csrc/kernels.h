@@ -12,11 +12,25 @@ namespace anncuda {
 // whole number of 128-byte TMA boxes.
 constexpr int kDimPad = 32;
 constexpr int kMaxK = 2048;  // largest k a search accepts
+// Longest list a first-stage kernel keeps: the split-product search selects k + kSplitSpare
+// candidates so that near ties at the k-th place can be settled by exact fp32 re-ranking.
+constexpr int kSplitSpare = 32;
+constexpr int kMaxListK = kMaxK + 2 * kSplitSpare;
 
 inline int pad_dim(int d) { return (d + kDimPad - 1) / kDimPad * kDimPad; }
 
 uint64_t launch_count_value();
 void count_launch(int n = 1);
+
+// Limit of every bounded wait inside the tensor-core kernel (process-wide; 2 s by default).
+uint64_t flat_wait_limit_ns();
+void set_flat_wait_limit_ns(uint64_t ns);
+// Test hook, off (-1) by default: with a value >= 0 the TMA producer of every CTA stops loading
+// after that many K blocks, so the MMA issuer's wait for the next stage runs out after the wait
+// limit, the kernel records the give-up code and every role leaves in order.  The search then
+// fails with an error; it never returns partial results as success.
+int flat_test_withhold_after();
+void set_flat_test_withhold_after(int k_blocks);
 
 // ---- prep.cu -----------------------------------------------------------------------------
 // x (n x d, row stride d) -> hi, lo (n x dp each): hi = x rounded to TF32, lo = x - hi
@@ -37,7 +51,7 @@ int launch_pad_rows(const float *x, int64_t n, int d, int dp, float *out, float 
 int launch_join_rows(const float *hi, const float *lo, int64_t n, int d, int dp, float *out, cudaStream_t stream);
 
 // ---- flat_tc.cu --------------------------------------------------------------------------
-constexpr int kAppendMaxK = 128;         // largest k the append-and-compact selection handles
+constexpr int kAppendMaxK = 256;         // largest k the append-and-compact selection handles
 constexpr int kMergeCandidates = 16384;  // most (list, slot) candidates per query the merge kernel sorts
 
 struct FlatPlan {
@@ -92,22 +106,31 @@ struct ScreenInput {
     int d;                        // true dimension
 };
 constexpr int kScreenMaxList = 256;  // longest list (k_rank + spare) the screened mode keeps
+constexpr int kScreenMaxK = kScreenMaxList - kSplitSpare;  // largest k searched with screening
 constexpr int kScreenOverflow = 100;  // status code: more rows inside the error band than the spare holds
-// Sets *status (if still 0) to kScreenOverflow when the last of the k_list merged candidates of
-// some query is still within the slack of its k_rank-th key.
+// Band check of a tensor-core ranking (screened = one-MMA keys, else split-product keys; see
+// key_slack): sets *overflow (if still 0) to kScreenOverflow when the last of the k_list merged
+// candidates of some query is still within the slack of its k_rank-th key - rows that belong
+// among the exact k_rank best may then have been left out.  *overflow_count (may be null) is
+// incremented once per launch that flags.
+// Every launcher that takes a `gate` runs its kernel only if gate is null or *gate ==
+// kScreenOverflow on the device when the kernel starts: that is how a fallback pass is enqueued
+// behind the pass it repairs without a host round trip.
 int launch_screen_check(const float *sel_key, int64_t nq, int k_list, int k_rank, const float *q_norm2,
-                        const unsigned *x_max_norm2, int d, int metric, int *status, cudaStream_t stream);
+                        const unsigned *x_max_norm2, int d, int metric, bool screened, int *overflow,
+                        int *overflow_count, cudaStream_t stream, const int *gate = nullptr);
 
 int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
                    int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
-                   const GroupedWork *grouped = nullptr, const ScreenInput *screen = nullptr);
+                   const GroupedWork *grouped = nullptr, const ScreenInput *screen = nullptr,
+                   const int *gate = nullptr);
 // The same kernel built with K blocks of 32 floats (flat_tc_bk32.cu); launch_flat_tc hands the
 // screened searches to it.
 int launch_flat_tc_bk32(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                         const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
                         int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
-                        const GroupedWork *grouped, const ScreenInput *screen);
+                        const GroupedWork *grouped, const ScreenInput *screen, const int *gate);
 // make_flat_plan for a screened search: lists of `k` (up to kScreenMaxList) in append mode
 FlatPlan make_flat_plan_screened(int64_t nq, int64_t n, int k, int sms);
 
@@ -146,7 +169,12 @@ int launch_residual_norms(const float *xhi, const float *xlo, int64_t n, int d, 
 int launch_scan_items(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
                       const int32_t *item_query, const int64_t *range_begin, const int64_t *range_end,
                       int64_t n_items, int k, int metric, float *part_key, int32_t *part_idx, uint32_t *qtau,
-                      int device, cudaStream_t stream);
+                      int device, cudaStream_t stream, const int *gate = nullptr);
+
+// Items of the exact flat scan, built on the device: item q * chunks + c = query q against rows
+// [c * per, min(n, (c + 1) * per)).
+int launch_fill_chunk_items(int32_t *item_query, int64_t *range_begin, int64_t *range_end, int64_t nq, int chunks,
+                            int64_t per, int64_t n, cudaStream_t stream);
 
 // Builds the (query, list) items of an IVF search from the coarse result:
 // probes (nq x nprobe) int32 list numbers (-1 = none); items are grouped by list so
@@ -170,17 +198,19 @@ int launch_build_ivf_items(const int32_t *probes, int64_t nq, int nprobe, int64_
 int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layout, const int *lists_started,
                        const int32_t *slot_of, int nparts, int64_t nq, int k, int list_stride, float *out_key,
                        int32_t *out_idx, int device, cudaStream_t stream, bool lists_sorted = false,
-                       const float *slot_key_offset = nullptr);
+                       const float *slot_key_offset = nullptr, const int *gate = nullptr);
 
-// Grouped list scan with GroupedWork::part_cnt: per query, the k best of the append buffers of
-// its nparts lists (gathered row slot_of[q * nparts + p], -1 = none; buffer = the first
-// part_cnt[row] of kAppendBuffer slots at part_*[row * kAppendBuffer]), sorted best first.
-// Entries above the query's final threshold qtau[q] (ordered-uint form, key + slot_key_offset[row])
-// are dropped before anything is sorted.
+// Grouped list scan: per query, the k best of the lists of its nparts probes (gathered row
+// slot_of[q * nparts + p], -1 = none), sorted best first.  A row's list is the first part_cnt[row]
+// of list_stride slots at part_*[row * list_stride] (append buffers left unsorted by the scan), or,
+// with part_cnt null, list_stride slots of which the empty ones carry index -1.  Entries above the
+// query's final threshold qtau[q] (ordered-uint form, key + slot_key_offset[row]) are dropped as
+// they are read, so any number of probes can be merged.
 constexpr int kAppendBuffer = 512;
 int launch_merge_filtered(const float *part_key, const int32_t *part_idx, const int32_t *part_cnt,
                           const int32_t *slot_of, const float *slot_key_offset, const uint32_t *qtau, int nparts,
-                          int64_t nq, int k, float *out_key, int32_t *out_idx, cudaStream_t stream);
+                          int64_t nq, int k, int list_stride, float *out_key, int32_t *out_idx,
+                          cudaStream_t stream);
 
 // Flat: recomputes the distance of every selected (query, row) pair in exact fp32
 // from the split store, sorts the k results best first and writes the user-facing
@@ -194,7 +224,7 @@ int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, co
                            const int32_t *sel_idx, int64_t nq, int k_sel, int k_out, int metric,
                            const int64_t *ids, int64_t label_offset, float *out_d, int64_t *out_i, int device,
                            cudaStream_t stream, const float *approx_key = nullptr, const float *rnorm = nullptr,
-                           const float *xnorm = nullptr, int32_t *out_row = nullptr);
+                           const float *xnorm = nullptr, int32_t *out_row = nullptr, const int *gate = nullptr);
 
 // Already-exact keys: just convert to user-facing values and labels, padding to k_out.
 int launch_finalize(const float *sel_key, const int32_t *sel_idx, int64_t nq, int k_sel, int k_out, int metric,

@@ -19,6 +19,9 @@ constexpr int kMaxCandidates = kMergeCandidates;
 // 2 * 2^-21 |v||x| <= 0.25e-4 * dist  <=>  dist >= 0.038 |v||x|
 constexpr float kRefineBelow = 0.04f;
 
+// A gated kernel runs only behind a pass whose band check flagged an overflow (see kernels.h).
+__device__ __forceinline__ bool gate_closed(const int *gate) { return gate && *gate != kScreenOverflow; }
+
 __host__ __device__ inline int next_pow2(int v) {
     int p = 1;
     while (p < v) p <<= 1;
@@ -52,8 +55,9 @@ __global__ void __launch_bounds__(kMergeThreads)
 merge_parts_kernel(const float *__restrict__ part_key, const int32_t *__restrict__ part_idx, int layout,
                    const int *__restrict__ lists_started, const int32_t *__restrict__ slot_of, int nparts, int64_t nq,
                    int k, int list_stride, int P_max, const float *__restrict__ slot_key_offset,
-                   float *__restrict__ out_key, int32_t *__restrict__ out_idx) {
+                   float *__restrict__ out_key, int32_t *__restrict__ out_idx, const int *gate) {
     extern __shared__ float smem_f[];
+    if (gate_closed(gate)) return;
     float *keys = smem_f;
     int32_t *vals = reinterpret_cast<int32_t *>(smem_f + P_max);
     const int64_t q = blockIdx.x;
@@ -107,8 +111,9 @@ __global__ void __launch_bounds__(kMergeThreads)
 merge_sorted_kernel(const float *__restrict__ part_key, const int32_t *__restrict__ part_idx, int layout,
                     const int *__restrict__ lists_started, const int32_t *__restrict__ slot_of, int nparts, int64_t nq,
                     int k, int list_stride, int K2, int L2n, const float *__restrict__ slot_key_offset,
-                    float *__restrict__ out_key, int32_t *__restrict__ out_idx) {
+                    float *__restrict__ out_key, int32_t *__restrict__ out_idx, const int *gate) {
     extern __shared__ float smem_f[];
+    if (gate_closed(gate)) return;
     float *keys = smem_f;                                              // [L2n][K2]
     int32_t *vals = reinterpret_cast<int32_t *>(smem_f + L2n * K2);
     const int64_t q = blockIdx.x;
@@ -178,19 +183,20 @@ merge_sorted_kernel(const float *__restrict__ part_key, const int32_t *__restric
     }
 }
 
-// Streaming top-k over the unsorted append buffers of one query's lists.  Candidates above the
-// query's final threshold are dropped as they are read; the survivors collect in a shared
-// buffer of kFilterCap pairs; when the next round of reads might not fit, the buffer is sorted,
-// cut to its best k and its k-th key becomes the threshold.  Exact for any input; with the
-// threshold the scan kernel leaves behind, the usual case is one small sort at the end.
+// Streaming top-k over the lists of one query's probes.  Candidates above the query's final
+// threshold are dropped as they are read; the survivors collect in a shared buffer of `cap` pairs;
+// when the next round of reads might not fit, the buffer is sorted, cut to its best k and its k-th
+// key becomes the threshold.  Exact for any input and any number of lists; with the threshold the
+// scan kernel leaves behind, the usual case is one small sort at the end.
 constexpr int kFilterCap = 2048;
 __global__ void __launch_bounds__(kMergeThreads)
 merge_filtered_kernel(const float *__restrict__ part_key, const int32_t *__restrict__ part_idx,
                       const int32_t *__restrict__ part_cnt, const int32_t *__restrict__ slot_of,
                       const float *__restrict__ slot_key_offset, const uint32_t *__restrict__ qtau, int nparts,
-                      int k, float *__restrict__ out_key, int32_t *__restrict__ out_idx) {
-    __shared__ float keys[kFilterCap];
-    __shared__ int32_t vals[kFilterCap];
+                      int k, int list_stride, int cap, float *__restrict__ out_key, int32_t *__restrict__ out_idx) {
+    extern __shared__ float smem_f[];
+    float *keys = smem_f;
+    int32_t *vals = reinterpret_cast<int32_t *>(smem_f + cap);
     __shared__ int count;
     const int64_t q = blockIdx.x;
     if (threadIdx.x == 0) count = 0;
@@ -218,14 +224,14 @@ merge_filtered_kernel(const float *__restrict__ part_key, const int32_t *__restr
     for (int p = 0; p < nparts; p++) {
         const int32_t g = slot_of[q * nparts + p];
         if (g < 0) continue;  // block-uniform
-        const int c = part_cnt[g];
+        const int c = part_cnt ? part_cnt[g] : list_stride;
         const float off = slot_key_offset ? slot_key_offset[g] : 0.f;
         for (int j0 = 0; j0 < c; j0 += blockDim.x) {
-            if (count + (int)blockDim.x > kFilterCap) shrink();  // block-uniform: count is read after a barrier
+            if (count + (int)blockDim.x > cap) shrink();  // block-uniform: count is read after a barrier
             const int j = j0 + threadIdx.x;
             if (j < c) {
-                const int32_t idx = part_idx[(size_t)g * kAppendBuffer + j];
-                const float key = part_key[(size_t)g * kAppendBuffer + j] + off;
+                const int32_t idx = part_idx[(size_t)g * list_stride + j];
+                const float key = part_key[(size_t)g * list_stride + j] + off;
                 if (idx >= 0 && key <= tau) {
                     const int pos = atomicAdd(&count, 1);
                     keys[pos] = key;
@@ -244,18 +250,22 @@ merge_filtered_kernel(const float *__restrict__ part_key, const int32_t *__restr
     }
 }
 
-// Screened flat search: the guarantee holds while fewer than k_list - k_rank rows sit within the
-// slack above the k_rank-th coarse key.  If the LAST candidate of a query is still inside that
-// band, rows may have been left out: status (0 so far) becomes kScreenOverflow and the host entry
-// points repeat the search with the three-MMA product.
+// Band check of a tensor-core ranking.  The guarantee of the screened search (and of the split
+// product with spare candidates) holds while the LAST of the k_list candidates of a query lies
+// beyond the slack above its k_rank-th key.  If it is still inside that band, rows may have been
+// left out: *overflow (0 so far) becomes kScreenOverflow and the search is repeated one tier up
+// (split product, then the exact fp32 scan).
 __global__ void screen_check_kernel(const float *__restrict__ sel_key, int64_t nq, int k_list, int k_rank,
                                     const float *__restrict__ q_norm2, const unsigned *__restrict__ x_max_norm2, int d,
-                                    int l2, int *__restrict__ status) {
+                                    int l2, int screened, int *__restrict__ overflow, int *__restrict__ overflow_count,
+                                    const int *gate) {
+    if (gate_closed(gate)) return;
     const int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (q >= nq) return;
     const float last = sel_key[q * k_list + k_list - 1], kth = sel_key[q * k_list + k_rank - 1];
-    if (last < kInf && last <= kth + screen_slack(q_norm2[q], __uint_as_float(*x_max_norm2), d, l2 != 0))
-        atomicCAS(status, 0, kScreenOverflow);
+    if (last < kInf && last <= kth + key_slack(q_norm2[q], __uint_as_float(*x_max_norm2), d, l2 != 0, screened != 0)) {
+        if (atomicCAS(overflow, 0, kScreenOverflow) == 0 && overflow_count) atomicAdd(overflow_count, 1);
+    }
 }
 
 // Exact fp32 re-evaluation of the selected pairs, sort, and user-facing output.
@@ -265,8 +275,9 @@ refine_finalize_kernel(const float *__restrict__ xhi, const float *__restrict__ 
                        int k_sel, int k_out, int P, int metric, const int64_t *__restrict__ ids,
                        int64_t label_offset, const float *__restrict__ approx_key, const float *__restrict__ rnorm,
                        const float *__restrict__ xnorm, float *__restrict__ out_d, int64_t *__restrict__ out_i,
-                       int32_t *__restrict__ out_row) {
+                       int32_t *__restrict__ out_row, const int *gate) {
     extern __shared__ float smem_f[];
+    if (gate_closed(gate)) return;
     float *keys = smem_f;
     int32_t *vals = reinterpret_cast<int32_t *>(smem_f + P);
     const int64_t q = blockIdx.x;
@@ -414,7 +425,7 @@ int opt_in_smem(K kernel, size_t smem) {
 int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layout, const int *lists_started,
                        const int32_t *slot_of, int nparts, int64_t nq, int k, int list_stride, float *out_key,
                        int32_t *out_idx, int device, cudaStream_t stream, bool lists_sorted,
-                       const float *slot_key_offset) {
+                       const float *slot_key_offset, const int *gate) {
     (void)device;
     if (nq <= 0) return 0;
     const int total = nparts * k;
@@ -426,7 +437,7 @@ int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layou
             if (opt_in_smem(merge_sorted_kernel, smem)) return -1;
             merge_sorted_kernel<<<(unsigned)nq, kMergeThreads, smem, stream>>>(
                 part_key, part_idx, layout, lists_started, slot_of, nparts, nq, k, list_stride, K2, L2n, slot_key_offset,
-                out_key, out_idx);
+                out_key, out_idx, gate);
             count_launch();
             ANN_CUDA_TRY(cudaGetLastError());
             return 0;
@@ -437,7 +448,7 @@ int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layou
     if (opt_in_smem(merge_parts_kernel, smem)) return -1;
     merge_parts_kernel<<<(unsigned)nq, kMergeThreads, smem, stream>>>(part_key, part_idx, layout, lists_started, slot_of,
                                                                       nparts, nq, k, list_stride, P, slot_key_offset, out_key,
-                                                                      out_idx);
+                                                                      out_idx, gate);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -445,21 +456,29 @@ int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layou
 
 int launch_merge_filtered(const float *part_key, const int32_t *part_idx, const int32_t *part_cnt,
                           const int32_t *slot_of, const float *slot_key_offset, const uint32_t *qtau, int nparts,
-                          int64_t nq, int k, float *out_key, int32_t *out_idx, cudaStream_t stream) {
+                          int64_t nq, int k, int list_stride, float *out_key, int32_t *out_idx,
+                          cudaStream_t stream) {
     if (nq <= 0) return 0;
-    if (k > kFilterCap / 2) return set_error("merge: k = %d is too large for the filtered merge", k);
-    merge_filtered_kernel<<<(unsigned)nq, kMergeThreads, 0, stream>>>(part_key, part_idx, part_cnt, slot_of,
-                                                                     slot_key_offset, qtau, nparts, k, out_key, out_idx);
+    // room for the k kept entries plus one round of reads, as a power of two for the sort
+    int cap = kFilterCap;
+    while (cap < k + kMergeThreads) cap <<= 1;
+    const size_t smem = (size_t)cap * 8;
+    if (opt_in_smem(merge_filtered_kernel, smem)) return -1;
+    merge_filtered_kernel<<<(unsigned)nq, kMergeThreads, smem, stream>>>(part_key, part_idx, part_cnt, slot_of,
+                                                                        slot_key_offset, qtau, nparts, k, list_stride,
+                                                                        cap, out_key, out_idx);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
 }
 
 int launch_screen_check(const float *sel_key, int64_t nq, int k_list, int k_rank, const float *q_norm2,
-                        const unsigned *x_max_norm2, int d, int metric, int *status, cudaStream_t stream) {
+                        const unsigned *x_max_norm2, int d, int metric, bool screened, int *overflow,
+                        int *overflow_count, cudaStream_t stream, const int *gate) {
     if (nq <= 0 || k_list <= k_rank) return 0;
     screen_check_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, stream>>>(sel_key, nq, k_list, k_rank, q_norm2, x_max_norm2,
-                                                                          d, metric != 0, status);
+                                                                          d, metric != 0, screened ? 1 : 0, overflow,
+                                                                          overflow_count, gate);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -469,7 +488,7 @@ int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, co
                            const int32_t *sel_idx, int64_t nq, int k_sel, int k_out, int metric,
                            const int64_t *ids, int64_t label_offset, float *out_d, int64_t *out_i, int device,
                            cudaStream_t stream, const float *approx_key, const float *rnorm, const float *xnorm,
-                           int32_t *out_row) {
+                           int32_t *out_row, const int *gate) {
     (void)device;
     if (nq <= 0) return 0;
     const int P = next_pow2(k_sel < 2 ? 2 : k_sel);
@@ -477,7 +496,7 @@ int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, co
     if (opt_in_smem(refine_finalize_kernel, smem)) return -1;
     refine_finalize_kernel<<<(unsigned)nq, 128, smem, stream>>>(xhi, xlo, dp, d, queries, q_stride, sel_idx, k_sel,
                                                                 k_out, P, metric, ids, label_offset, approx_key, rnorm, xnorm,
-                                                                out_d, out_i, out_row);
+                                                                out_d, out_i, out_row, gate);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

@@ -16,6 +16,13 @@ static std::atomic<uint64_t> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 uint64_t launch_count_value() { return g_launches.load(std::memory_order_relaxed); }
 
+static std::atomic<uint64_t> g_wait_limit_ns{2000000000ull};
+static std::atomic<int> g_withhold_after{-1};
+uint64_t flat_wait_limit_ns() { return g_wait_limit_ns.load(std::memory_order_relaxed); }
+void set_flat_wait_limit_ns(uint64_t ns) { g_wait_limit_ns.store(ns ? ns : 2000000000ull, std::memory_order_relaxed); }
+int flat_test_withhold_after() { return g_withhold_after.load(std::memory_order_relaxed); }
+void set_flat_test_withhold_after(int k_blocks) { g_withhold_after.store(k_blocks, std::memory_order_relaxed); }
+
 namespace {
 
 constexpr int kWarps = 8;

@@ -36,8 +36,9 @@ scan_items_kernel(const float *__restrict__ x, const float *__restrict__ xlo, in
                   const float *__restrict__ queries, int q_stride, const int32_t *__restrict__ item_query,
                   const int64_t *__restrict__ range_begin, const int64_t *__restrict__ range_end, int64_t n_items,
                   int k, int metric, float *__restrict__ part_key, int32_t *__restrict__ part_idx,
-                  uint32_t *__restrict__ qtau) {
+                  uint32_t *__restrict__ qtau, const int *gate) {
     extern __shared__ float4 smem_q4[];
+    if (gate && *gate != kScreenOverflow) return;  // a fallback pass that is not needed
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float *myq = reinterpret_cast<float *>(smem_q4) + (size_t)warp * dp;
     const float4 *myq4 = reinterpret_cast<const float4 *>(myq);
@@ -125,6 +126,18 @@ scan_items_kernel(const float *__restrict__ x, const float *__restrict__ xlo, in
         }
         list.store(lk, k, lane);
     }
+}
+
+// ---- items of the exact flat scan -------------------------------------------------------------
+__global__ void fill_chunk_items_kernel(int32_t *__restrict__ item_query, int64_t *__restrict__ range_begin,
+                                        int64_t *__restrict__ range_end, int64_t n_items, int chunks, int64_t per,
+                                        int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_items) return;
+    const int64_t q = i / chunks, c = i - q * chunks;
+    item_query[i] = (int32_t)q;
+    range_begin[i] = c * per;
+    range_end[i] = (c + 1) * per < n ? (c + 1) * per : n;
 }
 
 // ---- IVF item construction ------------------------------------------------------------------
@@ -256,7 +269,8 @@ __global__ void group_place_kernel(const int32_t *__restrict__ probes, int64_t n
 template <int KR>
 int launch_scan_kr(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
                    const int32_t *item_query, const int64_t *rb, const int64_t *re, int64_t n_items, int k,
-                   int metric, float *part_key, int32_t *part_idx, uint32_t *qtau, int device, cudaStream_t stream) {
+                   int metric, float *part_key, int32_t *part_idx, uint32_t *qtau, int device, cudaStream_t stream,
+                   const int *gate) {
     const size_t smem = (size_t)kWarps * dp * sizeof(float);
     if (smem > 48 * 1024) {
         ANN_CUDA_TRY(cudaFuncSetAttribute(scan_items_kernel<KR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -266,7 +280,7 @@ int launch_scan_kr(const float *x, const float *xlo, int dp, int d, const float 
     const int64_t cap = (int64_t)sm_count(device) * 16;
     if (blocks > cap) blocks = cap;
     scan_items_kernel<KR><<<(unsigned)blocks, kWarps * 32, smem, stream>>>(
-        x, xlo, dp, d, queries, q_stride, item_query, rb, re, n_items, k, metric, part_key, part_idx, qtau);
+        x, xlo, dp, d, queries, q_stride, item_query, rb, re, n_items, k, metric, part_key, part_idx, qtau, gate);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -277,21 +291,32 @@ int launch_scan_kr(const float *x, const float *xlo, int dp, int d, const float 
 int launch_scan_items(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
                       const int32_t *item_query, const int64_t *range_begin, const int64_t *range_end,
                       int64_t n_items, int k, int metric, float *part_key, int32_t *part_idx, uint32_t *qtau,
-                      int device, cudaStream_t stream) {
+                      int device, cudaStream_t stream, const int *gate) {
     if (n_items <= 0) return 0;
     if (k <= 0 || k > kMaxK) return set_error("k must be in [1, %d]", kMaxK);
     if ((size_t)kWarps * dp * sizeof(float) > 200 * 1024) return set_error("dimension %d too large for the scan kernel", d);
     if (k <= 32)
         return launch_scan_kr<1>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k,
-                                 metric, part_key, part_idx, qtau, device, stream);
+                                 metric, part_key, part_idx, qtau, device, stream, gate);
     if (k <= 128)
         return launch_scan_kr<4>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k,
-                                 metric, part_key, part_idx, qtau, device, stream);
+                                 metric, part_key, part_idx, qtau, device, stream, gate);
     if (k <= 512)
         return launch_scan_kr<16>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k,
-                                  metric, part_key, part_idx, qtau, device, stream);
+                                  metric, part_key, part_idx, qtau, device, stream, gate);
     return launch_scan_kr<64>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k, metric,
-                              part_key, part_idx, qtau, device, stream);
+                              part_key, part_idx, qtau, device, stream, gate);
+}
+
+int launch_fill_chunk_items(int32_t *item_query, int64_t *range_begin, int64_t *range_end, int64_t nq, int chunks,
+                            int64_t per, int64_t n, cudaStream_t stream) {
+    const int64_t n_items = nq * chunks;
+    if (n_items <= 0) return 0;
+    fill_chunk_items_kernel<<<(unsigned)((n_items + 255) / 256), 256, 0, stream>>>(item_query, range_begin, range_end,
+                                                                                   n_items, chunks, per, n);
+    count_launch();
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
 }
 
 int launch_build_ivf_items(const int32_t *probes, int64_t nq, int nprobe, int64_t nlist, const int64_t *list_off,

@@ -151,6 +151,14 @@ class _CudaIndex:
                                                      label_offset, C.c_void_p(s.cuda_stream)), "search_device")
         return D, I
 
+    def search_status(self, stream=None) -> None:
+        """Waits for `stream` (default: torch's current stream) and raises if a search_device call
+        made on it since the last check failed on the device."""
+        import torch
+        s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_index_search_status(self._h, C.c_void_p(s.cuda_stream)), "search_status")
+
     def reset(self) -> None:
         p = _pkg()
         p.check(p.lib().ann_cuda_index_reset(self._h), "reset")

@@ -109,10 +109,20 @@ int ann_cuda_index_search(const ann_cuda_index *index, int64_t n, const float *x
 
 /* Same with DEVICE pointers; work is enqueued on `stream` (cudaStream_t, NULL =
  * default stream) and not synchronised.  label_offset is added to every valid
- * label (row-sharded indexes pass the shard's first row). */
+ * label (row-sharded indexes pass the shard's first row).  Should a pass of the flat
+ * search find more near ties inside its error band than it kept candidates for, the
+ * next more exact pass is already enqueued behind it and runs by itself (decided on
+ * the device): when the stream reaches the end of the call the results are complete.
+ * No counterpart in the reference (its index takes host pointers only). */
 int ann_cuda_index_search_device(const ann_cuda_index *index, int64_t n, const float *x_device, int64_t k,
                                  float *distances_device, int64_t *labels_device, int64_t label_offset,
                                  void *stream);
+
+/* Waits for `stream` and reports on the ann_cuda_index_search_device calls made on it
+ * since the last such report: 0 = fine; -1 = a kernel gave up on one of its bounded
+ * waits (a device in trouble), the results of those calls are not valid.  The role
+ * of the command buffer's status check, MetalIndexFlat.mm:348-351. */
+int ann_cuda_index_search_status(const ann_cuda_index *index, void *stream);
 
 /* MetalIndexFlat::searchAsync and its MetalSearchToken (MetalIndexFlat.h:15-36,
  * MetalIndexFlat.mm:371-443): the search is enqueued and the call returns; `x` may be reused
@@ -163,6 +173,13 @@ void ann_cuda_index_free(ann_cuda_index *index);
 int ann_cuda_flat_search_small_static(const ann_cuda_index *index, int64_t n, const float *x_device, int64_t k,
                                       float *distances_device, int64_t *labels_device, int64_t label_offset,
                                       void *stream);
+/* Waits for `stream` and reports on the allocation-free searches run on `device` since
+ * the last report: 0 = fine; 1 = some query had more near ties around its k-th place
+ * than the 16 candidates this entry point keeps can settle (its result may differ from
+ * the regular search inside that tie; repeat it with a regular entry point);
+ * -1 = a kernel gave up on a bounded wait, results are not valid.  Allocates nothing.
+ * No counterpart in the reference. */
+int ann_cuda_flat_search_small_static_status(int device, void *stream);
 
 /* ---- multi-GPU merge -------------------------------------------------------------
  * Final k-select over per-shard results.  parts_*: (nparts x nq x k) in DEVICE
@@ -179,21 +196,32 @@ int ann_cuda_merge_topk_device(int device, const float *parts_distances, const i
 const char *ann_cuda_flat_kernel_name(void);
 /* Overrides that choice for the whole process; used by the tests to cross-check one
  * kernel against the other.  "tcgen05": tensor-core kernel; flat stores of two
- * million rows or more are searched with one-MMA screening (candidates chosen by
- * q_hi.x_hi keys under a proven error slack, then re-ranked in exact fp32), smaller
- * ones with the three-MMA split product.  "tcgen05-screened" / "tcgen05-split":
- * screening always / never.  "simt": the exact-fp32 cross-check kernels.
- * Screening returns exactly the split product's answer as long as fewer than 256 - k
- * rows lie within its error band (about 0.2 % of |q||x|max) above the k-th best; the
- * library checks that for every query.  ann_cuda_index_search then repeats the
- * block with the split product by itself; ann_cuda_index_search_device, which
- * returns before the search has run, reports it as an error of the NEXT call on
- * that stream. */
+ * million rows or more are searched with one-MMA screening (256 candidates chosen by
+ * q_hi.x_hi keys under a proven error slack), smaller ones with the three-MMA split
+ * product (k + 32 candidates); either way the candidates are re-ranked in exact fp32.
+ * "tcgen05-screened" / "tcgen05-split": screening always / never.  "simt": the
+ * exact-fp32 scan only.  Each tensor-core pass checks, for every query, that its last
+ * candidate lies outside the error band above the k-th (about 0.2 % of |q||x|max for
+ * screening, 0.03 % for the split product at d = 768); otherwise the query block is
+ * searched again one tier up (screened -> split -> exact scan), by every entry point. */
 int ann_cuda_set_flat_kernel(const char *name);
 
-/* How many query blocks ann_cuda_index_search has repeated with the split product
- * because the screened search ran out of spare candidates (process-wide, since load). */
+/* How many times a pass of the flat search found more rows inside its error band than
+ * it kept candidates for, so that the query block was searched again one tier up
+ * (screened -> split product -> exact fp32 scan).  Process-wide, since load; passes
+ * repeated on the device are counted when their stream is next waited for
+ * (ann_cuda_index_search_status, ann_cuda_search_token_wait). */
 uint64_t ann_cuda_screen_fallbacks(void);
+
+/* Every wait inside the tensor-core kernel is bounded; a wait that runs out makes the
+ * search fail with an error instead of hanging.  Sets that bound (default 2000 ms;
+ * ms <= 0 restores it).  Process-wide. */
+void ann_cuda_set_wait_limit_ms(int ms);
+/* Test support: with after_k_blocks >= 0 the loader of every CTA stops after that many
+ * blocks of the dimension, the kernel's waits run out and the search FAILS with the
+ * give-up error (it never returns partial results as success); -1 = off (default).
+ * Lets a test exercise the give-up path without a fault. */
+void ann_cuda_test_withhold_loads(int after_k_blocks);
 
 /* Measurement hook.  With timing on, every search records CUDA events around
  * its flat-search kernel on the stream the kernel is launched on;

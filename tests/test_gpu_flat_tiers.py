@@ -1,0 +1,186 @@
+"""The three tiers of the flat search (one-MMA screening -> three-MMA split product -> exact fp32
+scan) and what moves a query block from one to the next, through every entry point of the C ABI.
+
+The acceptance rule is the one of the other parity tests: distances within 1e-4 relative of the
+CPU oracle, identical id sets except for tolerance ties at the k-th place
+(faiss-metal/tests/test_metal_flat.mm:25-60 is the reference's own, looser, form of it)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from parity import assert_topk_matches
+
+pytestmark = pytest.mark.gpu
+
+
+def _metric(pkg, name):
+    return pkg.METRIC_L2 if name == "L2" else pkg.METRIC_INNER_PRODUCT
+
+
+def _near_tie_store(rng, d, n_far, n_near, metric_name, step):
+    """`n_near` rows whose distance to the query q grows by `step` from one to the next, among
+    `n_far` Gaussian rows that are all much farther away."""
+    q = rng.standard_normal(d)
+    q /= np.linalg.norm(q)
+    u = rng.standard_normal((n_near, d))
+    u /= np.linalg.norm(u, axis=1, keepdims=True)
+    far = rng.standard_normal((n_far, d)).astype(np.float32)
+    if metric_name == "L2":
+        near = q[None, :] + np.sqrt(0.5 + step * np.arange(n_near))[:, None] * u
+    else:
+        r = u - (u @ q)[:, None] * q[None, :]
+        near = (50.0 - 2 * step * np.arange(n_near))[:, None] * q[None, :] + 0.1 * r
+    xb = np.concatenate([far, near.astype(np.float32)])
+    xb = xb[np.random.default_rng(3).permutation(len(xb))]
+    return xb, q[None, :].astype(np.float32)
+
+
+def test_tight_clusters_far_from_the_origin(pkg, oracle):
+    """The flat twin of the IVF test of the same name: neighbour distances ~1e-4 of the operands'
+    squared norms, so that split-product keys alone cannot rank the neighbours.  The band check
+    has to notice and the exact tier has to answer."""
+    rng = np.random.default_rng(11)
+    nc, d = 32, 96
+    centers = (rng.standard_normal((nc, d)) * 3 + 2).astype(np.float32)
+    xb = (centers[rng.integers(0, nc, 8000)] + 0.05 * rng.standard_normal((8000, d))).astype(np.float32)
+    xq = (centers[rng.integers(0, nc, 150)] + 0.05 * rng.standard_normal((150, d))).astype(np.float32)
+    xq[:20] = xb[rng.integers(0, len(xb), 20)]
+    xq[20:40] = xb[rng.integers(0, len(xb), 20)] + np.float32(1e-3)
+    for kernel in ("tcgen05", "tcgen05-screened", "tcgen05-split"):
+        assert pkg.lib().ann_cuda_set_flat_kernel(kernel.encode()) == 0
+        try:
+            for metric_name in ("L2", "IP"):
+                m = _metric(pkg, metric_name)
+                idx = pkg.CudaIndexFlat(d, m)
+                idx.add(xb)
+                for k in (5, 20, 300):
+                    D, I = idx.search(xq, k)
+                    Dref, Iref = oracle.flat_search(xb, xq, k, m)
+                    assert_topk_matches(oracle, xb, xq, m, D, I, Dref, Iref, f"tight clusters {kernel} {metric_name} k={k}")
+                if metric_name == "L2":
+                    assert (D[:20, 0] == 0.0).all()
+                idx.close()
+        finally:
+            pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05")
+
+
+def test_near_ties_far_denser_than_the_split_product_resolves(pkg, oracle):
+    """200 rows whose distances to the query differ by 1e-7 of |q||x|max each: the split product's
+    band check must flag it (more than 32 of them sit inside its band) and the exact scan settles
+    the order.  The counter shows that the fallback really ran."""
+    rng = np.random.default_rng(23)
+    for metric_name in ("L2", "IP"):
+        xb, xq = _near_tie_store(rng, 64, 20000, 200, metric_name, 1e-6)
+        m = _metric(pkg, metric_name)
+        idx = pkg.CudaIndexFlat(64, m)
+        idx.add(xb)
+        before = pkg.lib().ann_cuda_screen_fallbacks()
+        for k in (8, 40):
+            D, I = idx.search(xq, k)
+            Dref, Iref = oracle.flat_search(xb, xq, k, m)
+            assert_topk_matches(oracle, xb, xq, m, D, I, Dref, Iref, f"dense ties {metric_name} k={k}")
+        assert pkg.lib().ann_cuda_screen_fallbacks() >= before + 2, "the split product's band overflow went unnoticed"
+        idx.close()
+
+
+@pytest.mark.parametrize("entry", ["device", "async"])
+def test_fallback_passes_run_on_the_device_for_the_entries_that_do_not_wait(pkg, oracle, entry):
+    """search_device and search_async return before anything has run: the higher tiers are enqueued
+    behind the first, gated by its band check.  More than two query blocks (16384 queries each),
+    with the near ties that overflow the screened tier visible to the queries of block 0 only -
+    a clean later block must not hide what an earlier one needed."""
+    import torch
+    rng = np.random.default_rng(31)
+    d, k = 32, 20
+    xb, q0 = _near_tie_store(rng, d, 6000, 600, "L2", 1e-4)
+    nq = 2 * 16384 + 100
+    xq = (rng.standard_normal((nq, d)) * 4).astype(np.float32)      # far from the tie cluster: clean blocks
+    xq[:3] = q0
+    assert pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05-screened") == 0
+    try:
+        idx = pkg.CudaIndexFlat(d, pkg.METRIC_L2)
+        idx.add(xb)
+        before = pkg.lib().ann_cuda_screen_fallbacks()
+        if entry == "device":
+            Dd, Id = idx.search_device(torch.from_numpy(xq).cuda(), k)
+            idx.search_status()                                       # waits; raises on a device-side failure
+            D, I = Dd.cpu().numpy(), Id.cpu().numpy()
+        else:
+            D, I = idx.search_async(xq, k).wait()
+        assert pkg.lib().ann_cuda_screen_fallbacks() >= before + 1, "no fallback pass ran"
+        sample = np.concatenate([np.arange(0, 40), np.arange(16384 - 5, 16384 + 5), np.arange(nq - 20, nq)])
+        Dref, Iref = oracle.flat_search(xb, xq[sample], k, oracle.METRIC_L2)
+        assert_topk_matches(oracle, xb, xq[sample], oracle.METRIC_L2, D[sample], I[sample], Dref, Iref, f"gated tiers ({entry})")
+        # the synchronous entry point repeats on the host instead and must give the same answer
+        Ds, Is = idx.search(xq[sample], k)
+        np.testing.assert_array_equal(Is, I[sample])
+        np.testing.assert_array_equal(Ds, D[sample])
+        idx.close()
+    finally:
+        pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05")
+
+
+@pytest.mark.parametrize("k", [130, 200, 256, 1024, 2048])
+def test_large_k(pkg, oracle, k):
+    """k beyond the shared-memory and one-MMA modes: append-and-compact lists up to 256 entries,
+    replace-max lists up to the limit of 2048 (the reference's block select takes k up to 4096 on
+    its newest GPUs, faiss-metal/src/MetalSelect.mm:53-56), screened search up to k = 224."""
+    rng = np.random.default_rng(k)
+    nv, nq, d = 9000, 130, 40
+    xb = rng.uniform(-1, 1, (nv, d)).astype(np.float32)
+    xq = rng.uniform(-1, 1, (nq, d)).astype(np.float32)
+    for kernel in ("tcgen05", "tcgen05-screened"):
+        assert pkg.lib().ann_cuda_set_flat_kernel(kernel.encode()) == 0
+        try:
+            for metric_name in ("L2", "IP"):
+                m = _metric(pkg, metric_name)
+                idx = pkg.CudaIndexFlat(d, m)
+                idx.add(xb)
+                D, I = idx.search(xq, k)
+                Dref, Iref = oracle.flat_search(xb, xq, k, m)
+                assert_topk_matches(oracle, xb, xq, m, D, I, Dref, Iref, f"{kernel} {metric_name} k={k}")
+                idx.close()
+        finally:
+            pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05")
+    idx = pkg.CudaIndexFlat(d, pkg.METRIC_L2)
+    idx.add(xb)
+    with pytest.raises(pkg.AnnCudaError, match="2048"):
+        idx.search(xq, 2049)
+    idx.close()
+
+
+def test_a_wait_that_runs_out_fails_the_search_and_leaves_the_device_usable(pkg, oracle):
+    """Every wait inside the tensor-core kernel is bounded.  With the bound lowered to 20 ms and the
+    loader told to stop after three blocks of the dimension, the MMA issuer waits for a stage that
+    never arrives: the kernel must give up in order, the search must FAIL (not return partial
+    lists), and the next search on the same index must work."""
+    rng = np.random.default_rng(5)
+    xb = rng.uniform(-1, 1, (20000, 128)).astype(np.float32)
+    xq = rng.uniform(-1, 1, (40, 128)).astype(np.float32)
+    lib = pkg.lib()
+    idx = pkg.CudaIndexFlat(128, pkg.METRIC_L2)
+    idx.add(xb)
+    D0, I0 = idx.search(xq, 10)
+    lib.ann_cuda_set_wait_limit_ms(20)
+    lib.ann_cuda_test_withhold_loads(3)
+    try:
+        with pytest.raises(pkg.AnnCudaError, match="gave up on a wait"):
+            idx.search(xq, 10)
+        tok = idx.search_async(xq, 10)
+        with pytest.raises(pkg.AnnCudaError, match="gave up on a wait"):
+            tok.wait()
+        import torch
+        idx.search_device(torch.from_numpy(xq).cuda(), 10)
+        with pytest.raises(pkg.AnnCudaError, match="gave up on a wait"):
+            idx.search_status()
+        idx.search_status()          # collected: the stream's record is clean again
+    finally:
+        lib.ann_cuda_test_withhold_loads(-1)
+        lib.ann_cuda_set_wait_limit_ms(0)
+    D1, I1 = idx.search(xq, 10)
+    np.testing.assert_array_equal(I1, I0)
+    np.testing.assert_array_equal(D1, D0)
+    Dref, Iref = oracle.flat_search(xb, xq, 10, oracle.METRIC_L2)
+    assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D1, I1, Dref, Iref, "after a failed search")
+    idx.close()

@@ -256,3 +256,22 @@ def test_list_sharding_matches_unsharded(pkg, oracle):
     np.testing.assert_allclose(D.cpu().numpy(), Dref, rtol=1e-4)
     for s in shards:
         s.close()
+
+
+@pytest.mark.parametrize("k,nprobe", [(100, 256), (10, 256), (300, 64), (2048, 4)])
+def test_any_nprobe_and_k(pkg, oracle, k, nprobe):
+    """The reference scans whatever nprobe <= nlist asks for (faiss-metal/src/MetalIndexIVFFlat.mm:122-256,
+    275-279).  nprobe = nlist = 256 with k = 100 is 27,648 candidates per query; the per-query merge
+    streams them, so no product of nprobe and k is too large.  All three selection modes of the scan."""
+    rng = np.random.default_rng(k + nprobe)
+    xb = rng.standard_normal((20000, 32)).astype(np.float32)
+    xq = rng.standard_normal((40, 32)).astype(np.float32)
+    idx, cent, off, rows = _build(pkg, oracle, xb, 256, pkg.METRIC_L2, seed=3)
+    _check(pkg, oracle, idx, xb, cent, off, rows, xq, k, nprobe, pkg.METRIC_L2, f"k={k} nprobe={nprobe}")
+    if nprobe == 256:   # every list probed: the flat answer
+        D, I = idx.search(xq, k)
+        Dref, Iref = oracle.flat_search(xb, xq, k, oracle.METRIC_L2)
+        assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D, I, Dref, Iref, "nprobe = nlist equals flat")
+    with pytest.raises(pkg.AnnCudaError, match="2048"):
+        idx.search(xq, 2049)     # an error, as for Flat, not a silently shortened result
+    idx.close()

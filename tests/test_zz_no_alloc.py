@@ -14,6 +14,8 @@ import ctypes as C
 import numpy as np
 import pytest
 
+from parity import assert_topk_matches
+
 pytestmark = pytest.mark.gpu
 
 
@@ -22,7 +24,7 @@ def _free_bytes(torch):
     return free
 
 
-def test_static_scratch_search_matches_regular_search_twice_in_a_row(pkg):
+def test_static_scratch_search_matches_regular_search_twice_in_a_row(pkg, oracle):
     import torch
     rng = np.random.default_rng(77)
     d, nv = 96, 30000
@@ -60,6 +62,11 @@ def test_static_scratch_search_matches_regular_search_twice_in_a_row(pkg):
         torch.cuda.synchronize()
         assert (I.cpu().numpy() == Iw).all()
         np.testing.assert_allclose(D.cpu().numpy(), Dw, rtol=1e-4, atol=0)  # the tolerance of the parity tests
+        # ... and against the CPU oracle, like every other search path
+        Dref, Iref = oracle.flat_search(xb, x.cpu().numpy(), k, oracle.METRIC_L2)
+        assert_topk_matches(oracle, xb, x.cpu().numpy(), oracle.METRIC_L2, D.cpu().numpy(), I.cpu().numpy(), Dref, Iref,
+                            "allocation-free search")
+    assert lib.ann_cuda_flat_search_small_static_status(0, C.c_void_p(stream.cuda_stream)) == 0, pkg.last_error()
     assert _free_bytes(torch) == free_before, "the allocation-free entry point changed the amount of free device memory"
     idx.close()
 
