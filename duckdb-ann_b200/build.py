@@ -1,10 +1,15 @@
 """Builds the CUDA library in-tree with nvcc for sm_100a (and nothing else).
 
-    python duckdb-ann_b200/build.py        # or: __graft_entry__.build()
+    python duckdb-ann_b200/build.py            # or: __graft_entry__.build()
+    python duckdb-ann_b200/build.py --measure  # profiling build, see below
 
 Outputs, beside the sources (git-ignored, but they travel with the working tree):
     duckdb-ann_b200/libann_cuda.so        the search library (C ABI of include/*.h)
     duckdb-ann_b200/backend_driver        C++ driver that exercises the GpuBackend classes
+    duckdb-ann_b200/libann_cuda_measure.so  (--measure only) the same library compiled with
+        -DANN_CUDA_MEASURE: the flat kernel then carries its cycle counters and stage switches
+        (environment variables ANN_CUDA_TC_STATS, ANN_CUDA_TC_DEBUG).  The product library has
+        none of that code; load the profiling build with ANN_CUDA_LIB=<path>.
 """
 from __future__ import annotations
 
@@ -43,7 +48,11 @@ def _newer(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, measure: bool = False) -> str:
+    global OBJ, LIB
+    if measure:
+        OBJ = os.path.join(HERE, "build_measure")
+        LIB = os.path.join(HERE, "libann_cuda_measure.so")
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".hpp"))]
     headers.append(os.path.join(CSRC, "flat_tc.cu"))  # flat_tc_bk32.cu includes it
@@ -57,7 +66,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         o = os.path.join(OBJ, src.replace(".cu", ".o"))
         objs.append(o)
         if force or _newer(o, [s] + headers):
-            cmd = [nvcc()] + ARCH + COMMON + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            cmd = ([nvcc()] + ARCH + COMMON + (["-DANN_CUDA_MEASURE"] if measure else []) +
+                   (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o])
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for src, p in procs:
@@ -72,7 +82,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if force or _newer(LIB, objs):
         subprocess.check_call([nvcc()] + ARCH + ["-shared", "-o", LIB] + objs + ["-ccbin", "/usr/bin/g++", "-lcudart"])
     drv_src = os.path.join(CSRC, "backend_driver.cpp")
-    if force or _newer(DRIVER, [drv_src, LIB] + headers):
+    if not measure and (force or _newer(DRIVER, [drv_src, LIB] + headers)):
         subprocess.check_call(["/usr/bin/g++", "-O2", "-std=c++17", "-DFAISS_AVAILABLE", "-DFAISS_CUDA_ENABLED",
                                "-I", INCLUDE, "-I", CSRC, drv_src, "-o", DRIVER, "-L", HERE, "-lann_cuda",
                                "-Wl,-rpath,$ORIGIN"])
@@ -80,4 +90,4 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, measure="--measure" in sys.argv))

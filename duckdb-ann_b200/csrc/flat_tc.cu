@@ -316,8 +316,9 @@ struct KernelArgs {
     // K + E', and a row can be among the k_rank best only if its coarse key is <= K + 2E'.  The
     // lists therefore keep k > k_rank entries, the threshold is the k_rank-th key + 2E', and the
     // caller re-ranks the k candidates it gets back by their exact fp32 distance.
-    int screen;
-    int k_rank;                   // = k when not screening
+    int screen;                   // one-MMA keys
+    int banded;                   // lists pruned by the k_rank-th key + slack (screen implies banded)
+    int k_rank;                   // = k when not banded
     const float *q_norm2;         // per query |q - mu|^2 (L2, mu = the store's reference point) or |q|^2 (IP)
     const unsigned *x_max_norm2;  // bits of the largest |x|^2 in the store
     int d;
@@ -416,11 +417,14 @@ __device__ __forceinline__ void warp_sort(uint32_t (&key)[E], int32_t (&idx)[E],
     }
 }
 
-// Sorts the first 32 * E slots of one row's append buffer (c <= 32 * E of them filled), writes
-// the best k back in order (index -1 past the end) and returns the k_rank-th best key (k_rank <= k;
-// meaningful only if c >= k_rank).
+// Sorts the first 32 * E slots of one row's append buffer (c <= 32 * E of them filled) and writes
+// back, in order, those of the best k that lie within `slack` of the k_rank-th best key (nothing
+// above that can reach the final top k_rank; index -1 in the slots up to k that stay empty).
+// Returns the k_rank-th best key (k_rank <= k; meaningful only if c >= k_rank) and, in `kept`,
+// how many entries the row keeps.
 template <int E>
-__device__ __forceinline__ float compact_one(float *bk, int32_t *bi, int c, int k, int k_rank, int lane) {
+__device__ __forceinline__ float compact_one(float *bk, int32_t *bi, int c, int k, int k_rank, float slack, int lane,
+                                             int &kept) {
     uint32_t key[E];
     int32_t idx[E];
     if (E >= 4) {
@@ -448,17 +452,24 @@ __device__ __forceinline__ float compact_one(float *bk, int32_t *bi, int c, int 
     warp_sort<E>(key, idx, lane);
     float kth = kInf;
 #pragma unroll
+    for (int i = 0; i < E; i++) kth = (lane * E + i == k_rank - 1) ? ordered_to_float(key[i]) : kth;
+    kth = 32 * E < k_rank ? kInf : __shfl_sync(kFullMask, kth, (k_rank - 1) / E);
+    // fewer than k_rank entries (their tail sorts as +inf): no threshold yet, everything stays
+    const float cut = (c >= k_rank) ? kth + slack : kInf;
+    int mine = 0;
+#pragma unroll
     for (int i = 0; i < E; i++) {
         const int e = lane * E + i;
         const float kf = ordered_to_float(key[i]);
+        const bool keep = e < k && idx[i] >= 0 && kf <= cut;
         st_global_if(e < k, bk + e, kf);
-        st_global_if(e < k, bi + e, idx[i]);
-        kth = (e == k_rank - 1) ? kf : kth;
+        st_global_if(e < k, bi + e, keep ? idx[i] : -1);
+        mine += keep ? 1 : 0;
     }
     if (32 * E < k)  // the sorted part is shorter than the list: mark the rest empty
         for (int e = 32 * E + lane; e < k; e += 32) bi[e] = -1;
-    if (32 * E < k_rank) return kInf;
-    return __shfl_sync(kFullMask, kth, (k_rank - 1) / E);
+    kept = __reduce_add_sync(kFullMask, mine);
+    return kth;
 }
 
 // Compacts the append buffers of the rows in `need` (bit r = row row0 + r of this warp) down to
@@ -476,13 +487,14 @@ __device__ __noinline__ void compact_rows(float *slot_key, int32_t *slot_idx, in
         float *bk = slot_key + (size_t)(row0 + r) * kBuf;
         int32_t *bi = slot_idx + (size_t)(row0 + r) * kBuf;
         float kth;
-        if (c > 256) kth = compact_one<16>(bk, bi, c, k, k_rank, lane);
-        else if (c > 128) kth = compact_one<8>(bk, bi, c, k, k_rank, lane);
-        else if (c > 64) kth = compact_one<4>(bk, bi, c, k, k_rank, lane);
-        else if (c > 32) kth = compact_one<2>(bk, bi, c, k, k_rank, lane);
-        else kth = compact_one<1>(bk, bi, c, k, k_rank, lane);
+        int kept;
+        if (c > 256) kth = compact_one<16>(bk, bi, c, k, k_rank, slack, lane, kept);
+        else if (c > 128) kth = compact_one<8>(bk, bi, c, k, k_rank, slack, lane, kept);
+        else if (c > 64) kth = compact_one<4>(bk, bi, c, k, k_rank, slack, lane, kept);
+        else if (c > 32) kth = compact_one<2>(bk, bi, c, k, k_rank, slack, lane, kept);
+        else kth = compact_one<1>(bk, bi, c, k, k_rank, slack, lane, kept);
         if (lane == r) {
-            cnt = c < k ? c : k;
+            cnt = kept;
             if (c >= k_rank) {
                 // the k_rank-th best key so far (plus this row's error slack when the keys are
                 // coarse): nothing above it can reach the final top k_rank
@@ -809,7 +821,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
         const int stride = APPEND ? kBuf : k;  // slots per row in the list memory
         int cur_slot = 0;
         float slack = 0.f;  // screened mode: twice the error bound of this row's coarse keys
-        const int k_rank = (APPEND && args.screen) ? args.k_rank : k;
+        const int k_rank = (APPEND && args.banded) ? args.k_rank : k;
         auto close_list = [&]() {
             if (!unit_key) return;
             if (APPEND && args.part_cnt) {
@@ -861,9 +873,9 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 } else {
                     row_valid = (int64_t)qt * BM + row < args.nq;
                     qtau_word = args.qtau + (size_t)qt * BM + row;
-                    if (APPEND && args.screen && row_valid) {
-                        slack = screen_slack(args.q_norm2[(size_t)qt * BM + row], __uint_as_float(*args.x_max_norm2), args.d,
-                                             args.l2 != 0);
+                    if (APPEND && args.banded && row_valid) {
+                        slack = key_slack(args.q_norm2[(size_t)qt * BM + row], __uint_as_float(*args.x_max_norm2), args.d,
+                                          args.l2 != 0, args.screen != 0);
                     }
                 }
                 tau = row_valid ? kInf : -kInf;
@@ -1210,8 +1222,9 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     static_assert(kMaxListK <= 66 * 32, "the widest replace-max list covers every list length");
     if (k <= 0 || k > kMaxListK) return set_error("k must be in [1, %d]", kMaxListK);
 #ifndef ANN_TC_VARIANT_BK32
-    // the screened search runs in the build of this file with K blocks of 32 floats
-    if (screen && !grouped && screen->k_rank >= 1 && screen->k_rank <= k && k <= kScreenMaxList && dp % 32 == 0)
+    // the screened (one-MMA) search runs in the build of this file with K blocks of 32 floats
+    if (screen && screen->one_mma && !grouped && screen->k_rank >= 1 && screen->k_rank <= k && k <= kScreenMaxList &&
+        dp % 32 == 0)
         return launch_flat_tc_bk32(plan, xhi, xlo, xnorm, n, qhi, qlo, nq, dp, k, metric, part_key, part_idx, qtau, sched,
                                    status, device, stream, grouped, screen, gate);
 #endif
@@ -1249,14 +1262,16 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     a.qrow_query = grouped ? grouped->qrow_query : nullptr;
     a.qrow_const = grouped ? grouped->qrow_const : nullptr;
     a.part_cnt = grouped ? grouped->part_cnt : nullptr;
-    const bool use_screen = screen && !grouped && screen->k_rank >= 1 && screen->k_rank <= k && k <= kScreenMaxList;
+    const bool use_band = screen && !grouped && screen->k_rank >= 1 && screen->k_rank <= k && k <= kScreenMaxList;
+    const bool use_screen = use_band && screen->one_mma;
     a.screen = use_screen ? 1 : 0;
+    a.banded = use_band ? 1 : 0;
     // the static schedule parks and resumes append buffers; it pays for the screened search only
     a.static_g = use_screen ? plan.static_g : 0;
-    a.k_rank = use_screen ? screen->k_rank : k;
-    a.q_norm2 = use_screen ? screen->q_norm2 : nullptr;
-    a.x_max_norm2 = use_screen ? screen->x_max_norm2 : nullptr;
-    a.d = use_screen ? screen->d : dp;
+    a.k_rank = use_band ? screen->k_rank : k;
+    a.q_norm2 = use_band ? screen->q_norm2 : nullptr;
+    a.x_max_norm2 = use_band ? screen->x_max_norm2 : nullptr;
+    a.d = use_band ? screen->d : dp;
     a.wait_ns = flat_wait_limit_ns();
     a.withhold_after = flat_test_withhold_after();
     a.gate = gate;
@@ -1276,7 +1291,7 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
 #endif
     int rc;
     if (k <= kQueueDepth) rc = launch_variant<1, kSelSmem>(plan, maps, a, stream);
-    else if (k <= kAppendMaxK || use_screen) rc = launch_variant<1, kSelAppend>(plan, maps, a, stream);
+    else if (k <= kAppendMaxK || use_band) rc = launch_variant<1, kSelAppend>(plan, maps, a, stream);
     else if (k <= 17 * 32) rc = launch_variant<17, kSelReplace>(plan, maps, a, stream);
     else if (k <= 33 * 32) rc = launch_variant<33, kSelReplace>(plan, maps, a, stream);
     else rc = launch_variant<66, kSelReplace>(plan, maps, a, stream);

@@ -126,7 +126,9 @@ struct SplitStore {
 };
 
 constexpr int kStatusWords = 8;
-constexpr int kStatusWait = 0, kStatusTier0 = 1, kStatusFallbacks = 4;
+constexpr int kTiers = 4;
+constexpr int kStatusWait = 0, kStatusTier0 = 1, kStatusFallbacks = kStatusTier0 + kTiers;
+static_assert(kStatusFallbacks < kStatusWords, "status words");
 
 struct Workspace {
     cudaStream_t own_stream = nullptr;
@@ -135,9 +137,9 @@ struct Workspace {
     GrowBuf item_q, item_rb, item_re, item_slot, scratch, probes_key, probes, qtau, sched, gq, items, qconst, part_cnt;
     // Status words (device: `status`, pinned host copy: `status_host`), kStatusWords ints:
     //   [0]      first give-up code of a bounded wait inside a kernel; sticky for one API call
-    //   [1 + t]  tier t of the flat search (0 screened, 1 split product, 2 exact) found more rows
-    //            inside its error band than it kept candidates for: kScreenOverflow; per query block
-    //   [4]      how often a tier flagged such an overflow during the API call
+    //   [1 + t]  tier t of the flat search (see kTierScreen ...) found more rows inside its error band
+    //            than it kept candidates for: kScreenOverflow; per query block
+    //   [5]      how often a tier flagged such an overflow during the API call
     int *status_host = nullptr;  // pinned
     int fallbacks_seen = 0;      // part of status_host[4] already added to the process-wide counter
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;  // bracket the flat kernel when timing is on
@@ -341,8 +343,9 @@ void ws_absorb_fallbacks(Workspace &ws) {
 
 // ---- top-k over a split store (flat database, or IVF centroids) ---------------------------------
 struct TopkOpts {
-    int k_rank = 0;      // > 0: screened search - the kernel forms one-MMA keys and keeps the k candidates
-                         // around rank k_rank that its error slack cannot rule out (see ScreenInput)
+    int k_rank = 0;      // > 0: banded lists - the kernel keeps the (at most k) candidates that the error slack
+                         // of its keys cannot rule out of the best k_rank (see ScreenInput)
+    bool one_mma = false;  // with k_rank: one-MMA keys (screened search); else the split product
     int check_rank = 0;  // > 0: band check - is the last of the k candidates beyond the slack above the
                          // check_rank-th?  If not, status word kStatusTier0 + tier becomes kScreenOverflow
     int tier = 0;
@@ -363,9 +366,9 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         if (launch_split_rows(x_dev, nq, d, dp, ws.qhi.as<float>(), ws.qlo.as<float>(), ws.qn.as<float>(), stream,
                               st.center(), true))
             return -1;
-        const FlatPlan plan = o.k_rank > 0 ? make_flat_plan_screened(nq, st.n, k, sm_count(ix.device))
-                                           : make_flat_plan(nq, st.n, k, sm_count(ix.device));
-        const ScreenInput screen{o.k_rank, ws.qn.as<float>(), st.max_norm2, d};
+        const FlatPlan plan = o.k_rank > 0 && o.one_mma ? make_flat_plan_screened(nq, st.n, k, sm_count(ix.device))
+                                                        : make_flat_plan(nq, st.n, k, sm_count(ix.device));
+        const ScreenInput screen{o.k_rank, ws.qn.as<float>(), st.max_norm2, d, o.one_mma};
         const size_t qtau_bytes = (size_t)plan.nq_tiles * 128 * 4, sched_bytes = plan.sched_ints * 4;
         if (ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4) ||
             ws.qtau.ensure(qtau_bytes) || ws.sched.ensure(sched_bytes))
@@ -400,7 +403,8 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         // (a list that holds every row of the store has left nothing out)
         if (o.check_rank > 0 && k < st.n &&
             launch_screen_check(ws.sel_key.as<float>(), nq, k, o.check_rank, ws.qn.as<float>(), st.max_norm2, d, ix.metric,
-                                o.k_rank > 0, status + kStatusTier0 + o.tier, status + kStatusFallbacks, stream, o.gate))
+                                o.k_rank > 0 && o.one_mma, status + kStatusTier0 + o.tier, status + kStatusFallbacks, stream,
+                                o.gate))
             return -1;
         return ws_publish_status(ws, stream);
     }
@@ -679,53 +683,67 @@ int ensure_device(const ann_cuda_index *ix, DeviceGuard &g) {
 }
 
 // ---- flat search: tiers ---------------------------------------------------------------------------
-// A flat search runs in up to three tiers, each exact within its own proof:
-//   0  screened       one-MMA keys, kScreenMaxList candidates kept under the one-MMA error slack;
-//   1  split product  three-MMA keys, k + kSplitSpare candidates (16 for k <= 12);
-//   2  exact          direct-form fp32 scan (scan_items_kernel), no tensor cores.
-// Tiers 0 and 1 end with the band check of key_slack: if the last candidate of some query is still
+// A flat search runs in up to four tiers, each exact within its own proof:
+//   0  screened    one-MMA keys; lists of up to kScreenMaxList candidates pruned by the k-th key plus
+//                  the one-MMA error slack (stores of kScreenMinRows rows and more, k <= kScreenMaxK);
+//   1  split       three-MMA keys.  k <= 12: the 16 best in shared memory.  k <= kScreenMaxK: the same
+//                  banded lists of up to kScreenMaxList candidates, under the much smaller slack of the
+//                  split product.  Larger k: the k + kSplitSpare best;
+//   2  split-wide  (only after a 16-list of tier 1) banded lists of tier 1's second form;
+//   3  exact       direct-form fp32 scan (scan_items_kernel), no tensor cores.
+// Tiers 0-2 end with the band check of key_slack: if the last candidate of some query is still
 // within the slack above the k-th, rows that belong among the exact k best may be missing and the
 // tier's overflow word is set; the block is then searched again one tier up.  All tiers re-rank
 // their candidates by the exact fp32 distance, so the answer never depends on the tier.
-enum { kTierScreen = 0, kTierSplit = 1, kTierExact = 2 };
+enum { kTierScreen = 0, kTierSplit = 1, kTierSplitWide = 2, kTierExact = 3 };
+static_assert(kTierExact == kTiers - 1, "tier count");
+
+bool banded_lists_fit(const ann_cuda_index &ix, int k_sel) {
+    return k_sel <= kScreenMaxK && ix.store.max_norm2 && std::min<int64_t>(kScreenMaxList, ix.store.n) > k_sel;
+}
 
 int flat_first_tier(const ann_cuda_index &ix, int k_sel) {
     if (flat_kernel_choice() != FlatKernel::TC) return kTierExact;
     // (ANN_CUDA_FLAT_SCREEN=0 turns screening off, =1 applies it to stores of any size)
     const int screen_env = g_flat_screen.load(std::memory_order_relaxed);
-    if (k_sel <= kScreenMaxK && ix.store.max_norm2 && std::min<int64_t>(kScreenMaxList, ix.store.n) > k_sel &&
-        (screen_env == 1 || (screen_env != 0 && ix.store.n >= kScreenMinRows)))
+    if (banded_lists_fit(ix, k_sel) && (screen_env == 1 || (screen_env != 0 && ix.store.n >= kScreenMinRows)))
         return kTierScreen;
     return kTierSplit;
 }
 
-// Candidates the split-product tier selects for a search that needs k_sel results: the shared-memory
-// selection holds 16, longer lists get kSplitSpare extra.
-int split_list_len(int k_sel, int64_t n) {
-    const int64_t k_list = k_sel <= 12 ? 16 : (int64_t)k_sel + kSplitSpare;
-    return (int)std::min<int64_t>(k_list, n);
+// The tier after `tier` for this search (tier 2 exists only behind a 16-list).
+int flat_next_tier(const ann_cuda_index &ix, int k_sel, int tier) {
+    if (tier == kTierScreen) return kTierSplit;
+    if (tier == kTierSplit && k_sel <= 12 && banded_lists_fit(ix, k_sel)) return kTierSplitWide;
+    return kTierExact;
 }
 
 int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const float *x_dev, int64_t k, float *d_dev,
                      int64_t *i_dev, int64_t label_offset, cudaStream_t stream, int tier, const int *gate) {
     const int k_sel = (int)std::min<int64_t>(k, ix.store.n);
+    const int64_t n = ix.store.n;
     TopkOpts o;
     o.tier = tier;
     o.gate = gate;
     int k_list = k_sel;
-    if (tier == kTierScreen) {
-        k_list = (int)std::min<int64_t>((int64_t)kScreenMaxList, ix.store.n);
-        o.k_rank = o.check_rank = k_sel;
-    } else if (tier == kTierSplit) {
-        k_list = split_list_len(k_sel, ix.store.n);
-        o.check_rank = k_list > k_sel ? k_sel : 0;
-    } else {
+    const bool banded = tier == kTierScreen || tier == kTierSplitWide ||
+                        (tier == kTierSplit && k_sel > 12 && banded_lists_fit(ix, k_sel));
+    if (tier == kTierExact) {
         o.exact = true;
+    } else if (banded) {
+        k_list = (int)std::min<int64_t>((int64_t)kScreenMaxList, n);
+        o.k_rank = o.check_rank = k_sel;
+        o.one_mma = tier == kTierScreen;
+    } else {
+        k_list = (int)std::min<int64_t>(k_sel <= 12 ? 16 : (int64_t)k_sel + kSplitSpare, n);
+        o.check_rank = k_list > k_sel ? k_sel : 0;
     }
     if (split_store_topk(ix, ix.store, ws, x_dev, nq, k_list, stream, o)) return -1;
+    // banded lists: only what lies within the slack of the k-th ranking key needs the exact distance
+    const RefineBand band{ws.sel_key.as<float>(), k_sel, ws.qn.as<float>(), ix.store.max_norm2, ix.d, o.one_mma};
     return launch_refine_finalize(ix.store.hi, ix.store.lo, ix.dp, ix.d, x_dev, ix.d, ws.sel_idx.as<int32_t>(), nq, k_list,
                                   (int)k, ix.metric, nullptr, label_offset, d_dev, i_dev, ix.device, stream, nullptr, nullptr,
-                                  nullptr, nullptr, gate);
+                                  nullptr, nullptr, gate, banded ? &band : nullptr);
 }
 
 // The whole search for one block of queries, all pointers on the device.
@@ -736,13 +754,15 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
                         float *d_dev, int64_t *i_dev, int64_t label_offset, cudaStream_t stream, int tier_hint,
                         bool gated) {
     if (!ix.ivf) {
-        int tier = std::max(tier_hint, flat_first_tier(ix, (int)std::min<int64_t>(k, ix.store.n)));
-        if (tier > kTierExact) tier = kTierExact;
+        const int k_sel = (int)std::min<int64_t>(k, ix.store.n);
+        int tier = flat_first_tier(ix, k_sel);
+        while (tier < tier_hint && tier < kTierExact) tier = flat_next_tier(ix, k_sel, tier);
         const int *gate = nullptr;
-        for (;; tier++) {
+        for (;;) {
             if (flat_tier_search(ix, ws, nq, x_dev, k, d_dev, i_dev, label_offset, stream, tier, gate)) return -1;
             if (!gated || tier == kTierExact) return 0;
             gate = ws.status.as<int>() + kStatusTier0 + tier;
+            tier = flat_next_tier(ix, k_sel, tier);
         }
     }
     const int nprobe = (int)std::min<int64_t>(std::max<int64_t>(ix.nprobe, 1), ix.nlist);
@@ -870,7 +890,7 @@ int search_device_impl(const ann_cuda_index &ix, Workspace &ws, int64_t n, const
         const int64_t nb = std::min(kQueryBlock, n - q0);
         // the overflow words speak of one block of queries
         if (q0 > 0 || keep_sticky)
-            ANN_CUDA_TRY(cudaMemsetAsync(ws.status.as<int>() + kStatusTier0, 0, 3 * sizeof(int), stream));
+            ANN_CUDA_TRY(cudaMemsetAsync(ws.status.as<int>() + kStatusTier0, 0, kTiers * sizeof(int), stream));
         if (search_block_device(ix, ws, nb, x_dev + q0 * ix.d, k, d_dev + q0 * k, i_dev + q0 * k, label_offset, stream,
                                 tier_hint, gated))
             return -1;
@@ -1692,7 +1712,7 @@ extern "C" int ann_cuda_flat_search_small_static(const ann_cuda_index *ix, int64
     const int k_sel = (int)std::min<int64_t>(k, ix->store.n);
     // like the regular split-product search: 16 candidates for k <= 12, so that near ties at the
     // k-th place are settled by the exact re-ranking below (k = 13..16: no spare, no band check)
-    const int k_list = split_list_len(k_sel, ix->store.n) <= kStaticMaxK ? split_list_len(k_sel, ix->store.n) : k_sel;
+    const int k_list = k_sel <= 12 ? (int)std::min<int64_t>(16, ix->store.n) : k_sel;
     const FlatPlan plan = make_flat_plan(n, ix->store.n, k_list, sm_count(ix->device));
     if (plan.list_stride > kStaticMaxK)
         return set_error("allocation-free search: lists of %d entries exceed the limit of %d", plan.list_stride, kStaticMaxK);

@@ -104,6 +104,10 @@ struct ScreenInput {
     const float *q_norm2;         // per query |q - mu|^2 (L2) or |q|^2 (IP)
     const unsigned *x_max_norm2;  // device word: bits of the largest |x|^2 in the store
     int d;                        // true dimension
+    // true: one-MMA keys (q_hi.x_hi only; the build with 32-float K blocks, static schedule on
+    // large stores).  false: the three-MMA split product with the same banded lists - the slack is
+    // then the split product's much smaller one (see key_slack).
+    bool one_mma = true;
 };
 constexpr int kScreenMaxList = 256;  // longest list (k_rank + spare) the screened mode keeps
 constexpr int kScreenMaxK = kScreenMaxList - kSplitSpare;  // largest k searched with screening
@@ -212,6 +216,18 @@ int launch_merge_filtered(const float *part_key, const int32_t *part_idx, const 
                           int64_t nq, int k, int list_stride, float *out_key, int32_t *out_idx,
                           cudaStream_t stream);
 
+// Optional input of launch_refine_finalize: the candidates were ranked by tensor-core keys
+// (key[q * k_sel + j], ascending) under the slack of key_slack; only those within the slack of the
+// rank-th key can be among the exact `rank` best, the others are not re-evaluated.
+struct RefineBand {
+    const float *key;
+    int rank;
+    const float *q_norm2;
+    const unsigned *x_max_norm2;
+    int d;
+    bool one_mma;
+};
+
 // Flat: recomputes the distance of every selected (query, row) pair in exact fp32
 // from the split store, sorts the k results best first and writes the user-facing
 // distances (squared L2 / raw dot) and int64 labels (row + label_offset, or
@@ -224,7 +240,8 @@ int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, co
                            const int32_t *sel_idx, int64_t nq, int k_sel, int k_out, int metric,
                            const int64_t *ids, int64_t label_offset, float *out_d, int64_t *out_i, int device,
                            cudaStream_t stream, const float *approx_key = nullptr, const float *rnorm = nullptr,
-                           const float *xnorm = nullptr, int32_t *out_row = nullptr, const int *gate = nullptr);
+                           const float *xnorm = nullptr, int32_t *out_row = nullptr, const int *gate = nullptr,
+                           const RefineBand *band = nullptr);
 
 // Already-exact keys: just convert to user-facing values and labels, padding to k_out.
 int launch_finalize(const float *sel_key, const int32_t *sel_idx, int64_t nq, int k_sel, int k_out, int metric,

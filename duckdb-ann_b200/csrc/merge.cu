@@ -275,19 +275,24 @@ refine_finalize_kernel(const float *__restrict__ xhi, const float *__restrict__ 
                        int k_sel, int k_out, int P, int metric, const int64_t *__restrict__ ids,
                        int64_t label_offset, const float *__restrict__ approx_key, const float *__restrict__ rnorm,
                        const float *__restrict__ xnorm, float *__restrict__ out_d, int64_t *__restrict__ out_i,
-                       int32_t *__restrict__ out_row, const int *gate) {
+                       int32_t *__restrict__ out_row, const int *gate, const RefineBand band) {
     extern __shared__ float smem_f[];
     if (gate_closed(gate)) return;
     float *keys = smem_f;
     int32_t *vals = reinterpret_cast<int32_t *>(smem_f + P);
     const int64_t q = blockIdx.x;
+    // candidates beyond the slack above the rank-th ranking key cannot be among the exact best
+    float band_cut = kInf;
+    if (band.key && band.rank <= k_sel)
+        band_cut = band.key[q * k_sel + band.rank - 1] +
+                   key_slack(band.q_norm2[q], __uint_as_float(*band.x_max_norm2), band.d, metric != 0, band.one_mma);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const bool l2 = metric != 0;
     const float *qv = queries + q * (int64_t)q_stride;
     for (int j = warp; j < P; j += nwarps) {
         float key = kInf;
         int32_t val = 0x7fffffff;
-        if (j < k_sel) {
+        if (j < k_sel && !(band.key && band.key[q * k_sel + j] > band_cut)) {
             const int32_t idx = sel_idx[q * k_sel + j];
             bool keep_approx = false;
             if (idx >= 0 && approx_key) {
@@ -488,7 +493,7 @@ int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, co
                            const int32_t *sel_idx, int64_t nq, int k_sel, int k_out, int metric,
                            const int64_t *ids, int64_t label_offset, float *out_d, int64_t *out_i, int device,
                            cudaStream_t stream, const float *approx_key, const float *rnorm, const float *xnorm,
-                           int32_t *out_row, const int *gate) {
+                           int32_t *out_row, const int *gate, const RefineBand *band) {
     (void)device;
     if (nq <= 0) return 0;
     const int P = next_pow2(k_sel < 2 ? 2 : k_sel);
@@ -496,7 +501,8 @@ int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, co
     if (opt_in_smem(refine_finalize_kernel, smem)) return -1;
     refine_finalize_kernel<<<(unsigned)nq, 128, smem, stream>>>(xhi, xlo, dp, d, queries, q_stride, sel_idx, k_sel,
                                                                 k_out, P, metric, ids, label_offset, approx_key, rnorm, xnorm,
-                                                                out_d, out_i, out_row, gate);
+                                                                out_d, out_i, out_row, gate,
+                                                                band ? *band : RefineBand{nullptr, 0, nullptr, nullptr, 0, false});
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

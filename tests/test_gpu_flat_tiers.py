@@ -66,12 +66,13 @@ def test_tight_clusters_far_from_the_origin(pkg, oracle):
 
 
 def test_near_ties_far_denser_than_the_split_product_resolves(pkg, oracle):
-    """200 rows whose distances to the query differ by 1e-7 of |q||x|max each: the split product's
-    band check must flag it (more than 32 of them sit inside its band) and the exact scan settles
-    the order.  The counter shows that the fallback really ran."""
+    """400 rows whose distances to the query differ by 1e-7 of |q||x|max each: more than the 256
+    candidates a banded list holds sit inside the split product's error band, so its band check
+    must flag it (k = 8: first the 16-list, then the banded lists; k = 40: the banded lists) and the
+    exact scan settles the order.  The counter shows that the fallbacks really ran."""
     rng = np.random.default_rng(23)
     for metric_name in ("L2", "IP"):
-        xb, xq = _near_tie_store(rng, 64, 20000, 200, metric_name, 1e-6)
+        xb, xq = _near_tie_store(rng, 64, 20000, 400, metric_name, 1e-6)
         m = _metric(pkg, metric_name)
         idx = pkg.CudaIndexFlat(64, m)
         idx.add(xb)
@@ -80,7 +81,7 @@ def test_near_ties_far_denser_than_the_split_product_resolves(pkg, oracle):
             D, I = idx.search(xq, k)
             Dref, Iref = oracle.flat_search(xb, xq, k, m)
             assert_topk_matches(oracle, xb, xq, m, D, I, Dref, Iref, f"dense ties {metric_name} k={k}")
-        assert pkg.lib().ann_cuda_screen_fallbacks() >= before + 2, "the split product's band overflow went unnoticed"
+        assert pkg.lib().ann_cuda_screen_fallbacks() == before + 3, "the split product's band overflow went unnoticed"
         idx.close()
 
 
