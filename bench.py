@@ -17,20 +17,39 @@ Workloads (synthetic, seeded; shapes of the reference configurations):
 A step is one pass of the hot path over one batch of queries.  `value` is measured with the
 inputs resident in HBM; `e2e` goes through the host-pointer C-ABI call (or, for N > 1, pinned-host
 copies around the sharded search) with the copies inside the timed region.
+
+Without --workload the line is the headline workload (flat_ip_20m) and carries a `workloads`
+object with the other configurations measured the same way in the same run (N = 1: all four;
+N > 1: ivf_1m with its lists sharded over the ranks).  Every entry has `value`, `ms_per_step`,
+`roofline`, `e2e`, `clocks`, `parity_check` and, at N = 1, `cpu_baseline`.  `parity_check` compares
+a sample of the timed output with the exact-fp32 scan kernel over the same shard(s) and with the
+CPU oracle; a mismatch makes the run fail after the line is printed.
 """
 from __future__ import annotations
 
-import argparse
-import importlib.util
-import json
 import os
-import statistics
-import subprocess
 import sys
-import threading
-import time
 
-import numpy as np
+
+def _host_cores() -> int:
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+# The CPU arm uses every host core.  torchrun exports OMP_NUM_THREADS=1 to its workers, and numpy's
+# BLAS reads the variable when it is first imported - so it is corrected here, before that import.
+if "reference" in sys.argv[1:]:
+    for _v in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_v] = str(_host_cores())
+
+import argparse  # noqa: E402
+import importlib.util  # noqa: E402
+import json  # noqa: E402
+import statistics  # noqa: E402
+import subprocess  # noqa: E402
+import threading  # noqa: E402
+import time  # noqa: E402
+
+import numpy as np  # noqa: E402
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
@@ -141,6 +160,63 @@ def unit_rows(gen_seed, rows, d, device, torch):
 
 
 # ------------------------------------------------------------------------------------------------
+# Parity of the timed output (the acceptance rule of the parity tests: distances within 1e-4
+# relative; id sets identical except for tolerance ties at the k-th place)
+# ------------------------------------------------------------------------------------------------
+RTOL = 1e-4
+
+
+def compare_topk(D, I, Dref, Iref, larger_is_better):
+    """Both (nq, k), best first.  Returns (id mismatches that are not tolerance ties, max relative
+    distance error position by position)."""
+    D, Dref = np.asarray(D, np.float64), np.asarray(Dref, np.float64)
+    mism = 0
+    for q in range(D.shape[0]):
+        got, want = set(I[q][I[q] >= 0].tolist()), set(Iref[q][Iref[q] >= 0].tolist())
+        if got == want:
+            continue
+        valid = Iref[q] >= 0
+        kth = Dref[q][valid][-1] if valid.any() else 0.0
+        band = 2 * RTOL * abs(kth) + 1e-30
+        dist_of = {int(i): float(d) for i, d in zip(I[q], D[q])}
+        dist_of.update({int(i): float(d) for i, d in zip(Iref[q], Dref[q])})
+        mism += sum(1 for i in got ^ want if abs(dist_of[i] - kth) > band)
+    fin = np.isfinite(Dref) & np.isfinite(D)
+    rel = np.abs(D - Dref)[fin] / np.maximum(np.abs(Dref)[fin], 1e-30)
+    return int(mism), float(rel.max()) if rel.size else 0.0
+
+
+def gather_and_merge(torch, dist, D, I, world, larger_is_better):
+    """Per-rank (nq, k) results of a sample -> the global top k on every rank (plain torch: this is
+    the checker, not the product's merge kernel)."""
+    if world == 1:
+        return D, I
+    gd = [torch.empty_like(D) for _ in range(world)]
+    gi = [torch.empty_like(I) for _ in range(world)]
+    dist.all_gather(gd, D.contiguous())
+    dist.all_gather(gi, I.contiguous())
+    allD, allI = torch.cat(gd, 1), torch.cat(gi, 1)
+    key = -allD if larger_is_better else allD
+    key = torch.where(allI < 0, torch.full_like(key, float("inf")), key)
+    order = torch.argsort(key, dim=1, stable=True)[:, :D.shape[1]]
+    return torch.gather(allD, 1, order), torch.gather(allI, 1, order)
+
+
+def search_sample_exact(wl, torch, dist, sample, label_offset):
+    """The sample queries through the library's exact-fp32 scan kernels (no tensor cores) over this
+    rank's shard, merged over the ranks."""
+    lib = wl.pkg.lib()
+    qs = wl.q_dev[torch.from_numpy(sample).to(wl.q_dev.device)].contiguous()
+    assert lib.ann_cuda_set_flat_kernel(b"simt") == 0
+    try:
+        Ds, Is = wl.index.search_device(qs, wl.k, label_offset=label_offset)
+        wl.index.search_status()
+    finally:
+        lib.ann_cuda_set_flat_kernel(b"tcgen05")
+    return gather_and_merge(torch, dist, Ds, Is, wl.world, wl.metric_name == "IP")
+
+
+# ------------------------------------------------------------------------------------------------
 # Workloads
 # ------------------------------------------------------------------------------------------------
 class FlatWorkload:
@@ -169,7 +245,8 @@ class FlatWorkload:
             q /= q.norm(dim=1, keepdim=True)
         else:
             q = torch.rand((self.nq, self.d), generator=g)
-        return q.contiguous().pin_memory()
+        q = q.contiguous()
+        return q.pin_memory() if torch.cuda.is_available() else q
 
     def setup(self, pkg, torch, rank, world, device):
         self.pkg = pkg
@@ -220,7 +297,8 @@ class FlatWorkload:
                 if self.n * self.d * 8 / max(world, 1) > 1e9 else "database is L2-sized (a warm-cache figure; the full-size workload is the headline)",
                 "flat_kernel": self.pkg.lib().ann_cuda_flat_kernel_name().decode() if getattr(self, "pkg", None)
                 else "cpu",
-                "search": "one-MMA screening + exact re-ranking (stores >= 2M rows, k <= 128), else three-MMA split product"}
+                "search": "one-MMA screening (stores >= 2M rows, k <= 224), else three-MMA split product; banded candidate "
+                          "lists, exact fp32 re-ranking, band check with fallback one tier up"}
 
     def roofline(self, peaks, kernel_ms):
         local_rows = self.hi - self.lo
@@ -228,7 +306,7 @@ class FlatWorkload:
         achieved = flops / (kernel_ms * 1e-3) / 1e12 if kernel_ms and kernel_ms > 0 else None
         # Stores of two million rows or more are searched with one-MMA screening (one TF32 MMA per
         # product, candidates re-ranked exactly); smaller ones with the three-MMA split product.
-        screened = local_rows >= 2_000_000 and self.k <= 128 and self.pkg.lib().ann_cuda_flat_kernel_name().decode() == "tcgen05"
+        screened = local_rows >= 2_000_000 and self.k <= 224 and self.pkg.lib().ann_cuda_flat_kernel_name().decode() == "tcgen05"
         mmas = 1 if screened else 3
         peak = peaks["bf16_tflops_sustained"] / 2.0 / mmas
         # DRAM traffic of one launch.  Screened search: ncu capture of the full-size launch (20M rows of
@@ -253,24 +331,47 @@ class FlatWorkload:
                                 " / 3 (split-TF32 issues three MMAs per product)")
                              + "; 'achieved' counts 2*Q*N*d once"}
 
-    def verify(self, torch, D, I):
-        """Size-independent properties: sorted best first, labels valid and distinct, and the
-        reported distance of a sample of (query, label) pairs equals the exact dot / L2."""
-        D, I = D.cpu().numpy(), I.cpu().numpy()
-        sgn = -1.0 if self.metric_name == "IP" else 1.0
-        assert (np.diff(sgn * D, axis=1) >= 0).all(), "results are not sorted best first"
-        assert (I >= 0).all() and (I < self.n).all()
-        assert all(len(set(r.tolist())) == len(r) for r in I[:64]), "duplicate labels"
-        q = self.q_host.numpy()
-        for qi in (0, self.nq // 2, self.nq - 1):
-            for j in (0, self.k - 1):
-                lab = int(I[qi, j])
-                if not (self.lo <= lab < self.hi):
-                    continue
-                row = self.index.reconstruct(lab - self.lo).astype(np.float64)
-                true = float(row @ q[qi].astype(np.float64)) if self.metric_name == "IP" else float(
-                    ((row - q[qi].astype(np.float64)) ** 2).sum())
-                assert abs(true - float(D[qi, j])) <= 1e-4 * abs(true) + 1e-7, (qi, j, true, float(D[qi, j]))
+    def parity_check(self, torch, dist, D, I, oracle):
+        """Size-independent properties over the whole output (sorted best first, labels valid and
+        distinct); 32 of the queries against the exact-fp32 scan kernel over the full store (all
+        shards) and, on rank 0, against the CPU oracle on a slice of the rows."""
+        Dh, Ih = D.cpu().numpy(), I.cpu().numpy()
+        ip = self.metric_name == "IP"
+        assert (np.diff((-1.0 if ip else 1.0) * Dh, axis=1) >= 0).all(), "results are not sorted best first"
+        assert (Ih >= 0).all() and (Ih < self.n).all()
+        assert all(len(set(r.tolist())) == len(r) for r in Ih[:64]), "duplicate labels"
+        sample = np.unique(np.linspace(0, self.nq - 1, 32).astype(np.int64))
+        Ds, Is = search_sample_exact(self, torch, dist, sample, self.lo)
+        mism, err = compare_topk(Dh[sample], Ih[sample], Ds.cpu().numpy(), Is.cpu().numpy(), ip)
+        res = {"queries": int(len(sample)), "id_mismatches": mism, "max_rel_err": err,
+               "against": "exact-fp32 scan kernel over the full store (ids outside a 1e-4 tolerance tie at the k-th place count as mismatches)"}
+        if oracle is not None:
+            # CPU oracle over a slice of this rank's rows: every oracle hit that beats the reported
+            # k-th distance by more than the tolerance must have been reported, at the same distance
+            rows = min(self.hi - self.lo, 200_000)
+            xb = self.index.get_rows(0, rows)
+            m = oracle.METRIC_IP if ip else oracle.METRIC_L2
+            Do, Io = oracle.flat_search(xb, self.q_host.numpy()[sample], self.k, m)
+            missing, oerr = 0, 0.0
+            for j, q in enumerate(sample):
+                kth = float(Dh[q, -1])
+                reported = {int(i): float(d) for i, d in zip(Ih[q], Dh[q])}
+                for lab, do in zip(Io[j], Do[j]):
+                    if lab < 0:
+                        continue
+                    lab = int(lab) + self.lo
+                    better = (do - kth) if ip else (kth - do)
+                    if lab in reported:
+                        oerr = max(oerr, abs(reported[lab] - do) / max(abs(do), 1e-30))
+                    elif better > 2 * RTOL * abs(kth):
+                        missing += 1
+            res.update({"oracle_rows": int(rows), "oracle_missing": missing, "oracle_max_rel_err": oerr})
+        res["ok"] = bool(mism == 0 and err <= RTOL and res.get("oracle_missing", 0) == 0
+                         and res.get("oracle_max_rel_err", 0.0) <= RTOL)
+        return res
+
+    def close(self):
+        self.index.close()
 
     # ---- CPU baseline: blocked sgemm + heap on the host cores, on a bounded sample
     def cpu_sample(self, torch, device):
@@ -413,11 +514,31 @@ class IvfWorkload:
                 "traffic_gbs": (IVF_SCAN_TRAFFIC.get((self.n, self.nq, self.world), 0) / 1e9 / secs
                                 if secs and IVF_SCAN_TRAFFIC.get((self.n, self.nq, self.world)) else None)}
 
-    def verify(self, torch, D, I):
-        D = D.cpu().numpy()
-        assert (np.diff(D, axis=1) >= 0).all()
-        I = I.cpu().numpy()
-        assert (I >= 0).all() and (I < self.n).all()
+    def parity_check(self, torch, dist, D, I, oracle):
+        """Sortedness and label range over the whole output; 32 queries against the exact-fp32 scan
+        kernel over the same probe lists (all shards) and, at one GPU, against the CPU oracle run
+        with the index's own centroids, lists and nprobe."""
+        Dh, Ih = D.cpu().numpy(), I.cpu().numpy()
+        assert (np.diff(Dh, axis=1) >= 0).all()
+        assert (Ih >= 0).all() and (Ih < self.n).all()
+        sample = np.unique(np.linspace(0, self.nq - 1, 32).astype(np.int64))
+        Ds, Is = search_sample_exact(self, torch, dist, sample, 0)
+        mism, err = compare_topk(Dh[sample], Ih[sample], Ds.cpu().numpy(), Is.cpu().numpy(), False)
+        res = {"queries": int(len(sample)), "id_mismatches": mism, "max_rel_err": err,
+               "against": "exact-fp32 scan kernel over the same probe lists"}
+        if oracle is not None and getattr(self, "_cpu_sample", None) is not None:
+            xb, cent, off, rows, _, _ = self._cpu_sample
+            Do, Io = oracle.ivf_search(xb, cent, off, rows, self.q_host.numpy()[sample], self.k, self.nprobe,
+                                       oracle.METRIC_L2)
+            omism, oerr = compare_topk(Dh[sample], Ih[sample], Do, Io, False)
+            # (a query whose nprobe-th and (nprobe+1)-th centroids tie may take either probe set)
+            res.update({"oracle_id_mismatches": omism, "oracle_max_rel_err": oerr,
+                        "oracle": "CPU oracle, same centroids, lists and nprobe"})
+        res["ok"] = bool(mism == 0 and err <= RTOL)
+        return res
+
+    def close(self):
+        self.index.close()
 
     # ---- CPU baseline: per-query list scan with a heap, OpenMP over queries, same centroids and lists
     def cpu_sample(self, torch, device):
@@ -431,7 +552,8 @@ class IvfWorkload:
             xb[ids] = vecs
             rows.append(ids)
             off[l + 1] = off[l] + len(ids)
-        return xb, cent, off, np.concatenate(rows), self.q_host.numpy()[:nq].copy(), nq
+        self._cpu_sample = (xb, cent, off, np.concatenate(rows), self.q_host.numpy()[:nq].copy(), nq)
+        return self._cpu_sample
 
     def cpu_run(self, oracle, sample):
         xb, cent, off, rows, xq, nq = sample
@@ -573,8 +695,32 @@ class BatchWorkload:
         return {"bound": "hbm", "achieved": None, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None,
                 "traffic": traffic, "kernel": "batch_distance_sq8_dp4a_kernel" if self.sq8 else "batch_distance_f32_kernel"}
 
-    def verify(self, torch, D, I):
-        assert torch.isfinite(D).all()
+    def parity_check(self, torch, dist, D, I, oracle):
+        """One batch more, of which 4,096 (query, row) pairs are checked against the CPU oracle
+        (the reference's scalar loop in double precision)."""
+        ids = self.ids[0]
+        out = self.table.batch_distances_by_id_device(self.q_dev, ids, self.qmap, 0, out=self.out)
+        torch.cuda.synchronize()
+        assert torch.isfinite(out).all()
+        res = {"pairs": 0, "max_rel_err": None, "against": "not checked (no oracle on this rank)", "ok": True}
+        if oracle is not None:
+            pick = np.unique(np.linspace(0, self.total - 1, 4096).astype(np.int64))
+            pick_t = torch.from_numpy(pick).to(ids.device)
+            rows = self.table._keepalive[ids[pick_t].long()].cpu().numpy()
+            qm = self.qmap_host[pick]
+            got = out[pick_t].cpu().numpy().astype(np.float64)
+            if self.sq8:
+                want = oracle.sq8_batch_distances_by_id(rows, self.mins_host, self.scale_host, self.q_host,
+                                                        np.arange(len(pick), dtype=np.uint32), qm, 0, exact=True)
+            else:
+                want = oracle.multi_batch_distances(self.q_host, rows, qm, 0, exact=True)
+            err = float((np.abs(got - want) / np.maximum(np.abs(want), 1e-30)).max())
+            res = {"pairs": int(len(pick)), "max_rel_err": err, "against": "CPU oracle (scalar loop, double accumulation)",
+                   "ok": bool(err <= RTOL)}
+        return res
+
+    def close(self):
+        self.table.close()
 
     # ---- CPU baseline: the reference's per-candidate loop, OpenMP over candidates, on one batch
     def cpu_sample(self, torch, device):
@@ -611,6 +757,16 @@ def make_workload(name, scale):
 
 
 # ------------------------------------------------------------------------------------------------
+def blas_threads():
+    """Threads numpy's BLAS will really use (the blocked sgemm of the flat CPU arm runs there)."""
+    try:
+        from threadpoolctl import threadpool_info
+        n = [int(i.get("num_threads", 0)) for i in threadpool_info() if i.get("user_api") == "blas"]
+        return max(n) if n else None
+    except Exception:
+        return None
+
+
 def run_reference(args, wl):
     """The reference's CPU path (oracle port: blocked sgemm + heap, all host threads) on a bounded
     sample per step.  Rank 0 only."""
@@ -618,9 +774,7 @@ def run_reference(args, wl):
     rank, local, world = dist_info(args)
     if rank != 0:
         return
-    # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every host core it can get
-    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    os.environ["OMP_NUM_THREADS"] = str(cores)
+    cores = _host_cores()
     try:
         from threadpoolctl import threadpool_limits
         threadpool_limits(limits=cores)
@@ -641,53 +795,31 @@ def run_reference(args, wl):
     for _ in range(min(args.warmup, 1)):
         wl.cpu_run(oracle, sample)
     vals, times = [], []
-    for _ in range(args.steps):
+    steps = args.steps if args.steps is not None else 5
+    for _ in range(steps):
         qps, dt, desc = wl.cpu_run(oracle, sample)
         vals.append(qps)
         times.append(dt)
     value = len(vals) / sum(1.0 / v for v in vals)
     line = {"impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
+            "steps": steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
             "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": wl.config(max(args.gpus, 1)) | {"flat_kernel": "cpu"},
             "cpu_baseline": {"value": value, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
-                             "sample": desc},
+                             "blas_threads": blas_threads(), "sample": desc},
             "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=None, help="timed steps (default 5; 100 for the batch-distance workloads)")
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="flat_ip_20m")
-    ap.add_argument("--scale", type=float, default=1.0, help="shrinks the row counts (debugging / profiling captures)")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    wl = make_workload(args.workload, args.scale)
-    if args.steps is None:
-        # a batch-distance step is ~20-40 us: the steady-state rate needs a stream of >= 100 of them
-        args.steps = 100 if isinstance(wl, BatchWorkload) and args.impl == "ours" else 5
-    if args.impl == "reference":
-        run_reference(args, wl)
-        return
+DEFAULT_STEPS = {"flat_ip_20m": 5, "flat_l2_100k": 50, "ivf_1m": 10, "batch_c2": 100, "sq8_c5": 100}
 
-    import torch
-    import torch.distributed as dist
-    rank, local, world = dist_info(args)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    pkg = load_package()
-    if not pkg.get_gpu_backend().IsAvailable():
-        raise SystemExit("no sm_100 GPU: " + pkg.get_gpu_backend().DeviceInfo())
-    peaks = measured_peaks()
-    lib = pkg.lib()
+
+def run_workload(args, name, steps, ctx, with_cpu_baseline):
+    """Sets the workload up, times `steps` steps (device-resident inputs, then end to end), checks
+    the timed output and returns the result as a dict (the JSON line of that workload)."""
+    torch, dist, pkg, lib, peaks = ctx["torch"], ctx["dist"], ctx["pkg"], ctx["lib"], ctx["peaks"]
+    rank, local, world, device = ctx["rank"], ctx["local"], ctx["world"], ctx["device"]
+    wl = make_workload(name, args.scale)
 
     t_setup = time.perf_counter()
     wl.setup(pkg, torch, rank, world, device)
@@ -717,12 +849,12 @@ def main():
     if stream_of_batches:
         # for comparison: the same batches one launch each, back to back (launch gaps included)
         ev0.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             out = wl.step()
         ev1.record()
         torch.cuda.synchronize()
-        one_per_launch_ms = ev0.elapsed_time(ev1) / args.steps
-        wl.prepare_stream_of_batches(torch, args.steps)
+        one_per_launch_ms = ev0.elapsed_time(ev1) / steps
+        wl.prepare_stream_of_batches(torch, steps)
         wl.run_stream_of_batches()  # warm
         launches0 = lib.ann_cuda_launch_count()
     barrier()
@@ -731,7 +863,7 @@ def main():
     if stream_of_batches:
         out = wl.run_stream_of_batches()
     else:
-        for _ in range(args.steps):
+        for _ in range(steps):
             out = wl.step()
     ev1.record()
     barrier()
@@ -739,25 +871,27 @@ def main():
     elapsed_ms = ev0.elapsed_time(ev1)
     launches = lib.ann_cuda_launch_count() - launches0
     clocks = sampler.stop(t_begin, t_end)
+    fallbacks0 = lib.ann_cuda_screen_fallbacks()
     if hasattr(wl, "index"):
+        wl.index.search_status()  # raises if a kernel of the timed searches gave up on a wait
         ms = lib.ann_cuda_index_last_flat_kernel_ms(wl.index._h)
         if ms > 0:
             kernel_ms.append(ms)
+    fallback_passes = int(lib.ann_cuda_screen_fallbacks() - fallbacks0)
     lib.ann_cuda_set_kernel_timing(0)
     t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     elapsed_ms = float(t.item())
-    units = wl.units_per_step() * args.steps * (world if wl.scaling == "weak" else 1)
+    units = wl.units_per_step() * steps * (world if wl.scaling == "weak" else 1)
     value = units / (elapsed_ms * 1e-3)
-    wl.verify(torch, out[0], out[1])
 
     # ---- end to end: host buffers, copies inside the timed region
     for _ in range(2):
         wl.step_e2e(torch)
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         wl.step_e2e(torch)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
@@ -770,7 +904,7 @@ def main():
 
     roof = wl.roofline(peaks, kernel_ms[-1] if kernel_ms else None)
     if roof["bound"] == "hbm" and isinstance(wl, BatchWorkload):
-        per_launch_ms = elapsed_ms / args.steps
+        per_launch_ms = elapsed_ms / steps
         roof["achieved"] = wl.bytes_per_step() / 1e9 / (per_launch_ms * 1e-3)
         roof["frac"] = roof["achieved"] / roof["peak"]
         roof["kernel_ms"] = per_launch_ms
@@ -778,31 +912,91 @@ def main():
     if roof["bound"] == "hbm" and roof.get("achieved"):
         roof["frac_of_nominal_8000"] = roof["achieved"] / 8000.0
 
-    line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+    line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": steps,
+            "warmup": args.warmup, "ms_per_step": elapsed_ms / steps, "higher_is_better": True,
             "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
             "config": wl.config(world), "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": 1e3 * e2e_s / args.steps},
+                    "ms_per_step": 1e3 * e2e_s / steps},
             "gpu_launches": int(launches), "roofline": roof, "setup_s": t_setup}
+    if hasattr(wl, "index"):
+        line["fallback_passes"] = fallback_passes  # searches repeated one tier up inside the timed region
 
     if one_per_launch_ms is not None:
         line["one_batch_per_launch"] = {"ms_per_step": one_per_launch_ms,
                                         "value": wl.units_per_step() / (one_per_launch_ms * 1e-3), "unit": wl.unit}
     if isinstance(wl, BatchWorkload) and not wl.sq8 and rank == 0:
         line["single_query"] = wl.single_query_shapes(torch)
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    oracle = None
+    if rank == 0:
         from oracle import oracle
         oracle.build()
+    if rank == 0 and world == 1 and with_cpu_baseline:
         sample = wl.cpu_sample(torch, device)
         qps, dt, desc = wl.cpu_run(oracle, sample)
         line["cpu_baseline"] = {"value": qps, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
-                                "sample": desc, "seconds": dt}
+                                "blas_threads": blas_threads(), "sample": desc, "seconds": dt}
+    # ---- the timed output against the exact kernels and the oracle (every rank takes part in the
+    # gather of the sample; the oracle runs on rank 0)
+    line["parity_check"] = wl.parity_check(torch, dist, out[0], out[1], oracle)
+    wl.close()
+    del wl, out
+    torch.cuda.empty_cache()
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None,
+                    help="timed steps of the headline workload (default 5; 100 for the batch-distance workloads)")
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None,
+                    help="time this workload alone (default: flat_ip_20m plus the other configurations under `workloads`)")
+    ap.add_argument("--scale", type=float, default=1.0, help="shrinks the row counts (debugging / profiling captures)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="headline workload only")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    headline = args.workload or "flat_ip_20m"
+    if args.impl == "reference":
+        run_reference(args, make_workload(headline, args.scale))
+        return
+
+    import torch
+    import torch.distributed as dist
+    rank, local, world = dist_info(args)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    pkg = load_package()
+    if not pkg.get_gpu_backend().IsAvailable():
+        raise SystemExit("no sm_100 GPU: " + pkg.get_gpu_backend().DeviceInfo())
+    ctx = {"torch": torch, "dist": dist, "pkg": pkg, "lib": pkg.lib(), "peaks": measured_peaks(), "rank": rank,
+           "local": local, "world": world, "device": device}
+
+    steps = args.steps if args.steps is not None else DEFAULT_STEPS[headline]
+    line = run_workload(args, headline, steps, ctx, not args.no_cpu_baseline)
+    ok = line["parity_check"]["ok"]
+    if args.workload is None and not args.no_extras:
+        # the other configurations, measured the same way in the same process; the batch-distance
+        # and 100k-row configurations are single-GPU by definition
+        extras = ["flat_l2_100k", "ivf_1m", "batch_c2", "sq8_c5"] if world == 1 else ["ivf_1m"]
+        line["workloads"] = {}
+        for name in extras:
+            sub = run_workload(args, name, DEFAULT_STEPS[name], ctx, not args.no_cpu_baseline)
+            ok = ok and sub["parity_check"]["ok"]
+            line["workloads"][name] = sub
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not ok:
+        raise SystemExit("parity check failed: see parity_check in the line above")
 
 
 if __name__ == "__main__":

@@ -87,6 +87,20 @@ SIGNATURES = {
     "ann_cuda_index_is_ivf": (C.c_int, [_P]),
     "ann_cuda_index_device": (C.c_int, [_P]),
     "ann_cuda_index_free": (None, [_P]),
+    "ann_cuda_sharded_create": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, _I64, C.POINTER(_P)]),
+    "ann_cuda_sharded_free": (None, [_P]),
+    "ann_cuda_sharded_shard_count": (C.c_int, [_P]),
+    "ann_cuda_sharded_shard": (_P, [_P, C.c_int]),
+    "ann_cuda_sharded_ntotal": (_I64, [_P]),
+    "ann_cuda_sharded_add": (C.c_int, [_P, _I64, _P]),
+    "ann_cuda_sharded_train": (C.c_int, [_P, _I64, _P]),
+    "ann_cuda_sharded_set_centroids": (C.c_int, [_P, _P]),
+    "ann_cuda_sharded_add_list": (C.c_int, [_P, _I64, _I64, _P, _P]),
+    "ann_cuda_sharded_set_nprobe": (C.c_int, [_P, _I64]),
+    "ann_cuda_sharded_search": (C.c_int, [_P, _I64, _P, _I64, _P, _P]),
+    "ann_cuda_sharded_reset": (C.c_int, [_P]),
+    "ann_cuda_sharded_reconstruct": (C.c_int, [_P, _I64, _P]),
+    "ann_cuda_sharded_get_rows": (C.c_int, [_P, _I64, _I64, _P]),
     "ann_cuda_merge_topk_device": (C.c_int, [C.c_int, _P, _P, C.c_int, _I64, _I64, C.c_int, _P, _P, _P]),
     "ann_cuda_flat_kernel_name": (C.c_char_p, []),
     "ann_cuda_set_flat_kernel": (C.c_int, [C.c_char_p]),
@@ -133,10 +147,10 @@ def check(rc: int, what: str) -> None:
 
 
 from .faiss_like import (METRIC_INNER_PRODUCT, METRIC_L2, CudaGpuBackend, CudaIndexFlat,  # noqa: E402
-                         CudaIndexIVFFlat, SearchToken, get_gpu_backend, merge_topk_device)
+                         CudaIndexIVFFlat, CudaShardedIndex, SearchToken, get_gpu_backend, merge_topk_device)
 from . import diskann_bridge  # noqa: E402
 from . import sharded  # noqa: E402
 
-__all__ = ["lib", "last_error", "AnnCudaError", "CudaIndexFlat", "CudaIndexIVFFlat", "CudaGpuBackend",
+__all__ = ["lib", "last_error", "AnnCudaError", "CudaIndexFlat", "CudaIndexIVFFlat", "CudaShardedIndex", "CudaGpuBackend",
            "get_gpu_backend", "merge_topk_device", "METRIC_L2", "METRIC_INNER_PRODUCT", "diskann_bridge",
            "sharded"]

@@ -26,8 +26,8 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libann_cuda.so")
 DRIVER = os.path.join(HERE, "backend_driver")
 
-LIB_SOURCES = ["prep.cu", "scan.cu", "merge.cu", "flat_tc.cu", "flat_tc_bk32.cu", "index.cu", "cuda_diskann_bridge.cu",
-               "gpu_backend_cuda.cu"]
+LIB_SOURCES = ["prep.cu", "scan.cu", "merge.cu", "flat_tc.cu", "flat_tc_bk32.cu", "index.cu", "sharded.cu",
+               "cuda_diskann_bridge.cu", "gpu_backend_cuda.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # /usr/bin/g++ is the system compiler; the image's $CXX points at a gcc without OpenMP support files
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", INCLUDE, "-I", CSRC,
@@ -80,7 +80,7 @@ def build(force: bool = False, verbose: bool = False, measure: bool = False) -> 
     if failed:
         raise RuntimeError("nvcc failed")
     if force or _newer(LIB, objs):
-        subprocess.check_call([nvcc()] + ARCH + ["-shared", "-o", LIB] + objs + ["-ccbin", "/usr/bin/g++", "-lcudart"])
+        subprocess.check_call([nvcc()] + ARCH + ["-shared", "-o", LIB] + objs + ["-ccbin", "/usr/bin/g++", "-lcudart", "-lpthread"])
     drv_src = os.path.join(CSRC, "backend_driver.cpp")
     if not measure and (force or _newer(DRIVER, [drv_src, LIB] + headers)):
         subprocess.check_call(["/usr/bin/g++", "-O2", "-std=c++17", "-DFAISS_AVAILABLE", "-DFAISS_CUDA_ENABLED",

@@ -82,8 +82,9 @@ int main(int argc, char **argv) {
         // searchAsync (MetalIndexFlat.h:71-76): one token per query, all in flight, then waited
         // on in reverse order; the answers are those of the synchronous calls
         int async_ok = 1;
-        if (!ivf) {  // CpuToGpu hands out a CudaIndexFlat for an IndexFlat
-            auto *gf = static_cast<faiss_cuda::CudaIndexFlat *>(gpu.get());
+        // CpuToGpu hands out a CudaIndexFlat for an IndexFlat on one device (a CudaShardedIndex,
+        // which has no tokens, when several devices are configured)
+        if (auto *gf = dynamic_cast<faiss_cuda::CudaIndexFlat *>(gpu.get())) {
             std::vector<float> D2((size_t)(nq * k));
             std::vector<int64_t> I2((size_t)(nq * k));
             std::vector<faiss_cuda::CudaSearchToken> tokens;
@@ -137,8 +138,9 @@ int main(int argc, char **argv) {
         fwrite(D1.data(), 4, D1.size(), o);
         fwrite(I1.data(), 8, I1.size(), o);
         fclose(o);
-        printf("{\"backend\": \"%s\", \"roundtrip_ok\": %d, \"rejects_unknown\": %d, \"async_ok\": %d}\n",
-               backend.BackendName().c_str(), roundtrip_ok, rejects_unknown, async_ok);
+        auto *sharded = dynamic_cast<faiss_cuda::CudaShardedIndex *>(gpu.get());
+        printf("{\"backend\": \"%s\", \"roundtrip_ok\": %d, \"rejects_unknown\": %d, \"async_ok\": %d, \"shards\": %d}\n",
+               backend.BackendName().c_str(), roundtrip_ok, rejects_unknown, async_ok, sharded ? sharded->shardCount() : 1);
         return 0;
     } catch (const std::exception &e) {
         fprintf(stderr, "error: %s\n", e.what());

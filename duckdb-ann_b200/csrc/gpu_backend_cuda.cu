@@ -193,6 +193,115 @@ ANN_CUDA_EXPORT std::unique_ptr<faiss::IndexIVFFlat> index_cuda_to_cpu_ivf(const
     return cpu;
 }
 
+// ---------------------------------------------------------------- CudaShardedIndex
+ANN_CUDA_EXPORT CudaShardedIndex::CudaShardedIndex(const std::vector<int> &devices, int d, size_t nlist,
+                                                   faiss::MetricType metric)
+    : faiss::Index(d, metric), nlist_(nlist) {
+    if (ann_cuda_sharded_create(devices.data(), (int)devices.size(), d, metric_code(metric), (int64_t)nlist, &handle_))
+        fail("CudaShardedIndex");
+    is_trained = nlist == 0;
+}
+ANN_CUDA_EXPORT CudaShardedIndex::~CudaShardedIndex() { ann_cuda_sharded_free(handle_); }
+ANN_CUDA_EXPORT int CudaShardedIndex::shardCount() const { return ann_cuda_sharded_shard_count(handle_); }
+ANN_CUDA_EXPORT void CudaShardedIndex::train(faiss::idx_t n, const float *x) {
+    if (!isIVF()) return;
+    if (ann_cuda_sharded_train(handle_, n, x)) fail("CudaShardedIndex::train");
+    is_trained = true;
+}
+ANN_CUDA_EXPORT void CudaShardedIndex::add(faiss::idx_t n, const float *x) {
+    if (!is_trained) throw std::runtime_error("add: index must be trained first");
+    if (ann_cuda_sharded_add(handle_, n, x)) fail("CudaShardedIndex::add");
+    ntotal = ann_cuda_sharded_ntotal(handle_);
+}
+ANN_CUDA_EXPORT void CudaShardedIndex::search(faiss::idx_t n, const float *x, faiss::idx_t k, float *distances,
+                                              faiss::idx_t *labels, const faiss::SearchParameters *) const {
+    if (!is_trained) throw std::runtime_error("search: index must be trained first");
+    if (k <= 0) throw std::runtime_error("k must be > 0");
+    if (ann_cuda_sharded_search(handle_, n, x, k, distances, labels)) fail("CudaShardedIndex::search");
+}
+ANN_CUDA_EXPORT void CudaShardedIndex::reset() {
+    if (ann_cuda_sharded_reset(handle_)) fail("CudaShardedIndex::reset");
+    ntotal = 0;
+}
+ANN_CUDA_EXPORT void CudaShardedIndex::reconstruct(faiss::idx_t key, float *recons) const {
+    if (ann_cuda_sharded_reconstruct(handle_, key, recons)) fail("CudaShardedIndex::reconstruct");
+}
+ANN_CUDA_EXPORT void CudaShardedIndex::setNprobe(size_t nprobe) {
+    if (!isIVF()) return;
+    nprobe_ = nprobe < 1 ? 1 : (nprobe > nlist_ ? nlist_ : nprobe);  // MetalIndexIVFFlat.mm:275-279
+    if (ann_cuda_sharded_set_nprobe(handle_, (int64_t)nprobe_)) fail("CudaShardedIndex::setNprobe");
+}
+
+ANN_CUDA_EXPORT std::unique_ptr<CudaShardedIndex> index_cpu_to_cuda_sharded(const std::vector<int> &devices,
+                                                                            const faiss::IndexFlat *cpu) {
+    std::unique_ptr<CudaShardedIndex> gpu(new CudaShardedIndex(devices, cpu->d, 0, cpu->metric_type));
+    if (cpu->ntotal > 0) gpu->add(cpu->ntotal, cpu->get_xb());  // one add: equal contiguous row ranges
+    return gpu;
+}
+
+ANN_CUDA_EXPORT std::unique_ptr<CudaShardedIndex> index_cpu_to_cuda_sharded_ivf(const std::vector<int> &devices,
+                                                                                const faiss::IndexIVFFlat *cpu) {
+    if (!cpu->is_trained) throw std::runtime_error("CPU IndexIVFFlat must be trained");
+    auto *quantizer = dynamic_cast<const faiss::IndexFlat *>(cpu->quantizer);
+    if (!quantizer) throw std::runtime_error("IndexIVFFlat quantizer must be IndexFlat");
+    if ((size_t)quantizer->ntotal != cpu->nlist) throw std::runtime_error("quantizer size does not match nlist");
+    std::unique_ptr<CudaShardedIndex> gpu(new CudaShardedIndex(devices, cpu->d, cpu->nlist, cpu->metric_type));
+    if (ann_cuda_sharded_set_centroids(gpu->handle(), quantizer->get_xb())) fail("index_cpu_to_cuda_sharded_ivf");
+    gpu->is_trained = true;
+    const faiss::InvertedLists *lists = cpu->invlists;
+    for (size_t c = 0; c < cpu->nlist; c++) {
+        const size_t n = lists->list_size(c);
+        if (n == 0) continue;
+        const faiss::idx_t *ids = lists->get_ids(c);
+        const uint8_t *codes = lists->get_codes(c);
+        const int rc = ann_cuda_sharded_add_list(gpu->handle(), (int64_t)c, (int64_t)n, ids, reinterpret_cast<const float *>(codes));
+        lists->release_ids(c, ids);
+        lists->release_codes(c, codes);
+        if (rc) fail("index_cpu_to_cuda_sharded_ivf");
+    }
+    gpu->ntotal = cpu->ntotal;
+    gpu->setNprobe(cpu->nprobe);
+    return gpu;
+}
+
+ANN_CUDA_EXPORT std::unique_ptr<faiss::Index> index_cuda_sharded_to_cpu(const CudaShardedIndex *gpu) {
+    const int d = gpu->d;
+    if (!gpu->isIVF()) {
+        std::unique_ptr<faiss::IndexFlat> cpu(new faiss::IndexFlat(d, gpu->metric_type));
+        if (gpu->ntotal > 0) {
+            std::vector<float> rows((size_t)gpu->ntotal * d);
+            if (ann_cuda_sharded_get_rows(gpu->handle(), 0, gpu->ntotal, rows.data())) fail("index_cuda_sharded_to_cpu");
+            cpu->add(gpu->ntotal, rows.data());
+        }
+        return cpu;
+    }
+    if (!gpu->is_trained) throw std::runtime_error("CUDA index must be trained");
+    const size_t nlist = gpu->getNlist();
+    const int shards = gpu->shardCount();
+    std::vector<float> cent(nlist * (size_t)d);
+    if (ann_cuda_ivfflat_get_centroids(ann_cuda_sharded_shard(gpu->handle(), 0), cent.data())) fail("index_cuda_sharded_to_cpu");
+    auto *quantizer = new faiss::IndexFlat(d, gpu->metric_type);
+    quantizer->add((faiss::idx_t)nlist, cent.data());
+    std::unique_ptr<faiss::IndexIVFFlat> cpu(new faiss::IndexIVFFlat(quantizer, d, nlist, gpu->metric_type));
+    cpu->own_fields = true;
+    cpu->is_trained = true;
+    cpu->nprobe = gpu->getNprobe();
+    std::vector<faiss::idx_t> ids;
+    std::vector<float> rows;
+    for (size_t c = 0; c < nlist; c++) {
+        const ann_cuda_index *owner = ann_cuda_sharded_shard(gpu->handle(), (int)(c % (size_t)shards));
+        const int64_t n = ann_cuda_ivfflat_list_size(owner, (int64_t)c);
+        if (n < 0) fail("index_cuda_sharded_to_cpu");
+        if (n == 0) continue;
+        ids.resize((size_t)n);
+        rows.resize((size_t)n * d);
+        if (ann_cuda_ivfflat_get_list(owner, (int64_t)c, ids.data(), rows.data())) fail("index_cuda_sharded_to_cpu");
+        cpu->invlists->add_entries(c, (size_t)n, ids.data(), reinterpret_cast<const uint8_t *>(rows.data()));
+    }
+    cpu->ntotal = gpu->ntotal;
+    return cpu;
+}
+
 }  // namespace faiss_cuda
 
 // ---------------------------------------------------------------- the backend
@@ -203,27 +312,61 @@ public:
     // Availability is a flag; the constructor never throws (gpu_backend_metal.mm:17-24).
     CudaGpuBackend() {
         available_ = ann_cuda_available() != 0;
-        const char *env = std::getenv("ANN_CUDA_DEVICE");
-        device_ = env ? std::atoi(env) : 0;
-        if (device_ < 0 || device_ >= ann_cuda_device_count()) device_ = 0;
+        const int count = ann_cuda_device_count();
+        // ANN_CUDA_DEVICES = "0,1,2,3" or "all": indexes are spread over these devices (one process,
+        // one host thread and stream per device).  Otherwise ANN_CUDA_DEVICE (one device, default 0).
+        if (const char *many = std::getenv("ANN_CUDA_DEVICES")) {
+            const std::string list(many);
+            if (list == "all") {
+                for (int i = 0; i < count; i++) devices_.push_back(i);
+            } else {
+                size_t pos = 0;
+                while (pos < list.size()) {
+                    size_t end = list.find(',', pos);
+                    if (end == std::string::npos) end = list.size();
+                    const std::string item = list.substr(pos, end - pos);
+                    if (!item.empty()) {
+                        const int dev = std::atoi(item.c_str());
+                        if (dev >= 0 && dev < count) devices_.push_back(dev);
+                    }
+                    pos = end + 1;
+                }
+            }
+        }
+        if (devices_.empty()) {
+            const char *env = std::getenv("ANN_CUDA_DEVICE");
+            int device = env ? std::atoi(env) : 0;
+            if (device < 0 || device >= count) device = 0;
+            devices_.push_back(device);
+        }
     }
     bool IsAvailable() const override { return available_; }
     std::string DeviceInfo() const override {
         if (!available_) return "CUDA: not available";
         char buf[256];
         if (ann_cuda_device_info(buf, sizeof buf)) return "CUDA GPU";
-        return buf;
+        std::string info(buf);
+        if (devices_.size() > 1) info += " [indexes sharded over " + std::to_string(devices_.size()) + " devices]";
+        return info;
     }
     std::string BackendName() const override { return "cuda"; }
 
     std::unique_ptr<faiss::Index> CpuToGpu(faiss::Index *cpu_index) override {
         if (!available_) throw std::runtime_error("CUDA GPU backend not available");
+        const bool sharded = devices_.size() > 1;
         // IVFFlat first: it also contains an IndexFlat quantizer (gpu_backend_metal.mm:47-51)
-        if (auto *ivf = dynamic_cast<faiss::IndexIVFFlat *>(cpu_index)) return faiss_cuda::index_cpu_to_cuda_ivf(device_, ivf);
-        if (auto *flat = dynamic_cast<faiss::IndexFlat *>(cpu_index)) return faiss_cuda::index_cpu_to_cuda(device_, flat);
+        if (auto *ivf = dynamic_cast<faiss::IndexIVFFlat *>(cpu_index)) {
+            if (sharded) return faiss_cuda::index_cpu_to_cuda_sharded_ivf(devices_, ivf);
+            return faiss_cuda::index_cpu_to_cuda_ivf(devices_[0], ivf);
+        }
+        if (auto *flat = dynamic_cast<faiss::IndexFlat *>(cpu_index)) {
+            if (sharded) return faiss_cuda::index_cpu_to_cuda_sharded(devices_, flat);
+            return faiss_cuda::index_cpu_to_cuda(devices_[0], flat);
+        }
         throw std::runtime_error("CUDA GPU supports IndexFlat and IndexIVFFlat. Got an unsupported index type.");
     }
     std::unique_ptr<faiss::Index> GpuToCpu(faiss::Index *gpu_index) override {
+        if (auto *sh = dynamic_cast<faiss_cuda::CudaShardedIndex *>(gpu_index)) return faiss_cuda::index_cuda_sharded_to_cpu(sh);
         if (auto *ivf = dynamic_cast<faiss_cuda::CudaIndexIVFFlat *>(gpu_index)) return faiss_cuda::index_cuda_to_cpu_ivf(ivf);
         if (auto *flat = dynamic_cast<faiss_cuda::CudaIndexFlat *>(gpu_index)) return faiss_cuda::index_cuda_to_cpu(flat);
         throw std::runtime_error("Index is not a CUDA index -- cannot convert to CPU");
@@ -231,7 +374,7 @@ public:
 
 private:
     bool available_ = false;
-    int device_ = 0;
+    std::vector<int> devices_;
 };
 
 ANN_CUDA_EXPORT GpuBackend &GetGpuBackend() {

@@ -282,6 +282,105 @@ class CudaIndexIVFFlat(_CudaIndex):
         p.check(p.lib().ann_cuda_ivfflat_set_shard(self._h, rank, count), "set_shard")
 
 
+class _ShardView(_CudaIndex):
+    """A borrowed shard of a CudaShardedIndex (never freed from here)."""
+
+    def __init__(self, handle):
+        super().__init__()
+        self._h = handle
+
+    def close(self) -> None:
+        self._h = C.c_void_p()
+
+
+class CudaShardedIndex:
+    """One Flat (nlist = 0) or IVFFlat index over several GPUs in this process: what
+    CudaGpuBackend::CpuToGpu hands out when ANN_CUDA_DEVICES names more than one device.
+    `devices` may repeat a device (several shards on one GPU)."""
+
+    def __init__(self, d: int, metric: int = METRIC_L2, devices=(0,), nlist: int = 0):
+        self._h = C.c_void_p()
+        self.d, self.metric_type, self.nlist = d, metric, nlist
+        dev = (C.c_int * len(devices))(*devices)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_sharded_create(dev, len(devices), d, metric, nlist, C.byref(self._h)), "CudaShardedIndex")
+
+    @property
+    def ntotal(self) -> int:
+        return _pkg().lib().ann_cuda_sharded_ntotal(self._h)
+
+    @property
+    def shard_count(self) -> int:
+        return _pkg().lib().ann_cuda_sharded_shard_count(self._h)
+
+    def shard(self, i: int) -> _ShardView:
+        h = _pkg().lib().ann_cuda_sharded_shard(self._h, i)
+        if not h:
+            raise IndexError(i)
+        return _ShardView(C.c_void_p(h))
+
+    def add(self, x) -> None:
+        x = _np_f32(x)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_sharded_add(self._h, x.shape[0], _ptr(x)), "sharded add")
+
+    def train(self, x) -> None:
+        x = _np_f32(x)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_sharded_train(self._h, x.shape[0], _ptr(x)), "sharded train")
+
+    def set_centroids(self, centroids) -> None:
+        c = _np_f32(centroids)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_sharded_set_centroids(self._h, _ptr(c)), "sharded set_centroids")
+
+    def add_list(self, list_no: int, ids, rows) -> None:
+        ids = np.ascontiguousarray(ids, np.int64)
+        rows = _np_f32(rows).reshape(len(ids), self.d)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_sharded_add_list(self._h, list_no, len(ids), _ptr(ids), _ptr(rows)), "sharded add_list")
+
+    def setNprobe(self, nprobe: int) -> None:
+        p = _pkg()
+        p.check(p.lib().ann_cuda_sharded_set_nprobe(self._h, nprobe), "sharded setNprobe")
+
+    def search(self, x, k: int):
+        x = _np_f32(x)
+        n = x.shape[0]
+        D = np.empty((n, max(k, 0)), np.float32)
+        I = np.empty((n, max(k, 0)), np.int64)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_sharded_search(self._h, n, _ptr(x), k, _ptr(D), _ptr(I)), "sharded search")
+        return D, I
+
+    def reset(self) -> None:
+        p = _pkg()
+        p.check(p.lib().ann_cuda_sharded_reset(self._h), "sharded reset")
+
+    def reconstruct(self, key: int):
+        out = np.empty(self.d, np.float32)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_sharded_reconstruct(self._h, key, _ptr(out)), "sharded reconstruct")
+        return out
+
+    def get_rows(self, first: int, n: int):
+        out = np.empty((n, self.d), np.float32)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_sharded_get_rows(self._h, first, n, _ptr(out)), "sharded get_rows")
+        return out
+
+    def close(self) -> None:
+        if self._h:
+            _pkg().lib().ann_cuda_sharded_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class CudaGpuBackend:
     """duckdb::GpuBackend for CUDA: IsAvailable / DeviceInfo / BackendName
     (src/include/gpu_backend.hpp:12-33, src/faiss_fn_gpu.cpp:33-46)."""

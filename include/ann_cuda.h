@@ -181,6 +181,41 @@ int ann_cuda_flat_search_small_static(const ann_cuda_index *index, int64_t n, co
  * No counterpart in the reference. */
 int ann_cuda_flat_search_small_static_status(int device, void *stream);
 
+/* ---- one index over several GPUs, in one process ------------------------------------
+ * No counterpart in the reference (single device).  This is the object CpuToGpu hands out
+ * when more than one device is configured, so that the one process that owns the index
+ * (src/faiss_index.cpp:108-149) searches all GPUs through the ordinary search() call.
+ * Flat (nlist = 0): rows in contiguous ranges, one per shard, labels = global positions.
+ * IVFFlat (nlist > 0): inverted list l on shard l % shards, coarse quantiser on every shard.
+ * search: every shard (own host thread, own stream) searches its part for all queries;
+ * the per-shard top-k lists are copied into the first device's memory and merged there
+ * (ann_cuda_merge_topk_device).  A device may be named more than once (several shards
+ * on one GPU).  Calls on one sharded index are serialised internally. */
+typedef struct ann_cuda_sharded_index ann_cuda_sharded_index;
+int ann_cuda_sharded_create(const int *devices, int ndev, int d, int metric, int64_t nlist,
+                            ann_cuda_sharded_index **out);
+void ann_cuda_sharded_free(ann_cuda_sharded_index *index);
+int ann_cuda_sharded_shard_count(const ann_cuda_sharded_index *index);
+/* The shard itself (borrowed), e.g. to fill it from device memory with ann_cuda_index_add_device
+ * or to read an inverted list back from its owner.  Flat shards must be filled in order: the
+ * label offset of a shard is the number of rows in the shards before it. */
+ann_cuda_index *ann_cuda_sharded_shard(const ann_cuda_sharded_index *index, int shard);
+int64_t ann_cuda_sharded_ntotal(const ann_cuda_sharded_index *index);
+/* faiss::Index::add.  Flat: the first add is cut into equal contiguous ranges, later adds go
+ * behind the last shard's rows.  IVFFlat: every shard assigns the rows and keeps its lists'. */
+int ann_cuda_sharded_add(ann_cuda_sharded_index *index, int64_t n, const float *x);
+int ann_cuda_sharded_train(ann_cuda_sharded_index *index, int64_t n, const float *x);
+int ann_cuda_sharded_set_centroids(ann_cuda_sharded_index *index, const float *centroids);
+int ann_cuda_sharded_add_list(ann_cuda_sharded_index *index, int64_t list_no, int64_t n, const int64_t *ids,
+                              const float *rows);
+int ann_cuda_sharded_set_nprobe(ann_cuda_sharded_index *index, int64_t nprobe);
+/* faiss::Index::search / reset / reconstruct with host pointers, as ann_cuda_index_search. */
+int ann_cuda_sharded_search(const ann_cuda_sharded_index *index, int64_t n, const float *x, int64_t k,
+                            float *distances, int64_t *labels);
+int ann_cuda_sharded_reset(ann_cuda_sharded_index *index);
+int ann_cuda_sharded_reconstruct(const ann_cuda_sharded_index *index, int64_t key, float *recons);
+int ann_cuda_sharded_get_rows(const ann_cuda_sharded_index *index, int64_t first, int64_t n, float *rows);
+
 /* ---- multi-GPU merge -------------------------------------------------------------
  * Final k-select over per-shard results.  parts_*: (nparts x nq x k) in DEVICE
  * memory, each (part, query) run sorted best first as search_device writes it;

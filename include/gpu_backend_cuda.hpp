@@ -12,15 +12,25 @@
 #include <faiss/IndexIVFFlat.h>
 
 #include <memory>
+#include <vector>
 
 struct ann_cuda_index;
 struct ann_cuda_search_token;
+struct ann_cuda_sharded_index;
+
+// The classes are part of the library's interface: their type information is exported even
+// though the library is built with hidden visibility (dynamic_cast across the boundary).
+#if defined(__GNUC__)
+#define ANN_CUDA_CLASS __attribute__((visibility("default")))
+#else
+#define ANN_CUDA_CLASS
+#endif
 
 namespace faiss_cuda {
 
 // Move-only handle of one in-flight search (the role of faiss_metal::MetalSearchToken,
 // faiss-metal/include/faiss-metal/MetalIndexFlat.h:15-36).
-class CudaSearchToken {
+class ANN_CUDA_CLASS CudaSearchToken {
 public:
     CudaSearchToken(CudaSearchToken &&o) noexcept : token_(o.token_) { o.token_ = nullptr; }
     CudaSearchToken &operator=(CudaSearchToken &&o) noexcept;
@@ -37,7 +47,7 @@ private:
     ann_cuda_search_token *token_ = nullptr;
 };
 
-class CudaIndexFlat : public faiss::Index {
+class ANN_CUDA_CLASS CudaIndexFlat : public faiss::Index {
 public:
     CudaIndexFlat(int device, int d, faiss::MetricType metric = faiss::METRIC_L2);
     ~CudaIndexFlat() override;
@@ -63,7 +73,7 @@ private:
     ann_cuda_index *handle_ = nullptr;
 };
 
-class CudaIndexIVFFlat : public faiss::Index {
+class ANN_CUDA_CLASS CudaIndexIVFFlat : public faiss::Index {
 public:
     CudaIndexIVFFlat(int device, int d, size_t nlist, faiss::MetricType metric = faiss::METRIC_L2);
     ~CudaIndexIVFFlat() override;
@@ -87,11 +97,46 @@ private:
     ann_cuda_index *handle_ = nullptr;
 };
 
+// One Flat (nlist = 0) or IVFFlat index spread over several GPUs of the box, searched from the one
+// process that owns it through the ordinary faiss::Index calls.  No counterpart in the reference
+// (single device); it is what CudaGpuBackend::CpuToGpu returns when ANN_CUDA_DEVICES names more
+// than one device.  Flat: contiguous row ranges; IVFFlat: list l on shard l % shards.
+class ANN_CUDA_CLASS CudaShardedIndex : public faiss::Index {
+public:
+    CudaShardedIndex(const std::vector<int> &devices, int d, size_t nlist, faiss::MetricType metric = faiss::METRIC_L2);
+    ~CudaShardedIndex() override;
+    CudaShardedIndex(const CudaShardedIndex &) = delete;
+    CudaShardedIndex &operator=(const CudaShardedIndex &) = delete;
+
+    void train(faiss::idx_t n, const float *x) override;
+    void add(faiss::idx_t n, const float *x) override;
+    void search(faiss::idx_t n, const float *x, faiss::idx_t k, float *distances, faiss::idx_t *labels,
+                const faiss::SearchParameters *params = nullptr) const override;
+    void reset() override;
+    void reconstruct(faiss::idx_t key, float *recons) const override;
+
+    bool isIVF() const { return nlist_ > 0; }
+    size_t getNlist() const { return nlist_; }
+    size_t getNprobe() const { return nprobe_; }
+    void setNprobe(size_t nprobe);
+    int shardCount() const;
+    ann_cuda_sharded_index *handle() const { return handle_; }
+
+private:
+    ann_cuda_sharded_index *handle_ = nullptr;
+    size_t nlist_ = 0, nprobe_ = 1;
+};
+
 // Conversions (faiss-metal/src/MetalIndexFlat.mm:504-535,
 // faiss-metal/src/MetalIndexIVFFlat.mm:283-356).
 std::unique_ptr<CudaIndexFlat> index_cpu_to_cuda(int device, const faiss::IndexFlat *cpu_index);
 std::unique_ptr<faiss::IndexFlat> index_cuda_to_cpu(const CudaIndexFlat *cuda_index);
 std::unique_ptr<CudaIndexIVFFlat> index_cpu_to_cuda_ivf(int device, const faiss::IndexIVFFlat *cpu_index);
 std::unique_ptr<faiss::IndexIVFFlat> index_cuda_to_cpu_ivf(const CudaIndexIVFFlat *cuda_index);
+// ... and the same onto / back from several devices
+std::unique_ptr<CudaShardedIndex> index_cpu_to_cuda_sharded(const std::vector<int> &devices, const faiss::IndexFlat *cpu_index);
+std::unique_ptr<CudaShardedIndex> index_cpu_to_cuda_sharded_ivf(const std::vector<int> &devices,
+                                                               const faiss::IndexIVFFlat *cpu_index);
+std::unique_ptr<faiss::Index> index_cuda_sharded_to_cpu(const CudaShardedIndex *cuda_index);
 
 }  // namespace faiss_cuda

@@ -14,14 +14,18 @@ pytestmark = pytest.mark.gpu
 DRIVER = os.path.join(ROOT, "duckdb-ann_b200", "backend_driver")
 
 
-def _run(tmp_path, mode, d, k, metric, xb, xq, nlist=0, nprobe=0, cent=None, assign=None):
+def _run(tmp_path, mode, d, k, metric, xb, xq, nlist=0, nprobe=0, cent=None, assign=None, devices=None):
     inp, out = tmp_path / "in.bin", tmp_path / "out.bin"
     with open(inp, "wb") as f:
         f.write(np.array([d, len(xb), len(xq), k, metric, nlist, nprobe], np.int64).tobytes())
         f.write(xb.tobytes()); f.write(xq.tobytes())
         if cent is not None:
             f.write(cent.tobytes()); f.write(assign.astype(np.int64).tobytes())
-    res = subprocess.run([DRIVER, mode, str(inp), str(out)], capture_output=True, text=True, timeout=300)
+    env = dict(os.environ)
+    env.pop("ANN_CUDA_DEVICES", None)
+    if devices:
+        env["ANN_CUDA_DEVICES"] = devices
+    res = subprocess.run([DRIVER, mode, str(inp), str(out)], capture_output=True, text=True, timeout=300, env=env)
     assert res.returncode == 0, res.stderr
     info = json.loads(res.stdout.strip().splitlines()[-1])
     raw = open(out, "rb").read()
@@ -45,7 +49,7 @@ def test_flat_through_gpu_backend(tmp_path, oracle, metric):
     xb = rng.uniform(-1, 1, (3000, 96)).astype(np.float32)
     xq = rng.uniform(-1, 1, (12, 96)).astype(np.float32)
     info, D, I, D1, I1 = _run(tmp_path, "flat", 96, 7, metric, xb, xq)
-    assert info == {"backend": "cuda", "roundtrip_ok": 1, "rejects_unknown": 1, "async_ok": 1}
+    assert info == {"backend": "cuda", "roundtrip_ok": 1, "rejects_unknown": 1, "async_ok": 1, "shards": 1}
     Dref, Iref = oracle.flat_search(xb, xq, 7, metric)
     assert_topk_matches(oracle, xb, xq, metric, D, I, Dref, Iref, "batch")
     assert_topk_matches(oracle, xb, xq, metric, D1, I1, Dref, Iref, "one query per call")
@@ -63,3 +67,47 @@ def test_ivf_through_gpu_backend(tmp_path, oracle):
     Dref, Iref = oracle.ivf_search(xb, cent, off, rows, xq, 6, 12, oracle.METRIC_L2)
     assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D, I, Dref, Iref, "ivf batch")
     assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D1, I1, Dref, Iref, "ivf one query per call")
+
+
+def _device_lists():
+    """Device lists for the sharded runs: three shards on device 0 always (the same code path as
+    one shard per GPU), and one shard on each of the first two GPUs where the box has them."""
+    import torch
+    lists = ["0,0,0"]
+    if torch.cuda.device_count() >= 2:
+        lists.append("0,1")
+    return lists
+
+
+@pytest.mark.parametrize("metric", [1, 0])
+def test_flat_sharded_behind_the_plugin(tmp_path, oracle, metric):
+    """ANN_CUDA_DEVICES with more than one entry: CpuToGpu hands out ONE index object spread over the
+    devices, and the process that owns it searches all of them through faiss::Index::search
+    (src/faiss_index.cpp:108-149, 729-737).  Same answers as on one device, bit for bit."""
+    rng = np.random.default_rng(42)
+    xb = rng.uniform(-1, 1, (3001, 96)).astype(np.float32)
+    xq = rng.uniform(-1, 1, (12, 96)).astype(np.float32)
+    _, D0, I0, _, _ = _run(tmp_path, "flat", 96, 7, metric, xb, xq)
+    Dref, Iref = oracle.flat_search(xb, xq, 7, metric)
+    for devices in _device_lists():
+        info, D, I, D1, I1 = _run(tmp_path, "flat", 96, 7, metric, xb, xq, devices=devices)
+        assert info["shards"] == len(devices.split(",")) and info["roundtrip_ok"] == 1, (devices, info)
+        np.testing.assert_array_equal(I, I0)
+        np.testing.assert_array_equal(D, D0)
+        assert_topk_matches(oracle, xb, xq, metric, D, I, Dref, Iref, f"sharded over {devices}")
+        assert_topk_matches(oracle, xb, xq, metric, D1, I1, Dref, Iref, f"sharded over {devices}, one query per call")
+
+
+def test_ivf_sharded_behind_the_plugin(tmp_path, oracle):
+    rng = np.random.default_rng(43)
+    xb = rng.uniform(-1, 1, (2500, 64)).astype(np.float32)
+    xq = rng.uniform(-1, 1, (9, 64)).astype(np.float32)
+    cent = oracle.kmeans(xb, 12, niter=5, seed=2)
+    assign = oracle.ivf_assign(xb, cent, oracle.METRIC_L2)
+    off, rows = oracle.lists_from_assign(assign, 12)
+    Dref, Iref = oracle.ivf_search(xb, cent, off, rows, xq, 6, 5, oracle.METRIC_L2)
+    for devices in _device_lists():
+        info, D, I, D1, I1 = _run(tmp_path, "ivf", 64, 6, 1, xb, xq, 12, 5, cent, assign, devices=devices)
+        assert info["shards"] == len(devices.split(",")) and info["roundtrip_ok"] == 1, (devices, info)
+        assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D, I, Dref, Iref, f"ivf sharded over {devices}")
+        assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D1, I1, Dref, Iref, f"ivf sharded over {devices}, one per call")
