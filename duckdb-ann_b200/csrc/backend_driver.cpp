@@ -7,6 +7,11 @@
 //
 //   backend_driver info
 //   backend_driver flat|ivf <in.bin> <out.bin>
+//   backend_driver glue <in.bin> <out.bin> [cpu|gpu|auto]     the FaissIndex glue of faiss_index_glue.hpp:
+//       in.bin : int64 {d, n, nq, k, metric, n0, ntomb}, float xb[n*d], float xq[nq*d], int64 tomb[ntomb]
+//       builds from the first n0 rows, searches (one query per call and as ONE batch), appends the rest,
+//       marks `tomb` deleted, searches again.  out.bin: for both phases D_single, I_single, D_batch, I_batch
+//       (nq*k each; slots a query could not fill hold label -1).
 // in.bin : int64 {d, n, nq, k, metric, nlist, nprobe}, float xb[n*d], float xq[nq*d],
 //          for ivf: float centroids[nlist*d], int64 assign[n]
 // out.bin: float D_batch[nq*k], int64 I_batch[nq*k], float D_single[nq*k], int64 I_single[nq*k]
@@ -19,6 +24,7 @@
 #ifndef FAISS_AVAILABLE
 #define FAISS_AVAILABLE
 #endif
+#include "faiss_index_glue.hpp"
 #include "gpu_backend.hpp"
 #include "gpu_backend_cuda.hpp"
 
@@ -26,6 +32,60 @@ template <class T>
 static bool read_vec(FILE *f, std::vector<T> &v, size_t n) {
     v.resize(n);
     return n == 0 || fread(v.data(), sizeof(T), n, f) == n;
+}
+
+static void write_results(FILE *o, const std::vector<std::vector<std::pair<faiss::idx_t, float>>> &res, int64_t nq, int64_t k) {
+    std::vector<float> D((size_t)(nq * k), 0.f);
+    std::vector<int64_t> I((size_t)(nq * k), -1);
+    for (int64_t q = 0; q < nq && q < (int64_t)res.size(); q++)
+        for (size_t j = 0; j < res[(size_t)q].size(); j++) {
+            I[(size_t)(q * k) + j] = res[(size_t)q][j].first;
+            D[(size_t)(q * k) + j] = res[(size_t)q][j].second;
+        }
+    fwrite(D.data(), 4, D.size(), o);
+    fwrite(I.data(), 8, I.size(), o);
+}
+
+// FaissIndex::Search / SearchBatch over the GPU backend, with an append and deletions in between.
+static int run_glue(int argc, char **argv) {
+    using duckdb_glue::FaissGpuMode;
+    FaissGpuMode mode = FaissGpuMode::AUTO;
+    if (argc >= 5 && strcmp(argv[4], "gpu") == 0) mode = FaissGpuMode::GPU;
+    if (argc >= 5 && strcmp(argv[4], "cpu") == 0) mode = FaissGpuMode::CPU;
+    FILE *f = fopen(argv[2], "rb");
+    if (!f) return 2;
+    int64_t h[7];
+    if (fread(h, 8, 7, f) != 7) return 2;
+    const int64_t d = h[0], n = h[1], nq = h[2], k = h[3], n0 = h[5], ntomb = h[6];
+    const faiss::MetricType metric = h[4] == 1 ? faiss::METRIC_L2 : faiss::METRIC_INNER_PRODUCT;
+    std::vector<float> xb, xq;
+    std::vector<int64_t> tomb;
+    if (!read_vec(f, xb, (size_t)(n * d)) || !read_vec(f, xq, (size_t)(nq * d)) || !read_vec(f, tomb, (size_t)ntomb)) return 2;
+    fclose(f);
+    auto *flat = new faiss::IndexFlat(d, metric);
+    flat->add(n0, xb.data());
+    duckdb_glue::FaissIndexGlue index(std::unique_ptr<faiss::Index>(flat), mode);
+    index.EnsureGpuIndex();  // Finalize (src/faiss_index.cpp:364)
+    const int on_gpu_after_build = index.OnGpu();
+    FILE *o = fopen(argv[3], "wb");
+    if (!o) return 2;
+    auto search_both = [&] {
+        std::vector<std::vector<std::pair<faiss::idx_t, float>>> single;
+        for (int64_t q = 0; q < nq; q++) single.push_back(index.Search(xq.data() + q * d, (int32_t)d, (int32_t)k));
+        write_results(o, single, nq, k);
+        write_results(o, index.SearchBatch(xq.data(), nq, (int32_t)d, (int32_t)k), nq, k);
+    };
+    search_both();
+    index.Append(n - n0, xb.data() + n0 * d);  // drops the GPU copy (src/faiss_index.cpp:469)
+    const int on_gpu_after_append = index.OnGpu();
+    for (int64_t t : tomb) index.Delete(t);
+    search_both();  // the first of these searches uploads the index again
+    fclose(o);
+    const int wrong_dim = index.Search(xq.data(), (int32_t)d + 1, (int32_t)k).empty();  // test/sql/faiss_basic.test:265-269
+    printf("{\"on_gpu_after_build\": %d, \"on_gpu_after_append\": %d, \"on_gpu_at_end\": %d, \"gpu_uploads\": %d, "
+           "\"wrong_dimension_is_empty\": %d}\n",
+           on_gpu_after_build, on_gpu_after_append, (int)index.OnGpu(), index.GpuUploads(), wrong_dim);
+    return 0;
 }
 
 int main(int argc, char **argv) {
@@ -37,9 +97,10 @@ int main(int argc, char **argv) {
             return 0;
         }
         if (argc < 4) {
-            fprintf(stderr, "usage: %s info | flat|ivf in.bin out.bin\n", argv[0]);
+            fprintf(stderr, "usage: %s info | flat|ivf in.bin out.bin | glue in.bin out.bin [cpu|gpu|auto]\n", argv[0]);
             return 2;
         }
+        if (strcmp(argv[1], "glue") == 0) return run_glue(argc, argv);
         const bool ivf = strcmp(argv[1], "ivf") == 0;
         FILE *f = fopen(argv[2], "rb");
         if (!f) return 2;

@@ -141,11 +141,16 @@ __global__ void fill_chunk_items_kernel(int32_t *__restrict__ item_query, int64_
 }
 
 // ---- IVF item construction ------------------------------------------------------------------
-__global__ void ivf_count_kernel(const int32_t *__restrict__ probes, int64_t n, int64_t nlist, int *counts) {
+// With list_off given, probes of lists that hold no rows here (empty, or stored on another shard)
+// are not counted: they get no query tile and no work item.
+__global__ void ivf_count_kernel(const int32_t *__restrict__ probes, int64_t n, int64_t nlist, int *counts,
+                                 const int64_t *__restrict__ list_off) {
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     int l = probes[i];
-    atomicAdd(&counts[(l >= 0 && l < nlist) ? l : nlist], 1);
+    const bool ok = l >= 0 && l < nlist;
+    if (ok && list_off && list_off[l + 1] == list_off[l]) return;
+    atomicAdd(&counts[ok ? l : nlist], 1);
 }
 
 // Exclusive scan of nlist+1 counters by one block; cursors[i] = start of bucket i.
@@ -327,7 +332,7 @@ int launch_build_ivf_items(const int32_t *probes, int64_t nq, int nprobe, int64_
     int *counts = scratch, *cursors = scratch + (nlist + 1);
     ANN_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)(nlist + 1), stream));
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    ivf_count_kernel<<<blocks, 256, 0, stream>>>(probes, n, nlist, counts);
+    ivf_count_kernel<<<blocks, 256, 0, stream>>>(probes, n, nlist, counts, nullptr);
     ivf_scan_kernel<<<1, 1024, 0, stream>>>(counts, cursors, nlist + 1);
     ivf_place_kernel<<<blocks, 256, 0, stream>>>(probes, n, nprobe, nlist, list_off, cursors, item_query,
                                                  range_begin, range_end, item_slot);
@@ -344,7 +349,7 @@ int launch_group_probes(const int32_t *probes, int64_t nq, int nprobe, int64_t n
     int *counts = scratch, *second = scratch + (nlist + 1);  // second: tile offsets, then placement cursors
     ANN_CUDA_TRY(cudaMemsetAsync(scratch, 0, sizeof(int) * (size_t)(nlist + 1) * 2, stream));
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    ivf_count_kernel<<<blocks, 256, 0, stream>>>(probes, n, nlist, counts);
+    ivf_count_kernel<<<blocks, 256, 0, stream>>>(probes, n, nlist, counts, list_off);
     // tile offsets live in `second`; the placement cursors reuse `counts` after it is consumed
     group_tiles_kernel<<<1, 1024, 0, stream>>>(counts, second, nlist, n_tiles);
     group_items_kernel<<<(unsigned)((nlist + 255) / 256), 256, 0, stream>>>(counts, second, nlist, list_off, items);

@@ -111,3 +111,53 @@ def test_ivf_sharded_behind_the_plugin(tmp_path, oracle):
         assert info["shards"] == len(devices.split(",")) and info["roundtrip_ok"] == 1, (devices, info)
         assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D, I, Dref, Iref, f"ivf sharded over {devices}")
         assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D1, I1, Dref, Iref, f"ivf sharded over {devices}, one per call")
+
+
+@pytest.mark.parametrize("devices", [None, "0,0"])
+def test_faiss_index_glue(tmp_path, oracle, devices):
+    """The FaissIndex glue (EnsureGpuIndex / InvalidateGpuIndex / Search, src/faiss_index.cpp:108-153,
+    708-762) over the CUDA backend: an append drops the GPU copy and the NEXT search uploads it
+    again; deleted labels are skipped and k results still come back; SearchBatch answers all
+    queries with one search(n, ...) call and agrees with one Search per query."""
+    rng = np.random.default_rng(8)
+    d, n, n0, nq, k = 128, 4000, 3000, 11, 6
+    xb = rng.uniform(-1, 1, (n, d)).astype(np.float32)
+    xq = rng.uniform(-1, 1, (nq, d)).astype(np.float32)
+    xq[0] = xb[3600] + np.float32(1e-3)        # its best hit arrives with the append
+    Dfull, Ifull = oracle.flat_search(xb, xq, k + 4, oracle.METRIC_L2)
+    tomb = np.array([Ifull[1, 0], Ifull[2, 1], Ifull[2, 2], 3500], np.int64)   # best hits of some queries
+    inp, out = tmp_path / "in.bin", tmp_path / "out.bin"
+    with open(inp, "wb") as f:
+        f.write(np.array([d, n, nq, k, 1, n0, len(tomb)], np.int64).tobytes())
+        f.write(xb.tobytes()); f.write(xq.tobytes()); f.write(tomb.tobytes())
+    env = dict(os.environ)
+    env.pop("ANN_CUDA_DEVICES", None)
+    if devices:
+        env["ANN_CUDA_DEVICES"] = devices
+    res = subprocess.run([DRIVER, "glue", str(inp), str(out), "auto"], capture_output=True, text=True, timeout=300, env=env)
+    assert res.returncode == 0, res.stderr
+    info = json.loads(res.stdout.strip().splitlines()[-1])
+    assert info == {"on_gpu_after_build": 1, "on_gpu_after_append": 0, "on_gpu_at_end": 1, "gpu_uploads": 2,
+                    "wrong_dimension_is_empty": 1}
+    raw = np.frombuffer(open(out, "rb").read(), np.uint8)
+    blocks, o = [], 0
+    for _ in range(4):
+        D = raw[o:o + nq * k * 4].view(np.float32).reshape(nq, k); o += nq * k * 4
+        I = raw[o:o + nq * k * 8].view(np.int64).reshape(nq, k); o += nq * k * 8
+        blocks.append((D, I))
+    # before the append: the first n0 rows
+    Dref, Iref = oracle.flat_search(xb[:n0], xq, k, oracle.METRIC_L2)
+    for D, I in blocks[:2]:
+        assert_topk_matches(oracle, xb[:n0], xq, oracle.METRIC_L2, D, I, Dref, Iref, "glue, before the append")
+    np.testing.assert_array_equal(blocks[0][1], blocks[1][1])
+    # after: all rows, minus the deleted labels
+    Dw = np.empty((nq, k), np.float32); Iw = np.empty((nq, k), np.int64)
+    for q in range(nq):
+        keep = [j for j in range(k + 4) if Ifull[q, j] not in set(tomb.tolist())][:k]
+        Dw[q], Iw[q] = Dfull[q, keep], Ifull[q, keep]
+    for D, I in blocks[2:]:
+        assert not np.isin(I, tomb).any()
+        np.testing.assert_array_equal(I, Iw)
+        np.testing.assert_allclose(D, Dw, rtol=1e-4)
+    np.testing.assert_array_equal(blocks[2][0], blocks[3][0])
+    assert blocks[2][1][0, 0] == 3600 and 3600 not in blocks[0][1][0]
