@@ -360,9 +360,10 @@ class FlatWorkload:
                     if lab < 0:
                         continue
                     lab = int(lab) + self.lo
+                    do = float(do)
                     better = (do - kth) if ip else (kth - do)
                     if lab in reported:
-                        oerr = max(oerr, abs(reported[lab] - do) / max(abs(do), 1e-30))
+                        oerr = max(oerr, float(abs(reported[lab] - do) / max(abs(do), 1e-30)))
                     elif better > 2 * RTOL * abs(kth):
                         missing += 1
             res.update({"oracle_rows": int(rows), "oracle_missing": missing, "oracle_max_rel_err": oerr})
@@ -811,6 +812,13 @@ def run_reference(args, wl):
     print(json.dumps(line))
 
 
+def _json_default(o):
+    """numpy scalars in the line (counts, errors) as plain numbers"""
+    if isinstance(o, np.generic):
+        return o.item()
+    raise TypeError(f"{type(o).__name__} is not JSON serializable")
+
+
 DEFAULT_STEPS = {"flat_ip_20m": 5, "flat_l2_100k": 50, "ivf_1m": 10, "batch_c2": 100, "sq8_c5": 100}
 
 
@@ -991,7 +999,7 @@ def main():
             ok = ok and sub["parity_check"]["ok"]
             line["workloads"][name] = sub
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line, default=_json_default))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

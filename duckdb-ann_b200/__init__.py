@@ -124,6 +124,14 @@ SIGNATURES = {
     "diskann_cuda_batch_distances_by_id": (C.c_int, [_P, _P, C.c_int, _P, _P, C.c_int, C.c_int, _P]),
     "diskann_cuda_batch_distances_by_id_device": (C.c_int, [_P, _P, C.c_int, _P, _P, C.c_int, C.c_int, _P, _P]),
     "diskann_cuda_batch_distances_by_id_device_multi": (C.c_int, [_P, _P, C.c_int, C.c_int, _P]),
+    "diskann_cuda_searcher_last_error": (C.c_char_p, []),
+    "diskann_cuda_searcher_open": (C.c_int, [C.c_int, _P, C.c_size_t, C.c_int, C.POINTER(_P)]),
+    "diskann_cuda_searcher_close": (None, [_P]),
+    "diskann_cuda_searcher_info": (C.c_int, [_P, _P]),
+    "diskann_cuda_searcher_search_batch": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P]),
+    "diskann_cuda_searcher_stats": (C.c_int, [_P, _P, _P, _P]),
+    "diskann_cuda_searcher_set_trace": (None, [_P, C.c_int]),
+    "diskann_cuda_searcher_trace": (_I64, [_P, _P, _P, _P, _I64, _I64]),
 }
 
 
@@ -138,7 +146,8 @@ def last_error() -> str:
     l = lib()
     a = (l.ann_cuda_last_error() or b"").decode()
     b = (l.diskann_cuda_last_error() or b"").decode()
-    return a or b
+    c = (l.diskann_cuda_searcher_last_error() or b"").decode()
+    return a or c or b
 
 
 def check(rc: int, what: str) -> None:

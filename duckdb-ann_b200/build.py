@@ -27,7 +27,7 @@ LIB = os.path.join(HERE, "libann_cuda.so")
 DRIVER = os.path.join(HERE, "backend_driver")
 
 LIB_SOURCES = ["prep.cu", "scan.cu", "merge.cu", "flat_tc.cu", "flat_tc_bk32.cu", "index.cu", "sharded.cu",
-               "cuda_diskann_bridge.cu", "gpu_backend_cuda.cu"]
+               "cuda_diskann_bridge.cu", "disk_search.cu", "gpu_backend_cuda.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # /usr/bin/g++ is the system compiler; the image's $CXX points at a gcc without OpenMP support files
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", INCLUDE, "-I", CSRC,

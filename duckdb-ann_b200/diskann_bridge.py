@@ -233,3 +233,64 @@ class DeviceTable:
             self.close()
         except Exception:
             pass
+
+
+class DiskSearcher:
+    """Lock-step batched graph search over a ".diskann" image whose vectors live in GPU memory:
+    DiskProvider::search_batch (rust_lib/src/disk_provider.rs:470-652) with the neighbour rows named
+    by id (diskann_cuda_searcher_*)."""
+
+    def __init__(self, image: bytes, device: int = 0, use_sq8: bool = False):
+        self._h = C.c_void_p()
+        self._image = bytes(image)
+        p = _pkg()
+        p.check(p.lib().diskann_cuda_searcher_open(device, self._image, len(self._image), int(use_sq8), C.byref(self._h)),
+                "DiskSearcher")
+        self.info = IndexInfo()
+        p.check(p.lib().diskann_cuda_searcher_info(self._h, C.byref(self.info)), "DiskSearcher info")
+
+    def search_batch(self, queries, k: int, l_search: int):
+        """-> list of (ids uint64, distances float32) per query, best first."""
+        q = np.ascontiguousarray(queries, np.float32)
+        nq = q.shape[0]
+        ids = np.zeros((nq, max(k, 1)), np.uint64)
+        dist = np.zeros((nq, max(k, 1)), np.float32)
+        counts = np.zeros(nq, np.int32)
+        p = _pkg()
+        p.check(p.lib().diskann_cuda_searcher_search_batch(self._h, _p(q), nq, k, l_search, _p(ids), _p(dist), _p(counts)),
+                "search_batch")
+        return [(ids[i, :counts[i]].copy(), dist[i, :counts[i]].copy()) for i in range(nq)]
+
+    def stats(self) -> dict:
+        it, pairs, calls = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        p = _pkg()
+        p.check(p.lib().diskann_cuda_searcher_stats(self._h, C.byref(it), C.byref(pairs), C.byref(calls)), "stats")
+        return {"iterations": it.value, "pairs_scored": pairs.value, "distance_calls": calls.value}
+
+    def set_trace(self, on: bool) -> None:
+        _pkg().lib().diskann_cuda_searcher_set_trace(self._h, int(on))
+
+    def trace(self):
+        """The id batches of the last traced search: list of (ids uint32, query_map uint32)."""
+        lib = _pkg().lib()
+        nb = lib.diskann_cuda_searcher_trace(self._h, None, None, None, 0, 0)
+        if nb <= 0:
+            return []
+        st = self.stats()
+        ids = np.empty(st["pairs_scored"], np.uint32)
+        qm = np.empty(st["pairs_scored"], np.uint32)
+        off = np.empty(nb + 1, np.uint64)
+        got = lib.diskann_cuda_searcher_trace(self._h, _p(ids), _p(qm), _p(off), len(ids), nb)
+        _pkg().check(0 if got == nb else -1, "trace")
+        return [(ids[int(off[i]):int(off[i + 1])], qm[int(off[i]):int(off[i + 1])]) for i in range(nb)]
+
+    def close(self) -> None:
+        if self._h:
+            _pkg().lib().diskann_cuda_searcher_close(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

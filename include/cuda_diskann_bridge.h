@@ -155,6 +155,35 @@ int diskann_cuda_load_index(int device, const void *image, size_t len, diskann_c
 int diskann_cuda_load_index_file(int device, const char *path, diskann_cuda_index_info *info,
                                  diskann_cuda_table **vectors, diskann_cuda_table **sq8);
 
+/* ---- the search loop that feeds the by-id entry points ------------------------------------
+ * DiskProvider::search_batch (rust_lib/src/disk_provider.rs:470-652; the in-memory provider
+ * has the same loop, rust_lib/src/provider.rs:333-427) over an image whose vectors were loaded
+ * into GPU memory: every iteration each active query pops its best candidate and the unvisited
+ * neighbours of all of them are scored by ONE by-id batch-distance call.  The reference's loop
+ * gathers the neighbour rows on the host instead (:592-600); its Rust form cannot be compiled
+ * here, so this C++ restatement is the caller the by-id path is tested and measured with.
+ * The graph (adjacency, entry points) is copied out of the image and stays on the host. */
+typedef struct diskann_cuda_searcher diskann_cuda_searcher;
+const char *diskann_cuda_searcher_last_error(void);
+/* use_sq8 != 0: score against the SQ8 codes of the image's trailer (asymmetric distance). */
+int diskann_cuda_searcher_open(int device, const void *image, size_t len, int use_sq8, diskann_cuda_searcher **out);
+void diskann_cuda_searcher_close(diskann_cuda_searcher *searcher);
+int diskann_cuda_searcher_info(const diskann_cuda_searcher *searcher, diskann_cuda_index_info *info);
+/* queries: nq x dim (host).  out_ids / out_distances: nq x k; out_counts[q] = results of query q
+ * (min(k, rows reached)), best first; distances as the batch-distance ABI returns them (squared L2,
+ * negated dot).  l_search is raised to k as in the reference (:486). */
+int diskann_cuda_searcher_search_batch(diskann_cuda_searcher *searcher, const float *queries, int nq, int k, int l_search,
+                                       uint64_t *out_ids, float *out_distances, int *out_counts);
+/* Iterations, (query, row) pairs scored and batch-distance calls of the last search. */
+int diskann_cuda_searcher_stats(const diskann_cuda_searcher *searcher, uint64_t *iterations, uint64_t *pairs_scored,
+                                uint64_t *distance_calls);
+/* With tracing on, a search records the id batch of every distance call; _trace returns the number
+ * of batches and, when the arrays are given, copies ids / query_map (all batches back to back) and
+ * offsets (batches + 1 entries).  The batches a real search produces, for workload generation. */
+void diskann_cuda_searcher_set_trace(diskann_cuda_searcher *searcher, int on);
+int64_t diskann_cuda_searcher_trace(const diskann_cuda_searcher *searcher, uint32_t *ids, uint32_t *query_map,
+                                    uint64_t *offsets, int64_t max_pairs, int64_t max_batches);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -348,3 +348,79 @@ def parse_diskann_image(image: bytes) -> dict:
         codes = np.frombuffer(image, np.uint8, qlen, p + sq_dim * 8).reshape(n, sq_dim)
         res["sq8"] = (mins, scale, codes)
     return res
+
+
+def disk_search_batch(image: bytes, queries, k: int, l_search: int, use_sq8: bool = False):
+    """Restates DiskProvider::search_batch (rust_lib/src/disk_provider.rs:470-652) with its
+    insert_result (:655-678): lock-step best-first search, one popped candidate per active query and
+    iteration, the unvisited neighbours of all of them scored together.  Distances in double
+    (`exact`), squared L2 or negated dot as rust_lib/src/distance.rs:15-25 returns them.  Pure
+    Python loops: small cases only.  Returns a list of (ids, distances) per query."""
+    import bisect
+    import heapq
+    im = parse_diskann_image(image)
+    n, deg, metric = im["num_vectors"], im["max_degree"], (BATCH_L2 if im["metric"] == 0 else BATCH_IP)
+    queries = _f32(queries)
+    nq = queries.shape[0]
+    if nq == 0 or n == 0 or k <= 0:
+        return [(np.zeros(0, np.uint64), np.zeros(0, np.float32)) for _ in range(nq)]
+    k = min(k, n)
+    l = max(l_search, k)
+    if use_sq8:
+        mins, scale, codes = im["sq8"]
+
+    def score(ids, qmap):
+        ids, qmap = np.asarray(ids, np.uint32), np.asarray(qmap, np.uint32)
+        if use_sq8:
+            return sq8_batch_distances_by_id(codes, mins, scale, queries, ids, qmap, metric, exact=True)
+        return batch_distances_by_id(im["vectors"], queries, ids, qmap, metric, exact=True)
+
+    visited = [set() for _ in range(nq)]
+    cands = [[] for _ in range(nq)]
+    result = [[] for _ in range(nq)]      # sorted (dist, id), at most l
+    active = [True] * nq
+    ids, qmap = [], []
+    for q in range(nq):
+        for ep in im["entry_points"].tolist():
+            if ep < n and ep not in visited[q]:
+                visited[q].add(ep)
+                ids.append(ep); qmap.append(q)
+    for d, i, q in zip(score(ids, qmap).tolist() if ids else [], ids, qmap):
+        d = float(np.float32(d))
+        heapq.heappush(cands[q], (d, i))
+        result[q].append((d, i))
+    for q in range(nq):
+        result[q].sort(key=lambda t: t[0])
+    while True:
+        ids, qmap = [], []
+        any_active = False
+        for q in range(nq):
+            if not active[q]:
+                continue
+            if not cands[q]:
+                active[q] = False
+                continue
+            c_dist, c_id = heapq.heappop(cands[q])
+            if len(result[q]) >= l and c_dist > result[q][l - 1][0]:
+                active[q] = False
+                continue
+            any_active = True
+            for v in im["adjacency"][c_id].tolist():
+                if v >= n or v in visited[q]:
+                    continue
+                visited[q].add(v)
+                ids.append(v); qmap.append(q)
+        if not any_active:
+            break
+        if not ids:
+            continue
+        for d, i, q in zip(score(ids, qmap).tolist(), ids, qmap):
+            d = float(np.float32(d))
+            r = result[q]
+            if len(r) < l or d < r[-1][0]:
+                pos = bisect.bisect_left([t[0] for t in r], d)
+                r.insert(pos, (d, i))
+                del r[l:]
+                heapq.heappush(cands[q], (d, i))
+    return [(np.array([t[1] for t in result[q][:k]], np.uint64), np.array([t[0] for t in result[q][:k]], np.float32))
+            for q in range(nq)]

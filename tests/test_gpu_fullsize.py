@@ -75,12 +75,13 @@ def test_screening_chosen_by_the_library_at_two_million_rows(pkg, oracle, kind, 
     Dref, Iref = oracle.flat_search(xb, xq[sample], k, om)
     assert_topk_matches(oracle, xb, xq[sample], om, D[sample], I[sample], Dref, Iref,
                         f"screened by the library's own choice, {metric_name}, 2.1M x 768")
-    # Unit-norm rows: the screened search answers by itself.  The shifted store is its hard case (the
-    # error band scales with |q - mean| |x|max, and |x|max is twelve times the spread of the rows):
-    # some queries have more rows inside the one-MMA band than the spare holds, and the block moves to
-    # the split product - once per entry point, never on to the exact scan.
+    # Unit-norm rows: the screened search answers by itself.  The shifted store is the hard case of
+    # the tensor-core tiers: their proven error bands scale with |q - mean| |x|max, and |x|max is twelve
+    # times the spread of the rows here, so at d = 768 even the split product's band (0.75 on squared
+    # distances of ~78) holds ~240 rows above the 100th - about what a banded list can keep.  Queries
+    # that exceed it send the block on, up to the exact scan: at most two passes more per entry point.
     fell_back = pkg.lib().ann_cuda_screen_fallbacks() - before
-    assert fell_back <= (0 if kind == "unit" else 2), f"{fell_back} fallback passes"
+    assert fell_back <= (0 if kind == "unit" else 4), f"{fell_back} fallback passes"
     idx.close()
 
 
