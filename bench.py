@@ -953,6 +953,58 @@ def run_workload(args, name, steps, ctx, with_cpu_baseline):
     return line
 
 
+def run_single_process(args, ctx, devices, steps):
+    """The headline workload through ONE index object spread over `devices` in this process
+    (ann_cuda_sharded_*: what CudaGpuBackend::CpuToGpu hands out when ANN_CUDA_DEVICES names several
+    devices): host queries in, host results out, one host thread and stream per shard, per-shard
+    lists copied into the first device and merged there.  Wall clock around the synchronous call."""
+    torch, pkg = ctx["torch"], ctx["pkg"]
+    wl = make_workload("flat_ip_20m", args.scale)
+    G = len(devices)
+    idx = pkg.CudaShardedIndex(wl.d, pkg.METRIC_INNER_PRODUCT, devices)
+    t0 = time.perf_counter()
+    for g, dev in enumerate(devices):
+        lo, hi = pkg.sharded.row_range(wl.n, g, G)
+        if hi <= lo:
+            continue
+        device = torch.device("cuda", dev)
+        shard = idx.shard(g)
+        shard.reserve(hi - lo)
+        for c in range(lo // wl.chunk, (hi - 1) // wl.chunk + 1):
+            x = wl.gen_chunk(c, device, torch)
+            a, b = max(lo, c * wl.chunk) - c * wl.chunk, min(hi, (c + 1) * wl.chunk) - c * wl.chunk
+            shard.add_device(x[a:b].contiguous())
+            del x
+    for dev in set(devices):
+        torch.cuda.synchronize(dev)
+    setup_s = time.perf_counter() - t0
+    assert idx.ntotal == wl.n
+    q = wl.queries_host(torch).numpy()
+    for _ in range(max(args.warmup, 3)):
+        D, I = idx.search(q, wl.k)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        D, I = idx.search(q, wl.k)
+    dt = (time.perf_counter() - t0) / steps
+    # parity: a sample of the queries through the exact-fp32 scan kernels of the same shards
+    sample = np.unique(np.linspace(0, wl.nq - 1, 32).astype(np.int64))
+    lib = pkg.lib()
+    assert lib.ann_cuda_set_flat_kernel(b"simt") == 0
+    try:
+        Ds, Is = idx.search(q[sample], wl.k)
+    finally:
+        lib.ann_cuda_set_flat_kernel(b"tcgen05")
+    mism, err = compare_topk(D[sample], I[sample], Ds, Is, True)
+    idx.close()
+    for dev in set(devices):
+        with torch.cuda.device(dev):
+            torch.cuda.empty_cache()
+    return {"value": wl.nq / dt, "unit": wl.unit, "ms_per_step": 1e3 * dt, "devices": list(devices), "steps": steps,
+            "setup_s": setup_s, "what": "one process, one index object over all devices (host pointers in and out)",
+            "parity_check": {"queries": int(len(sample)), "id_mismatches": mism, "max_rel_err": err,
+                             "against": "exact-fp32 scan kernels over the same shards", "ok": bool(mism == 0 and err <= RTOL)}}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -965,6 +1017,9 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="shrinks the row counts (debugging / profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="headline workload only")
+    ap.add_argument("--single-process", default=None, metavar="DEVICES",
+                    help="also time the headline workload through one sharded index object in ONE process over these "
+                         "devices, e.g. 0,1,2,3 (default under torchrun: all ranks' devices, run by rank 0)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     headline = args.workload or "flat_ip_20m"
@@ -998,6 +1053,15 @@ def main():
             sub = run_workload(args, name, DEFAULT_STEPS[name], ctx, not args.no_cpu_baseline)
             ok = ok and sub["parity_check"]["ok"]
             line["workloads"][name] = sub
+    # the same headline search from ONE process that owns an index over all the devices (the form a
+    # DuckDB process uses); the other ranks have released their memory and wait
+    single = args.single_process.split(",") if args.single_process else ([str(i) for i in range(world)] if world > 1 else None)
+    if single and args.workload is None:
+        if world > 1:
+            dist.barrier()
+        if rank == 0:
+            line["single_process"] = run_single_process(args, ctx, [int(v) for v in single], steps)
+            ok = ok and line["single_process"]["parity_check"]["ok"]
     if rank == 0:
         print(json.dumps(line, default=_json_default))
     if world > 1:

@@ -97,7 +97,7 @@ constexpr uint64_t kDescSbo = (8 * kRowBytes) >> 4;         // 8-row group strid
 constexpr int kABytes = BM * BK * 4;                    // 16 KB
 constexpr int kBBytes = BN * BK * 4;                    // 32 KB
 constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;  // hi + lo of both operands: 96 KB
-constexpr int kQueueDepth = 16;   // per-row candidate queue, also the small-k list capacity
+constexpr int kQueueDepth = kSmemListMax;   // per-row candidate queue, also the small-k list capacity
 constexpr int kThreads = 192;
 constexpr int kPaceSpins = 10000;  // polls of ~100 ns a CTA of the static schedule waits for the others, once
 constexpr int kWorkRing = 4;       // chunk descriptors in flight between the scheduler and the other roles
@@ -240,6 +240,15 @@ __device__ __forceinline__ void st_global_if(bool p, int32_t *addr, int32_t v) {
     asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %0, 0;\n\t@q st.global.s32 [%1], %2;\n\t}" ::"r"((int)p), "l"(addr),
                  "r"(v)
                  : "memory");
+}
+
+// One append: key and row number stored together, or not at all (one predicate for both).
+__device__ __forceinline__ void st_global_pair_if(bool p, float *kaddr, float key, int32_t *iaddr, int32_t idx) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %0, 0;\n\t@q st.global.f32 [%1], %2;\n\t@q st.global.s32 [%3], %4;\n\t}" ::"r"(
+            (int)p),
+        "l"(kaddr), "f"(key), "l"(iaddr), "r"(idx)
+        : "memory");
 }
 
 // ---- selection helpers ------------------------------------------------------------------------
@@ -472,7 +481,88 @@ __device__ __forceinline__ float compact_one(float *bk, int32_t *bi, int c, int 
     return kth;
 }
 
-// Compacts the append buffers of the rows in `need` (bit r = row row0 + r of this warp) down to
+// Compaction of a full append buffer (up to 512 entries) WITHOUT sorting it.  A radix select over
+// the order-preserving integer images of the keys (two bits per round, the three counters of a
+// round packed into one warp reduction) finds the k_rank-th smallest key; everything within
+// `slack` of it moves to the front of the buffer, in no particular order, the rest is dropped.
+// ~2.5k cycles against ~14k for the 512-wide sorting network - and a row is compacted five or six
+// times per list.  Returns the k_rank-th key; kept = entries that stay, or -1 when more than k lie
+// inside the band (the caller then takes the sorting path, which cuts at k).
+__device__ __forceinline__ float select_one(float *bk, int32_t *bi, int c, int k, int k_rank, float slack, int lane,
+                                            int &kept) {
+    constexpr int E = 16;
+    uint32_t key[E];
+    int32_t idx[E];
+#pragma unroll
+    for (int v = 0; v < E / 4; v++) {
+        const float4 kk = *reinterpret_cast<const float4 *>(bk + lane * E + v * 4);
+        const int4 ii = *reinterpret_cast<const int4 *>(bi + lane * E + v * 4);
+        key[v * 4 + 0] = float_to_ordered(kk.x); key[v * 4 + 1] = float_to_ordered(kk.y);
+        key[v * 4 + 2] = float_to_ordered(kk.z); key[v * 4 + 3] = float_to_ordered(kk.w);
+        idx[v * 4 + 0] = ii.x; idx[v * 4 + 1] = ii.y; idx[v * 4 + 2] = ii.z; idx[v * 4 + 3] = ii.w;
+    }
+#pragma unroll
+    for (int i = 0; i < E; i++) {
+        const bool stale = lane * E + i >= c;  // slots past the fill hold old data
+        key[i] = stale ? 0xffffffffu : key[i];
+        idx[i] = stale ? -1 : idx[i];
+    }
+    if (c < k_rank) {  // fewer entries than the rank asked for: no threshold yet, everything stays (warp-uniform)
+        kept = c;
+        return kInf;
+    }
+    uint32_t prefix = 0;
+    int need = k_rank;  // rank of the wanted key among the entries that match the prefix so far
+#pragma unroll 1
+    for (int shift = 30; shift >= 0; shift -= 2) {
+        const uint32_t hi_mask = shift == 30 ? 0u : (0xffffffffu << (shift + 2));
+        uint32_t packed = 0;  // counts of digits 0, 1, 2 among the matching entries, 10 bits each
+#pragma unroll
+        for (int i = 0; i < E; i++) {
+            const uint32_t digit = (key[i] >> shift) & 3u;
+            const uint32_t one = ((key[i] & hi_mask) == prefix && digit != 3u) ? (1u << (10u * digit)) : 0u;
+            packed += one;
+        }
+        packed = __reduce_add_sync(kFullMask, packed);
+        const int c0 = (int)(packed & 1023u), c1 = (int)((packed >> 10) & 1023u), c2 = (int)((packed >> 20) & 1023u);
+        uint32_t digit;
+        if (need <= c0) digit = 0;
+        else if (need <= c0 + c1) { digit = 1; need -= c0; }
+        else if (need <= c0 + c1 + c2) { digit = 2; need -= c0 + c1; }
+        else { digit = 3; need -= c0 + c1 + c2; }
+        prefix |= digit << shift;
+    }
+    const float kth = ordered_to_float(prefix);
+    const uint32_t cut = float_to_ordered(kth + slack);
+    int mine = 0;
+#pragma unroll
+    for (int i = 0; i < E; i++) mine += (idx[i] >= 0 && key[i] <= cut) ? 1 : 0;
+    const int total = __reduce_add_sync(kFullMask, mine);
+    if (total > k) {
+        kept = -1;
+        return kth;
+    }
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(kFullMask, incl, o);
+        incl += lane >= o ? t : 0;
+    }
+    int pos = incl - mine;
+    __syncwarp();  // every lane holds its part of the buffer in registers before anything is overwritten
+#pragma unroll
+    for (int i = 0; i < E; i++) {
+        const bool keep = idx[i] >= 0 && key[i] <= cut;
+        st_global_if(keep, bk + pos, ordered_to_float(key[i]));
+        st_global_if(keep, bi + pos, idx[i]);
+        pos += keep ? 1 : 0;
+    }
+    kept = total;
+    return kth;
+}
+
+// Compacts the append buffers of the rows in `need` (bit r = row row0 + r of this warp): a full
+// buffer by select_one (unsorted), a partly filled one (and a band that holds more than k) down to
 // their best k, sorted.  The sort is as wide as the row's fill needs: a full buffer takes the
 // 512-wide network (~14k cycles); the few dozen entries typical when a list is closed behind a
 // tight threshold take the 32- or 64-wide one (a few hundred cycles).
@@ -488,8 +578,10 @@ __device__ __noinline__ void compact_rows(float *slot_key, int32_t *slot_idx, in
         int32_t *bi = slot_idx + (size_t)(row0 + r) * kBuf;
         float kth;
         int kept;
-        if (c > 256) kth = compact_one<16>(bk, bi, c, k, k_rank, slack, lane, kept);
-        else if (c > 128) kth = compact_one<8>(bk, bi, c, k, k_rank, slack, lane, kept);
+        if (c > 256) {
+            kth = select_one(bk, bi, c, k, k_rank, slack, lane, kept);
+            if (kept < 0) kth = compact_one<16>(bk, bi, c, k, k_rank, slack, lane, kept);
+        } else if (c > 128) kth = compact_one<8>(bk, bi, c, k, k_rank, slack, lane, kept);
         else if (c > 64) kth = compact_one<4>(bk, bi, c, k, k_rank, slack, lane, kept);
         else if (c > 32) kth = compact_one<2>(bk, bi, c, k, k_rank, slack, lane, kept);
         else kth = compact_one<1>(bk, bi, c, k, k_rank, slack, lane, kept);
@@ -827,6 +919,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             if (APPEND && args.part_cnt) {
                 // the per-query merge sees the final threshold of the query and throws most of
                 // these entries away before it sorts: nothing to do here but say how many there are
+                // (flat search: index = list slot * 128 + row as well)
                 args.part_cnt[(size_t)cur_slot * BM + row] = row_valid ? cnt : 0;
             } else if (APPEND) {
                 const unsigned need = __ballot_sync(kFullMask, cnt > 0);
@@ -978,14 +1071,30 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         }
                         if (kdebug(args) & 4) mask = 0;
                         if (kstats(args) && mask) atomicAdd(kstats(args) + kStatAppends, (unsigned long long)__popc(mask));
-                        // predicated appends: no branch per column, nothing stored where the bit is clear
+                        // Appends, column by column, for the columns in which SOME row of the warp has a
+                        // hit (about four of the 32 once the thresholds have settled; a row has about one
+                        // hit per tile).  The loop and the jump on the column number are warp-uniform;
+                        // inside a case the column is a compile-time register index.  Walking all 32
+                        // columns with predicated stores cost ~10 instructions per column whether or not
+                        // anything was stored, and made the epilogue as long as the MMAs of the tile.
                         float *bk = unit_key + (size_t)row * kBuf;
                         int32_t *bi = unit_idx + (size_t)row * kBuf;
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
+                        uint32_t cols = __reduce_or_sync(kFullMask, mask);
+                        while (cols) {
+                            const int j = __ffs(cols) - 1;
+                            cols &= cols - 1;
+                            float kj = 0.f;
+                            switch (j) {
+#define ANN_COL(J) case J: kj = key_of(raw, g, J); break;
+                                ANN_COL(0) ANN_COL(1) ANN_COL(2) ANN_COL(3) ANN_COL(4) ANN_COL(5) ANN_COL(6) ANN_COL(7)
+                                ANN_COL(8) ANN_COL(9) ANN_COL(10) ANN_COL(11) ANN_COL(12) ANN_COL(13) ANN_COL(14) ANN_COL(15)
+                                ANN_COL(16) ANN_COL(17) ANN_COL(18) ANN_COL(19) ANN_COL(20) ANN_COL(21) ANN_COL(22) ANN_COL(23)
+                                ANN_COL(24) ANN_COL(25) ANN_COL(26) ANN_COL(27) ANN_COL(28) ANN_COL(29) ANN_COL(30) ANN_COL(31)
+#undef ANN_COL
+                                default: break;
+                            }
                             const bool p = (mask >> j) & 1u;
-                            st_global_if(p, bk + cnt, key_of(raw, g, j));
-                            st_global_if(p, bi + cnt, colg + j);
+                            st_global_pair_if(p, bk + cnt, kj, bi + cnt, colg + j);
                             cnt += p ? 1 : 0;
                         }
                     } else if (SMALLK) {
@@ -1216,7 +1325,7 @@ FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms) {
 int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
                    int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
-                   const GroupedWork *grouped, const ScreenInput *screen, const int *gate) {
+                   const GroupedWork *grouped, const ScreenInput *screen, const int *gate, int32_t *flat_part_cnt) {
     (void)device;
     if (n <= 0 || nq <= 0) return 0;
     static_assert(kMaxListK <= 66 * 32, "the widest replace-max list covers every list length");
@@ -1224,9 +1333,9 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
 #ifndef ANN_TC_VARIANT_BK32
     // the screened (one-MMA) search runs in the build of this file with K blocks of 32 floats
     if (screen && screen->one_mma && !grouped && screen->k_rank >= 1 && screen->k_rank <= k && k <= kScreenMaxList &&
-        dp % 32 == 0)
+        k > kSmemListMax && dp % 32 == 0)
         return launch_flat_tc_bk32(plan, xhi, xlo, xnorm, n, qhi, qlo, nq, dp, k, metric, part_key, part_idx, qtau, sched,
-                                   status, device, stream, grouped, screen, gate);
+                                   status, device, stream, grouped, screen, gate, flat_part_cnt);
 #endif
     if (dp % BK != 0) return set_error("padded dimension must be a multiple of %d", BK);
     if (n > 0x7fffffffll - BN) return set_error("a flat shard holds at most 2^31 rows");
@@ -1261,8 +1370,9 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     a.slot_cnt = a.arrivals + plan.static_chunks;
     a.qrow_query = grouped ? grouped->qrow_query : nullptr;
     a.qrow_const = grouped ? grouped->qrow_const : nullptr;
-    a.part_cnt = grouped ? grouped->part_cnt : nullptr;
-    const bool use_band = screen && !grouped && screen->k_rank >= 1 && screen->k_rank <= k && k <= kScreenMaxList;
+    a.part_cnt = grouped ? grouped->part_cnt : flat_part_cnt;
+    const bool use_band = screen && !grouped && screen->k_rank >= 1 && screen->k_rank <= k && k <= kScreenMaxList &&
+                          k > kQueueDepth;  // banded lists are append buffers
     const bool use_screen = use_band && screen->one_mma;
     a.screen = use_screen ? 1 : 0;
     a.banded = use_band ? 1 : 0;

@@ -375,9 +375,17 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
             return -1;
         ANN_CUDA_TRY(cudaMemsetAsync(ws.qtau.ptr, 0xFF, qtau_bytes, stream));  // "no threshold yet"
         ANN_CUDA_TRY(cudaMemsetAsync(ws.sched.ptr, 0, sched_bytes, stream));
-        // every list empty: index -1 in the k slots the merge reads of each row
-        ANN_CUDA_TRY(cudaMemset2DAsync(ws.part_idx.ptr, (size_t)plan.list_stride * 4, 0xFF, (size_t)k * 4,
-                                       plan.part_entries / plan.list_stride, stream));
+        // Append selection: a list is the first part_cnt entries of its row's buffer, unsorted - every
+        // list empty means every count zero.  Other selections: index -1 in the k slots the merge reads.
+        const bool append = plan.lists_sorted;
+        const size_t cnt_bytes = (size_t)plan.nq_tiles * plan.lists_per_qt * 128 * 4;
+        if (append) {
+            if (ws.part_cnt.ensure(cnt_bytes)) return -1;
+            ANN_CUDA_TRY(cudaMemsetAsync(ws.part_cnt.ptr, 0, cnt_bytes, stream));
+        } else {
+            ANN_CUDA_TRY(cudaMemset2DAsync(ws.part_idx.ptr, (size_t)plan.list_stride * 4, 0xFF, (size_t)k * 4,
+                                           plan.part_entries / plan.list_stride, stream));
+        }
         const bool timing = !o.gate && g_time_kernels.load(std::memory_order_relaxed) != 0;
         if (timing) {
             if (!ws.ev0) {
@@ -389,16 +397,21 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         if (launch_flat_tc(plan, st.hi, st.lo, st.norms, st.n, ws.qhi.as<float>(), ws.qlo.as<float>(), nq, dp, k,
                            ix.metric, ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.qtau.as<uint32_t>(),
                            ws.sched.as<int>(), status + kStatusWait, ix.device, stream, nullptr,
-                           o.k_rank > 0 ? &screen : nullptr, o.gate))
+                           o.k_rank > 0 ? &screen : nullptr, o.gate, append ? ws.part_cnt.as<int32_t>() : nullptr))
             return -1;
         if (timing) {
             ANN_CUDA_TRY(cudaEventRecord(ws.ev1, stream));
             ws.timed = true;
             ix.last_timed_ws = &ws;
         }
-        if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 0, ws.sched.as<int>() + plan.nq_tiles,
-                               nullptr, plan.lists_per_qt, nq, k, plan.list_stride, ws.sel_key.as<float>(),
-                               ws.sel_idx.as<int32_t>(), ix.device, stream, plan.lists_sorted, nullptr, o.gate))
+        // per query: the lists of its query tile, filtered by the query's final threshold, sorted once
+        if (append ? launch_merge_filtered(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.part_cnt.as<int32_t>(), nullptr,
+                                           nullptr, ws.qtau.as<uint32_t>(), plan.lists_per_qt, nq, k, plan.list_stride,
+                                           ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), stream,
+                                           ws.sched.as<int>() + plan.nq_tiles, o.gate)
+                   : launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 0, ws.sched.as<int>() + plan.nq_tiles,
+                                        nullptr, plan.lists_per_qt, nq, k, plan.list_stride, ws.sel_key.as<float>(),
+                                        ws.sel_idx.as<int32_t>(), ix.device, stream, false, nullptr, o.gate))
             return -1;
         // (a list that holds every row of the store has left nothing out)
         if (o.check_rank > 0 && k < st.n &&
@@ -698,8 +711,11 @@ int ensure_device(const ann_cuda_index *ix, DeviceGuard &g) {
 enum { kTierScreen = 0, kTierSplit = 1, kTierSplitWide = 2, kTierExact = 3 };
 static_assert(kTierExact == kTiers - 1, "tier count");
 
+// Banded lists are append buffers: they need a store of more rows than the shared-memory lists hold
+// (a smaller store fits a list whole and needs no band at all).
 bool banded_lists_fit(const ann_cuda_index &ix, int k_sel) {
-    return k_sel <= kScreenMaxK && ix.store.max_norm2 && std::min<int64_t>(kScreenMaxList, ix.store.n) > k_sel;
+    return k_sel <= kScreenMaxK && ix.store.max_norm2 &&
+           std::min<int64_t>(kScreenMaxList, ix.store.n) > std::max(k_sel, kSmemListMax);
 }
 
 int flat_first_tier(const ann_cuda_index &ix, int k_sel) {

@@ -51,6 +51,7 @@ int launch_pad_rows(const float *x, int64_t n, int d, int dp, float *out, float 
 int launch_join_rows(const float *hi, const float *lo, int64_t n, int d, int dp, float *out, cudaStream_t stream);
 
 // ---- flat_tc.cu --------------------------------------------------------------------------
+constexpr int kSmemListMax = 16;         // lists up to this length are kept in shared memory
 constexpr int kAppendMaxK = 256;         // largest k the append-and-compact selection handles
 constexpr int kMergeCandidates = 16384;  // most (list, slot) candidates per query the merge kernel sorts
 
@@ -76,6 +77,9 @@ FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms);
 // stores of the database (n x dp) and the queries (nq x dp), plus row norms for L2.
 // Writes 128 unsorted lists of k (key, local row) pairs per list slot
 // (slot = query tile * lists_per_qt + j, j < sched[nq_tiles + query tile]).
+// Flat search with the append selection (FlatPlan::lists_sorted) and flat_part_cnt given: a list
+// stays UNSORTED in the first flat_part_cnt[slot * 128 + row] slots of its row's buffer, for
+// launch_merge_filtered (layout 0); nothing has to be cleared in the list memory then.
 // On entry: part_idx all -1 (bytes 0xFF); qtau (nq_tiles * 128 words, the per-query shared
 // threshold) all bytes 0xFF; sched (2 * nq_tiles ints: chunks taken, lists started) all zero.
 // status: device int, set non-zero if a bounded wait inside the kernel ran out.
@@ -128,13 +132,13 @@ int launch_flat_tc(const FlatPlan &plan, const float *xhi, const float *xlo, con
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
                    int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
                    const GroupedWork *grouped = nullptr, const ScreenInput *screen = nullptr,
-                   const int *gate = nullptr);
+                   const int *gate = nullptr, int32_t *flat_part_cnt = nullptr);
 // The same kernel built with K blocks of 32 floats (flat_tc_bk32.cu); launch_flat_tc hands the
 // screened searches to it.
 int launch_flat_tc_bk32(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                         const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
                         int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
-                        const GroupedWork *grouped, const ScreenInput *screen, const int *gate);
+                        const GroupedWork *grouped, const ScreenInput *screen, const int *gate, int32_t *flat_part_cnt);
 // make_flat_plan for a screened search: lists of `k` (up to kScreenMaxList) in append mode
 FlatPlan make_flat_plan_screened(int64_t nq, int64_t n, int k, int sms);
 
@@ -211,10 +215,12 @@ int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layou
 // query's final threshold qtau[q] (ordered-uint form, key + slot_key_offset[row]) are dropped as
 // they are read, so any number of probes can be merged.
 constexpr int kAppendBuffer = 512;
+// With lists_started given (flat search, see launch_flat_tc): the lists of query q are the first
+// min(nparts, lists_started[q / 128]) list slots of its query tile, row q % 128 of each.
 int launch_merge_filtered(const float *part_key, const int32_t *part_idx, const int32_t *part_cnt,
                           const int32_t *slot_of, const float *slot_key_offset, const uint32_t *qtau, int nparts,
                           int64_t nq, int k, int list_stride, float *out_key, int32_t *out_idx,
-                          cudaStream_t stream);
+                          cudaStream_t stream, const int *lists_started = nullptr, const int *gate = nullptr);
 
 // Optional input of launch_refine_finalize: the candidates were ranked by tensor-core keys
 // (key[q * k_sel + j], ascending) under the slack of key_slack; only those within the slack of the

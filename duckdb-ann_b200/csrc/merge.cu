@@ -193,8 +193,10 @@ __global__ void __launch_bounds__(kMergeThreads)
 merge_filtered_kernel(const float *__restrict__ part_key, const int32_t *__restrict__ part_idx,
                       const int32_t *__restrict__ part_cnt, const int32_t *__restrict__ slot_of,
                       const float *__restrict__ slot_key_offset, const uint32_t *__restrict__ qtau, int nparts,
-                      int k, int list_stride, int cap, float *__restrict__ out_key, int32_t *__restrict__ out_idx) {
+                      int k, int list_stride, int cap, float *__restrict__ out_key, int32_t *__restrict__ out_idx,
+                      const int *__restrict__ lists_started, const int *gate) {
     extern __shared__ float smem_f[];
+    if (gate_closed(gate)) return;
     float *keys = smem_f;
     int32_t *vals = reinterpret_cast<int32_t *>(smem_f + cap);
     __shared__ int count;
@@ -221,10 +223,16 @@ merge_filtered_kernel(const float *__restrict__ part_key, const int32_t *__restr
         }
         __syncthreads();
     };
-    for (int p = 0; p < nparts; p++) {
-        const int32_t g = slot_of[q * nparts + p];
+    int nlists = nparts;
+    if (lists_started) {
+        const int started = lists_started[q >> 7];
+        nlists = started < nparts ? started : nparts;
+    }
+    for (int p = 0; p < nlists; p++) {
+        const int64_t g = lists_started ? ((q >> 7) * (int64_t)nparts + p) * 128 + (q & 127) : (int64_t)slot_of[q * nparts + p];
         if (g < 0) continue;  // block-uniform
-        const int c = part_cnt ? part_cnt[g] : list_stride;
+        int c = part_cnt ? part_cnt[g] : list_stride;
+        c = c < list_stride ? c : list_stride;
         const float off = slot_key_offset ? slot_key_offset[g] : 0.f;
         for (int j0 = 0; j0 < c; j0 += blockDim.x) {
             if (count + (int)blockDim.x > cap) shrink();  // block-uniform: count is read after a barrier
@@ -462,7 +470,7 @@ int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layou
 int launch_merge_filtered(const float *part_key, const int32_t *part_idx, const int32_t *part_cnt,
                           const int32_t *slot_of, const float *slot_key_offset, const uint32_t *qtau, int nparts,
                           int64_t nq, int k, int list_stride, float *out_key, int32_t *out_idx,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const int *lists_started, const int *gate) {
     if (nq <= 0) return 0;
     // room for the k kept entries plus one round of reads, as a power of two for the sort
     int cap = kFilterCap;
@@ -471,7 +479,7 @@ int launch_merge_filtered(const float *part_key, const int32_t *part_idx, const 
     if (opt_in_smem(merge_filtered_kernel, smem)) return -1;
     merge_filtered_kernel<<<(unsigned)nq, kMergeThreads, smem, stream>>>(part_key, part_idx, part_cnt, slot_of,
                                                                         slot_key_offset, qtau, nparts, k, list_stride,
-                                                                        cap, out_key, out_idx);
+                                                                        cap, out_key, out_idx, lists_started, gate);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

@@ -47,10 +47,11 @@ def test_flat_rows_sharded(pkg, oracle, metric_name):
         assert idx.get_rows(sizes[0] - 2, 5).tobytes() == xb[sizes[0] - 2:sizes[0] + 3].tobytes()
         with pytest.raises(pkg.AnnCudaError):
             idx.reconstruct(9001)
-        D, I = idx.search(xq[:2], 9001 + 5)                # k > ntotal: padded
-        assert (I[:, 9001:] == -1).all() and (np.sort(I[0, :9001]) == np.arange(9001)).all()
         idx.reset()
         assert idx.ntotal == 0
+        idx.add(xb[:7])                                    # fewer rows than shards x k: k > ntotal is padded
+        D, I = idx.search(xq[:2], 12)
+        assert (I[:, 7:] == -1).all() and (np.sort(I[0, :7]) == np.arange(7)).all() and np.isinf(D[:, 7:]).all()
         idx.close()
     single.close()
 
