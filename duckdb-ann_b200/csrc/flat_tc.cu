@@ -219,6 +219,11 @@ __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
 }
+// Waits for every TMEM read this thread has in flight, naming no registers.  Needed before code
+// with calls, loops or jumps while a read into another register buffer is still in flight: the
+// compiler believes those registers were written when the read was ISSUED and may copy or save
+// them at any point after that - a copy taken before the data has landed is stale.
+__device__ __forceinline__ void tmem_ld_wait_all() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;"
                  : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
@@ -574,17 +579,19 @@ __device__ __noinline__ void compact_rows(float *slot_key, int32_t *slot_idx, in
         const int r = __ffs(need) - 1;
         need &= need - 1;
         const int c = __shfl_sync(kFullMask, cnt, r);
+        // every lane works on row r's buffer now: the band is row r's, not the lane's own row's
+        const float row_slack = __shfl_sync(kFullMask, slack, r);
         float *bk = slot_key + (size_t)(row0 + r) * kBuf;
         int32_t *bi = slot_idx + (size_t)(row0 + r) * kBuf;
         float kth;
         int kept;
         if (c > 256) {
-            kth = select_one(bk, bi, c, k, k_rank, slack, lane, kept);
-            if (kept < 0) kth = compact_one<16>(bk, bi, c, k, k_rank, slack, lane, kept);
-        } else if (c > 128) kth = compact_one<8>(bk, bi, c, k, k_rank, slack, lane, kept);
-        else if (c > 64) kth = compact_one<4>(bk, bi, c, k, k_rank, slack, lane, kept);
-        else if (c > 32) kth = compact_one<2>(bk, bi, c, k, k_rank, slack, lane, kept);
-        else kth = compact_one<1>(bk, bi, c, k, k_rank, slack, lane, kept);
+            kth = select_one(bk, bi, c, k, k_rank, row_slack, lane, kept);
+            if (kept < 0) kth = compact_one<16>(bk, bi, c, k, k_rank, row_slack, lane, kept);
+        } else if (c > 128) kth = compact_one<8>(bk, bi, c, k, k_rank, row_slack, lane, kept);
+        else if (c > 64) kth = compact_one<4>(bk, bi, c, k, k_rank, row_slack, lane, kept);
+        else if (c > 32) kth = compact_one<2>(bk, bi, c, k, k_rank, row_slack, lane, kept);
+        else kth = compact_one<1>(bk, bi, c, k, k_rank, row_slack, lane, kept);
         if (lane == r) {
             cnt = kept;
             if (c >= k_rank) {
@@ -1057,6 +1064,9 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     }
                     uint32_t mask = beat_mask(raw, g, valid);
                     if (!__any_sync(kFullMask, mask != 0)) return;
+                    // some row has a candidate: what follows has loops, jumps and a call, and the read of
+                    // the next 32 columns is in flight into the other register buffer - let it land first
+                    tmem_ld_wait_all();
                     const int32_t colg = col0 + g * 32;
                     if (APPEND) {
                         const unsigned need = __ballot_sync(kFullMask, cnt + __popc(mask) > kBuf);
