@@ -928,6 +928,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 // these entries away before it sorts: nothing to do here but say how many there are
                 // (flat search: index = list slot * 128 + row as well)
                 args.part_cnt[(size_t)cur_slot * BM + row] = row_valid ? cnt : 0;
+
             } else if (APPEND) {
                 const unsigned need = __ballot_sync(kFullMask, cnt > 0);
                 if (need) compact_rows(unit_key, unit_idx, k, quarter * 32, need, cnt, tau, lane, qtau_word, koff, k_rank, slack);

@@ -235,7 +235,13 @@ merge_filtered_kernel(const float *__restrict__ part_key, const int32_t *__restr
         c = c < list_stride ? c : list_stride;
         const float off = slot_key_offset ? slot_key_offset[g] : 0.f;
         for (int j0 = 0; j0 < c; j0 += blockDim.x) {
-            if (count + (int)blockDim.x > cap) shrink();  // block-uniform: count is read after a barrier
+            // Is there room for one more round of reads?  Every thread must take the same branch
+            // (shrink() has barriers inside): the count is read between two barriers, after the
+            // additions of the round before and before anybody adds again.
+            __syncthreads();
+            const int have = count;
+            __syncthreads();
+            if (have + (int)blockDim.x > cap) shrink();
             const int j = j0 + threadIdx.x;
             if (j < c) {
                 const int32_t idx = part_idx[(size_t)g * list_stride + j];
@@ -246,7 +252,6 @@ merge_filtered_kernel(const float *__restrict__ part_key, const int32_t *__restr
                     vals[pos] = idx;
                 }
             }
-            __syncthreads();
         }
     }
     shrink();
