@@ -1057,11 +1057,17 @@ def main():
     # DuckDB process uses); the other ranks have released their memory and wait
     single = args.single_process.split(",") if args.single_process else ([str(i) for i in range(world)] if world > 1 else None)
     if single and args.workload is None:
+        # The other ranks wait on the CPU (gloo): a pending NCCL barrier is a kernel spinning on their
+        # GPUs, and the searches rank 0 now runs on those GPUs want every SM.
+        cpu_group = dist.new_group(backend="gloo") if world > 1 else None
         if world > 1:
-            dist.barrier()
+            torch.cuda.synchronize()
+            dist.barrier(group=cpu_group)
         if rank == 0:
             line["single_process"] = run_single_process(args, ctx, [int(v) for v in single], steps)
             ok = ok and line["single_process"]["parity_check"]["ok"]
+        if world > 1:
+            dist.barrier(group=cpu_group)
     if rank == 0:
         print(json.dumps(line, default=_json_default))
     if world > 1:
