@@ -371,7 +371,8 @@ __device__ __forceinline__ int kdebug(const KernelArgs &) { return 0; }
 //               list in global memory (exact for any k, slower).
 // Slots of the optional statistics array (cycle counts are summed over CTAs / warps).
 enum { kStatCompactRows = 0, kStatAppends = 1, kStatCompactCycles = 2, kStatEpiWaitCycles = 3, kStatMmaWaitTmem = 4,
-       kStatMmaWaitSmem = 5, kStatEpiTileCycles = 6, kStatTiles = 7 };
+       kStatMmaWaitSmem = 5, kStatEpiTileCycles = 6, kStatTiles = 7, kStatSlowGroups = 8, kStatSlowCycles = 9,
+       kStatLdWaitCycles = 10, kStatCount = 12 };
 
 enum SelMode { kSelSmem = 0, kSelAppend = 1, kSelReplace = 2 };
 constexpr int kBuf = kAppendBuffer;  // candidate slots per row in append mode
@@ -429,6 +430,22 @@ __device__ __forceinline__ void warp_sort(uint32_t (&key)[E], int32_t (&idx)[E],
                 if ((i & stride) == 0) ce_swap(key[i], idx[i], key[i | stride], idx[i | stride], dm);
         }
     }
+}
+
+// raw[j] for a j known only at run time: registers cannot be indexed, so the value is chosen by a
+// select tree on the bits of j (16 + 8 + 4 + 2 + 1 selects, five levels deep).
+__device__ __forceinline__ uint32_t select32(const uint32_t (&raw)[32], int j) {
+    const bool b4 = (j & 16) != 0, b3 = (j & 8) != 0, b2 = (j & 4) != 0, b1 = (j & 2) != 0, b0 = (j & 1) != 0;
+    uint32_t a[16], b[8], c[4], d[2];
+#pragma unroll
+    for (int i = 0; i < 16; i++) a[i] = b4 ? raw[i + 16] : raw[i];
+#pragma unroll
+    for (int i = 0; i < 8; i++) b[i] = b3 ? a[i + 8] : a[i];
+#pragma unroll
+    for (int i = 0; i < 4; i++) c[i] = b2 ? b[i + 4] : b[i];
+#pragma unroll
+    for (int i = 0; i < 2; i++) d[i] = b1 ? c[i + 2] : c[i];
+    return b0 ? d[1] : d[0];
 }
 
 // Sorts the first 32 * E slots of one row's append buffer (c <= 32 * E of them filled) and writes
@@ -1067,7 +1084,9 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     if (!__any_sync(kFullMask, mask != 0)) return;
                     // some row has a candidate: what follows has loops, jumps and a call, and the read of
                     // the next 32 columns is in flight into the other register buffer - let it land first
+                    const long long s0 = kstats(args) ? clock64() : 0;
                     tmem_ld_wait_all();
+                    const long long s1 = kstats(args) ? clock64() : 0;
                     const int32_t colg = col0 + g * 32;
                     if (APPEND) {
                         const unsigned need = __ballot_sync(kFullMask, cnt + __popc(mask) > kBuf);
@@ -1082,31 +1101,52 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         }
                         if (kdebug(args) & 4) mask = 0;
                         if (kstats(args) && mask) atomicAdd(kstats(args) + kStatAppends, (unsigned long long)__popc(mask));
-                        // Appends, column by column, for the columns in which SOME row of the warp has a
-                        // hit (about four of the 32 once the thresholds have settled; a row has about one
-                        // hit per tile).  The loop and the jump on the column number are warp-uniform;
-                        // inside a case the column is a compile-time register index.  Walking all 32
-                        // columns with predicated stores cost ~10 instructions per column whether or not
-                        // anything was stored, and made the epilogue as long as the MMAs of the tile.
                         float *bk = unit_key + (size_t)row * kBuf;
                         int32_t *bi = unit_idx + (size_t)row * kBuf;
-                        uint32_t cols = __reduce_or_sync(kFullMask, mask);
-                        while (cols) {
-                            const int j = __ffs(cols) - 1;
-                            cols &= cols - 1;
-                            float kj = 0.f;
-                            switch (j) {
-#define ANN_COL(J) case J: kj = key_of(raw, g, J); break;
-                                ANN_COL(0) ANN_COL(1) ANN_COL(2) ANN_COL(3) ANN_COL(4) ANN_COL(5) ANN_COL(6) ANN_COL(7)
-                                ANN_COL(8) ANN_COL(9) ANN_COL(10) ANN_COL(11) ANN_COL(12) ANN_COL(13) ANN_COL(14) ANN_COL(15)
-                                ANN_COL(16) ANN_COL(17) ANN_COL(18) ANN_COL(19) ANN_COL(20) ANN_COL(21) ANN_COL(22) ANN_COL(23)
-                                ANN_COL(24) ANN_COL(25) ANN_COL(26) ANN_COL(27) ANN_COL(28) ANN_COL(29) ANN_COL(30) ANN_COL(31)
-#undef ANN_COL
-                                default: break;
+                        if (!__any_sync(kFullMask, __popc(mask) > 4)) {
+                            // Sparse hits (the steady state: about one per row and tile): every lane walks its
+                            // own hits, so the warp makes one or two rounds per 32 columns.  The column of a hit
+                            // is known only at run time and registers cannot be indexed: the value comes out of
+                            // a five-level select tree over the 32 registers (31 selects, no dependency chain
+                            // longer than five).
+                            while (__any_sync(kFullMask, mask != 0)) {
+                                const bool p = mask != 0;
+                                const int j = p ? __ffs(mask) - 1 : 0;
+                                mask &= mask - 1;
+                                const float acc = __uint_as_float(select32(raw, j));
+                                const float kj = args.l2 ? fmaf(-2.f, acc, xn_s[buf * BN + g * 32 + j]) : -acc;
+                                st_global_pair_if(p, bk + cnt, kj, bi + cnt, colg + j);
+                                cnt += p ? 1 : 0;
                             }
-                            const bool p = (mask >> j) & 1u;
-                            st_global_pair_if(p, bk + cnt, kj, bi + cnt, colg + j);
-                            cnt += p ? 1 : 0;
+                        } else {
+                            // Dense hits (a list that has no threshold yet): column by column, for the columns
+                            // in which SOME row of the warp has a hit.  The loop and the jump on the column
+                            // number are warp-uniform; inside a case the column is a compile-time register
+                            // index.  ~160 cycles per column with one warp per scheduler, whatever the number
+                            // of rows that store.
+                            uint32_t cols = __reduce_or_sync(kFullMask, mask);
+                            while (cols) {
+                                const int j = __ffs(cols) - 1;
+                                cols &= cols - 1;
+                                float kj = 0.f;
+                                switch (j) {
+#define ANN_COL(J) case J: kj = key_of(raw, g, J); break;
+                                    ANN_COL(0) ANN_COL(1) ANN_COL(2) ANN_COL(3) ANN_COL(4) ANN_COL(5) ANN_COL(6) ANN_COL(7)
+                                    ANN_COL(8) ANN_COL(9) ANN_COL(10) ANN_COL(11) ANN_COL(12) ANN_COL(13) ANN_COL(14) ANN_COL(15)
+                                    ANN_COL(16) ANN_COL(17) ANN_COL(18) ANN_COL(19) ANN_COL(20) ANN_COL(21) ANN_COL(22) ANN_COL(23)
+                                    ANN_COL(24) ANN_COL(25) ANN_COL(26) ANN_COL(27) ANN_COL(28) ANN_COL(29) ANN_COL(30) ANN_COL(31)
+#undef ANN_COL
+                                    default: break;
+                                }
+                                const bool p = (mask >> j) & 1u;
+                                st_global_pair_if(p, bk + cnt, kj, bi + cnt, colg + j);
+                                cnt += p ? 1 : 0;
+                            }
+                        }
+                        if (kstats(args) && lane == 0) {
+                            atomicAdd(kstats(args) + kStatSlowGroups, 1ull);
+                            atomicAdd(kstats(args) + kStatSlowCycles, (unsigned long long)(clock64() - s0));
+                            atomicAdd(kstats(args) + kStatLdWaitCycles, (unsigned long long)(s1 - s0));
                         }
                     } else if (SMALLK) {
                         while (mask) {
@@ -1405,8 +1445,8 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     static unsigned long long *stats_dev = nullptr;
     static const bool want_stats = getenv("ANN_CUDA_TC_STATS") != nullptr;
     if (want_stats) {  // synchronises and prints
-        if (!stats_dev) ANN_CUDA_TRY(cudaMalloc(&stats_dev, 8 * sizeof(unsigned long long)));
-        ANN_CUDA_TRY(cudaMemsetAsync(stats_dev, 0, 8 * sizeof(unsigned long long), stream));
+        if (!stats_dev) ANN_CUDA_TRY(cudaMalloc(&stats_dev, kStatCount * sizeof(unsigned long long)));
+        ANN_CUDA_TRY(cudaMemsetAsync(stats_dev, 0, kStatCount * sizeof(unsigned long long), stream));
         a.stats = stats_dev;
     }
 #endif
@@ -1418,14 +1458,16 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     else rc = launch_variant<66, kSelReplace>(plan, maps, a, stream);
 #ifdef ANN_CUDA_MEASURE
     if (rc == 0 && a.stats) {
-        unsigned long long h[8];
+        unsigned long long h[kStatCount];
         ANN_CUDA_TRY(cudaStreamSynchronize(stream));
         ANN_CUDA_TRY(cudaMemcpy(h, a.stats, sizeof h, cudaMemcpyDeviceToHost));
         fprintf(stderr,
                 "[flat_tc stats] grid %d k %d tiles(x4 warps) %llu | compact rows %llu cycles %llu | appends %llu | "
-                "epilogue: wait %llu work %llu cycles | mma wait: tmem %llu smem %llu cycles\n",
+                "epilogue: wait %llu work %llu cycles | mma wait: tmem %llu smem %llu cycles | slow groups %llu cycles %llu "
+                "(of which waiting for the load in flight %llu)\n",
                 plan.grid, k, h[kStatTiles], h[kStatCompactRows], h[kStatCompactCycles], h[kStatAppends],
-                h[kStatEpiWaitCycles], h[kStatEpiTileCycles], h[kStatMmaWaitTmem], h[kStatMmaWaitSmem]);
+                h[kStatEpiWaitCycles], h[kStatEpiTileCycles], h[kStatMmaWaitTmem], h[kStatMmaWaitSmem], h[kStatSlowGroups],
+                h[kStatSlowCycles], h[kStatLdWaitCycles]);
     }
 #endif
     return rc;
