@@ -91,12 +91,20 @@ constexpr int kStages = 64 / BK;  // the ring always holds 64 floats of K: 2 x 9
 // Screened mode needs the hi planes only: the lo half of every stage serves as a stage of its own,
 // so the ring is twice as deep (stage s = planes s & 1 of the physical stage s >> 1).
 constexpr int kMaxStages = 2 * kStages;
+// Pair mode (screened search with the static schedule): two CTAs of a cluster work on one 256-row
+// tile with tcgen05.mma.cta_group::2.  Each CTA stages its own 128 queries and HALF of the row
+// tile, so a K block costs a CTA kABytes + kBBytes / 2 of operand traffic instead of kABytes +
+// kBBytes, and the ring holds more, smaller stages.
+constexpr int kPairStages = 6;
+constexpr int kBarStages = kMaxStages > kPairStages ? kMaxStages : kPairStages;
 constexpr int kRowBytes = BK * 4;
 constexpr uint64_t kDescLayout = BK == 32 ? 2ull : 4ull;    // SWIZZLE_128B : SWIZZLE_64B
 constexpr uint64_t kDescSbo = (8 * kRowBytes) >> 4;         // 8-row group stride, in 16-byte units
 constexpr int kABytes = BM * BK * 4;                    // 16 KB
 constexpr int kBBytes = BN * BK * 4;                    // 32 KB
 constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;  // hi + lo of both operands: 96 KB
+constexpr int kPairStageBytes = kABytes + kBBytes / 2;  // pair mode: own queries + half of the row tile
+static_assert(kPairStages * kPairStageBytes <= kStages * kStageBytes, "the pair ring fits into the stage memory");
 constexpr int kQueueDepth = kSmemListMax;   // per-row candidate queue, also the small-k list capacity
 constexpr int kThreads = 192;
 constexpr int kPaceSpins = 10000;  // polls of ~100 ns a CTA of the static schedule waits for the others, once
@@ -108,8 +116,8 @@ struct SmemLayout {
     static constexpr int queue_idx = queue_key + kQueueDepth * BM * 4;
     static constexpr int xnorm = queue_idx + kQueueDepth * BM * 4;
     static constexpr int barriers = xnorm + 4 * 2 * BN * 4;  // (after a private norm copy per epilogue warp)
-    // barriers: full[kMaxStages] empty[kMaxStages] tmem_full[2] tmem_empty[2]
-    static constexpr int work_bars = barriers + (2 * kMaxStages + 4) * 8;  // wfull[kWorkRing] wempty[kWorkRing]
+    // barriers: full[kBarStages] empty[kBarStages] tmem_full[2] tmem_empty[2]
+    static constexpr int work_bars = barriers + (2 * kBarStages + 4) * 8;  // wfull[kWorkRing] wempty[kWorkRing]
     static constexpr int work_ring = work_bars + 2 * kWorkRing * 8;    // kWorkRing descriptors of 32 bytes
     static constexpr int tmem_ptr = work_ring + kWorkRing * 32;
     static constexpr int abort_flag = tmem_ptr + 4;
@@ -122,6 +130,9 @@ static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 // N = 256, M = 128.
 constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                 ((uint32_t)(BM >> 4) << 24);
+// The same for cta_group::2: M = 256, 128 rows of it in the tensor memory of each CTA of the pair.
+constexpr uint32_t kInstrDescPair = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                    ((uint32_t)((2 * BM) >> 4) << 24);
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -202,6 +213,55 @@ __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// ---- pair mode (a cluster of two CTAs, tcgen05 cta_group::2) ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The address, in the cluster's shared window, of this CTA's shared address `addr` in CTA `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// All threads of both CTAs meet (not .aligned: roles arrive from different paths).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Tiled load whose completion is counted on a barrier of the pair's leader CTA (`bar` is an address
+// in the cluster window).  No multicast: each CTA fetches what it stages.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int32_t c0, int32_t c1,
+                                                 uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        :
+        : "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+// One MMA over both CTAs of the pair: A = 2 x 128 queries (each CTA's own), B = 2 x 128 rows (half
+// of the tile in each CTA), D = 128 x 256 in each CTA's tensor memory.  Issued by the leader only.
+__device__ __forceinline__ void mma_tf32_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDescPair), "r"(accumulate)
+        : "memory");
+}
+// Arrives, once the MMAs issued so far are complete, on the barrier at the same address in BOTH CTAs.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+        "h"((uint16_t)3)
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tmem_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -343,6 +403,7 @@ struct KernelArgs {
     uint64_t wait_ns;     // limit of every bounded wait
     int withhold_after;   // test hook (-1 = off): see flat_test_withhold_after in kernels.h
     const int *gate;      // may be null: run only if *gate == kScreenOverflow (a fallback pass)
+    int pair;             // launched as clusters of two CTAs that share row tiles (screened, static schedule)
 #ifdef ANN_CUDA_MEASURE
     unsigned long long *stats;  // see kStat* below
     int debug;  // bit 0 = epilogue skips selection, bit 1 = MMA issuer skips the MMAs, bit 2 = no appends, bit 3 = consume only
@@ -623,7 +684,9 @@ __device__ __noinline__ void compact_rows(float *slot_key, int32_t *slot_idx, in
     __syncwarp();
 }
 
-template <int KR, int MODE>
+// PAIR: the kernel of the pair mode, launched as clusters of two CTAs.  A kernel of its own because
+// code that holds cta_group::2 instructions can only be launched with a cluster size that fits them.
+template <int KR, int MODE, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constant__ CUtensorMap map_qlo,
                const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
@@ -639,9 +702,12 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
     int32_t *qidx = reinterpret_cast<int32_t *>(smem + SmemLayout::queue_idx);
     float *xn_all = reinterpret_cast<float *>(smem + SmemLayout::xnorm);
     const uint32_t bar_full = smem_base + SmemLayout::barriers;
-    const uint32_t bar_empty = bar_full + 8 * kMaxStages;
-    const uint32_t bar_tfull = bar_empty + 8 * kMaxStages;
-    const uint32_t nstages = args.screen ? kMaxStages : kStages;
+    const uint32_t bar_empty = bar_full + 8 * kBarStages;
+    const uint32_t bar_tfull = bar_empty + 8 * kBarStages;
+    const uint32_t nstages = PAIR ? kPairStages : args.screen ? kMaxStages : kStages;
+    // pair mode: rank of this CTA in its cluster of two; rank 0 (the leader) issues the MMAs of both
+    const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
+    const bool leader = crank == 0;
     const uint32_t bar_tempty = bar_tfull + 16;
     volatile uint32_t *tmem_ptr_s = reinterpret_cast<volatile uint32_t *>(smem + SmemLayout::tmem_ptr);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + SmemLayout::abort_flag);
@@ -649,13 +715,14 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kMaxStages; s++) {
+        for (int s = 0; s < kBarStages; s++) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(bar_tfull + 8 * b, 1);
-            mbar_init(bar_tempty + 8 * b, 4);  // one arrival per epilogue warp
+            // one arrival per epilogue warp (pair mode: of both CTAs, on the leader's barrier)
+            mbar_init(bar_tempty + 8 * b, PAIR ? 8 : 4);
         }
         for (int w = 0; w < kWorkRing; w++) {
             mbar_init(smem_base + SmemLayout::work_bars + 8 * w, 1);                    // written by the scheduler
@@ -666,14 +733,25 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                         smem_base + SmemLayout::tmem_ptr),
-                     "r"(512u)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        // pair mode: the same warp of both CTAs allocates the same columns in both tensor memories
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_base + SmemLayout::tmem_ptr),
+                         "r"(512u)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_base + SmemLayout::tmem_ptr),
+                         "r"(512u)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tmem_fence_before();
     __syncthreads();
+    // pair mode: the peer's barriers are initialised before anything of this CTA signals them
+    if (PAIR) cluster_sync_all();
     tmem_fence_after();
     const uint32_t tmem_base = *tmem_ptr_s;
 
@@ -708,10 +786,15 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             const int n_items = args.items ? *args.n_items : 0;
             // static schedule: this CTA's share [ulo, uhi) of the units of every chunk, the (at
             // most two) query tiles it falls into, their list slots
+            // (pair mode: the schedule is the pair's - both CTAs compute the same one - over PAIRS of
+            // query tiles; this CTA's query tile of schedule tile t is 2 t + rank)
             const int G = args.static_g;
-            const long long U = (long long)args.nq_tiles * G;
-            const int ulo = G ? (int)(blockIdx.x * U / gridDim.x) : 0;
-            const int uhi = G ? (int)((blockIdx.x + 1) * U / gridDim.x) : 0;
+            const int sched_id = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+            const int sched_n = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+            const int sched_qt = PAIR ? args.nq_tiles >> 1 : args.nq_tiles;
+            const long long U = (long long)sched_qt * G;
+            const int ulo = G ? (int)(sched_id * U / sched_n) : 0;
+            const int uhi = G ? (int)((sched_id + 1) * U / sched_n) : 0;
             const int t_first = G ? ulo / G : 0, t_last = G ? (uhi - 1) / G : -1;
             int st_slot[2] = {-1, -1};
             int st_chunk = 0, st_tile = t_first, st_active = -1, st_close = 0;
@@ -753,20 +836,21 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         if (r_begin >= args.n) continue;
                         if (r_end > args.n) r_end = args.n;
                         const int si = t - t_first;
+                        const int my_qt = PAIR ? 2 * t + (int)crank : t;
                         if (st_slot[si] < 0) {
-                            const int j = atomicAdd(args.nlists + t, 1);
+                            const int j = atomicAdd(args.nlists + my_qt, 1);
                             if (j >= args.lists_per_qt) {  // cannot happen with the plan's list count
                                 atomicExch(args.status, 9);
                                 *abort_flag = 1;
                                 goto done;
                             }
-                            st_slot[si] = t * args.lists_per_qt + j;
+                            st_slot[si] = my_qt * args.lists_per_qt + j;
                             fresh = 1;
                         } else {
                             fresh = st_active != t ? 2 : 0;
                         }
                         st_active = t;
-                        cur = t;
+                        cur = my_qt;
                         slot = st_slot[si];
                         got = true;
                     }
@@ -774,10 +858,10 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         // all chunks done: one empty item per list, which closes it
                         while (st_close < 2 && st_slot[st_close] < 0) st_close++;
                         if (st_close >= 2) break;
-                        cur = t_first + st_close;
+                        cur = PAIR ? 2 * (t_first + st_close) + (int)crank : t_first + st_close;
                         slot = st_slot[st_close];
-                        fresh = (st_active != cur ? 2 : 0) | 4;
-                        st_active = cur;
+                        fresh = (st_active != t_first + st_close ? 2 : 0) | 4;
+                        st_active = t_first + st_close;
                         st_close++;
                         r_begin = r_end = 0;
                     }
@@ -825,7 +909,16 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         // wait for the stage runs out and the give-up path is exercised
                         if (args.withhold_after >= 0 && issued++ >= args.withhold_after) goto done;
                         const uint32_t full = bar_full + 8 * stage;
-                        if (args.screen) {  // hi planes only, into plane set stage & 1 of stage >> 1
+                        if (PAIR) {
+                            // own queries + this CTA's half of the row tile; the bytes of both CTAs are
+                            // counted on the LEADER's barrier, which its MMA issuer waits on
+                            const uint32_t base = smem_base + stage * kPairStageBytes;
+                            const uint32_t full_leader = map_to_cta(full, 0);
+                            if (leader) mbar_expect_tx(full, 2 * kPairStageBytes);
+                            tma_load_2d_pair(base, &map_qhi, kb * BK, cur * BM, full_leader);
+                            tma_load_2d_pair(base + kABytes, &map_xlo, kb * BK, (int32_t)trow + (int32_t)crank * (BN / 2),
+                                             full_leader);
+                        } else if (args.screen) {  // hi planes only, into plane set stage & 1 of stage >> 1
                             const uint32_t base = smem_base + (stage >> 1) * kStageBytes;
                             mbar_expect_tx(full, kABytes + kBBytes);
                             tma_load_2d(base + (stage & 1) * kABytes, &map_qhi, kb * BK, cur * BM, full);
@@ -865,6 +958,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 const int64_t r_begin = ring[w].row_begin, r_end = ring[w].row_end;
                 mbar_arrive(bar_wempty + 8 * w);
                 if (qt < 0) break;
+                if (PAIR && !leader) continue;  // the leader issues the MMAs of both CTAs
                 for (int64_t trow = r_begin; trow < r_end; trow += BN, it++) {
                     const uint32_t buf = it & 1;
                     long long t0 = kstats(args) ? clock64() : 0;
@@ -877,6 +971,22 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, args.status, args.wait_ns, 3)) goto done;
                         if (kstats(args)) atomicAdd(kstats(args) + kStatMmaWaitSmem, (unsigned long long)(clock64() - t0));
                         tmem_fence_after();
+                        if (PAIR) {
+                            const uint32_t base = smem_base + stage * kPairStageBytes;
+                            const uint64_t a0 = make_smem_desc(base);
+                            const uint64_t b0 = make_smem_desc(base + kABytes);
+                            if (!(kdebug(args) & 2)) {
+                                mma_tf32_pair(tmem_d, a0, b0, kb != 0);
+#pragma unroll
+                                for (int ks = 1; ks < BK / 8; ks++) mma_tf32_pair(tmem_d, a0 + 2 * ks, b0 + 2 * ks, 1);
+                            }
+                            mma_commit_pair(bar_empty + 8 * stage);  // frees the stage in both CTAs
+                            if (++stage == nstages) {
+                                stage = 0;
+                                phase ^= 1;
+                            }
+                            continue;
+                        }
                         if (args.screen) {
                             // One MMA per K step: the loop of this single thread is what paces the
                             // tensor pipe, so the descriptors are formed once per K block and only
@@ -909,7 +1019,9 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             phase ^= 1;
                         }
                     }
-                    mma_commit(bar_tfull + 8 * buf);  // accumulator complete
+                    // accumulator complete (pair mode: in both CTAs' tensor memories)
+                    if (PAIR) mma_commit_pair(bar_tfull + 8 * buf);
+                    else mma_commit(bar_tfull + 8 * buf);
                 }
             }
         }
@@ -1207,7 +1319,10 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                 }
                 tmem_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * buf, 0));
+                    else mbar_arrive(bar_tempty + 8 * buf);
+                }
                 if (kstats(args) && lane == 0) atomicAdd(kstats(args) + kStatEpiTileCycles, (unsigned long long)(clock64() - t1));
                 if (SMALLK && list_max < published) {
                     published = list_max;
@@ -1224,9 +1339,15 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
 done:
     tmem_fence_before();
     __syncthreads();
+    // pair mode: neither CTA frees its tensor memory or leaves while the other may still signal its
+    // barriers or (the leader) write its accumulators
+    if (PAIR) cluster_sync_all();
     if (warp == 1) {
         tmem_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        if (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
@@ -1266,12 +1387,67 @@ int make_map(CUtensorMap *map, const float *base, int64_t rows, int dp, int box_
 
 template <int KR, int MODE>
 int launch_variant(const FlatPlan &plan, const CUtensorMap maps[4], const KernelArgs &args, cudaStream_t stream) {
-    ANN_CUDA_TRY(cudaFuncSetAttribute(flat_tc_kernel<KR, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if constexpr (KR == 1 && MODE == kSelAppend && BK == 32) {
+      if (args.pair) {  // clusters of two CTAs
+        ANN_CUDA_TRY(cudaFuncSetAttribute(flat_tc_kernel<KR, MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          kSmemBytes));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)plan.grid);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = kSmemBytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        ANN_CUDA_TRY(cudaLaunchKernelEx(&cfg, flat_tc_kernel<KR, MODE, true>, maps[0], maps[1], maps[2], maps[3], args));
+        count_launch();
+        return 0;
+      }
+    }
+    if (args.pair) return set_error("internal: pair mode asked of a kernel variant that has none");
+    ANN_CUDA_TRY(cudaFuncSetAttribute(flat_tc_kernel<KR, MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       kSmemBytes));
-    flat_tc_kernel<KR, MODE><<<plan.grid, kThreads, kSmemBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], args);
+    flat_tc_kernel<KR, MODE, false><<<plan.grid, kThreads, kSmemBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], args);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
+}
+
+// Whether grid / 2 clusters of two CTAs of the append kernel can be resident at once (every SM
+// takes one CTA of this kernel; the pairs must find two free SMs side by side).  Asked once.
+bool pair_clusters_fit(int grid) {
+  if constexpr (BK != 32) {
+    (void)grid;
+    return false;
+  } else {
+    static int max_clusters = [] {
+        int n = 0;
+        if (cudaFuncSetAttribute(flat_tc_kernel<1, kSelAppend, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
+            cudaSuccess)
+            return 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = kSmemBytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, flat_tc_kernel<1, kSelAppend, true>, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            return 0;
+        }
+        return n;
+    }();
+    return 2 * max_clusters >= grid;
+  }
 }
 
 }  // namespace
@@ -1296,15 +1472,20 @@ int gcd_int(int a, int b) { return b ? gcd_int(b, a % b) : a; }
 void choose_static(FlatPlan &p, int64_t n, int sms, bool screened) {
     p.static_g = 0;
     p.static_chunks = 0;
+    p.pair = false;
     p.sched_ints = (size_t)p.nq_tiles * 2;
     static const bool off = [] { const char *e = getenv("ANN_CUDA_STATIC"); return e && atoi(e) == 0; }();
+    static const bool pair_off = [] { const char *e = getenv("ANN_CUDA_PAIR"); return e && atoi(e) == 0; }();
     if (!screened || off || p.nq_tiles > sms) return;
     const int64_t ntiles = (n + BN - 1) / BN;
-    const int g = sms / gcd_int(sms, p.nq_tiles);
+    // CTA pairs (sms / 2 of them over nq_tiles / 2 pairs of query tiles) when both are even
+    const bool pair = !pair_off && sms % 2 == 0 && p.nq_tiles % 2 == 0;
+    const int g = pair ? (sms / 2) / gcd_int(sms / 2, p.nq_tiles / 2) : sms / gcd_int(sms, p.nq_tiles);
     const int ctas_per_qt = (sms + p.nq_tiles - 1) / p.nq_tiles;
     if (ntiles < 16 * (int64_t)g || p.lists_per_qt < ctas_per_qt + 1) return;  // short stores: the ragged last chunk would cost more
     p.static_g = g;
     p.static_chunks = (int)((ntiles + g - 1) / g);
+    p.pair = pair;
     p.grid = sms;
     // + one arrival counter per chunk, + one fill count per (list, row)
     p.sched_ints += (size_t)p.static_chunks + (size_t)p.nq_tiles * p.lists_per_qt * BM;
@@ -1429,6 +1610,9 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     a.banded = use_band ? 1 : 0;
     // the static schedule parks and resumes append buffers; it pays for the screened search only
     a.static_g = use_screen ? plan.static_g : 0;
+    // pair mode: the fourth map becomes the hi plane of the rows in boxes of HALF a tile
+    a.pair = (a.static_g && plan.pair && BK == 32 && plan.grid % 2 == 0 && pair_clusters_fit(plan.grid)) ? 1 : 0;
+    if (a.pair && make_map(&maps[3], xhi, n, dp, BN / 2)) return -1;
     a.k_rank = use_band ? screen->k_rank : k;
     a.q_norm2 = use_band ? screen->q_norm2 : nullptr;
     a.x_max_norm2 = use_band ? screen->x_max_norm2 : nullptr;

@@ -68,6 +68,9 @@ struct FlatPlan {
     // the store is walked in chunks of static_g row tiles and every CTA owns a fixed share of the
     // nq_tiles * static_g (query tile, row tile) units of each chunk.
     int static_g = 0, static_chunks = 0;
+    // Static schedule over PAIRS of CTAs (clusters of two that share every row tile through
+    // tcgen05 cta_group::2): needs an even number of query tiles and of SMs.
+    bool pair = false;
     size_t sched_ints = 0;    // ints of scheduler memory (zero on entry)
 };
 // Chooses the decomposition for nq queries against n rows on a device with `sms` SMs.
