@@ -351,6 +351,9 @@ struct TopkOpts {
     int tier = 0;
     bool exact = false;  // exact-fp32 scan instead of the tensor cores
     const int *gate = nullptr;  // device word: run only if it holds kScreenOverflow (a fallback pass)
+    // a pass of a tier chain (flat_tier_search): the queries were split by the first pass, the band check runs
+    // inside the re-ranking kernel that follows, and the caller publishes the status words once at the end
+    bool chained = false;
 };
 // x_dev: nq x d queries on the device.  Leaves (nq x k) keys and int32 rows, best
 // first, in ws.sel_key / ws.sel_idx.  The status words must have been cleared by the caller.
@@ -362,8 +365,9 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         return -1;
     int *status = ws.status.as<int>();
     if (!o.exact && flat_kernel_choice() == FlatKernel::TC) {
-        // the split of the queries is the same in every tier: rewriting it in a fallback pass is harmless
-        if (launch_split_rows(x_dev, nq, d, dp, ws.qhi.as<float>(), ws.qlo.as<float>(), ws.qn.as<float>(), stream,
+        // the split of the queries is the same in every tier: a gated fallback pass finds it in place
+        if (!(o.chained && o.gate) &&
+            launch_split_rows(x_dev, nq, d, dp, ws.qhi.as<float>(), ws.qlo.as<float>(), ws.qn.as<float>(), stream,
                               st.center(), true))
             return -1;
         const FlatPlan plan = o.k_rank > 0 && o.one_mma ? make_flat_plan_screened(nq, st.n, k, sm_count(ix.device))
@@ -373,19 +377,17 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         if (ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4) ||
             ws.qtau.ensure(qtau_bytes) || ws.sched.ensure(sched_bytes))
             return -1;
-        ANN_CUDA_TRY(cudaMemsetAsync(ws.qtau.ptr, 0xFF, qtau_bytes, stream));  // "no threshold yet"
-        ANN_CUDA_TRY(cudaMemsetAsync(ws.sched.ptr, 0, sched_bytes, stream));
-        // Append selection: a list is the first part_cnt entries of its row's buffer, unsorted - every
-        // list empty means every count zero.  Other selections: index -1 in the k slots the merge reads.
+        // Thresholds "none yet", scheduler memory zero.  Append selection: a list is the first part_cnt
+        // entries of its row's buffer, unsorted - every list empty means every count zero.  Other
+        // selections: index -1 in the k slots the merge reads.  One kernel, gated like the pass.
         const bool append = plan.lists_sorted;
-        const size_t cnt_bytes = (size_t)plan.nq_tiles * plan.lists_per_qt * 128 * 4;
-        if (append) {
-            if (ws.part_cnt.ensure(cnt_bytes)) return -1;
-            ANN_CUDA_TRY(cudaMemsetAsync(ws.part_cnt.ptr, 0, cnt_bytes, stream));
-        } else {
-            ANN_CUDA_TRY(cudaMemset2DAsync(ws.part_idx.ptr, (size_t)plan.list_stride * 4, 0xFF, (size_t)k * 4,
-                                           plan.part_entries / plan.list_stride, stream));
-        }
+        const size_t cnt_words = (size_t)plan.nq_tiles * plan.lists_per_qt * 128;
+        if (append && ws.part_cnt.ensure(cnt_words * 4)) return -1;
+        if (launch_flat_scratch_init(ws.qtau.as<uint32_t>(), qtau_bytes / 4, ws.sched.as<int>(), plan.sched_ints,
+                                     append ? ws.part_cnt.as<int32_t>() : nullptr, cnt_words,
+                                     append ? nullptr : ws.part_idx.as<int32_t>(), plan.part_entries / plan.list_stride,
+                                     plan.list_stride, k, stream, o.gate))
+            return -1;
         const bool timing = !o.gate && g_time_kernels.load(std::memory_order_relaxed) != 0;
         if (timing) {
             if (!ws.ev0) {
@@ -414,12 +416,12 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
                                         ws.sel_idx.as<int32_t>(), ix.device, stream, false, nullptr, o.gate))
             return -1;
         // (a list that holds every row of the store has left nothing out)
-        if (o.check_rank > 0 && k < st.n &&
+        if (!o.chained && o.check_rank > 0 && k < st.n &&
             launch_screen_check(ws.sel_key.as<float>(), nq, k, o.check_rank, ws.qn.as<float>(), st.max_norm2, d, ix.metric,
                                 o.k_rank > 0 && o.one_mma, status + kStatusTier0 + o.tier, status + kStatusFallbacks, stream,
                                 o.gate))
             return -1;
-        return ws_publish_status(ws, stream);
+        return o.chained ? 0 : ws_publish_status(ws, stream);
     }
     // exact-fp32 scan: items = (query, database chunk), laid out on the device
     int chunks = (int)std::max<int64_t>(1, std::min<int64_t>({(int64_t)kMergeCandidates / k, (st.n + 255) / 256,
@@ -440,7 +442,7 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
     if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, nullptr, nullptr, chunks, nq, k, k,
                            ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream, false, nullptr, o.gate))
         return -1;
-    return ws_publish_status(ws, stream);
+    return o.chained ? 0 : ws_publish_status(ws, stream);
 }
 
 // Allocates the four row arrays of an IVF store for `cap` rows (all or nothing).
@@ -741,6 +743,7 @@ int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const 
     TopkOpts o;
     o.tier = tier;
     o.gate = gate;
+    o.chained = true;
     int k_list = k_sel;
     const bool banded = tier == kTierScreen || tier == kTierSplitWide ||
                         (tier == kTierSplit && k_sel > 12 && banded_lists_fit(ix, k_sel));
@@ -755,11 +758,17 @@ int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const 
         o.check_rank = k_list > k_sel ? k_sel : 0;
     }
     if (split_store_topk(ix, ix.store, ws, x_dev, nq, k_list, stream, o)) return -1;
-    // banded lists: only what lies within the slack of the k-th ranking key needs the exact distance
-    const RefineBand band{ws.sel_key.as<float>(), k_sel, ws.qn.as<float>(), ix.store.max_norm2, ix.d, o.one_mma};
+    // banded lists: only what lies within the slack of the k-th ranking key needs the exact distance.  The
+    // band check of the pass (is the last candidate still inside the band?) runs in the same kernel and
+    // leaves its verdict in this tier's overflow word, which gates the next tier.
+    // (a list that holds every row of the store has left nothing out: no check)
+    int *status = ws.status.as<int>();
+    const bool tc = tier != kTierExact && flat_kernel_choice() == FlatKernel::TC;
+    const RefineBand band{ws.sel_key.as<float>(), k_sel, ws.qn.as<float>(), ix.store.max_norm2, ix.d, o.one_mma, banded,
+                          (tc && k_list < n) ? o.check_rank : 0, status + kStatusTier0 + tier, status + kStatusFallbacks};
     return launch_refine_finalize(ix.store.hi, ix.store.lo, ix.dp, ix.d, x_dev, ix.d, ws.sel_idx.as<int32_t>(), nq, k_list,
                                   (int)k, ix.metric, nullptr, label_offset, d_dev, i_dev, ix.device, stream, nullptr, nullptr,
-                                  nullptr, nullptr, gate, banded ? &band : nullptr);
+                                  nullptr, nullptr, gate, (tc && (banded || band.check_rank > 0)) ? &band : nullptr);
 }
 
 // The whole search for one block of queries, all pointers on the device.

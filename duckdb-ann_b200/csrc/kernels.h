@@ -76,6 +76,14 @@ struct FlatPlan {
 // Chooses the decomposition for nq queries against n rows on a device with `sms` SMs.
 FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms);
 
+// Scratch of one flat_tc launch, set up by ONE kernel (gated like the launch it serves): the per-query
+// threshold words to "no threshold yet" (all ones), the scheduler memory and the fill counts of the append
+// lists (cnt, may be null) to zero, and - for the selections that write whole lists (idx non-null) - row
+// number -1 in the first k slots of each of the `lists` lists of `list_stride` slots.
+int launch_flat_scratch_init(uint32_t *qtau, size_t qtau_words, int *sched, size_t sched_ints, int32_t *cnt,
+                             size_t cnt_words, int32_t *idx, size_t lists, int list_stride, int k, cudaStream_t stream,
+                             const int *gate);
+
 // Fused split-TF32 GEMM + k-selection on the tensor cores.  Inputs are hi/lo row
 // stores of the database (n x dp) and the queries (nq x dp), plus row norms for L2.
 // Writes 128 unsorted lists of k (key, local row) pairs per list slot
@@ -226,8 +234,12 @@ int launch_merge_filtered(const float *part_key, const int32_t *part_idx, const 
                           cudaStream_t stream, const int *lists_started = nullptr, const int *gate = nullptr);
 
 // Optional input of launch_refine_finalize: the candidates were ranked by tensor-core keys
-// (key[q * k_sel + j], ascending) under the slack of key_slack; only those within the slack of the
-// rank-th key can be among the exact `rank` best, the others are not re-evaluated.
+// (key[q * k_sel + j], ascending) under the slack of key_slack.
+//  cut: only the candidates within the slack of the rank-th key can be among the exact `rank` best; the others
+//       are not re-evaluated.
+//  check_rank > 0: the band check of the pass that selected them - if the LAST candidate of a query lies within
+//       the slack of its check_rank-th key, rows that were not kept could belong to the answer: *overflow (0 so
+//       far) becomes kScreenOverflow and *overflow_count (optional) counts it once per pass.
 struct RefineBand {
     const float *key;
     int rank;
@@ -235,6 +247,10 @@ struct RefineBand {
     const unsigned *x_max_norm2;
     int d;
     bool one_mma;
+    bool cut;
+    int check_rank;
+    int *overflow;
+    int *overflow_count;
 };
 
 // Flat: recomputes the distance of every selected (query, row) pair in exact fp32

@@ -263,6 +263,20 @@ merge_filtered_kernel(const float *__restrict__ part_key, const int32_t *__restr
     }
 }
 
+// One kernel in place of three or four memsets in front of a flat_tc launch (see kernels.h).
+__global__ void flat_scratch_init_kernel(uint32_t *qtau, size_t qtau_words, int *sched, size_t sched_ints, int32_t *cnt,
+                                         size_t cnt_words, int32_t *idx, size_t lists, int list_stride, int k,
+                                         const int *gate) {
+    if (gate_closed(gate)) return;
+    const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, step = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = t0; i < qtau_words; i += step) qtau[i] = 0xffffffffu;
+    for (size_t i = t0; i < sched_ints; i += step) sched[i] = 0;
+    if (cnt)
+        for (size_t i = t0; i < cnt_words; i += step) cnt[i] = 0;
+    if (idx)
+        for (size_t i = t0; i < lists * (size_t)k; i += step) idx[(i / k) * (size_t)list_stride + i % k] = -1;
+}
+
 // Band check of a tensor-core ranking.  The guarantee of the screened search (and of the split
 // product with spare candidates) holds while the LAST of the k_list candidates of a query lies
 // beyond the slack above its k_rank-th key.  If it is still inside that band, rows may have been
@@ -296,16 +310,24 @@ refine_finalize_kernel(const float *__restrict__ xhi, const float *__restrict__ 
     const int64_t q = blockIdx.x;
     // candidates beyond the slack above the rank-th ranking key cannot be among the exact best
     float band_cut = kInf;
-    if (band.key && band.rank <= k_sel)
-        band_cut = band.key[q * k_sel + band.rank - 1] +
-                   key_slack(band.q_norm2[q], __uint_as_float(*band.x_max_norm2), band.d, metric != 0, band.one_mma);
+    if (band.key) {
+        const float slack = key_slack(band.q_norm2[q], __uint_as_float(*band.x_max_norm2), band.d, metric != 0, band.one_mma);
+        if (band.cut && band.rank <= k_sel) band_cut = band.key[q * k_sel + band.rank - 1] + slack;
+        // band check of the selecting pass: the last candidate still inside the band means rows may be missing
+        if (threadIdx.x == 0 && band.check_rank > 0 && band.check_rank < k_sel) {
+            const float last = band.key[q * k_sel + k_sel - 1], kth = band.key[q * k_sel + band.check_rank - 1];
+            if (last < kInf && last <= kth + slack) {
+                if (atomicCAS(band.overflow, 0, kScreenOverflow) == 0 && band.overflow_count) atomicAdd(band.overflow_count, 1);
+            }
+        }
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const bool l2 = metric != 0;
     const float *qv = queries + q * (int64_t)q_stride;
     for (int j = warp; j < P; j += nwarps) {
         float key = kInf;
         int32_t val = 0x7fffffff;
-        if (j < k_sel && !(band.key && band.key[q * k_sel + j] > band_cut)) {
+        if (j < k_sel && !(band.key && band.cut && band.key[q * k_sel + j] > band_cut)) {
             const int32_t idx = sel_idx[q * k_sel + j];
             bool keep_approx = false;
             if (idx >= 0 && approx_key) {
@@ -502,6 +524,21 @@ int launch_screen_check(const float *sel_key, int64_t nq, int k_list, int k_rank
     return 0;
 }
 
+int launch_flat_scratch_init(uint32_t *qtau, size_t qtau_words, int *sched, size_t sched_ints, int32_t *cnt,
+                             size_t cnt_words, int32_t *idx, size_t lists, int list_stride, int k, cudaStream_t stream,
+                             const int *gate) {
+    size_t most = qtau_words > sched_ints ? qtau_words : sched_ints;
+    if (cnt && cnt_words > most) most = cnt_words;
+    if (idx && lists * (size_t)k > most) most = lists * (size_t)k;
+    if (most == 0) return 0;
+    const unsigned blocks = (unsigned)std::min<size_t>((most + 255) / 256, 1184);
+    flat_scratch_init_kernel<<<blocks, 256, 0, stream>>>(qtau, qtau_words, sched, sched_ints, cnt, cnt_words, idx, lists,
+                                                         list_stride, k, gate);
+    count_launch();
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
 int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, const float *queries, int q_stride,
                            const int32_t *sel_idx, int64_t nq, int k_sel, int k_out, int metric,
                            const int64_t *ids, int64_t label_offset, float *out_d, int64_t *out_i, int device,
@@ -515,7 +552,9 @@ int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, co
     refine_finalize_kernel<<<(unsigned)nq, 128, smem, stream>>>(xhi, xlo, dp, d, queries, q_stride, sel_idx, k_sel,
                                                                 k_out, P, metric, ids, label_offset, approx_key, rnorm, xnorm,
                                                                 out_d, out_i, out_row, gate,
-                                                                band ? *band : RefineBand{nullptr, 0, nullptr, nullptr, 0, false});
+                                                                band ? *band
+                                                                     : RefineBand{nullptr, 0, nullptr, nullptr, 0, false, false, 0,
+                                                                                  nullptr, nullptr});
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
