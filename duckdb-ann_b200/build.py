@@ -26,7 +26,7 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libann_cuda.so")
 DRIVER = os.path.join(HERE, "backend_driver")
 
-LIB_SOURCES = ["prep.cu", "scan.cu", "merge.cu", "flat_tc.cu", "flat_tc_bk32.cu", "index.cu", "sharded.cu",
+LIB_SOURCES = ["prep.cu", "scan.cu", "merge.cu", "flat_tc.cu", "flat_tc_bk32.cu", "flat_tc_h16.cu", "index.cu", "sharded.cu",
                "cuda_diskann_bridge.cu", "disk_search.cu", "gpu_backend_cuda.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # /usr/bin/g++ is the system compiler; the image's $CXX points at a gcc without OpenMP support files
@@ -55,7 +55,7 @@ def build(force: bool = False, verbose: bool = False, measure: bool = False) -> 
         LIB = os.path.join(HERE, "libann_cuda_measure.so")
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".hpp"))]
-    headers.append(os.path.join(CSRC, "flat_tc.cu"))  # flat_tc_bk32.cu includes it
+    headers.append(os.path.join(CSRC, "flat_tc.cu"))  # flat_tc_bk32.cu and flat_tc_h16.cu include it
     headers += [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
     headers += [os.path.join(INCLUDE, "faiss", f) for f in os.listdir(os.path.join(INCLUDE, "faiss"))]
     headers.append(os.path.abspath(__file__))

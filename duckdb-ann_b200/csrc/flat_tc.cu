@@ -41,6 +41,17 @@
 // it alternates between their two lists, keeping the one it is not working on
 // parked (its fill counts in global memory).
 //
+// Pair mode of the static schedule (even number of query tiles and of SMs): the kernel is launched
+// as clusters of two CTAs, and a PAIR owns a share of the (pair of query tiles, row tile) units.
+// Both CTAs work on the same 256-row tile, each for its own query tile: a CTA stages its own 128
+// queries and HALF of the rows, the leader issues tcgen05.mma.cta_group::2 (M = 256 over the two
+// tensor memories, the two halves of the row tile read from both shared memories), and each CTA's
+// epilogue selects from its own accumulator.  A K block then costs a CTA 32 KB of shared-memory
+// fill instead of 48 KB, which is what bounded the one-CTA kernel.  Barriers: "stage full" lives in
+// the leader (both CTAs' loads count their bytes there), "stage empty" and "accumulator full" are
+// signalled in both CTAs by one multicast tcgen05.commit, "accumulator empty" collects the eight
+// epilogue warps of the pair in the leader.  No load is multicast.
+//
 // CTA layout (192 threads, one CTA per SM):
 //   warp 0     scheduler + TMA producer: takes the next chunk, announces it to the
 //              other roles through a small descriptor ring, then per K block
@@ -76,7 +87,18 @@ constexpr int BN = 256;           // database rows per tile (TMEM columns)
 // the three-MMA product and for the list scan, which want a deep ring) and, through
 // flat_tc_bk32.cu, with K blocks of 32 floats for the screened search, whose single MMA per K
 // step is otherwise dominated by the per-block bookkeeping of the issuing thread.
-#ifdef ANN_TC_VARIANT_BK32
+// A third build (flat_tc_h16.cu) is the same kernel over 16-bit operands (rows stored as fp16 or
+// bf16, queries rounded to the same type): tcgen05.mma kind::f16, K blocks of 64 elements = the
+// same 128-byte rows, 16 elements per MMA instead of 8 - twice the flops per byte staged.
+#if defined(ANN_TC_VARIANT_H16) || defined(ANN_TC_VARIANT_BK32)
+#define ANN_TC_SECONDARY 1  // a second or third build of this file: kernels and their launcher only
+#endif
+#if defined(ANN_TC_VARIANT_H16)
+#define ANN_TC_BK 64
+#define ANN_TC_ELEM_BYTES 2
+#define ANN_TC_KIND "kind::f16"
+#define ANN_TC_LAUNCH launch_flat_tc_h16
+#elif defined(ANN_TC_VARIANT_BK32)
 #define ANN_TC_BK 32
 #define ANN_TC_LAUNCH launch_flat_tc_bk32
 #else
@@ -85,9 +107,16 @@ constexpr int BN = 256;           // database rows per tile (TMEM columns)
 #ifndef ANN_TC_BK
 #define ANN_TC_BK 16
 #endif
-constexpr int BK = ANN_TC_BK;     // floats per K block: 32 = one 128-byte swizzled row, 16 = one 64-byte row
-static_assert(BK == 32 || BK == 16, "K block is one 128-byte or one 64-byte swizzled row");
-constexpr int kStages = 64 / BK;  // the ring always holds 64 floats of K: 2 x 96 KB or 4 x 48 KB
+#ifndef ANN_TC_ELEM_BYTES
+#define ANN_TC_ELEM_BYTES 4
+#define ANN_TC_KIND "kind::tf32"
+#endif
+constexpr int BK = ANN_TC_BK;     // elements per K block: one 128-byte swizzled row (32 floats, 64 halves) or one 64-byte row (16 floats)
+constexpr int kElemBytes = ANN_TC_ELEM_BYTES;
+constexpr bool kH16 = kElemBytes == 2;
+constexpr int kMmaK = 32 / kElemBytes;  // elements of K per MMA instruction: always 32 bytes of each operand row
+static_assert(BK * kElemBytes == 128 || BK * kElemBytes == 64, "K block is one 128-byte or one 64-byte swizzled row");
+constexpr int kStages = 256 / (BK * kElemBytes);  // the ring always holds 256 bytes of K per row: 2 x 96 KB or 4 x 48 KB
 // Screened mode needs the hi planes only: the lo half of every stage serves as a stage of its own,
 // so the ring is twice as deep (stage s = planes s & 1 of the physical stage s >> 1).
 constexpr int kMaxStages = 2 * kStages;
@@ -97,11 +126,12 @@ constexpr int kMaxStages = 2 * kStages;
 // kBBytes, and the ring holds more, smaller stages.
 constexpr int kPairStages = 6;
 constexpr int kBarStages = kMaxStages > kPairStages ? kMaxStages : kPairStages;
-constexpr int kRowBytes = BK * 4;
-constexpr uint64_t kDescLayout = BK == 32 ? 2ull : 4ull;    // SWIZZLE_128B : SWIZZLE_64B
+constexpr int kRowBytes = BK * kElemBytes;
+constexpr bool kWideRows = kRowBytes == 128;                // the builds that have the pair mode
+constexpr uint64_t kDescLayout = kWideRows ? 2ull : 4ull;   // SWIZZLE_128B : SWIZZLE_64B
 constexpr uint64_t kDescSbo = (8 * kRowBytes) >> 4;         // 8-row group stride, in 16-byte units
-constexpr int kABytes = BM * BK * 4;                    // 16 KB
-constexpr int kBBytes = BN * BK * 4;                    // 32 KB
+constexpr int kABytes = BM * kRowBytes;                 // 16 KB
+constexpr int kBBytes = BN * kRowBytes;                 // 32 KB
 constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;  // hi + lo of both operands: 96 KB
 constexpr int kPairStageBytes = kABytes + kBBytes / 2;  // pair mode: own queries + half of the row tile
 static_assert(kPairStages * kPairStageBytes <= kStages * kStageBytes, "the pair ring fits into the stage memory");
@@ -128,11 +158,14 @@ static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 
 // tcgen05 instruction descriptor, kind::tf32: D fp32, A and B TF32, both K-major,
 // N = 256, M = 128.
-constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
+// (16-bit build: the operand format, 0 = fp16, 1 = bf16, is added at run time - see operand_format)
+constexpr uint32_t kOperandTf32 = kH16 ? 0u : 2u;
+constexpr uint32_t kInstrDesc = (1u << 4) | (kOperandTf32 << 7) | (kOperandTf32 << 10) | ((uint32_t)(BN >> 3) << 17) |
                                 ((uint32_t)(BM >> 4) << 24);
 // The same for cta_group::2: M = 256, 128 rows of it in the tensor memory of each CTA of the pair.
-constexpr uint32_t kInstrDescPair = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
+constexpr uint32_t kInstrDescPair = (1u << 4) | (kOperandTf32 << 7) | (kOperandTf32 << 10) | ((uint32_t)(BN >> 3) << 17) |
                                     ((uint32_t)((2 * BM) >> 4) << 24);
+__host__ __device__ constexpr uint32_t operand_format(int bf16) { return bf16 ? ((1u << 7) | (1u << 10)) : 0u; }
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -201,13 +234,15 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
     return (uint64_t)((addr >> 4) & 0x3fffu) | (1ull << 16) | (kDescSbo << 32) | (1ull << 46) | (kDescLayout << 61);
 }
 
-__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+// (fmt: operand_format() of the 16-bit build, 0 otherwise)
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate,
+                                         uint32_t fmt = 0) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        "tcgen05.mma.cta_group::1." ANN_TC_KIND " [%0], %1, %2, %3, p;\n\t}"
         :
-        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate)
+        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDesc | fmt), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
@@ -245,13 +280,14 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
 }
 // One MMA over both CTAs of the pair: A = 2 x 128 queries (each CTA's own), B = 2 x 128 rows (half
 // of the tile in each CTA), D = 128 x 256 in each CTA's tensor memory.  Issued by the leader only.
-__device__ __forceinline__ void mma_tf32_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void mma_tf32_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate,
+                                              uint32_t fmt = 0) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        "tcgen05.mma.cta_group::2." ANN_TC_KIND " [%0], %1, %2, %3, p;\n\t}"
         :
-        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDescPair), "r"(accumulate)
+        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDescPair | fmt), "r"(accumulate)
         : "memory");
 }
 // Arrives, once the MMAs issued so far are complete, on the barrier at the same address in BOTH CTAs.
@@ -404,6 +440,7 @@ struct KernelArgs {
     int withhold_after;   // test hook (-1 = off): see flat_test_withhold_after in kernels.h
     const int *gate;      // may be null: run only if *gate == kScreenOverflow (a fallback pass)
     int pair;             // launched as clusters of two CTAs that share row tiles (screened, static schedule)
+    int bf16;             // 16-bit build: operands are bf16 (else fp16)
 #ifdef ANN_CUDA_MEASURE
     unsigned long long *stats;  // see kStat* below
     int debug;  // bit 0 = epilogue skips selection, bit 1 = MMA issuer skips the MMAs, bit 2 = no appends, bit 3 = consume only
@@ -941,11 +978,11 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             tma_load_2d(base + 2 * kABytes + (stage & 1) * kBBytes, &map_xhi, kb * BK, (int32_t)trow, full);
                         } else {
                             const uint32_t base = smem_base + stage * kStageBytes;
-                            mbar_expect_tx(full, kStageBytes);
+                            mbar_expect_tx(full, kH16 ? 2 * kABytes + kBBytes : kStageBytes);
                             tma_load_2d(base, &map_qhi, kb * BK, cur * BM, full);
                             tma_load_2d(base + kABytes, &map_qlo, kb * BK, cur * BM, full);
                             tma_load_2d(base + 2 * kABytes, &map_xhi, kb * BK, (int32_t)trow, full);
-                            tma_load_2d(base + 2 * kABytes + kBBytes, &map_xlo, kb * BK, (int32_t)trow, full);
+                            if (!kH16) tma_load_2d(base + 2 * kABytes + kBBytes, &map_xlo, kb * BK, (int32_t)trow, full);
                         }
                         if (++stage == nstages) {
                             stage = 0;
@@ -967,6 +1004,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             uint32_t it = 0;  // tiles issued by this CTA
+            const uint32_t fmt = kH16 ? operand_format(args.bf16) : 0u;
             for (uint32_t wi = 0;; wi++) {
                 const uint32_t w = wi % kWorkRing;
                 if (!mbar_wait(bar_wfull + 8 * w, (wi / kWorkRing) & 1, abort_flag, args.status, args.wait_ns, 6)) goto done;
@@ -992,9 +1030,9 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             const uint64_t a0 = make_smem_desc(base);
                             const uint64_t b0 = make_smem_desc(base + kABytes);
                             if (!(kdebug(args) & 2)) {
-                                mma_tf32_pair(tmem_d, a0, b0, kb != 0);
+                                mma_tf32_pair(tmem_d, a0, b0, kb != 0, fmt);
 #pragma unroll
-                                for (int ks = 1; ks < BK / 8; ks++) mma_tf32_pair(tmem_d, a0 + 2 * ks, b0 + 2 * ks, 1);
+                                for (int ks = 1; ks < BK / kMmaK; ks++) mma_tf32_pair(tmem_d, a0 + 2 * ks, b0 + 2 * ks, 1, fmt);
                             }
                             mma_commit_pair(bar_empty + 8 * stage);  // frees the stage in both CTAs
                             if (++stage == nstages) {
@@ -1011,22 +1049,28 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             const uint64_t a0 = make_smem_desc(base + (stage & 1) * kABytes);
                             const uint64_t b0 = make_smem_desc(base + 2 * kABytes + (stage & 1) * kBBytes);
                             if (!(kdebug(args) & 2)) {
-                                mma_tf32(tmem_d, a0, b0, kb != 0);
+                                mma_tf32(tmem_d, a0, b0, kb != 0, fmt);
 #pragma unroll
-                                for (int ks = 1; ks < BK / 8; ks++) mma_tf32(tmem_d, a0 + 2 * ks, b0 + 2 * ks, 1);
+                                for (int ks = 1; ks < BK / kMmaK; ks++) mma_tf32(tmem_d, a0 + 2 * ks, b0 + 2 * ks, 1, fmt);
                             }
                         } else {
                             const uint32_t base = smem_base + stage * kStageBytes;
 #pragma unroll
-                            for (int ks = 0; ks < BK / 8; ks++) {
+                            for (int ks = 0; ks < BK / kMmaK; ks++) {
                                 const uint64_t a_hi = make_smem_desc(base + ks * 32);
                                 const uint64_t a_lo = make_smem_desc(base + kABytes + ks * 32);
                                 const uint64_t b_hi = make_smem_desc(base + 2 * kABytes + ks * 32);
                                 const uint64_t b_lo = make_smem_desc(base + 2 * kABytes + kBBytes + ks * 32);
                                 if (kdebug(args) & 2) continue;
-                                mma_tf32(tmem_d, a_hi, b_lo, (kb | ks) != 0);
-                                mma_tf32(tmem_d, a_lo, b_hi, 1);
-                                mma_tf32(tmem_d, a_hi, b_hi, 1);
+                                if (kH16) {
+                                    // 16-bit rows are exact: the query alone is split, q = q_hi + q_lo
+                                    mma_tf32(tmem_d, a_lo, b_hi, (kb | ks) != 0, fmt);
+                                    mma_tf32(tmem_d, a_hi, b_hi, 1, fmt);
+                                } else {
+                                    mma_tf32(tmem_d, a_hi, b_lo, (kb | ks) != 0);
+                                    mma_tf32(tmem_d, a_lo, b_hi, 1);
+                                    mma_tf32(tmem_d, a_hi, b_hi, 1);
+                                }
                             }
                         }
                         mma_commit(bar_empty + 8 * stage);  // stage is free once these MMAs have read it
@@ -1189,13 +1233,10 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     for (int j = 0; j < 32; j++) mask |= (key_of(raw, g, j) < tau) ? (1u << j) : 0u;
                     return mask & valid;
                 };
-                // key of column j, j known only at run time (rare path): predicated selects
+                // key of column j, j known only at run time: the accumulator comes out of a select tree
                 auto pick = [&](const uint32_t (&raw)[32], int g, int j) -> float {
-                    float v = 0.f;
-#pragma unroll
-                    for (int jj = 0; jj < 32; jj++)
-                        if (jj == j) v = key_of(raw, g, jj);
-                    return v;
+                    const float acc = __uint_as_float(select32(raw, j));
+                    return args.l2 ? fmaf(-2.f, acc, xn_s[buf * BN + g * 32 + j]) : -acc;
                 };
                 auto process32 = [&](const uint32_t (&raw)[32], int g) {
                     const int nvalid = ncols - g * 32;
@@ -1244,33 +1285,18 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                                 const bool p = mask != 0;
                                 const int j = p ? __ffs(mask) - 1 : 0;
                                 mask &= mask - 1;
-                                const float acc = __uint_as_float(select32(raw, j));
-                                const float kj = args.l2 ? fmaf(-2.f, acc, xn_s[buf * BN + g * 32 + j]) : -acc;
-                                st_global_pair_if(p, bk + cnt, kj, bi + cnt, colg + j);
+                                st_global_pair_if(p, bk + cnt, pick(raw, g, j), bi + cnt, colg + j);
                                 cnt += p ? 1 : 0;
                             }
                         } else {
-                            // Dense hits (a list that has no threshold yet): column by column, for the columns
-                            // in which SOME row of the warp has a hit.  The loop and the jump on the column
-                            // number are warp-uniform; inside a case the column is a compile-time register
-                            // index.  ~160 cycles per column with one warp per scheduler, whatever the number
-                            // of rows that store.
-                            uint32_t cols = __reduce_or_sync(kFullMask, mask);
-                            while (cols) {
-                                const int j = __ffs(cols) - 1;
-                                cols &= cols - 1;
-                                float kj = 0.f;
-                                switch (j) {
-#define ANN_COL(J) case J: kj = key_of(raw, g, J); break;
-                                    ANN_COL(0) ANN_COL(1) ANN_COL(2) ANN_COL(3) ANN_COL(4) ANN_COL(5) ANN_COL(6) ANN_COL(7)
-                                    ANN_COL(8) ANN_COL(9) ANN_COL(10) ANN_COL(11) ANN_COL(12) ANN_COL(13) ANN_COL(14) ANN_COL(15)
-                                    ANN_COL(16) ANN_COL(17) ANN_COL(18) ANN_COL(19) ANN_COL(20) ANN_COL(21) ANN_COL(22) ANN_COL(23)
-                                    ANN_COL(24) ANN_COL(25) ANN_COL(26) ANN_COL(27) ANN_COL(28) ANN_COL(29) ANN_COL(30) ANN_COL(31)
-#undef ANN_COL
-                                    default: break;
-                                }
+                            // Dense hits (a list that has no threshold yet, or a short one): all 32 columns in
+                            // straight-line code, a predicated pair of stores each - ~25 cycles per column
+                            // whatever it holds.  (A warp-uniform loop over the columns that have a hit, with a
+                            // jump table on the column number, cost ~160 cycles per column it visited.)
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
                                 const bool p = (mask >> j) & 1u;
-                                st_global_pair_if(p, bk + cnt, kj, bi + cnt, colg + j);
+                                st_global_pair_if(p, bk + cnt, key_of(raw, g, j), bi + cnt, colg + j);
                                 cnt += p ? 1 : 0;
                             }
                         }
@@ -1389,15 +1415,19 @@ EncodeTiledFn encode_fn() {
 
 // Row-major (rows x dp) fp32 matrix, boxes of box_rows x BK floats, swizzled by
 // row width.  Rows past `rows` read as zero.
-int make_map(CUtensorMap *map, const float *base, int64_t rows, int dp, int box_rows) {
+int make_map(CUtensorMap *map, const float *base, int64_t rows, int dp, int box_rows, bool bf16 = false) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return set_error("cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)dp, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)dp * sizeof(float)};
+    cuuint64_t strides[1] = {(cuuint64_t)dp * kElemBytes};
     cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, BK == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+    // (16-bit build: `base` points at fp16 or bf16 elements)
+    const CUtensorMapDataType type = !kH16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                     : bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUresult r = fn(map, type, 2, const_cast<float *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, kWideRows ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return set_error("cuTensorMapEncodeTiled failed with code %d", (int)r);
@@ -1406,7 +1436,7 @@ int make_map(CUtensorMap *map, const float *base, int64_t rows, int dp, int box_
 
 template <int KR, int MODE>
 int launch_variant(const FlatPlan &plan, const CUtensorMap maps[4], const KernelArgs &args, cudaStream_t stream) {
-    if constexpr (KR == 1 && MODE == kSelAppend && BK == 32) {
+    if constexpr (KR == 1 && MODE == kSelAppend && kWideRows) {
       if (args.pair) {  // clusters of two CTAs
         ANN_CUDA_TRY(cudaFuncSetAttribute(flat_tc_kernel<KR, MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           kSmemBytes));
@@ -1439,7 +1469,7 @@ int launch_variant(const FlatPlan &plan, const CUtensorMap maps[4], const Kernel
 // Whether grid / 2 clusters of two CTAs of the append kernel can be resident at once (every SM
 // takes one CTA of this kernel; the pairs must find two free SMs side by side).  Asked once.
 bool pair_clusters_fit(int grid) {
-  if constexpr (BK != 32) {
+  if constexpr (!kWideRows) {
     (void)grid;
     return false;
   } else {
@@ -1471,7 +1501,7 @@ bool pair_clusters_fit(int grid) {
 
 }  // namespace
 
-#ifndef ANN_TC_VARIANT_BK32
+#ifndef ANN_TC_SECONDARY
 constexpr int64_t kMaxTilesPerChunk = 2;
 
 namespace {
@@ -1571,7 +1601,7 @@ FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms) {
     return p;
 }
 
-#endif  // !ANN_TC_VARIANT_BK32
+#endif  // !ANN_TC_SECONDARY
 
 int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
                    const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
@@ -1581,7 +1611,7 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     if (n <= 0 || nq <= 0) return 0;
     static_assert(kMaxListK <= 66 * 32, "the widest replace-max list covers every list length");
     if (k <= 0 || k > kMaxListK) return set_error("k must be in [1, %d]", kMaxListK);
-#ifndef ANN_TC_VARIANT_BK32
+#ifndef ANN_TC_SECONDARY
     // the screened (one-MMA) search runs in the build of this file with K blocks of 32 floats
     if (screen && screen->one_mma && !grouped && screen->k_rank >= 1 && screen->k_rank <= k && k <= kScreenMaxList &&
         k > kSmemListMax && dp % 32 == 0)
@@ -1591,8 +1621,10 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     if (dp % BK != 0) return set_error("padded dimension must be a multiple of %d", BK);
     if (n > 0x7fffffffll - BN) return set_error("a flat shard holds at most 2^31 rows");
     CUtensorMap maps[4];
-    if (make_map(&maps[0], qhi, nq, dp, BM) || make_map(&maps[1], qlo, nq, dp, BM) ||
-        make_map(&maps[2], xhi, n, dp, BN) || make_map(&maps[3], xlo, n, dp, BN))
+    const bool bf16 = kH16 && screen && screen->bf16;
+    // (16-bit build: there is no lo plane of the rows; the fourth map repeats the third)
+    if (make_map(&maps[0], qhi, nq, dp, BM, bf16) || make_map(&maps[1], qlo ? qlo : qhi, nq, dp, BM, bf16) ||
+        make_map(&maps[2], xhi, n, dp, BN, bf16) || make_map(&maps[3], kH16 ? xhi : xlo, n, dp, BN, bf16))
         return -1;
     KernelArgs a;
     a.xnorm = xnorm;
@@ -1630,8 +1662,9 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     // the static schedule parks and resumes append buffers; it pays for the screened search only
     a.static_g = use_screen ? plan.static_g : 0;
     // pair mode: the fourth map becomes the hi plane of the rows in boxes of HALF a tile
-    a.pair = (a.static_g && plan.pair && BK == 32 && plan.grid % 2 == 0 && pair_clusters_fit(plan.grid)) ? 1 : 0;
-    if (a.pair && make_map(&maps[3], xhi, n, dp, BN / 2)) return -1;
+    a.pair = (a.static_g && plan.pair && kWideRows && plan.grid % 2 == 0 && pair_clusters_fit(plan.grid)) ? 1 : 0;
+    if (a.pair && make_map(&maps[3], xhi, n, dp, BN / 2, bf16)) return -1;
+    a.bf16 = bf16 ? 1 : 0;
     a.k_rank = use_band ? screen->k_rank : k;
     a.q_norm2 = use_band ? screen->q_norm2 : nullptr;
     a.x_max_norm2 = use_band ? screen->x_max_norm2 : nullptr;

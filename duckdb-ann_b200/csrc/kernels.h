@@ -123,6 +123,9 @@ struct ScreenInput {
     // large stores).  false: the three-MMA split product with the same banded lists - the slack is
     // then the split product's much smaller one (see key_slack).
     bool one_mma = true;
+    // 16-bit build only (launch_flat_tc_h16): 0 = fp16 operands, 1 = bf16.  There the rows are exact in
+    // their 16-bit type and only the query is rounded (one_mma) or split in two 16-bit parts.
+    int bf16 = 0;
 };
 constexpr int kScreenMaxList = 256;  // longest list (k_rank + spare) the screened mode keeps
 constexpr int kScreenMaxK = kScreenMaxList - kSplitSpare;  // largest k searched with screening
@@ -150,6 +153,14 @@ int launch_flat_tc_bk32(const FlatPlan &plan, const float *xhi, const float *xlo
                         const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
                         int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
                         const GroupedWork *grouped, const ScreenInput *screen, const int *gate, int32_t *flat_part_cnt);
+// The same kernel over 16-bit operands (flat_tc_h16.cu; tcgen05.mma kind::f16): xhi = rows as fp16 or bf16
+// (n x dp elements, dp a multiple of 64), qhi / qlo = the two 16-bit parts of the queries, xlo unused.
+// Banded lists only (screen non-null): one_mma -> q_hi.x, static schedule and pair mode as in the
+// 32-float build; else q_hi.x + q_lo.x with dynamic chunks.
+int launch_flat_tc_h16(const FlatPlan &plan, const float *xhi, const float *xlo, const float *xnorm, int64_t n,
+                       const float *qhi, const float *qlo, int64_t nq, int dp, int k, int metric, float *part_key,
+                       int32_t *part_idx, uint32_t *qtau, int *sched, int *status, int device, cudaStream_t stream,
+                       const GroupedWork *grouped, const ScreenInput *screen, const int *gate, int32_t *flat_part_cnt);
 // make_flat_plan for a screened search: lists of `k` (up to kScreenMaxList) in append mode
 FlatPlan make_flat_plan_screened(int64_t nq, int64_t n, int k, int sms);
 

@@ -151,40 +151,51 @@ def test_large_k(pkg, oracle, k):
     idx.close()
 
 
-def test_a_wait_that_runs_out_fails_the_search_and_leaves_the_device_usable(pkg, oracle):
+@pytest.mark.parametrize("shape", ["split", "screened-pairs"])
+def test_a_wait_that_runs_out_fails_the_search_and_leaves_the_device_usable(pkg, oracle, shape):
     """Every wait inside the tensor-core kernel is bounded.  With the bound lowered to 20 ms and the
     loader told to stop after three blocks of the dimension, the MMA issuer waits for a stage that
     never arrives: the kernel must give up in order, the search must FAIL (not return partial
-    lists), and the next search on the same index must work."""
+    lists), and the next search on the same index must work.  "screened-pairs" is the same on the
+    kernel that runs as clusters of two CTAs (tcgen05 cta_group::2): both CTAs of every pair have
+    to find their way out, the one that issues the MMAs and the one that only feeds it."""
     rng = np.random.default_rng(5)
-    xb = rng.uniform(-1, 1, (20000, 128)).astype(np.float32)
-    xq = rng.uniform(-1, 1, (40, 128)).astype(np.float32)
+    if shape == "split":
+        n, d, nq, k, kernel = 20000, 128, 40, 10, b"tcgen05"
+    else:
+        n, d, nq, k, kernel = 200_000, 32, 256, 30, b"tcgen05-screened"
+    xb = rng.uniform(-1, 1, (n, d)).astype(np.float32)
+    xq = rng.uniform(-1, 1, (nq, d)).astype(np.float32)
     lib = pkg.lib()
-    idx = pkg.CudaIndexFlat(128, pkg.METRIC_L2)
-    idx.add(xb)
-    D0, I0 = idx.search(xq, 10)
-    lib.ann_cuda_set_wait_limit_ms(20)
-    lib.ann_cuda_test_withhold_loads(3)
+    assert lib.ann_cuda_set_flat_kernel(kernel) == 0
     try:
-        with pytest.raises(pkg.AnnCudaError, match="gave up on a wait"):
-            idx.search(xq, 10)
-        tok = idx.search_async(xq, 10)
-        with pytest.raises(pkg.AnnCudaError, match="gave up on a wait"):
-            tok.wait()
-        import torch
-        idx.search_device(torch.from_numpy(xq).cuda(), 10)
-        with pytest.raises(pkg.AnnCudaError, match="gave up on a wait"):
-            idx.search_status()
-        idx.search_status()          # collected: the stream's record is clean again
+        idx = pkg.CudaIndexFlat(d, pkg.METRIC_L2)
+        idx.add(xb)
+        D0, I0 = idx.search(xq, k)
+        lib.ann_cuda_set_wait_limit_ms(20)
+        lib.ann_cuda_test_withhold_loads(3)
+        try:
+            with pytest.raises(pkg.AnnCudaError, match="gave up on a wait"):
+                idx.search(xq, k)
+            tok = idx.search_async(xq, k)
+            with pytest.raises(pkg.AnnCudaError, match="gave up on a wait"):
+                tok.wait()
+            import torch
+            idx.search_device(torch.from_numpy(xq).cuda(), k)
+            with pytest.raises(pkg.AnnCudaError, match="gave up on a wait"):
+                idx.search_status()
+            idx.search_status()          # collected: the stream's record is clean again
+        finally:
+            lib.ann_cuda_test_withhold_loads(-1)
+            lib.ann_cuda_set_wait_limit_ms(0)
+        D1, I1 = idx.search(xq, k)
+        np.testing.assert_array_equal(I1, I0)
+        np.testing.assert_array_equal(D1, D0)
+        Dref, Iref = oracle.flat_search(xb, xq, k, oracle.METRIC_L2)
+        assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D1, I1, Dref, Iref, "after a failed search")
+        idx.close()
     finally:
-        lib.ann_cuda_test_withhold_loads(-1)
-        lib.ann_cuda_set_wait_limit_ms(0)
-    D1, I1 = idx.search(xq, 10)
-    np.testing.assert_array_equal(I1, I0)
-    np.testing.assert_array_equal(D1, D0)
-    Dref, Iref = oracle.flat_search(xb, xq, 10, oracle.METRIC_L2)
-    assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D1, I1, Dref, Iref, "after a failed search")
-    idx.close()
+        lib.ann_cuda_set_flat_kernel(b"tcgen05")
 
 
 @pytest.mark.parametrize("flat_kernel", ["tcgen05-screened", "tcgen05-split"])

@@ -82,6 +82,13 @@ def test_screening_chosen_by_the_library_at_two_million_rows(pkg, oracle, kind, 
     # that exceed it send the block on, up to the exact scan: at most two passes more per entry point.
     fell_back = pkg.lib().ann_cuda_screen_fallbacks() - before
     assert fell_back <= (0 if kind == "unit" else 4), f"{fell_back} fallback passes"
+    # 300 queries are three tiles of 128, an odd number, which the kernel that runs as clusters of two
+    # CTAs (one query tile each on a shared row tile, tcgen05 cta_group::2) does not take.  The first
+    # 200 are two tiles, the second one ragged: the same answers must come back from that kernel
+    # (2.1M rows end in a ragged row tile whose second half lies wholly past the store).
+    D2, I2 = idx.search(xq[:200], k)
+    np.testing.assert_array_equal(I2, I[:200])
+    np.testing.assert_array_equal(D2, D[:200])
     idx.close()
 
 
