@@ -311,7 +311,10 @@ class FlatWorkload:
         peak = peaks["bf16_tflops_sustained"] / 2.0 / mmas
         # DRAM traffic of one launch.  Screened search: ncu capture of the full-size launch (20M rows of
         # 768 floats, 4,096 queries: 67.5 GB read + 1.2 GB written; the hi planes are 61.4 GB and are
-        # read once for all query tiles), scaled by the rows of this launch.  Split product: captures
+        # read once for all query tiles), scaled by the rows of this launch.  That capture was taken
+        # once with three one-pass metrics (a launch that holds 123 GB on the device is not captured
+        # with more); the loads it measures have not changed since.  What is re-captured with every
+        # change of the kernel is the 400,000-row case (profiles/flat_tc_kernel__flat_ip_20m.md).  Split product: captures
         # on 400,000 rows with 4,096 queries (16.2-22.3 GB + 0.47-0.49 GB), scaled by rows and query
         # tiles: there every 128-query tile streams the shard and L2 absorbs part of it.
         traffic, note = None, "no capture for this shape"
