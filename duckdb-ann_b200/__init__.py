@@ -51,6 +51,8 @@ SIGNATURES = {
     "ann_cuda_device_count": (C.c_int, []),
     "ann_cuda_device_info": (C.c_int, [C.c_char_p, C.c_size_t]),
     "ann_cuda_flat_create": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(_P)]),
+    "ann_cuda_flat_create_storage": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(_P)]),
+    "ann_cuda_index_storage": (C.c_int, [_P]),
     "ann_cuda_ivfflat_create": (C.c_int, [C.c_int, C.c_int, _I64, C.c_int, C.POINTER(_P)]),
     "ann_cuda_ivfflat_set_centroids": (C.c_int, [_P, _P]),
     "ann_cuda_ivfflat_train": (C.c_int, [_P, _I64, _P]),
@@ -155,11 +157,12 @@ def check(rc: int, what: str) -> None:
         raise AnnCudaError(f"{what}: {last_error()}")
 
 
-from .faiss_like import (METRIC_INNER_PRODUCT, METRIC_L2, CudaGpuBackend, CudaIndexFlat,  # noqa: E402
-                         CudaIndexIVFFlat, CudaShardedIndex, SearchToken, get_gpu_backend, merge_topk_device)
+from .faiss_like import (METRIC_INNER_PRODUCT, METRIC_L2, STORAGE_BF16, STORAGE_F16, STORAGE_F32,  # noqa: E402
+                         CudaGpuBackend, CudaIndexFlat, CudaIndexIVFFlat, CudaShardedIndex, SearchToken,
+                         get_gpu_backend, merge_topk_device)
 from . import diskann_bridge  # noqa: E402
 from . import sharded  # noqa: E402
 
 __all__ = ["lib", "last_error", "AnnCudaError", "CudaIndexFlat", "CudaIndexIVFFlat", "CudaShardedIndex", "CudaGpuBackend",
-           "get_gpu_backend", "merge_topk_device", "METRIC_L2", "METRIC_INNER_PRODUCT", "diskann_bridge",
-           "sharded"]
+           "get_gpu_backend", "merge_topk_device", "METRIC_L2", "METRIC_INNER_PRODUCT", "STORAGE_F32",
+           "STORAGE_F16", "STORAGE_BF16", "diskann_bridge", "sharded"]

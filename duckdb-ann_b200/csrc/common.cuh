@@ -1,6 +1,8 @@
 // Shared host/device helpers of the CUDA search library (sm_100a only).
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cstdarg>
@@ -114,13 +116,41 @@ constexpr float kInf = __builtin_huge_valf();
 // the stored norm (<= (d / 32 + 6) 2^-24 of a value that is at most 4 xm2).
 // If K is the k-th smallest ranking key of a query, its exact k-th best key is <= K + E' and a row
 // can be among the exact k best only if its ranking key is <= K + 2E' = K + slack.
-__host__ __device__ inline float key_slack(float qn, float xm2, int d, bool l2, bool screened) {
-    const float rel = screened ? 9.8e-4f + (float)d * 1.2e-7f : 1.2e-6f + (float)d * 3.6e-7f;
-    const float e = rel * sqrtf(qn * xm2);
+//
+// 16-bit stores (elem = kElemF16 / kElemBF16: rows kept as fp16 or bf16, exact in that type; only the
+// query is rounded).  One 16-bit part of the query per product ("screened"): each query element is off
+// by at most 2^-11 (fp16) or 2^-8 (bf16) of itself, fp16 elements below 2^-14 by at most 2^-25
+// absolutely, so the dot product is off by at most  rel |q||x| + 2^-25 sqrt(d) |x|  with
+//   rel = 2^-11 (1 + 2^-11) + d 2^-23 (fp16),  2^-8 (1 + 2^-8) + d 2^-23 (bf16);
+// two parts (q = q_hi + q_lo, "split"): rel = 2^-22 + 2 d 2^-23 (fp16), 2^-16 + 2 d 2^-23 (bf16).
+// Products of two 16-bit values are exact in fp32; the d 2^-23 terms bound the accumulation as above.
+constexpr int kElemF32 = 0, kElemF16 = 1, kElemBF16 = 2;
+__host__ __device__ inline float key_slack(float qn, float xm2, int d, bool l2, bool screened, int elem = kElemF32) {
+    float rel, abs_term = 0.f;
+    if (elem == kElemF32) {
+        rel = screened ? 9.8e-4f + (float)d * 1.2e-7f : 1.2e-6f + (float)d * 3.6e-7f;
+    } else if (elem == kElemF16) {
+        rel = screened ? 4.9e-4f + (float)d * 1.2e-7f : 2.4e-7f + (float)d * 2.4e-7f;
+        abs_term = 3.0e-8f * sqrtf((float)d * xm2);
+    } else {
+        rel = screened ? 3.93e-3f + (float)d * 1.2e-7f : 1.53e-5f + (float)d * 2.4e-7f;
+    }
+    const float e = rel * sqrtf(qn * xm2) + abs_term;
     return 2.f * (l2 ? 2.f * e + ((float)d * (1.f / 32.f) + 6.f) * 6e-8f * 4.f * xm2 : e);
 }
 __host__ __device__ inline float screen_slack(float qn, float xm2, int d, bool l2) {
     return key_slack(qn, xm2, d, l2, true);
 }
+
+#ifdef __CUDACC__
+// 16-bit row elements <-> float (elem = kElemF16 or kElemBF16).  Round to nearest even, as
+// faiss-metal/src/MetalIndexFlat.mm:211-236 converts rows on add; widening is exact.
+__device__ __forceinline__ float h16_to_float(uint16_t b, int elem) {
+    return elem == kElemBF16 ? __uint_as_float((uint32_t)b << 16) : __half2float(__ushort_as_half(b));
+}
+__device__ __forceinline__ uint16_t float_to_h16(float v, int elem) {
+    return elem == kElemBF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+}
+#endif
 
 }  // namespace anncuda

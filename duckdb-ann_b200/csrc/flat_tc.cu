@@ -1165,7 +1165,8 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     qtau_word = args.qtau + (size_t)qt * BM + row;
                     if (APPEND && args.banded && row_valid) {
                         slack = key_slack(args.q_norm2[(size_t)qt * BM + row], __uint_as_float(*args.x_max_norm2), args.d,
-                                          args.l2 != 0, args.screen != 0);
+                                          args.l2 != 0, args.screen != 0,
+                                          kH16 ? (args.bf16 ? kElemBF16 : kElemF16) : kElemF32);
                     }
                 }
                 tau = row_valid ? kInf : -kInf;
@@ -1621,7 +1622,7 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     if (dp % BK != 0) return set_error("padded dimension must be a multiple of %d", BK);
     if (n > 0x7fffffffll - BN) return set_error("a flat shard holds at most 2^31 rows");
     CUtensorMap maps[4];
-    const bool bf16 = kH16 && screen && screen->bf16;
+    const bool bf16 = kH16 && screen && screen->elem == kElemBF16;
     // (16-bit build: there is no lo plane of the rows; the fourth map repeats the third)
     if (make_map(&maps[0], qhi, nq, dp, BM, bf16) || make_map(&maps[1], qlo ? qlo : qhi, nq, dp, BM, bf16) ||
         make_map(&maps[2], xhi, n, dp, BN, bf16) || make_map(&maps[3], kH16 ? xhi : xlo, n, dp, BN, bf16))

@@ -41,6 +41,15 @@ ANN_CUDA_EXPORT CudaIndexFlat::CudaIndexFlat(int device, int d, faiss::MetricTyp
     if (ann_cuda_flat_create(device, d, metric_code(metric), &handle_)) fail("CudaIndexFlat");
     is_trained = true;
 }
+ANN_CUDA_EXPORT CudaIndexFlat::CudaIndexFlat(int device, int d, faiss::MetricType metric, StorageType storage)
+    : faiss::Index(d, metric) {
+    if (ann_cuda_flat_create_storage(device, d, metric_code(metric), (int)storage, &handle_)) fail("CudaIndexFlat");
+    is_trained = true;
+}
+ANN_CUDA_EXPORT StorageType CudaIndexFlat::getStorageType() const {
+    const int s = ann_cuda_index_storage(handle_);
+    return s == ANN_CUDA_STORAGE_F16 ? StorageType::Float16 : s == ANN_CUDA_STORAGE_BF16 ? StorageType::BFloat16 : StorageType::Float32;
+}
 ANN_CUDA_EXPORT CudaIndexFlat::~CudaIndexFlat() { ann_cuda_index_free(handle_); }
 
 ANN_CUDA_EXPORT void CudaIndexFlat::add(faiss::idx_t n, const float *x) {

@@ -53,10 +53,18 @@ FlatKernel flat_kernel_choice() {
 
 // Split (hi/lo) row store that grows by doubling, at least 1024 rows at a time
 // (the growth rule of faiss-metal/src/MetalIndexFlat.mm:255-270).
+// A reduced-precision store (elem = kElemF16 / kElemBF16, the StorageType of
+// faiss-metal/include/faiss-metal/MetalIndexFlat.h:38-43) keeps ONE plane of dp 16-bit elements per
+// row behind `hi` (the rows rounded to that type; nothing else is kept of them) and no `lo`.
 struct SplitStore {
     float *hi = nullptr, *lo = nullptr, *norms = nullptr;
     int64_t n = 0, cap = 0;
     int dp = 0;
+    int elem = kElemF32;
+    size_t row_bytes() const { return (size_t)dp * (elem == kElemF32 ? sizeof(float) : sizeof(uint16_t)); }
+    // plane pointers `r` rows in (a row of a 16-bit store is half as long as the pointer type says)
+    float *hi_at(int64_t r) const { return hi ? reinterpret_cast<float *>(reinterpret_cast<char *>(hi) + (size_t)r * row_bytes()) : nullptr; }
+    float *lo_at(int64_t r) const { return lo ? reinterpret_cast<float *>(reinterpret_cast<char *>(lo) + (size_t)r * row_bytes()) : nullptr; }
     // L2 stores: a reference point near the data (mean of the first rows added).  norms hold
     // |x - mu|^2 and queries are searched as q - mu: distances are the same, the dot products
     // the tensor cores form are smaller, and so is their absolute error.  Fixed while n > 0.
@@ -67,8 +75,9 @@ struct SplitStore {
     int reserve(int64_t want) {
         if (want <= cap) return 0;
         float *nh = nullptr, *nl = nullptr, *nn = nullptr;
-        const size_t row = (size_t)dp * sizeof(float);
-        if (cudaMalloc(&nh, (size_t)want * row) != cudaSuccess || cudaMalloc(&nl, (size_t)want * row) != cudaSuccess ||
+        const size_t row = row_bytes();
+        const bool two = elem == kElemF32;
+        if (cudaMalloc(&nh, (size_t)want * row) != cudaSuccess || (two && cudaMalloc(&nl, (size_t)want * row) != cudaSuccess) ||
             cudaMalloc(&nn, (size_t)want * sizeof(float)) != cudaSuccess) {
             cudaGetLastError();
             if (nh) cudaFree(nh);
@@ -79,7 +88,7 @@ struct SplitStore {
         }
         if (n > 0) {
             ANN_CUDA_TRY(cudaMemcpy(nh, hi, (size_t)n * row, cudaMemcpyDeviceToDevice));
-            ANN_CUDA_TRY(cudaMemcpy(nl, lo, (size_t)n * row, cudaMemcpyDeviceToDevice));
+            if (two) ANN_CUDA_TRY(cudaMemcpy(nl, lo, (size_t)n * row, cudaMemcpyDeviceToDevice));
             ANN_CUDA_TRY(cudaMemcpy(nn, norms, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice));
         }
         release_buffers();
@@ -102,9 +111,14 @@ struct SplitStore {
         }
         if (!max_norm2) ANN_CUDA_TRY(cudaMalloc(&max_norm2, sizeof(unsigned)));
         if (n == 0) ANN_CUDA_TRY(cudaMemsetAsync(max_norm2, 0, sizeof(unsigned), stream));
-        if (launch_split_rows(x, cnt, d, dp, hi + n * dp, lo + n * dp, norms + n, stream, l2 ? mu : nullptr, false,
-                              max_norm2))
+        if (elem != kElemF32) {
+            if (launch_split_rows_h16(x, cnt, d, dp, hi_at(n), nullptr, norms + n, stream,
+                                      l2 ? mu : nullptr, false, max_norm2, elem, nullptr))
+                return -1;
+        } else if (launch_split_rows(x, cnt, d, dp, hi + n * dp, lo + n * dp, norms + n, stream, l2 ? mu : nullptr, false,
+                                     max_norm2)) {
             return -1;
+        }
         n += cnt;
         return 0;
     }
@@ -366,13 +380,20 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
     int *status = ws.status.as<int>();
     if (!o.exact && flat_kernel_choice() == FlatKernel::TC) {
         // the split of the queries is the same in every tier: a gated fallback pass finds it in place
+        // (16-bit store: the two 16-bit parts of q - mu; a query element that overflows the type flags both
+        // tensor-core tiers, which sends the block to the exact scan)
+        if (st.elem != kElemF32 && (!o.chained || o.k_rank <= 0))
+            return set_error("internal: a 16-bit store is searched with banded lists through the tier chain only");
         if (!(o.chained && o.gate) &&
-            launch_split_rows(x_dev, nq, d, dp, ws.qhi.as<float>(), ws.qlo.as<float>(), ws.qn.as<float>(), stream,
-                              st.center(), true))
+            (st.elem != kElemF32
+                 ? launch_split_rows_h16(x_dev, nq, d, dp, ws.qhi.ptr, ws.qlo.ptr, ws.qn.as<float>(), stream, st.center(), true,
+                                         nullptr, st.elem, status + kStatusTier0)
+                 : launch_split_rows(x_dev, nq, d, dp, ws.qhi.as<float>(), ws.qlo.as<float>(), ws.qn.as<float>(), stream,
+                                     st.center(), true)))
             return -1;
         const FlatPlan plan = o.k_rank > 0 && o.one_mma ? make_flat_plan_screened(nq, st.n, k, sm_count(ix.device))
                                                         : make_flat_plan(nq, st.n, k, sm_count(ix.device));
-        const ScreenInput screen{o.k_rank, ws.qn.as<float>(), st.max_norm2, d, o.one_mma};
+        const ScreenInput screen{o.k_rank, ws.qn.as<float>(), st.max_norm2, d, o.one_mma, st.elem};
         const size_t qtau_bytes = (size_t)plan.nq_tiles * 128 * 4, sched_bytes = plan.sched_ints * 4;
         if (ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4) ||
             ws.qtau.ensure(qtau_bytes) || ws.sched.ensure(sched_bytes))
@@ -396,10 +417,15 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
             }
             ANN_CUDA_TRY(cudaEventRecord(ws.ev0, stream));
         }
-        if (launch_flat_tc(plan, st.hi, st.lo, st.norms, st.n, ws.qhi.as<float>(), ws.qlo.as<float>(), nq, dp, k,
-                           ix.metric, ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.qtau.as<uint32_t>(),
-                           ws.sched.as<int>(), status + kStatusWait, ix.device, stream, nullptr,
-                           o.k_rank > 0 ? &screen : nullptr, o.gate, append ? ws.part_cnt.as<int32_t>() : nullptr))
+        if (st.elem != kElemF32
+                ? launch_flat_tc_h16(plan, st.hi, nullptr, st.norms, st.n, ws.qhi.as<float>(), ws.qlo.as<float>(), nq, dp, k,
+                                     ix.metric, ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.qtau.as<uint32_t>(),
+                                     ws.sched.as<int>(), status + kStatusWait, ix.device, stream, nullptr, &screen, o.gate,
+                                     append ? ws.part_cnt.as<int32_t>() : nullptr)
+                : launch_flat_tc(plan, st.hi, st.lo, st.norms, st.n, ws.qhi.as<float>(), ws.qlo.as<float>(), nq, dp, k,
+                                 ix.metric, ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.qtau.as<uint32_t>(),
+                                 ws.sched.as<int>(), status + kStatusWait, ix.device, stream, nullptr,
+                                 o.k_rank > 0 ? &screen : nullptr, o.gate, append ? ws.part_cnt.as<int32_t>() : nullptr))
             return -1;
         if (timing) {
             ANN_CUDA_TRY(cudaEventRecord(ws.ev1, stream));
@@ -437,7 +463,7 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         return -1;
     if (launch_scan_items(st.hi, st.lo, dp, d, x_dev, d, ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(),
                           ws.item_re.as<int64_t>(), n_items, k, ix.metric, ws.part_key.as<float>(),
-                          ws.part_idx.as<int32_t>(), nullptr, ix.device, stream, o.gate))
+                          ws.part_idx.as<int32_t>(), nullptr, ix.device, stream, o.gate, st.elem))
         return -1;
     if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, nullptr, nullptr, chunks, nq, k, k,
                            ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream, false, nullptr, o.gate))
@@ -722,6 +748,9 @@ bool banded_lists_fit(const ann_cuda_index &ix, int k_sel) {
 
 int flat_first_tier(const ann_cuda_index &ix, int k_sel) {
     if (flat_kernel_choice() != FlatKernel::TC) return kTierExact;
+    // 16-bit store: one 16-bit part of the query per product, then two, then the exact scan - always
+    // with banded lists (stores too small for them, and k beyond them, are scanned exactly)
+    if (ix.store.elem != kElemF32) return banded_lists_fit(ix, k_sel) ? kTierScreen : kTierExact;
     // (ANN_CUDA_FLAT_SCREEN=0 turns screening off, =1 applies it to stores of any size)
     const int screen_env = g_flat_screen.load(std::memory_order_relaxed);
     if (banded_lists_fit(ix, k_sel) && (screen_env == 1 || (screen_env != 0 && ix.store.n >= kScreenMinRows)))
@@ -732,6 +761,7 @@ int flat_first_tier(const ann_cuda_index &ix, int k_sel) {
 // The tier after `tier` for this search (tier 2 exists only behind a 16-list).
 int flat_next_tier(const ann_cuda_index &ix, int k_sel, int tier) {
     if (tier == kTierScreen) return kTierSplit;
+    if (ix.store.elem != kElemF32) return kTierExact;
     if (tier == kTierSplit && k_sel <= 12 && banded_lists_fit(ix, k_sel)) return kTierSplitWide;
     return kTierExact;
 }
@@ -746,7 +776,7 @@ int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const 
     o.chained = true;
     int k_list = k_sel;
     const bool banded = tier == kTierScreen || tier == kTierSplitWide ||
-                        (tier == kTierSplit && k_sel > 12 && banded_lists_fit(ix, k_sel));
+                        (tier == kTierSplit && (k_sel > 12 || ix.store.elem != kElemF32) && banded_lists_fit(ix, k_sel));
     if (tier == kTierExact) {
         o.exact = true;
     } else if (banded) {
@@ -764,11 +794,14 @@ int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const 
     // (a list that holds every row of the store has left nothing out: no check)
     int *status = ws.status.as<int>();
     const bool tc = tier != kTierExact && flat_kernel_choice() == FlatKernel::TC;
-    const RefineBand band{ws.sel_key.as<float>(), k_sel, ws.qn.as<float>(), ix.store.max_norm2, ix.d, o.one_mma, banded,
-                          (tc && k_list < n) ? o.check_rank : 0, status + kStatusTier0 + tier, status + kStatusFallbacks};
+    const RefineBand band{tc ? ws.sel_key.as<float>() : nullptr, k_sel, ws.qn.as<float>(), ix.store.max_norm2, ix.d, o.one_mma,
+                          ix.store.elem, banded, (tc && k_list < n) ? o.check_rank : 0, status + kStatusTier0 + tier,
+                          status + kStatusFallbacks};
+    // (a 16-bit store always hands the band over: it says how the rows are to be read)
+    const bool give = (tc && (banded || band.check_rank > 0)) || ix.store.elem != kElemF32;
     return launch_refine_finalize(ix.store.hi, ix.store.lo, ix.dp, ix.d, x_dev, ix.d, ws.sel_idx.as<int32_t>(), nq, k_list,
                                   (int)k, ix.metric, nullptr, label_offset, d_dev, i_dev, ix.device, stream, nullptr, nullptr,
-                                  nullptr, nullptr, gate, (tc && (banded || band.check_rank > 0)) ? &band : nullptr);
+                                  nullptr, nullptr, gate, give ? &band : nullptr);
 }
 
 // The whole search for one block of queries, all pointers on the device.
@@ -1074,6 +1107,24 @@ static int create_common(int device, int d, int metric, bool ivf, int64_t nlist,
 
 int ann_cuda_flat_create(int device, int d, int metric, ann_cuda_index **out) {
     return create_common(device, d, metric, false, 0, out);
+}
+
+int ann_cuda_flat_create_storage(int device, int d, int metric, int storage, ann_cuda_index **out) {
+    if (storage != ANN_CUDA_STORAGE_F32 && storage != ANN_CUDA_STORAGE_F16 && storage != ANN_CUDA_STORAGE_BF16)
+        return set_error("unknown storage type %d", storage);
+    if (create_common(device, d, metric, false, 0, out)) return -1;
+    if (storage != ANN_CUDA_STORAGE_F32) {
+        // one plane of 16-bit elements, rows padded to whole 128-byte K blocks
+        (*out)->store.elem = storage == ANN_CUDA_STORAGE_F16 ? kElemF16 : kElemBF16;
+        (*out)->dp = (d + 63) / 64 * 64;
+        (*out)->store.dp = (*out)->dp;
+    }
+    return 0;
+}
+
+int ann_cuda_index_storage(const ann_cuda_index *ix) {
+    if (!ix) return -1;
+    return ix->store.elem == kElemF16 ? ANN_CUDA_STORAGE_F16 : ix->store.elem == kElemBF16 ? ANN_CUDA_STORAGE_BF16 : ANN_CUDA_STORAGE_F32;
 }
 
 int ann_cuda_ivfflat_create(int device, int d, int64_t nlist, int metric, ann_cuda_index **out) {
@@ -1618,8 +1669,8 @@ int ann_cuda_flat_get_rows(const ann_cuda_index *ix, int64_t first, int64_t n, f
     int rc = 0;
     for (int64_t r0 = 0; r0 < n && rc == 0; r0 += slab) {
         const int64_t nb = std::min(slab, n - r0);
-        rc = launch_join_rows(ix->store.hi + (first + r0) * ix->dp, ix->store.lo + (first + r0) * ix->dp, nb, ix->d,
-                              ix->dp, buf, nullptr);
+        rc = launch_join_rows(ix->store.hi_at(first + r0), ix->store.lo_at(first + r0), nb, ix->d, ix->dp, buf, nullptr,
+                              ix->store.elem);
         if (rc == 0 && cudaMemcpy(rows + r0 * ix->d, buf, (size_t)nb * ix->d * 4, cudaMemcpyDeviceToHost) != cudaSuccess)
             rc = set_error("device to host copy failed");
     }
@@ -1737,6 +1788,7 @@ extern "C" int ann_cuda_flat_search_small_static(const ann_cuda_index *ix, int64
     const int k_sel = (int)std::min<int64_t>(k, ix->store.n);
     // like the regular split-product search: 16 candidates for k <= 12, so that near ties at the
     // k-th place are settled by the exact re-ranking below (k = 13..16: no spare, no band check)
+    if (ix->store.elem != kElemF32) return set_error("allocation-free search: fp32 storage only");
     const int k_list = k_sel <= 12 ? (int)std::min<int64_t>(16, ix->store.n) : k_sel;
     const FlatPlan plan = make_flat_plan(n, ix->store.n, k_list, sm_count(ix->device));
     if (plan.list_stride > kStaticMaxK)

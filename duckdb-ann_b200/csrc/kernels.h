@@ -48,7 +48,13 @@ int launch_column_mean(const float *x, int64_t n, int d, float *mu, cudaStream_t
 // x (n x d) -> out (n x dp) zero padded, norms (may be nullptr).
 int launch_pad_rows(const float *x, int64_t n, int d, int dp, float *out, float *norms, cudaStream_t stream);
 // out (n x d) <- hi + lo (n x dp)
-int launch_join_rows(const float *hi, const float *lo, int64_t n, int d, int dp, float *out, cudaStream_t stream);
+// (elem != kElemF32: `hi` holds n x dp 16-bit elements of that type, `lo` is unused)
+int launch_join_rows(const float *hi, const float *lo, int64_t n, int d, int dp, float *out, cudaStream_t stream,
+                     int elem = 0);
+// Rows or queries of a 16-bit store (see prep_rows_h16_kernel): hi (and lo, queries only) are n x dp 16-bit
+// elements; overflow (may be null) points at the status words of the two tensor-core tiers.
+int launch_split_rows_h16(const float *x, int64_t n, int d, int dp, void *hi, void *lo, float *norms, cudaStream_t stream,
+                          const float *mu, bool center_rows, unsigned *max_norm2_bits, int elem, int *overflow);
 
 // ---- flat_tc.cu --------------------------------------------------------------------------
 constexpr int kSmemListMax = 16;         // lists up to this length are kept in shared memory
@@ -123,9 +129,9 @@ struct ScreenInput {
     // large stores).  false: the three-MMA split product with the same banded lists - the slack is
     // then the split product's much smaller one (see key_slack).
     bool one_mma = true;
-    // 16-bit build only (launch_flat_tc_h16): 0 = fp16 operands, 1 = bf16.  There the rows are exact in
+    // 16-bit build only (launch_flat_tc_h16): kElemF16 or kElemBF16 operands.  There the rows are exact in
     // their 16-bit type and only the query is rounded (one_mma) or split in two 16-bit parts.
-    int bf16 = 0;
+    int elem = 0;
 };
 constexpr int kScreenMaxList = 256;  // longest list (k_rank + spare) the screened mode keeps
 constexpr int kScreenMaxK = kScreenMaxList - kSplitSpare;  // largest k searched with screening
@@ -196,10 +202,11 @@ int launch_residual_norms(const float *xhi, const float *xlo, int64_t n, int d, 
 // key = squared L2 distance, or negated dot.  qtau (optional, one word per query, all
 // bytes 0xFF on entry): items of the same query share their k-th best key through it,
 // so later items skip rows that cannot reach the query's final top-k.
+// (elem != kElemF32: x holds 16-bit elements of that type, dp of them per row, xlo is unused)
 int launch_scan_items(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
                       const int32_t *item_query, const int64_t *range_begin, const int64_t *range_end,
                       int64_t n_items, int k, int metric, float *part_key, int32_t *part_idx, uint32_t *qtau,
-                      int device, cudaStream_t stream, const int *gate = nullptr);
+                      int device, cudaStream_t stream, const int *gate = nullptr, int elem = 0);
 
 // Items of the exact flat scan, built on the device: item q * chunks + c = query q against rows
 // [c * per, min(n, (c + 1) * per)).
@@ -258,6 +265,7 @@ struct RefineBand {
     const unsigned *x_max_norm2;
     int d;
     bool one_mma;
+    int elem;  // kElemF32, or the 16-bit type of the store (rows and slack, see key_slack)
     bool cut;
     int check_rank;
     int *overflow;

@@ -311,7 +311,8 @@ refine_finalize_kernel(const float *__restrict__ xhi, const float *__restrict__ 
     // candidates beyond the slack above the rank-th ranking key cannot be among the exact best
     float band_cut = kInf;
     if (band.key) {
-        const float slack = key_slack(band.q_norm2[q], __uint_as_float(*band.x_max_norm2), band.d, metric != 0, band.one_mma);
+        const float slack =
+            key_slack(band.q_norm2[q], __uint_as_float(*band.x_max_norm2), band.d, metric != 0, band.one_mma, band.elem);
         if (band.cut && band.rank <= k_sel) band_cut = band.key[q * k_sel + band.rank - 1] + slack;
         // band check of the selecting pass: the last candidate still inside the band means rows may be missing
         if (threadIdx.x == 0 && band.check_rank > 0 && band.check_rank < k_sel) {
@@ -346,9 +347,12 @@ refine_finalize_kernel(const float *__restrict__ xhi, const float *__restrict__ 
             if (idx >= 0 && !keep_approx) {
                 const float *h = xhi + (int64_t)idx * dp;
                 const float *l = xlo ? xlo + (int64_t)idx * dp : nullptr;
+                // (16-bit store: xhi holds dp elements of the band's type per row, widened exactly)
+                const uint16_t *h16 = reinterpret_cast<const uint16_t *>(xhi) + (int64_t)idx * dp;
                 float acc = 0.f;
                 for (int c = lane; c < d; c += 32) {
-                    float x = h[c] + (l ? l[c] : 0.f);  // exact: lo = x - hi
+                    float x = band.elem != kElemF32 ? h16_to_float(h16[c], band.elem)
+                                                    : h[c] + (l ? l[c] : 0.f);  // exact: lo = x - hi
                     float a = qv[c];
                     if (l2) {
                         float t = a - x;
@@ -553,8 +557,8 @@ int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, co
                                                                 k_out, P, metric, ids, label_offset, approx_key, rnorm, xnorm,
                                                                 out_d, out_i, out_row, gate,
                                                                 band ? *band
-                                                                     : RefineBand{nullptr, 0, nullptr, nullptr, 0, false, false, 0,
-                                                                                  nullptr, nullptr});
+                                                                     : RefineBand{nullptr, 0, nullptr, nullptr, 0, false, kElemF32,
+                                                                                  false, 0, nullptr, nullptr});
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

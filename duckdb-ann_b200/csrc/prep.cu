@@ -71,6 +71,56 @@ prep_rows_kernel(const float *__restrict__ x, int64_t n, int d, int dp, float *_
     }
 }
 
+// Rows or queries for a 16-bit store (elem = kElemF16 / kElemBF16; dp a multiple of 64 elements).
+//  Database rows (center_rows = 0): h = the row rounded to the 16-bit type - from then on THAT is the stored
+//    row; norms[r] = |h - mu|^2 and the store's largest |h|^2 are taken from the rounded values, so that
+//    the keys formed from them belong to the rows that are kept.
+//  Queries (center_rows = 1): w = q - mu is split into two 16-bit parts, h = round(w), l = round(w - h);
+//    norms[r] = |w|^2 (unrounded).  A finite query element that overflows the 16-bit type (fp16: above
+//    65504) makes every tensor-core key of the block meaningless: overflow[0..1] (the status words of the
+//    two tensor-core tiers, may be null) are set to kScreenOverflow, which sends the block to the exact scan.
+__global__ void __launch_bounds__(kWarps * 32)
+prep_rows_h16_kernel(const float *__restrict__ x, int64_t n, int d, int dp, uint16_t *__restrict__ hi,
+                     uint16_t *__restrict__ lo, float *__restrict__ norms, const float *__restrict__ mu, int center_rows,
+                     unsigned *__restrict__ max_norm2_bits, int elem, int *__restrict__ overflow) {
+    const int lane = threadIdx.x & 31;
+    for (int64_t r = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); r < n; r += (int64_t)gridDim.x * kWarps) {
+        const float *src = x + r * (int64_t)d;
+        float acc = 0.f, raw = 0.f;
+        bool bad = false;
+        for (int c = lane; c < dp; c += 32) {
+            const float v = c < d ? src[c] : 0.f;
+            const float m = (mu && c < d) ? mu[c] : 0.f;
+            if (center_rows) {
+                const float w = v - m;
+                const uint16_t hb = float_to_h16(w, elem);
+                const float hf = h16_to_float(hb, elem);
+                bad |= !isfinite(hf) && isfinite(w);
+                hi[r * (int64_t)dp + c] = hb;
+                if (lo) lo[r * (int64_t)dp + c] = float_to_h16(isfinite(hf) ? w - hf : 0.f, elem);
+                acc = fmaf(w, w, acc);
+            } else {
+                const uint16_t hb = float_to_h16(v, elem);
+                const float hf = h16_to_float(hb, elem);
+                hi[r * (int64_t)dp + c] = hb;
+                const float w = c < d ? hf - m : 0.f;
+                acc = fmaf(w, w, acc);
+                raw = fmaf(hf, hf, raw);
+            }
+        }
+        acc = warp_sum(acc);
+        if (norms && lane == 0) norms[r] = acc;
+        if (max_norm2_bits) {
+            raw = warp_sum(raw);
+            if (lane == 0) atomicMax(max_norm2_bits, __float_as_uint(raw));
+        }
+        if (overflow && __any_sync(0xffffffffu, bad) && lane == 0) {
+            overflow[0] = kScreenOverflow;
+            overflow[1] = kScreenOverflow;
+        }
+    }
+}
+
 // mu[c] += (sum over this block's rows of x[r][c]) / n; mu zero on entry
 __global__ void __launch_bounds__(128)
 column_mean_kernel(const float *__restrict__ x, int64_t n, int d, float *__restrict__ mu) {
@@ -83,13 +133,16 @@ column_mean_kernel(const float *__restrict__ x, int64_t n, int d, float *__restr
     if (r1 > r0) atomicAdd(mu + c, acc / (float)n);
 }
 
+// (elem != kElemF32: `hi` holds 16-bit elements, widened exactly)
 __global__ void __launch_bounds__(kWarps * 32)
 join_rows_kernel(const float *__restrict__ hi, const float *__restrict__ lo, int64_t n, int d, int dp,
-                 float *__restrict__ out) {
+                 float *__restrict__ out, int elem) {
     const int lane = threadIdx.x & 31;
+    const uint16_t *h16 = reinterpret_cast<const uint16_t *>(hi);
     for (int64_t r = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); r < n; r += (int64_t)gridDim.x * kWarps)
         for (int c = lane; c < d; c += 32)
-            out[r * (int64_t)d + c] = hi[r * (int64_t)dp + c] + (lo ? lo[r * (int64_t)dp + c] : 0.f);
+            out[r * (int64_t)d + c] = elem != kElemF32 ? h16_to_float(h16[r * (int64_t)dp + c], elem)
+                                                       : hi[r * (int64_t)dp + c] + (lo ? lo[r * (int64_t)dp + c] : 0.f);
 }
 
 __global__ void __launch_bounds__(kWarps * 32)
@@ -209,9 +262,20 @@ int launch_pad_rows(const float *x, int64_t n, int d, int dp, float *out, float 
     return 0;
 }
 
-int launch_join_rows(const float *hi, const float *lo, int64_t n, int d, int dp, float *out, cudaStream_t stream) {
+int launch_split_rows_h16(const float *x, int64_t n, int d, int dp, void *hi, void *lo, float *norms, cudaStream_t stream,
+                          const float *mu, bool center_rows, unsigned *max_norm2_bits, int elem, int *overflow) {
     if (n <= 0) return 0;
-    join_rows_kernel<<<grid_for(n), kWarps * 32, 0, stream>>>(hi, lo, n, d, dp, out);
+    prep_rows_h16_kernel<<<grid_for(n), kWarps * 32, 0, stream>>>(x, n, d, dp, static_cast<uint16_t *>(hi),
+                                                                  static_cast<uint16_t *>(lo), norms, mu, center_rows ? 1 : 0,
+                                                                  max_norm2_bits, elem, overflow);
+    count_launch();
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int launch_join_rows(const float *hi, const float *lo, int64_t n, int d, int dp, float *out, cudaStream_t stream, int elem) {
+    if (n <= 0) return 0;
+    join_rows_kernel<<<grid_for(n), kWarps * 32, 0, stream>>>(hi, lo, n, d, dp, out, elem);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

@@ -36,7 +36,7 @@ scan_items_kernel(const float *__restrict__ x, const float *__restrict__ xlo, in
                   const float *__restrict__ queries, int q_stride, const int32_t *__restrict__ item_query,
                   const int64_t *__restrict__ range_begin, const int64_t *__restrict__ range_end, int64_t n_items,
                   int k, int metric, float *__restrict__ part_key, int32_t *__restrict__ part_idx,
-                  uint32_t *__restrict__ qtau, const int *gate) {
+                  uint32_t *__restrict__ qtau, const int *gate, int elem) {
     extern __shared__ float4 smem_q4[];
     if (gate && *gate != kScreenOverflow) return;  // a fallback pass that is not needed
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -79,6 +79,14 @@ scan_items_kernel(const float *__restrict__ x, const float *__restrict__ xlo, in
                     for (int r = 0; r < kRows; r++) {
                         if (r < nrows) {
                             const int64_t off = (row0 + r) * (int64_t)n4 + c4;
+                            if (elem != kElemF32) {  // 16-bit rows: four elements are eight bytes
+                                const uint2 b = __ldg(reinterpret_cast<const uint2 *>(x) + off);
+                                xv[r].x = h16_to_float((uint16_t)(b.x & 0xffffu), elem);
+                                xv[r].y = h16_to_float((uint16_t)(b.x >> 16), elem);
+                                xv[r].z = h16_to_float((uint16_t)(b.y & 0xffffu), elem);
+                                xv[r].w = h16_to_float((uint16_t)(b.y >> 16), elem);
+                                continue;
+                            }
                             xv[r] = ld_row4(reinterpret_cast<const float4 *>(x) + off);
                             if (xlo) {
                                 float4 t = ld_row4(reinterpret_cast<const float4 *>(xlo) + off);
@@ -275,7 +283,7 @@ template <int KR>
 int launch_scan_kr(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
                    const int32_t *item_query, const int64_t *rb, const int64_t *re, int64_t n_items, int k,
                    int metric, float *part_key, int32_t *part_idx, uint32_t *qtau, int device, cudaStream_t stream,
-                   const int *gate) {
+                   const int *gate, int elem) {
     const size_t smem = (size_t)kWarps * dp * sizeof(float);
     if (smem > 48 * 1024) {
         ANN_CUDA_TRY(cudaFuncSetAttribute(scan_items_kernel<KR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -285,7 +293,7 @@ int launch_scan_kr(const float *x, const float *xlo, int dp, int d, const float 
     const int64_t cap = (int64_t)sm_count(device) * 16;
     if (blocks > cap) blocks = cap;
     scan_items_kernel<KR><<<(unsigned)blocks, kWarps * 32, smem, stream>>>(
-        x, xlo, dp, d, queries, q_stride, item_query, rb, re, n_items, k, metric, part_key, part_idx, qtau, gate);
+        x, xlo, dp, d, queries, q_stride, item_query, rb, re, n_items, k, metric, part_key, part_idx, qtau, gate, elem);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -296,21 +304,21 @@ int launch_scan_kr(const float *x, const float *xlo, int dp, int d, const float 
 int launch_scan_items(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
                       const int32_t *item_query, const int64_t *range_begin, const int64_t *range_end,
                       int64_t n_items, int k, int metric, float *part_key, int32_t *part_idx, uint32_t *qtau,
-                      int device, cudaStream_t stream, const int *gate) {
+                      int device, cudaStream_t stream, const int *gate, int elem) {
     if (n_items <= 0) return 0;
     if (k <= 0 || k > kMaxK) return set_error("k must be in [1, %d]", kMaxK);
     if ((size_t)kWarps * dp * sizeof(float) > 200 * 1024) return set_error("dimension %d too large for the scan kernel", d);
     if (k <= 32)
         return launch_scan_kr<1>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k,
-                                 metric, part_key, part_idx, qtau, device, stream, gate);
+                                 metric, part_key, part_idx, qtau, device, stream, gate, elem);
     if (k <= 128)
         return launch_scan_kr<4>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k,
-                                 metric, part_key, part_idx, qtau, device, stream, gate);
+                                 metric, part_key, part_idx, qtau, device, stream, gate, elem);
     if (k <= 512)
         return launch_scan_kr<16>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k,
-                                  metric, part_key, part_idx, qtau, device, stream, gate);
+                                  metric, part_key, part_idx, qtau, device, stream, gate, elem);
     return launch_scan_kr<64>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k, metric,
-                              part_key, part_idx, qtau, device, stream, gate);
+                              part_key, part_idx, qtau, device, stream, gate, elem);
 }
 
 int launch_fill_chunk_items(int32_t *item_query, int64_t *range_begin, int64_t *range_end, int64_t nq, int chunks,

@@ -181,13 +181,28 @@ class _CudaIndex:
             pass
 
 
-class CudaIndexFlat(_CudaIndex):
-    """MetalIndexFlat(resources, d, metric) -> CudaIndexFlat(d, metric, device)."""
+# StorageType of faiss-metal/include/faiss-metal/MetalIndexFlat.h:38-43
+STORAGE_F32, STORAGE_F16, STORAGE_BF16 = 0, 1, 2
 
-    def __init__(self, d: int, metric: int = METRIC_L2, device: int = 0):
+
+class CudaIndexFlat(_CudaIndex):
+    """MetalIndexFlat(resources, d, metric[, storage]) -> CudaIndexFlat(d, metric, device, storage).
+
+    storage = STORAGE_F16 / STORAGE_BF16 keeps the rows rounded to that type (2 bytes per element) and
+    searches the rounded rows; queries stay fp32 (MetalIndexFlat.h:53-60)."""
+
+    def __init__(self, d: int, metric: int = METRIC_L2, device: int = 0, storage: int = STORAGE_F32):
         super().__init__()
         p = _pkg()
-        p.check(p.lib().ann_cuda_flat_create(device, d, metric, C.byref(self._h)), "CudaIndexFlat")
+        if storage == STORAGE_F32:
+            p.check(p.lib().ann_cuda_flat_create(device, d, metric, C.byref(self._h)), "CudaIndexFlat")
+        else:
+            p.check(p.lib().ann_cuda_flat_create_storage(device, d, metric, storage, C.byref(self._h)), "CudaIndexFlat")
+
+    @property
+    def storage(self) -> int:
+        """MetalIndexFlat::getStorageType (MetalIndexFlat.h:90)."""
+        return _pkg().lib().ann_cuda_index_storage(self._h)
 
     def search_small_static(self, x, k: int, D=None, I=None, label_offset: int = 0, stream=None):
         """search_device() for callers that may not allocate device memory (a worker under a

@@ -51,6 +51,24 @@ int ann_cuda_device_info(char *buf, size_t buflen);
  * MetalIndexFlat(resources, d, metric) (faiss-metal/include/faiss-metal/MetalIndexFlat.h:47-59). */
 int ann_cuda_flat_create(int device, int d, int metric, ann_cuda_index **out);
 
+/* Storage precision of a flat index: StorageType of faiss-metal/include/faiss-metal/MetalIndexFlat.h:38-43
+ * (Float32 = 0, Float16 = 1, BFloat16 = 2) and its extended constructor (:60).  With F16 / BF16 the rows are
+ * rounded to that type (nearest even, faiss-metal/src/MetalIndexFlat.mm:211-236) when they are added and
+ * only the rounded rows are kept: 2 bytes per element instead of 8 (the fp32 store keeps two TF32 planes).
+ * Queries stay fp32.  Distances and neighbours are those of the ROUNDED rows, to the same 1e-4 as for the
+ * fp32 store (the reference checks its fp16 index against the unrounded CPU index with 5e-2 and a top-1
+ * match, faiss-metal/tests/test_metal_flat.mm:259-261); reconstruct returns the rounded row widened to
+ * fp32 (:262-268).  fp16 elements beyond +-65504 become infinite, as in the reference.
+ * Searched on the tensor cores with 16-bit operands (tcgen05.mma kind::f16) and the same banded candidate
+ * lists, band check and exact re-ranking as the fp32 store; k above 224 and stores of fewer than ~256 rows
+ * go to the exact scan.  Not available for IVFFlat, the sharded index or the allocation-free entry point. */
+#define ANN_CUDA_STORAGE_F32 0
+#define ANN_CUDA_STORAGE_F16 1
+#define ANN_CUDA_STORAGE_BF16 2
+int ann_cuda_flat_create_storage(int device, int d, int metric, int storage, ann_cuda_index **out);
+/* MetalIndexFlat::getStorageType (MetalIndexFlat.h:90): one of ANN_CUDA_STORAGE_*, -1 for a null handle. */
+int ann_cuda_index_storage(const ann_cuda_index *index);
+
 /* ---- IVFFlat -----------------------------------------------------------------
  * MetalIndexIVFFlat(resources, d, nlist, metric) (faiss-metal/include/faiss-metal/MetalIndexIVFFlat.h:25-33). */
 int ann_cuda_ivfflat_create(int device, int d, int64_t nlist, int metric, ann_cuda_index **out);

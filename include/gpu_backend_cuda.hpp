@@ -11,6 +11,7 @@
 #include <faiss/IndexFlat.h>
 #include <faiss/IndexIVFFlat.h>
 
+#include <cstdint>
 #include <memory>
 #include <vector>
 
@@ -47,9 +48,20 @@ private:
     ann_cuda_search_token *token_ = nullptr;
 };
 
+// Row storage precision of CudaIndexFlat: faiss_metal::StorageType
+// (faiss-metal/include/faiss-metal/MetalIndexFlat.h:38-43), same values.
+enum class StorageType : uint8_t {
+    Float32 = 0,
+    Float16 = 1,   // rows rounded to fp16 when added, 2 bytes per element
+    BFloat16 = 2,  // rows rounded to bf16 when added, 2 bytes per element
+};
+
 class ANN_CUDA_CLASS CudaIndexFlat : public faiss::Index {
 public:
     CudaIndexFlat(int device, int d, faiss::MetricType metric = faiss::METRIC_L2);
+    // MetalIndexFlat(resources, d, metric, storage) (MetalIndexFlat.h:60): queries stay fp32, the search
+    // answers for the rounded rows.
+    CudaIndexFlat(int device, int d, faiss::MetricType metric, StorageType storage);
     ~CudaIndexFlat() override;
     CudaIndexFlat(const CudaIndexFlat &) = delete;
     CudaIndexFlat &operator=(const CudaIndexFlat &) = delete;
@@ -65,8 +77,13 @@ public:
     CudaSearchToken searchAsync(faiss::idx_t n, const float *x, faiss::idx_t k, float *distances, faiss::idx_t *labels,
                                 const faiss::SearchParameters *params = nullptr) const;
 
-    // Copies rows [first, first + n) to host memory (the role of getVectorsData()).
+    // Copies rows [first, first + n) to host memory (the role of getVectorsData()); a reduced-precision
+    // store hands out its rounded rows widened to fp32.
     void getRows(faiss::idx_t first, faiss::idx_t n, float *rows) const;
+    // MetalIndexFlat.h:83-90
+    bool isFloat16Storage() const { return getStorageType() == StorageType::Float16; }
+    bool isBFloat16Storage() const { return getStorageType() == StorageType::BFloat16; }
+    StorageType getStorageType() const;
     ann_cuda_index *handle() const { return handle_; }
 
 private:

@@ -160,6 +160,21 @@ def sq8_batch_distances_by_id(codes, mins, scale, queries, ids, query_map, metri
 
 
 # --------------------------------------------------------------------------- flat
+def round_storage(x, kind: str):
+    """Rows as a reduced-precision flat index keeps them: rounded to nearest even to fp16 ("f16": the
+    (__fp16) cast of faiss-metal/src/MetalIndexFlat.mm:228-236) or bf16 ("bf16": bits + 0x7FFF + lsb, then
+    the upper half, :211-226), widened back to float32 (reconstruct, :461-478)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    if kind == "f16":
+        with np.errstate(over="ignore"):
+            return x.astype(np.float16).astype(np.float32)
+    if kind == "bf16":
+        bits = x.view(np.uint32).astype(np.uint64)
+        lsb = (bits >> 16) & 1
+        return (((bits + 0x7FFF + lsb) >> 16) << 16).astype(np.uint32).view(np.float32).reshape(x.shape)
+    raise ValueError(kind)
+
+
 def flat_search(xb, xq, k: int, metric: int):
     """Exact top-k, distances accumulated in double (faiss-metal/src/MetalIndexFlat.mm:294-369)."""
     xb, xq = _f32(xb), _f32(xq)
