@@ -220,8 +220,11 @@ def search_sample_exact(wl, torch, dist, sample, label_offset):
 # Workloads
 # ------------------------------------------------------------------------------------------------
 class FlatWorkload:
-    def __init__(self, name, n, d, nq, k, metric_name, dist_kind, scale=1.0):
+    def __init__(self, name, n, d, nq, k, metric_name, dist_kind, scale=1.0, storage="f32"):
         self.name, self.d, self.nq, self.k = name, d, nq, k
+        # "f16" / "bf16": the rows are kept rounded to that type (2 bytes per element) and the search
+        # answers for the rounded rows - a variant of the workload, never part of the default run
+        self.storage = storage
         self.n = max(1024, int(n * scale))
         self.metric_name, self.dist_kind = metric_name, dist_kind
         self.chunk = 250_000
@@ -254,7 +257,8 @@ class FlatWorkload:
         self.m = m
         lo, hi = pkg.sharded.row_range(self.n, rank, world)
         self.lo, self.hi = lo, hi
-        self.index = pkg.CudaIndexFlat(self.d, m, device.index)
+        self.index = pkg.CudaIndexFlat(self.d, m, device.index,
+                                       {"f32": pkg.STORAGE_F32, "f16": pkg.STORAGE_F16, "bf16": pkg.STORAGE_BF16}[self.storage])
         self.index.reserve(hi - lo)
         c0, c1 = lo // self.chunk, (hi - 1) // self.chunk
         for c in range(c0, c1 + 1):
@@ -297,8 +301,12 @@ class FlatWorkload:
                 if self.n * self.d * 8 / max(world, 1) > 1e9 else "database is L2-sized (a warm-cache figure; the full-size workload is the headline)",
                 "flat_kernel": self.pkg.lib().ann_cuda_flat_kernel_name().decode() if getattr(self, "pkg", None)
                 else "cpu",
+                "storage": self.storage,
                 "search": "one-MMA screening (stores >= 2M rows, k <= 224), else three-MMA split product; banded candidate "
-                          "lists, exact fp32 re-ranking, band check with fallback one tier up"}
+                          "lists, exact fp32 re-ranking, band check with fallback one tier up"
+                if self.storage == "f32" else
+                "16-bit rows (rounded when added), tcgen05 kind::f16 with one 16-bit part of the query per product, then two; "
+                "banded candidate lists, exact fp32 re-ranking against the rounded rows, band check with fallback one tier up"}
 
     def roofline(self, peaks, kernel_ms):
         local_rows = self.hi - self.lo
@@ -309,6 +317,14 @@ class FlatWorkload:
         screened = local_rows >= 2_000_000 and self.k <= 224 and self.pkg.lib().ann_cuda_flat_kernel_name().decode() == "tcgen05"
         mmas = 1 if screened else 3
         peak = peaks["bf16_tflops_sustained"] / 2.0 / mmas
+        if self.storage != "f32":
+            # 16-bit operands (kind::f16): one MMA per product at the bf16 rate itself
+            return {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["bf16_tflops_sustained"] if achieved else None, "traffic": None,
+                    "traffic_note": "no capture for this storage type",
+                    "kernel": "flat_tc_kernel (16-bit operands, one MMA per product)", "kernel_ms": kernel_ms,
+                    "algorithmic_flops_per_launch": flops, "mma_per_product": 1,
+                    "peak_note": f"{peaks['_source']} bf16 sustained {peaks['bf16_tflops_sustained']} TFLOP/s; 'achieved' counts 2*Q*N*d once"}
         # DRAM traffic of one launch.  Screened search: ncu capture of the full-size launch (20M rows of
         # 768 floats, 4,096 queries: 67.5 GB read + 1.2 GB written; the hi planes are 61.4 GB and are
         # read once for all query tiles), scaled by the rows of this launch.  That capture was taken
@@ -749,6 +765,8 @@ class BatchWorkload:
 def make_workload(name, scale):
     if name == "flat_ip_20m":
         return FlatWorkload(name, 20_000_000, 768, 4096, 100, "IP", "unit", scale)
+    if name in ("flat_ip_20m_f16", "flat_ip_20m_bf16"):  # the same store kept in 16-bit rows
+        return FlatWorkload(name, 20_000_000, 768, 4096, 100, "IP", "unit", scale, storage=name.rsplit("_", 1)[1])
     if name == "flat_l2_100k":
         return FlatWorkload(name, 100_000, 384, 1000, 10, "L2", "uniform", scale)
     if name == "ivf_1m":
@@ -822,7 +840,8 @@ def _json_default(o):
     raise TypeError(f"{type(o).__name__} is not JSON serializable")
 
 
-DEFAULT_STEPS = {"flat_ip_20m": 5, "flat_l2_100k": 50, "ivf_1m": 10, "batch_c2": 100, "sq8_c5": 100}
+DEFAULT_STEPS = {"flat_ip_20m": 5, "flat_l2_100k": 50, "ivf_1m": 10, "batch_c2": 100, "sq8_c5": 100,
+                 "flat_ip_20m_f16": 5, "flat_ip_20m_bf16": 5}
 
 
 def run_workload(args, name, steps, ctx, with_cpu_baseline):

@@ -7,6 +7,10 @@
 //
 //   backend_driver info
 //   backend_driver flat|ivf <in.bin> <out.bin>
+//   backend_driver storage <in.bin> <out.bin> f16|bf16        CudaIndexFlat with reduced-precision rows
+//       (faiss_metal::StorageType, MetalIndexFlat.h:38-60): same in.bin / out.bin as `flat`; the JSON line says
+//       whether the storage flags read back, reconstruct returns the same row twice, and GpuToCpu hands out
+//       exactly the rows reconstruct shows.
 //   backend_driver glue <in.bin> <out.bin> [cpu|gpu|auto]     the FaissIndex glue of faiss_index_glue.hpp:
 //       in.bin : int64 {d, n, nq, k, metric, n0, ntomb}, float xb[n*d], float xq[nq*d], int64 tomb[ntomb]
 //       builds from the first n0 rows, searches (one query per call and as ONE batch), appends the rest,
@@ -44,6 +48,62 @@ static void write_results(FILE *o, const std::vector<std::vector<std::pair<faiss
         }
     fwrite(D.data(), 4, D.size(), o);
     fwrite(I.data(), 8, I.size(), o);
+}
+
+// CudaIndexFlat(device, d, metric, StorageType): the index answers for the rows it keeps (rounded to fp16 / bf16).
+static int run_storage(int argc, char **argv) {
+    if (argc < 5) return 2;
+    const bool bf16 = strcmp(argv[4], "bf16") == 0;
+    FILE *f = fopen(argv[2], "rb");
+    if (!f) return 2;
+    int64_t h[7];
+    if (fread(h, 8, 7, f) != 7) return 2;
+    const int64_t d = h[0], n = h[1], nq = h[2], k = h[3];
+    const faiss::MetricType metric = h[4] == 1 ? faiss::METRIC_L2 : faiss::METRIC_INNER_PRODUCT;
+    std::vector<float> xb, xq;
+    if (!read_vec(f, xb, (size_t)(n * d)) || !read_vec(f, xq, (size_t)(nq * d))) return 2;
+    fclose(f);
+    try {
+        using faiss_cuda::StorageType;
+        const StorageType st = bf16 ? StorageType::BFloat16 : StorageType::Float16;
+        faiss_cuda::CudaIndexFlat gpu(0, (int)d, metric, st);
+        gpu.add(n, xb.data());
+        const int flags_ok = gpu.getStorageType() == st && gpu.isBFloat16Storage() == bf16 && gpu.isFloat16Storage() == !bf16 &&
+                             gpu.ntotal == n;
+        std::vector<float> D((size_t)(nq * k)), D1((size_t)(nq * k));
+        std::vector<int64_t> I((size_t)(nq * k)), I1((size_t)(nq * k));
+        gpu.search(nq, xq.data(), k, D.data(), I.data());
+        for (int64_t q = 0; q < nq; q++) gpu.search(1, xq.data() + q * d, k, D1.data() + q * k, I1.data() + q * k);
+        // GpuToCpu: a CPU IndexFlat over the rounded rows, the same values reconstruct returns
+        std::unique_ptr<faiss::Index> back = duckdb::GetGpuBackend().GpuToCpu(&gpu);
+        auto *bf = dynamic_cast<faiss::IndexFlat *>(back.get());
+        int roundtrip_ok = bf && back->ntotal == n;
+        std::vector<float> one((size_t)d), again((size_t)d);
+        float worst = 0.f;
+        for (int64_t r = 0; roundtrip_ok && r < n; r += (n > 64 ? n / 64 : 1)) {
+            gpu.reconstruct(r, one.data());
+            gpu.reconstruct(r, again.data());
+            roundtrip_ok = memcmp(one.data(), again.data(), (size_t)d * 4) == 0 &&
+                           memcmp(one.data(), bf->get_xb() + r * d, (size_t)d * 4) == 0;
+            for (int64_t c = 0; c < d; c++) {
+                const float e = one[(size_t)c] - xb[(size_t)(r * d + c)];
+                worst = e > worst ? e : (-e > worst ? -e : worst);
+            }
+        }
+        FILE *o = fopen(argv[3], "wb");
+        if (!o) return 2;
+        fwrite(D.data(), 4, D.size(), o);
+        fwrite(I.data(), 8, I.size(), o);
+        fwrite(D1.data(), 4, D1.size(), o);
+        fwrite(I1.data(), 8, I1.size(), o);
+        fclose(o);
+        printf("{\"backend\": \"%s\", \"flags_ok\": %d, \"roundtrip_ok\": %d, \"worst_rounding\": %g}\n",
+               duckdb::GetGpuBackend().BackendName().c_str(), flags_ok, roundtrip_ok, (double)worst);
+        return 0;
+    } catch (const std::exception &e) {
+        fprintf(stderr, "error: %s\n", e.what());
+        return 1;
+    }
 }
 
 // FaissIndex::Search / SearchBatch over the GPU backend, with an append and deletions in between.
@@ -97,10 +157,11 @@ int main(int argc, char **argv) {
             return 0;
         }
         if (argc < 4) {
-            fprintf(stderr, "usage: %s info | flat|ivf in.bin out.bin | glue in.bin out.bin [cpu|gpu|auto]\n", argv[0]);
+            fprintf(stderr, "usage: %s info | flat|ivf in.bin out.bin | storage in.bin out.bin f16|bf16 | glue in.bin out.bin [cpu|gpu|auto]\n", argv[0]);
             return 2;
         }
         if (strcmp(argv[1], "glue") == 0) return run_glue(argc, argv);
+        if (strcmp(argv[1], "storage") == 0) return run_storage(argc, argv);
         const bool ivf = strcmp(argv[1], "ivf") == 0;
         FILE *f = fopen(argv[2], "rb");
         if (!f) return 2;

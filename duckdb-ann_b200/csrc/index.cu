@@ -750,7 +750,13 @@ int flat_first_tier(const ann_cuda_index &ix, int k_sel) {
     if (flat_kernel_choice() != FlatKernel::TC) return kTierExact;
     // 16-bit store: one 16-bit part of the query per product, then two, then the exact scan - always
     // with banded lists (stores too small for them, and k beyond them, are scanned exactly)
-    if (ix.store.elem != kElemF32) return banded_lists_fit(ix, k_sel) ? kTierScreen : kTierExact;
+    // (bf16 rounds a query element to 8 bits: the band of a single part is eight times as wide as fp16's and
+    // holds more rows than a list keeps once k is more than a few dozen - measured at 20M x 768, k = 100:
+    // every block went on to the two-part product - so larger k starts there)
+    if (ix.store.elem != kElemF32) {
+        if (!banded_lists_fit(ix, k_sel)) return kTierExact;
+        return (ix.store.elem == kElemBF16 && k_sel > 32) ? kTierSplit : kTierScreen;
+    }
     // (ANN_CUDA_FLAT_SCREEN=0 turns screening off, =1 applies it to stores of any size)
     const int screen_env = g_flat_screen.load(std::memory_order_relaxed);
     if (banded_lists_fit(ix, k_sel) && (screen_env == 1 || (screen_env != 0 && ix.store.n >= kScreenMinRows)))

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 DRIVER = os.path.join(ROOT, "duckdb-ann_b200", "backend_driver")
 
 
-def _run(tmp_path, mode, d, k, metric, xb, xq, nlist=0, nprobe=0, cent=None, assign=None, devices=None):
+def _run(tmp_path, mode, d, k, metric, xb, xq, nlist=0, nprobe=0, cent=None, assign=None, devices=None, extra=()):
     inp, out = tmp_path / "in.bin", tmp_path / "out.bin"
     with open(inp, "wb") as f:
         f.write(np.array([d, len(xb), len(xq), k, metric, nlist, nprobe], np.int64).tobytes())
@@ -25,7 +25,7 @@ def _run(tmp_path, mode, d, k, metric, xb, xq, nlist=0, nprobe=0, cent=None, ass
     env.pop("ANN_CUDA_DEVICES", None)
     if devices:
         env["ANN_CUDA_DEVICES"] = devices
-    res = subprocess.run([DRIVER, mode, str(inp), str(out)], capture_output=True, text=True, timeout=300, env=env)
+    res = subprocess.run([DRIVER, mode, str(inp), str(out), *extra], capture_output=True, text=True, timeout=300, env=env)
     assert res.returncode == 0, res.stderr
     info = json.loads(res.stdout.strip().splitlines()[-1])
     raw = open(out, "rb").read()
@@ -53,6 +53,23 @@ def test_flat_through_gpu_backend(tmp_path, oracle, metric):
     Dref, Iref = oracle.flat_search(xb, xq, 7, metric)
     assert_topk_matches(oracle, xb, xq, metric, D, I, Dref, Iref, "batch")
     assert_topk_matches(oracle, xb, xq, metric, D1, I1, Dref, Iref, "one query per call")
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("metric", [1, 0])
+def test_reduced_precision_storage_through_the_cpp_class(tmp_path, oracle, kind, metric):
+    """faiss_cuda::CudaIndexFlat(device, d, metric, StorageType) (the extended constructor of
+    faiss-metal/include/faiss-metal/MetalIndexFlat.h:60): the index answers for the rounded rows."""
+    rng = np.random.default_rng(42)
+    xb = rng.uniform(-1, 1, (3000, 96)).astype(np.float32)
+    xq = rng.uniform(-1, 1, (12, 96)).astype(np.float32)
+    info, D, I, D1, I1 = _run(tmp_path, "storage", 96, 7, metric, xb, xq, extra=(kind,))
+    assert info["backend"] == "cuda" and info["flags_ok"] == 1 and info["roundtrip_ok"] == 1
+    assert 0 < info["worst_rounding"] < (2e-3 if kind == "f16" else 8e-3)   # test_metal_flat.mm:262-268
+    xr = oracle.round_storage(xb, kind)
+    Dref, Iref = oracle.flat_search(xr, xq, 7, metric)
+    assert_topk_matches(oracle, xr, xq, metric, D, I, Dref, Iref, f"{kind} batch")
+    assert_topk_matches(oracle, xr, xq, metric, D1, I1, Dref, Iref, f"{kind} one query per call")
 
 
 def test_ivf_through_gpu_backend(tmp_path, oracle):
