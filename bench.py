@@ -302,7 +302,9 @@ class FlatWorkload:
                 "flat_kernel": self.pkg.lib().ann_cuda_flat_kernel_name().decode() if getattr(self, "pkg", None)
                 else "cpu",
                 "storage": self.storage,
-                "search": "one-MMA screening (stores >= 2M rows, k <= 224), else three-MMA split product; banded candidate "
+                "search": "CPU: blocked sgemm distances + heap select over all host threads (the oracle's port of the FAISS CPU path)"
+                if not getattr(self, "pkg", None) else
+                "one-MMA screening (stores >= 2M rows, k <= 224), else three-MMA split product; banded candidate "
                           "lists, exact fp32 re-ranking, band check with fallback one tier up"
                 if self.storage == "f32" else
                 "16-bit rows (rounded when added), tcgen05 kind::f16 with one 16-bit part of the query per product, then two; "
