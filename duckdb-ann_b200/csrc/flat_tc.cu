@@ -137,6 +137,10 @@ constexpr int kPairStageBytes = kABytes + kBBytes / 2;  // pair mode: own querie
 static_assert(kPairStages * kPairStageBytes <= kStages * kStageBytes, "the pair ring fits into the stage memory");
 constexpr int kQueueDepth = kSmemListMax;   // per-row candidate queue, also the small-k list capacity
 constexpr int kThreads = 192;
+// Launches whose rows come as one plain fp32 plane (KernelArgs::derive_lo) add two converter warps
+// that split every row tile into TF32 hi / lo parts in shared memory.
+constexpr int kConvWarps = 2;
+constexpr int kThreadsDerive = kThreads + 32 * kConvWarps;
 constexpr int kPaceSpins = 10000;  // polls of ~100 ns a CTA of the static schedule waits for the others, once
 constexpr int kWorkRing = 4;       // chunk descriptors in flight between the scheduler and the other roles
 
@@ -146,8 +150,8 @@ struct SmemLayout {
     static constexpr int queue_idx = queue_key + kQueueDepth * BM * 4;
     static constexpr int xnorm = queue_idx + kQueueDepth * BM * 4;
     static constexpr int barriers = xnorm + 4 * 2 * BN * 4;  // (after a private norm copy per epilogue warp)
-    // barriers: full[kBarStages] empty[kBarStages] tmem_full[2] tmem_empty[2]
-    static constexpr int work_bars = barriers + (2 * kBarStages + 4) * 8;  // wfull[kWorkRing] wempty[kWorkRing]
+    // barriers: full[kBarStages] empty[kBarStages] tmem_full[2] tmem_empty[2] converted[kBarStages]
+    static constexpr int work_bars = barriers + (3 * kBarStages + 4) * 8;  // wfull[kWorkRing] wempty[kWorkRing]
     static constexpr int work_ring = work_bars + 2 * kWorkRing * 8;    // kWorkRing descriptors of 32 bytes
     static constexpr int tmem_ptr = work_ring + kWorkRing * 32;
     static constexpr int abort_flag = tmem_ptr + 4;
@@ -298,6 +302,13 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
         : "memory");
 }
 
+// value rounded to TF32 (10 mantissa bits, to nearest, ties away from zero): what the row planes hold
+__device__ __forceinline__ float round_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
 __device__ __forceinline__ void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tmem_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -441,6 +452,7 @@ struct KernelArgs {
     const int *gate;      // may be null: run only if *gate == kScreenOverflow (a fallback pass)
     int pair;             // launched as clusters of two CTAs that share row tiles (screened, static schedule)
     int bf16;             // 16-bit build: operands are bf16 (else fp16)
+    int derive_lo;        // rows come as one plain fp32 plane; converter warps split them in shared memory
 #ifdef ANN_CUDA_MEASURE
     unsigned long long *stats;  // see kStat* below
     int debug;  // bit 0 = epilogue skips selection, bit 1 = MMA issuer skips the MMAs, bit 2 = no appends, bit 3 = consume only
@@ -740,7 +752,7 @@ __device__ __noinline__ void compact_rows(float *slot_key, int32_t *slot_idx, in
 // PAIR: the kernel of the pair mode, launched as clusters of two CTAs.  A kernel of its own because
 // code that holds cta_group::2 instructions can only be launched with a cluster size that fits them.
 template <int KR, int MODE, bool PAIR>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreadsDerive, 1)
 flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constant__ CUtensorMap map_qlo,
                const __grid_constant__ CUtensorMap map_xhi, const __grid_constant__ CUtensorMap map_xlo,
                const KernelArgs args) {
@@ -762,6 +774,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
     const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
     const bool leader = crank == 0;
     const uint32_t bar_tempty = bar_tfull + 16;
+    const uint32_t bar_conv = bar_tempty + 16;  // derive_lo: the converter warps are done with the stage
     volatile uint32_t *tmem_ptr_s = reinterpret_cast<volatile uint32_t *>(smem + SmemLayout::tmem_ptr);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + SmemLayout::abort_flag);
 
@@ -772,6 +785,7 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
+        for (int s = 0; s < kBarStages; s++) mbar_init(bar_conv + 8 * s, kConvWarps);
         for (int b = 0; b < 2; b++) {
             mbar_init(bar_tfull + 8 * b, 1);
             // one arrival per epilogue warp (pair mode: of both CTAs, on the leader's barrier)
@@ -779,7 +793,8 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
         }
         for (int w = 0; w < kWorkRing; w++) {
             mbar_init(smem_base + SmemLayout::work_bars + 8 * w, 1);                    // written by the scheduler
-            mbar_init(smem_base + SmemLayout::work_bars + 8 * (kWorkRing + w), 5);      // read by MMA + 4 epilogue warps
+            // read by MMA + 4 epilogue warps (+ the converter warps)
+            mbar_init(smem_base + SmemLayout::work_bars + 8 * (kWorkRing + w), 5 + (args.derive_lo ? kConvWarps : 0));
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -978,11 +993,13 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             tma_load_2d(base + 2 * kABytes + (stage & 1) * kBBytes, &map_xhi, kb * BK, (int32_t)trow, full);
                         } else {
                             const uint32_t base = smem_base + stage * kStageBytes;
-                            mbar_expect_tx(full, kH16 ? 2 * kABytes + kBBytes : kStageBytes);
+                            // (16-bit build: no lo plane of the rows exists; derive_lo: it is formed in shared memory)
+                            const bool one_row_plane = kH16 || args.derive_lo;
+                            mbar_expect_tx(full, one_row_plane ? 2 * kABytes + kBBytes : kStageBytes);
                             tma_load_2d(base, &map_qhi, kb * BK, cur * BM, full);
                             tma_load_2d(base + kABytes, &map_qlo, kb * BK, cur * BM, full);
                             tma_load_2d(base + 2 * kABytes, &map_xhi, kb * BK, (int32_t)trow, full);
-                            if (!kH16) tma_load_2d(base + 2 * kABytes + kBBytes, &map_xlo, kb * BK, (int32_t)trow, full);
+                            if (!one_row_plane) tma_load_2d(base + 2 * kABytes + kBBytes, &map_xlo, kb * BK, (int32_t)trow, full);
                         }
                         if (++stage == nstages) {
                             stage = 0;
@@ -1022,7 +1039,9 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     const uint32_t tmem_d = tmem_base + buf * BN;
                     for (int kb = 0; kb < args.kblocks; kb++) {
                         t0 = kstats(args) ? clock64() : 0;
-                        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, args.status, args.wait_ns, 3)) goto done;
+                        if (!mbar_wait((args.derive_lo ? bar_conv : bar_full) + 8 * stage, phase, abort_flag, args.status,
+                                       args.wait_ns, 3))
+                            goto done;
                         if (kstats(args)) atomicAdd(kstats(args) + kStatMmaWaitSmem, (unsigned long long)(clock64() - t0));
                         tmem_fence_after();
                         if (PAIR) {
@@ -1082,6 +1101,50 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                     // accumulator complete (pair mode: in both CTAs' tensor memories)
                     if (PAIR) mma_commit_pair(bar_tfull + 8 * buf);
                     else mma_commit(bar_tfull + 8 * buf);
+                }
+            }
+        }
+    } else if (warp >= 2 + 4) {
+        // ---------------------------------------------------------------- row-plane converter (derive_lo launches only)
+        // The row tile arrives as plain fp32 values.  Each converter warp takes its share of the
+        // stage's row slot, writes hi = the value rounded to TF32 back in place and lo = value - hi
+        // into the lo slot (same swizzled offsets: the operation is element-wise), makes the writes
+        // visible to the tensor core's reads and arrives on the stage's "converted" barrier.
+        const int cw = warp - (2 + 4);
+        uint32_t stage = 0, phase = 0;
+        for (uint32_t wi = 0;; wi++) {
+            const uint32_t w = wi % kWorkRing;
+            if (!mbar_wait(bar_wfull + 8 * w, (wi / kWorkRing) & 1, abort_flag, args.status, args.wait_ns, 10)) goto done;
+            const int qt = ring[w].qt;
+            const int64_t r_begin = ring[w].row_begin, r_end = ring[w].row_end;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_wempty + 8 * w);
+            if (qt < 0) break;
+            for (int64_t trow = r_begin; trow < r_end; trow += BN) {
+                for (int kb = 0; kb < args.kblocks; kb++) {
+                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, args.status, args.wait_ns, 11)) goto done;
+                    constexpr int kVecs = kBBytes / 16 / kConvWarps;  // float4 per converter warp
+                    float4 *hi4 = reinterpret_cast<float4 *>(smem + (size_t)stage * kStageBytes + 2 * kABytes) + cw * kVecs;
+                    float4 *lo4 = hi4 + kBBytes / 16;
+                    // all loads first: a store to the lo slot in between would keep the compiler from
+                    // moving the next load up (it cannot see that the slots do not overlap)
+                    static_assert(kVecs % 32 == 0, "whole rounds of the warp");
+                    float4 v[kVecs / 32];
+#pragma unroll
+                    for (int j = 0; j < kVecs / 32; j++) v[j] = hi4[lane + 32 * j];
+#pragma unroll
+                    for (int j = 0; j < kVecs / 32; j++) {
+                        const float4 h = make_float4(round_tf32(v[j].x), round_tf32(v[j].y), round_tf32(v[j].z), round_tf32(v[j].w));
+                        hi4[lane + 32 * j] = h;
+                        lo4[lane + 32 * j] = make_float4(v[j].x - h.x, v[j].y - h.y, v[j].z - h.z, v[j].w - h.w);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_conv + 8 * stage);
+                    if (++stage == nstages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
                 }
             }
         }
@@ -1461,7 +1524,8 @@ int launch_variant(const FlatPlan &plan, const CUtensorMap maps[4], const Kernel
     if (args.pair) return set_error("internal: pair mode asked of a kernel variant that has none");
     ANN_CUDA_TRY(cudaFuncSetAttribute(flat_tc_kernel<KR, MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       kSmemBytes));
-    flat_tc_kernel<KR, MODE, false><<<plan.grid, kThreads, kSmemBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], args);
+    flat_tc_kernel<KR, MODE, false><<<plan.grid, args.derive_lo ? kThreadsDerive : kThreads, kSmemBytes, stream>>>(
+        maps[0], maps[1], maps[2], maps[3], args);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -1625,7 +1689,7 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     const bool bf16 = kH16 && screen && screen->elem == kElemBF16;
     // (16-bit build: there is no lo plane of the rows; the fourth map repeats the third)
     if (make_map(&maps[0], qhi, nq, dp, BM, bf16) || make_map(&maps[1], qlo ? qlo : qhi, nq, dp, BM, bf16) ||
-        make_map(&maps[2], xhi, n, dp, BN, bf16) || make_map(&maps[3], kH16 ? xhi : xlo, n, dp, BN, bf16))
+        make_map(&maps[2], xhi, n, dp, BN, bf16) || make_map(&maps[3], (kH16 || !xlo) ? xhi : xlo, n, dp, BN, bf16))
         return -1;
     KernelArgs a;
     a.xnorm = xnorm;
@@ -1666,6 +1730,7 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     a.pair = (a.static_g && plan.pair && kWideRows && plan.grid % 2 == 0 && pair_clusters_fit(plan.grid)) ? 1 : 0;
     if (a.pair && make_map(&maps[3], xhi, n, dp, BN / 2, bf16)) return -1;
     a.bf16 = bf16 ? 1 : 0;
+    a.derive_lo = (grouped && grouped->derive_lo && !kH16) ? 1 : 0;
     a.k_rank = use_band ? screen->k_rank : k;
     a.q_norm2 = use_band ? screen->q_norm2 : nullptr;
     a.x_max_norm2 = use_band ? screen->x_max_norm2 : nullptr;

@@ -185,7 +185,10 @@ struct ann_cuda_index {
     // IVFFlat
     int64_t nlist = 0, nprobe = 1;
     int shard_rank = 0, shard_count = 1;
-    float *vhi = nullptr, *vlo = nullptr;  // rows x dp each: TF32 split of the stored rows, grouped by list
+    // Inverted-list rows, grouped by list: ONE plane of plain fp32 values (rows x dp) behind vhi.  The list
+    // scan splits each row tile into its TF32 hi / lo parts in shared memory (GroupedWork::derive_lo), so a
+    // row costs 4 bytes per element in memory and from DRAM, not 8.  vlo stays null.
+    float *vhi = nullptr, *vlo = nullptr;
     float *vnorm = nullptr;                // rows: squared norms
     float *vrnorm = nullptr;               // rows: |x - centroid of its list|^2 (L2; rebuilt with the CSR form)
     int64_t vrnorm_cap = 0;
@@ -319,7 +322,7 @@ __global__ void gather_rows_kernel(const float *__restrict__ shi, const float *_
         const int64_t s = perm[r];
         for (int c = lane; c < dp; c += 32) {
             dhi[r * (int64_t)dp + c] = shi[s * (int64_t)dp + c];
-            dlo[r * (int64_t)dp + c] = slo[s * (int64_t)dp + c];
+            if (slo) dlo[r * (int64_t)dp + c] = slo[s * (int64_t)dp + c];
         }
         if (lane == 0) {
             dst_ids[r] = src_ids[s];
@@ -475,13 +478,14 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
 int ivf_alloc_rows(int64_t cap, int dp, float **hi, float **lo, float **norm, int64_t **ids) {
     *hi = *lo = *norm = nullptr;
     *ids = nullptr;
-    if (cudaMalloc(hi, (size_t)cap * dp * 4) != cudaSuccess || cudaMalloc(lo, (size_t)cap * dp * 4) != cudaSuccess ||
-        cudaMalloc(norm, (size_t)cap * 4) != cudaSuccess || cudaMalloc(ids, (size_t)cap * 8) != cudaSuccess) {
+    if (cudaMalloc(hi, (size_t)cap * dp * 4) != cudaSuccess || cudaMalloc(norm, (size_t)cap * 4) != cudaSuccess ||
+        cudaMalloc(ids, (size_t)cap * 8) != cudaSuccess) {
         cudaGetLastError();
-        for (void *p : {(void *)*hi, (void *)*lo, (void *)*norm, (void *)*ids})
+        for (void *p : {(void *)*hi, (void *)*norm, (void *)*ids})
             if (p) cudaFree(p);
-        return set_error("out of device memory for %lld inverted-list rows of %d floats (x2 for the TF32 split)",
-                         (long long)cap, dp);
+        *hi = *norm = nullptr;
+        *ids = nullptr;
+        return set_error("out of device memory for %lld inverted-list rows of %d floats", (long long)cap, dp);
     }
     return 0;
 }
@@ -514,7 +518,7 @@ int ivf_finalize_lists(const ann_cuda_index &cix) {
         if (ivf_alloc_rows(cap, ix.dp, &nh, &nl, &nn, &ni)) return -1;
         if (cudaMalloc(&dperm, (size_t)n * 8) != cudaSuccess) {
             cudaGetLastError();
-            for (void *p : {(void *)nh, (void *)nl, (void *)nn, (void *)ni}) cudaFree(p);
+            for (void *p : {(void *)nh, (void *)nn, (void *)ni}) cudaFree(p);
             return set_error("out of device memory regrouping the inverted lists");
         }
         ANN_CUDA_TRY(cudaMemcpy(dperm, perm.data(), (size_t)n * 8, cudaMemcpyHostToDevice));
@@ -566,7 +570,6 @@ int ivf_grow_rows(ann_cuda_index &ix, int64_t extra) {
     if (ivf_alloc_rows(want, ix.dp, &nh, &nl, &nn, &ni)) return -1;
     if (ix.rows > 0) {
         ANN_CUDA_TRY(cudaMemcpy(nh, ix.vhi, (size_t)ix.rows * ix.dp * 4, cudaMemcpyDeviceToDevice));
-        ANN_CUDA_TRY(cudaMemcpy(nl, ix.vlo, (size_t)ix.rows * ix.dp * 4, cudaMemcpyDeviceToDevice));
         ANN_CUDA_TRY(cudaMemcpy(nn, ix.vnorm, (size_t)ix.rows * 4, cudaMemcpyDeviceToDevice));
         ANN_CUDA_TRY(cudaMemcpy(ni, ix.ids, (size_t)ix.rows * 8, cudaMemcpyDeviceToDevice));
     }
@@ -878,7 +881,7 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
         const bool filtered = plan.lists_sorted;
         if (filtered && ws.part_cnt.ensure((size_t)max_rows * 4)) return -1;
         GroupedWork gw{ws.items.as<int4>(), n_tiles, item_counter, ws.gq.as<int32_t>(), qconst,
-                       filtered ? ws.part_cnt.as<int32_t>() : nullptr};
+                       filtered ? ws.part_cnt.as<int32_t>() : nullptr, /*derive_lo=*/true};
         const bool timing = g_time_kernels.load(std::memory_order_relaxed) != 0;
         if (timing) {
             if (!ws.ev0) {
@@ -1346,7 +1349,7 @@ int ann_cuda_ivfflat_get_list(const ann_cuda_index *ix, int64_t list_no, int64_t
     if (rows) {
         float *buf = nullptr;
         ANN_CUDA_TRY(cudaMalloc(&buf, (size_t)n * ix->d * 4));
-        int rc = launch_join_rows(ix->vhi + b * ix->dp, ix->vlo + b * ix->dp, n, ix->d, ix->dp, buf, nullptr);
+        int rc = launch_join_rows(ix->vhi + b * ix->dp, nullptr, n, ix->d, ix->dp, buf, nullptr);
         cudaError_t e = cudaMemcpy(rows, buf, (size_t)n * ix->d * 4, cudaMemcpyDeviceToHost);
         cudaFree(buf);
         if (rc) return -1;
@@ -1656,7 +1659,7 @@ int ann_cuda_index_reconstruct(const ann_cuda_index *ix, int64_t key, float *rec
     if (h == 0x7fffffffffffffffll) return set_error("reconstruct: key %lld not found", (long long)key);
     float *buf = nullptr;
     ANN_CUDA_TRY(cudaMalloc(&buf, (size_t)ix->d * 4));
-    int rc = launch_join_rows(ix->vhi + h * ix->dp, ix->vlo + h * ix->dp, 1, ix->d, ix->dp, buf, nullptr);
+    int rc = launch_join_rows(ix->vhi + h * ix->dp, nullptr, 1, ix->d, ix->dp, buf, nullptr);
     cudaError_t e = cudaMemcpy(recons, buf, (size_t)ix->d * 4, cudaMemcpyDeviceToHost);
     cudaFree(buf);
     if (rc) return -1;

@@ -114,6 +114,10 @@ struct GroupedWork {
     // append mode only (16 < k <= kAppendMaxK), may be null: finished rows keep their append
     // buffer unsorted and write its fill count to part_cnt[gathered row]; use launch_merge_filtered
     int32_t *part_cnt = nullptr;
+    // The rows are ONE plane of plain fp32 values (xhi; xlo is not read): two more warps of every CTA
+    // split each row tile into its TF32 hi / lo parts in shared memory, between the load and the MMAs -
+    // the same operands as with two stored planes, for half the bytes from DRAM.
+    bool derive_lo = false;
 };
 FlatPlan make_grouped_plan(int64_t max_query_tiles, int k, int sms);
 

@@ -155,10 +155,14 @@ scatter_rows_kernel(const float *__restrict__ x, int64_t n, int d, int dp, const
         float acc = 0.f;
         for (int c = lane; c < dp; c += 32) {
             const float v = c < d ? x[r * (int64_t)d + c] : 0.f;
-            const float h = to_tf32(v);
             acc = fmaf(v, v, acc);
-            hi[dst * (int64_t)dp + c] = h;
-            lo[dst * (int64_t)dp + c] = v - h;
+            if (lo) {
+                const float h = to_tf32(v);
+                hi[dst * (int64_t)dp + c] = h;
+                lo[dst * (int64_t)dp + c] = v - h;
+            } else {  // one plane of plain rows
+                hi[dst * (int64_t)dp + c] = v;
+            }
         }
         acc = warp_sum(acc);
         if (lane == 0) norms[dst] = acc;
@@ -216,7 +220,8 @@ residual_norms_kernel(const float *__restrict__ xhi, const float *__restrict__ x
         }
         float acc = 0.f;
         for (int c = lane; c < d; c += 32) {
-            const float v = (xhi[r * (int64_t)dp + c] + xlo[r * (int64_t)dp + c]) -
+            // (xlo null: xhi holds the plain rows)
+            const float v = (xhi[r * (int64_t)dp + c] + (xlo ? xlo[r * (int64_t)dp + c] : 0.f)) -
                             (chi[(int64_t)lo_l * dp + c] + clo[(int64_t)lo_l * dp + c]);
             acc = fmaf(v, v, acc);
         }
