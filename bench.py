@@ -420,8 +420,9 @@ class FlatWorkload:
 
 
 # DRAM read + write bytes of one grouped list-scan launch, keyed by (rows, queries, GPUs), from the
-# ncu capture of the grouped list scan at the default shape (14.6-14.8 GB read + 0.2 GB written)
-IVF_SCAN_TRAFFIC = {(1_000_000, 10_000, 1): 14.8e9}
+# ncu capture of the grouped list scan at the default shape (10.0-10.1 GB read + 0.23 GB written with the
+# lists kept as one fp32 plane; 14.6-14.8 GB + 0.2 GB while they were two TF32 planes)
+IVF_SCAN_TRAFFIC = {(1_000_000, 10_000, 1): 10.3e9}
 
 
 class IvfWorkload:
@@ -512,7 +513,7 @@ class IvfWorkload:
         # (rows scanned x d x 4, per GPU).  The kernel gathers the queries probing a list into
         # tiles of 128 and reads a list row once per tile, on the tensor cores, so the
         # algorithmic rate EXCEEDS the HBM peak by design (frac > 1); `traffic` is what DRAM
-        # really moved (the physical bound: ~5.5 TB/s of it at the full size), and `tensor` restates
+        # really moved (~4 TB/s of it at the full size; the launch is bound by shared-memory bandwidth now), and `tensor` restates
         # the same launch against the MMA roofline (useful flops = 2 d per (query, row) pair; tile
         # padding not counted).
         pairs = self.rows_scanned / max(self.world, 1)
