@@ -61,6 +61,8 @@ SIGNATURES = {
     "ann_cuda_ivfflat_get_list": (C.c_int, [_P, _I64, _P, _P]),
     "ann_cuda_ivfflat_get_centroids": (C.c_int, [_P, _P]),
     "ann_cuda_ivfflat_coarse": (C.c_int, [_P, _I64, _P, _I64, _P]),
+    "ann_cuda_ivfflat_coarse_device": (C.c_int, [_P, C.c_int64, _P, _P, _P]),
+    "ann_cuda_ivfflat_search_preassigned_device": (C.c_int, [_P, C.c_int64, _P, _P, C.c_int64, _P, _P, C.c_int64, _P]),
     "ann_cuda_ivfflat_set_nprobe": (C.c_int, [_P, _I64]),
     "ann_cuda_ivfflat_get_nprobe": (_I64, [_P]),
     "ann_cuda_ivfflat_nlist": (_I64, [_P]),

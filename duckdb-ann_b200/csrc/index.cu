@@ -817,9 +817,11 @@ int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const 
 // Flat: tier_hint = lowest tier to start from.  gated = false runs that one tier and leaves the
 // verdict of its band check in the status words for the host to act on; gated = true enqueues the
 // higher tiers behind it, each running only if the tier before it flagged an overflow.
+// IVF: given_probes (may be null) = nq x nprobe list numbers on the device, best first, -1 = none; the
+// coarse quantiser is then skipped (the probes were chosen elsewhere, e.g. by another shard's GPU).
 int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const float *x_dev, int64_t k,
                         float *d_dev, int64_t *i_dev, int64_t label_offset, cudaStream_t stream, int tier_hint,
-                        bool gated) {
+                        bool gated, const int32_t *given_probes = nullptr) {
     if (!ix.ivf) {
         const int k_sel = (int)std::min<int64_t>(k, ix.store.n);
         int tier = flat_first_tier(ix, k_sel);
@@ -844,7 +846,11 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
     if (ws.probes.ensure((size_t)n_items * 4) || ws.item_slot.ensure(n_items * 4) ||
         ws.scratch.ensure((size_t)(ix.nlist + 1) * 2 * 4))
         return -1;
-    if (coarse_probes(ix, ws, x_dev, nq, nprobe, ws.probes.as<int32_t>(), stream, ix.coarse_exact)) return -1;
+    if (given_probes) {
+        ANN_CUDA_TRY(cudaMemcpyAsync(ws.probes.ptr, given_probes, (size_t)n_items * 4, cudaMemcpyDeviceToDevice, stream));
+    } else if (coarse_probes(ix, ws, x_dev, nq, nprobe, ws.probes.as<int32_t>(), stream, ix.coarse_exact)) {
+        return -1;
+    }
     if (ws.qtau.ensure((size_t)nq * 4)) return -1;
     ANN_CUDA_TRY(cudaMemsetAsync(ws.qtau.ptr, 0xFF, (size_t)nq * 4, stream));
     if (flat_kernel_choice() == FlatKernel::TC) {
@@ -939,7 +945,7 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
 // calls on a caller's stream until ann_cuda_index_search_status collects them).
 int search_device_impl(const ann_cuda_index &ix, Workspace &ws, int64_t n, const float *x_dev, int64_t k, float *d_dev,
                        int64_t *i_dev, int64_t label_offset, cudaStream_t stream, int tier_hint, bool gated,
-                       bool keep_sticky = false) {
+                       bool keep_sticky = false, const int32_t *given_probes = nullptr) {
     if (k <= 0) return set_error("k must be > 0");  // MetalIndexFlat.mm:297
     if (n <= 0) return 0;
     if (!ix.trained) return set_error("search: index must be trained first");  // MetalIndexIVFFlat.mm:125
@@ -958,8 +964,9 @@ int search_device_impl(const ann_cuda_index &ix, Workspace &ws, int64_t n, const
         // the overflow words speak of one block of queries
         if (q0 > 0 || keep_sticky)
             ANN_CUDA_TRY(cudaMemsetAsync(ws.status.as<int>() + kStatusTier0, 0, kTiers * sizeof(int), stream));
+        const int64_t np = ix.ivf ? std::min<int64_t>(std::max<int64_t>(ix.nprobe, 1), ix.nlist) : 0;
         if (search_block_device(ix, ws, nb, x_dev + q0 * ix.d, k, d_dev + q0 * k, i_dev + q0 * k, label_offset, stream,
-                                tier_hint, gated))
+                                tier_hint, gated, given_probes ? given_probes + q0 * np : nullptr))
             return -1;
     }
     return ws_publish_status(ws, stream);
@@ -1383,6 +1390,40 @@ int ann_cuda_ivfflat_coarse(const ann_cuda_index *ix, int64_t n, const float *x,
             for (int64_t p = 0; p < nprobe; p++) lists[(q0 + q) * nprobe + p] = p < np ? tmp[q * np + p] : -1;
     }
     return 0;
+}
+
+int ann_cuda_ivfflat_coarse_device(const ann_cuda_index *ix, int64_t n, const float *x_device, int32_t *lists_device,
+                                   void *stream) {
+    if (!ix || !ix->ivf || n < 0 || (n > 0 && (!x_device || !lists_device))) return set_error("invalid arguments");
+    if (!ix->trained) return set_error("index is not trained");
+    if (n == 0) return 0;
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    WsLease lease(ix, s, false);
+    if (!lease.ws) return -1;
+    Workspace &ws = *lease.ws;
+    const int np = (int)std::min<int64_t>(std::max<int64_t>(ix->nprobe, 1), ix->nlist);
+    if (ws_status_ready(ws)) return -1;
+    for (int64_t q0 = 0; q0 < n; q0 += kQueryBlock) {
+        const int64_t nb = std::min(kQueryBlock, n - q0);
+        if (coarse_probes(*ix, ws, x_device + q0 * ix->d, nb, np, lists_device + q0 * np, s, ix->coarse_exact)) return -1;
+    }
+    return ws_publish_status(ws, s);
+}
+
+int ann_cuda_ivfflat_search_preassigned_device(const ann_cuda_index *ix, int64_t n, const float *x_device,
+                                               const int32_t *assign_device, int64_t k, float *distances_device,
+                                               int64_t *labels_device, int64_t label_offset, void *stream) {
+    if (!ix || !ix->ivf || n < 0 || (n > 0 && (!x_device || !assign_device || !distances_device || !labels_device)))
+        return set_error("invalid arguments");
+    DeviceGuard g(ix->device);
+    if (ensure_device(ix, g)) return -1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    WsLease lease(ix, s, false);
+    if (!lease.ws) return -1;
+    return search_device_impl(*ix, *lease.ws, n, x_device, k, distances_device, labels_device, label_offset, s, 0, true, true,
+                              assign_device);
 }
 
 int ann_cuda_ivfflat_set_nprobe(ann_cuda_index *ix, int64_t nprobe) {

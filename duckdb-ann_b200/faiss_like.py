@@ -282,6 +282,41 @@ class CudaIndexIVFFlat(_CudaIndex):
         p.check(p.lib().ann_cuda_ivfflat_coarse(self._h, x.shape[0], _ptr(x), nprobe, _ptr(out)), "coarse")
         return out
 
+    def coarse_device(self, x, out=None, stream=None):
+        """Coarse quantiser on device buffers: (n, nprobe) int32 list numbers, nearest centroid first
+        (nprobe = the index's), enqueued on `stream`, not synchronised."""
+        import torch
+        assert x.is_cuda and x.is_contiguous() and x.dtype == torch.float32 and x.shape[1] == self.d
+        n, nprobe = x.shape[0], min(self.getNprobe(), self.getNlist())
+        if out is None:
+            out = torch.empty((n, nprobe), dtype=torch.int32, device=x.device)
+        assert out.is_contiguous() and out.dtype == torch.int32 and tuple(out.shape) == (n, nprobe)
+        s = stream if stream is not None else torch.cuda.current_stream(x.device)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_ivfflat_coarse_device(self._h, n, C.c_void_p(x.data_ptr()), C.c_void_p(out.data_ptr()),
+                                                       C.c_void_p(s.cuda_stream)), "coarse_device")
+        return out
+
+    def search_preassigned_device(self, x, assign, k: int, D=None, I=None, label_offset: int = 0, stream=None):
+        """search_device() with the probe lists given (faiss::IndexIVF::search_preassigned): assign is an
+        (n, nprobe) int32 CUDA tensor of list numbers, -1 = none.  Lists this shard does not store are skipped."""
+        import torch
+        assert x.is_cuda and x.is_contiguous() and x.dtype == torch.float32 and x.shape[1] == self.d
+        n = x.shape[0]
+        assert assign.is_cuda and assign.is_contiguous() and assign.dtype == torch.int32
+        assert tuple(assign.shape) == (n, min(self.getNprobe(), self.getNlist()))
+        if D is None:
+            D = torch.empty((n, k), dtype=torch.float32, device=x.device)
+        if I is None:
+            I = torch.empty((n, k), dtype=torch.int64, device=x.device)
+        s = stream if stream is not None else torch.cuda.current_stream(x.device)
+        p = _pkg()
+        p.check(p.lib().ann_cuda_ivfflat_search_preassigned_device(self._h, n, C.c_void_p(x.data_ptr()),
+                                                                   C.c_void_p(assign.data_ptr()), k, C.c_void_p(D.data_ptr()),
+                                                                   C.c_void_p(I.data_ptr()), label_offset,
+                                                                   C.c_void_p(s.cuda_stream)), "search_preassigned_device")
+        return D, I
+
     def getNlist(self) -> int:
         return _pkg().lib().ann_cuda_ivfflat_nlist(self._h)
 

@@ -2,7 +2,8 @@
 
 One process per GPU (torch.distributed).  Flat: database rows are split into
 contiguous ranges, one per rank.  IVFFlat: inverted list l lives on rank
-l % world; the coarse quantiser is replicated.  Every rank searches its shard
+l % world; every rank runs the coarse quantiser for its slice of the queries and
+the probe lists are all-gathered (centroids are replicated).  Every rank searches its shard
 for ALL queries, the per-shard (distance, label) top-k lists are exchanged with
 one all-gather (k * 12 bytes per query per rank) and a final k-select kernel
 merges them on every rank.  The reference has no multi-GPU path; this follows
@@ -54,6 +55,30 @@ class ShardedSearcher:
         self._merge = merge
         self._gather_d = None
         self._gather_i = None
+        # IVFFlat over several ranks: each rank runs the coarse quantiser for its slice of the queries only
+        self.split_coarse = True
+        self._probes = None
+        self._my_probes = None
+
+    def _ivf_search_split_coarse(self, x, k: int, world: int):
+        """IVFFlat over several ranks without a replicated coarse quantiser: this rank ranks the centroids
+        for ITS slice of the queries, the probe lists are all-gathered (nq * nprobe * 4 bytes in total) and
+        the lists stored here are scanned for all queries with the probes given."""
+        import torch
+        import torch.distributed as dist
+        rank = dist.get_rank(self.group)
+        nq = x.shape[0]
+        per = (nq + world - 1) // world          # equal slices, the last ones padded with "no list"
+        lo, hi = min(nq, rank * per), min(nq, (rank + 1) * per)
+        nprobe = min(self.index.getNprobe(), self.index.getNlist())
+        if self._probes is None or tuple(self._probes.shape) != (world * per, nprobe) or self._probes.device != x.device:
+            self._probes = torch.empty((world * per, nprobe), dtype=torch.int32, device=x.device)
+            self._my_probes = torch.empty((per, nprobe), dtype=torch.int32, device=x.device)
+        self._my_probes.fill_(-1)
+        if hi > lo:
+            self.index.coarse_device(x[lo:hi], out=self._my_probes[: hi - lo])
+        dist.all_gather_into_tensor(self._probes, self._my_probes, group=self.group)
+        return self.index.search_preassigned_device(x, self._probes[:nq], k, label_offset=self.label_offset)
 
     def _world(self) -> int:
         import torch.distributed as dist
@@ -68,7 +93,10 @@ class ShardedSearcher:
         else:
             if self.index is None:
                 raise RuntimeError("ShardedSearcher needs a CUDA index (there is no CPU search path)")
-            d_loc, i_loc = self.index.search_device(x, k, label_offset=self.label_offset)
+            if world > 1 and self.split_coarse and hasattr(self.index, "search_preassigned_device"):
+                d_loc, i_loc = self._ivf_search_split_coarse(x, k, world)
+            else:
+                d_loc, i_loc = self.index.search_device(x, k, label_offset=self.label_offset)
         if world == 1:
             return d_loc, i_loc
         shape = (world,) + tuple(d_loc.shape)

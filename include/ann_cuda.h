@@ -96,6 +96,18 @@ int ann_cuda_ivfflat_get_centroids(const ann_cuda_index *index, float *centroids
  * coarse_search step of MetalIndexIVFFlat::search (MetalIndexIVFFlat.mm:60-66, 155). */
 int ann_cuda_ivfflat_coarse(const ann_cuda_index *index, int64_t n, const float *x, int64_t nprobe, int64_t *lists);
 
+/* Multi-GPU IVFFlat without a replicated coarse quantiser: every GPU ranks the centroids for ITS share of the
+ * queries (ann_cuda_ivfflat_coarse_device: n x nprobe list numbers, int32, best first, nprobe = the index's),
+ * the probe lists are exchanged (a few hundred KB), and every GPU scans the lists it stores for ALL queries
+ * with the probes given (faiss::IndexIVF::search_preassigned with `assign`; -1 = no list).  Both are
+ * stream-ordered like ann_cuda_index_search_device; ann_cuda_index_search_status collects a failed wait.
+ * No counterpart in the reference (it has no multi-GPU path). */
+int ann_cuda_ivfflat_coarse_device(const ann_cuda_index *index, int64_t n, const float *x_device, int32_t *lists_device,
+                                   void *stream);
+int ann_cuda_ivfflat_search_preassigned_device(const ann_cuda_index *index, int64_t n, const float *x_device,
+                                               const int32_t *assign_device, int64_t k, float *distances_device,
+                                               int64_t *labels_device, int64_t label_offset, void *stream);
+
 /* setNprobe / getNprobe (MetalIndexIVFFlat.mm:267-279): clamped to [1, nlist]. */
 int ann_cuda_ivfflat_set_nprobe(ann_cuda_index *index, int64_t nprobe);
 int64_t ann_cuda_ivfflat_get_nprobe(const ann_cuda_index *index);

@@ -254,6 +254,27 @@ def test_list_sharding_matches_unsharded(pkg, oracle):
     Dref, Iref = oracle.ivf_search(xb, cent, off, rows, xq, 10, 8, oracle.METRIC_L2)
     assert (I.cpu().numpy() == Iref).mean() > 0.995
     np.testing.assert_allclose(D.cpu().numpy(), Dref, rtol=1e-4)
+    # The same without a replicated coarse quantiser (what the sharded searcher does over several ranks):
+    # every shard ranks the centroids for ITS slice of the queries, the slices are put together (the
+    # all-gather), and every shard scans its lists for all queries with the probes given.
+    per = (len(xq) + 2) // 3
+    probes = torch.full((3 * per, 8), -1, dtype=torch.int32, device="cuda")
+    for rank, sh in enumerate(shards):
+        lo, hi = min(len(xq), rank * per), min(len(xq), (rank + 1) * per)
+        sh.coarse_device(xq_dev[lo:hi], out=probes[lo:hi])
+    np.testing.assert_array_equal(probes[:len(xq)].cpu().numpy(), shards[0].coarse(xq, 8))
+    parts2 = [sh.search_preassigned_device(xq_dev, probes[:len(xq)], 10) for sh in shards]
+    for sh in shards:
+        sh.search_status()
+    D2, I2 = pkg.merge_topk_device(torch.stack([p[0] for p in parts2]).contiguous(),
+                                   torch.stack([p[1] for p in parts2]).contiguous(), pkg.METRIC_L2)
+    np.testing.assert_array_equal(I2.cpu().numpy(), I.cpu().numpy())
+    np.testing.assert_array_equal(D2.cpu().numpy(), D.cpu().numpy())
+    # a probe list of "no list" entries finds nothing
+    none = torch.full((len(xq), 8), -1, dtype=torch.int32, device="cuda")
+    D3, I3 = shards[0].search_preassigned_device(xq_dev, none, 10)
+    torch.cuda.synchronize()
+    assert (I3.cpu().numpy() == -1).all() and np.isinf(D3.cpu().numpy()).all()
     for s in shards:
         s.close()
 
