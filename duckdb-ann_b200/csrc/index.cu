@@ -1404,7 +1404,10 @@ int ann_cuda_ivfflat_coarse_device(const ann_cuda_index *ix, int64_t n, const fl
     if (!lease.ws) return -1;
     Workspace &ws = *lease.ws;
     const int np = (int)std::min<int64_t>(std::max<int64_t>(ix->nprobe, 1), ix->nlist);
-    if (ws_status_ready(ws)) return -1;
+    // (the words of a workspace that has never searched start at zero; later ones keep what the stream's
+    // earlier calls left for ann_cuda_index_search_status to collect)
+    const bool fresh = ws.status.ptr == nullptr;
+    if (ws_status_ready(ws) || (fresh && ws_clear_status(ws, s))) return -1;
     for (int64_t q0 = 0; q0 < n; q0 += kQueryBlock) {
         const int64_t nb = std::min(kQueryBlock, n - q0);
         if (coarse_probes(*ix, ws, x_device + q0 * ix->d, nb, np, lists_device + q0 * np, s, ix->coarse_exact)) return -1;

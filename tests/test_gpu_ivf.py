@@ -270,6 +270,16 @@ def test_list_sharding_matches_unsharded(pkg, oracle):
                                    torch.stack([p[1] for p in parts2]).contiguous(), pkg.METRIC_L2)
     np.testing.assert_array_equal(I2.cpu().numpy(), I.cpu().numpy())
     np.testing.assert_array_equal(D2.cpu().numpy(), D.cpu().numpy())
+    # the coarse quantiser as the FIRST call on an index and stream leaves a clean status behind
+    fresh = pkg.CudaIndexIVFFlat(64, 32, pkg.METRIC_L2)
+    fresh.set_centroids(cent)
+    fresh.setNprobe(8)
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        p0 = fresh.coarse_device(xq_dev, stream=st)
+        fresh.search_status(stream=st)
+    np.testing.assert_array_equal(p0.cpu().numpy(), shards[0].coarse(xq, 8))
+    fresh.close()
     # a probe list of "no list" entries finds nothing
     none = torch.full((len(xq), 8), -1, dtype=torch.int32, device="cuda")
     D3, I3 = shards[0].search_preassigned_device(xq_dev, none, 10)
