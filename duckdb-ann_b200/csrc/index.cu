@@ -149,6 +149,11 @@ struct Workspace {
     cudaStream_t bound = nullptr;  // stream whose work may still use these buffers
     GrowBuf x, qhi, qlo, qn, part_key, part_idx, sel_key, sel_idx, status, out_d, out_i;
     GrowBuf item_q, item_rb, item_re, item_slot, scratch, probes_key, probes, qtau, sched, gq, items, qconst, part_cnt;
+    // Flat tier chain: one word per query of the block, set by the band check of the latest tensor-core tier
+    // for the queries it could not prove complete; the exact tier then repairs those queries only.
+    GrowBuf over_q;
+    GrowBuf bad_q;  // 16-bit stores: queries that overflow the type (set when the queries are split)
+    bool over_q_valid = false;  // a tensor-core tier of the current block search has (been enqueued to) set them
     // Status words (device: `status`, pinned host copy: `status_host`), kStatusWords ints:
     //   [0]      first give-up code of a bounded wait inside a kernel; sticky for one API call
     //   [1 + t]  tier t of the flat search (see kTierScreen ...) found more rows inside its error band
@@ -163,7 +168,7 @@ struct Workspace {
         if (ev1) cudaEventDestroy(ev1);
         for (GrowBuf *b : {&x, &qhi, &qlo, &qn, &part_key, &part_idx, &sel_key, &sel_idx, &status, &out_d, &out_i,
                            &item_q, &item_rb, &item_re, &item_slot, &scratch, &probes_key, &probes, &qtau, &sched, &gq, &items,
-                           &qconst, &part_cnt})
+                           &qconst, &part_cnt, &over_q, &bad_q})
             b->release();
         if (status_host) cudaFreeHost(status_host);
         if (own_stream) cudaStreamDestroy(own_stream);
@@ -371,6 +376,8 @@ struct TopkOpts {
     // a pass of a tier chain (flat_tier_search): the queries were split by the first pass, the band check runs
     // inside the re-ranking kernel that follows, and the caller publishes the status words once at the end
     bool chained = false;
+    // exact tier: repair only the queries whose word in ws.over_q is set (the others keep their results)
+    bool flagged_only = false;
 };
 // x_dev: nq x d queries on the device.  Leaves (nq x k) keys and int32 rows, best
 // first, in ws.sel_key / ws.sel_idx.  The status words must have been cleared by the caller.
@@ -390,7 +397,7 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         if (!(o.chained && o.gate) &&
             (st.elem != kElemF32
                  ? launch_split_rows_h16(x_dev, nq, d, dp, ws.qhi.ptr, ws.qlo.ptr, ws.qn.as<float>(), stream, st.center(), true,
-                                         nullptr, st.elem, status + kStatusTier0)
+                                         nullptr, st.elem, status + kStatusTier0, ws.bad_q.as<int32_t>())
                  : launch_split_rows(x_dev, nq, d, dp, ws.qhi.as<float>(), ws.qlo.as<float>(), ws.qn.as<float>(), stream,
                                      st.center(), true)))
             return -1;
@@ -410,7 +417,7 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         if (launch_flat_scratch_init(ws.qtau.as<uint32_t>(), qtau_bytes / 4, ws.sched.as<int>(), plan.sched_ints,
                                      append ? ws.part_cnt.as<int32_t>() : nullptr, cnt_words,
                                      append ? nullptr : ws.part_idx.as<int32_t>(), plan.part_entries / plan.list_stride,
-                                     plan.list_stride, k, stream, o.gate))
+                                     plan.list_stride, k, stream, o.gate, o.chained ? ws.over_q.as<int32_t>() : nullptr, (size_t)nq))
             return -1;
         const bool timing = !o.gate && g_time_kernels.load(std::memory_order_relaxed) != 0;
         if (timing) {
@@ -453,8 +460,14 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         return o.chained ? 0 : ws_publish_status(ws, stream);
     }
     // exact-fp32 scan: items = (query, database chunk), laid out on the device
+    // (all queries: enough items to fill the device; flagged queries only: nobody knows here how many there are,
+    // so every query is cut into as many chunks as the merge takes and the scratch allows - one hard query
+    // among thousands is then still scanned by dozens of warps)
+    const int64_t fill = (int64_t)sm_count(ix.device) * 32 / std::max<int64_t>(nq, 1) + 1;
+    const int64_t wide = std::max<int64_t>(fill, (int64_t)(16 << 20) / std::max<int64_t>(nq * k, 1));
     int chunks = (int)std::max<int64_t>(1, std::min<int64_t>({(int64_t)kMergeCandidates / k, (st.n + 255) / 256,
-                                                             (int64_t)sm_count(ix.device) * 32 / std::max<int64_t>(nq, 1) + 1}));
+                                                             o.flagged_only ? wide : fill}));
+    const int32_t *only_q = o.flagged_only ? ws.over_q.as<int32_t>() : nullptr;
     const int64_t per = (st.n + chunks - 1) / chunks;
     chunks = (int)((st.n + per - 1) / per);
     const int64_t n_items = nq * chunks;
@@ -462,14 +475,14 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
         ws.part_key.ensure((size_t)n_items * k * 4) || ws.part_idx.ensure((size_t)n_items * k * 4))
         return -1;
     if (launch_fill_chunk_items(ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(), ws.item_re.as<int64_t>(), nq, chunks, per,
-                                st.n, stream))
+                                st.n, stream, only_q))
         return -1;
     if (launch_scan_items(st.hi, st.lo, dp, d, x_dev, d, ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(),
                           ws.item_re.as<int64_t>(), n_items, k, ix.metric, ws.part_key.as<float>(),
                           ws.part_idx.as<int32_t>(), nullptr, ix.device, stream, o.gate, st.elem))
         return -1;
     if (launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 1, nullptr, nullptr, chunks, nq, k, k,
-                           ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream, false, nullptr, o.gate))
+                           ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device, stream, false, nullptr, o.gate, only_q))
         return -1;
     return o.chained ? 0 : ws_publish_status(ws, stream);
 }
@@ -786,14 +799,21 @@ int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const 
     int k_list = k_sel;
     const bool banded = tier == kTierScreen || tier == kTierSplitWide ||
                         (tier == kTierSplit && (k_sel > 12 || ix.store.elem != kElemF32) && banded_lists_fit(ix, k_sel));
+    if (ws.over_q.ensure((size_t)nq * 4) || (ix.store.elem != kElemF32 && ws.bad_q.ensure((size_t)nq * 4))) return -1;
     if (tier == kTierExact) {
         o.exact = true;
+        // behind a tensor-core tier of the same block search: only the queries that tier flagged
+        o.flagged_only = ws.over_q_valid;
     } else if (banded) {
         k_list = (int)std::min<int64_t>((int64_t)kScreenMaxList, n);
         o.k_rank = o.check_rank = k_sel;
         o.one_mma = tier == kTierScreen;
     } else {
-        k_list = (int)std::min<int64_t>(k_sel <= 12 ? 16 : (int64_t)k_sel + kSplitSpare, n);
+        // Spare candidates beyond k for the band check: the rows inside the error band of the k-th key grow
+        // with k and with the store (5M unit-norm rows of 768 floats: ~15 at k = 256, ~33 at k = 512, ~130 at
+        // k = 2048), so a quarter of k, at least kSplitSpare, as far as the longest list allows.
+        const int64_t spare = std::max<int64_t>(kSplitSpare, std::min<int64_t>(k_sel / 4, (int64_t)kMaxListK - k_sel));
+        k_list = (int)std::min<int64_t>(k_sel <= 12 ? 16 : (int64_t)k_sel + spare, n);
         o.check_rank = k_list > k_sel ? k_sel : 0;
     }
     if (split_store_topk(ix, ix.store, ws, x_dev, nq, k_list, stream, o)) return -1;
@@ -805,9 +825,12 @@ int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const 
     const bool tc = tier != kTierExact && flat_kernel_choice() == FlatKernel::TC;
     const RefineBand band{tc ? ws.sel_key.as<float>() : nullptr, k_sel, ws.qn.as<float>(), ix.store.max_norm2, ix.d, o.one_mma,
                           ix.store.elem, banded, (tc && k_list < n) ? o.check_rank : 0, status + kStatusTier0 + tier,
-                          status + kStatusFallbacks};
+                          status + kStatusFallbacks, tc ? ws.over_q.as<int32_t>() : nullptr,
+                          o.flagged_only ? ws.over_q.as<int32_t>() : nullptr,
+                          (tc && ix.store.elem != kElemF32) ? ws.bad_q.as<int32_t>() : nullptr};
+    if (tc) ws.over_q_valid = true;  // (its scratch-init kernel cleared the words, this kernel sets them)
     // (a 16-bit store always hands the band over: it says how the rows are to be read)
-    const bool give = (tc && (banded || band.check_rank > 0)) || ix.store.elem != kElemF32;
+    const bool give = (tc && (banded || band.check_rank > 0)) || ix.store.elem != kElemF32 || o.flagged_only;
     return launch_refine_finalize(ix.store.hi, ix.store.lo, ix.dp, ix.d, x_dev, ix.d, ws.sel_idx.as<int32_t>(), nq, k_list,
                                   (int)k, ix.metric, nullptr, label_offset, d_dev, i_dev, ix.device, stream, nullptr, nullptr,
                                   nullptr, nullptr, gate, give ? &band : nullptr);
@@ -825,6 +848,9 @@ int search_block_device(const ann_cuda_index &ix, Workspace &ws, int64_t nq, con
     if (!ix.ivf) {
         const int k_sel = (int)std::min<int64_t>(k, ix.store.n);
         int tier = flat_first_tier(ix, k_sel);
+        // a search that starts at its first tier has no flagged queries yet; one that repeats from a higher
+        // tier (the host's repeat after reading the band check) inherits those of the pass before it
+        if (tier_hint <= tier) ws.over_q_valid = false;
         while (tier < tier_hint && tier < kTierExact) tier = flat_next_tier(ix, k_sel, tier);
         const int *gate = nullptr;
         for (;;) {

@@ -54,7 +54,8 @@ int launch_join_rows(const float *hi, const float *lo, int64_t n, int d, int dp,
 // Rows or queries of a 16-bit store (see prep_rows_h16_kernel): hi (and lo, queries only) are n x dp 16-bit
 // elements; overflow (may be null) points at the status words of the two tensor-core tiers.
 int launch_split_rows_h16(const float *x, int64_t n, int d, int dp, void *hi, void *lo, float *norms, cudaStream_t stream,
-                          const float *mu, bool center_rows, unsigned *max_norm2_bits, int elem, int *overflow);
+                          const float *mu, bool center_rows, unsigned *max_norm2_bits, int elem, int *overflow,
+                          int32_t *bad_row = nullptr);
 
 // ---- flat_tc.cu --------------------------------------------------------------------------
 constexpr int kSmemListMax = 16;         // lists up to this length are kept in shared memory
@@ -88,7 +89,7 @@ FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms);
 // number -1 in the first k slots of each of the `lists` lists of `list_stride` slots.
 int launch_flat_scratch_init(uint32_t *qtau, size_t qtau_words, int *sched, size_t sched_ints, int32_t *cnt,
                              size_t cnt_words, int32_t *idx, size_t lists, int list_stride, int k, cudaStream_t stream,
-                             const int *gate);
+                             const int *gate, int32_t *over_q = nullptr, size_t nq = 0);
 
 // Fused split-TF32 GEMM + k-selection on the tensor cores.  Inputs are hi/lo row
 // stores of the database (n x dp) and the queries (nq x dp), plus row norms for L2.
@@ -213,9 +214,11 @@ int launch_scan_items(const float *x, const float *xlo, int dp, int d, const flo
                       int device, cudaStream_t stream, const int *gate = nullptr, int elem = 0);
 
 // Items of the exact flat scan, built on the device: item q * chunks + c = query q against rows
-// [c * per, min(n, (c + 1) * per)).
+// [c * per, min(n, (c + 1) * per)).  With only_q (one word per query) the items of queries whose word is zero
+// are marked "skip" (kItemSkip): the scan neither works on them nor writes their lists.
+constexpr int32_t kItemSkip = -2;
 int launch_fill_chunk_items(int32_t *item_query, int64_t *range_begin, int64_t *range_end, int64_t nq, int chunks,
-                            int64_t per, int64_t n, cudaStream_t stream);
+                            int64_t per, int64_t n, cudaStream_t stream, const int32_t *only_q = nullptr);
 
 // Builds the (query, list) items of an IVF search from the coarse result:
 // probes (nq x nprobe) int32 list numbers (-1 = none); items are grouped by list so
@@ -239,7 +242,7 @@ int launch_build_ivf_items(const int32_t *probes, int64_t nq, int nprobe, int64_
 int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layout, const int *lists_started,
                        const int32_t *slot_of, int nparts, int64_t nq, int k, int list_stride, float *out_key,
                        int32_t *out_idx, int device, cudaStream_t stream, bool lists_sorted = false,
-                       const float *slot_key_offset = nullptr, const int *gate = nullptr);
+                       const float *slot_key_offset = nullptr, const int *gate = nullptr, const int32_t *only_q = nullptr);
 
 // Grouped list scan: per query, the k best of the lists of its nparts probes (gathered row
 // slot_of[q * nparts + p], -1 = none), sorted best first.  A row's list is the first part_cnt[row]
@@ -274,6 +277,9 @@ struct RefineBand {
     int check_rank;
     int *overflow;
     int *overflow_count;
+    int32_t *over_q;          // optional, one word per query: set to 1 for every query whose band check fails
+    const int32_t *only_q;    // optional: re-rank (and write results for) the queries with a non-zero word only
+    const int32_t *bad_q;     // optional: queries whose keys are meaningless (non-zero word): their check fails
 };
 
 // Flat: recomputes the distance of every selected (query, row) pair in exact fp32

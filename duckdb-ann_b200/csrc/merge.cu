@@ -55,12 +55,14 @@ __global__ void __launch_bounds__(kMergeThreads)
 merge_parts_kernel(const float *__restrict__ part_key, const int32_t *__restrict__ part_idx, int layout,
                    const int *__restrict__ lists_started, const int32_t *__restrict__ slot_of, int nparts, int64_t nq,
                    int k, int list_stride, int P_max, const float *__restrict__ slot_key_offset,
-                   float *__restrict__ out_key, int32_t *__restrict__ out_idx, const int *gate) {
+                   float *__restrict__ out_key, int32_t *__restrict__ out_idx, const int *gate,
+                   const int32_t *__restrict__ only_q) {
     extern __shared__ float smem_f[];
     if (gate_closed(gate)) return;
     float *keys = smem_f;
     int32_t *vals = reinterpret_cast<int32_t *>(smem_f + P_max);
     const int64_t q = blockIdx.x;
+    if (only_q && !only_q[q]) return;  // a pass that repairs the flagged queries only
     int nlists = nparts;
     if (layout == 0) {
         const int started = lists_started[q >> 7];
@@ -266,9 +268,11 @@ merge_filtered_kernel(const float *__restrict__ part_key, const int32_t *__restr
 // One kernel in place of three or four memsets in front of a flat_tc launch (see kernels.h).
 __global__ void flat_scratch_init_kernel(uint32_t *qtau, size_t qtau_words, int *sched, size_t sched_ints, int32_t *cnt,
                                          size_t cnt_words, int32_t *idx, size_t lists, int list_stride, int k,
-                                         const int *gate) {
+                                         const int *gate, int32_t *over_q, size_t nq) {
     if (gate_closed(gate)) return;
     const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, step = (size_t)gridDim.x * blockDim.x;
+    if (over_q)
+        for (size_t i = t0; i < nq; i += step) over_q[i] = 0;
     for (size_t i = t0; i < qtau_words; i += step) qtau[i] = 0xffffffffu;
     for (size_t i = t0; i < sched_ints; i += step) sched[i] = 0;
     if (cnt)
@@ -308,6 +312,7 @@ refine_finalize_kernel(const float *__restrict__ xhi, const float *__restrict__ 
     float *keys = smem_f;
     int32_t *vals = reinterpret_cast<int32_t *>(smem_f + P);
     const int64_t q = blockIdx.x;
+    if (band.only_q && !band.only_q[q]) return;  // a pass that repairs the flagged queries only
     // candidates beyond the slack above the rank-th ranking key cannot be among the exact best
     float band_cut = kInf;
     if (band.key) {
@@ -317,8 +322,9 @@ refine_finalize_kernel(const float *__restrict__ xhi, const float *__restrict__ 
         // band check of the selecting pass: the last candidate still inside the band means rows may be missing
         if (threadIdx.x == 0 && band.check_rank > 0 && band.check_rank < k_sel) {
             const float last = band.key[q * k_sel + k_sel - 1], kth = band.key[q * k_sel + band.check_rank - 1];
-            if (last < kInf && last <= kth + slack) {
+            if ((last < kInf && last <= kth + slack) || (band.bad_q && band.bad_q[q])) {
                 if (atomicCAS(band.overflow, 0, kScreenOverflow) == 0 && band.overflow_count) atomicAdd(band.overflow_count, 1);
+                if (band.over_q) band.over_q[q] = 1;
             }
         }
     }
@@ -469,8 +475,9 @@ int opt_in_smem(K kernel, size_t smem) {
 int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layout, const int *lists_started,
                        const int32_t *slot_of, int nparts, int64_t nq, int k, int list_stride, float *out_key,
                        int32_t *out_idx, int device, cudaStream_t stream, bool lists_sorted,
-                       const float *slot_key_offset, const int *gate) {
+                       const float *slot_key_offset, const int *gate, const int32_t *only_q) {
     (void)device;
+    if (only_q) lists_sorted = false;  // (the pairwise merge of sorted lists has no such filter)
     if (nq <= 0) return 0;
     const int total = nparts * k;
     if (total > kMaxCandidates) return set_error("merge: %d candidates per query exceeds %d", total, kMaxCandidates);
@@ -492,7 +499,7 @@ int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layou
     if (opt_in_smem(merge_parts_kernel, smem)) return -1;
     merge_parts_kernel<<<(unsigned)nq, kMergeThreads, smem, stream>>>(part_key, part_idx, layout, lists_started, slot_of,
                                                                       nparts, nq, k, list_stride, P, slot_key_offset, out_key,
-                                                                      out_idx, gate);
+                                                                      out_idx, gate, only_q);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -530,14 +537,14 @@ int launch_screen_check(const float *sel_key, int64_t nq, int k_list, int k_rank
 
 int launch_flat_scratch_init(uint32_t *qtau, size_t qtau_words, int *sched, size_t sched_ints, int32_t *cnt,
                              size_t cnt_words, int32_t *idx, size_t lists, int list_stride, int k, cudaStream_t stream,
-                             const int *gate) {
+                             const int *gate, int32_t *over_q, size_t nq) {
     size_t most = qtau_words > sched_ints ? qtau_words : sched_ints;
     if (cnt && cnt_words > most) most = cnt_words;
     if (idx && lists * (size_t)k > most) most = lists * (size_t)k;
     if (most == 0) return 0;
     const unsigned blocks = (unsigned)std::min<size_t>((most + 255) / 256, 1184);
     flat_scratch_init_kernel<<<blocks, 256, 0, stream>>>(qtau, qtau_words, sched, sched_ints, cnt, cnt_words, idx, lists,
-                                                         list_stride, k, gate);
+                                                         list_stride, k, gate, over_q, nq);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -558,7 +565,7 @@ int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, co
                                                                 out_d, out_i, out_row, gate,
                                                                 band ? *band
                                                                      : RefineBand{nullptr, 0, nullptr, nullptr, 0, false, kElemF32,
-                                                                                  false, 0, nullptr, nullptr});
+                                                                                  false, 0, nullptr, nullptr, nullptr, nullptr, nullptr});
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

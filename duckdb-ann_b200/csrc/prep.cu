@@ -78,11 +78,13 @@ prep_rows_kernel(const float *__restrict__ x, int64_t n, int d, int dp, float *_
 //  Queries (center_rows = 1): w = q - mu is split into two 16-bit parts, h = round(w), l = round(w - h);
 //    norms[r] = |w|^2 (unrounded).  A finite query element that overflows the 16-bit type (fp16: above
 //    65504) makes every tensor-core key of the block meaningless: overflow[0..1] (the status words of the
-//    two tensor-core tiers, may be null) are set to kScreenOverflow, which sends the block to the exact scan.
+//    two tensor-core tiers, may be null) are set to kScreenOverflow, which sends the block to the exact scan,
+//    and bad_row[r] (may be null) says for every query whether it is such a one.
 __global__ void __launch_bounds__(kWarps * 32)
 prep_rows_h16_kernel(const float *__restrict__ x, int64_t n, int d, int dp, uint16_t *__restrict__ hi,
                      uint16_t *__restrict__ lo, float *__restrict__ norms, const float *__restrict__ mu, int center_rows,
-                     unsigned *__restrict__ max_norm2_bits, int elem, int *__restrict__ overflow) {
+                     unsigned *__restrict__ max_norm2_bits, int elem, int *__restrict__ overflow,
+                     int32_t *__restrict__ bad_row) {
     const int lane = threadIdx.x & 31;
     for (int64_t r = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); r < n; r += (int64_t)gridDim.x * kWarps) {
         const float *src = x + r * (int64_t)d;
@@ -114,7 +116,9 @@ prep_rows_h16_kernel(const float *__restrict__ x, int64_t n, int d, int dp, uint
             raw = warp_sum(raw);
             if (lane == 0) atomicMax(max_norm2_bits, __float_as_uint(raw));
         }
-        if (overflow && __any_sync(0xffffffffu, bad) && lane == 0) {
+        const bool any_bad = __any_sync(0xffffffffu, bad);
+        if (bad_row && lane == 0) bad_row[r] = any_bad ? 1 : 0;  // (per row: the band checks count it as failed)
+        if (overflow && any_bad && lane == 0) {
             overflow[0] = kScreenOverflow;
             overflow[1] = kScreenOverflow;
         }
@@ -268,11 +272,12 @@ int launch_pad_rows(const float *x, int64_t n, int d, int dp, float *out, float 
 }
 
 int launch_split_rows_h16(const float *x, int64_t n, int d, int dp, void *hi, void *lo, float *norms, cudaStream_t stream,
-                          const float *mu, bool center_rows, unsigned *max_norm2_bits, int elem, int *overflow) {
+                          const float *mu, bool center_rows, unsigned *max_norm2_bits, int elem, int *overflow,
+                          int32_t *bad_row) {
     if (n <= 0) return 0;
     prep_rows_h16_kernel<<<grid_for(n), kWarps * 32, 0, stream>>>(x, n, d, dp, static_cast<uint16_t *>(hi),
                                                                   static_cast<uint16_t *>(lo), norms, mu, center_rows ? 1 : 0,
-                                                                  max_norm2_bits, elem, overflow);
+                                                                  max_norm2_bits, elem, overflow, bad_row);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

@@ -46,6 +46,7 @@ scan_items_kernel(const float *__restrict__ x, const float *__restrict__ xlo, in
     const int n4 = dp >> 2;
     for (int64_t item = (int64_t)blockIdx.x * kWarps + warp; item < n_items; item += (int64_t)gridDim.x * kWarps) {
         const int q = item_query[item];
+        if (q == kItemSkip) continue;  // a query this pass does not repair: its lists are never read
         const int64_t begin = range_begin[item], end = range_end[item];
         float *lk = part_key + item * (int64_t)k;
         int32_t *li = part_idx + item * (int64_t)k;
@@ -139,11 +140,11 @@ scan_items_kernel(const float *__restrict__ x, const float *__restrict__ xlo, in
 // ---- items of the exact flat scan -------------------------------------------------------------
 __global__ void fill_chunk_items_kernel(int32_t *__restrict__ item_query, int64_t *__restrict__ range_begin,
                                         int64_t *__restrict__ range_end, int64_t n_items, int chunks, int64_t per,
-                                        int64_t n) {
+                                        int64_t n, const int32_t *__restrict__ only_q) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_items) return;
     const int64_t q = i / chunks, c = i - q * chunks;
-    item_query[i] = (int32_t)q;
+    item_query[i] = (only_q && !only_q[q]) ? kItemSkip : (int32_t)q;
     range_begin[i] = c * per;
     range_end[i] = (c + 1) * per < n ? (c + 1) * per : n;
 }
@@ -322,11 +323,11 @@ int launch_scan_items(const float *x, const float *xlo, int dp, int d, const flo
 }
 
 int launch_fill_chunk_items(int32_t *item_query, int64_t *range_begin, int64_t *range_end, int64_t nq, int chunks,
-                            int64_t per, int64_t n, cudaStream_t stream) {
+                            int64_t per, int64_t n, cudaStream_t stream, const int32_t *only_q) {
     const int64_t n_items = nq * chunks;
     if (n_items <= 0) return 0;
     fill_chunk_items_kernel<<<(unsigned)((n_items + 255) / 256), 256, 0, stream>>>(item_query, range_begin, range_end,
-                                                                                   n_items, chunks, per, n);
+                                                                                   n_items, chunks, per, n, only_q);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

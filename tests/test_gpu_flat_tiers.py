@@ -85,6 +85,33 @@ def test_near_ties_far_denser_than_the_split_product_resolves(pkg, oracle):
         idx.close()
 
 
+@pytest.mark.parametrize("entry", ["host", "device"])
+def test_the_exact_scan_repairs_the_flagged_queries_only(pkg, oracle, entry):
+    """One query in 300 sits on 400 near ties that no tensor-core tier can order; the other 299 are
+    ordinary.  The exact scan that settles it runs for the flagged query alone - the others keep the
+    answers of the tier before, which must still be the oracle's - whether the host repeats the
+    search tier by tier or the tiers were enqueued behind one another on the device."""
+    import torch
+    rng = np.random.default_rng(29)
+    xb, q0 = _near_tie_store(rng, 64, 20000, 400, "L2", 1e-6)
+    xq = (rng.standard_normal((300, 64))).astype(np.float32)
+    xq[137] = q0
+    idx = pkg.CudaIndexFlat(64, pkg.METRIC_L2)
+    idx.add(xb)
+    before = pkg.lib().ann_cuda_screen_fallbacks()
+    for k in (8, 40):
+        if entry == "host":
+            D, I = idx.search(xq, k)
+        else:
+            Dd, Id = idx.search_device(torch.from_numpy(xq).cuda(), k)
+            idx.search_status()
+            D, I = Dd.cpu().numpy(), Id.cpu().numpy()
+        Dref, Iref = oracle.flat_search(xb, xq, k, oracle.METRIC_L2)
+        assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D, I, Dref, Iref, f"one hard query among 300, k={k}, {entry}")
+    assert pkg.lib().ann_cuda_screen_fallbacks() >= before + 2, "the exact scan never ran"
+    idx.close()
+
+
 @pytest.mark.parametrize("entry", ["device", "async"])
 def test_fallback_passes_run_on_the_device_for_the_entries_that_do_not_wait(pkg, oracle, entry):
     """search_device and search_async return before anything has run: the higher tiers are enqueued
