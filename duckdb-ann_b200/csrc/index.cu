@@ -775,7 +775,13 @@ int flat_first_tier(const ann_cuda_index &ix, int k_sel) {
     }
     // (ANN_CUDA_FLAT_SCREEN=0 turns screening off, =1 applies it to stores of any size)
     const int screen_env = g_flat_screen.load(std::memory_order_relaxed);
-    if (banded_lists_fit(ix, k_sel) && (screen_env == 1 || (screen_env != 0 && ix.store.n >= kScreenMinRows)))
+    // The one-MMA band holds ~0.3 k rows above the k-th on the stores measured (5M-20M unit-norm rows of 768
+    // floats), and a list keeps 256 - k of them: from k ~ 200 on the screened pass only discovers that it
+    // overflowed (k = 200: 180 ms against 140 ms when the split product's banded lists go first).  Forcing the
+    // screened tier (tests) takes it for every k the lists can hold.
+    constexpr int kScreenTierMaxK = 160;
+    if (banded_lists_fit(ix, k_sel) &&
+        (screen_env == 1 || (screen_env != 0 && ix.store.n >= kScreenMinRows && k_sel <= kScreenTierMaxK)))
         return kTierScreen;
     return kTierSplit;
 }
