@@ -153,6 +153,7 @@ struct Workspace {
     // for the queries it could not prove complete; the exact tier then repairs those queries only.
     GrowBuf over_q;
     GrowBuf bad_q;  // 16-bit stores: queries that overflow the type (set when the queries are split)
+    GrowBuf complete_to;  // per query: key below which the merged candidates of several replace-max lists are complete
     bool over_q_valid = false;  // a tensor-core tier of the current block search has (been enqueued to) set them
     // Status words (device: `status`, pinned host copy: `status_host`), kStatusWords ints:
     //   [0]      first give-up code of a bounded wait inside a kernel; sticky for one API call
@@ -168,7 +169,7 @@ struct Workspace {
         if (ev1) cudaEventDestroy(ev1);
         for (GrowBuf *b : {&x, &qhi, &qlo, &qn, &part_key, &part_idx, &sel_key, &sel_idx, &status, &out_d, &out_i,
                            &item_q, &item_rb, &item_re, &item_slot, &scratch, &probes_key, &probes, &qtau, &sched, &gq, &items,
-                           &qconst, &part_cnt, &over_q, &bad_q})
+                           &qconst, &part_cnt, &over_q, &bad_q, &complete_to})
             b->release();
         if (status_host) cudaFreeHost(status_host);
         if (own_stream) cudaStreamDestroy(own_stream);
@@ -378,15 +379,22 @@ struct TopkOpts {
     bool chained = false;
     // exact tier: repair only the queries whose word in ws.over_q is set (the others keep their results)
     bool flagged_only = false;
+    // replace-max lists (k beyond the append lists): the merge may hand on more candidates than one list is
+    // long - up to this many - with the bound below which they are complete in ws.complete_to; *wide_used
+    // receives the number of candidates per query that came out (k if the selection has no such lists)
+    int wide_out = 0;
+    int *wide_used = nullptr;
 };
 // x_dev: nq x d queries on the device.  Leaves (nq x k) keys and int32 rows, best
 // first, in ws.sel_key / ws.sel_idx.  The status words must have been cleared by the caller.
 int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &ws, const float *x_dev, int64_t nq,
                      int k, cudaStream_t stream, const TopkOpts &o = TopkOpts()) {
     const int dp = st.dp, d = ix.d;
+    const size_t k_buf = (size_t)std::max(k, o.wide_out);
     if (ws.qhi.ensure((size_t)nq * dp * 4) || ws.qlo.ensure((size_t)nq * dp * 4) || ws.qn.ensure((size_t)nq * 4) ||
-        ws.sel_key.ensure((size_t)nq * k * 4) || ws.sel_idx.ensure((size_t)nq * k * 4) || ws_status_ready(ws))
+        ws.sel_key.ensure((size_t)nq * k_buf * 4) || ws.sel_idx.ensure((size_t)nq * k_buf * 4) || ws_status_ready(ws))
         return -1;
+    if (o.wide_used) *o.wide_used = k;
     int *status = ws.status.as<int>();
     if (!o.exact && flat_kernel_choice() == FlatKernel::TC) {
         // the split of the queries is the same in every tier: a gated fallback pass finds it in place
@@ -447,9 +455,21 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
                                            nullptr, ws.qtau.as<uint32_t>(), plan.lists_per_qt, nq, k, plan.list_stride,
                                            ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), stream,
                                            ws.sched.as<int>() + plan.nq_tiles, o.gate)
-                   : launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 0, ws.sched.as<int>() + plan.nq_tiles,
-                                        nullptr, plan.lists_per_qt, nq, k, plan.list_stride, ws.sel_key.as<float>(),
-                                        ws.sel_idx.as<int32_t>(), ix.device, stream, false, nullptr, o.gate))
+                   : [&] {
+                         // several replace-max lists per query: their union holds more than one list's length
+                         int k_out = 0;
+                         float *complete_to = nullptr;
+                         if (o.wide_out > k && o.wide_used && plan.lists_per_qt > 1 && plan.lists_per_qt <= 32 &&
+                             !ws.complete_to.ensure((size_t)nq * 4)) {
+                             k_out = (int)std::min<int64_t>(o.wide_out, (int64_t)plan.lists_per_qt * k);
+                             complete_to = ws.complete_to.as<float>();
+                             *o.wide_used = k_out;
+                         }
+                         return launch_merge_parts(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), 0,
+                                                   ws.sched.as<int>() + plan.nq_tiles, nullptr, plan.lists_per_qt, nq, k,
+                                                   plan.list_stride, ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), ix.device,
+                                                   stream, false, nullptr, o.gate, nullptr, k_out, complete_to);
+                     }())
             return -1;
         // (a list that holds every row of the store has left nothing out)
         if (!o.chained && o.check_rank > 0 && k < st.n &&
@@ -802,7 +822,7 @@ int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const 
     o.tier = tier;
     o.gate = gate;
     o.chained = true;
-    int k_list = k_sel;
+    int k_list = k_sel, k_cand = 0;
     const bool banded = tier == kTierScreen || tier == kTierSplitWide ||
                         (tier == kTierSplit && (k_sel > 12 || ix.store.elem != kElemF32) && banded_lists_fit(ix, k_sel));
     if (ws.over_q.ensure((size_t)nq * 4) || (ix.store.elem != kElemF32 && ws.bad_q.ensure((size_t)nq * 4))) return -1;
@@ -821,8 +841,17 @@ int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const 
         const int64_t spare = std::max<int64_t>(kSplitSpare, std::min<int64_t>(k_sel / 4, (int64_t)kMaxListK - k_sel));
         k_list = (int)std::min<int64_t>(k_sel <= 12 ? 16 : (int64_t)k_sel + spare, n);
         o.check_rank = k_list > k_sel ? k_sel : 0;
+        // replace-max lists: every CTA that worked on a query tile leaves a list of ITS rows' best k_list, so the
+        // merge can hand on up to 512 candidates more than one list is long (k = 2,048: the longest list holds
+        // 2,112, the error band of a 5M-row store ~130 rows above the 2,048-th)
+        if (k_list > kAppendMaxK) {
+            o.wide_out = (int)std::min<int64_t>((int64_t)k_list + 512, n);
+            o.wide_used = &k_cand;
+        }
     }
     if (split_store_topk(ix, ix.store, ws, x_dev, nq, k_list, stream, o)) return -1;
+    const bool widened = k_cand > k_list;  // the merge handed on more than one list's length, with ws.complete_to
+    if (widened) k_list = k_cand;          // what the re-ranking below sees
     // banded lists: only what lies within the slack of the k-th ranking key needs the exact distance.  The
     // band check of the pass (is the last candidate still inside the band?) runs in the same kernel and
     // leaves its verdict in this tier's overflow word, which gates the next tier.
@@ -833,7 +862,8 @@ int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const 
                           ix.store.elem, banded, (tc && k_list < n) ? o.check_rank : 0, status + kStatusTier0 + tier,
                           status + kStatusFallbacks, tc ? ws.over_q.as<int32_t>() : nullptr,
                           o.flagged_only ? ws.over_q.as<int32_t>() : nullptr,
-                          (tc && ix.store.elem != kElemF32) ? ws.bad_q.as<int32_t>() : nullptr};
+                          (tc && ix.store.elem != kElemF32) ? ws.bad_q.as<int32_t>() : nullptr,
+                          (tc && widened) ? ws.complete_to.as<float>() : nullptr};
     if (tc) ws.over_q_valid = true;  // (its scratch-init kernel cleared the words, this kernel sets them)
     // (a 16-bit store always hands the band over: it says how the rows are to be read)
     const bool give = (tc && (banded || band.check_rank > 0)) || ix.store.elem != kElemF32 || o.flagged_only;

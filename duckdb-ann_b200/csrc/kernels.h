@@ -242,7 +242,8 @@ int launch_build_ivf_items(const int32_t *probes, int64_t nq, int nprobe, int64_
 int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layout, const int *lists_started,
                        const int32_t *slot_of, int nparts, int64_t nq, int k, int list_stride, float *out_key,
                        int32_t *out_idx, int device, cudaStream_t stream, bool lists_sorted = false,
-                       const float *slot_key_offset = nullptr, const int *gate = nullptr, const int32_t *only_q = nullptr);
+                       const float *slot_key_offset = nullptr, const int *gate = nullptr, const int32_t *only_q = nullptr,
+                       int k_out = 0, float *complete_to = nullptr);
 
 // Grouped list scan: per query, the k best of the lists of its nparts probes (gathered row
 // slot_of[q * nparts + p], -1 = none), sorted best first.  A row's list is the first part_cnt[row]
@@ -280,6 +281,10 @@ struct RefineBand {
     int32_t *over_q;          // optional, one word per query: set to 1 for every query whose band check fails
     const int32_t *only_q;    // optional: re-rank (and write results for) the queries with a non-zero word only
     const int32_t *bad_q;     // optional: queries whose keys are meaningless (non-zero word): their check fails
+    // optional, per query: the candidates are the best of a UNION of lists and are known to be complete only
+    // for keys below this bound (launch_merge_parts, complete_to); the check takes the smaller of it and the
+    // last candidate's key
+    const float *complete_to;
 };
 
 // Flat: recomputes the distance of every selected (query, row) pair in exact fp32

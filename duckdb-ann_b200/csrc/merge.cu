@@ -56,13 +56,21 @@ merge_parts_kernel(const float *__restrict__ part_key, const int32_t *__restrict
                    const int *__restrict__ lists_started, const int32_t *__restrict__ slot_of, int nparts, int64_t nq,
                    int k, int list_stride, int P_max, const float *__restrict__ slot_key_offset,
                    float *__restrict__ out_key, int32_t *__restrict__ out_idx, const int *gate,
-                   const int32_t *__restrict__ only_q) {
+                   const int32_t *__restrict__ only_q, int k_out, float *__restrict__ complete_to) {
     extern __shared__ float smem_f[];
+    // per list (up to 32 of them when complete_to is asked for): entries present, largest key
+    __shared__ int list_cnt[32];
+    __shared__ unsigned list_max[32];
     if (gate_closed(gate)) return;
     float *keys = smem_f;
     int32_t *vals = reinterpret_cast<int32_t *>(smem_f + P_max);
     const int64_t q = blockIdx.x;
     if (only_q && !only_q[q]) return;  // a pass that repairs the flagged queries only
+    if (complete_to && threadIdx.x < 32) {
+        list_cnt[threadIdx.x] = 0;
+        list_max[threadIdx.x] = 0u;
+    }
+    if (complete_to) __syncthreads();
     int nlists = nparts;
     if (layout == 0) {
         const int started = lists_started[q >> 7];
@@ -86,16 +94,30 @@ merge_parts_kernel(const float *__restrict__ part_key, const int32_t *__restrict
             if (idx >= 0) {
                 key = part_key[list * list_stride + j] + (slot_key_offset ? slot_key_offset[list] : 0.f);
                 val = idx;
+                if (complete_to) {
+                    atomicAdd(&list_cnt[p], 1);
+                    atomicMax(&list_max[p], float_to_ordered(key));
+                }
             }
         }
         keys[t] = key;
         vals[t] = val;
     }
     bitonic_sort(keys, vals, P);
-    for (int j = threadIdx.x; j < k; j += blockDim.x) {
+    // k_out entries go out (k_out >= k: the union of the lists holds more than one list's length)
+    for (int j = threadIdx.x; j < k_out; j += blockDim.x) {
         const bool ok = j < P && vals[j] != 0x7fffffff;
-        out_key[q * k + j] = ok ? keys[j] : kInf;
-        out_idx[q * k + j] = ok ? vals[j] : -1;
+        out_key[q * k_out + j] = ok ? keys[j] : kInf;
+        out_idx[q * k_out + j] = ok ? vals[j] : -1;
+    }
+    // Every list holds the k best keys of ITS rows: a row that is in no list has a key at least as large as
+    // the largest key of the (full) list its rows went to.  The union is therefore complete below the smallest
+    // of those maxima - a list that is not full left nothing out.
+    if (complete_to && threadIdx.x == 0) {
+        float t_min = kInf;
+        for (int p = 0; p < nlists; p++)
+            if (list_cnt[p] >= k) t_min = fminf(t_min, ordered_to_float(list_max[p]));
+        complete_to[q] = t_min;
     }
 }
 
@@ -321,7 +343,10 @@ refine_finalize_kernel(const float *__restrict__ xhi, const float *__restrict__ 
         if (band.cut && band.rank <= k_sel) band_cut = band.key[q * k_sel + band.rank - 1] + slack;
         // band check of the selecting pass: the last candidate still inside the band means rows may be missing
         if (threadIdx.x == 0 && band.check_rank > 0 && band.check_rank < k_sel) {
-            const float last = band.key[q * k_sel + k_sel - 1], kth = band.key[q * k_sel + band.check_rank - 1];
+            float last = band.key[q * k_sel + k_sel - 1];
+            const float kth = band.key[q * k_sel + band.check_rank - 1];
+            // (candidates merged from several lists: complete only below the bound the merge found)
+            if (band.complete_to) last = fminf(last, band.complete_to[q]);
             if ((last < kInf && last <= kth + slack) || (band.bad_q && band.bad_q[q])) {
                 if (atomicCAS(band.overflow, 0, kScreenOverflow) == 0 && band.overflow_count) atomicAdd(band.overflow_count, 1);
                 if (band.over_q) band.over_q[q] = 1;
@@ -475,9 +500,12 @@ int opt_in_smem(K kernel, size_t smem) {
 int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layout, const int *lists_started,
                        const int32_t *slot_of, int nparts, int64_t nq, int k, int list_stride, float *out_key,
                        int32_t *out_idx, int device, cudaStream_t stream, bool lists_sorted,
-                       const float *slot_key_offset, const int *gate, const int32_t *only_q) {
+                       const float *slot_key_offset, const int *gate, const int32_t *only_q, int k_out,
+                       float *complete_to) {
     (void)device;
-    if (only_q) lists_sorted = false;  // (the pairwise merge of sorted lists has no such filter)
+    if (only_q || complete_to || k_out > 0) lists_sorted = false;  // (the pairwise merge of sorted lists has none of these)
+    if (k_out <= 0) k_out = k;
+    if (k_out < k || (complete_to && nparts > 32)) return set_error("merge: invalid output length or too many lists");
     if (nq <= 0) return 0;
     const int total = nparts * k;
     if (total > kMaxCandidates) return set_error("merge: %d candidates per query exceeds %d", total, kMaxCandidates);
@@ -499,7 +527,7 @@ int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layou
     if (opt_in_smem(merge_parts_kernel, smem)) return -1;
     merge_parts_kernel<<<(unsigned)nq, kMergeThreads, smem, stream>>>(part_key, part_idx, layout, lists_started, slot_of,
                                                                       nparts, nq, k, list_stride, P, slot_key_offset, out_key,
-                                                                      out_idx, gate, only_q);
+                                                                      out_idx, gate, only_q, k_out, complete_to);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -565,7 +593,7 @@ int launch_refine_finalize(const float *xhi, const float *xlo, int dp, int d, co
                                                                 out_d, out_i, out_row, gate,
                                                                 band ? *band
                                                                      : RefineBand{nullptr, 0, nullptr, nullptr, 0, false, kElemF32,
-                                                                                  false, 0, nullptr, nullptr, nullptr, nullptr, nullptr});
+                                                                                  false, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr});
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
