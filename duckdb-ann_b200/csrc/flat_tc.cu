@@ -52,6 +52,14 @@
 // signalled in both CTAs by one multicast tcgen05.commit, "accumulator empty" collects the eight
 // epilogue warps of the pair in the leader.  No load is multicast.
 //
+// This file is compiled three times: as it stands (TF32 operands, K blocks of 16 floats), through
+// flat_tc_bk32.cu (K blocks of 32 floats: the screened search) and through flat_tc_h16.cu (fp16 / bf16
+// operands, tcgen05.mma kind::f16: stores that keep their rows in 16 bits).
+//
+// Inverted-list scans read their rows as ONE plane of plain fp32 values (KernelArgs::derive_lo): such
+// launches have two more warps (256 threads) that turn each row tile, once it has landed in shared
+// memory, into its TF32 hi / lo parts in place - see the converter role below.
+//
 // CTA layout (192 threads, one CTA per SM):
 //   warp 0     scheduler + TMA producer: takes the next chunk, announces it to the
 //              other roles through a small descriptor ring, then per K block
@@ -239,7 +247,7 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
 }
 
 // (fmt: operand_format() of the 16-bit build, 0 otherwise)
-__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate,
+__device__ __forceinline__ void mma_issue(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate,
                                          uint32_t fmt = 0) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -284,7 +292,7 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
 }
 // One MMA over both CTAs of the pair: A = 2 x 128 queries (each CTA's own), B = 2 x 128 rows (half
 // of the tile in each CTA), D = 128 x 256 in each CTA's tensor memory.  Issued by the leader only.
-__device__ __forceinline__ void mma_tf32_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate,
+__device__ __forceinline__ void mma_issue_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate,
                                               uint32_t fmt = 0) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -1049,9 +1057,9 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             const uint64_t a0 = make_smem_desc(base);
                             const uint64_t b0 = make_smem_desc(base + kABytes);
                             if (!(kdebug(args) & 2)) {
-                                mma_tf32_pair(tmem_d, a0, b0, kb != 0, fmt);
+                                mma_issue_pair(tmem_d, a0, b0, kb != 0, fmt);
 #pragma unroll
-                                for (int ks = 1; ks < BK / kMmaK; ks++) mma_tf32_pair(tmem_d, a0 + 2 * ks, b0 + 2 * ks, 1, fmt);
+                                for (int ks = 1; ks < BK / kMmaK; ks++) mma_issue_pair(tmem_d, a0 + 2 * ks, b0 + 2 * ks, 1, fmt);
                             }
                             mma_commit_pair(bar_empty + 8 * stage);  // frees the stage in both CTAs
                             if (++stage == nstages) {
@@ -1068,9 +1076,9 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                             const uint64_t a0 = make_smem_desc(base + (stage & 1) * kABytes);
                             const uint64_t b0 = make_smem_desc(base + 2 * kABytes + (stage & 1) * kBBytes);
                             if (!(kdebug(args) & 2)) {
-                                mma_tf32(tmem_d, a0, b0, kb != 0, fmt);
+                                mma_issue(tmem_d, a0, b0, kb != 0, fmt);
 #pragma unroll
-                                for (int ks = 1; ks < BK / kMmaK; ks++) mma_tf32(tmem_d, a0 + 2 * ks, b0 + 2 * ks, 1, fmt);
+                                for (int ks = 1; ks < BK / kMmaK; ks++) mma_issue(tmem_d, a0 + 2 * ks, b0 + 2 * ks, 1, fmt);
                             }
                         } else {
                             const uint32_t base = smem_base + stage * kStageBytes;
@@ -1083,12 +1091,12 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                                 if (kdebug(args) & 2) continue;
                                 if (kH16) {
                                     // 16-bit rows are exact: the query alone is split, q = q_hi + q_lo
-                                    mma_tf32(tmem_d, a_lo, b_hi, (kb | ks) != 0, fmt);
-                                    mma_tf32(tmem_d, a_hi, b_hi, 1, fmt);
+                                    mma_issue(tmem_d, a_lo, b_hi, (kb | ks) != 0, fmt);
+                                    mma_issue(tmem_d, a_hi, b_hi, 1, fmt);
                                 } else {
-                                    mma_tf32(tmem_d, a_hi, b_lo, (kb | ks) != 0);
-                                    mma_tf32(tmem_d, a_lo, b_hi, 1);
-                                    mma_tf32(tmem_d, a_hi, b_hi, 1);
+                                    mma_issue(tmem_d, a_hi, b_lo, (kb | ks) != 0);
+                                    mma_issue(tmem_d, a_lo, b_hi, 1);
+                                    mma_issue(tmem_d, a_hi, b_hi, 1);
                                 }
                             }
                         }
