@@ -1696,7 +1696,10 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     CUtensorMap maps[4];
     const bool bf16 = kH16 && screen && screen->elem == kElemBF16;
     // (16-bit build: there is no lo plane of the rows; the fourth map repeats the third)
-    if (make_map(&maps[0], qhi, nq, dp, BM, bf16) || make_map(&maps[1], qlo ? qlo : qhi, nq, dp, BM, bf16) ||
+    // The query planes are allocated in whole tiles of 128 rows (the rows past nq hold anything: their
+    // accumulator rows are never looked at), so no query load ever reaches past the end of its tensor.
+    const int64_t nq_rows = grouped ? nq : (nq + BM - 1) / BM * BM;
+    if (make_map(&maps[0], qhi, nq_rows, dp, BM, bf16) || make_map(&maps[1], qlo ? qlo : qhi, nq_rows, dp, BM, bf16) ||
         make_map(&maps[2], xhi, n, dp, BN, bf16) || make_map(&maps[3], (kH16 || !xlo) ? xhi : xlo, n, dp, BN, bf16))
         return -1;
     KernelArgs a;

@@ -391,7 +391,8 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
                      int k, cudaStream_t stream, const TopkOpts &o = TopkOpts()) {
     const int dp = st.dp, d = ix.d;
     const size_t k_buf = (size_t)std::max(k, o.wide_out);
-    if (ws.qhi.ensure((size_t)nq * dp * 4) || ws.qlo.ensure((size_t)nq * dp * 4) || ws.qn.ensure((size_t)nq * 4) ||
+    const size_t nq_rows = (size_t)(nq + 127) / 128 * 128;  // the kernel loads the query planes in whole tiles
+    if (ws.qhi.ensure(nq_rows * dp * 4) || ws.qlo.ensure(nq_rows * dp * 4) || ws.qn.ensure((size_t)nq * 4) ||
         ws.sel_key.ensure((size_t)nq * k_buf * 4) || ws.sel_idx.ensure((size_t)nq * k_buf * 4) || ws_status_ready(ws))
         return -1;
     if (o.wide_used) *o.wide_used = k;
@@ -451,7 +452,12 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
             ix.last_timed_ws = &ws;
         }
         // per query: the lists of its query tile, filtered by the query's final threshold, sorted once
-        if (append ? launch_merge_filtered(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(), ws.part_cnt.as<int32_t>(), nullptr,
+        // (lists in shared memory, k <= 16: whole lists of k slots, no fill counts; the per-query threshold word
+        // holds the smallest "largest key of a full list", above which nothing can be among the k best)
+        const bool small_lists = !append && k <= kSmemListMax;
+        if ((append || small_lists)
+                ? launch_merge_filtered(ws.part_key.as<float>(), ws.part_idx.as<int32_t>(),
+                                           append ? ws.part_cnt.as<int32_t>() : nullptr, nullptr,
                                            nullptr, ws.qtau.as<uint32_t>(), plan.lists_per_qt, nq, k, plan.list_stride,
                                            ws.sel_key.as<float>(), ws.sel_idx.as<int32_t>(), stream,
                                            ws.sched.as<int>() + plan.nq_tiles, o.gate)

@@ -92,7 +92,8 @@ int launch_flat_scratch_init(uint32_t *qtau, size_t qtau_words, int *sched, size
                              const int *gate, int32_t *over_q = nullptr, size_t nq = 0);
 
 // Fused split-TF32 GEMM + k-selection on the tensor cores.  Inputs are hi/lo row
-// stores of the database (n x dp) and the queries (nq x dp), plus row norms for L2.
+// stores of the database (n x dp) and the queries (nq x dp, in buffers that hold whole tiles of 128
+// rows: ceil(nq / 128) * 128 x dp elements each, the rows past nq unspecified), plus row norms for L2.
 // Writes 128 unsorted lists of k (key, local row) pairs per list slot
 // (slot = query tile * lists_per_qt + j, j < sched[nq_tiles + query tile]).
 // Flat search with the append selection (FlatPlan::lists_sorted) and flat_part_cnt given: a list

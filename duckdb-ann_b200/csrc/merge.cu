@@ -252,6 +252,31 @@ merge_filtered_kernel(const float *__restrict__ part_key, const int32_t *__restr
         const int started = lists_started[q >> 7];
         nlists = started < nparts ? started : nparts;
     }
+    if (lists_started && !part_cnt) {
+        // Whole lists of list_stride slots (empty ones carry index -1), many and short: one flat walk over
+        // (list, slot) pairs instead of a loop over the lists (a single query of a small-k search has ~200
+        // lists of 16 entries - a block-wide sort of all of them took 62 us, this takes a few).
+        const int total = nlists * list_stride;
+        for (int t0 = 0; t0 < total; t0 += blockDim.x) {
+            __syncthreads();
+            const int have = count;
+            __syncthreads();
+            if (have + (int)blockDim.x > cap) shrink();
+            const int t = t0 + threadIdx.x;
+            if (t < total) {
+                const int p = t / list_stride, j = t - p * list_stride;
+                const int64_t g = ((q >> 7) * (int64_t)nparts + p) * 128 + (q & 127);
+                const int32_t idx = part_idx[(size_t)g * list_stride + j];
+                const float key = part_key[(size_t)g * list_stride + j];
+                if (idx >= 0 && key <= tau) {
+                    const int pos = atomicAdd(&count, 1);
+                    keys[pos] = key;
+                    vals[pos] = idx;
+                }
+            }
+        }
+        nlists = 0;  // (done: the loop below has nothing left)
+    }
     for (int p = 0; p < nlists; p++) {
         const int64_t g = lists_started ? ((q >> 7) * (int64_t)nparts + p) * 128 + (q & 127) : (int64_t)slot_of[q * nparts + p];
         if (g < 0) continue;  // block-uniform
