@@ -130,8 +130,10 @@ ANN_CUDA_EXPORT void CudaIndexIVFFlat::setNprobe(size_t nprobe) {
 }
 
 // ---------------------------------------------------------------- conversions
-ANN_CUDA_EXPORT std::unique_ptr<CudaIndexFlat> index_cpu_to_cuda(int device, const faiss::IndexFlat *cpu) {
-    std::unique_ptr<CudaIndexFlat> gpu(new CudaIndexFlat(device, cpu->d, cpu->metric_type));
+ANN_CUDA_EXPORT std::unique_ptr<CudaIndexFlat> index_cpu_to_cuda(int device, const faiss::IndexFlat *cpu, StorageType storage) {
+    std::unique_ptr<CudaIndexFlat> gpu(storage == StorageType::Float32
+                                           ? new CudaIndexFlat(device, cpu->d, cpu->metric_type)
+                                           : new CudaIndexFlat(device, cpu->d, cpu->metric_type, storage));
     if (cpu->ntotal > 0) {
         if (ann_cuda_index_reserve(gpu->handle(), cpu->ntotal)) fail("index_cpu_to_cuda");
         gpu->add(cpu->ntotal, cpu->get_xb());
@@ -342,6 +344,12 @@ public:
                 }
             }
         }
+        // ANN_CUDA_STORAGE = f16 | bf16: flat indexes on one device keep their rows in 16 bits (the CPU index the
+        // extension holds stays the source of truth in fp32; searches answer for the rounded rows)
+        if (const char *st = std::getenv("ANN_CUDA_STORAGE")) {
+            if (std::string(st) == "f16") storage_ = faiss_cuda::StorageType::Float16;
+            if (std::string(st) == "bf16") storage_ = faiss_cuda::StorageType::BFloat16;
+        }
         if (devices_.empty()) {
             const char *env = std::getenv("ANN_CUDA_DEVICE");
             int device = env ? std::atoi(env) : 0;
@@ -370,7 +378,7 @@ public:
         }
         if (auto *flat = dynamic_cast<faiss::IndexFlat *>(cpu_index)) {
             if (sharded) return faiss_cuda::index_cpu_to_cuda_sharded(devices_, flat);
-            return faiss_cuda::index_cpu_to_cuda(devices_[0], flat);
+            return faiss_cuda::index_cpu_to_cuda(devices_[0], flat, storage_);
         }
         throw std::runtime_error("CUDA GPU supports IndexFlat and IndexIVFFlat. Got an unsupported index type.");
     }
@@ -384,6 +392,7 @@ public:
 private:
     bool available_ = false;
     std::vector<int> devices_;
+    faiss_cuda::StorageType storage_ = faiss_cuda::StorageType::Float32;
 };
 
 ANN_CUDA_EXPORT GpuBackend &GetGpuBackend() {

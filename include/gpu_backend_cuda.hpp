@@ -146,7 +146,8 @@ private:
 
 // Conversions (faiss-metal/src/MetalIndexFlat.mm:504-535,
 // faiss-metal/src/MetalIndexIVFFlat.mm:283-356).
-std::unique_ptr<CudaIndexFlat> index_cpu_to_cuda(int device, const faiss::IndexFlat *cpu_index);
+std::unique_ptr<CudaIndexFlat> index_cpu_to_cuda(int device, const faiss::IndexFlat *cpu_index,
+                                                 StorageType storage = StorageType::Float32);
 std::unique_ptr<faiss::IndexFlat> index_cuda_to_cpu(const CudaIndexFlat *cuda_index);
 std::unique_ptr<CudaIndexIVFFlat> index_cpu_to_cuda_ivf(int device, const faiss::IndexIVFFlat *cpu_index);
 std::unique_ptr<faiss::IndexIVFFlat> index_cuda_to_cpu_ivf(const CudaIndexIVFFlat *cuda_index);

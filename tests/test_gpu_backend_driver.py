@@ -14,7 +14,8 @@ pytestmark = pytest.mark.gpu
 DRIVER = os.path.join(ROOT, "duckdb-ann_b200", "backend_driver")
 
 
-def _run(tmp_path, mode, d, k, metric, xb, xq, nlist=0, nprobe=0, cent=None, assign=None, devices=None, extra=()):
+def _run(tmp_path, mode, d, k, metric, xb, xq, nlist=0, nprobe=0, cent=None, assign=None, devices=None, extra=(),
+         storage=None):
     inp, out = tmp_path / "in.bin", tmp_path / "out.bin"
     with open(inp, "wb") as f:
         f.write(np.array([d, len(xb), len(xq), k, metric, nlist, nprobe], np.int64).tobytes())
@@ -23,6 +24,9 @@ def _run(tmp_path, mode, d, k, metric, xb, xq, nlist=0, nprobe=0, cent=None, ass
             f.write(cent.tobytes()); f.write(assign.astype(np.int64).tobytes())
     env = dict(os.environ)
     env.pop("ANN_CUDA_DEVICES", None)
+    env.pop("ANN_CUDA_STORAGE", None)
+    if storage:
+        env["ANN_CUDA_STORAGE"] = storage
     if devices:
         env["ANN_CUDA_DEVICES"] = devices
     res = subprocess.run([DRIVER, mode, str(inp), str(out), *extra], capture_output=True, text=True, timeout=300, env=env)
@@ -70,6 +74,22 @@ def test_reduced_precision_storage_through_the_cpp_class(tmp_path, oracle, kind,
     Dref, Iref = oracle.flat_search(xr, xq, 7, metric)
     assert_topk_matches(oracle, xr, xq, metric, D, I, Dref, Iref, f"{kind} batch")
     assert_topk_matches(oracle, xr, xq, metric, D1, I1, Dref, Iref, f"{kind} one query per call")
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+def test_reduced_precision_storage_chosen_by_the_environment(tmp_path, oracle, kind):
+    """ANN_CUDA_STORAGE=f16|bf16: GetGpuBackend().CpuToGpu keeps a flat index's rows in 16 bits without a change
+    to the caller; the searches answer for the rounded rows, and GpuToCpu hands those out (so the round trip is
+    no longer bit for bit - the extension keeps its own fp32 CPU index, src/faiss_index.cpp:108-149)."""
+    rng = np.random.default_rng(42)
+    xb = rng.uniform(-1, 1, (3000, 96)).astype(np.float32)
+    xq = rng.uniform(-1, 1, (12, 96)).astype(np.float32)
+    info, D, I, D1, I1 = _run(tmp_path, "flat", 96, 7, 1, xb, xq, storage=kind)
+    assert info["backend"] == "cuda" and info["roundtrip_ok"] == 0 and info["async_ok"] == 1
+    xr = oracle.round_storage(xb, kind)
+    Dref, Iref = oracle.flat_search(xr, xq, 7, 1)
+    assert_topk_matches(oracle, xr, xq, 1, D, I, Dref, Iref, f"{kind} by environment, batch")
+    assert_topk_matches(oracle, xr, xq, 1, D1, I1, Dref, Iref, f"{kind} by environment, one query per call")
 
 
 def test_ivf_through_gpu_backend(tmp_path, oracle):
@@ -149,6 +169,7 @@ def test_faiss_index_glue(tmp_path, oracle, devices):
         f.write(xb.tobytes()); f.write(xq.tobytes()); f.write(tomb.tobytes())
     env = dict(os.environ)
     env.pop("ANN_CUDA_DEVICES", None)
+    env.pop("ANN_CUDA_STORAGE", None)
     if devices:
         env["ANN_CUDA_DEVICES"] = devices
     res = subprocess.run([DRIVER, "glue", str(inp), str(out), "auto"], capture_output=True, text=True, timeout=300, env=env)
