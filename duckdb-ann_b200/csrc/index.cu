@@ -860,7 +860,7 @@ int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const 
     if (widened) k_list = k_cand;          // what the re-ranking below sees
     // banded lists: only what lies within the slack of the k-th ranking key needs the exact distance.  The
     // band check of the pass (is the last candidate still inside the band?) runs in the same kernel and
-    // leaves its verdict in this tier's overflow word, which gates the next tier.
+    // leaves its finding in this tier's overflow word, which gates the next tier.
     // (a list that holds every row of the store has left nothing out: no check)
     int *status = ws.status.as<int>();
     const bool tc = tier != kTierExact && flat_kernel_choice() == FlatKernel::TC;
@@ -880,7 +880,7 @@ int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const 
 
 // The whole search for one block of queries, all pointers on the device.
 // Flat: tier_hint = lowest tier to start from.  gated = false runs that one tier and leaves the
-// verdict of its band check in the status words for the host to act on; gated = true enqueues the
+// finding of its band check in the status words for the host to act on; gated = true enqueues the
 // higher tiers behind it, each running only if the tier before it flagged an overflow.
 // IVF: given_probes (may be null) = nq x nprobe list numbers on the device, best first, -1 = none; the
 // coarse quantiser is then skipped (the probes were chosen elsewhere, e.g. by another shard's GPU).
