@@ -1740,12 +1740,23 @@ FlatPlan make_flat_plan(int64_t nq, int64_t n, int k, int sms) {
 }
 
 FlatPlan make_flat_plan_screened(int64_t nq, int64_t n, int k, int sms) {
-    FlatPlan p = make_flat_plan(nq, n, k, sms);
-    // lists of up to kScreenMaxList entries, kept by the append selection
-    p.list_stride = kBuf;
-    p.lists_sorted = true;
-    p.part_entries = (size_t)p.nq_tiles * p.lists_per_qt * BM * (size_t)p.list_stride;
-    choose_static(p, n, sms, true);
+    auto screened_plan = [&](int64_t nq_planned) {
+        FlatPlan p = make_flat_plan(nq_planned, n, k, sms);
+        // lists of up to kScreenMaxList entries, kept by the append selection
+        p.list_stride = kBuf;
+        p.lists_sorted = true;
+        p.part_entries = (size_t)p.nq_tiles * p.lists_per_qt * BM * (size_t)p.list_stride;
+        choose_static(p, n, sms, true);
+        return p;
+    };
+    FlatPlan p = screened_plan(nq);
+    // An odd number of query tiles has no pair mode.  With eleven tiles or more, one more tile that holds no
+    // query (its rows are never looked at, its lists stay empty) costs less than pair mode gains: the plan is
+    // made for the even count; the kernel's callers size their per-tile memory by plan.nq_tiles.
+    if (p.static_g && !p.pair && p.nq_tiles % 2 == 1 && p.nq_tiles >= 11) {
+        const FlatPlan padded = screened_plan((int64_t)(p.nq_tiles + 1) * BM);
+        if (padded.pair) return padded;
+    }
     return p;
 }
 
@@ -1788,7 +1799,7 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     // (16-bit build: there is no lo plane of the rows; the fourth map repeats the third)
     // The query planes are allocated in whole tiles of 128 rows (the rows past nq hold anything: their
     // accumulator rows are never looked at), so no query load ever reaches past the end of its tensor.
-    const int64_t nq_rows = grouped ? nq : (nq + BM - 1) / BM * BM;
+    const int64_t nq_rows = grouped ? nq : (int64_t)plan.nq_tiles * BM;
     if (make_map(&maps[0], qhi, nq_rows, dp, BM, bf16) || make_map(&maps[1], qlo ? qlo : qhi, nq_rows, dp, BM, bf16) ||
         make_map(&maps[2], xhi, n, dp, BN, bf16) || make_map(&maps[3], (kH16 || !xlo) ? xhi : xlo, n, dp, BN, bf16))
         return -1;

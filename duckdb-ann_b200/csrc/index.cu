@@ -391,7 +391,8 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
                      int k, cudaStream_t stream, const TopkOpts &o = TopkOpts()) {
     const int dp = st.dp, d = ix.d;
     const size_t k_buf = (size_t)std::max(k, o.wide_out);
-    const size_t nq_rows = (size_t)(nq + 127) / 128 * 128;  // the kernel loads the query planes in whole tiles
+    // the kernel loads the query planes in whole tiles (one more when it pairs up an odd number of tiles)
+    const size_t nq_rows = ((size_t)(nq + 127) / 128 + 1) * 128;
     if (ws.qhi.ensure(nq_rows * dp * 4) || ws.qlo.ensure(nq_rows * dp * 4) || ws.qn.ensure((size_t)nq * 4) ||
         ws.sel_key.ensure((size_t)nq * k_buf * 4) || ws.sel_idx.ensure((size_t)nq * k_buf * 4) || ws_status_ready(ws))
         return -1;

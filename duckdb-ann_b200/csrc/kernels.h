@@ -93,7 +93,8 @@ int launch_flat_scratch_init(uint32_t *qtau, size_t qtau_words, int *sched, size
 
 // Fused split-TF32 GEMM + k-selection on the tensor cores.  Inputs are hi/lo row
 // stores of the database (n x dp) and the queries (nq x dp, in buffers that hold whole tiles of 128
-// rows: ceil(nq / 128) * 128 x dp elements each, the rows past nq unspecified), plus row norms for L2.
+// rows: plan.nq_tiles * 128 x dp elements each - plan.nq_tiles may be one more than ceil(nq / 128) - the
+// rows past nq unspecified), plus row norms for L2.
 // Writes 128 unsorted lists of k (key, local row) pairs per list slot
 // (slot = query tile * lists_per_qt + j, j < sched[nq_tiles + query tile]).
 // Flat search with the append selection (FlatPlan::lists_sorted) and flat_part_cnt given: a list

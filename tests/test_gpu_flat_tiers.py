@@ -225,6 +225,26 @@ def test_a_wait_that_runs_out_fails_the_search_and_leaves_the_device_usable(pkg,
         lib.ann_cuda_set_flat_kernel(b"tcgen05")
 
 
+@pytest.mark.parametrize("nq", [11 * 128 - 5, 13 * 128, 9 * 128 + 1])
+def test_an_odd_number_of_query_tiles(pkg, oracle, nq):
+    """The kernel that runs as clusters of two CTAs gives each CTA of a pair one query tile.  Eleven or thirteen
+    tiles are planned as twelve or fourteen, the last one holding no query; nine tiles (and a ragged tenth) stay
+    as they are.  Every query must come back with the oracle's answer either way."""
+    rng = np.random.default_rng(41)
+    xb = rng.uniform(-1, 1, (200_000, 32)).astype(np.float32)
+    xq = rng.uniform(-1, 1, (nq, 32)).astype(np.float32)
+    assert pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05-screened") == 0
+    try:
+        idx = pkg.CudaIndexFlat(32, pkg.METRIC_INNER_PRODUCT)
+        idx.add(xb)
+        D, I = idx.search(xq, 30)
+        Dref, Iref = oracle.flat_search(xb, xq, 30, oracle.METRIC_IP)
+        assert_topk_matches(oracle, xb, xq, oracle.METRIC_IP, D, I, Dref, Iref, f"{nq} queries")
+        idx.close()
+    finally:
+        pkg.lib().ann_cuda_set_flat_kernel(b"tcgen05")
+
+
 @pytest.mark.parametrize("flat_kernel", ["tcgen05-screened", "tcgen05-split"])
 def test_every_repetition_gives_the_oracle_answer(pkg, oracle, flat_kernel):
     """Thresholds travel between CTAs through memory, so WHICH rows reach the candidate lists depends on
