@@ -350,7 +350,12 @@ class FlatWorkload:
                 "peak_note": f"{peaks['_source']} bf16 sustained {peaks['bf16_tflops_sustained']} TFLOP/s / 2 (TF32 rate)"
                              + (" (screened search: one TF32 MMA per product)" if screened else
                                 " / 3 (split-TF32 issues three MMAs per product)")
-                             + "; 'achieved' counts 2*Q*N*d once"}
+                             + "; 'achieved' counts 2*Q*N*d once; the denominator is a library GEMM under the board's "
+                               "power cap, not a hardware limit: a kernel that moves fewer bytes per flop through shared "
+                               "memory (pair mode) can exceed it",
+                # cuBLAS's own TF32 GEMM on this pool (8192^3 through torch.matmul, CUDA events): the same kind of
+                # figure as the bf16 peaks, measured directly for this operand type
+                "cublas_tf32_tflops": {"burst": 753.5, "sustained": 636.1, "source": "profiles/tf32_peak.md"}}
 
     def parity_check(self, torch, dist, D, I, oracle):
         """Size-independent properties over the whole output (sorted best first, labels valid and
