@@ -133,6 +133,7 @@ constexpr int kMaxStages = 2 * kStages;
 // tile, so a K block costs a CTA kABytes + kBBytes / 2 of operand traffic instead of kABytes +
 // kBBytes, and the ring holds more, smaller stages.
 constexpr int kPairStages = 6;
+constexpr int kPairStagesSplit2 = 4;  // 16-bit build, both parts of the queries staged: 48 KB per stage
 constexpr int kBarStages = kMaxStages > kPairStages ? kMaxStages : kPairStages;
 constexpr int kRowBytes = BK * kElemBytes;
 constexpr bool kWideRows = kRowBytes == 128;                // the builds that have the pair mode
@@ -143,6 +144,7 @@ constexpr int kBBytes = BN * kRowBytes;                 // 32 KB
 constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;  // hi + lo of both operands: 96 KB
 constexpr int kPairStageBytes = kABytes + kBBytes / 2;  // pair mode: own queries + half of the row tile
 static_assert(kPairStages * kPairStageBytes <= kStages * kStageBytes, "the pair ring fits into the stage memory");
+static_assert(kPairStagesSplit2 * (kPairStageBytes + kABytes) <= kStages * kStageBytes, "and so does the two-part one");
 constexpr int kQueueDepth = kSmemListMax;   // per-row candidate queue, also the small-k list capacity
 constexpr int kThreads = 192;
 // Launches whose rows come as one plain fp32 plane (KernelArgs::derive_lo) add two converter warps
@@ -461,6 +463,7 @@ struct KernelArgs {
     int pair;             // launched as clusters of two CTAs that share row tiles (screened, static schedule)
     int bf16;             // 16-bit build: operands are bf16 (else fp16)
     int derive_lo;        // rows come as one plain fp32 plane; converter warps split them in shared memory
+    int split2;           // 16-bit build, pair mode: both 16-bit parts of the queries (q_hi.x + q_lo.x)
 #ifdef ANN_CUDA_MEASURE
     unsigned long long *stats;  // see kStat* below
     int debug;  // bit 0 = epilogue skips selection, bit 1 = MMA issuer skips the MMAs, bit 2 = no appends, bit 3 = consume only
@@ -867,7 +870,9 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
     const uint32_t bar_full = smem_base + SmemLayout::barriers;
     const uint32_t bar_empty = bar_full + 8 * kBarStages;
     const uint32_t bar_tfull = bar_empty + 8 * kBarStages;
-    const uint32_t nstages = PAIR ? kPairStages : args.screen ? kMaxStages : kStages;
+    // (pair mode with both 16-bit parts of the queries staged, split2: stages of A_hi, A_lo and half a row tile)
+    const uint32_t pair_stage_bytes = args.split2 ? kPairStageBytes + kABytes : kPairStageBytes;
+    const uint32_t nstages = PAIR ? (args.split2 ? kPairStagesSplit2 : kPairStages) : args.screen ? kMaxStages : kStages;
     // pair mode: rank of this CTA in its cluster of two; rank 0 (the leader) issues the MMAs of both
     const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
     const bool leader = crank == 0;
@@ -1078,12 +1083,13 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         if (PAIR) {
                             // own queries + this CTA's half of the row tile; the bytes of both CTAs are
                             // counted on the LEADER's barrier, which its MMA issuer waits on
-                            const uint32_t base = smem_base + stage * kPairStageBytes;
+                            const uint32_t base = smem_base + stage * pair_stage_bytes;
                             const uint32_t full_leader = map_to_cta(full, 0);
-                            if (leader) mbar_expect_tx(full, 2 * kPairStageBytes);
+                            if (leader) mbar_expect_tx(full, 2 * pair_stage_bytes);
                             tma_load_2d_pair(base, &map_qhi, kb * BK, cur * BM, full_leader);
-                            tma_load_2d_pair(base + kABytes, &map_xlo, kb * BK, (int32_t)trow + (int32_t)crank * (BN / 2),
-                                             full_leader);
+                            if (args.split2) tma_load_2d_pair(base + kABytes, &map_qlo, kb * BK, cur * BM, full_leader);
+                            tma_load_2d_pair(base + (args.split2 ? 2 : 1) * kABytes, &map_xlo, kb * BK,
+                                             (int32_t)trow + (int32_t)crank * (BN / 2), full_leader);
                         } else if (args.screen) {  // hi planes only, into plane set stage & 1 of stage >> 1
                             const uint32_t base = smem_base + (stage >> 1) * kStageBytes;
                             mbar_expect_tx(full, kABytes + kBBytes);
@@ -1143,10 +1149,18 @@ flat_tc_kernel(const __grid_constant__ CUtensorMap map_qhi, const __grid_constan
                         if (kstats(args)) atomicAdd(kstats(args) + kStatMmaWaitSmem, (unsigned long long)(clock64() - t0));
                         tmem_fence_after();
                         if (PAIR) {
-                            const uint32_t base = smem_base + stage * kPairStageBytes;
+                            const uint32_t base = smem_base + stage * pair_stage_bytes;
                             const uint64_t a0 = make_smem_desc(base);
-                            const uint64_t b0 = make_smem_desc(base + kABytes);
-                            if (!(kdebug(args) & 2)) {
+                            const uint64_t b0 = make_smem_desc(base + (args.split2 ? 2 : 1) * kABytes);
+                            if (args.split2) {
+                                // 16-bit rows are exact: the query alone is split, q = q_hi + q_lo
+                                const uint64_t a1 = make_smem_desc(base + kABytes);
+#pragma unroll
+                                for (int ks = 0; ks < BK / kMmaK; ks++) {
+                                    mma_issue_pair(tmem_d, a1 + 2 * ks, b0 + 2 * ks, (kb | ks) != 0, fmt);
+                                    mma_issue_pair(tmem_d, a0 + 2 * ks, b0 + 2 * ks, 1, fmt);
+                                }
+                            } else if (!(kdebug(args) & 2)) {
                                 mma_issue_pair(tmem_d, a0, b0, kb != 0, fmt);
 #pragma unroll
                                 for (int ks = 1; ks < BK / kMmaK; ks++) mma_issue_pair(tmem_d, a0 + 2 * ks, b0 + 2 * ks, 1, fmt);
@@ -1837,9 +1851,13 @@ int ANN_TC_LAUNCH(const FlatPlan &plan, const float *xhi, const float *xlo, cons
     a.screen = use_screen ? 1 : 0;
     a.banded = use_band ? 1 : 0;
     // the static schedule parks and resumes append buffers; it pays for the screened search only
-    a.static_g = use_screen ? plan.static_g : 0;
+    // (16-bit build: the two-part product of banded lists takes it too, in pair mode)
+    const bool two_part = kH16 && use_band && !use_screen;
+    a.static_g = (use_screen || two_part) ? plan.static_g : 0;
     // pair mode: the fourth map becomes the hi plane of the rows in boxes of HALF a tile
     a.pair = (a.static_g && plan.pair && kWideRows && plan.grid % 2 == 0 && pair_clusters_fit(plan.grid)) ? 1 : 0;
+    a.split2 = (two_part && a.pair) ? 1 : 0;
+    if (two_part && !a.pair) a.static_g = 0;  // (the one-CTA static path stages hi planes only)
     if (a.pair && make_map(&maps[3], xhi, n, dp, BN / 2, bf16)) return -1;
     a.bf16 = bf16 ? 1 : 0;
     a.derive_lo = (grouped && grouped->derive_lo && !kH16) ? 1 : 0;

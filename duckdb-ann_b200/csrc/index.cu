@@ -411,8 +411,10 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
                  : launch_split_rows(x_dev, nq, d, dp, ws.qhi.as<float>(), ws.qlo.as<float>(), ws.qn.as<float>(), stream,
                                      st.center(), true)))
             return -1;
-        const FlatPlan plan = o.k_rank > 0 && o.one_mma ? make_flat_plan_screened(nq, st.n, k, sm_count(ix.device))
-                                                        : make_flat_plan(nq, st.n, k, sm_count(ix.device));
+        // (the static schedule and the pair mode serve the one-MMA tiers and, for 16-bit stores, the two-part tier)
+        const FlatPlan plan = o.k_rank > 0 && (o.one_mma || st.elem != kElemF32)
+                                  ? make_flat_plan_screened(nq, st.n, k, sm_count(ix.device))
+                                  : make_flat_plan(nq, st.n, k, sm_count(ix.device));
         const ScreenInput screen{o.k_rank, ws.qn.as<float>(), st.max_norm2, d, o.one_mma, st.elem};
         const size_t qtau_bytes = (size_t)plan.nq_tiles * 128 * 4, sched_bytes = plan.sched_ints * 4;
         if (ws.part_key.ensure(plan.part_entries * 4) || ws.part_idx.ensure(plan.part_entries * 4) ||
