@@ -154,6 +154,9 @@ struct Workspace {
     GrowBuf over_q;
     GrowBuf bad_q;  // 16-bit stores: queries that overflow the type (set when the queries are split)
     GrowBuf complete_to;  // per query: key below which the merged candidates of several replace-max lists are complete
+    // Exact tier, threshold scan of the flagged queries: the compacted list of them, each one's place in it, the
+    // fill of its candidate buffer, the buffers, and the queries left for the item scan
+    GrowBuf flag_aux, flag_rank, flag_counts, cand_key, cand_idx, left_q;
     bool over_q_valid = false;  // a tensor-core tier of the current block search has (been enqueued to) set them
     // Status words (device: `status`, pinned host copy: `status_host`), kStatusWords ints:
     //   [0]      first give-up code of a bounded wait inside a kernel; sticky for one API call
@@ -169,7 +172,8 @@ struct Workspace {
         if (ev1) cudaEventDestroy(ev1);
         for (GrowBuf *b : {&x, &qhi, &qlo, &qn, &part_key, &part_idx, &sel_key, &sel_idx, &status, &out_d, &out_i,
                            &item_q, &item_rb, &item_re, &item_slot, &scratch, &probes_key, &probes, &qtau, &sched, &gq, &items,
-                           &qconst, &part_cnt, &over_q, &bad_q, &complete_to})
+                           &qconst, &part_cnt, &over_q, &bad_q, &complete_to, &flag_aux, &flag_rank, &flag_counts, &cand_key,
+                           &cand_idx, &left_q})
             b->release();
         if (status_host) cudaFreeHost(status_host);
         if (own_stream) cudaStreamDestroy(own_stream);
@@ -379,6 +383,11 @@ struct TopkOpts {
     bool chained = false;
     // exact tier: repair only the queries whose word in ws.over_q is set (the others keep their results)
     bool flagged_only = false;
+    // with flagged_only: what the tier before left for every query of the block (prev_k per query, user-facing
+    // distances and labels) - its k-th distance bounds the true one
+    const float *prev_d = nullptr;
+    const int64_t *prev_i = nullptr;
+    int prev_k = 0;
     // replace-max lists (k beyond the append lists): the merge may hand on more candidates than one list is
     // long - up to this many - with the bound below which they are complete in ws.complete_to; *wide_used
     // receives the number of candidates per query that came out (k if the selection has no such lists)
@@ -503,8 +512,35 @@ int split_store_topk(const ann_cuda_index &ix, const SplitStore &st, Workspace &
     if (ws.item_q.ensure(n_items * 4) || ws.item_rb.ensure(n_items * 8) || ws.item_re.ensure(n_items * 8) ||
         ws.part_key.ensure((size_t)n_items * k * 4) || ws.part_idx.ensure((size_t)n_items * k * 4))
         return -1;
-    if (launch_fill_chunk_items(ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(), ws.item_re.as<int64_t>(), nq, chunks, per,
-                                st.n, stream, only_q))
+    // Flagged queries first get one pass over the store that keeps the rows at or below the k-th distance
+    // the tier before found (work cut by rows: a single hard query is scanned by the whole device); the item
+    // scan below then runs for the queries that pass could not settle - normally none.
+    bool items_laid_out = false;
+    if (o.flagged_only && o.prev_d && o.prev_i && st.max_norm2 && st.n <= (int64_t)0x7fffffff &&
+        scan_flagged_group(dp) > 0) {
+        const int lists = std::max(2, kFlaggedCandidates / k);
+        const int cap = lists * k;
+        const int r_max = (int)std::max<int64_t>(1, std::min<int64_t>(nq, kFlaggedEntries / cap));
+        if (cap <= kMergeCandidates) {
+            if (ws.flag_aux.ensure((size_t)(nq + 1) * 4) || ws.flag_rank.ensure((size_t)nq * 4) ||
+                ws.flag_counts.ensure((size_t)r_max * 4) || ws.left_q.ensure((size_t)nq * 4) ||
+                ws.cand_key.ensure((size_t)r_max * cap * 4) || ws.cand_idx.ensure((size_t)r_max * cap * 4))
+                return -1;
+            if (launch_scan_flagged(st.hi, st.lo, dp, d, st.n, x_dev, d, only_q, nq, ws.flag_aux.as<int>(),
+                                    ws.flag_rank.as<int32_t>(), ws.flag_counts.as<int>(), r_max, cap, o.prev_k,
+                                    (int)std::min<int64_t>(o.prev_k, st.n) - 1, o.prev_d, o.prev_i, st.max_norm2, ix.metric,
+                                    ws.cand_key.as<float>(), ws.cand_idx.as<int32_t>(), ix.device, stream, o.gate, st.elem) ||
+                launch_select_flagged(ws.cand_key.as<float>(), ws.cand_idx.as<int32_t>(), ws.flag_counts.as<int>(),
+                                      ws.flag_rank.as<int32_t>(), only_q, r_max, cap, nq, k, ws.sel_key.as<float>(),
+                                      ws.sel_idx.as<int32_t>(), ws.left_q.as<int32_t>(), ws.item_q.as<int32_t>(),
+                                      ws.item_rb.as<int64_t>(), ws.item_re.as<int64_t>(), chunks, per, st.n, stream, o.gate))
+                return -1;
+            only_q = ws.left_q.as<int32_t>();
+            items_laid_out = true;  // (by the kernel that decided which queries are left)
+        }
+    }
+    if (!items_laid_out && launch_fill_chunk_items(ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(), ws.item_re.as<int64_t>(),
+                                                   nq, chunks, per, st.n, stream, only_q))
         return -1;
     if (launch_scan_items(st.hi, st.lo, dp, d, x_dev, d, ws.item_q.as<int32_t>(), ws.item_rb.as<int64_t>(),
                           ws.item_re.as<int64_t>(), n_items, k, ix.metric, ws.part_key.as<float>(),
@@ -839,6 +875,11 @@ int flat_tier_search(const ann_cuda_index &ix, Workspace &ws, int64_t nq, const 
         o.exact = true;
         // behind a tensor-core tier of the same block search: only the queries that tier flagged
         o.flagged_only = ws.over_q_valid;
+        if (o.flagged_only) {
+            o.prev_d = d_dev;
+            o.prev_i = i_dev;
+            o.prev_k = (int)k;
+        }
     } else if (banded) {
         k_list = (int)std::min<int64_t>((int64_t)kScreenMaxList, n);
         o.k_rank = o.check_rank = k_sel;

@@ -61,6 +61,10 @@ int launch_split_rows_h16(const float *x, int64_t n, int d, int dp, void *hi, vo
 constexpr int kSmemListMax = 16;         // lists up to this length are kept in shared memory
 constexpr int kAppendMaxK = 256;         // largest k the append-and-compact selection handles
 constexpr int kMergeCandidates = 16384;  // most (list, slot) candidates per query the merge kernel sorts
+// Threshold scan of the exact tier: entries of one flagged query's candidate buffer (at least two k), and
+// of all buffers of a query block together (8 bytes each)
+constexpr int kFlaggedCandidates = 4096;
+constexpr int64_t kFlaggedEntries = 4 << 20;
 
 struct FlatPlan {
     int nq_tiles = 0;         // ceil(nq / 128)
@@ -221,6 +225,26 @@ int launch_scan_items(const float *x, const float *xlo, int dp, int d, const flo
 constexpr int32_t kItemSkip = -2;
 int launch_fill_chunk_items(int32_t *item_query, int64_t *range_begin, int64_t *range_end, int64_t nq, int chunks,
                             int64_t per, int64_t n, cudaStream_t stream, const int32_t *only_q = nullptr);
+
+// Exact tier behind a tensor-core tier, for the queries flagged in over_q (one word per query): the k-th
+// distance that tier left in out_d / out_i (k_out per query, the k-th at k_last) bounds the true k-th, so one
+// pass over the store appends every row at or below it (plus the rounding of two fp32 sums) to the query's
+// candidate buffer (cap entries at cand_*[rank * cap], rank = the query's place among the flagged ones, the
+// first r_max of them get a buffer).  Work is cut by rows, so one flagged query occupies the whole device, and
+// a row is read once for 16 queries (8 when the dimension leaves no room for more).  Scratch: aux (1 + nq ints), rank_of (nq), counts (r_max).
+// launch_select_flagged then sorts each buffer and writes the k best of it; left_q[q] = 1 for the flagged
+// queries it could not settle (buffer overflowed, no buffer, bound not usable), which the item scan takes;
+// the same kernel lays out that scan's items (as launch_fill_chunk_items would, with only_q = left_q).
+int scan_flagged_group(int dp);  // queries per group: 16 or 8 by shared memory; 0: the dimension is too large
+int launch_scan_flagged(const float *x, const float *xlo, int dp, int d, int64_t n, const float *queries, int q_stride,
+                        const int32_t *over_q, int64_t nq, int *aux, int32_t *rank_of, int *counts, int r_max, int cap,
+                        int k_out, int k_last, const float *out_d, const int64_t *out_i, const unsigned *x_max_norm2,
+                        int metric, float *cand_key, int32_t *cand_idx, int device, cudaStream_t stream, const int *gate,
+                        int elem);
+int launch_select_flagged(const float *cand_key, const int32_t *cand_idx, const int *counts, const int32_t *rank_of,
+                          const int32_t *over_q, int r_max, int cap, int64_t nq, int k, float *out_key, int32_t *out_idx,
+                          int32_t *left_q, int32_t *item_query, int64_t *range_begin, int64_t *range_end, int chunks,
+                          int64_t per, int64_t n, cudaStream_t stream, const int *gate);
 
 // Builds the (query, list) items of an IVF search from the coarse result:
 // probes (nq x nprobe) int32 list numbers (-1 = none); items are grouped by list so

@@ -121,6 +121,48 @@ merge_parts_kernel(const float *__restrict__ part_key, const int32_t *__restrict
     }
 }
 
+// The k best of a flagged query's candidate buffer (the rows the threshold scan appended, in no order),
+// sorted best first.  left_q[q] says whether the query still needs the item scan: its buffer overflowed,
+// it got no buffer, or the bound let fewer than k rows through (it was no bound at all).  The block also
+// lays out the query's items for that scan (query q against rows [c * per, (c + 1) * per) for each of
+// `chunks` chunks; "skip" unless the query is left).
+__global__ void __launch_bounds__(kMergeThreads)
+select_flagged_kernel(const float *__restrict__ cand_key, const int32_t *__restrict__ cand_idx,
+                      const int *__restrict__ counts, const int32_t *__restrict__ rank_of,
+                      const int32_t *__restrict__ over_q, int r_max, int cap, int k, float *__restrict__ out_key,
+                      int32_t *__restrict__ out_idx, int32_t *__restrict__ left_q, int32_t *__restrict__ item_query,
+                      int64_t *__restrict__ range_begin, int64_t *__restrict__ range_end, int chunks, int64_t per,
+                      int64_t n, const int *gate) {
+    extern __shared__ float smem_f[];
+    if (gate_closed(gate)) return;
+    const int64_t q = blockIdx.x;
+    const bool flagged = over_q[q] != 0;
+    const int r = flagged ? rank_of[q] : -1;
+    const int cnt = (r >= 0 && r < r_max) ? counts[r] : -1;
+    const bool left = flagged && (cnt < k || cnt > cap);
+    if (threadIdx.x == 0) left_q[q] = left ? 1 : 0;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        const int64_t i = q * chunks + c;
+        item_query[i] = left ? (int32_t)q : kItemSkip;
+        range_begin[i] = c * per;
+        range_end[i] = (c + 1) * per < n ? (c + 1) * per : n;
+    }
+    if (!flagged || left) return;
+    int P = 2;
+    while (P < cnt) P <<= 1;
+    float *keys = smem_f;
+    int32_t *vals = reinterpret_cast<int32_t *>(smem_f + P);
+    for (int t = threadIdx.x; t < P; t += blockDim.x) {
+        keys[t] = t < cnt ? cand_key[(int64_t)r * cap + t] : kInf;
+        vals[t] = t < cnt ? cand_idx[(int64_t)r * cap + t] : 0x7fffffff;
+    }
+    bitonic_sort(keys, vals, P);
+    for (int j = threadIdx.x; j < k; j += blockDim.x) {
+        out_key[q * k + j] = keys[j];
+        out_idx[q * k + j] = vals[j];
+    }
+}
+
 // (key, val) order used by every merge here: smaller key first, ties by smaller val
 __device__ __forceinline__ bool pair_after(float a, int32_t va, float b, int32_t vb) {
     return (a > b) || (a == b && va > vb);
@@ -553,6 +595,22 @@ int launch_merge_parts(const float *part_key, const int32_t *part_idx, int layou
     merge_parts_kernel<<<(unsigned)nq, kMergeThreads, smem, stream>>>(part_key, part_idx, layout, lists_started, slot_of,
                                                                       nparts, nq, k, list_stride, P, slot_key_offset, out_key,
                                                                       out_idx, gate, only_q, k_out, complete_to);
+    count_launch();
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int launch_select_flagged(const float *cand_key, const int32_t *cand_idx, const int *counts, const int32_t *rank_of,
+                          const int32_t *over_q, int r_max, int cap, int64_t nq, int k, float *out_key, int32_t *out_idx,
+                          int32_t *left_q, int32_t *item_query, int64_t *range_begin, int64_t *range_end, int chunks,
+                          int64_t per, int64_t n, cudaStream_t stream, const int *gate) {
+    if (nq <= 0) return 0;
+    if (cap > kMaxCandidates || k > cap) return set_error("select: %d candidates per query exceeds %d", cap, kMaxCandidates);
+    const size_t smem = (size_t)next_pow2(cap < 2 ? 2 : cap) * 8;
+    if (opt_in_smem(select_flagged_kernel, smem)) return -1;
+    select_flagged_kernel<<<(unsigned)nq, kMergeThreads, smem, stream>>>(cand_key, cand_idx, counts, rank_of, over_q, r_max,
+                                                                         cap, k, out_key, out_idx, left_q, item_query,
+                                                                         range_begin, range_end, chunks, per, n, gate);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;

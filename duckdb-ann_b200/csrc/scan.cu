@@ -16,6 +16,8 @@
 #include "kernels.h"
 #include "select.cuh"
 
+#include <algorithm>
+
 namespace anncuda {
 namespace {
 
@@ -134,6 +136,204 @@ scan_items_kernel(const float *__restrict__ x, const float *__restrict__ xlo, in
             }
         }
         list.store(lk, k, lane);
+    }
+}
+
+// ---- threshold scan of the flagged queries ---------------------------------------------------
+// The exact tier behind a tensor-core tier: that tier has already left k real rows with their exact
+// distances in the output arrays of every query, flagged or not, so the k-th of them bounds the true
+// k-th distance from above.  The flagged queries are compacted into a list, and one CTA takes one
+// (row tile, group of QB flagged queries) item: the group's queries sit in shared memory, the warps
+// share out the tile's rows (RB = 32 / QB rows at a time each), every lane accumulates its slice of the
+// RB x QB dot products, a transposing butterfly (31 shuffles for 32 sums) leaves each lane with one
+// finished (row, query) distance, and the lane appends the row to the query's candidate buffer if the
+// distance is at or below the query's bound.  The parallelism comes from the rows, so a single flagged
+// query is scanned by the whole device, and a row is read once for QB queries.  A query whose buffer
+// overflows (more rows inside the bound than the buffer holds: duplicates by the thousand) or whose
+// bound is not usable is left to the item scan above.
+constexpr int kFilterTile = 256;  // rows of one work item
+
+__device__ __forceinline__ float4 ld_row_any(const float *__restrict__ x, const float *__restrict__ xlo, int64_t off,
+                                             int elem) {
+    float4 v;
+    if (elem != kElemF32) {  // 16-bit rows: four elements are eight bytes
+        const uint2 b = __ldg(reinterpret_cast<const uint2 *>(x) + off);
+        v.x = h16_to_float((uint16_t)(b.x & 0xffffu), elem);
+        v.y = h16_to_float((uint16_t)(b.x >> 16), elem);
+        v.z = h16_to_float((uint16_t)(b.y & 0xffffu), elem);
+        v.w = h16_to_float((uint16_t)(b.y >> 16), elem);
+        return v;
+    }
+    v = __ldg(reinterpret_cast<const float4 *>(x) + off);
+    if (xlo) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(xlo) + off);
+        v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+    }
+    return v;
+}
+
+// Sums v[i] over the warp for all 32 i at once: lane l returns the total of v[l].
+__device__ __forceinline__ float transpose_sum32(float (&v)[32], int lane) {
+#pragma unroll
+    for (int half = 16; half >= 1; half >>= 1) {
+        const bool upper = (lane & half) != 0;
+#pragma unroll
+        for (int i = 0; i < half; i++) {
+            const float send = upper ? v[i] : v[i + half];
+            const float keep = upper ? v[i + half] : v[i];
+            v[i] = keep + __shfl_xor_sync(kFullMask, send, half);
+        }
+    }
+    return v[0];
+}
+
+// aux[0] = number of flagged queries, aux[1 + r] = the r-th of them; rank_of[q] = r or -1;
+// counts[r] = 0 for the ranks that get a candidate buffer.
+__global__ void __launch_bounds__(1024)
+compact_flagged_kernel(const int32_t *__restrict__ over_q, int64_t nq, int *__restrict__ aux,
+                       int32_t *__restrict__ rank_of, int *__restrict__ counts, int r_max, const int *gate) {
+    __shared__ int warp_tot[32];
+    __shared__ int base_s;
+    if (gate && *gate != kScreenOverflow) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) base_s = 0;
+    __syncthreads();
+    for (int64_t start = 0; start < nq; start += 1024) {
+        const int64_t i = start + tid;
+        const bool f = i < nq && over_q[i] != 0;
+        const unsigned b = __ballot_sync(kFullMask, f);
+        if (lane == 0) warp_tot[warp] = __popc(b);
+        __syncthreads();
+        int off = base_s;
+        for (int w = 0; w < warp; w++) off += warp_tot[w];
+        off += __popc(b & ((1u << lane) - 1u));
+        if (i < nq) rank_of[i] = f ? off : -1;
+        if (f) {
+            aux[1 + off] = (int)i;
+            if (off < r_max) counts[off] = 0;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int t = 0;
+            for (int w = 0; w < 32; w++) t += warp_tot[w];
+            base_s += t;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) aux[0] = base_s;
+}
+
+template <int QB>
+__global__ void __launch_bounds__(kWarps * 32, 3)
+scan_flagged_kernel(const float *__restrict__ x, const float *__restrict__ xlo, int dp, int d, int64_t n,
+                    const float *__restrict__ queries, int q_stride, const int *__restrict__ aux, int *counts, int r_max,
+                    int cap, int k_out, int k_last, const float *__restrict__ out_d, const int64_t *__restrict__ out_i,
+                    const unsigned *__restrict__ x_max_norm2, int metric, float *__restrict__ cand_key,
+                    int32_t *__restrict__ cand_idx, const int *gate, int elem) {
+    constexpr int RB = 32 / QB;  // rows a warp has in flight: RB x QB sums fill the butterfly
+    extern __shared__ float4 smem_q4[];
+    __shared__ float s_thr[QB];
+    __shared__ int s_rank[QB];
+    if (gate && *gate != kScreenOverflow) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float *sq = reinterpret_cast<float *>(smem_q4);
+    const bool l2 = metric != 0;
+    const int n4 = dp >> 2;
+    int nf = aux[0];
+    if (nf > r_max) nf = r_max;
+    if (nf <= 0) return;
+    const int n_groups = (nf + QB - 1) / QB;
+    const int64_t n_tiles = (n + kFilterTile - 1) / kFilterTile;
+    const int64_t n_items = n_tiles * n_groups;
+    // Both this scan and the re-ranking that left the bound sum d products in fp32, each within
+    // ~d 2^-24 of the exact value relative to the sum of the terms' magnitudes: twice that, doubled.
+    const float eps = 4.f * (float)(d + 4) * 5.9604645e-8f;
+    const float xm2 = __uint_as_float(*x_max_norm2);
+    const int my_r = lane / QB, my_qi = lane % QB;  // the (row, query) pair whose sum this lane ends up with
+    // (items of one tile are neighbours: CTAs that run together read the same rows)
+    for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const int64_t tile = item / n_groups;
+        const int g = (int)(item - tile * n_groups);
+        __syncthreads();  // the item before is done with the queries and bounds
+        for (int qi = warp; qi < QB; qi += kWarps) {
+            int r = g * QB + qi;
+            if (r >= nf || __ldcg(counts + r) > cap) r = -1;  // (a buffer that has overflowed is a lost cause)
+            const int q = r >= 0 ? aux[1 + r] : -1;
+            float qn = 0.f;
+            for (int c = lane; c < dp; c += 32) {
+                const float v = (q >= 0 && c < d) ? queries[(int64_t)q * q_stride + c] : 0.f;
+                sq[qi * dp + c] = v;
+                qn = fmaf(v, v, qn);
+            }
+            qn = warp_sum(qn);
+            float t = -kInf;  // nothing passes
+            if (q >= 0) {
+                const float dist = out_d[(int64_t)q * k_out + k_last];
+                const int64_t label = out_i[(int64_t)q * k_out + k_last];
+                const float key = l2 ? dist : -dist;
+                const float slack = l2 ? key * eps : eps * sqrtf(qn * xm2);
+                // no k-th row, or a distance that is no number: every row passes and the buffer overflows
+                t = (label >= 0 && key == key && fabsf(key) < kInf) ? key + slack : kInf;
+            }
+            if (lane == 0) {
+                s_rank[qi] = r;
+                s_thr[qi] = t;
+            }
+        }
+        __syncthreads();
+        const int rank = s_rank[my_qi];
+        const float thr = s_thr[my_qi];
+        const float4 *sq4 = reinterpret_cast<const float4 *>(sq);
+        const int64_t begin = tile * kFilterTile;
+        const int64_t end = begin + kFilterTile < n ? begin + kFilterTile : n;
+        for (int64_t row0 = begin + warp * RB; row0 < end; row0 += kWarps * RB) {
+            float acc[32];
+#pragma unroll
+            for (int i = 0; i < 32; i++) acc[i] = 0.f;
+            float4 xn[RB];
+#pragma unroll
+            for (int r = 0; r < RB; r++)
+                xn[r] = (row0 + r < end && lane < n4) ? ld_row_any(x, xlo, (row0 + r) * (int64_t)n4 + lane, elem)
+                                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c4 = lane; c4 < n4; c4 += 32) {
+                float4 xv[RB];
+#pragma unroll
+                for (int r = 0; r < RB; r++) {
+                    xv[r] = xn[r];
+                    if (c4 + 32 < n4 && row0 + r < end) xn[r] = ld_row_any(x, xlo, (row0 + r) * (int64_t)n4 + c4 + 32, elem);
+                }
+#pragma unroll
+                for (int qi = 0; qi < QB; qi++) {
+                    const float4 qv = sq4[qi * n4 + c4];
+#pragma unroll
+                    for (int r = 0; r < RB; r++) {
+                        float s = acc[r * QB + qi];
+                        if (l2) {
+                            const float a = qv.x - xv[r].x, b = qv.y - xv[r].y, c = qv.z - xv[r].z, e = qv.w - xv[r].w;
+                            s = fmaf(a, a, s);
+                            s = fmaf(b, b, s);
+                            s = fmaf(c, c, s);
+                            s = fmaf(e, e, s);
+                        } else {
+                            s = fmaf(qv.x, xv[r].x, s);
+                            s = fmaf(qv.y, xv[r].y, s);
+                            s = fmaf(qv.z, xv[r].z, s);
+                            s = fmaf(qv.w, xv[r].w, s);
+                        }
+                        acc[r * QB + qi] = s;
+                    }
+                }
+            }
+            const float sum = transpose_sum32(acc, lane);  // of pair (my_r, my_qi)
+            const float key = l2 ? sum : -sum;
+            if (row0 + my_r < end && rank >= 0 && key <= thr) {
+                const int pos = atomicAdd(counts + rank, 1);
+                if (pos < cap) {
+                    cand_key[(int64_t)rank * cap + pos] = key;
+                    cand_idx[(int64_t)rank * cap + pos] = (int32_t)(row0 + my_r);
+                }
+            }
+        }
     }
 }
 
@@ -300,7 +500,44 @@ int launch_scan_kr(const float *x, const float *xlo, int dp, int d, const float 
     return 0;
 }
 
+struct FlaggedScanArgs {
+    const float *x, *xlo;
+    int dp, d;
+    int64_t n;
+    const float *queries;
+    int q_stride;
+    const int *aux;
+    int *counts;
+    int r_max, cap, k_out, k_last;
+    const float *out_d;
+    const int64_t *out_i;
+    const unsigned *x_max_norm2;
+    int metric;
+    float *cand_key;
+    int32_t *cand_idx;
+    const int *gate;
+    int elem;
+};
+
+template <int QB>
+int launch_scan_flagged_qb(const FlaggedScanArgs &a, int64_t blocks, size_t smem, cudaStream_t stream) {
+    if (smem > 40 * 1024)  // (the kernel's static arrays count toward the 48 KB a launch gets unasked)
+        ANN_CUDA_TRY(cudaFuncSetAttribute(scan_flagged_kernel<QB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    scan_flagged_kernel<QB><<<(unsigned)blocks, kWarps * 32, smem, stream>>>(
+        a.x, a.xlo, a.dp, a.d, a.n, a.queries, a.q_stride, a.aux, a.counts, a.r_max, a.cap, a.k_out, a.k_last, a.out_d,
+        a.out_i, a.x_max_norm2, a.metric, a.cand_key, a.cand_idx, a.gate, a.elem);
+    count_launch();
+    ANN_CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
 }  // namespace
+
+int scan_flagged_group(int dp) {
+    for (int qb = 16; qb >= 8; qb >>= 1)
+        if ((size_t)qb * dp * sizeof(float) <= 200 * 1024) return qb;
+    return 0;
+}
 
 int launch_scan_items(const float *x, const float *xlo, int dp, int d, const float *queries, int q_stride,
                       const int32_t *item_query, const int64_t *range_begin, const int64_t *range_end,
@@ -320,6 +557,29 @@ int launch_scan_items(const float *x, const float *xlo, int dp, int d, const flo
                                   metric, part_key, part_idx, qtau, device, stream, gate, elem);
     return launch_scan_kr<64>(x, xlo, dp, d, queries, q_stride, item_query, range_begin, range_end, n_items, k, metric,
                               part_key, part_idx, qtau, device, stream, gate, elem);
+}
+
+int launch_scan_flagged(const float *x, const float *xlo, int dp, int d, int64_t n, const float *queries, int q_stride,
+                        const int32_t *over_q, int64_t nq, int *aux, int32_t *rank_of, int *counts, int r_max, int cap,
+                        int k_out, int k_last, const float *out_d, const int64_t *out_i, const unsigned *x_max_norm2,
+                        int metric, float *cand_key, int32_t *cand_idx, int device, cudaStream_t stream, const int *gate,
+                        int elem) {
+    if (nq <= 0 || n <= 0) return 0;
+    const int qb = scan_flagged_group(dp);
+    if (qb == 0) return set_error("dimension %d too large for the scan kernel", d);
+    compact_flagged_kernel<<<1, 1024, 0, stream>>>(over_q, nq, aux, rank_of, counts, r_max, gate);
+    count_launch();
+    ANN_CUDA_TRY(cudaGetLastError());
+    const size_t smem = (size_t)qb * dp * sizeof(float);
+    const int64_t n_tiles = (n + kFilterTile - 1) / kFilterTile;
+    const int64_t max_groups = (std::min<int64_t>(nq, r_max) + qb - 1) / qb;
+    int64_t blocks = n_tiles * max_groups;
+    const int64_t most = (int64_t)sm_count(device) * 3;  // three CTAs fit an SM
+    if (blocks > most) blocks = most;
+    const FlaggedScanArgs a{x, xlo, dp, d, n, queries, q_stride, aux, counts, r_max, cap, k_out, k_last, out_d, out_i,
+                            x_max_norm2, metric, cand_key, cand_idx, gate, elem};
+    if (qb == 16) return launch_scan_flagged_qb<16>(a, blocks, smem, stream);
+    return launch_scan_flagged_qb<8>(a, blocks, smem, stream);
 }
 
 int launch_fill_chunk_items(int32_t *item_query, int64_t *range_begin, int64_t *range_end, int64_t nq, int chunks,

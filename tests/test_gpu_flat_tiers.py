@@ -112,6 +112,79 @@ def test_the_exact_scan_repairs_the_flagged_queries_only(pkg, oracle, entry):
     idx.close()
 
 
+@pytest.mark.parametrize("storage_kind", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("metric_name", ["L2", "IP"])
+def test_many_flagged_queries_share_one_pass_over_the_store(pkg, oracle, metric_name, storage_kind):
+    """23 of 300 queries sit on the near ties (copies of the hard query, some moved by 1e-6): the exact
+    tier compacts them, scans the store once with the k-th distance of the tier before as the bound
+    (16 queries per row tile and CTA, the last group ragged) and sorts what passed; k below and above one list."""
+    import torch
+    rng = np.random.default_rng(41)
+    d = 64
+    xb, q0 = _near_tie_store(rng, d, 20000, 400, metric_name, 1e-6)
+    xq = rng.standard_normal((300, d)).astype(np.float32)
+    hard = rng.choice(300, 23, replace=False)
+    for j, h in enumerate(hard):
+        xq[h] = q0[0] + (1e-6 * rng.standard_normal(d) if j % 3 == 0 else 0.0)
+    storage = {"f32": pkg.STORAGE_F32, "f16": pkg.STORAGE_F16, "bf16": pkg.STORAGE_BF16}[storage_kind]
+    xr = xb if storage_kind == "f32" else oracle.round_storage(xb, storage_kind)
+    m, om = _metric(pkg, metric_name), (oracle.METRIC_L2 if metric_name == "L2" else oracle.METRIC_IP)
+    idx = pkg.CudaIndexFlat(d, m, 0, storage)
+    idx.add(xb)
+    before = pkg.lib().ann_cuda_screen_fallbacks()
+    for k in (8, 40, 300):
+        D, I = idx.search(xq, k)
+        Dref, Iref = oracle.flat_search(xr, xq, k, om)
+        assert_topk_matches(oracle, xr, xq, om, D, I, Dref, Iref, f"23 hard queries, {metric_name}, {storage_kind}, k={k}")
+        Dd, Id = idx.search_device(torch.from_numpy(xq).cuda(), k)
+        idx.search_status()
+        np.testing.assert_array_equal(Id.cpu().numpy(), I)
+        np.testing.assert_array_equal(Dd.cpu().numpy(), D)
+    assert pkg.lib().ann_cuda_screen_fallbacks() > before, "no tier flagged anything"
+    idx.close()
+
+
+@pytest.mark.parametrize("d", [768, 2000, 4000])
+def test_the_threshold_scan_at_larger_dimensions(pkg, oracle, d):
+    """Shared memory holds a group of 16 queries up to 3,200 floats each, of 8 beyond; at 768 floats the
+    group fills exactly the 48 KB a launch gets without asking for more."""
+    rng = np.random.default_rng(43)
+    xb, q0 = _near_tie_store(rng, d, 3000, 300, "L2", 1e-6)
+    xq = rng.standard_normal((9, d)).astype(np.float32)
+    xq[1] = xq[4] = xq[5] = xq[8] = q0[0]
+    idx = pkg.CudaIndexFlat(d, pkg.METRIC_L2)
+    idx.add(xb)
+    D, I = idx.search(xq, 20)
+    Dref, Iref = oracle.flat_search(xb, xq, 20, oracle.METRIC_L2)
+    assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D, I, Dref, Iref, f"near ties at d={d}")
+    idx.close()
+
+
+@pytest.mark.parametrize("metric_name", ["L2", "IP"])
+def test_duplicates_by_the_thousand_overflow_the_threshold_scan(pkg, oracle, metric_name):
+    """5,000 copies of one row next to the query: every one of them is at the k-th distance, more than a
+    candidate buffer holds, so the query is handed on to the scan that keeps k rows per item.  Any k of
+    the copies are a right answer (ties at the k-th place)."""
+    rng = np.random.default_rng(47)
+    d = 48
+    far = rng.standard_normal((12000, d)).astype(np.float32)
+    q = rng.standard_normal(d).astype(np.float32)
+    q /= np.linalg.norm(q)
+    # (inner product: Gaussian rows reach ~4 along the unit query, the copies 6)
+    row = (6.0 * q if metric_name == "IP" else q + 0.05 * rng.standard_normal(d)).astype(np.float32)
+    xb = np.concatenate([far, np.repeat(row[None, :], 5000, 0)])
+    xb = xb[np.random.default_rng(5).permutation(len(xb))]
+    xq = np.stack([q, rng.standard_normal(d).astype(np.float32), q]).astype(np.float32)
+    m, om = _metric(pkg, metric_name), (oracle.METRIC_L2 if metric_name == "L2" else oracle.METRIC_IP)
+    idx = pkg.CudaIndexFlat(d, m)
+    idx.add(xb)
+    for k in (10, 100):
+        D, I = idx.search(xq, k)
+        Dref, Iref = oracle.flat_search(xb, xq, k, om)
+        assert_topk_matches(oracle, xb, xq, om, D, I, Dref, Iref, f"5,000 duplicates, {metric_name}, k={k}")
+    idx.close()
+
+
 @pytest.mark.parametrize("entry", ["device", "async"])
 def test_fallback_passes_run_on_the_device_for_the_entries_that_do_not_wait(pkg, oracle, entry):
     """search_device and search_async return before anything has run: the higher tiers are enqueued
