@@ -12,6 +12,9 @@
 //     (faiss-metal/shaders/fused_l2_topk.metal:18,135) and used as an on-device
 //     cross-check of the tensor-core path.
 // Distances are the direct forms sum (q-x)^2 and sum q*x in fp32.
+//
+// Further down: the threshold scan of the flat search's exact tier (compact_flagged_kernel,
+// scan_flagged_kernel), which cuts the work by rows instead of by query.
 #include "common.cuh"
 #include "kernels.h"
 #include "select.cuh"
@@ -229,7 +232,7 @@ scan_flagged_kernel(const float *__restrict__ x, const float *__restrict__ xlo, 
                     const float *__restrict__ queries, int q_stride, const int *__restrict__ aux, int *counts, int r_max,
                     int cap, int k_out, int k_last, const float *__restrict__ out_d, const int64_t *__restrict__ out_i,
                     const unsigned *__restrict__ x_max_norm2, int metric, float *__restrict__ cand_key,
-                    int32_t *__restrict__ cand_idx, const int *gate, int elem) {
+                    int32_t *__restrict__ cand_idx, const int *gate, int elem, int round_tiles) {
     constexpr int RB = 32 / QB;  // rows a warp has in flight: RB x QB sums fill the butterfly
     extern __shared__ float4 smem_q4[];
     __shared__ float s_thr[QB];
@@ -250,10 +253,17 @@ scan_flagged_kernel(const float *__restrict__ x, const float *__restrict__ xlo, 
     const float eps = 4.f * (float)(d + 4) * 5.9604645e-8f;
     const float xm2 = __uint_as_float(*x_max_norm2);
     const int my_r = lane / QB, my_qi = lane % QB;  // the (row, query) pair whose sum this lane ends up with
-    // (items of one tile are neighbours: CTAs that run together read the same rows)
+    // Order of the items: the tiles go in rounds of round_tiles (a few dozen MB of rows); within a round every
+    // group takes all its tiles before the next group starts.  CTAs that run together are thus spread over
+    // many tiles (and L2 slices), and the later groups of a round find its rows in L2.
+    const int64_t round_items = (int64_t)round_tiles * n_groups;
     for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const int64_t tile = item / n_groups;
-        const int g = (int)(item - tile * n_groups);
+        const int64_t round = item / round_items;
+        const int64_t rem = item - round * round_items;
+        const int64_t first = round * round_tiles;
+        const int64_t tcount = n_tiles - first < round_tiles ? n_tiles - first : round_tiles;
+        const int g = (int)(rem / tcount);
+        const int64_t tile = first + (rem - g * tcount);
         __syncthreads();  // the item before is done with the queries and bounds
         for (int qi = warp; qi < QB; qi += kWarps) {
             int r = g * QB + qi;
@@ -517,6 +527,7 @@ struct FlaggedScanArgs {
     int32_t *cand_idx;
     const int *gate;
     int elem;
+    int round_tiles;
 };
 
 template <int QB>
@@ -525,7 +536,7 @@ int launch_scan_flagged_qb(const FlaggedScanArgs &a, int64_t blocks, size_t smem
         ANN_CUDA_TRY(cudaFuncSetAttribute(scan_flagged_kernel<QB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     scan_flagged_kernel<QB><<<(unsigned)blocks, kWarps * 32, smem, stream>>>(
         a.x, a.xlo, a.dp, a.d, a.n, a.queries, a.q_stride, a.aux, a.counts, a.r_max, a.cap, a.k_out, a.k_last, a.out_d,
-        a.out_i, a.x_max_norm2, a.metric, a.cand_key, a.cand_idx, a.gate, a.elem);
+        a.out_i, a.x_max_norm2, a.metric, a.cand_key, a.cand_idx, a.gate, a.elem, a.round_tiles);
     count_launch();
     ANN_CUDA_TRY(cudaGetLastError());
     return 0;
@@ -576,8 +587,11 @@ int launch_scan_flagged(const float *x, const float *xlo, int dp, int d, int64_t
     int64_t blocks = n_tiles * max_groups;
     const int64_t most = (int64_t)sm_count(device) * 3;  // three CTAs fit an SM
     if (blocks > most) blocks = most;
+    // a round of tiles: ~24 MB of rows, a fraction of L2
+    const int64_t tile_bytes = (int64_t)kFilterTile * dp * (elem != kElemF32 ? 2 : (xlo ? 8 : 4));
+    const int64_t round_tiles = std::max<int64_t>(4, std::min<int64_t>(512, (24ll << 20) / tile_bytes));
     const FlaggedScanArgs a{x, xlo, dp, d, n, queries, q_stride, aux, counts, r_max, cap, k_out, k_last, out_d, out_i,
-                            x_max_norm2, metric, cand_key, cand_idx, gate, elem};
+                            x_max_norm2, metric, cand_key, cand_idx, gate, elem, (int)round_tiles};
     if (qb == 16) return launch_scan_flagged_qb<16>(a, blocks, smem, stream);
     return launch_scan_flagged_qb<8>(a, blocks, smem, stream);
 }
