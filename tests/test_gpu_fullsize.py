@@ -4,7 +4,8 @@ These are the shapes the benchmark times: Flat L2 100,000 x 384 with 1,000 queri
 full; a flat inner-product store of 2.1 million unit-norm rows of 768 floats with k = 100, large
 enough that the library chooses one-MMA screening and the static schedule BY ITSELF (the
 sharded 20M-row configuration puts 2.5 million rows on each of 8 GPUs); the same for L2 with the
-store's mean far from the origin; one full aggregated batch of the DiskANN batch distance
+store's mean far from the origin; a million rows with planted groups of duplicates, which only the exact
+tier can answer; one full aggregated batch of the DiskANN batch distance
 (256 x 128 rows of 1536 floats) and of the SQ8 distance (1,024 x 128 rows of 384 codes).
 The oracle runs on a sample of the queries where the full set would take minutes."""
 import numpy as np
@@ -89,6 +90,49 @@ def test_screening_chosen_by_the_library_at_two_million_rows(pkg, oracle, kind, 
     D2, I2 = idx.search(xq[:200], k)
     np.testing.assert_array_equal(I2, I[:200])
     np.testing.assert_array_equal(D2, D[:200])
+    idx.close()
+
+
+@pytest.mark.parametrize("metric_name", ["L2", "IP"])
+def test_duplicate_groups_at_one_million_rows(pkg, oracle, metric_name):
+    """200 groups of 400 identical rows planted in a million: a query equal to a group's row has 400 neighbours
+    at one distance, more than a candidate list of the tensor-core tiers holds, so every tier's band check flags
+    it and the exact tier answers - for the 200 flagged queries among 600 only, with one threshold scan of the
+    store per 16 of them.  Size-independent properties over all queries (a flagged query gets ten members of its
+    own group, at distance exactly 0 for L2), the oracle on a sample."""
+    import torch
+    n, d, nq, k, groups, copies = 1_000_000, 256, 600, 10, 200, 400
+    m = pkg.METRIC_INNER_PRODUCT if metric_name == "IP" else pkg.METRIC_L2
+    g = torch.Generator(device="cuda").manual_seed(77)
+    x = torch.randn((n, d), generator=g, device="cuda", dtype=torch.float32)
+    member = torch.randperm(n, generator=g, device="cuda")[: groups * copies].view(groups, copies)
+    x[member.flatten()] = x[member[:, 0]].repeat_interleave(copies, 0)
+    idx = pkg.CudaIndexFlat(d, m)
+    idx.add_device(x)
+    q = torch.randn((nq, d), generator=g, device="cuda", dtype=torch.float32)
+    hard = torch.randperm(nq, generator=g, device="cuda")[:groups]
+    # (inner product: three times the row, so that nothing but the copies comes near |row|^2 * 3)
+    q[hard] = x[member[:, 0]] * (3.0 if metric_name == "IP" else 1.0)
+    before = pkg.lib().ann_cuda_screen_fallbacks()
+    Dd, Id = idx.search_device(q, k)
+    idx.search_status()
+    assert pkg.lib().ann_cuda_screen_fallbacks() > before, "no band check flagged the duplicates"
+    in_group = (Id[hard].unsqueeze(2) == member.unsqueeze(1)).any(2)
+    assert bool(in_group.all()), f"{int((~in_group).sum())} neighbours of flagged queries are outside their group"
+    if metric_name == "L2":
+        assert bool((Dd[hard] == 0).all())
+    xq = q.cpu().numpy()
+    D, I = idx.search(xq, k)                      # the host entry repeats tier by tier from the host
+    np.testing.assert_array_equal(Id.cpu().numpy(), I)
+    np.testing.assert_array_equal(Dd.cpu().numpy(), D)
+    xb = x.cpu().numpy()
+    del x
+    hs = hard.cpu().numpy()
+    sample = np.concatenate([hs[:12], np.setdiff1d(np.arange(nq), hs)[:12]])
+    om = oracle.METRIC_IP if metric_name == "IP" else oracle.METRIC_L2
+    Dref, Iref = oracle.flat_search(xb, xq[sample], k, om)
+    assert_topk_matches(oracle, xb, xq[sample], om, D[sample], I[sample], Dref, Iref,
+                        f"duplicate groups, {metric_name}, 1M x 256")
     idx.close()
 
 
