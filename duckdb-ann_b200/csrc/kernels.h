@@ -64,7 +64,7 @@ constexpr int kMergeCandidates = 16384;  // most (list, slot) candidates per que
 // Threshold scan of the exact tier: entries of one flagged query's candidate buffer (at least two k), and
 // of all buffers of a query block together (8 bytes each)
 constexpr int kFlaggedCandidates = 4096;
-constexpr int64_t kFlaggedEntries = 4 << 20;
+constexpr int64_t kFlaggedEntries = 16 << 20;
 
 struct FlatPlan {
     int nq_tiles = 0;         // ceil(nq / 128)

@@ -185,6 +185,24 @@ def test_duplicates_by_the_thousand_overflow_the_threshold_scan(pkg, oracle, met
     idx.close()
 
 
+def test_more_flagged_queries_than_candidate_buffers(pkg, oracle):
+    """4,200 queries of one block sit on the near ties; the candidate buffers of a block (16 M entries, 4,096
+    per query at k = 8) serve the first 4,096 flagged queries, the item scan the other 104."""
+    rng = np.random.default_rng(53)
+    d = 64
+    xb, q0 = _near_tie_store(rng, d, 20000, 400, "L2", 1e-6)
+    xq = np.repeat(q0, 4200, 0)
+    xq[::7] += (1e-6 * rng.standard_normal((len(xq[::7]), d))).astype(np.float32)
+    idx = pkg.CudaIndexFlat(d, pkg.METRIC_L2)
+    idx.add(xb)
+    before = pkg.lib().ann_cuda_screen_fallbacks()
+    D, I = idx.search(xq, 8)
+    assert pkg.lib().ann_cuda_screen_fallbacks() == before + 2, "the exact tier did not run"
+    Dref, Iref = oracle.flat_search(xb, xq, 8, oracle.METRIC_L2)
+    assert_topk_matches(oracle, xb, xq, oracle.METRIC_L2, D, I, Dref, Iref, "4,200 flagged queries in one block")
+    idx.close()
+
+
 @pytest.mark.parametrize("entry", ["device", "async"])
 def test_fallback_passes_run_on_the_device_for_the_entries_that_do_not_wait(pkg, oracle, entry):
     """search_device and search_async return before anything has run: the higher tiers are enqueued
